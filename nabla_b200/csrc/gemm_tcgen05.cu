@@ -1,0 +1,502 @@
+// bf16 GEMM for sm_100a on the 5th-generation tensor cores.
+//
+//   D[b] = epilogue( A[b] (M x K)  *  B[b] (K x N) )        fp32 accumulation in TMEM
+//
+// Structure (one persistent CTA per SM, 256 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of A/B tiles into a shared-memory ring
+//   warp 1      MMA issuer:   one thread issues tcgen05.mma (128 x BN x 16) from smem descriptors
+//   warp 2      TMEM allocator (2 accumulator buffers of BN columns each)
+//   warps 4..7  epilogue: tcgen05.ld the accumulator, bias / relu / gelu / d-activation /
+//               residual add, cast and store; overlaps the next tile's MMAs (double-buffered TMEM)
+//
+// Both operands may be K-major (row = M or N index, K contiguous) or MN-major (row = K index,
+// M or N contiguous), so x@W, dY@W^T and X^T@dY all run without materialising a transpose.
+// No TMA multicast is used anywhere: every CTA loads its own tiles.
+//
+// Replaces what the reference obtains from MAX's matmul (nabla/ops/binary.py:197-198) and the
+// matmul + add + relu/gelu composition of nabla/nn/functional/layers.py:30-35.
+#include "sm100_ptx.cuh"
+#include <stdio.h>
+
+namespace nb {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 64;   // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 256;
+constexpr int EPI_THREADS = 128;
+
+enum Epi : int { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_RELU = 2, EPI_BIAS_GELU = 3 };
+enum Aux : int { AUX_NONE = 0, AUX_STORE_PREACT = 1, AUX_MUL_DRELU = 2, AUX_MUL_DGELU = 3, AUX_ADD = 4 };
+
+struct GemmArgs {
+  int M, N, K, batch;
+  void* out;                // bf16 or fp32
+  const void* bias;         // [N] bf16 or fp32, may be null
+  const __nv_bfloat16* aux_in;
+  __nv_bfloat16* aux_out;
+  long long ldc, stride_c;  // elements
+  long long ld_aux, stride_aux;
+  int a_mn, b_mn;           // 1 = MN-major operand
+  int out_fp32, bias_fp32;
+  int epi, aux, accumulate, gelu_tanh;
+  int vec_ok;               // output/aux rows are 16-byte aligned
+  float alpha;              // scale applied to the accumulator before the epilogue
+  int* status;              // device status word (0 = ok)
+};
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
+  static constexpr int B_BYTES = BN * BLOCK_K * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int BIAS_BYTES = BN * 4;
+  static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+  static constexpr int TOTAL = RING_BYTES + BIAS_BYTES + BAR_BYTES + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& b, int& m, int& n) {
+  const int per_batch = num_m * num_n;
+  b = t / per_batch;
+  int r = t - b * per_batch;
+  constexpr int GROUP_M = 8;
+  const int group = GROUP_M * num_n;
+  const int gid = r / group;
+  const int first_m = gid * GROUP_M;
+  const int gsz = min(num_m - first_m, GROUP_M);
+  const int rr = r - gid * group;
+  m = first_m + rr % gsz;
+  n = rr / gsz;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const GemmArgs args) {
+  using L = SmemLayout<BN>;
+  constexpr int STAGES = L::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ring = smem;
+  float* sbias = reinterpret_cast<float*>(smem + L::RING_BYTES);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::RING_BYTES + L::BIAS_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;       // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int num_m = (args.M + BLOCK_M - 1) / BLOCK_M;
+  const int num_n = (args.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n * args.batch;
+  const int num_kb = (args.K + BLOCK_K - 1) / BLOCK_K;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&tmem_full[0], 1);
+    mbar_init(&tmem_full[1], 1);
+    mbar_init(&tmem_empty[0], EPI_THREADS);
+    mbar_init(&tmem_empty[1], EPI_THREADS);
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int b, tm, tn;
+        tile_coords(t, num_m, num_n, b, tm, tn);
+        const int m0 = tm * BLOCK_M, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            ok = false;
+            atomicExch(args.status, NB_ERR_TIMEOUT_PRODUCER);
+            break;
+          }
+          uint8_t* sA = ring + stage * L::STAGE_BYTES;
+          uint8_t* sB = sA + L::A_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+          const int k0 = kb * BLOCK_K;
+          if (!args.a_mn) {
+            tma_load_3d(sA, &tmA, &full_bar[stage], k0, m0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BLOCK_M / 64; ++j)
+              tma_load_3d(sA + j * (BLOCK_K * 128), &tmA, &full_bar[stage], m0 + j * 64, k0, b);
+          }
+          if (!args.b_mn) {
+            tma_load_3d(sB, &tmB, &full_bar[stage], k0, n0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(sB + j * (BLOCK_K * 128), &tmB, &full_bar[stage], n0 + j * 64, k0, b);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(BLOCK_M, BN, args.a_mn, args.b_mn);
+      // Per-operand descriptor constants.
+      const uint32_t a_lbo = args.a_mn ? BLOCK_K * 128 : 16, a_sbo = 1024;
+      const uint32_t b_lbo = args.b_mn ? BLOCK_K * 128 : 16, b_sbo = 1024;
+      // Descriptor start-address step per UMMA_K (in 16-byte units).
+      const uint32_t a_kstep = args.a_mn ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
+      const uint32_t b_kstep = args.b_mn ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1)) {
+          atomicExch(args.status, NB_ERR_TIMEOUT_MMA);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) {
+            atomicExch(args.status, NB_ERR_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(ring + stage * L::STAGE_BYTES);
+          const uint32_t sB = sA + L::A_BYTES;
+          const uint64_t da = make_smem_desc_sw128(sA, a_lbo, a_sbo);
+          const uint64_t db = make_smem_desc_sw128(sB, b_lbo, b_sbo);
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+            umma_f16_ss(tmem_d, da + static_cast<uint64_t>(k * a_kstep), db + static_cast<uint64_t>(k * b_kstep),
+                        idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);   // frees the smem slot when these MMAs retire
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tmem_full[buf]);
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue
+    const int wq = warp & 3;                 // TMEM lane quarter this warp may read
+    const int et = threadIdx.x - 128;        // 0..127
+    bool ok = true;
+    int it = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      int b, tm, tn;
+      tile_coords(t, num_m, num_n, b, tm, tn);
+      const int m0 = tm * BLOCK_M, n0 = tn * BN;
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      // stage the bias slice of this tile
+      named_bar_sync(1, EPI_THREADS);
+      for (int j = et; j < BN; j += EPI_THREADS) {
+        float bv = 0.f;
+        if (args.bias != nullptr && args.epi != EPI_NONE && n0 + j < args.N) {
+          bv = args.bias_fp32 ? reinterpret_cast<const float*>(args.bias)[n0 + j]
+                              : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(args.bias)[n0 + j]);
+        }
+        sbias[j] = bv;
+      }
+      named_bar_sync(1, EPI_THREADS);
+      if (ok && !mbar_wait(&tmem_full[buf], acc_phase)) {
+        atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) continue;   // keep barrier participation uniform, skip the work
+      tc_fence_after();
+      const int row = m0 + wq * 32 + lane;
+      const bool row_ok = row < args.M;
+      const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(wq * 32) << 16);
+      const long long out_off = static_cast<long long>(b) * args.stride_c + static_cast<long long>(row) * args.ldc;
+      const long long aux_off =
+          static_cast<long long>(b) * args.stride_aux + static_cast<long long>(row) * args.ld_aux;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int nb0 = n0 + c * 32;
+        if (nb0 >= args.N) break;   // warp-uniform
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + c * 32, v);
+        tmem_ld_wait();
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * args.alpha + sbias[c * 32 + j];
+        const bool full = (nb0 + 32 <= args.N) && args.vec_ok;
+        // ---- auxiliary output: pre-activation
+        if (args.aux == AUX_STORE_PREACT && row_ok) {
+          __nv_bfloat16* ap = args.aux_out + aux_off + nb0;
+          if (full) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 pk;
+              uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(f[q * 8 + 2 * j], f[q * 8 + 2 * j + 1]);
+                pw[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              reinterpret_cast<uint4*>(ap)[q] = pk;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (nb0 + j < args.N) ap[j] = __float2bfloat16(f[j]);
+          }
+        }
+        // ---- activation
+        if (args.epi == EPI_BIAS_RELU) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = fmaxf(f[j], 0.f);
+        } else if (args.epi == EPI_BIAS_GELU) {
+          if (args.gelu_tanh) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = gelu_tanh(f[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = gelu_erf(f[j]);
+          }
+        }
+        // ---- auxiliary input: d-activation multiply or residual add
+        if (args.aux >= AUX_MUL_DRELU && row_ok) {
+          const __nv_bfloat16* ap = args.aux_in + aux_off + nb0;
+          float a[32];
+          if (full) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 pk = reinterpret_cast<const uint4*>(ap)[q];
+              const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 x = __bfloat1622float2(ph[j]);
+                a[q * 8 + 2 * j] = x.x;
+                a[q * 8 + 2 * j + 1] = x.y;
+              }
+            }
+          } else {
+            for (int j = 0; j < 32; ++j) a[j] = (nb0 + j < args.N) ? __bfloat162float(ap[j]) : 0.f;
+          }
+          if (args.aux == AUX_MUL_DRELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = a[j] > 0.f ? f[j] : 0.f;
+          } else if (args.aux == AUX_MUL_DGELU) {
+            if (args.gelu_tanh) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) f[j] *= dgelu_tanh(a[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) f[j] *= dgelu_erf(a[j]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] += a[j];
+          }
+        }
+        // ---- store
+        if (row_ok) {
+          if (args.out_fp32) {
+            float* op = reinterpret_cast<float*>(args.out) + out_off + nb0;
+            if (full) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                float4 o = make_float4(f[q * 4], f[q * 4 + 1], f[q * 4 + 2], f[q * 4 + 3]);
+                if (args.accumulate) {
+                  float4 old = reinterpret_cast<float4*>(op)[q];
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                reinterpret_cast<float4*>(op)[q] = o;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (nb0 + j < args.N) op[j] = args.accumulate ? op[j] + f[j] : f[j];
+            }
+          } else {
+            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + out_off + nb0;
+            if (full) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 pk;
+                uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+                if (args.accumulate) {
+                  uint4 old = reinterpret_cast<uint4*>(op)[q];
+                  const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    float2 x = __bfloat1622float2(ph[j]);
+                    f[q * 8 + 2 * j] += x.x;
+                    f[q * 8 + 2 * j + 1] += x.y;
+                  }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(f[q * 8 + 2 * j], f[q * 8 + 2 * j + 1]);
+                  pw[j] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                reinterpret_cast<uint4*>(op)[q] = pk;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (nb0 + j < args.N)
+                  op[j] = __float2bfloat16(args.accumulate ? __bfloat162float(op[j]) + f[j] : f[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tmem_empty[buf]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Tensor map over a bf16 operand seen as [batch][rows][cols] with cols contiguous.
+// Box = 64 cols (128 B, SWIZZLE_128B) x box_rows x 1.
+static int make_map(CUtensorMap* map, const void* ptr, long long cols, long long rows, long long batch,
+                    long long ld, long long stride_b, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return -1;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  if (batch == 1 || stride_b == 0) stride_b = rows * ld;
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)stride_b * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(int)r - 100;
+}
+
+static int g_num_sms = 0;
+
+template <int BN>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, int max_ctas,
+                  cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         L::TOTAL);
+    if (e != cudaSuccess) return -2;
+    configured = true;
+  }
+  const int num_m = (a.M + BLOCK_M - 1) / BLOCK_M, num_n = (a.N + BN - 1) / BN;
+  long long tiles = (long long)num_m * num_n * a.batch;
+  int grid = (int)(tiles < max_ctas ? tiles : max_ctas);
+  if (grid < 1) return 0;
+  gemm_bf16_tcgen05_kernel<BN><<<grid, NUM_THREADS, L::TOTAL, stream>>>(ta, tb, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+}  // namespace nb
+
+// C entry point. All leading dimensions / strides are in elements.
+//   A: a_mn == 0 -> [batch][M][K] (K contiguous, row stride lda); a_mn == 1 -> [batch][K][M]
+//   B: b_mn == 0 -> [batch][N][K] (K contiguous, row stride ldb); b_mn == 1 -> [batch][K][N]
+// Requirements: base pointers 16-byte aligned, lda/ldb/strides multiples of 8 elements.
+// Returns 0 on launch success; the device status word reports bounded-wait failures.
+extern "C" int nb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const void* aux_in,
+                            void* aux_out, int M, int N, int K, int batch, long long lda, long long ldb,
+                            long long ldc, long long stride_a, long long stride_b, long long stride_c,
+                            long long ld_aux, long long stride_aux, int a_mn, int b_mn, int out_fp32,
+                            int bias_fp32, int epi, int aux, int accumulate, int gelu_tanh, float alpha,
+                            int block_n, int max_ctas, int* status, void* stream) {
+  using namespace nb;
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
+  if (K <= 0) return -10;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -11;
+  if ((lda & 7) || (ldb & 7) || (batch > 1 && ((stride_a & 7) || (stride_b & 7)))) return -12;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  if (max_ctas <= 0 || max_ctas > g_num_sms) max_ctas = g_num_sms;
+  int bn = block_n;
+  if (bn != 256 && bn != 128 && bn != 64) {
+    // Largest tile that still gives every SM a tile; small problems use narrower tiles.
+    const long long m_tiles = (M + BLOCK_M - 1) / BLOCK_M;
+    bn = 256;
+    if (N <= 64 || m_tiles * ((N + 255) / 256) * batch < g_num_sms / 2) bn = 128;
+    if (N <= 64 || (bn == 128 && m_tiles * ((N + 127) / 128) * batch < g_num_sms / 2)) bn = 64;
+  }
+  CUtensorMap ta, tb;
+  int r;
+  if (!a_mn) r = make_map(&ta, A, K, M, batch, lda, stride_a, BLOCK_M);
+  else       r = make_map(&ta, A, M, K, batch, lda, stride_a, BLOCK_K);
+  if (r) return r;
+  if (!b_mn) r = make_map(&tb, B, K, N, batch, ldb, stride_b, bn);
+  else       r = make_map(&tb, B, N, K, batch, ldb, stride_b, BLOCK_K);
+  if (r) return r;
+  GemmArgs g;
+  g.M = M; g.N = N; g.K = K; g.batch = batch;
+  g.out = C; g.bias = bias;
+  g.aux_in = reinterpret_cast<const __nv_bfloat16*>(aux_in);
+  g.aux_out = reinterpret_cast<__nv_bfloat16*>(aux_out);
+  g.ldc = ldc; g.stride_c = stride_c; g.ld_aux = ld_aux; g.stride_aux = stride_aux;
+  g.a_mn = a_mn; g.b_mn = b_mn; g.out_fp32 = out_fp32; g.bias_fp32 = bias_fp32;
+  g.epi = epi; g.aux = aux; g.accumulate = accumulate; g.gelu_tanh = gelu_tanh;
+  g.alpha = alpha;
+  g.status = status;
+  const int oes = out_fp32 ? 4 : 2;
+  bool vec = ((reinterpret_cast<uintptr_t>(C) & 15) == 0) && ((ldc * oes) % 16 == 0) &&
+             (batch == 1 || (stride_c * oes) % 16 == 0);
+  if (aux != AUX_NONE) {
+    const void* ap = aux == AUX_STORE_PREACT ? aux_out : aux_in;
+    vec = vec && ((reinterpret_cast<uintptr_t>(ap) & 15) == 0) && ((ld_aux * 2) % 16 == 0) &&
+          (batch == 1 || (stride_aux * 2) % 16 == 0);
+  }
+  g.vec_ok = vec ? 1 : 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 256) return launch<256>(ta, tb, g, max_ctas, s);
+  if (bn == 128) return launch<128>(ta, tb, g, max_ctas, s);
+  return launch<64>(ta, tb, g, max_ctas, s);
+}

@@ -1,0 +1,96 @@
+"""ctypes bindings to the hand-written sm_100a libraries in ``nabla_b200/lib``.
+
+The libraries export plain C symbols (see ``nabla_b200/csrc``). Tensors stay torch tensors;
+the wrappers pass raw device pointers and the current CUDA stream. On a machine with a GPU a
+missing library is an error (no silent fallback): ``require()`` raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+import torch
+
+_LIB_DIR = Path(__file__).resolve().parent.parent / "lib"
+_libs: dict[str, ctypes.CDLL] = {}
+_status: dict[int, torch.Tensor] = {}
+
+
+class NativeLibraryMissing(RuntimeError):
+    pass
+
+
+def lib_path(name: str) -> Path:
+    return _LIB_DIR / name
+
+
+def available(name: str) -> bool:
+    return lib_path(name).exists()
+
+
+def load(name: str) -> ctypes.CDLL:
+    """Load (once) and return the named shared library; build it first if it is absent."""
+    lib = _libs.get(name)
+    if lib is not None:
+        return lib
+    p = lib_path(name)
+    if not p.exists():
+        try:
+            from ..csrc.build import build_all
+
+            build_all()
+        except Exception as e:  # pragma: no cover - build environment problems
+            raise NativeLibraryMissing(f"{name} is not built and building failed: {e}") from e
+    if not p.exists():
+        raise NativeLibraryMissing(f"{p} not found; run `python -m nabla_b200.csrc.build`")
+    lib = ctypes.CDLL(str(p))
+    _libs[name] = lib
+    return lib
+
+
+def use_native(t: torch.Tensor) -> bool:
+    """True when ``t`` lives on a CUDA device and native kernels are not disabled."""
+    return t.is_cuda and os.environ.get("NABLA_B200_DISABLE_NATIVE", "0") != "1"
+
+
+def stream_ptr() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 status word that kernels with bounded waits write on failure."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    s = _status.get(idx)
+    if s is None:
+        s = torch.zeros(4, dtype=torch.int32, device=device)
+        _status[idx] = s
+    return s
+
+
+class KernelStatusError(RuntimeError):
+    """A device-side bounded wait ran out (the kernel returned an error status)."""
+
+
+_STATUS_NAMES = {1: "TMA producer wait timed out", 2: "MMA issuer wait timed out",
+                 3: "epilogue wait timed out", 4: "peer flag wait timed out"}
+
+
+def check_status(device: torch.device | None = None) -> None:
+    """Synchronise and raise if any kernel on ``device`` reported a bounded-wait failure."""
+    devs = list(_status) if device is None else [device.index or 0]
+    for idx in devs:
+        s = _status.get(idx)
+        if s is None:
+            continue
+        code = int(s[0].item())
+        if code != 0:
+            s.zero_()
+            raise KernelStatusError(f"cuda:{idx}: kernel status {code}: {_STATUS_NAMES.get(code, 'unknown')}")
+
+
+from .gemm import gemm_bf16, gemm_supported  # noqa: E402,F401
