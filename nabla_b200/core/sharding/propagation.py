@@ -1,0 +1,215 @@
+"""Factor-based sharding propagation (reference: nabla/core/sharding/propagation.py:42-324).
+
+Every op describes its dimensions with einsum-like *factors*
+(``"... m k, ... k n -> ... m n"``). Shardings flow from input dims to factors and from
+factors to output dims; a factor that appears in inputs but in no output is *contracting*,
+and a sharded contracting factor leaves the output with a pending sum over those mesh axes
+(``partial_sum_axes``). Conflicts are resolved first-input-wins, and an axis is claimed by
+the first output dimension that asks for it.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence
+
+from .spec import DeviceMesh, DimSpec, ShardingSpec
+
+Mapping = dict[int, list[str]]
+
+
+@dataclass
+class OpShardingRule:
+    input_mappings: list[Mapping]
+    output_mappings: list[Mapping]
+    factor_sizes: dict[str, int] = field(default_factory=dict)
+
+    def get_all_factors(self) -> set[str]:
+        out: set[str] = set()
+        for m in self.input_mappings + self.output_mappings:
+            for fs in m.values():
+                out.update(fs)
+        return out
+
+    def get_contracting_factors(self) -> set[str]:
+        ins: set[str] = set()
+        outs: set[str] = set()
+        for m in self.input_mappings:
+            for fs in m.values():
+                ins.update(fs)
+        for m in self.output_mappings:
+            for fs in m.values():
+                outs.update(fs)
+        return ins - outs
+
+    def to_einsum_notation(self) -> str:
+        def side(ms):
+            return ", ".join(" ".join("(" + " ".join(fs) + ")" if len(fs) != 1 else fs[0]
+                                      for _, fs in sorted(m.items())) for m in ms)
+        return f"{side(self.input_mappings)} -> {side(self.output_mappings)}"
+
+
+class OpShardingRuleTemplate:
+    """A rule written with ``...`` for leading batch dims, instantiated against shapes."""
+
+    def __init__(self, inputs: list[list], outputs: list[list]):
+        self.inputs = inputs      # each: list of tokens; token = str | tuple[str,...] | Ellipsis
+        self.outputs = outputs
+
+    @staticmethod
+    def parse(notation: str) -> "OpShardingRuleTemplate":
+        def toks(s: str) -> list:
+            out: list = []
+            i, s = 0, s.strip()
+            parts = s.replace("(", " ( ").replace(")", " ) ").split()
+            group = None
+            for p in parts:
+                if p == "(":
+                    group = []
+                elif p == ")":
+                    out.append(tuple(group))
+                    group = None
+                elif group is not None:
+                    group.append(p)
+                elif p == "...":
+                    out.append(Ellipsis)
+                else:
+                    out.append(p)
+            return out
+        lhs, rhs = notation.split("->")
+        return OpShardingRuleTemplate([toks(x) for x in lhs.split(",")], [toks(x) for x in rhs.split(",")])
+
+    def instantiate(self, input_shapes: Sequence[Sequence[int]],
+                    output_shapes: Sequence[Sequence[int]] | None = None) -> OpShardingRule:
+        sizes: dict[str, int] = {}
+
+        def expand(tokens: list, shape: Sequence[int] | None) -> Mapping:
+            n_named = sum(1 for t in tokens if t is not Ellipsis)
+            rank = len(shape) if shape is not None else n_named
+            n_batch = max(0, rank - n_named) if Ellipsis in tokens else 0
+            mapping: Mapping = {}
+            d = 0
+            for t in tokens:
+                if t is Ellipsis:
+                    # batch factors are right-aligned across operands (numpy broadcasting)
+                    for b in range(n_batch):
+                        mapping[d] = [f"_b{n_batch - 1 - b}"]
+                        d += 1
+                else:
+                    fs = list(t) if isinstance(t, tuple) else [t]
+                    mapping[d] = fs
+                    if shape is not None and d < len(shape) and len(fs) == 1:
+                        sizes.setdefault(fs[0], int(shape[d]))
+                    d += 1
+            return mapping
+
+        ins = [expand(t, input_shapes[i] if i < len(input_shapes) else None) for i, t in enumerate(self.inputs)]
+        outs = [expand(t, output_shapes[i] if output_shapes and i < len(output_shapes) else None)
+                for i, t in enumerate(self.outputs)]
+        return OpShardingRule(ins, outs, sizes)
+
+
+def elementwise_rule(input_shapes: Sequence[Sequence[int]], output_rank: int) -> OpShardingRule:
+    """Right-aligned broadcasting rule: dim j (from the right) of every operand shares factor
+    ``d<j>`` unless the operand's extent there is 1 while the output's is not."""
+    out_map: Mapping = {i: [f"d{output_rank - 1 - i}"] for i in range(output_rank)}
+    out_extent = [1] * output_rank
+    for s in input_shapes:
+        for j in range(len(s)):
+            k = output_rank - len(s) + j
+            if k >= 0:
+                out_extent[k] = max(out_extent[k], int(s[j]))
+    ins = []
+    for s in input_shapes:
+        m: Mapping = {}
+        for j in range(len(s)):
+            k = output_rank - len(s) + j
+            if k < 0:
+                continue
+            if int(s[j]) == 1 and out_extent[k] != 1:
+                m[j] = [f"bcast{len(ins)}_{j}"]   # size-1 dim: its own factor (never sharded)
+            else:
+                m[j] = [f"d{output_rank - 1 - k}"]
+        ins.append(m)
+    return OpShardingRule(ins, [out_map])
+
+
+def infer_from_rule(rule: OpShardingRule, input_specs: Sequence[ShardingSpec | None], mesh: DeviceMesh,
+                    output_index: int = 0) -> tuple[ShardingSpec, set[str]]:
+    """Output sharding and the set of mesh axes that became partial by contraction."""
+    factor_axes: dict[str, list[str]] = {}
+    for t_idx, spec in enumerate(input_specs):
+        if spec is None or t_idx >= len(rule.input_mappings):
+            continue
+        for dim_idx, factors in rule.input_mappings[t_idx].items():
+            if dim_idx >= len(spec.dim_specs):
+                continue
+            axes = spec.dim_specs[dim_idx].axes
+            if not axes:
+                continue
+            # a dim made of several factors gives its axes to the first (major) factor
+            f = factors[0]
+            if f not in factor_axes:
+                factor_axes[f] = list(axes)
+    contracting = rule.get_contracting_factors()
+    out_map = rule.output_mappings[output_index] if rule.output_mappings else {}
+    rank = max(out_map.keys(), default=-1) + 1
+    used: set[str] = set()
+    dims: list[DimSpec] = []
+    for d in range(rank):
+        axes: list[str] = []
+        for f in out_map.get(d, []):
+            for a in factor_axes.get(f, []):
+                if a not in used:
+                    axes.append(a)
+                    used.add(a)
+        dims.append(DimSpec(axes))
+    partial: set[str] = set()
+    for f in contracting:
+        for a in factor_axes.get(f, []):
+            if a not in used:
+                partial.add(a)
+    return ShardingSpec(mesh, dims, partial_sum_axes=set(partial)), partial
+
+
+def required_input_specs(rule: OpShardingRule, input_specs: Sequence[ShardingSpec | None], mesh: DeviceMesh,
+                         input_ranks: Sequence[int]) -> list[ShardingSpec]:
+    """Input layouts consistent with the factor assignment chosen by ``infer_from_rule``:
+    every input dim takes the axes of its factor (first-wins), so operands that disagree are
+    resharded to agree before the per-shard kernel runs."""
+    factor_axes: dict[str, list[str]] = {}
+    for t_idx, spec in enumerate(input_specs):
+        if spec is None or t_idx >= len(rule.input_mappings):
+            continue
+        for dim_idx, factors in rule.input_mappings[t_idx].items():
+            if dim_idx < len(spec.dim_specs) and spec.dim_specs[dim_idx].axes and factors[0] not in factor_axes:
+                factor_axes[factors[0]] = list(spec.dim_specs[dim_idx].axes)
+    out = []
+    for t_idx, rank in enumerate(input_ranks):
+        spec = input_specs[t_idx] if t_idx < len(input_specs) else None
+        mapping = rule.input_mappings[t_idx] if t_idx < len(rule.input_mappings) else {}
+        used: set[str] = set()
+        dims = []
+        for d in range(rank):
+            fs = mapping.get(d, [])
+            axes = []
+            if fs and not fs[0].startswith("bcast"):
+                for a in factor_axes.get(fs[0], []):
+                    if a not in used:
+                        axes.append(a)
+                        used.add(a)
+            dims.append(DimSpec(axes))
+        partial = set(spec.partial_sum_axes) if spec is not None else set()
+        partial -= used
+        out.append(ShardingSpec(mesh, dims, partial_sum_axes=partial))
+    return out
+
+
+def propagate_sharding(rule: OpShardingRule, input_specs, output_specs, *args, **kwargs) -> bool:
+    """Legacy entry point kept for API compatibility: fills ``output_specs[0]`` in place."""
+    if not input_specs:
+        return False
+    spec, _ = infer_from_rule(rule, input_specs, input_specs[0].mesh)
+    if output_specs:
+        output_specs[0].dim_specs = spec.dim_specs
+        output_specs[0].partial_sum_axes = spec.partial_sum_axes
+    return True

@@ -1,0 +1,154 @@
+"""SPMD glue between ops and the sharding model (reference: nabla/core/sharding/spmd.py:18-370,
+nabla/ops/utils.py:446-508).
+
+``prepare`` is called by ``Operation.__call__`` when any operand lives on a mesh. It decides,
+from shapes only, (a) which pending partial sums must be reduced *before* the op because the
+op is not linear in that operand, (b) how operands must be laid out so that every shard can
+run the kernel locally, (c) the output layout including new pending sums from sharded
+contractions, and (d) reductions that must happen right after the op (max/min reductions).
+"""
+from __future__ import annotations
+
+from typing import Any, Callable
+
+from ..common import pytree
+from .propagation import infer_from_rule, required_input_specs
+from .spec import DeviceMesh, DimSpec, ShardingSpec
+
+
+def get_mesh_from_args(args) -> DeviceMesh | None:
+    for t in pytree.tensor_leaves(args):
+        if t._impl.sharding is not None:
+            return t._impl.sharding.mesh
+    return None
+
+
+def replicated_spec(mesh: DeviceMesh, rank: int) -> ShardingSpec:
+    return ShardingSpec(mesh, [DimSpec([]) for _ in range(rank)])
+
+
+create_replicated_spec = replicated_spec
+
+
+def _fit_rank(spec: ShardingSpec, rank: int) -> ShardingSpec:
+    dims = [d.clone() for d in spec.dim_specs[:rank]]
+    while len(dims) < rank:
+        dims.append(DimSpec([]))
+    return ShardingSpec(spec.mesh, dims, set(spec.replicated_axes), set(spec.partial_sum_axes))
+
+
+def prepare(op, args: tuple, kwargs: dict, mesh: DeviceMesh):
+    """Returns ``(new_args, out_specs_fn, reduce_axes)``; ``out_specs_fn(out_shapes)`` gives one
+    ``ShardingSpec`` per output."""
+    from ..tensor.api import Tensor
+
+    custom = getattr(op, "infer_sharding_spec", None)
+    if custom is not None:
+        return custom(args, mesh, kwargs)
+
+    leaves, treedef = pytree.tree_flatten(args)
+    t_idx = [i for i, a in enumerate(leaves) if isinstance(a, Tensor)]
+    tensors = [leaves[i] for i in t_idx]
+    if not tensors:
+        return args, (lambda shapes: [replicated_spec(mesh, len(s)) for s in shapes]), set()
+    shapes = [t._impl._shape for t in tensors]
+    specs = [t._impl.sharding.clone() if t._impl.sharding is not None else replicated_spec(mesh, len(s))
+             for t, s in zip(tensors, shapes)]
+
+    # (a) partial sums the op cannot carry are reduced on the inputs
+    incoming: set[str] = set()
+    for s in specs:
+        incoming |= s.partial_sum_axes
+    keep = op.partial_passthrough_axes(specs, kwargs) & incoming if incoming else set()
+    must_reduce = incoming - keep
+    if must_reduce:
+        from ...ops.communication import all_reduce
+
+        for j, t in enumerate(tensors):
+            over = specs[j].partial_sum_axes & must_reduce
+            if over:
+                tensors[j] = all_reduce(t, reduce_axes=over)
+                specs[j] = tensors[j]._impl.sharding.clone()
+
+    # (b) operand layouts that agree on every factor
+    try:
+        rule = op.sharding_rule(list(shapes), None, **kwargs)
+    except NotImplementedError:
+        rule = None
+    if rule is None:
+        want = [ShardingSpec(mesh, [DimSpec([]) for _ in s], partial_sum_axes=set(sp.partial_sum_axes))
+                for s, sp in zip(shapes, specs)]
+    else:
+        want = required_input_specs(rule, specs, mesh, [len(s) for s in shapes])
+    from ...ops.communication import reshard_to_spec
+
+    for j, t in enumerate(tensors):
+        cur = specs[j]
+        if any(a.axes != b.axes for a, b in zip(cur.dim_specs, want[j].dim_specs)) or t._impl.sharding is None:
+            tensors[j] = reshard_to_spec(t, want[j])
+            specs[j] = tensors[j]._impl.sharding.clone()
+
+    for i, t in zip(t_idx, tensors):
+        leaves[i] = t
+    new_args = pytree.tree_unflatten(treedef, leaves)
+
+    # (c) + (d) output layouts
+    non_sum = op.collective_reduce_type != "sum"
+    reduce_axes: set[str] = set()
+    contraction: set[str] = set()
+    if rule is not None:
+        _, contraction = infer_from_rule(rule, specs, mesh)
+        if non_sum:
+            reduce_axes = set(contraction)
+
+    def out_specs_fn(out_shapes) -> list[ShardingSpec]:
+        res = []
+        for i, shp in enumerate(out_shapes):
+            if rule is None or i >= max(1, len(rule.output_mappings)):
+                spec = replicated_spec(mesh, len(shp))
+                spec.partial_sum_axes = set(keep)
+            else:
+                spec, contr = infer_from_rule(rule, specs, mesh, output_index=i)
+                spec = _fit_rank(spec, len(shp))
+                # never shard a dim of extent 1 or one the axes do not cover sensibly
+                for d, ds in enumerate(spec.dim_specs):
+                    if ds.axes and shp[d] <= 1:
+                        ds.axes = []
+                used = spec.used_axes()
+                spec.partial_sum_axes = {a for a in (set(contr) | set(keep)) if a not in used}
+            res.append(spec)
+        return res
+
+    return new_args, out_specs_fn, reduce_axes
+
+
+def ensure_specs(args, mesh: DeviceMesh):
+    """Give every unsharded tensor argument a replicated spec on ``mesh`` (by resharding)."""
+    from ...ops.communication import reshard_to_spec
+
+    def f(x):
+        if pytree.is_tensor(x) and x._impl.sharding is None:
+            return reshard_to_spec(x, replicated_spec(mesh, len(x._impl._shape)))
+        return x
+
+    return pytree.tree_map(f, args)
+
+
+def infer_output_sharding(op, args, mesh, kwargs=None):
+    """Reference-shaped entry point: ``(output_spec, input_specs, reduce_axes)`` for the
+    first output, without performing any data movement."""
+    if mesh is None:
+        return None, [], set()
+    tensors = pytree.tensor_leaves(args)
+    shapes = [t._impl._shape for t in tensors]
+    specs = [t._impl.sharding.clone() if t._impl.sharding is not None else replicated_spec(mesh, len(s))
+             for t, s in zip(tensors, shapes)]
+    rule = op.sharding_rule(list(shapes), None, **(kwargs or {}))
+    incoming: set[str] = set()
+    for s in specs:
+        incoming |= s.partial_sum_axes
+    keep = op.partial_passthrough_axes(specs, kwargs) & incoming
+    out, contr = infer_from_rule(rule, specs, mesh)
+    used = out.used_axes()
+    out.partial_sum_axes = {a for a in (contr | keep) if a not in used}
+    return out, specs, incoming - keep

@@ -1,0 +1,68 @@
+"""Comparison and logical ops; results are bool (reference: nabla/ops/comparison.py:27-192).
+None of them is differentiable: VJP/JVP give zeros."""
+from __future__ import annotations
+
+import torch
+
+from ..core.tensor.api import Tensor
+from .base import BinaryOperation, UnaryOperation
+
+
+class _Cmp(BinaryOperation):
+    fn = None
+
+    def torch_fn(self, a, b):
+        return type(self).fn(a, b)
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        return (None, None)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return None
+
+
+class _Logical(_Cmp):
+    def torch_fn(self, a, b):
+        return type(self).fn(a.bool(), b.bool())
+
+
+def _mk(name, fn, base=_Cmp):
+    cls = type(name, (base,), {"fn": staticmethod(fn)})
+    return cls()
+
+
+_equal = _mk("EqualOp", torch.eq)
+_not_equal = _mk("NotEqualOp", torch.ne)
+_greater = _mk("GreaterOp", torch.gt)
+_greater_equal = _mk("GreaterEqualOp", torch.ge)
+_less = _mk("LessOp", torch.lt)
+_less_equal = _mk("LessEqualOp", torch.le)
+_logical_and = _mk("LogicalAndOp", torch.logical_and, _Logical)
+_logical_or = _mk("LogicalOrOp", torch.logical_or, _Logical)
+_logical_xor = _mk("LogicalXorOp", torch.logical_xor, _Logical)
+
+
+class LogicalNotOp(UnaryOperation):
+    def torch_fn(self, x):
+        return torch.logical_not(x)
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        return (None,)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return None
+
+
+_logical_not = LogicalNotOp()
+
+
+def equal(a, b) -> Tensor: return _equal(a, b)
+def not_equal(a, b) -> Tensor: return _not_equal(a, b)
+def greater(a, b) -> Tensor: return _greater(a, b)
+def greater_equal(a, b) -> Tensor: return _greater_equal(a, b)
+def less(a, b) -> Tensor: return _less(a, b)
+def less_equal(a, b) -> Tensor: return _less_equal(a, b)
+def logical_and(a, b) -> Tensor: return _logical_and(a, b)
+def logical_or(a, b) -> Tensor: return _logical_or(a, b)
+def logical_xor(a, b) -> Tensor: return _logical_xor(a, b)
+def logical_not(a) -> Tensor: return _logical_not(a)

@@ -1,0 +1,144 @@
+"""Ops with several outputs (reference: nabla/ops/multi_output.py:52-546): split (tuple),
+chunk (list, uneven tail), unbind (tuple), minmax (dict). The split axis must be whole on
+every shard, so a sharded split axis is gathered first."""
+from __future__ import annotations
+
+import torch
+
+from ..core.sharding.propagation import OpShardingRule
+from ..core.tensor.api import Tensor
+from .base import AxisOp, ensure_tensor
+
+
+class _SplitBase(AxisOp):
+    partial_policy = "any"
+
+    def _rule(self, rank, axis, n_out, drop=False):
+        ins = {i: [f"d{i}"] if i != axis else [f"bcast_sp{i}"] for i in range(rank)}
+        outs = []
+        for k in range(n_out):
+            m, j = {}, 0
+            for i in range(rank):
+                if i == axis:
+                    if drop:
+                        continue
+                    m[j] = [f"piece{k}"]
+                else:
+                    m[j] = [f"d{i}"]
+                j += 1
+            outs.append(m)
+        return OpShardingRule([ins], outs)
+
+
+class SplitOp(_SplitBase):
+    def kernel(self, x, *, sizes, axis: int):
+        return tuple(torch.split(x, list(sizes), dim=axis))
+
+    def sharding_rule(self, input_shapes, output_shapes, *, sizes, axis: int, **kw):
+        return self._rule(len(input_shapes[0]), axis, len(sizes))
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        from .creation import zeros_like
+        from .view import concatenate
+
+        cots = [c if c is not None else zeros_like(o) for c, o in zip(cot, outputs)]
+        return (concatenate(cots, axis=kwargs["axis"]),)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return _split(tangents[0], **kwargs)
+
+
+class UnbindOp(_SplitBase):
+    def kernel(self, x, *, axis: int):
+        return tuple(torch.unbind(x, dim=axis))
+
+    def sharding_rule(self, input_shapes, output_shapes, *, axis: int, **kw):
+        return self._rule(len(input_shapes[0]), axis, input_shapes[0][axis], drop=True)
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        from .creation import zeros_like
+        from .view import stack
+
+        cots = [c if c is not None else zeros_like(o) for c, o in zip(cot, outputs)]
+        return (stack(cots, axis=kwargs["axis"]),)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return _unbind(tangents[0], **kwargs)
+
+
+class MinMaxOp(AxisOp):
+    collective_reduce_type = "max"
+
+    def kernel(self, x, *, axis: int, keepdims: bool = False):
+        return {"min": torch.amin(x, dim=axis, keepdim=keepdims), "max": torch.amax(x, dim=axis, keepdim=keepdims)}
+
+    def sharding_rule(self, input_shapes, output_shapes, *, axis: int, keepdims: bool = False, **kw):
+        rank = len(input_shapes[0])
+        ins = {i: [f"d{i}"] if i != axis else [f"bcast_mm{i}"] for i in range(rank)}
+        m, j = {}, 0
+        for i in range(rank):
+            if i == axis and not keepdims:
+                continue
+            m[j] = [f"d{i}"] if i != axis else ["one"]
+            j += 1
+        return OpShardingRule([ins], [dict(m), dict(m)])
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        from .reduction import _reduce_max, _reduce_min
+
+        x = primals[0]
+        g = None
+        for key, op in (("max", _reduce_max), ("min", _reduce_min)):
+            c = cot.get(key) if isinstance(cot, dict) else None
+            if c is None:
+                continue
+            (gi,) = op.vjp_rule((x,), c, outputs[key], kwargs)
+            g = gi if g is None else g + gi
+        return (g,)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        from .reduction import _reduce_max, _reduce_min
+
+        return {"max": _reduce_max.jvp_rule(primals, tangents, outputs["max"], kwargs),
+                "min": _reduce_min.jvp_rule(primals, tangents, outputs["min"], kwargs)}
+
+
+_split, _unbind, _minmax = SplitOp(), UnbindOp(), MinMaxOp()
+
+
+def split(x, num_or_sizes, axis: int = 0) -> tuple[Tensor, ...]:
+    """Split into equal parts (int) or the given sizes (list)."""
+    x = ensure_tensor(x)
+    rank = len(x._impl.global_shape)
+    n = x._impl.global_shape[axis + rank if axis < 0 else axis]
+    if isinstance(num_or_sizes, int):
+        if n % num_or_sizes != 0:
+            raise ValueError(f"axis of size {n} is not divisible into {num_or_sizes} parts")
+        sizes = (n // num_or_sizes,) * num_or_sizes
+    else:
+        sizes = tuple(int(s) for s in num_or_sizes)
+        if sum(sizes) != n:
+            raise ValueError(f"split sizes {sizes} do not sum to {n}")
+    return tuple(_split(x, sizes=sizes, axis=int(axis)))
+
+
+def chunk(x, chunks: int, axis: int = 0) -> list[Tensor]:
+    """Like torch.chunk: ceil-div pieces, the last may be smaller."""
+    x = ensure_tensor(x)
+    rank = len(x._impl.global_shape)
+    n = x._impl.global_shape[axis + rank if axis < 0 else axis]
+    size = -(-n // chunks)
+    sizes = []
+    left = n
+    while left > 0:
+        sizes.append(min(size, left))
+        left -= sizes[-1]
+    return list(_split(x, sizes=tuple(sizes), axis=int(axis)))
+
+
+def unbind(x, axis: int = 0) -> tuple[Tensor, ...]:
+    return tuple(_unbind(ensure_tensor(x), axis=int(axis)))
+
+
+def minmax(x, axis: int = -1, keepdims: bool = False) -> dict[str, Tensor]:
+    return _minmax(ensure_tensor(x), axis=int(axis), keepdims=keepdims)

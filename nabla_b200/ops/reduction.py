@@ -1,0 +1,242 @@
+"""Reductions (reference: nabla/ops/reduction.py:67-955).
+
+Single-axis primitives with ``keepdims``; multi-axis and ``axis=None`` forms chain them.
+Reducing over a sharded dimension leaves a pending cross-device reduction: sum stays deferred
+(``partial_sum_axes``), max/min are resolved immediately with a max/min collective.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..core.tensor.api import Tensor
+from ..types import DType
+from .base import AxisOp, ReduceOperation, ensure_tensor
+
+
+class ReduceSumOp(ReduceOperation):
+    def torch_reduce(self, x, axis, keepdims):
+        if x.dtype == torch.bool:
+            x = x.to(torch.int64)
+        return torch.sum(x, dim=axis, keepdim=keepdims)
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        from .view import broadcast_to, unsqueeze
+
+        x = primals[0]
+        if not kwargs.get("keepdims", False):
+            cot = unsqueeze(cot, axis=kwargs["axis"])
+        return (broadcast_to(cot, tuple(x._impl.global_shape)),)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return _reduce_sum(tangents[0], **kwargs)
+
+
+class _ReduceExt(ReduceOperation):
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        from .comparison import equal
+        from .unary import cast
+        from .view import broadcast_to, unsqueeze
+
+        x = primals[0]
+        y = outputs
+        if not kwargs.get("keepdims", False):
+            cot = unsqueeze(cot, axis=kwargs["axis"])
+            y = unsqueeze(y, axis=kwargs["axis"])
+        shape = tuple(x._impl.global_shape)
+        mask = cast(equal(x, broadcast_to(y, shape)), x.dtype)
+        count = _reduce_sum(mask, axis=kwargs["axis"], keepdims=True)
+        return (broadcast_to(cot, shape) * mask / count,)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        from .comparison import equal
+        from .unary import cast
+        from .view import broadcast_to, unsqueeze
+
+        x = primals[0]
+        y = outputs if kwargs.get("keepdims", False) else unsqueeze(outputs, axis=kwargs["axis"])
+        mask = cast(equal(x, broadcast_to(y, tuple(x._impl.global_shape))), x.dtype)
+        count = _reduce_sum(mask, axis=kwargs["axis"], keepdims=True)
+        return _reduce_sum(tangents[0] * mask / count, **kwargs)
+
+
+class ReduceMaxOp(_ReduceExt):
+    collective_reduce_type = "max"
+
+    def torch_reduce(self, x, axis, keepdims):
+        return torch.amax(x, dim=axis, keepdim=keepdims)
+
+
+class ReduceMinOp(_ReduceExt):
+    collective_reduce_type = "min"
+
+    def torch_reduce(self, x, axis, keepdims):
+        return torch.amin(x, dim=axis, keepdim=keepdims)
+
+
+class _ArgOp(AxisOp):
+    fn = None
+
+    def kernel(self, x, *, axis: int, keepdims: bool = False):
+        return type(self).fn(x, dim=axis, keepdim=keepdims)
+
+    def sharding_rule(self, input_shapes, output_shapes, *, axis: int, keepdims: bool = False, **kw):
+        # the searched axis must be whole on every shard: give it a factor nobody shards
+        from ..core.sharding.propagation import OpShardingRule
+
+        rank = len(input_shapes[0])
+        ins = {i: [f"d{i}"] if i != axis else [f"bcast_arg{i}"] for i in range(rank)}
+        outs, j = {}, 0
+        for i in range(rank):
+            if i == axis and not keepdims:
+                continue
+            outs[j] = [f"d{i}"] if i != axis else [f"one{i}"]
+            j += 1
+        return OpShardingRule([ins], [outs])
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        return (None,)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return None
+
+
+class ArgmaxOp(_ArgOp):
+    fn = staticmethod(torch.argmax)
+
+
+class ArgminOp(_ArgOp):
+    fn = staticmethod(torch.argmin)
+
+
+class CumsumOp(AxisOp):
+    def kernel(self, x, *, axis: int, exclusive: bool = False, reverse: bool = False):
+        if reverse:
+            x = torch.flip(x, dims=(axis,))
+        y = torch.cumsum(x, dim=axis)
+        if exclusive:
+            y = y - x
+        if reverse:
+            y = torch.flip(y, dims=(axis,))
+        return y
+
+    def sharding_rule(self, input_shapes, output_shapes, *, axis: int, **kw):
+        from ..core.sharding.propagation import OpShardingRule
+
+        rank = len(input_shapes[0])
+        m = {i: [f"d{i}"] if i != axis else [f"bcast_scan{i}"] for i in range(rank)}
+        return OpShardingRule([dict(m)], [dict(m)])
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        kw = dict(kwargs)
+        kw["reverse"] = not kwargs.get("reverse", False)
+        return (_cumsum(cot, **kw),)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return _cumsum(tangents[0], **kwargs)
+
+
+_reduce_sum, _reduce_max, _reduce_min = ReduceSumOp(), ReduceMaxOp(), ReduceMinOp()
+_argmax, _argmin, _cumsum = ArgmaxOp(), ArgminOp(), CumsumOp()
+
+
+def _axes(x: Tensor, axis) -> list[int]:
+    rank = len(x._impl.global_shape)
+    if axis is None:
+        return list(range(rank))
+    if isinstance(axis, (tuple, list)):
+        ax = [int(a) + rank if int(a) < 0 else int(a) for a in axis]
+    else:
+        ax = [int(axis) + rank if int(axis) < 0 else int(axis)]
+    for a in ax:
+        if not 0 <= a < max(rank, 1):
+            raise ValueError(f"axis {axis} out of range for rank {rank}")
+    return sorted(set(ax))
+
+
+def _chain(op, x: Tensor, axis, keepdims: bool) -> Tensor:
+    x = ensure_tensor(x)
+    if len(x._impl.global_shape) == 0:
+        return x
+    axes = _axes(x, axis)
+    # reduce from the last axis so earlier indices stay valid when dims are dropped
+    for a in reversed(axes):
+        x = op(x, axis=a, keepdims=keepdims)
+    return x
+
+
+def reduce_sum(x, *, axis=None, keepdims: bool = False) -> Tensor:
+    return _chain(_reduce_sum, x, axis, keepdims)
+
+
+def reduce_max(x, *, axis=None, keepdims: bool = False) -> Tensor:
+    return _chain(_reduce_max, x, axis, keepdims)
+
+
+def reduce_min(x, *, axis=None, keepdims: bool = False) -> Tensor:
+    return _chain(_reduce_min, x, axis, keepdims)
+
+
+def mean(x, *, axis=None, keepdims: bool = False) -> Tensor:
+    x = ensure_tensor(x)
+    axes = _axes(x, axis)
+    n = 1
+    for a in axes:
+        n *= x._impl.global_shape[a]
+    s = reduce_sum(x, axis=axis, keepdims=keepdims)
+    return s * (1.0 / max(n, 1))
+
+
+def argmax(x, axis: int = -1, keepdims: bool = False) -> Tensor:
+    return _argmax(ensure_tensor(x), axis=axis, keepdims=keepdims)
+
+
+def argmin(x, axis: int = -1, keepdims: bool = False) -> Tensor:
+    return _argmin(ensure_tensor(x), axis=axis, keepdims=keepdims)
+
+
+def cumsum(x, axis: int = -1, exclusive: bool = False, reverse: bool = False) -> Tensor:
+    return _cumsum(ensure_tensor(x), axis=axis, exclusive=exclusive, reverse=reverse)
+
+
+# ---- physical variants: axes index the physical shape (batch dims included); used by vmap
+class _PhysMixin:
+    def adapt_kwargs(self, args, kwargs, batch_dims):
+        out = dict(kwargs)
+        t = args[0]
+        rank = len(t._impl._shape)
+        a = int(out["axis"])
+        out["axis"] = a + rank if a < 0 else a
+        return out
+
+    def output_batch_dims(self, batch_dims, kwargs):
+        if kwargs["axis"] < batch_dims and not kwargs.get("keepdims", False):
+            return batch_dims - 1
+        return batch_dims
+
+
+class ReduceSumPhysicalOp(_PhysMixin, ReduceSumOp):
+    _name = "reduce_sum_physical"
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        from .view.axes import unsqueeze_physical
+        from .view.shape import broadcast_to_physical
+
+        x = primals[0]
+        if not kwargs.get("keepdims", False):
+            cot = unsqueeze_physical(cot, axis=kwargs["axis"])
+        return (broadcast_to_physical(cot, tuple(x._impl._shape)),)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return reduce_sum_physical(tangents[0], **kwargs)
+
+
+_reduce_sum_physical = ReduceSumPhysicalOp()
+
+
+def reduce_sum_physical(x, axis: int, keepdims: bool = False) -> Tensor:
+    return _reduce_sum_physical(x, axis=axis, keepdims=keepdims)
+
+
+def mean_physical(x, axis: int, keepdims: bool = False) -> Tensor:
+    n = x._impl._shape[axis]
+    return reduce_sum_physical(x, axis=axis, keepdims=keepdims) * (1.0 / max(n, 1))

@@ -1,0 +1,3 @@
+"""Multi-GPU runtime: process-group setup, collective backend, symmetric memory and the fused
+compute+collective kernels."""
+from .launch import init_distributed, is_distributed, local_rank, rank, world_size  # noqa: F401
