@@ -111,7 +111,7 @@ def _is_bias_add(m: OpNode, mm_out: TensorImpl) -> bool:
     return len(shp) >= 1 and shp[-1] == n and all(d == 1 for d in shp[:-1]) and other.dtype is mm_out.dtype
 
 
-def run_fused(kind: str, group: list[OpNode]) -> None:
+def run_fused(kind: str, group: list[OpNode], keep_graph: bool = False) -> None:
     from .engine import store_outputs
 
     if kind == "linear_epilogue":
@@ -128,6 +128,11 @@ def run_fused(kind: str, group: list[OpNode]) -> None:
         a2 = a.reshape(-1, a.shape[-1])
         out = gemm_bf16(a2, b, bias=bias, epilogue=epi, gelu_tanh=tanh).reshape(*a.shape[:-1], b.shape[-1])
         last = group[-1]
-        store_outputs(last, [[out]])
+        if keep_graph:
+            o = last.outputs()[0]
+            if o is not None:
+                o._buffers = [out]
+        else:
+            store_outputs(last, [[out]])
         return
     raise ValueError(f"unknown fused step {kind}")

@@ -1,0 +1,925 @@
+// Memory-bound fused kernels for sm_100a: LayerNorm fwd/bwd, softmax / log-softmax,
+// cross-entropy fwd/bwd, AdamW / SGD steps, embedding gather / scatter-add, activation
+// backward, column sums (bias gradients), casts, Philox RNG, dropout, NF4 dequantisation,
+// pooling and a direct NHWC convolution for small channel counts.
+//
+// These replace compositions of primitive ops in the reference:
+//   layer_norm         nabla/nn/functional/layers.py:38-56   (9 primitive ops)
+//   cross_entropy      nabla/nn/functional/losses.py:20-44   (logsoftmax, one-hot mul, sum)
+//   adamw_step         nabla/nn/optim/functional.py:116-162  (~15 primitive ops per leaf)
+//   embedding          nabla/nn/functional/layers.py:84-98 + nabla/ops/view/indexing.py
+//   dequantize_nf4     nabla/nn/finetune/qlora.py:77-98
+//   pooling            nabla/ops/pooling.py:53-137 (python loop of slices)
+// All of them are bandwidth bound: 16-byte vector accesses, fp32 math, one pass over DRAM
+// where the row fits in registers / L1.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace nbk {
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16(v); }
+
+// 16-byte vector of T
+template <typename T> struct Vec { static constexpr int N = 16 / sizeof(T); };
+
+template <typename T>
+__device__ __forceinline__ void load_vec(const T* p, float* out) {
+  uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < Vec<T>::N; ++i) out[i] = to_f<T>(e[i]);
+}
+template <typename T>
+__device__ __forceinline__ void store_vec(T* p, const float* in) {
+  uint4 raw;
+  T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < Vec<T>::N; ++i) e[i] = from_f<T>(in[i]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+template <int NW>
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float r = 0.f;
+#pragma unroll
+  for (int i = 0; i < NW; ++i) r += sh[i];
+  return r;
+}
+template <int NW>
+__device__ __forceinline__ float block_max(float v, float* sh) {
+  v = warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float r = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < NW; ++i) r = fmaxf(r, sh[i]);
+  return r;
+}
+
+// ============================================================== LayerNorm
+// One warp per row. The row is read once into registers when D <= 32 * VPL * Vec::N.
+template <typename T, int VPL>
+__global__ void __launch_bounds__(128) layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
+                                                           const T* __restrict__ beta, T* __restrict__ y,
+                                                           float* __restrict__ mean, float* __restrict__ rstd,
+                                                           int rows, int D, float eps) {
+  constexpr int V = Vec<T>::N;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const T* xr = x + (size_t)row * D;
+  float v[VPL][V];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = (i * 32 + lane) * V;
+    if (c < D) {
+      load_vec<T>(xr + c, v[i]);
+#pragma unroll
+      for (int j = 0; j < V; ++j) s += v[i][j];
+    }
+  }
+  const float mu = warp_sum(s) / D;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = (i * 32 + lane) * V;
+    if (c < D) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float d = v[i][j] - mu;
+        q += d * d;
+      }
+    }
+  }
+  const float rs = rsqrtf(warp_sum(q) / D + eps);
+  if (lane == 0) {
+    if (mean) mean[row] = mu;
+    if (rstd) rstd[row] = rs;
+  }
+  T* yr = y + (size_t)row * D;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = (i * 32 + lane) * V;
+    if (c < D) {
+      float g[V], b[V], o[V];
+      if (gamma) load_vec<T>(gamma + c, g);
+      if (beta) load_vec<T>(beta + c, b);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        float n = (v[i][j] - mu) * rs;
+        o[j] = n * (gamma ? g[j] : 1.f) + (beta ? b[j] : 0.f);
+      }
+      store_vec<T>(yr + c, o);
+    }
+  }
+}
+
+// Backward: dx per row (one warp per row); dgamma/dbeta partial sums per block are written to
+// `partial` ([gridDim.x][2][D] fp32) and folded by colsum_partials_kernel.
+template <typename T, int VPL>
+__global__ void __launch_bounds__(128) layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                                           const T* __restrict__ gamma, const float* __restrict__ mean,
+                                                           const float* __restrict__ rstd, T* __restrict__ dx,
+                                                           float* __restrict__ partial, int rows, int D,
+                                                           int rows_per_block) {
+  constexpr int V = Vec<T>::N;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  extern __shared__ float sh[];   // [4 warps][2][D]
+  float* my_dg = sh + (size_t)warp * 2 * D;
+  float* my_db = my_dg + D;
+  for (int c = lane; c < D; c += 32) { my_dg[c] = 0.f; my_db[c] = 0.f; }
+  __syncwarp();
+  const int r0 = blockIdx.x * rows_per_block;
+  const int r1 = min(rows, r0 + rows_per_block);
+  for (int row = r0 + warp; row < r1; row += 4) {
+    const T* xr = x + (size_t)row * D;
+    const T* dyr = dy + (size_t)row * D;
+    const float mu = mean[row], rs = rstd[row];
+    float xh[VPL][V], g[VPL][V];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int c = (i * 32 + lane) * V;
+      if (c < D) {
+        float xv[V], dv[V], gm[V];
+        load_vec<T>(xr + c, xv);
+        load_vec<T>(dyr + c, dv);
+        if (gamma) load_vec<T>(gamma + c, gm);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          xh[i][j] = (xv[j] - mu) * rs;
+          my_dg[c + j] += dv[j] * xh[i][j];
+          my_db[c + j] += dv[j];
+          g[i][j] = dv[j] * (gamma ? gm[j] : 1.f);
+          s1 += g[i][j];
+          s2 += g[i][j] * xh[i][j];
+        }
+      }
+    }
+    s1 = warp_sum(s1) / D;
+    s2 = warp_sum(s2) / D;
+    T* dxr = dx + (size_t)row * D;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int c = (i * 32 + lane) * V;
+      if (c < D) {
+        float o[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) o[j] = (g[i][j] - s1 - xh[i][j] * s2) * rs;
+        store_vec<T>(dxr + c, o);
+      }
+    }
+  }
+  __syncthreads();
+  float* pg = partial + (size_t)blockIdx.x * 2 * D;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      a += sh[(size_t)w * 2 * D + c];
+      b += sh[(size_t)w * 2 * D + D + c];
+    }
+    pg[c] = a;
+    pg[D + c] = b;
+  }
+}
+
+// out[k][c] = sum_b partial[b][k][c]  (k < K planes of width D)
+template <typename T>
+__global__ void colsum_partials_kernel(const float* __restrict__ partial, T* __restrict__ out0, T* __restrict__ out1,
+                                       int nblocks, int D) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= D) return;
+  float a = 0.f, b = 0.f;
+  for (int i = 0; i < nblocks; ++i) {
+    a += partial[(size_t)i * 2 * D + c];
+    b += partial[(size_t)i * 2 * D + D + c];
+  }
+  if (out0) out0[c] = from_f<T>(a);
+  if (out1) out1[c] = from_f<T>(b);
+}
+
+// ============================================================== column sum (bias gradient)
+// x [rows][N] -> partial[gridDim.y][N] ; each block sums a slab of rows for 32*V columns.
+template <typename T>
+__global__ void __launch_bounds__(256) colsum_kernel(const T* __restrict__ x, float* __restrict__ partial, int rows,
+                                                    int N, int rows_per_block) {
+  constexpr int V = Vec<T>::N;
+  __shared__ float sh[8][32 * V];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = (blockIdx.x * 32 + lane) * V;
+  const int r0 = blockIdx.y * rows_per_block, r1 = min(rows, r0 + rows_per_block);
+  float acc[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) acc[j] = 0.f;
+  if (c < N) {
+    for (int r = r0 + warp; r < r1; r += 8) {
+      float v[V];
+      load_vec<T>(x + (size_t)r * N + c, v);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] += v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j) sh[warp][lane * V + j] = acc[j];
+  __syncthreads();
+  for (int i = threadIdx.x; i < 32 * V; i += blockDim.x) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += sh[w][i];
+    const int col = blockIdx.x * 32 * V + i;
+    if (col < N) partial[(size_t)blockIdx.y * N + col] = s;
+  }
+}
+template <typename T>
+__global__ void colsum_final_kernel(const float* __restrict__ partial, T* __restrict__ out, int nparts, int N) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= N) return;
+  float s = 0.f;
+  for (int i = 0; i < nparts; ++i) s += partial[(size_t)i * N + c];
+  out[c] = from_f<T>(s);
+}
+
+// ============================================================== softmax / log-softmax (last dim)
+template <typename T, bool LOG>
+__global__ void __launch_bounds__(256) softmax_kernel(const T* __restrict__ x, T* __restrict__ y, int rows, int D) {
+  __shared__ float sh[8];
+  const int row = blockIdx.x;
+  const T* xr = x + (size_t)row * D;
+  T* yr = y + (size_t)row * D;
+  float m = -INFINITY, s = 0.f;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    const float v = to_f<T>(xr[c]);
+    if (v > m) { s = s * __expf(m - v); m = v; }
+    s += __expf(v - m);
+  }
+  const float gm = block_max<8>(m, sh);
+  s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
+  const float gs = block_sum<8>(s, sh);
+  const float lse = gm + logf(gs);
+  const float inv = 1.f / gs;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    const float v = to_f<T>(xr[c]);
+    yr[c] = from_f<T>(LOG ? (v - lse) : __expf(v - gm) * inv);
+  }
+}
+
+// ============================================================== cross entropy
+// loss_row = lse(logits_row) - logits_row[target]; stores lse for the backward.
+template <typename T>
+__global__ void __launch_bounds__(256) ce_fwd_kernel(const T* __restrict__ logits, const long long* __restrict__ tgt,
+                                                    float* __restrict__ loss, float* __restrict__ lse_out, int rows,
+                                                    int D, long long ignore_index) {
+  __shared__ float sh[8];
+  const int row = blockIdx.x;
+  const T* xr = logits + (size_t)row * D;
+  float m = -INFINITY, s = 0.f;
+  constexpr int V = Vec<T>::N;
+  if ((D % V) == 0) {
+    for (int c = threadIdx.x * V; c < D; c += blockDim.x * V) {
+      float v[V];
+      load_vec<T>(xr + c, v);
+      float lm = v[0];
+#pragma unroll
+      for (int j = 1; j < V; ++j) lm = fmaxf(lm, v[j]);
+      if (lm > m) { s = s * __expf(m - lm); m = lm; }
+#pragma unroll
+      for (int j = 0; j < V; ++j) s += __expf(v[j] - m);
+    }
+  } else {
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+      const float v = to_f<T>(xr[c]);
+      if (v > m) { s = s * __expf(m - v); m = v; }
+      s += __expf(v - m);
+    }
+  }
+  const float gm = block_max<8>(m, sh);
+  s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
+  const float gs = block_sum<8>(s, sh);
+  if (threadIdx.x == 0) {
+    const float lse = gm + logf(gs);
+    const long long t = tgt[row];
+    lse_out[row] = lse;
+    loss[row] = (t == ignore_index || t < 0 || t >= D) ? 0.f : lse - to_f<T>(xr[t]);
+  }
+}
+// dlogits = (softmax - onehot) * gscale[0] * scale
+template <typename T>
+__global__ void __launch_bounds__(256) ce_bwd_kernel(const T* __restrict__ logits, const long long* __restrict__ tgt,
+                                                    const float* __restrict__ lse, const float* __restrict__ gscale,
+                                                    T* __restrict__ dlogits, int rows, int D, float scale,
+                                                    long long ignore_index, int g_per_row) {
+  const int row = blockIdx.x;
+  const T* xr = logits + (size_t)row * D;
+  T* dr = dlogits + (size_t)row * D;
+  const float l = lse[row];
+  const long long t = tgt[row];
+  const bool ign = (t == ignore_index || t < 0 || t >= D);
+  const float g = (gscale ? gscale[g_per_row ? row : 0] : 1.f) * scale * (ign ? 0.f : 1.f);
+  constexpr int V = Vec<T>::N;
+  if ((D % V) == 0) {
+    for (int c = threadIdx.x * V; c < D; c += blockDim.x * V) {
+      float v[V], o[V];
+      load_vec<T>(xr + c, v);
+#pragma unroll
+      for (int j = 0; j < V; ++j) o[j] = (__expf(v[j] - l) - ((c + j) == t ? 1.f : 0.f)) * g;
+      store_vec<T>(dr + c, o);
+    }
+  } else {
+    for (int c = threadIdx.x; c < D; c += blockDim.x)
+      dr[c] = from_f<T>((__expf(to_f<T>(xr[c]) - l) - (c == t ? 1.f : 0.f)) * g);
+  }
+}
+
+// ============================================================== optimizers
+// AdamW with decoupled weight decay; P/G may be bf16 or fp32, moments fp32.
+// step-dependent bias corrections are passed as bc1 = 1 - b1^t, bc2 = 1 - b2^t via device scalars
+// when `hyper` is non-null: hyper = {lr, bc1, bc2, grad_scale}.
+template <typename TP, typename TG>
+__global__ void __launch_bounds__(256) adamw_kernel(const TP* __restrict__ p, const TG* __restrict__ g,
+                                                   const float* __restrict__ m, const float* __restrict__ v,
+                                                   TP* __restrict__ p_out, float* __restrict__ m_out,
+                                                   float* __restrict__ v_out, size_t n, float lr, float b1, float b2,
+                                                   float eps, float wd, float bc1, float bc2, float grad_scale,
+                                                   const float* __restrict__ hyper) {
+  if (hyper) { lr = hyper[0]; bc1 = hyper[1]; bc2 = hyper[2]; grad_scale = hyper[3]; }
+  const size_t i0 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  const size_t stride = (size_t)gridDim.x * blockDim.x * 4;
+  for (size_t i = i0; i < n; i += stride) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const size_t k = i + j;
+      if (k < n) {
+        const float gr = to_f<TG>(g[k]) * grad_scale;
+        const float pm = to_f<TP>(p[k]);
+        const float mn = b1 * m[k] + (1.f - b1) * gr;
+        const float vn = b2 * v[k] + (1.f - b2) * gr * gr;
+        const float mh = mn / bc1, vh = vn / bc2;
+        const float upd = mh / (sqrtf(vh) + eps) + wd * pm;
+        p_out[k] = from_f<TP>(pm - lr * upd);
+        m_out[k] = mn;
+        v_out[k] = vn;
+      }
+    }
+  }
+}
+template <typename TP, typename TG>
+__global__ void __launch_bounds__(256) sgd_kernel(const TP* __restrict__ p, const TG* __restrict__ g,
+                                                 const float* __restrict__ buf, TP* __restrict__ p_out,
+                                                 float* __restrict__ buf_out, size_t n, float lr, float momentum,
+                                                 float wd, float grad_scale) {
+  const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t k = i0; k < n; k += stride) {
+    const float pm = to_f<TP>(p[k]);
+    float gr = to_f<TG>(g[k]) * grad_scale + wd * pm;
+    if (buf) {
+      gr = momentum * buf[k] + gr;
+      buf_out[k] = gr;
+    }
+    p_out[k] = from_f<TP>(pm - lr * gr);
+  }
+}
+
+// ============================================================== embedding
+template <typename T>
+__global__ void __launch_bounds__(128) embedding_gather_kernel(const T* __restrict__ table,
+                                                              const long long* __restrict__ ids, T* __restrict__ out,
+                                                              int n_ids, int D, int vocab) {
+  constexpr int V = Vec<T>::N;
+  const int i = blockIdx.x;
+  long long id = ids[i];
+  const bool ok = id >= 0 && id < vocab;
+  const T* src = table + (size_t)(ok ? id : 0) * D;
+  T* dst = out + (size_t)i * D;
+  if ((D % V) == 0) {
+    for (int c = threadIdx.x * V; c < D; c += blockDim.x * V) {
+      uint4 raw = ok ? *reinterpret_cast<const uint4*>(src + c) : make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(dst + c) = raw;
+    }
+  } else {
+    for (int c = threadIdx.x; c < D; c += blockDim.x) dst[c] = ok ? src[c] : from_f<T>(0.f);
+  }
+}
+// acc[ids[i]] += upd[i]  (fp32 accumulation table)
+template <typename T>
+__global__ void __launch_bounds__(128) embedding_scatter_add_kernel(float* __restrict__ acc,
+                                                                   const long long* __restrict__ ids,
+                                                                   const T* __restrict__ upd, int n_ids, int D,
+                                                                   int vocab) {
+  const int i = blockIdx.x;
+  const long long id = ids[i];
+  if (id < 0 || id >= vocab) return;
+  float* dst = acc + (size_t)id * D;
+  const T* src = upd + (size_t)i * D;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) atomicAdd(dst + c, to_f<T>(src[c]));
+}
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n,
+                                                  const TO* __restrict__ add_to) {
+  const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t k = i0; k < n; k += stride) {
+    float v = to_f<TI>(in[k]);
+    if (add_to) v += to_f<TO>(add_to[k]);
+    out[k] = from_f<TO>(v);
+  }
+}
+
+// ============================================================== activations
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+  return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float dgelu_f(float x) {
+  return 0.5f * (1.f + erff(x * 0.70710678118654752f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+}
+__device__ __forceinline__ float dgelu_tanh_f(float x) {
+  const float x2 = x * x, u = 0.7978845608028654f * (x + 0.044715f * x * x2), t = tanhf(u);
+  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * 0.7978845608028654f * (1.f + 3.f * 0.044715f * x2);
+}
+// mode: 0 relu, 1 gelu(erf), 2 gelu(tanh), 3 silu ; bwd: out = dy * act'(z)
+template <typename T, bool BWD>
+__global__ void __launch_bounds__(256) act_kernel(const T* __restrict__ z, const T* __restrict__ dy, T* __restrict__ out,
+                                                 size_t n, int mode) {
+  constexpr int V = Vec<T>::N;
+  const size_t i0 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * V;
+  const size_t stride = (size_t)gridDim.x * blockDim.x * V;
+  for (size_t i = i0; i < n; i += stride) {
+    float zv[V], dv[V], o[V];
+    if (i + V <= n) {
+      load_vec<T>(z + i, zv);
+      if (BWD) load_vec<T>(dy + i, dv);
+    } else {
+      for (int j = 0; j < V; ++j) {
+        zv[j] = (i + j < n) ? to_f<T>(z[i + j]) : 0.f;
+        dv[j] = (BWD && i + j < n) ? to_f<T>(dy[i + j]) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const float x = zv[j];
+      float r;
+      if (!BWD) {
+        r = mode == 0 ? fmaxf(x, 0.f) : mode == 1 ? gelu_f(x) : mode == 2 ? gelu_tanh_f(x) : x / (1.f + __expf(-x));
+      } else {
+        float d;
+        if (mode == 0) d = x > 0.f ? 1.f : 0.f;
+        else if (mode == 1) d = dgelu_f(x);
+        else if (mode == 2) d = dgelu_tanh_f(x);
+        else { const float sg = 1.f / (1.f + __expf(-x)); d = sg * (1.f + x * (1.f - sg)); }
+        r = dv[j] * d;
+      }
+      o[j] = r;
+    }
+    if (i + V <= n) store_vec<T>(out + i, o);
+    else for (int j = 0; j < V; ++j) if (i + j < n) out[i + j] = from_f<T>(o[j]);
+  }
+}
+
+// ============================================================== Philox4x32-10 RNG
+struct Philox {
+  uint32_t key[2];
+  uint32_t ctr[4];
+  __device__ Philox(uint64_t seed, uint64_t subseq, uint64_t offset) {
+    key[0] = (uint32_t)seed; key[1] = (uint32_t)(seed >> 32);
+    ctr[0] = (uint32_t)offset; ctr[1] = (uint32_t)(offset >> 32);
+    ctr[2] = (uint32_t)subseq; ctr[3] = (uint32_t)(subseq >> 32);
+  }
+  __device__ uint4 next() {
+    uint32_t c0 = ctr[0], c1 = ctr[1], c2 = ctr[2], c3 = ctr[3], k0 = key[0], k1 = key[1];
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+      const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+      const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+      const uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
+      c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+      k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+    if (++ctr[0] == 0) ++ctr[1];
+    return make_uint4(c0, c1, c2, c3);
+  }
+};
+__device__ __forceinline__ float u01(uint32_t x) { return ((x >> 8) + 0.5f) * (1.0f / 16777216.0f); }
+
+// mode 0: uniform in [a, b); mode 1: gaussian mean a std b
+template <typename T>
+__global__ void __launch_bounds__(256) rng_kernel(T* __restrict__ out, size_t n, uint64_t seed, uint64_t offset,
+                                                 int mode, float a, float b) {
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t nthreads = (size_t)gridDim.x * blockDim.x;
+  Philox ph(seed, tid, offset);
+  for (size_t i = tid * 4; i < n; i += nthreads * 4) {
+    const uint4 r = ph.next();
+    float f[4];
+    if (mode == 0) {
+      f[0] = a + (b - a) * u01(r.x); f[1] = a + (b - a) * u01(r.y);
+      f[2] = a + (b - a) * u01(r.z); f[3] = a + (b - a) * u01(r.w);
+    } else {
+      const float r1 = sqrtf(-2.f * logf(u01(r.x))), t1 = 6.283185307179586f * u01(r.y);
+      const float r2 = sqrtf(-2.f * logf(u01(r.z))), t2 = 6.283185307179586f * u01(r.w);
+      f[0] = a + b * r1 * cosf(t1); f[1] = a + b * r1 * sinf(t1);
+      f[2] = a + b * r2 * cosf(t2); f[3] = a + b * r2 * sinf(t2);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) if (i + j < n) out[i + j] = from_f<T>(f[j]);
+  }
+}
+// y = x * mask / (1-p); mask (uint8) kept for the backward
+template <typename T>
+__global__ void __launch_bounds__(256) dropout_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                     uint8_t* __restrict__ mask, size_t n, float p, uint64_t seed,
+                                                     uint64_t offset) {
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t nthreads = (size_t)gridDim.x * blockDim.x;
+  Philox ph(seed, tid, offset);
+  const float keep_scale = 1.f / (1.f - p);
+  for (size_t i = tid * 4; i < n; i += nthreads * 4) {
+    const uint4 r = ph.next();
+    const float u[4] = {u01(r.x), u01(r.y), u01(r.z), u01(r.w)};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (i + j < n) {
+        const bool keep = u[j] >= p;
+        mask[i + j] = keep ? 1 : 0;
+        y[i + j] = from_f<T>(keep ? to_f<T>(x[i + j]) * keep_scale : 0.f);
+      }
+    }
+  }
+}
+
+// ============================================================== NF4 dequantisation
+// packed: 2 codes per byte (high nibble first); absmax per block of `block` elements.
+__constant__ float NF4_CODE[16] = {-1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+                                   -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+                                   0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f,
+                                   0.33791524171829224f, 0.44070982933044434f, 0.5626170039176941f,
+                                   0.7229568362236023f, 1.0f};
+template <typename T>
+__global__ void __launch_bounds__(256) nf4_dequant_kernel(const uint8_t* __restrict__ packed,
+                                                         const float* __restrict__ absmax, T* __restrict__ out,
+                                                         size_t n, int block) {
+  const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t b = i0; b * 2 < n; b += stride) {
+    const uint8_t byte = packed[b];
+    const size_t e0 = b * 2;
+    out[e0] = from_f<T>(NF4_CODE[byte >> 4] * absmax[e0 / block]);
+    if (e0 + 1 < n) out[e0 + 1] = from_f<T>(NF4_CODE[byte & 15] * absmax[(e0 + 1) / block]);
+  }
+}
+
+// ============================================================== pooling (NHWC)
+// mode 0 avg, 1 max. Backward: avg spreads dy/(kh*kw); max routes to the first arg-max.
+template <typename T>
+__global__ void __launch_bounds__(256) pool2d_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int N, int H, int W,
+                                                        int C, int OH, int OW, int kh, int kw, int sh, int sw, int ph,
+                                                        int pw, int mode) {
+  const size_t total = (size_t)N * OH * OW * C;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int c = i % C;
+    size_t r = i / C;
+    const int ow = r % OW; r /= OW;
+    const int oh = r % OH;
+    const int n = r / OH;
+    float acc = mode == 0 ? 0.f : -INFINITY;
+    for (int a = 0; a < kh; ++a)
+      for (int b = 0; b < kw; ++b) {
+        const int ih = oh * sh - ph + a, iw = ow * sw - pw + b;
+        float v = mode == 0 ? 0.f : -INFINITY;
+        if (ih >= 0 && ih < H && iw >= 0 && iw < W) v = to_f<T>(x[(((size_t)n * H + ih) * W + iw) * C + c]);
+        acc = mode == 0 ? acc + v : fmaxf(acc, v);
+      }
+    y[i] = from_f<T>(mode == 0 ? acc / (kh * kw) : acc);
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(256) pool2d_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy,
+                                                        float* __restrict__ dx, int N, int H, int W, int C, int OH,
+                                                        int OW, int kh, int kw, int sh, int sw, int ph, int pw, int mode) {
+  const size_t total = (size_t)N * OH * OW * C;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int c = i % C;
+    size_t r = i / C;
+    const int ow = r % OW; r /= OW;
+    const int oh = r % OH;
+    const int n = r / OH;
+    const float g = to_f<T>(dy[i]);
+    if (mode == 0) {
+      const float gg = g / (kh * kw);
+      for (int a = 0; a < kh; ++a)
+        for (int b = 0; b < kw; ++b) {
+          const int ih = oh * sh - ph + a, iw = ow * sw - pw + b;
+          if (ih >= 0 && ih < H && iw >= 0 && iw < W) atomicAdd(dx + (((size_t)n * H + ih) * W + iw) * C + c, gg);
+        }
+    } else {
+      float best = -INFINITY;
+      int bh = -1, bw = -1;
+      for (int a = 0; a < kh; ++a)
+        for (int b = 0; b < kw; ++b) {
+          const int ih = oh * sh - ph + a, iw = ow * sw - pw + b;
+          if (ih >= 0 && ih < H && iw >= 0 && iw < W) {
+            const float v = to_f<T>(x[(((size_t)n * H + ih) * W + iw) * C + c]);
+            if (v > best) { best = v; bh = ih; bw = iw; }
+          }
+        }
+      if (bh >= 0) atomicAdd(dx + (((size_t)n * H + bh) * W + bw) * C + c, g);
+    }
+  }
+}
+
+// ============================================================== direct conv2d NHWC x RSCF (small C)
+// y[n,oh,ow,f] = sum_{r,s,c} x[n, oh*sh - pt + r*dh, ow*sw - pl + s*dw, c] * w[r,s,c,f] (+ bias[f])
+template <typename T>
+__global__ void __launch_bounds__(128) conv2d_direct_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                                           const T* __restrict__ bias, T* __restrict__ y, int N, int H,
+                                                           int W, int C, int R, int S, int F, int OH, int OW, int sh,
+                                                           int sw, int pt, int pl) {
+  const size_t total = (size_t)N * OH * OW * F;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int f = i % F;
+    size_t r_ = i / F;
+    const int ow = r_ % OW; r_ /= OW;
+    const int oh = r_ % OH;
+    const int n = r_ / OH;
+    float acc = bias ? to_f<T>(bias[f]) : 0.f;
+    for (int r = 0; r < R; ++r) {
+      const int ih = oh * sh - pt + r;
+      if (ih < 0 || ih >= H) continue;
+      for (int s = 0; s < S; ++s) {
+        const int iw = ow * sw - pl + s;
+        if (iw < 0 || iw >= W) continue;
+        const T* xp = x + (((size_t)n * H + ih) * W + iw) * C;
+        const T* wp = w + ((size_t)(r * S + s) * C) * F + f;
+        for (int c = 0; c < C; ++c) acc += to_f<T>(xp[c]) * to_f<T>(wp[(size_t)c * F]);
+      }
+    }
+    y[i] = from_f<T>(acc);
+  }
+}
+
+static inline int grid_for(size_t n, int per_block, int cap = 148 * 16) {
+  size_t g = (n + per_block - 1) / per_block;
+  if (g < 1) g = 1;
+  return (int)(g > (size_t)cap ? cap : g);
+}
+
+}  // namespace nbk
+
+using namespace nbk;
+#define STREAM reinterpret_cast<cudaStream_t>(stream)
+#define CHECK_LAUNCH() (cudaGetLastError() == cudaSuccess ? 0 : -1)
+
+// dtype codes: 0 = fp32, 1 = bf16
+extern "C" {
+
+int nb_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd, int rows,
+                     int D, float eps, int dtype, void* stream) {
+  if (rows <= 0) return 0;
+  const int V = dtype ? 8 : 4;
+  if (D % V) return -2;
+  const int vpl = (D / V + 31) / 32;
+  dim3 grid((rows + 3) / 4), block(128);
+#define LN_FWD(T, VPL) layernorm_fwd_kernel<T, VPL><<<grid, block, 0, STREAM>>>((const T*)x, (const T*)gamma, (const T*)beta, (T*)y, mean, rstd, rows, D, eps)
+  if (dtype) {
+    if (vpl <= 1) LN_FWD(bf16, 1); else if (vpl <= 2) LN_FWD(bf16, 2); else if (vpl <= 4) LN_FWD(bf16, 4);
+    else if (vpl <= 8) LN_FWD(bf16, 8); else if (vpl <= 16) LN_FWD(bf16, 16); else return -3;
+  } else {
+    if (vpl <= 1) LN_FWD(float, 1); else if (vpl <= 2) LN_FWD(float, 2); else if (vpl <= 4) LN_FWD(float, 4);
+    else if (vpl <= 8) LN_FWD(float, 8); else if (vpl <= 16) LN_FWD(float, 16); else return -3;
+  }
+  return CHECK_LAUNCH();
+}
+
+// Number of row slabs (= rows of the `partial` scratch buffer, each 2*D floats).
+int nb_layernorm_bwd_nblocks(int rows) {
+  int nb = (rows + 127) / 128;
+  if (nb > 148 * 2) nb = 148 * 2;
+  return nb < 1 ? 1 : nb;
+}
+
+int nb_layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                     void* dgamma, void* dbeta, float* partial, int rows, int D, int dtype, void* stream) {
+  if (rows <= 0) return 0;
+  const int V = dtype ? 8 : 4;
+  if (D % V) return -2;
+  const int vpl = (D / V + 31) / 32;
+  const int nb = nb_layernorm_bwd_nblocks(rows);
+  const int rpb = (rows + nb - 1) / nb;
+  const size_t smem = (size_t)4 * 2 * D * sizeof(float);
+  if (smem > 200 * 1024) return -3;
+#define LN_BWD(T, VPL)                                                                                               \
+  {                                                                                                                  \
+    cudaFuncSetAttribute(layernorm_bwd_kernel<T, VPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+    layernorm_bwd_kernel<T, VPL><<<nb, 128, smem, STREAM>>>((const T*)dy, (const T*)x, (const T*)gamma, mean, rstd,  \
+                                                             (T*)dx, partial, rows, D, rpb);                         \
+    colsum_partials_kernel<T><<<(D + 255) / 256, 256, 0, STREAM>>>(partial, (T*)dgamma, (T*)dbeta, nb, D);           \
+  }
+  if (dtype) {
+    if (vpl <= 1) LN_BWD(bf16, 1) else if (vpl <= 2) LN_BWD(bf16, 2) else if (vpl <= 4) LN_BWD(bf16, 4)
+    else if (vpl <= 8) LN_BWD(bf16, 8) else return -3;
+  } else {
+    if (vpl <= 1) LN_BWD(float, 1) else if (vpl <= 2) LN_BWD(float, 2) else if (vpl <= 4) LN_BWD(float, 4)
+    else if (vpl <= 8) LN_BWD(float, 8) else if (vpl <= 16) LN_BWD(float, 16) else return -3;
+  }
+  return CHECK_LAUNCH();
+}
+
+int nb_colsum_nparts(int rows) {
+  int np = (rows + 511) / 512;
+  if (np > 64) np = 64;
+  return np < 1 ? 1 : np;
+}
+int nb_colsum(const void* x, void* out, float* partial, int rows, int N, int in_dtype, int out_dtype, void* stream) {
+  const int V = in_dtype ? 8 : 4;
+  if (N % V) return -2;
+  const int np = nb_colsum_nparts(rows);
+  const int rpb = (rows + np - 1) / np;
+  dim3 grid((N + 32 * V - 1) / (32 * V), np);
+  if (in_dtype) colsum_kernel<bf16><<<grid, 256, 0, STREAM>>>((const bf16*)x, partial, rows, N, rpb);
+  else colsum_kernel<float><<<grid, 256, 0, STREAM>>>((const float*)x, partial, rows, N, rpb);
+  if (out_dtype) colsum_final_kernel<bf16><<<(N + 255) / 256, 256, 0, STREAM>>>(partial, (bf16*)out, np, N);
+  else colsum_final_kernel<float><<<(N + 255) / 256, 256, 0, STREAM>>>(partial, (float*)out, np, N);
+  return CHECK_LAUNCH();
+}
+
+int nb_softmax(const void* x, void* y, int rows, int D, int log, int dtype, void* stream) {
+  if (rows <= 0) return 0;
+  if (dtype) {
+    if (log) softmax_kernel<bf16, true><<<rows, 256, 0, STREAM>>>((const bf16*)x, (bf16*)y, rows, D);
+    else softmax_kernel<bf16, false><<<rows, 256, 0, STREAM>>>((const bf16*)x, (bf16*)y, rows, D);
+  } else {
+    if (log) softmax_kernel<float, true><<<rows, 256, 0, STREAM>>>((const float*)x, (float*)y, rows, D);
+    else softmax_kernel<float, false><<<rows, 256, 0, STREAM>>>((const float*)x, (float*)y, rows, D);
+  }
+  return CHECK_LAUNCH();
+}
+
+int nb_ce_fwd(const void* logits, const long long* tgt, float* loss, float* lse, int rows, int D, long long ignore,
+              int dtype, void* stream) {
+  if (rows <= 0) return 0;
+  if (dtype) ce_fwd_kernel<bf16><<<rows, 256, 0, STREAM>>>((const bf16*)logits, tgt, loss, lse, rows, D, ignore);
+  else ce_fwd_kernel<float><<<rows, 256, 0, STREAM>>>((const float*)logits, tgt, loss, lse, rows, D, ignore);
+  return CHECK_LAUNCH();
+}
+int nb_ce_bwd(const void* logits, const long long* tgt, const float* lse, const float* gscale, void* dlogits, int rows,
+              int D, float scale, long long ignore, int g_per_row, int dtype, void* stream) {
+  if (rows <= 0) return 0;
+  if (dtype)
+    ce_bwd_kernel<bf16><<<rows, 256, 0, STREAM>>>((const bf16*)logits, tgt, lse, gscale, (bf16*)dlogits, rows, D, scale, ignore, g_per_row);
+  else
+    ce_bwd_kernel<float><<<rows, 256, 0, STREAM>>>((const float*)logits, tgt, lse, gscale, (float*)dlogits, rows, D, scale, ignore, g_per_row);
+  return CHECK_LAUNCH();
+}
+
+int nb_adamw(const void* p, const void* g, const float* m, const float* v, void* p_out, float* m_out, float* v_out,
+             long long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale,
+             const float* hyper, int p_dtype, int g_dtype, void* stream) {
+  if (n <= 0) return 0;
+  const int grid = grid_for((size_t)n, 256 * 4);
+#define ADAMW(TP, TG) adamw_kernel<TP, TG><<<grid, 256, 0, STREAM>>>((const TP*)p, (const TG*)g, m, v, (TP*)p_out, m_out, v_out, (size_t)n, lr, b1, b2, eps, wd, bc1, bc2, grad_scale, hyper)
+  if (p_dtype && g_dtype) ADAMW(bf16, bf16);
+  else if (p_dtype) ADAMW(bf16, float);
+  else if (g_dtype) ADAMW(float, bf16);
+  else ADAMW(float, float);
+  return CHECK_LAUNCH();
+}
+int nb_sgd(const void* p, const void* g, const float* buf, void* p_out, float* buf_out, long long n, float lr,
+           float momentum, float wd, float grad_scale, int p_dtype, int g_dtype, void* stream) {
+  if (n <= 0) return 0;
+  const int grid = grid_for((size_t)n, 256);
+#define SGD(TP, TG) sgd_kernel<TP, TG><<<grid, 256, 0, STREAM>>>((const TP*)p, (const TG*)g, buf, (TP*)p_out, buf_out, (size_t)n, lr, momentum, wd, grad_scale)
+  if (p_dtype && g_dtype) SGD(bf16, bf16);
+  else if (p_dtype) SGD(bf16, float);
+  else if (g_dtype) SGD(float, bf16);
+  else SGD(float, float);
+  return CHECK_LAUNCH();
+}
+
+int nb_embedding_gather(const void* table, const long long* ids, void* out, int n_ids, int D, int vocab, int dtype,
+                        void* stream) {
+  if (n_ids <= 0) return 0;
+  if (dtype) embedding_gather_kernel<bf16><<<n_ids, 128, 0, STREAM>>>((const bf16*)table, ids, (bf16*)out, n_ids, D, vocab);
+  else embedding_gather_kernel<float><<<n_ids, 128, 0, STREAM>>>((const float*)table, ids, (float*)out, n_ids, D, vocab);
+  return CHECK_LAUNCH();
+}
+// acc (fp32, [vocab][D]) must be zeroed by the caller; out = base + acc, cast to dtype.
+int nb_embedding_scatter_add(float* acc, const long long* ids, const void* upd, const void* base, void* out, int n_ids,
+                             int D, int vocab, int dtype, void* stream) {
+  if (n_ids > 0) {
+    if (dtype) embedding_scatter_add_kernel<bf16><<<n_ids, 128, 0, STREAM>>>(acc, ids, (const bf16*)upd, n_ids, D, vocab);
+    else embedding_scatter_add_kernel<float><<<n_ids, 128, 0, STREAM>>>(acc, ids, (const float*)upd, n_ids, D, vocab);
+  }
+  const size_t n = (size_t)vocab * D;
+  const int grid = grid_for(n, 256);
+  if (dtype) cast_kernel<float, bf16><<<grid, 256, 0, STREAM>>>(acc, (bf16*)out, n, (const bf16*)base);
+  else cast_kernel<float, float><<<grid, 256, 0, STREAM>>>(acc, (float*)out, n, (const float*)base);
+  return CHECK_LAUNCH();
+}
+
+int nb_cast(const void* in, void* out, long long n, int in_dtype, int out_dtype, void* stream) {
+  if (n <= 0) return 0;
+  const int grid = grid_for((size_t)n, 256);
+  if (in_dtype && !out_dtype) cast_kernel<bf16, float><<<grid, 256, 0, STREAM>>>((const bf16*)in, (float*)out, (size_t)n, nullptr);
+  else if (!in_dtype && out_dtype) cast_kernel<float, bf16><<<grid, 256, 0, STREAM>>>((const float*)in, (bf16*)out, (size_t)n, nullptr);
+  else return -2;
+  return CHECK_LAUNCH();
+}
+
+int nb_activation(const void* z, const void* dy, void* out, long long n, int mode, int bwd, int dtype, void* stream) {
+  if (n <= 0) return 0;
+  const int V = dtype ? 8 : 4;
+  const int grid = grid_for((size_t)n, 256 * V);
+  if (dtype) {
+    if (bwd) act_kernel<bf16, true><<<grid, 256, 0, STREAM>>>((const bf16*)z, (const bf16*)dy, (bf16*)out, (size_t)n, mode);
+    else act_kernel<bf16, false><<<grid, 256, 0, STREAM>>>((const bf16*)z, nullptr, (bf16*)out, (size_t)n, mode);
+  } else {
+    if (bwd) act_kernel<float, true><<<grid, 256, 0, STREAM>>>((const float*)z, (const float*)dy, (float*)out, (size_t)n, mode);
+    else act_kernel<float, false><<<grid, 256, 0, STREAM>>>((const float*)z, nullptr, (float*)out, (size_t)n, mode);
+  }
+  return CHECK_LAUNCH();
+}
+
+int nb_rng(void* out, long long n, unsigned long long seed, unsigned long long offset, int mode, float a, float b,
+           int dtype, void* stream) {
+  if (n <= 0) return 0;
+  const int grid = grid_for((size_t)n, 256 * 4, 148 * 8);
+  if (dtype) rng_kernel<bf16><<<grid, 256, 0, STREAM>>>((bf16*)out, (size_t)n, seed, offset, mode, a, b);
+  else rng_kernel<float><<<grid, 256, 0, STREAM>>>((float*)out, (size_t)n, seed, offset, mode, a, b);
+  return CHECK_LAUNCH();
+}
+int nb_dropout(const void* x, void* y, unsigned char* mask, long long n, float p, unsigned long long seed,
+               unsigned long long offset, int dtype, void* stream) {
+  if (n <= 0) return 0;
+  const int grid = grid_for((size_t)n, 256 * 4, 148 * 8);
+  if (dtype) dropout_kernel<bf16><<<grid, 256, 0, STREAM>>>((const bf16*)x, (bf16*)y, mask, (size_t)n, p, seed, offset);
+  else dropout_kernel<float><<<grid, 256, 0, STREAM>>>((const float*)x, (float*)y, mask, (size_t)n, p, seed, offset);
+  return CHECK_LAUNCH();
+}
+
+int nb_nf4_dequant(const unsigned char* packed, const float* absmax, void* out, long long n, int block, int dtype,
+                   void* stream) {
+  if (n <= 0) return 0;
+  const int grid = grid_for((size_t)(n + 1) / 2, 256);
+  if (dtype) nf4_dequant_kernel<bf16><<<grid, 256, 0, STREAM>>>(packed, absmax, (bf16*)out, (size_t)n, block);
+  else nf4_dequant_kernel<float><<<grid, 256, 0, STREAM>>>(packed, absmax, (float*)out, (size_t)n, block);
+  return CHECK_LAUNCH();
+}
+
+int nb_pool2d_fwd(const void* x, void* y, int N, int H, int W, int C, int OH, int OW, int kh, int kw, int sh, int sw,
+                  int ph, int pw, int mode, int dtype, void* stream) {
+  const size_t total = (size_t)N * OH * OW * C;
+  if (!total) return 0;
+  const int grid = grid_for(total, 256);
+  if (dtype) pool2d_fwd_kernel<bf16><<<grid, 256, 0, STREAM>>>((const bf16*)x, (bf16*)y, N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw, mode);
+  else pool2d_fwd_kernel<float><<<grid, 256, 0, STREAM>>>((const float*)x, (float*)y, N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw, mode);
+  return CHECK_LAUNCH();
+}
+// dx must be a zeroed fp32 buffer of the input's shape.
+int nb_pool2d_bwd(const void* x, const void* dy, float* dx, int N, int H, int W, int C, int OH, int OW, int kh, int kw,
+                  int sh, int sw, int ph, int pw, int mode, int dtype, void* stream) {
+  const size_t total = (size_t)N * OH * OW * C;
+  if (!total) return 0;
+  const int grid = grid_for(total, 256);
+  if (dtype) pool2d_bwd_kernel<bf16><<<grid, 256, 0, STREAM>>>((const bf16*)x, (const bf16*)dy, dx, N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw, mode);
+  else pool2d_bwd_kernel<float><<<grid, 256, 0, STREAM>>>((const float*)x, (const float*)dy, dx, N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw, mode);
+  return CHECK_LAUNCH();
+}
+
+int nb_conv2d_direct(const void* x, const void* w, const void* bias, void* y, int N, int H, int W, int C, int R, int S,
+                     int F, int OH, int OW, int sh, int sw, int pt, int pl, int dtype, void* stream) {
+  const size_t total = (size_t)N * OH * OW * F;
+  if (!total) return 0;
+  const int grid = grid_for(total, 128, 148 * 32);
+  if (dtype) conv2d_direct_kernel<bf16><<<grid, 128, 0, STREAM>>>((const bf16*)x, (const bf16*)w, (const bf16*)bias, (bf16*)y, N, H, W, C, R, S, F, OH, OW, sh, sw, pt, pl);
+  else conv2d_direct_kernel<float><<<grid, 128, 0, STREAM>>>((const float*)x, (const float*)w, (const float*)bias, (float*)y, N, H, W, C, R, S, F, OH, OW, sh, sw, pt, pl);
+  return CHECK_LAUNCH();
+}
+
+}  // extern "C"

@@ -1,0 +1,301 @@
+"""Python wrappers of the memory-bound fused kernels (``csrc/fused_kernels.cu``).
+
+Inputs and outputs are torch CUDA tensors (bf16 or fp32, contiguous); scratch buffers come
+from torch's caching allocator. ``launch_count`` counts kernel launches issued from here.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import load, ptr, stream_ptr
+
+_lib = None
+launch_count = 0
+c_int, c_ll, c_f, c_vp, c_ull = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p, ctypes.c_ulonglong
+
+
+def _L():
+    global _lib
+    if _lib is None:
+        lib = load("libnb_kernels.so")
+        sig = {
+            "nb_layernorm_fwd": [c_vp] * 6 + [c_int, c_int, c_f, c_int, c_vp],
+            "nb_layernorm_bwd_nblocks": [c_int],
+            "nb_layernorm_bwd": [c_vp] * 9 + [c_int, c_int, c_int, c_vp],
+            "nb_colsum_nparts": [c_int],
+            "nb_colsum": [c_vp] * 3 + [c_int] * 4 + [c_vp],
+            "nb_softmax": [c_vp, c_vp, c_int, c_int, c_int, c_int, c_vp],
+            "nb_ce_fwd": [c_vp] * 4 + [c_int, c_int, c_ll, c_int, c_vp],
+            "nb_ce_bwd": [c_vp] * 5 + [c_int, c_int, c_f, c_ll, c_int, c_int, c_vp],
+            "nb_adamw": [c_vp] * 7 + [c_ll] + [c_f] * 8 + [c_vp, c_int, c_int, c_vp],
+            "nb_sgd": [c_vp] * 5 + [c_ll] + [c_f] * 4 + [c_int, c_int, c_vp],
+            "nb_embedding_gather": [c_vp] * 3 + [c_int] * 4 + [c_vp],
+            "nb_embedding_scatter_add": [c_vp] * 5 + [c_int] * 4 + [c_vp],
+            "nb_cast": [c_vp, c_vp, c_ll, c_int, c_int, c_vp],
+            "nb_activation": [c_vp] * 3 + [c_ll, c_int, c_int, c_int, c_vp],
+            "nb_rng": [c_vp, c_ll, c_ull, c_ull, c_int, c_f, c_f, c_int, c_vp],
+            "nb_dropout": [c_vp] * 3 + [c_ll, c_f, c_ull, c_ull, c_int, c_vp],
+            "nb_nf4_dequant": [c_vp] * 3 + [c_ll, c_int, c_int, c_vp],
+            "nb_pool2d_fwd": [c_vp, c_vp] + [c_int] * 14 + [c_vp],
+            "nb_pool2d_bwd": [c_vp] * 3 + [c_int] * 14 + [c_vp],
+            "nb_conv2d_direct": [c_vp] * 4 + [c_int] * 14 + [c_vp],
+        }
+        for name, args in sig.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = c_int
+        _lib = lib
+    return _lib
+
+
+def has(name: str) -> bool:
+    """True when the native library is present (every kernel family ships in one library)."""
+    try:
+        _L()
+        return True
+    except Exception:
+        return False
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return 1
+    if t.dtype == torch.float32:
+        return 0
+    raise TypeError(f"native kernels take bf16 or fp32, got {t.dtype}")
+
+
+def _ok(rc: int, what: str) -> None:
+    global launch_count
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")
+    launch_count += 1
+
+
+def supports_rows(x: torch.Tensor, d_limit: int = 4096) -> bool:
+    v = 8 if x.dtype == torch.bfloat16 else 4
+    return x.dtype in (torch.bfloat16, torch.float32) and x.shape[-1] % v == 0 and x.shape[-1] <= d_limit * (v // 4)
+
+
+# ---------------------------------------------------------------- layer norm
+def layernorm_fwd(x: torch.Tensor, gamma, beta, eps: float):
+    D = x.shape[-1]
+    x2 = x.contiguous().view(-1, D)
+    rows = x2.shape[0]
+    y = torch.empty_like(x2)
+    mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    g = gamma.contiguous().to(x.dtype) if gamma is not None else None
+    b = beta.contiguous().to(x.dtype) if beta is not None else None
+    _ok(_L().nb_layernorm_fwd(ptr(x2), ptr(g), ptr(b), ptr(y), ptr(mean), ptr(rstd), rows, D, float(eps), _dt(x),
+                              stream_ptr()), "layernorm_fwd")
+    return y.view(x.shape), mean, rstd
+
+
+def layernorm_bwd(dy: torch.Tensor, x: torch.Tensor, gamma, mean: torch.Tensor, rstd: torch.Tensor):
+    global launch_count
+    D = x.shape[-1]
+    x2 = x.contiguous().view(-1, D)
+    dy2 = dy.contiguous().view(-1, D)
+    rows = x2.shape[0]
+    dx = torch.empty_like(x2)
+    dgamma = torch.empty(D, dtype=x.dtype, device=x.device)
+    dbeta = torch.empty(D, dtype=x.dtype, device=x.device)
+    nb = _L().nb_layernorm_bwd_nblocks(rows)
+    partial = torch.empty((nb, 2, D), dtype=torch.float32, device=x.device)
+    g = gamma.contiguous().to(x.dtype) if gamma is not None else None
+    _ok(_L().nb_layernorm_bwd(ptr(dy2), ptr(x2), ptr(g), ptr(mean), ptr(rstd), ptr(dx), ptr(dgamma), ptr(dbeta),
+                              ptr(partial), rows, D, _dt(x), stream_ptr()), "layernorm_bwd")
+    launch_count += 1
+    return dx.view(x.shape), dgamma, dbeta
+
+
+def colsum(x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """Sum over all leading dims: (..., N) -> (N,)."""
+    global launch_count
+    N = x.shape[-1]
+    x2 = x.contiguous().view(-1, N)
+    rows = x2.shape[0]
+    out = torch.empty(N, dtype=out_dtype or x.dtype, device=x.device)
+    np_ = _L().nb_colsum_nparts(rows)
+    partial = torch.empty((np_, N), dtype=torch.float32, device=x.device)
+    _ok(_L().nb_colsum(ptr(x2), ptr(out), ptr(partial), rows, N, _dt(x), _dt(out), stream_ptr()), "colsum")
+    launch_count += 1
+    return out
+
+
+# ---------------------------------------------------------------- softmax / cross entropy
+def softmax(x: torch.Tensor, log: bool = False) -> torch.Tensor:
+    D = x.shape[-1]
+    x2 = x.contiguous().view(-1, D)
+    y = torch.empty_like(x2)
+    _ok(_L().nb_softmax(ptr(x2), ptr(y), x2.shape[0], D, int(log), _dt(x), stream_ptr()), "softmax")
+    return y.view(x.shape)
+
+
+def cross_entropy_fwd(logits: torch.Tensor, targets: torch.Tensor, ignore_index: int = -100):
+    D = logits.shape[-1]
+    l2 = logits.contiguous().view(-1, D)
+    t = targets.contiguous().view(-1).to(torch.int64)
+    rows = l2.shape[0]
+    loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    _ok(_L().nb_ce_fwd(ptr(l2), ptr(t), ptr(loss), ptr(lse), rows, D, ignore_index, _dt(logits), stream_ptr()), "ce_fwd")
+    return loss, lse
+
+
+def cross_entropy_bwd(logits: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor, gscale: torch.Tensor | None,
+                      scale: float, ignore_index: int = -100) -> torch.Tensor:
+    D = logits.shape[-1]
+    l2 = logits.contiguous().view(-1, D)
+    t = targets.contiguous().view(-1).to(torch.int64)
+    d = torch.empty_like(l2)
+    gs = gscale.reshape(-1).to(torch.float32).contiguous() if gscale is not None else None
+    per_row = 1 if (gs is not None and gs.numel() == l2.shape[0] and l2.shape[0] > 1) else 0
+    _ok(_L().nb_ce_bwd(ptr(l2), ptr(t), ptr(lse), ptr(gs), ptr(d), l2.shape[0], D, float(scale), ignore_index, per_row,
+                       _dt(logits), stream_ptr()), "ce_bwd")
+    return d.view(logits.shape)
+
+
+# ---------------------------------------------------------------- optimizers
+def adamw(p, g, m, v, *, lr, b1, b2, eps, wd, step: int | None = None, hyper: torch.Tensor | None = None,
+          grad_scale: float = 1.0, inplace: bool = False):
+    """Returns (p', m', v'). ``hyper`` = device tensor [lr, 1-b1^t, 1-b2^t, grad_scale] overrides
+    the scalar arguments (lets a captured CUDA graph advance the step)."""
+    p = p.contiguous()
+    g = g.contiguous()
+    po = p if inplace else torch.empty_like(p)
+    mo = m if inplace else torch.empty_like(m)
+    vo = v if inplace else torch.empty_like(v)
+    bc1 = 1.0 - b1 ** step if step is not None else 1.0
+    bc2 = 1.0 - b2 ** step if step is not None else 1.0
+    _ok(_L().nb_adamw(ptr(p), ptr(g), ptr(m), ptr(v), ptr(po), ptr(mo), ptr(vo), p.numel(), float(lr), float(b1),
+                      float(b2), float(eps), float(wd), float(bc1), float(bc2), float(grad_scale), ptr(hyper), _dt(p),
+                      _dt(g), stream_ptr()), "adamw")
+    return po, mo, vo
+
+
+def sgd(p, g, buf, *, lr, momentum=0.0, wd=0.0, grad_scale=1.0):
+    p = p.contiguous()
+    g = g.contiguous()
+    po = torch.empty_like(p)
+    bo = torch.empty_like(buf) if buf is not None else None
+    _ok(_L().nb_sgd(ptr(p), ptr(g), ptr(buf), ptr(po), ptr(bo), p.numel(), float(lr), float(momentum), float(wd),
+                    float(grad_scale), _dt(p), _dt(g), stream_ptr()), "sgd")
+    return po, bo
+
+
+# ---------------------------------------------------------------- embedding
+def embedding_gather(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    table = table.contiguous()
+    flat = ids.contiguous().view(-1).to(torch.int64)
+    D = table.shape[1]
+    out = torch.empty((flat.numel(), D), dtype=table.dtype, device=table.device)
+    _ok(_L().nb_embedding_gather(ptr(table), ptr(flat), ptr(out), flat.numel(), D, table.shape[0], _dt(table),
+                                 stream_ptr()), "embedding_gather")
+    return out.view(*ids.shape, D)
+
+
+def embedding_scatter_add(base: torch.Tensor, ids: torch.Tensor, upd: torch.Tensor) -> torch.Tensor:
+    """base + scatter_add(ids, upd) with fp32 accumulation (embedding backward)."""
+    global launch_count
+    base = base.contiguous()
+    V, D = base.shape
+    flat = ids.contiguous().view(-1).to(torch.int64)
+    u = upd.contiguous().view(-1, D).to(base.dtype)
+    acc = torch.zeros((V, D), dtype=torch.float32, device=base.device)
+    out = torch.empty_like(base)
+    _ok(_L().nb_embedding_scatter_add(ptr(acc), ptr(flat), ptr(u), ptr(base), ptr(out), flat.numel(), D, V, _dt(base),
+                                      stream_ptr()), "embedding_scatter_add")
+    launch_count += 1
+    return out
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    x = x.contiguous()
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _ok(_L().nb_cast(ptr(x), ptr(out), x.numel(), _dt(x), _dt(out), stream_ptr()), "cast")
+    return out
+
+
+ACT = {"relu": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3}
+
+
+def activation(z: torch.Tensor, mode: str) -> torch.Tensor:
+    z = z.contiguous()
+    out = torch.empty_like(z)
+    _ok(_L().nb_activation(ptr(z), None, ptr(out), z.numel(), ACT[mode], 0, _dt(z), stream_ptr()), "activation")
+    return out
+
+
+def activation_bwd(z: torch.Tensor, dy: torch.Tensor, mode: str) -> torch.Tensor:
+    z = z.contiguous()
+    dy = dy.contiguous().to(z.dtype)
+    out = torch.empty_like(z)
+    _ok(_L().nb_activation(ptr(z), ptr(dy), ptr(out), z.numel(), ACT[mode], 1, _dt(z), stream_ptr()), "activation_bwd")
+    return out
+
+
+# ---------------------------------------------------------------- RNG
+def rng(shape, dtype: torch.dtype, device, seed: int, offset: int, mode: str, a: float, b: float) -> torch.Tensor:
+    out = torch.empty(shape, dtype=dtype, device=device)
+    _ok(_L().nb_rng(ptr(out), out.numel(), seed & (2 ** 64 - 1), offset & (2 ** 64 - 1), 0 if mode == "uniform" else 1,
+                    float(a), float(b), _dt(out), stream_ptr()), "rng")
+    return out
+
+
+def dropout(x: torch.Tensor, p: float, seed: int, offset: int):
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    mask = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    _ok(_L().nb_dropout(ptr(x), ptr(y), ptr(mask), x.numel(), float(p), seed & (2 ** 64 - 1), offset & (2 ** 64 - 1),
+                        _dt(x), stream_ptr()), "dropout")
+    return y, mask
+
+
+def nf4_dequant(packed: torch.Tensor, absmax: torch.Tensor, n: int, block: int, dtype: torch.dtype) -> torch.Tensor:
+    out = torch.empty(n, dtype=dtype, device=packed.device)
+    _ok(_L().nb_nf4_dequant(ptr(packed.contiguous()), ptr(absmax.contiguous().float()), ptr(out), n, block, _dt(out),
+                            stream_ptr()), "nf4_dequant")
+    return out
+
+
+# ---------------------------------------------------------------- pooling / conv (NHWC)
+def pool2d_fwd(x, kh, kw, sh, sw, ph, pw, mode: str):
+    x = x.contiguous()
+    N, H, W, C = x.shape
+    OH = (H + 2 * ph - kh) // sh + 1
+    OW = (W + 2 * pw - kw) // sw + 1
+    y = torch.empty((N, OH, OW, C), dtype=x.dtype, device=x.device)
+    _ok(_L().nb_pool2d_fwd(ptr(x), ptr(y), N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw, 0 if mode == "avg" else 1,
+                           _dt(x), stream_ptr()), "pool2d_fwd")
+    return y
+
+
+def pool2d_bwd(x, dy, kh, kw, sh, sw, ph, pw, mode: str):
+    x = x.contiguous()
+    dy = dy.contiguous()
+    N, H, W, C = x.shape
+    _, OH, OW, _ = dy.shape
+    dx = torch.zeros((N, H, W, C), dtype=torch.float32, device=x.device)
+    _ok(_L().nb_pool2d_bwd(ptr(x), ptr(dy), ptr(dx), N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw,
+                           0 if mode == "avg" else 1, _dt(x), stream_ptr()), "pool2d_bwd")
+    return dx.to(x.dtype)
+
+
+def conv2d_direct(x, w, bias, stride, padding):
+    """NHWC x RSCF direct convolution; padding = (top, bottom, left, right)."""
+    x = x.contiguous()
+    w = w.contiguous().to(x.dtype)
+    N, H, W, C = x.shape
+    R, S, _, F = w.shape
+    pt, pb, pl, pr = padding
+    OH = (H + pt + pb - R) // stride[0] + 1
+    OW = (W + pl + pr - S) // stride[1] + 1
+    y = torch.empty((N, OH, OW, F), dtype=x.dtype, device=x.device)
+    b = bias.contiguous().to(x.dtype).view(-1) if bias is not None else None
+    _ok(_L().nb_conv2d_direct(ptr(x), ptr(w), ptr(b), ptr(y), N, H, W, C, R, S, F, OH, OW, stride[0], stride[1], pt, pl,
+                              _dt(x), stream_ptr()), "conv2d_direct")
+    return y

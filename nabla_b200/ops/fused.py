@@ -1,0 +1,690 @@
+"""First-class fused operations: linear(+bias,+activation), layer_norm, scaled dot-product
+attention, cross-entropy, AdamW/SGD steps, dropout.
+
+The reference composes these from primitives (nabla/nn/functional/layers.py:30-153,
+losses.py:20-44, optim/functional.py:14-162), which costs ~10 kernel launches and as many
+DRAM round trips each. Here each is one ``Operation`` with its own kernel, sharding rule and
+VJP (the backward is again a fused op), executed by hand-written sm_100a kernels on CUDA and
+by an equivalent torch expression on CPU. Forward-mode derivatives and second derivatives go
+through the decomposed primitive implementation (``decomposed``), which stays available as
+``nabla_b200.nn.functional.*_reference``.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..core.sharding.propagation import OpShardingRule
+from ..core.tensor.api import Tensor
+from ..types import DType
+from .base import Operation, ensure_tensor
+
+
+def _native(x: torch.Tensor) -> bool:
+    from .. import native
+
+    return native.use_native(x) and x.dtype in (torch.bfloat16, torch.float32)
+
+
+class _Fused(Operation):
+    """JVP of a fused op = JVP of its decomposition into primitives."""
+
+    def decomposed(self, *primals, **kwargs):
+        raise NotImplementedError
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        from ..transforms.jvp import jvp
+
+        tensors = [p for p in primals if isinstance(p, Tensor)]
+        tans = [t for p, t in zip(primals, tangents) if isinstance(p, Tensor)]
+        statics = [(i, p) for i, p in enumerate(primals) if not isinstance(p, Tensor)]
+
+        def f(*ts):
+            it = iter(ts)
+            full = [next(it) if isinstance(p, Tensor) else p for p in primals]
+            return self.decomposed(*full, **kwargs)
+
+        _, t = jvp(f, tuple(tensors), tuple(tans))
+        return t
+
+
+# ================================================================ linear
+_ACT_MODE = {"relu": "relu", "gelu": "gelu", "gelu_tanh": "gelu_tanh", "silu": "silu"}
+
+
+def _apply_act(z: torch.Tensor, act: str | None) -> torch.Tensor:
+    if act is None:
+        return z
+    if act == "relu":
+        return torch.relu(z)
+    if act == "gelu":
+        return torch.nn.functional.gelu(z)
+    if act == "gelu_tanh":
+        return torch.nn.functional.gelu(z, approximate="tanh")
+    if act == "silu":
+        return torch.nn.functional.silu(z)
+    raise ValueError(f"unknown activation {act}")
+
+
+class LinearOp(_Fused):
+    """``y = act(x @ w + b)``; with an activation the pre-activation ``z`` is a second output
+    kept for the backward (written by the same GEMM epilogue)."""
+
+    partial_policy = "none"
+
+    def kernel(self, x, w, b=None, *, activation: str | None = None, residual: bool = False, r=None):
+        if _native(x) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.numel() and activation != "silu":
+            from ..native.gemm import gemm_bf16
+
+            x2 = x.reshape(-1, x.shape[-1])
+            if activation is None:
+                y = gemm_bf16(x2, w, bias=b)
+                return y.reshape(*x.shape[:-1], w.shape[-1])
+            epi = "relu" if activation == "relu" else "gelu"
+            y, z = gemm_bf16(x2, w, bias=b if b is not None else torch.zeros(w.shape[-1], dtype=w.dtype, device=w.device),
+                             epilogue=epi, aux="store_preact", gelu_tanh=activation == "gelu_tanh")
+            shp = (*x.shape[:-1], w.shape[-1])
+            return y.reshape(shp), z.reshape(shp)
+        z = torch.matmul(x, w)
+        if b is not None:
+            z = z + b.reshape(-1).to(z.dtype)
+        if activation is None:
+            return z
+        return _apply_act(z, activation), z
+
+    def sharding_rule(self, input_shapes, output_shapes, *, activation=None, **kw):
+        xs, ws = input_shapes[0], input_shapes[1]
+        r = len(xs)
+        mx = {i: [f"m{i}"] for i in range(r - 1)}
+        mx[r - 1] = ["k"]
+        mw = {0: ["k"], 1: ["n"]}
+        ins = [mx, mw]
+        if len(input_shapes) > 2:
+            bs = input_shapes[2]
+            ins.append({i: ["n"] if i == len(bs) - 1 else [f"bcast_b{i}"] for i in range(len(bs))})
+        out = {i: [f"m{i}"] for i in range(r - 1)}
+        out[r - 1] = ["n"]
+        outs = [out] if activation is None else [dict(out), dict(out)]
+        return OpShardingRule(ins, outs)
+
+    def partial_passthrough_axes(self, input_specs, kwargs=None):
+        # linear in x (and in w) only without bias and activation
+        if (kwargs or {}).get("activation") is None and len(input_specs) == 2:
+            carriers = {a for s in input_specs for a in s.partial_sum_axes}
+            ok = set()
+            for a in carriers:
+                if sum(1 for s in input_specs if a in s.partial_sum_axes) == 1:
+                    ok.add(a)
+            return ok
+        return set()
+
+    def compute_cost(self, input_shapes, output_shapes) -> float:
+        xs, ws = input_shapes[0], input_shapes[1]
+        m = 1
+        for d in xs[:-1]:
+            m *= int(d)
+        return 2.0 * m * int(ws[0]) * int(ws[1])
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        from .binary import matmul
+        from .reduction import reduce_sum
+        from .view import reshape, swap_axes
+
+        x, w = primals[0], primals[1]
+        b = primals[2] if len(primals) > 2 else None
+        act = kwargs.get("activation")
+        if act is not None:
+            dy = cot[0] if isinstance(cot, (tuple, list)) else cot
+            z = outputs[1]
+            dz = dact_mul(dy, z, act)
+            if isinstance(cot, (tuple, list)) and cot[1] is not None:
+                dz = dz + cot[1]
+        else:
+            dz = cot
+        dx = matmul(dz, swap_axes(w, 0, 1))
+        kdim = x._impl.global_shape[-1]
+        ndim = w._impl.global_shape[-1]
+        x2 = reshape(x, (-1, kdim)) if x.rank != 2 else x
+        dz2 = reshape(dz, (-1, ndim)) if dz.rank != 2 else dz
+        dw = matmul(swap_axes(x2, 0, 1), dz2)
+        res = [dx, dw]
+        if b is not None:
+            db = bias_grad(dz2)
+            res.append(reshape(db, tuple(b._impl.global_shape)))
+        return tuple(res)
+
+    def decomposed(self, x, w, b=None, *, activation=None, **kw):
+        from . import unary
+        from .binary import matmul
+
+        z = matmul(x, w)
+        if b is not None:
+            z = z + b
+        if activation is None:
+            return z
+        y = {"relu": unary.relu, "gelu": unary.gelu, "silu": unary.silu,
+             "gelu_tanh": lambda t: unary.gelu(t, approximate="tanh")}[activation](z)
+        return y, z
+
+
+class DActMulOp(Operation):
+    """``dy * act'(z)`` (activation backward)."""
+
+    def kernel(self, dy, z, *, activation: str):
+        if _native(z) and dy.shape == z.shape and dy.dtype == z.dtype:
+            from ..native import kernels
+
+            return kernels.activation_bwd(z, dy, activation)
+        zf = z.float()
+        if activation == "relu":
+            d = (zf > 0).float()
+        elif activation == "gelu":
+            d = 0.5 * (1 + torch.erf(zf / math.sqrt(2))) + zf * torch.exp(-0.5 * zf * zf) / math.sqrt(2 * math.pi)
+        elif activation == "gelu_tanh":
+            c = math.sqrt(2 / math.pi)
+            u = c * (zf + 0.044715 * zf ** 3)
+            t = torch.tanh(u)
+            d = 0.5 * (1 + t) + 0.5 * zf * (1 - t * t) * c * (1 + 3 * 0.044715 * zf * zf)
+        else:
+            sg = torch.sigmoid(zf)
+            d = sg * (1 + zf * (1 - sg))
+        return (dy.float() * d).to(dy.dtype)
+
+    def partial_passthrough_axes(self, input_specs, kwargs=None):
+        return set(input_specs[0].partial_sum_axes) - set(input_specs[1].partial_sum_axes)
+
+    def _deriv(self, z, act):
+        from . import unary
+
+        op = {"relu": unary._relu, "gelu": unary._gelu, "gelu_tanh": unary._gelu, "silu": unary._silu}[act]
+        kw = {"approximate": "tanh"} if act == "gelu_tanh" else {}
+        return op._derivative(z, None if act != "silu" else None, kw) if act != "relu" else unary._step(z)
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        dy, z = primals
+        # second-order term wrt z is dropped only for relu (zero a.e.); others go through primitives
+        d = self._deriv(z, kwargs["activation"])
+        return (cot * d, None if kwargs["activation"] == "relu" else _second_order_dact(cot, dy, z, kwargs["activation"]))
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        dy, z = primals
+        return tangents[0] * self._deriv(z, kwargs["activation"])
+
+
+def _second_order_dact(cot, dy, z, act):
+    from ..transforms.vjp import vjp
+
+    op = DActMulOp()
+    _, pull = vjp(lambda zz: dy * op._deriv(zz, act), z)
+    return pull(cot)[0]
+
+
+class BiasGradOp(Operation):
+    """Sum over all leading dims: (rows, n) -> (n,)."""
+
+    partial_policy = "any"
+
+    def kernel(self, x):
+        if _native(x) and x.dim() == 2 and x.shape[1] % 8 == 0 and x.shape[0] > 0:
+            from ..native import kernels
+
+            return kernels.colsum(x)
+        return x.float().sum(dim=0).to(x.dtype)
+
+    def sharding_rule(self, input_shapes, output_shapes, **kw):
+        return OpShardingRule([{0: ["m"], 1: ["n"]}], [{0: ["n"]}])
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        from .view import broadcast_to
+
+        return (broadcast_to(cot, tuple(primals[0]._impl.global_shape)),)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return bias_grad(tangents[0])
+
+
+# ================================================================ layer norm
+class LayerNormOp(_Fused):
+    """Outputs (y, mean, rstd); mean/rstd (fp32, one per row) are kept for the backward."""
+
+    def kernel(self, x, gamma=None, beta=None, *, eps: float = 1e-5):
+        if _native(x) and x.numel():
+            from ..native import kernels
+
+            if kernels.supports_rows(x):
+                y, mean, rstd = kernels.layernorm_fwd(x, gamma, beta, eps)
+                return y, mean.view(x.shape[:-1]), rstd.view(x.shape[:-1])
+        xf = x.float()
+        mean = xf.mean(dim=-1)
+        var = xf.var(dim=-1, unbiased=False)
+        rstd = torch.rsqrt(var + eps)
+        y = (xf - mean.unsqueeze(-1)) * rstd.unsqueeze(-1)
+        if gamma is not None:
+            y = y * gamma.float().reshape(-1)
+        if beta is not None:
+            y = y + beta.float().reshape(-1)
+        return y.to(x.dtype), mean, rstd
+
+    def sharding_rule(self, input_shapes, output_shapes, **kw):
+        xs = input_shapes[0]
+        r = len(xs)
+        mx = {i: [f"d{i}"] for i in range(r - 1)}
+        mx[r - 1] = ["bcast_norm"]
+        ins = [mx] + [{i: ["bcast_norm_p%d" % j] for i in range(len(s))} for j, s in enumerate(input_shapes[1:])]
+        stat = {i: [f"d{i}"] for i in range(r - 1)}
+        return OpShardingRule(ins, [dict(mx), dict(stat), dict(stat)])
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        x = primals[0]
+        gamma = primals[1] if len(primals) > 1 else None
+        beta = primals[2] if len(primals) > 2 else None
+        dy = cot[0]
+        if dy is None:
+            return tuple(None for _ in primals)
+        y, mean, rstd = outputs
+        args = [dy, x, mean, rstd] + ([gamma] if gamma is not None else [])
+        dx, dg, db = _ln_bwd(*args, has_gamma=gamma is not None)
+        res = [dx]
+        if gamma is not None:
+            from .view import reshape
+
+            res.append(reshape(dg, tuple(gamma._impl.global_shape)))
+        if beta is not None:
+            from .view import reshape
+
+            res.append(reshape(db, tuple(beta._impl.global_shape)))
+        return tuple(res)
+
+    def decomposed(self, x, gamma=None, beta=None, *, eps=1e-5):
+        from .reduction import mean as _mean
+        from .unary import rsqrt
+
+        mu = _mean(x, axis=-1, keepdims=True)
+        xc = x - mu
+        var = _mean(xc * xc, axis=-1, keepdims=True)
+        rs = rsqrt(var + eps)
+        y = xc * rs
+        if gamma is not None:
+            y = y * gamma
+        if beta is not None:
+            y = y + beta
+        from .view import squeeze
+
+        return y, squeeze(mu, axis=-1), squeeze(rs, axis=-1)
+
+
+class LayerNormBwdOp(Operation):
+    def kernel(self, dy, x, mean, rstd, gamma=None, *, has_gamma: bool = False):
+        if _native(x) and x.numel():
+            from ..native import kernels
+
+            if kernels.supports_rows(x, 2048) and dy.dtype == x.dtype:
+                return kernels.layernorm_bwd(dy, x, gamma, mean.reshape(-1), rstd.reshape(-1))
+        D = x.shape[-1]
+        xf = x.float().reshape(-1, D)
+        dyf = dy.float().reshape(-1, D)
+        xh = (xf - mean.reshape(-1, 1).float()) * rstd.reshape(-1, 1).float()
+        g = dyf * (gamma.float().reshape(-1) if gamma is not None else 1.0)
+        s1 = g.mean(dim=-1, keepdim=True)
+        s2 = (g * xh).mean(dim=-1, keepdim=True)
+        dx = (g - s1 - xh * s2) * rstd.reshape(-1, 1).float()
+        return dx.reshape(x.shape).to(x.dtype), (dyf * xh).sum(0).to(x.dtype), dyf.sum(0).to(x.dtype)
+
+    def sharding_rule(self, input_shapes, output_shapes, **kw):
+        xs = input_shapes[1]
+        r = len(xs)
+        mx = {i: [f"d{i}"] for i in range(r - 1)}
+        mx[r - 1] = ["bcast_norm"]
+        stat = {i: [f"d{i}"] for i in range(r - 1)}
+        ins = [dict(mx), dict(mx), dict(stat), dict(stat)]
+        if len(input_shapes) > 4:
+            ins.append({i: ["bcast_g"] for i in range(len(input_shapes[4]))})
+        return OpShardingRule(ins, [dict(mx), {0: ["gn"]}, {0: ["gn"]}])
+
+    def partial_passthrough_axes(self, input_specs, kwargs=None):
+        return set()
+
+
+# ================================================================ attention
+class SDPAOp(_Fused):
+    """softmax(q k^T * scale + mask) v on (..., heads, seq, head_dim). Outputs (o, lse)."""
+
+    def kernel(self, q, k, v, mask=None, *, causal: bool = False, scale: float | None = None, dropout_p: float = 0.0):
+        sc = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+        if q.device.type != "meta" and _native(q):
+            from ..native import attention
+
+            if attention.supported(q, k, v, mask, dropout_p):
+                return attention.sdpa_fwd(q, k, v, causal=causal, scale=sc)
+        s = torch.matmul(q.float(), k.float().transpose(-1, -2)) * sc
+        if causal:
+            L, S = q.shape[-2], k.shape[-2]
+            cm = torch.ones(L, S, dtype=torch.bool, device=q.device).tril(S - L)
+            s = s.masked_fill(~cm, float("-inf"))
+        if mask is not None:
+            s = s + mask.float() if mask.dtype != torch.bool else s.masked_fill(~mask, float("-inf"))
+        lse = torch.logsumexp(s, dim=-1)
+        p = torch.exp(s - lse.unsqueeze(-1))
+        o = torch.matmul(p, v.float()).to(q.dtype)
+        return o, lse
+
+    def sharding_rule(self, input_shapes, output_shapes, **kw):
+        r = len(input_shapes[0])
+        lead = {i: [f"b{i}"] for i in range(r - 2)}
+        q = {**lead, r - 2: ["bcast_s"], r - 1: ["bcast_d"]}
+        kv = {**lead, r - 2: ["bcast_t"], r - 1: ["bcast_d2"]}
+        ins = [q, dict(kv), dict(kv)]
+        if len(input_shapes) > 3:
+            ms = input_shapes[3]
+            off = r - len(ms)
+            ins.append({i: ([f"b{i + off}"] if (i + off) < r - 2 and ms[i] != 1 else [f"bcast_m{i}"]) for i in range(len(ms))})
+        return OpShardingRule(ins, [dict(q), {**lead, r - 2: ["bcast_s"]}])
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        q, k, v = primals[:3]
+        mask = primals[3] if len(primals) > 3 else None
+        do = cot[0]
+        if do is None:
+            return tuple(None for _ in primals)
+        o, lse = outputs
+        args = [do, q, k, v, o, lse] + ([mask] if mask is not None else [])
+        dq, dk, dv = _sdpa_bwd(*args, causal=kwargs.get("causal", False), scale=kwargs.get("scale"),
+                               has_mask=mask is not None)
+        return (dq, dk, dv) + ((None,) if mask is not None else ())
+
+    def decomposed(self, q, k, v, mask=None, *, causal=False, scale=None, dropout_p=0.0):
+        from ..nn.functional.layers import scaled_dot_product_attention_reference as ref
+
+        o = ref(q, k, v, attn_mask=mask, is_causal=causal, scale=scale)
+        from .creation import zeros
+
+        return o, zeros(tuple(q._impl.global_shape[:-1]), dtype=DType.float32, device=q.device)
+
+
+class SDPABwdOp(Operation):
+    def kernel(self, do, q, k, v, o, lse, mask=None, *, causal: bool = False, scale: float | None = None,
+               has_mask: bool = False):
+        sc = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+        if q.device.type != "meta" and _native(q):
+            from ..native import attention
+
+            if attention.supported(q, k, v, mask, 0.0) and attention.bwd_available():
+                return attention.sdpa_bwd(do, q, k, v, o, lse, causal=causal, scale=sc)
+        qf, kf, vf, dof = q.float(), k.float(), v.float(), do.float()
+        s = torch.matmul(qf, kf.transpose(-1, -2)) * sc
+        if causal:
+            L, S = q.shape[-2], k.shape[-2]
+            cm = torch.ones(L, S, dtype=torch.bool, device=q.device).tril(S - L)
+            s = s.masked_fill(~cm, float("-inf"))
+        if mask is not None:
+            s = s + mask.float() if mask.dtype != torch.bool else s.masked_fill(~mask, float("-inf"))
+        p = torch.exp(s - lse.float().unsqueeze(-1))
+        dv = torch.matmul(p.transpose(-1, -2), dof)
+        dp = torch.matmul(dof, vf.transpose(-1, -2))
+        delta = (dof * o.float()).sum(dim=-1, keepdim=True)
+        ds = p * (dp - delta) * sc
+        dq = torch.matmul(ds, kf)
+        dk = torch.matmul(ds.transpose(-1, -2), qf)
+        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
+
+    def sharding_rule(self, input_shapes, output_shapes, **kw):
+        r = len(input_shapes[1])
+        lead = {i: [f"b{i}"] for i in range(r - 2)}
+        q = {**lead, r - 2: ["bcast_s"], r - 1: ["bcast_d"]}
+        kv = {**lead, r - 2: ["bcast_t"], r - 1: ["bcast_d2"]}
+        ins = [dict(q), dict(q), dict(kv), dict(kv), dict(q), {**lead, r - 2: ["bcast_s"]}]
+        if len(input_shapes) > 6:
+            ms = input_shapes[6]
+            ins.append({i: [f"bcast_m{i}"] for i in range(len(ms))})
+        return OpShardingRule(ins, [dict(q), dict(kv), dict(kv)])
+
+
+# ================================================================ cross entropy
+class CrossEntropyOp(_Fused):
+    """Per-row ``lse(logits) - logits[target]`` for integer targets. Outputs (loss fp32 [rows...], lse)."""
+
+    def kernel(self, logits, targets, *, ignore_index: int = -100):
+        if logits.device.type != "meta" and _native(logits) and logits.numel():
+            from ..native import kernels
+
+            loss, lse = kernels.cross_entropy_fwd(logits, targets, ignore_index)
+            return loss.view(targets.shape), lse.view(targets.shape)
+        lf = logits.float()
+        lse = torch.logsumexp(lf, dim=-1)
+        t = targets.long()
+        valid = (t != ignore_index) & (t >= 0) & (t < logits.shape[-1])
+        picked = torch.gather(lf, -1, t.clamp(0, logits.shape[-1] - 1).unsqueeze(-1)).squeeze(-1)
+        loss = torch.where(valid, lse - picked, torch.zeros_like(lse))
+        return loss, lse
+
+    def sharding_rule(self, input_shapes, output_shapes, **kw):
+        r = len(input_shapes[0])
+        rows = {i: [f"d{i}"] for i in range(r - 1)}
+        return OpShardingRule([{**rows, r - 1: ["bcast_vocab"]}, dict(rows)], [dict(rows), dict(rows)])
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        logits, targets = primals
+        g = cot[0]
+        if g is None:
+            return (None, None)
+        return (_ce_bwd(g, logits, targets, outputs[1], ignore_index=kwargs.get("ignore_index", -100)), None)
+
+    def decomposed(self, logits, targets, *, ignore_index=-100):
+        from .reduction import reduce_sum
+        from .unary import cast, logsoftmax
+        from .view import gather, reshape, unsqueeze
+
+        ls = logsoftmax(cast(logits, DType.float32), axis=-1)
+        v = logits._impl.global_shape[-1]
+        flat = reshape(ls, (-1, v))
+        t = reshape(targets, (-1,))
+        from .creation import arange
+        from .comparison import equal
+
+        onehot = cast(equal(unsqueeze(cast(t, DType.int64), axis=-1),
+                            arange(0, v, 1, dtype=DType.int64, device=logits.device)), DType.float32)
+        loss = -reduce_sum(flat * onehot, axis=-1)
+        loss = reshape(loss, tuple(targets._impl.global_shape))
+        return loss, loss
+
+
+class CrossEntropyBwdOp(Operation):
+    def kernel(self, g, logits, targets, lse, *, ignore_index: int = -100):
+        if logits.device.type != "meta" and _native(logits) and logits.numel():
+            from ..native import kernels
+
+            return kernels.cross_entropy_bwd(logits, targets, lse.reshape(-1), g.reshape(-1), 1.0, ignore_index)
+        lf = logits.float()
+        p = torch.exp(lf - lse.float().unsqueeze(-1))
+        t = targets.long()
+        valid = ((t != ignore_index) & (t >= 0) & (t < logits.shape[-1])).unsqueeze(-1)
+        oh = torch.zeros_like(p).scatter_(-1, t.clamp(0, logits.shape[-1] - 1).unsqueeze(-1), 1.0)
+        d = (p - oh) * g.float().unsqueeze(-1) * valid
+        return d.to(logits.dtype)
+
+    def sharding_rule(self, input_shapes, output_shapes, **kw):
+        r = len(input_shapes[1])
+        rows = {i: [f"d{i}"] for i in range(r - 1)}
+        return OpShardingRule([dict(rows), {**rows, r - 1: ["bcast_vocab"]}, dict(rows), dict(rows)],
+                              [{**rows, r - 1: ["bcast_vocab"]}])
+
+
+# ================================================================ optimizers
+class AdamWStepOp(Operation):
+    """One AdamW update: (p, g, m, v) -> (p', m', v'). ``step`` may be a python int (baked) or
+    a 0-d tensor (so compiled steps do not retrace when it advances)."""
+
+    def kernel(self, p, g, m, v, step=None, *, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float,
+               step_value: int | None = None, bias_correction: bool = True):
+        if p.device.type != "meta" and _native(p) and p.numel() and m.dtype == torch.float32 and v.dtype == torch.float32 \
+                and g.dtype in (torch.bfloat16, torch.float32):
+            from ..native import kernels
+
+            hyper = None
+            if step is not None and bias_correction:
+                s = step.reshape(()).float()
+                hyper = torch.stack([torch.full((), lr, device=p.device), 1 - beta1 ** s, 1 - beta2 ** s,
+                                     torch.ones((), device=p.device)]).float().contiguous()
+            return kernels.adamw(p, g, m, v, lr=lr, b1=beta1, b2=beta2, eps=eps, wd=weight_decay,
+                                 step=step_value if bias_correction else None, hyper=hyper)
+        gf, pf = g.float(), p.float()
+        mn = beta1 * m.float() + (1 - beta1) * gf
+        vn = beta2 * v.float() + (1 - beta2) * gf * gf
+        if bias_correction:
+            if step is not None:
+                s = step.reshape(()).float()
+                bc1, bc2 = 1 - beta1 ** s, 1 - beta2 ** s
+            else:
+                bc1, bc2 = 1 - beta1 ** step_value, 1 - beta2 ** step_value
+        else:
+            bc1 = bc2 = 1.0
+        upd = (mn / bc1) / (torch.sqrt(vn / bc2) + eps) + weight_decay * pf
+        return (pf - lr * upd).to(p.dtype), mn.to(m.dtype), vn.to(v.dtype)
+
+    def sharding_rule(self, input_shapes, output_shapes, **kw):
+        r = len(input_shapes[0])
+        m = {i: [f"d{i}"] for i in range(r)}
+        ins = [dict(m) for _ in range(4)] + [{} for _ in input_shapes[4:]]
+        return OpShardingRule(ins, [dict(m), dict(m), dict(m)])
+
+
+class SGDStepOp(Operation):
+    def kernel(self, p, g, buf=None, *, lr: float, momentum: float = 0.0, weight_decay: float = 0.0):
+        if p.device.type != "meta" and _native(p) and p.numel() and (buf is None or buf.dtype == torch.float32):
+            from ..native import kernels
+
+            po, bo = kernels.sgd(p, g, buf, lr=lr, momentum=momentum, wd=weight_decay)
+            return (po, bo) if buf is not None else po
+        gf = g.float() + weight_decay * p.float()
+        if buf is not None:
+            bn = momentum * buf.float() + gf
+            return (p.float() - lr * bn).to(p.dtype), bn.to(buf.dtype)
+        return (p.float() - lr * gf).to(p.dtype)
+
+    def sharding_rule(self, input_shapes, output_shapes, **kw):
+        r = len(input_shapes[0])
+        m = {i: [f"d{i}"] for i in range(r)}
+        n_out = 2 if len(input_shapes) > 2 else 1
+        return OpShardingRule([dict(m) for _ in input_shapes], [dict(m) for _ in range(n_out)])
+
+
+# ================================================================ dropout
+class DropoutOp(Operation):
+    """Outputs (y, keep-mask uint8). Fresh Philox stream per execution and per shard."""
+
+    partial_policy = "none"
+
+    def execute(self, node):
+        from ..core.graph.engine import GRAPH
+
+        self._rng = GRAPH.next_rng()
+        return super().execute(node)
+
+    def shard_kwargs(self, kwargs, node, shard_idx, device_id):
+        return {**kwargs, "_shard": device_id}
+
+    def kernel(self, x, *, p: float, _shard: int = 0):
+        seed, counter = getattr(self, "_rng", (0, 0))
+        if x.device.type != "meta" and _native(x) and x.numel():
+            from ..native import kernels
+
+            return kernels.dropout(x, p, seed * 1000003 + _shard, counter << 32)
+        if x.device.type == "meta":
+            return torch.empty_like(x), torch.empty(x.shape, dtype=torch.uint8, device="meta")
+        from .creation import _generator
+
+        g = _generator(x.device, seed, counter, _shard)
+        keep = torch.rand(x.shape, device=x.device, generator=g) >= p
+        return (x * keep.to(x.dtype) / (1.0 - p)).to(x.dtype), keep.to(torch.uint8)
+
+    def sharding_rule(self, input_shapes, output_shapes, **kw):
+        r = len(input_shapes[0])
+        m = {i: [f"d{i}"] for i in range(r)}
+        return OpShardingRule([dict(m)], [dict(m), dict(m)])
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        from .unary import cast
+
+        if cot[0] is None:
+            return (None,)
+        x = primals[0]
+        return (cot[0] * cast(outputs[1], x.dtype) * (1.0 / (1.0 - kwargs["p"])),)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        from .unary import cast
+
+        x = primals[0]
+        return tangents[0] * cast(outputs[1], x.dtype) * (1.0 / (1.0 - kwargs["p"])), None
+
+
+_linear, _dact, _bias_grad = LinearOp(), DActMulOp(), BiasGradOp()
+_ln, _ln_bwd_op = LayerNormOp(), LayerNormBwdOp()
+_sdpa, _sdpa_bwd_op = SDPAOp(), SDPABwdOp()
+_ce, _ce_bwd_op = CrossEntropyOp(), CrossEntropyBwdOp()
+_adamw, _sgd, _dropout = AdamWStepOp(), SGDStepOp(), DropoutOp()
+
+
+def linear(x, w, b=None, activation: str | None = None) -> Tensor:
+    """Fused ``act(x @ w + b)`` with ``w`` of shape (in, out)."""
+    args = (x, w) if b is None else (x, w, b)
+    out = _linear(*args, activation=activation)
+    return out[0] if activation is not None else out
+
+
+def dact_mul(dy, z, activation: str) -> Tensor:
+    return _dact(dy, z, activation=activation)
+
+
+def bias_grad(x) -> Tensor:
+    return _bias_grad(x)
+
+
+def layer_norm(x, gamma=None, beta=None, eps: float = 1e-5) -> Tensor:
+    args = [x] + ([gamma] if gamma is not None else []) + ([beta] if beta is not None else [])
+    if gamma is None and beta is not None:
+        from .creation import ones_like
+
+        args = [x, ones_like(beta), beta]
+    return _ln(*args, eps=float(eps))[0]
+
+
+def _ln_bwd(*args, has_gamma: bool):
+    return _ln_bwd_op(*args, has_gamma=has_gamma)
+
+
+def scaled_dot_product_attention(q, k, v, mask=None, *, causal: bool = False, scale: float | None = None,
+                                 dropout_p: float = 0.0) -> Tensor:
+    args = (q, k, v) if mask is None else (q, k, v, mask)
+    return _sdpa(*args, causal=bool(causal), scale=scale, dropout_p=float(dropout_p))[0]
+
+
+def _sdpa_bwd(*args, causal, scale, has_mask):
+    return _sdpa_bwd_op(*args, causal=causal, scale=scale, has_mask=has_mask)
+
+
+def cross_entropy_rows(logits, targets, ignore_index: int = -100) -> Tensor:
+    """Per-row negative log-likelihood (fp32) for integer class targets."""
+    return _ce(logits, targets, ignore_index=int(ignore_index))[0]
+
+
+def _ce_bwd(g, logits, targets, lse, ignore_index):
+    return _ce_bwd_op(g, logits, targets, lse, ignore_index=ignore_index)
+
+
+def adamw_step_fused(p, g, m, v, step, *, lr, beta1, beta2, eps, weight_decay, bias_correction=True):
+    if isinstance(step, Tensor):
+        return _adamw(p, g, m, v, step, lr=float(lr), beta1=float(beta1), beta2=float(beta2), eps=float(eps),
+                      weight_decay=float(weight_decay), step_value=None, bias_correction=bias_correction)
+    return _adamw(p, g, m, v, lr=float(lr), beta1=float(beta1), beta2=float(beta2), eps=float(eps),
+                  weight_decay=float(weight_decay), step_value=int(step), bias_correction=bias_correction)
+
+
+def sgd_step_fused(p, g, buf=None, *, lr, momentum=0.0, weight_decay=0.0):
+    if buf is None:
+        return _sgd(p, g, lr=float(lr), momentum=float(momentum), weight_decay=float(weight_decay))
+    return _sgd(p, g, buf, lr=float(lr), momentum=float(momentum), weight_decay=float(weight_decay))
+
+
+def dropout_fused(x, p: float) -> Tensor:
+    return _dropout(x, p=float(p))[0]

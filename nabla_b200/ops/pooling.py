@@ -1,0 +1,128 @@
+"""2-D pooling on NHWC tensors (reference: nabla/ops/pooling.py:24-214, where pooling is a
+Python double loop of slice + reduce + stack per output pixel). Here each of avg/max pooling
+is one op with a single forward and a single backward kernel. Average pooling counts padded
+zeros in the divisor (kernel area), max pooling ignores padding."""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as TF
+
+from ..core.sharding.propagation import OpShardingRule
+from ..core.tensor.api import Tensor
+from .base import Operation, ensure_tensor
+from .convolution import _fold, _pad4, _two
+
+
+def _native_ok(x):
+    from .. import native
+
+    return native.use_native(x) and x.dtype in (torch.bfloat16, torch.float32) and x.numel() > 0
+
+
+def _rule(input_shapes):
+    r = len(input_shapes[0])
+    m = {i: [f"b{i}"] for i in range(r - 3)}
+    m.update({r - 3: ["bcast_h"], r - 2: ["bcast_w"], r - 1: ["c"]})
+    out = {i: [f"b{i}"] for i in range(r - 3)}
+    out.update({r - 3: ["oh"], r - 2: ["ow"], r - 1: ["c"]})
+    return m, out
+
+
+class Pool2dOp(Operation):
+    def kernel(self, x, *, kernel_size, stride, padding, mode: str):
+        x4, lead = _fold(x)
+        kh, kw = kernel_size
+        pt, pb, pl, pr = padding
+        if _native_ok(x4) and pt == pb and pl == pr:
+            from ..native import kernels
+
+            y = kernels.pool2d_fwd(x4, kh, kw, stride[0], stride[1], pt, pl, mode)
+            return y.reshape(*lead, *y.shape[1:])
+        xc = x4.permute(0, 3, 1, 2)
+        if mode == "avg":
+            xc = TF.pad(xc, (pl, pr, pt, pb))
+            y = TF.avg_pool2d(xc, (kh, kw), stride)
+        else:
+            xc = TF.pad(xc, (pl, pr, pt, pb), value=float("-inf"))
+            y = TF.max_pool2d(xc, (kh, kw), stride)
+        y = y.permute(0, 2, 3, 1).contiguous()
+        return y.reshape(*lead, *y.shape[1:])
+
+    def sharding_rule(self, input_shapes, output_shapes, **kw):
+        m, out = _rule(input_shapes)
+        return OpShardingRule([m], [out])
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        return (_pool_bwd(primals[0], cot, **kwargs),)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        if kwargs["mode"] == "avg":
+            return _pool(tangents[0], **kwargs)
+        from ..transforms.vjp import vjp  # max: tangent follows the arg-max (same routing as the VJP transpose)
+        from .creation import ones_like
+
+        x = primals[0]
+        mask = _pool_bwd(x, ones_like(outputs), **kwargs)
+        kw = dict(kwargs)
+        kw["mode"] = "avg"
+        kh, kw_ = kwargs["kernel_size"]
+        return _pool(tangents[0] * mask, **kw) * float(kh * kw_)
+
+
+class Pool2dBwdOp(Operation):
+    def kernel(self, x, dy, *, kernel_size, stride, padding, mode: str):
+        x4, lead = _fold(x)
+        dy4, _ = _fold(dy)
+        kh, kw = kernel_size
+        pt, pb, pl, pr = padding
+        if _native_ok(x4) and pt == pb and pl == pr and dy4.dtype == x4.dtype:
+            from ..native import kernels
+
+            return kernels.pool2d_bwd(x4, dy4, kh, kw, stride[0], stride[1], pt, pl, mode).reshape(x.shape)
+        xr = x4.detach().float().permute(0, 3, 1, 2).requires_grad_(True)
+        with torch.enable_grad():
+            if mode == "avg":
+                y = TF.avg_pool2d(TF.pad(xr, (pl, pr, pt, pb)), (kh, kw), stride)
+            else:
+                y = TF.max_pool2d(TF.pad(xr, (pl, pr, pt, pb), value=float("-inf")), (kh, kw), stride)
+            (g,) = torch.autograd.grad(y, xr, dy4.float().permute(0, 3, 1, 2))
+        return g.permute(0, 2, 3, 1).contiguous().to(x.dtype).reshape(x.shape)
+
+    def sharding_rule(self, input_shapes, output_shapes, **kw):
+        m, out = _rule(input_shapes)
+        return OpShardingRule([m, out], [dict(m)])
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        if kwargs["mode"] == "avg":
+            return (None, _pool(cot, **kwargs))
+        raise NotImplementedError("second derivative of max_pool2d")
+
+
+_pool, _pool_bwd = Pool2dOp(), Pool2dBwdOp()
+
+
+def _call(x, kernel_size, stride, padding, dilation, mode):
+    x = ensure_tensor(x)
+    if len(x.shape) < 4:
+        raise ValueError(f"pool2d expects an NHWC tensor, got shape {tuple(x.shape)}")
+    if _two(dilation, "dilation") != (1, 1):
+        raise ValueError("pool2d currently supports only dilation=(1, 1)")
+    k = _two(kernel_size, "kernel_size")
+    s = _two(stride if stride is not None else k, "stride")
+    p = _pad4(padding)
+    if min(k) <= 0 or min(s) <= 0 or min(p) < 0:
+        raise ValueError("kernel_size and stride must be positive, padding non-negative")
+    H, W = int(x.shape[-3]), int(x.shape[-2])
+    oh = (H + p[0] + p[1] - k[0]) // s[0] + 1
+    ow = (W + p[2] + p[3] - k[1]) // s[1] + 1
+    if oh <= 0 or ow <= 0:
+        raise ValueError(f"Non-positive pool2d output size H={oh}, W={ow}.")
+    return _pool(x, kernel_size=k, stride=s, padding=p, mode=mode)
+
+
+def avg_pool2d(x, kernel_size, stride=None, padding=0, dilation=1) -> Tensor:
+    return _call(x, kernel_size, stride, padding, dilation, "avg")
+
+
+def max_pool2d(x, kernel_size, stride=None, padding=0, dilation=1) -> Tensor:
+    return _call(x, kernel_size, stride, padding, dilation, "max")

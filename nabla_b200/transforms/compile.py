@@ -1,0 +1,330 @@
+"""``compile`` (reference: nabla/transforms/compile.py:40-602).
+
+The first call with a new signature runs the Python function ONCE on placeholder tensors,
+recording a private graph of ``OpNode``s; later calls skip the Python function and the op
+pipeline (no shape inference, no sharding propagation): they bind the new input buffers to
+the placeholders and replay the recorded, fused schedule, freeing every intermediate right
+after its last use. With ``cuda_graph=True`` the replay is captured into a CUDA graph so a
+launch-bound step (small pipeline ticks) costs one graph launch.
+
+Cache key = (pytree structure, per-tensor (shape, dtype, sharding signature), static values);
+dimensions named in ``dynamic_dims={arg_idx: {dim_idx: "name"}}`` enter the key as ``"$name"``
+so all sizes share one entry (each concrete size is specialised lazily inside that entry).
+"""
+from __future__ import annotations
+
+import time
+from collections import OrderedDict
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+import torch
+
+from .. import config
+from ..core.common import pytree
+from ..core.graph import fusion
+from ..core.graph.engine import GRAPH, _STATS, store_outputs
+from ..core.graph.tracing import OpNode, topo_nodes
+from ..core.tensor.api import Tensor
+from ..core.tensor.impl import TensorImpl
+
+
+@dataclass
+class CompilationStats:
+    hits: int = 0
+    misses: int = 0
+    fallbacks: int = 0
+    retraces: int = 0
+    compile_time_s: float = 0.0
+    replay_time_s: float = 0.0
+    graph_nodes: int = 0
+    graph_steps: int = 0
+
+    @property
+    def hit_rate(self) -> float:
+        t = self.hits + self.misses
+        return self.hits / t if t else 0.0
+
+    def __repr__(self) -> str:
+        return (f"CompilationStats(hits={self.hits}, misses={self.misses}, fallbacks={self.fallbacks}, "
+                f"hit_rate={self.hit_rate:.1%}, compile_time={self.compile_time_s * 1e3:.2f}ms, "
+                f"nodes={self.graph_nodes}, steps={self.graph_steps})")
+
+
+class _Recorded:
+    """One specialisation: placeholder impls, ordered nodes, fused steps, output recipe."""
+
+    def __init__(self):
+        self.placeholders: list[TensorImpl] = []
+        self.nodes: list[OpNode] = []
+        self.keep: list[list[TensorImpl]] = []      # strong refs to every node's outputs
+        self.steps: list = []
+        self.free_after: list[list[TensorImpl]] = []
+        self.out_impls: list[TensorImpl | None] = []
+        self.out_static: list[Any] = []
+        self.out_treedef = None
+        self.cuda_graph = None
+        self.static_inputs: list[list[torch.Tensor]] | None = None
+        self.static_outputs: list[list[torch.Tensor]] | None = None
+
+
+def _normalize_step_scalars(tree: Any) -> Any:
+    """Optimizer state dicts carry ``step`` as a python int that changes every call; turn it
+    into a 0-d tensor so the cache key stays stable (reference: compile.py:138-170)."""
+    if isinstance(tree, dict):
+        out = {}
+        for k, v in tree.items():
+            if k == "step" and isinstance(v, (int, float)) and not isinstance(v, bool) and ("m" in tree or "v" in tree or "momentum_buffers" in tree):
+                from ..ops.creation import constant
+                from ..types import DType
+
+                dev = None
+                for leaf in pytree.tensor_leaves(tree):
+                    dev = leaf.device
+                    break
+                out[k] = constant(float(v), dtype=DType.float32, device=dev)
+            else:
+                out[k] = _normalize_step_scalars(v)
+        return out
+    if isinstance(tree, (list, tuple)) and not hasattr(tree, "_fields"):
+        return type(tree)(_normalize_step_scalars(v) for v in tree)
+    return tree
+
+
+class CompiledFunction:
+    def __init__(self, fn: Callable, *, fullgraph: bool = False, max_cache_size: int = 64,
+                 dynamic_dims: dict[int, dict[int, str]] | None = None, cuda_graph: bool = False):
+        self.fn = fn
+        self.fullgraph = fullgraph
+        self.max_cache_size = int(max_cache_size)
+        self.dynamic_dims = dynamic_dims or {}
+        self.use_cuda_graph = bool(cuda_graph)
+        self._cache: "OrderedDict[Any, dict[Any, _Recorded]]" = OrderedDict()
+        self._stats = CompilationStats()
+        self.__name__ = getattr(fn, "__name__", "compiled")
+        self.__doc__ = getattr(fn, "__doc__", None)
+
+    @property
+    def stats(self) -> CompilationStats:
+        return self._stats
+
+    def clear_cache(self) -> None:
+        self._cache.clear()
+
+    # ---- keys
+    def _signature(self, t: Tensor, arg_idx: int | None) -> tuple[tuple, tuple]:
+        im = t._impl
+        shape = tuple(im._shape)
+        dyn = self.dynamic_dims.get(arg_idx, {}) if arg_idx is not None else {}
+        sym = tuple(f"${dyn[i - im.batch_dims]}" if (i - im.batch_dims) in dyn else d for i, d in enumerate(shape))
+        sh = im.sharding.effect_signature() if im.sharding is not None else None
+        rest = (im.dtype, sh, im.batch_dims, im.device, bool(im.requires_grad))
+        return (sym,) + rest, (shape,) + rest
+
+    def _keys(self, args, kwargs):
+        leaves, td = pytree.tree_flatten((args, kwargs))
+        # which top-level positional argument does each leaf belong to (for dynamic_dims)
+        owner: list[int | None] = []
+        for i, a in enumerate(args):
+            owner += [i] * len(pytree.tree_leaves(a))
+        owner += [None] * (len(leaves) - len(owner))
+        sym, conc = [], []
+        for leaf, ow in zip(leaves, owner):
+            if isinstance(leaf, Tensor):
+                s, c = self._signature(leaf, ow)
+                sym.append(s)
+                conc.append(c)
+            else:
+                from ..core.graph.engine import _freeze
+
+                f = ("static", _freeze(leaf))
+                sym.append(f)
+                conc.append(f)
+        return (td, tuple(sym)), tuple(conc), leaves, td
+
+    # ---- call
+    def __call__(self, *args, **kwargs):
+        args = tuple(_normalize_step_scalars(a) for a in args)
+        kwargs = {k: _normalize_step_scalars(v) for k, v in kwargs.items()}
+        tensors = pytree.tensor_leaves((args, kwargs))
+        pending = [t for t in tensors if not t._impl.is_realized]
+        if pending:
+            GRAPH.evaluate(*pending)
+        key, conc, leaves, td = self._keys(args, kwargs)
+        entry = self._cache.get(key)
+        if entry is None:
+            self._stats.misses += 1
+            entry = {}
+            self._cache[key] = entry
+            while len(self._cache) > self.max_cache_size:
+                self._cache.popitem(last=False)
+        else:
+            self._cache.move_to_end(key)
+            self._stats.hits += 1
+        rec = entry.get(conc)
+        if rec is None:
+            if entry:
+                self._stats.retraces += 1
+            t0 = time.perf_counter()
+            try:
+                rec, result = self._trace(leaves, td)
+            except Exception:
+                self._stats.fallbacks += 1
+                raise
+            entry[conc] = rec
+            self._stats.compile_time_s += time.perf_counter() - t0
+            return result
+        t0 = time.perf_counter()
+        out = self._replay(rec, [l for l in leaves if isinstance(l, Tensor)])
+        self._stats.replay_time_s += time.perf_counter() - t0
+        return out
+
+    # ---- trace
+    def _trace(self, leaves: list, td) -> tuple[_Recorded, Any]:
+        rec = _Recorded()
+        ph_leaves = []
+        for l in leaves:
+            if isinstance(l, Tensor):
+                im = l._impl
+                ph = TensorImpl(list(im._buffers), shape=im._shape, dtype=im.dtype, device=im.device,
+                                sharding=im.sharding, batch_dims=im.batch_dims, is_traced=False)
+                ph.requires_grad = im.requires_grad
+                ph.is_traced = im.requires_grad
+                rec.placeholders.append(ph)
+                ph_leaves.append(Tensor(impl=ph))
+            else:
+                ph_leaves.append(l)
+        p_args, p_kwargs = pytree.tree_unflatten(td, ph_leaves)
+        with config.tracing(True), config.eager_max_graph(False):
+            result = self.fn(*p_args, **p_kwargs)
+        out_leaves, out_td = pytree.tree_flatten(result)
+        rec.out_treedef = out_td
+        targets = []
+        for o in out_leaves:
+            if isinstance(o, Tensor):
+                rec.out_impls.append(o._impl)
+                rec.out_static.append(None)
+                if not o._impl.is_realized:
+                    targets.append(o._impl)
+            else:
+                rec.out_impls.append(None)
+                rec.out_static.append(o)
+        nodes = topo_nodes(targets, lambda impl: impl.is_realized)
+        rec.nodes = nodes
+        rec.keep = [[o for o in n.outputs() if o is not None] for n in nodes]
+        plan = fusion.build_plan(nodes, targets) if fusion.enabled() else None
+        rec.steps = plan.steps if plan is not None else [("op", (i,)) for i in range(len(nodes))]
+        # liveness: free an intermediate after the last step that reads it
+        out_ids = {id(i) for i in rec.out_impls if i is not None}
+        produced = {id(o): o for outs in rec.keep for o in outs}
+        last_use: dict[int, int] = {}
+        for si, (kind, idxs) in enumerate(rec.steps):
+            for ni in idxs:
+                for a in nodes[ni].input_impls():
+                    if id(a) in produced:
+                        last_use[id(a)] = si
+                for o in rec.keep[ni]:
+                    last_use.setdefault(id(o), si)
+        rec.free_after = [[] for _ in rec.steps]
+        for k, si in last_use.items():
+            if k not in out_ids:
+                rec.free_after[si].append(produced[k])
+        self._stats.graph_nodes = len(nodes)
+        self._stats.graph_steps = len(rec.steps)
+        self._run(rec)
+        return rec, self._collect(rec)
+
+    # ---- execution of a recorded graph
+    def _run(self, rec: _Recorded) -> None:
+        nodes = rec.nodes
+        _STATS["nodes_executed"] += len(nodes)
+        for si, (kind, idxs) in enumerate(rec.steps):
+            if kind == "op":
+                n = nodes[idxs[0]]
+                outs = n.op.execute(n)
+                for i, ref in enumerate(n.out_refs):
+                    o = ref()
+                    if o is not None:
+                        o._buffers = outs[i]
+            else:
+                fusion.run_fused(kind, [nodes[i] for i in idxs], keep_graph=True)
+            for dead in rec.free_after[si]:
+                dead._buffers = None
+
+    def _collect(self, rec: _Recorded) -> Any:
+        outs = []
+        for impl, static in zip(rec.out_impls, rec.out_static):
+            if impl is None:
+                outs.append(static)
+                continue
+            new = TensorImpl(list(impl._buffers), shape=impl._shape, dtype=impl.dtype, device=impl.device,
+                             sharding=impl.sharding, batch_dims=impl.batch_dims)
+            outs.append(Tensor(impl=new))
+        # drop our references to output buffers produced by nodes (placeholders are re-bound per call)
+        ph = {id(p) for p in rec.placeholders}
+        for impl in rec.out_impls:
+            if impl is not None and id(impl) not in ph and impl.output_refs is not None:
+                impl._buffers = None
+        return pytree.tree_unflatten(rec.out_treedef, outs)
+
+    def _replay(self, rec: _Recorded, tensors: list[Tensor]) -> Any:
+        if self.use_cuda_graph and tensors and tensors[0]._impl.device.label == "gpu":
+            return self._replay_cuda_graph(rec, tensors)
+        for ph, t in zip(rec.placeholders, tensors):
+            ph._buffers = t._impl._buffers
+        try:
+            self._run(rec)
+            return self._collect(rec)
+        finally:
+            for ph in rec.placeholders:
+                ph._buffers = None
+
+    def _replay_cuda_graph(self, rec: _Recorded, tensors: list[Tensor]) -> Any:
+        if rec.cuda_graph is None:
+            rec.static_inputs = [[b.clone() for b in t._impl._buffers] for t in tensors]
+            for ph, bufs in zip(rec.placeholders, rec.static_inputs):
+                ph._buffers = bufs
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._run(rec)       # warm-up on the side stream (allocator, lazy inits)
+                for impl in rec.out_impls:
+                    if impl is not None and impl.output_refs is not None:
+                        impl._buffers = None
+            torch.cuda.current_stream().wait_stream(s)
+            g = torch.cuda.CUDAGraph()
+            try:
+                with torch.cuda.graph(g):
+                    self._run(rec)
+                    rec.static_outputs = [list(i._buffers) if i is not None else None for i in rec.out_impls]
+            except Exception:
+                self._stats.fallbacks += 1
+                self.use_cuda_graph = False
+                for ph in rec.placeholders:
+                    ph._buffers = None
+                return self._replay(rec, tensors)
+            rec.cuda_graph = g
+        for bufs, t in zip(rec.static_inputs, tensors):
+            for dst, src in zip(bufs, t._impl._buffers):
+                if dst.data_ptr() != src.data_ptr():
+                    dst.copy_(src)
+        rec.cuda_graph.replay()
+        outs = []
+        for impl, static, bufs in zip(rec.out_impls, rec.out_static, rec.static_outputs):
+            if impl is None:
+                outs.append(static)
+            else:
+                new = TensorImpl([b.clone() for b in bufs], shape=impl._shape, dtype=impl.dtype, device=impl.device,
+                                 sharding=impl.sharding, batch_dims=impl.batch_dims)
+                outs.append(Tensor(impl=new))
+        return pytree.tree_unflatten(rec.out_treedef, outs)
+
+
+def compile(fn: Callable | None = None, *, fullgraph: bool = False, max_cache_size: int = 64,
+            dynamic_dims: dict[int, dict[int, str]] | None = None, cuda_graph: bool = False):
+    """Decorator / wrapper: ``@compile`` or ``compile(fn, dynamic_dims={0: {0: "batch"}})``."""
+    if fn is None:
+        return lambda f: CompiledFunction(f, fullgraph=fullgraph, max_cache_size=max_cache_size,
+                                          dynamic_dims=dynamic_dims, cuda_graph=cuda_graph)
+    return CompiledFunction(fn, fullgraph=fullgraph, max_cache_size=max_cache_size, dynamic_dims=dynamic_dims,
+                            cuda_graph=cuda_graph)
