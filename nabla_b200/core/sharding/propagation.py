@@ -82,10 +82,18 @@ class OpShardingRuleTemplate:
                     output_shapes: Sequence[Sequence[int]] | None = None) -> OpShardingRule:
         sizes: dict[str, int] = {}
 
+        max_batch = 0
+        for i, toks in enumerate(self.inputs):
+            if Ellipsis in toks and i < len(input_shapes):
+                max_batch = max(max_batch, len(input_shapes[i]) - sum(1 for t in toks if t is not Ellipsis))
+
         def expand(tokens: list, shape: Sequence[int] | None) -> Mapping:
             n_named = sum(1 for t in tokens if t is not Ellipsis)
-            rank = len(shape) if shape is not None else n_named
-            n_batch = max(0, rank - n_named) if Ellipsis in tokens else 0
+            if shape is not None:
+                n_batch = max(0, len(shape) - n_named) if Ellipsis in tokens else 0
+            else:
+                # unknown (output) shape: it carries the broadcast of all operands' batch dims
+                n_batch = max_batch if Ellipsis in tokens else 0
             mapping: Mapping = {}
             d = 0
             for t in tokens:
@@ -150,8 +158,12 @@ def infer_from_rule(rule: OpShardingRule, input_specs: Sequence[ShardingSpec | N
             f = factors[0]
             if f not in factor_axes:
                 factor_axes[f] = list(axes)
-    contracting = rule.get_contracting_factors()
     out_map = rule.output_mappings[output_index] if rule.output_mappings else {}
+    # contraction is judged per output: a sharded input factor that this output does not carry
+    # was summed away on the way to it (e.g. the row factors for LayerNorm's dgamma)
+    own = {f for fs in out_map.values() for f in fs}
+    in_factors = {f for m in rule.input_mappings for fs in m.values() for f in fs}
+    contracting = in_factors - own
     rank = max(out_map.keys(), default=-1) + 1
     used: set[str] = set()
     dims: list[DimSpec] = []

@@ -25,7 +25,7 @@ if TYPE_CHECKING:
 class TensorImpl:
     __slots__ = ("_buffers", "_shape", "_dtype", "_device", "sharding", "sharding_constraint", "is_traced",
                  "requires_grad", "grad", "tangent", "cotangent", "dual", "batch_dims", "output_refs",
-                 "output_index", "_local_shapes", "__weakref__")
+                 "output_index", "_local_shapes", "_keepalive", "__weakref__")
 
     def __init__(self, buffers: list[torch.Tensor] | torch.Tensor | None = None, *, shape=None, dtype: DType | None = None,
                  device: Device | None = None, sharding: "ShardingSpec | None" = None, batch_dims: int = 0,
@@ -45,6 +45,7 @@ class TensorImpl:
         self.output_refs: "OpNode | None" = None
         self.output_index = 0
         self._local_shapes = None
+        self._keepalive = None
         if buffers is not None and shape is None:
             b0 = buffers[0]
             if sharding is not None:

@@ -290,12 +290,14 @@ __global__ void __launch_bounds__(256) softmax_kernel(const T* __restrict__ x, T
   }
 }
 
-// ============================================================== cross entropy
-// loss_row = lse(logits_row) - logits_row[target]; stores lse for the backward.
+// ============================================================== cross entropy building blocks
+// Per row: lse = logsumexp(logits_row); picked = logits_row[target] when 0 <= target < D else 0.
+// A vocabulary shard passes targets shifted by its offset, so out-of-range simply means
+// "another shard holds this class"; the caller combines shards with max/sum reductions.
 template <typename T>
-__global__ void __launch_bounds__(256) ce_fwd_kernel(const T* __restrict__ logits, const long long* __restrict__ tgt,
-                                                    float* __restrict__ loss, float* __restrict__ lse_out, int rows,
-                                                    int D, long long ignore_index) {
+__global__ void __launch_bounds__(256) lse_pick_fwd_kernel(const T* __restrict__ logits,
+                                                          const long long* __restrict__ tgt, float* __restrict__ lse_out,
+                                                          float* __restrict__ picked, int rows, int D) {
   __shared__ float sh[8];
   const int row = blockIdx.x;
   const T* xr = logits + (size_t)row * D;
@@ -323,37 +325,37 @@ __global__ void __launch_bounds__(256) ce_fwd_kernel(const T* __restrict__ logit
   s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
   const float gs = block_sum<8>(s, sh);
   if (threadIdx.x == 0) {
-    const float lse = gm + logf(gs);
     const long long t = tgt[row];
-    lse_out[row] = lse;
-    loss[row] = (t == ignore_index || t < 0 || t >= D) ? 0.f : lse - to_f<T>(xr[t]);
+    lse_out[row] = gm + logf(gs);
+    picked[row] = (t >= 0 && t < D) ? to_f<T>(xr[t]) : 0.f;
   }
 }
-// dlogits = (softmax - onehot) * gscale[0] * scale
+// dlogits = exp(logits - lse) * g_lse[row] + onehot(target) * g_pick[row]
 template <typename T>
-__global__ void __launch_bounds__(256) ce_bwd_kernel(const T* __restrict__ logits, const long long* __restrict__ tgt,
-                                                    const float* __restrict__ lse, const float* __restrict__ gscale,
-                                                    T* __restrict__ dlogits, int rows, int D, float scale,
-                                                    long long ignore_index, int g_per_row) {
+__global__ void __launch_bounds__(256) lse_pick_bwd_kernel(const T* __restrict__ logits,
+                                                          const long long* __restrict__ tgt,
+                                                          const float* __restrict__ lse, const float* __restrict__ g_lse,
+                                                          const float* __restrict__ g_pick, T* __restrict__ dlogits,
+                                                          int rows, int D) {
   const int row = blockIdx.x;
   const T* xr = logits + (size_t)row * D;
   T* dr = dlogits + (size_t)row * D;
   const float l = lse[row];
   const long long t = tgt[row];
-  const bool ign = (t == ignore_index || t < 0 || t >= D);
-  const float g = (gscale ? gscale[g_per_row ? row : 0] : 1.f) * scale * (ign ? 0.f : 1.f);
+  const float gl = g_lse ? g_lse[row] : 0.f;
+  const float gp = g_pick ? g_pick[row] : 0.f;
   constexpr int V = Vec<T>::N;
   if ((D % V) == 0) {
     for (int c = threadIdx.x * V; c < D; c += blockDim.x * V) {
       float v[V], o[V];
       load_vec<T>(xr + c, v);
 #pragma unroll
-      for (int j = 0; j < V; ++j) o[j] = (__expf(v[j] - l) - ((c + j) == t ? 1.f : 0.f)) * g;
+      for (int j = 0; j < V; ++j) o[j] = __expf(v[j] - l) * gl + ((c + j) == t ? gp : 0.f);
       store_vec<T>(dr + c, o);
     }
   } else {
     for (int c = threadIdx.x; c < D; c += blockDim.x)
-      dr[c] = from_f<T>((__expf(to_f<T>(xr[c]) - l) - (c == t ? 1.f : 0.f)) * g);
+      dr[c] = from_f<T>(__expf(to_f<T>(xr[c]) - l) * gl + (c == t ? gp : 0.f));
   }
 }
 
@@ -781,20 +783,20 @@ int nb_softmax(const void* x, void* y, int rows, int D, int log, int dtype, void
   return CHECK_LAUNCH();
 }
 
-int nb_ce_fwd(const void* logits, const long long* tgt, float* loss, float* lse, int rows, int D, long long ignore,
-              int dtype, void* stream) {
+int nb_lse_pick_fwd(const void* logits, const long long* tgt, float* lse, float* picked, int rows, int D, int dtype,
+                    void* stream) {
   if (rows <= 0) return 0;
-  if (dtype) ce_fwd_kernel<bf16><<<rows, 256, 0, STREAM>>>((const bf16*)logits, tgt, loss, lse, rows, D, ignore);
-  else ce_fwd_kernel<float><<<rows, 256, 0, STREAM>>>((const float*)logits, tgt, loss, lse, rows, D, ignore);
+  if (dtype) lse_pick_fwd_kernel<bf16><<<rows, 256, 0, STREAM>>>((const bf16*)logits, tgt, lse, picked, rows, D);
+  else lse_pick_fwd_kernel<float><<<rows, 256, 0, STREAM>>>((const float*)logits, tgt, lse, picked, rows, D);
   return CHECK_LAUNCH();
 }
-int nb_ce_bwd(const void* logits, const long long* tgt, const float* lse, const float* gscale, void* dlogits, int rows,
-              int D, float scale, long long ignore, int g_per_row, int dtype, void* stream) {
+int nb_lse_pick_bwd(const void* logits, const long long* tgt, const float* lse, const float* g_lse, const float* g_pick,
+                    void* dlogits, int rows, int D, int dtype, void* stream) {
   if (rows <= 0) return 0;
   if (dtype)
-    ce_bwd_kernel<bf16><<<rows, 256, 0, STREAM>>>((const bf16*)logits, tgt, lse, gscale, (bf16*)dlogits, rows, D, scale, ignore, g_per_row);
+    lse_pick_bwd_kernel<bf16><<<rows, 256, 0, STREAM>>>((const bf16*)logits, tgt, lse, g_lse, g_pick, (bf16*)dlogits, rows, D);
   else
-    ce_bwd_kernel<float><<<rows, 256, 0, STREAM>>>((const float*)logits, tgt, lse, gscale, (float*)dlogits, rows, D, scale, ignore, g_per_row);
+    lse_pick_bwd_kernel<float><<<rows, 256, 0, STREAM>>>((const float*)logits, tgt, lse, g_lse, g_pick, (float*)dlogits, rows, D);
   return CHECK_LAUNCH();
 }
 

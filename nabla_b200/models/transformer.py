@@ -1,0 +1,121 @@
+"""Decoder-only pre-LayerNorm transformer (the dp x tp benchmark model).
+
+Parameters are a plain pytree of Tensors; tensor parallelism is expressed only through their
+shardings (Megatron layout): ``wqkv``/``w1``/``lm_head`` are column-parallel ``P(None, 'tp')``,
+``wo``/``w2`` row-parallel ``P('tp', None)``, the batch is ``P('dp', None)``. The sharding
+propagation inserts the collectives. ``wqkv`` columns are ordered (head, {q,k,v}, head_dim) so
+that splitting the column dim splits heads.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Any
+
+from ..core.tensor.api import Tensor
+from ..nn import functional as F
+from ..ops import fused
+from ..ops.creation import arange, gaussian, ones, zeros
+from ..ops.view import gather, reshape
+from ..types import DType
+
+
+@dataclass
+class TransformerConfig:
+    n_layers: int = 24
+    d_model: int = 2048
+    n_heads: int = 16
+    d_ff: int = 8192
+    vocab: int = 32000
+    max_seq: int = 2048
+    dtype: DType = DType.bfloat16
+    init_std: float = 0.02
+
+    @property
+    def head_dim(self) -> int:
+        return self.d_model // self.n_heads
+
+    def num_params(self) -> int:
+        d, f, v = self.d_model, self.d_ff, self.vocab
+        per_layer = 4 * d * d + 4 * d + 2 * d * f + f + d + 4 * d
+        return self.n_layers * per_layer + 2 * v * d + self.max_seq * d + 2 * d
+
+    def flops_per_token(self, seq: int) -> float:
+        """Training FLOPs per token: 6 x matmul parameters + causal attention."""
+        d, f, v = self.d_model, self.d_ff, self.vocab
+        mm = self.n_layers * (4 * d * d + 2 * d * f) + v * d
+        attn = self.n_layers * 2 * seq * d      # QK^T and PV, causal halves the 4*s*d
+        return 6.0 * mm + 3.0 * attn
+
+
+def init_params(cfg: TransformerConfig, mesh=None, tp_axis: str | None = "tp", device=None) -> dict[str, Any]:
+    """Random-normal weights (std ``init_std``), zero biases, unit LayerNorm gains."""
+    dt = cfg.dtype
+    d, f, v = cfg.d_model, cfg.d_ff, cfg.vocab
+
+    def col(t):   # split output features
+        return t.shard(mesh, (None, tp_axis)) if mesh is not None and tp_axis else t
+
+    def row(t):   # split input features
+        return t.shard(mesh, (tp_axis, None)) if mesh is not None and tp_axis else t
+
+    def vec_col(t):
+        return t.shard(mesh, (tp_axis,)) if mesh is not None and tp_axis else t
+
+    def rep(t):
+        return t.shard(mesh, tuple(None for _ in t.shape)) if mesh is not None else t
+
+    def w(shape, std=cfg.init_std):
+        return gaussian(shape, 0.0, std, dtype=dt, device=device)
+
+    layers = []
+    out_std = cfg.init_std / math.sqrt(2 * cfg.n_layers)
+    for _ in range(cfg.n_layers):
+        layers.append({
+            "ln1_g": rep(ones((d,), dtype=dt, device=device)), "ln1_b": rep(zeros((d,), dtype=dt, device=device)),
+            "wqkv": col(w((d, 3 * d))), "bqkv": vec_col(zeros((3 * d,), dtype=dt, device=device)),
+            "wo": row(w((d, d), out_std)), "bo": rep(zeros((d,), dtype=dt, device=device)),
+            "ln2_g": rep(ones((d,), dtype=dt, device=device)), "ln2_b": rep(zeros((d,), dtype=dt, device=device)),
+            "w1": col(w((d, f))), "b1": vec_col(zeros((f,), dtype=dt, device=device)),
+            "w2": row(w((f, d), out_std)), "b2": rep(zeros((d,), dtype=dt, device=device)),
+        })
+    return {
+        "tok_emb": rep(w((v, d))), "pos_emb": rep(w((cfg.max_seq, d))),
+        "layers": layers,
+        "lnf_g": rep(ones((d,), dtype=dt, device=device)), "lnf_b": rep(zeros((d,), dtype=dt, device=device)),
+        "lm_head": col(w((d, v))),
+    }
+
+
+def block(x: Tensor, p: dict[str, Tensor], cfg: TransformerConfig) -> Tensor:
+    h = F.layer_norm(x, p["ln1_g"], p["ln1_b"])
+    qkv = F.linear(h, p["wqkv"], p["bqkv"])
+    a = fused.packed_self_attention(qkv, cfg.head_dim, causal=True)
+    x = x + F.linear(a, p["wo"], p["bo"])
+    h = F.layer_norm(x, p["ln2_g"], p["ln2_b"])
+    m = F.linear(h, p["w1"], p["b1"], activation="gelu")
+    return x + F.linear(m, p["w2"], p["b2"])
+
+
+def forward(params: dict[str, Any], tokens: Tensor, cfg: TransformerConfig) -> Tensor:
+    """tokens (B, S) int64 -> logits (B, S, vocab)."""
+    S = int(tokens.shape[1])
+    x = gather(params["tok_emb"], tokens, axis=0)
+    pos = params["pos_emb"]
+    if int(pos.shape[0]) != S:
+        pos = pos[:S]
+    x = x + pos
+    for p in params["layers"]:
+        x = block(x, p, cfg)
+    x = F.layer_norm(x, params["lnf_g"], params["lnf_b"])
+    return F.linear(x, params["lm_head"])
+
+
+def loss_fn(params: dict[str, Any], tokens: Tensor, targets: Tensor, cfg: TransformerConfig) -> Tensor:
+    """Mean next-token cross-entropy over all positions (fp32 scalar)."""
+    from ..ops.reduction import reduce_sum
+
+    logits = forward(params, tokens, cfg)
+    rows = fused.cross_entropy_rows(logits, targets)
+    n = int(tokens.shape[0]) * int(tokens.shape[1])
+    return reduce_sum(rows) * (1.0 / n)

@@ -27,8 +27,8 @@ def _L():
             "nb_colsum_nparts": [c_int],
             "nb_colsum": [c_vp] * 3 + [c_int] * 4 + [c_vp],
             "nb_softmax": [c_vp, c_vp, c_int, c_int, c_int, c_int, c_vp],
-            "nb_ce_fwd": [c_vp] * 4 + [c_int, c_int, c_ll, c_int, c_vp],
-            "nb_ce_bwd": [c_vp] * 5 + [c_int, c_int, c_f, c_ll, c_int, c_int, c_vp],
+            "nb_lse_pick_fwd": [c_vp] * 4 + [c_int, c_int, c_int, c_vp],
+            "nb_lse_pick_bwd": [c_vp] * 6 + [c_int, c_int, c_int, c_vp],
             "nb_adamw": [c_vp] * 7 + [c_ll] + [c_f] * 8 + [c_vp, c_int, c_int, c_vp],
             "nb_sgd": [c_vp] * 5 + [c_ll] + [c_f] * 4 + [c_int, c_int, c_vp],
             "nb_embedding_gather": [c_vp] * 3 + [c_int] * 4 + [c_vp],
@@ -135,27 +135,27 @@ def softmax(x: torch.Tensor, log: bool = False) -> torch.Tensor:
     return y.view(x.shape)
 
 
-def cross_entropy_fwd(logits: torch.Tensor, targets: torch.Tensor, ignore_index: int = -100):
+def lse_pick_fwd(logits: torch.Tensor, targets: torch.Tensor):
+    """Per row: (logsumexp(logits), logits[target] or 0 when the target is outside [0, D))."""
     D = logits.shape[-1]
     l2 = logits.contiguous().view(-1, D)
     t = targets.contiguous().view(-1).to(torch.int64)
     rows = l2.shape[0]
-    loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
     lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
-    _ok(_L().nb_ce_fwd(ptr(l2), ptr(t), ptr(loss), ptr(lse), rows, D, ignore_index, _dt(logits), stream_ptr()), "ce_fwd")
-    return loss, lse
+    picked = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    _ok(_L().nb_lse_pick_fwd(ptr(l2), ptr(t), ptr(lse), ptr(picked), rows, D, _dt(logits), stream_ptr()), "lse_pick_fwd")
+    return lse.view(targets.shape), picked.view(targets.shape)
 
 
-def cross_entropy_bwd(logits: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor, gscale: torch.Tensor | None,
-                      scale: float, ignore_index: int = -100) -> torch.Tensor:
+def lse_pick_bwd(logits: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor, g_lse, g_pick) -> torch.Tensor:
     D = logits.shape[-1]
     l2 = logits.contiguous().view(-1, D)
     t = targets.contiguous().view(-1).to(torch.int64)
     d = torch.empty_like(l2)
-    gs = gscale.reshape(-1).to(torch.float32).contiguous() if gscale is not None else None
-    per_row = 1 if (gs is not None and gs.numel() == l2.shape[0] and l2.shape[0] > 1) else 0
-    _ok(_L().nb_ce_bwd(ptr(l2), ptr(t), ptr(lse), ptr(gs), ptr(d), l2.shape[0], D, float(scale), ignore_index, per_row,
-                       _dt(logits), stream_ptr()), "ce_bwd")
+    gl = g_lse.reshape(-1).float().contiguous() if g_lse is not None else None
+    gp = g_pick.reshape(-1).float().contiguous() if g_pick is not None else None
+    _ok(_L().nb_lse_pick_bwd(ptr(l2), ptr(t), ptr(lse.reshape(-1).float().contiguous()), ptr(gl), ptr(gp), ptr(d),
+                             l2.shape[0], D, _dt(logits), stream_ptr()), "lse_pick_bwd")
     return d.view(logits.shape)
 
 

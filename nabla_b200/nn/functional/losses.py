@@ -35,8 +35,7 @@ def cross_entropy_loss(logits: Tensor, targets: Tensor, axis: int = -1) -> Tenso
 
     int_targets = len(targets.shape) < len(logits.shape)
     last = axis in (-1, logits.rank - 1)
-    vocab_sharded = logits._impl.sharding is not None and bool(logits._impl.sharding.dim_specs[-1].axes)
-    if int_targets and last and use_fused(logits) and not vocab_sharded:
+    if int_targets and last and use_fused(logits):
         rows = fused.cross_entropy_rows(logits, targets)
         return reduce_sum(rows) / float(int(logits.shape[0]))
     return cross_entropy_loss_reference(logits, targets, axis)

@@ -238,6 +238,10 @@ class Operation:
             impl.output_index = i
             node.out_refs.append(weakref.ref(impl))
             outs.append(Tensor(impl=impl))
+        if traced and len(outs) > 1:
+            # auxiliary outputs saved for the backward (pre-activations, statistics) must live
+            # as long as the primary output does, even if the caller drops their handles
+            outs[0]._impl._keepalive = [o._impl for o in outs[1:]]
         if config.get_flag("EAGER_MAX_GRAPH") and not config.get_flag("TRACING"):
             from ..core.graph.engine import GRAPH
 

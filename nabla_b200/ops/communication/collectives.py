@@ -404,6 +404,35 @@ class TransferOp(Operation):
         return _transfer_op(tangents[0], device=kwargs["device"])
 
 
+class RelabelOp(_LayoutOp):
+    """Reinterpret the per-device buffers under another spec of the same local shapes (no data
+    movement). Used to turn "pending partial sum" labels into plain per-device values before a
+    max/min combination, and back."""
+
+    def out_spec(self, x, mesh, kwargs):
+        return kwargs["spec"].clone()
+
+    def execute(self, node):
+        mesh = self._mesh(node)
+        return [self._shards(node.input_impls()[0], mesh)]
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        x = primals[0]
+        sp = x._impl.sharding.clone()
+        sp.partial_sum_axes = set()
+        return (reshard_to_spec(cot, sp) if needs_reshard(cot._impl.sharding, sp) else cot,)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return _relabel_op(tangents[0], **kwargs)
+
+
+_relabel_op = RelabelOp()
+
+
+def relabel_spec(x, spec: ShardingSpec):
+    return _relabel_op(x, spec=spec)
+
+
 _shard_op, _all_gather_op, _gather_all_op = ShardOp(), AllGatherOp(), GatherAllAxesOp()
 _all_reduce_op, _reduce_scatter_op, _ppermute_op, _transfer_op = (AllReduceOp(), ReduceScatterOp(), PPermuteOp(),
                                                                   TransferOp())

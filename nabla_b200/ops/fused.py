@@ -440,74 +440,176 @@ class SDPABwdOp(Operation):
         return OpShardingRule(ins, [dict(q), dict(kv), dict(kv)])
 
 
-# ================================================================ cross entropy
-class CrossEntropyOp(_Fused):
-    """Per-row ``lse(logits) - logits[target]`` for integer targets. Outputs (loss fp32 [rows...], lse)."""
+class PackedSelfAttentionOp(_Fused):
+    """Causal/non-causal self-attention on a packed projection ``qkv`` of shape (B, S, H*3*hd)
+    whose last dim is laid out (head, {q,k,v}, head_dim). Output (B, S, H*hd) plus the row
+    log-sum-exp (B, H, S) for the backward. Nothing is transposed or copied: the kernel reads
+    q/k/v through strides and writes the heads side by side. Splitting the last dim over a
+    mesh axis splits the heads (tensor parallelism)."""
 
-    def kernel(self, logits, targets, *, ignore_index: int = -100):
+    def kernel(self, qkv, *, head_dim: int, causal: bool = True, scale: float | None = None):
+        B, S, W = qkv.shape
+        H = W // (3 * head_dim)
+        sc = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+        if qkv.device.type == "meta":
+            return (torch.empty((B, S, H * head_dim), dtype=qkv.dtype, device="meta"),
+                    torch.empty((B, H, S), dtype=torch.float32, device="meta"))
+        v5 = qkv.view(B, S, H, 3, head_dim)
+        q, k, v = (v5[:, :, :, i, :].permute(0, 2, 1, 3) for i in range(3))     # (B,H,S,hd) views
+        if _native(qkv):
+            from ..native import attention
+
+            if attention.supported(q, k, v, None, 0.0):
+                o, lse = attention.sdpa_fwd(q, k, v, causal=causal, scale=sc)   # o: (B,H,S,hd) view of (B,S,H,hd)
+                return o.permute(0, 2, 1, 3).reshape(B, S, H * head_dim), lse
+        o, lse = _sdpa.kernel(q, k, v, causal=causal, scale=sc)
+        return o.permute(0, 2, 1, 3).reshape(B, S, H * head_dim), lse
+
+    def sharding_rule(self, input_shapes, output_shapes, **kw):
+        return OpShardingRule([{0: ["b"], 1: ["bcast_s"], 2: ["h"]}],
+                              [{0: ["b"], 1: ["bcast_s"], 2: ["h"]}, {0: ["b"], 1: ["h"], 2: ["bcast_s"]}])
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        do = cot[0]
+        if do is None:
+            return (None,)
+        o, lse = outputs
+        return (_packed_attn_bwd_op(do, primals[0], o, lse, **kwargs),)
+
+    def decomposed(self, qkv, *, head_dim, causal=True, scale=None):
+        from ..nn.functional.layers import scaled_dot_product_attention_reference as ref
+        from .creation import zeros
+        from .view import reshape, slice_tensor, squeeze, swap_axes
+
+        B, S, W = (int(d) for d in qkv.shape)
+        H = W // (3 * head_dim)
+        v5 = reshape(qkv, (B, S, H, 3, head_dim))
+        parts = [swap_axes(squeeze(slice_tensor(v5, (0, 0, 0, i, 0), (B, S, H, 1, head_dim)), axis=3), 1, 2)
+                 for i in range(3)]
+        o = ref(parts[0], parts[1], parts[2], is_causal=causal, scale=scale)
+        return reshape(swap_axes(o, 1, 2), (B, S, H * head_dim)), zeros((B, H, S), dtype=DType.float32, device=qkv.device)
+
+
+class PackedSelfAttentionBwdOp(Operation):
+    def kernel(self, do, qkv, o, lse, *, head_dim: int, causal: bool = True, scale: float | None = None):
+        B, S, W = qkv.shape
+        H = W // (3 * head_dim)
+        sc = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+        if qkv.device.type == "meta":
+            return torch.empty_like(qkv)
+        v5 = qkv.view(B, S, H, 3, head_dim)
+        q, k, v = (v5[:, :, :, i, :].permute(0, 2, 1, 3) for i in range(3))
+        do4 = do.reshape(B, S, H, head_dim).permute(0, 2, 1, 3)
+        o4 = o.reshape(B, S, H, head_dim).permute(0, 2, 1, 3)
+        dqkv = torch.empty_like(qkv)
+        d5 = dqkv.view(B, S, H, 3, head_dim)
+        if _native(qkv):
+            from ..native import attention
+
+            if attention.supported(q, k, v, None, 0.0) and attention.bwd_available():
+                attention.sdpa_bwd(do4, q, k, v, o4, lse, causal=causal, scale=sc,
+                                   out=tuple(d5[:, :, :, i, :].permute(0, 2, 1, 3) for i in range(3)))
+                return dqkv
+        dq, dk, dv = _sdpa_bwd_op.kernel(do4, q, k, v, o4, lse, causal=causal, scale=sc)
+        d5[:, :, :, 0, :] = dq.permute(0, 2, 1, 3)
+        d5[:, :, :, 1, :] = dk.permute(0, 2, 1, 3)
+        d5[:, :, :, 2, :] = dv.permute(0, 2, 1, 3)
+        return dqkv
+
+    def sharding_rule(self, input_shapes, output_shapes, **kw):
+        m = {0: ["b"], 1: ["bcast_s"], 2: ["h"]}
+        return OpShardingRule([dict(m), dict(m), dict(m), {0: ["b"], 1: ["h"], 2: ["bcast_s"]}], [dict(m)])
+
+
+# ================================================================ cross entropy
+class LsePickOp(_Fused):
+    """Cross-entropy building block. Per row of ``logits`` (..., V): ``lse = logsumexp`` and
+    ``picked = logits[target - vocab_offset]`` (0 when that index falls outside this shard).
+    ``loss = lse - picked``; with the vocabulary split over a mesh axis the caller combines the
+    shards' (lse, picked) with max / sum reductions on small per-row vectors."""
+
+    def kernel(self, logits, targets, *, vocab_offset: int = 0):
+        t = targets.long() - vocab_offset
         if logits.device.type != "meta" and _native(logits) and logits.numel():
             from ..native import kernels
 
-            loss, lse = kernels.cross_entropy_fwd(logits, targets, ignore_index)
-            return loss.view(targets.shape), lse.view(targets.shape)
+            return kernels.lse_pick_fwd(logits, t)
         lf = logits.float()
         lse = torch.logsumexp(lf, dim=-1)
-        t = targets.long()
-        valid = (t != ignore_index) & (t >= 0) & (t < logits.shape[-1])
-        picked = torch.gather(lf, -1, t.clamp(0, logits.shape[-1] - 1).unsqueeze(-1)).squeeze(-1)
-        loss = torch.where(valid, lse - picked, torch.zeros_like(lse))
-        return loss, lse
+        V = logits.shape[-1]
+        inr = (t >= 0) & (t < V)
+        picked = torch.gather(lf, -1, t.clamp(0, V - 1).unsqueeze(-1)).squeeze(-1)
+        return lse, torch.where(inr, picked, torch.zeros_like(picked))
+
+    def shard_kwargs(self, kwargs, node, shard_idx, device_id):
+        lg = node.input_impls()[0]
+        sp = lg.sharding
+        if sp is None or not sp.dim_specs[-1].axes:
+            return kwargs
+        from ..core.sharding.spec import local_slice, shard_index
+
+        idx, tot = shard_index(sp, len(sp.dim_specs) - 1, device_id)
+        start, _ = local_slice(lg._shape[-1], idx, tot)
+        return {**kwargs, "vocab_offset": kwargs.get("vocab_offset", 0) + start}
 
     def sharding_rule(self, input_shapes, output_shapes, **kw):
         r = len(input_shapes[0])
         rows = {i: [f"d{i}"] for i in range(r - 1)}
-        return OpShardingRule([{**rows, r - 1: ["bcast_vocab"]}, dict(rows)], [dict(rows), dict(rows)])
+        # the vocabulary factor "v" may be sharded: outputs are then per-shard partial statistics
+        return OpShardingRule([{**rows, r - 1: ["v"]}, dict(rows)], [dict(rows), dict(rows)])
 
     def vjp_rule(self, primals, cot, outputs, kwargs):
         logits, targets = primals
-        g = cot[0]
-        if g is None:
+        g_lse, g_pick = cot
+        if g_lse is None and g_pick is None:
             return (None, None)
-        return (_ce_bwd(g, logits, targets, outputs[1], ignore_index=kwargs.get("ignore_index", -100)), None)
+        from .creation import zeros_like
 
-    def decomposed(self, logits, targets, *, ignore_index=-100):
-        from .reduction import reduce_sum
-        from .unary import cast, logsoftmax
-        from .view import gather, reshape, unsqueeze
+        lse = outputs[0]
+        if lse._impl.sharding is not None and lse._impl.sharding.partial_sum_axes:
+            # per-shard statistic, not a pending sum: hand the local values to the backward
+            lse = _as_values(lse, set(lse._impl.sharding.partial_sum_axes))
+        g_lse = g_lse if g_lse is not None else zeros_like(lse)
+        g_pick = g_pick if g_pick is not None else zeros_like(lse)
+        return (_lse_pick_bwd_op(logits, targets, lse, g_lse, g_pick, vocab_offset=kwargs.get("vocab_offset", 0)), None)
 
-        ls = logsoftmax(cast(logits, DType.float32), axis=-1)
-        v = logits._impl.global_shape[-1]
-        flat = reshape(ls, (-1, v))
-        t = reshape(targets, (-1,))
-        from .creation import arange
+    def decomposed(self, logits, targets, *, vocab_offset=0):
         from .comparison import equal
+        from .creation import arange
+        from .reduction import reduce_max, reduce_sum
+        from .unary import cast, exp, log
+        from .view import unsqueeze
 
-        onehot = cast(equal(unsqueeze(cast(t, DType.int64), axis=-1),
-                            arange(0, v, 1, dtype=DType.int64, device=logits.device)), DType.float32)
-        loss = -reduce_sum(flat * onehot, axis=-1)
-        loss = reshape(loss, tuple(targets._impl.global_shape))
-        return loss, loss
+        lf = cast(logits, DType.float32)
+        m = reduce_max(lf, axis=-1, keepdims=True)
+        lse = log(reduce_sum(exp(lf - m), axis=-1)) + reduce_max(lf, axis=-1)
+        v = logits._impl.global_shape[-1]
+        oh = cast(equal(unsqueeze(cast(targets, DType.int64) - vocab_offset, axis=-1),
+                        arange(0, v, 1, dtype=DType.int64, device=logits.device)), DType.float32)
+        return lse, reduce_sum(lf * oh, axis=-1)
 
 
-class CrossEntropyBwdOp(Operation):
-    def kernel(self, g, logits, targets, lse, *, ignore_index: int = -100):
+class LsePickBwdOp(Operation):
+    def kernel(self, logits, targets, lse, g_lse, g_pick, *, vocab_offset: int = 0):
+        t = targets.long() - vocab_offset
         if logits.device.type != "meta" and _native(logits) and logits.numel():
             from ..native import kernels
 
-            return kernels.cross_entropy_bwd(logits, targets, lse.reshape(-1), g.reshape(-1), 1.0, ignore_index)
+            return kernels.lse_pick_bwd(logits, t, lse, g_lse, g_pick)
         lf = logits.float()
-        p = torch.exp(lf - lse.float().unsqueeze(-1))
-        t = targets.long()
-        valid = ((t != ignore_index) & (t >= 0) & (t < logits.shape[-1])).unsqueeze(-1)
-        oh = torch.zeros_like(p).scatter_(-1, t.clamp(0, logits.shape[-1] - 1).unsqueeze(-1), 1.0)
-        d = (p - oh) * g.float().unsqueeze(-1) * valid
-        return d.to(logits.dtype)
+        V = logits.shape[-1]
+        p = torch.exp(lf - lse.float().unsqueeze(-1)) * g_lse.float().unsqueeze(-1)
+        inr = ((t >= 0) & (t < V)).unsqueeze(-1)
+        oh = torch.zeros_like(p).scatter_(-1, t.clamp(0, V - 1).unsqueeze(-1), 1.0) * inr
+        return (p + oh * g_pick.float().unsqueeze(-1)).to(logits.dtype)
+
+    shard_kwargs = LsePickOp.shard_kwargs
 
     def sharding_rule(self, input_shapes, output_shapes, **kw):
-        r = len(input_shapes[1])
+        r = len(input_shapes[0])
         rows = {i: [f"d{i}"] for i in range(r - 1)}
-        return OpShardingRule([dict(rows), {**rows, r - 1: ["bcast_vocab"]}, dict(rows), dict(rows)],
-                              [{**rows, r - 1: ["bcast_vocab"]}])
+        full = {**rows, r - 1: ["v"]}
+        return OpShardingRule([dict(full), dict(rows), dict(rows), dict(rows), dict(rows)], [dict(full)])
 
 
 # ================================================================ optimizers
@@ -621,12 +723,32 @@ class DropoutOp(Operation):
 _linear, _dact, _bias_grad = LinearOp(), DActMulOp(), BiasGradOp()
 _ln, _ln_bwd_op = LayerNormOp(), LayerNormBwdOp()
 _sdpa, _sdpa_bwd_op = SDPAOp(), SDPABwdOp()
-_ce, _ce_bwd_op = CrossEntropyOp(), CrossEntropyBwdOp()
+_lse_pick, _lse_pick_bwd_op = LsePickOp(), LsePickBwdOp()
+_packed_attn, _packed_attn_bwd_op = PackedSelfAttentionOp(), PackedSelfAttentionBwdOp()
 _adamw, _sgd, _dropout = AdamWStepOp(), SGDStepOp(), DropoutOp()
 
 
+def _contracting_sharded(x: Tensor, w: Tensor) -> bool:
+    xs, ws = x._impl.sharding, w._impl.sharding
+    return bool((xs is not None and xs.dim_specs[-1].axes) or (ws is not None and ws.dim_specs[0].axes))
+
+
 def linear(x, w, b=None, activation: str | None = None) -> Tensor:
-    """Fused ``act(x @ w + b)`` with ``w`` of shape (in, out)."""
+    """Fused ``act(x @ w + b)`` with ``w`` of shape (in, out).
+
+    When the contraction dimension is split over mesh axes (row-parallel layer) the product is
+    a pending partial sum: bias and activation must see the reduced value, so they are applied
+    after it (the bias add triggers the all-reduce)."""
+    if (b is not None or activation is not None) and _contracting_sharded(x, w):
+        y = _linear(x, w, activation=None)
+        if b is not None:
+            y = y + b
+        if activation is not None:
+            from . import unary
+
+            y = {"relu": unary.relu, "gelu": unary.gelu, "silu": unary.silu,
+                 "gelu_tanh": lambda t: unary.gelu(t, approximate="tanh")}[activation](y)
+        return y
     args = (x, w) if b is None else (x, w, b)
     out = _linear(*args, activation=activation)
     return out[0] if activation is not None else out
@@ -659,17 +781,52 @@ def scaled_dot_product_attention(q, k, v, mask=None, *, causal: bool = False, sc
     return _sdpa(*args, causal=bool(causal), scale=scale, dropout_p=float(dropout_p))[0]
 
 
+def packed_self_attention(qkv, head_dim: int, causal: bool = True, scale: float | None = None) -> Tensor:
+    return _packed_attn(qkv, head_dim=int(head_dim), causal=bool(causal), scale=scale)[0]
+
+
 def _sdpa_bwd(*args, causal, scale, has_mask):
     return _sdpa_bwd_op(*args, causal=causal, scale=scale, has_mask=has_mask)
 
 
-def cross_entropy_rows(logits, targets, ignore_index: int = -100) -> Tensor:
-    """Per-row negative log-likelihood (fp32) for integer class targets."""
-    return _ce(logits, targets, ignore_index=int(ignore_index))[0]
+def cross_entropy_rows(logits, targets, ignore_index: int | None = None) -> Tensor:
+    """Per-row negative log-likelihood (fp32) for integer class targets; works with the class
+    dimension split over mesh axes (vocabulary-parallel)."""
+    lse, picked = _lse_pick(logits, targets, vocab_offset=0)
+    sp = logits._impl.sharding
+    if sp is not None and sp.dim_specs[-1].axes:
+        from .communication import all_reduce
+        from .unary import exp, log
+
+        axes = set(sp.dim_specs[-1].axes)
+        # lse / picked come out marked as pending sums over the vocabulary axes; they are
+        # per-shard statistics, so combine them explicitly: max for the shift, sum for the rest
+        from .unary import stop_gradient
+
+        # the shift is only for numerical range: its derivative is exactly zero
+        m = stop_gradient(all_reduce(_as_values(lse, axes), reduce_axes=axes, reduce_op="max"))
+        ssum = all_reduce(_as_values(exp(_as_values(lse, axes) - m), axes), reduce_axes=axes)
+        lse = m + log(ssum)
+        picked = all_reduce(_as_values(picked, axes), reduce_axes=axes)
+    loss = lse - picked
+    if ignore_index is not None:
+        from .comparison import not_equal
+        from .unary import cast
+
+        loss = loss * cast(not_equal(targets, ignore_index), DType.float32)
+    return loss
 
 
-def _ce_bwd(g, logits, targets, lse, ignore_index):
-    return _ce_bwd_op(g, logits, targets, lse, ignore_index=ignore_index)
+def _as_values(t: Tensor, axes) -> Tensor:
+    """Reinterpret a tensor whose spec marks ``axes`` as pending sums as plain per-device values."""
+    sp = t._impl.sharding
+    if sp is None or not (sp.partial_sum_axes & set(axes)):
+        return t
+    new = sp.clone()
+    new.partial_sum_axes = set(sp.partial_sum_axes) - set(axes)
+    from .communication import relabel_spec
+
+    return relabel_spec(t, new)
 
 
 def adamw_step_fused(p, g, m, v, step, *, lr, beta1, beta2, eps, weight_decay, bias_correction=True):

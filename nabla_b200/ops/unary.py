@@ -102,6 +102,28 @@ class GeluOp(UnaryOperation):
 _gelu = GeluOp()
 
 
+class StopGradientOp(UnaryOperation):
+    """Identity whose derivative is zero (``jax.lax.stop_gradient``)."""
+
+    partial_policy = "any"
+
+    def torch_fn(self, x):
+        return x
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        return (None,)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return None
+
+
+_stop_gradient = StopGradientOp()
+
+
+def stop_gradient(x) -> Tensor:
+    return _stop_gradient(ensure_tensor(x))
+
+
 class CastOp(Operation):
     """dtype conversion. Deliberately not partial-passthrough: rounding a partial sum and then
     summing differs from summing and then rounding."""

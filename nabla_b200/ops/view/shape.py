@@ -163,8 +163,9 @@ class ReshapeOp(ShapeOp):
         """factor maps + which input dims keep their sharding."""
         ins, outs = {}, {}
         for gi, gj in _reshape_groups(list(in_shape), list(out_shape)):
-            lead_i = gi[0] if gi else None
-            lead_j = gj[0] if gj else None
+            # the dimension that can keep a sharding is the first one of extent > 1 on each side
+            lead_i = next((d for d in gi if in_shape[d] != 1), gi[0] if gi else None)
+            lead_j = next((d for d in gj if out_shape[d] != 1), gj[0] if gj else None)
             for d in gi:
                 ins[d] = [f"bcast_r{d}"]
             for d in gj:
@@ -178,10 +179,13 @@ class ReshapeOp(ShapeOp):
             shards = 1
             if spec is not None and lead_i < len(spec.dim_specs):
                 shards = spec.dim_specs[lead_i].get_total_shards(spec.mesh)
-            others_sharded = spec is not None and any(spec.dim_specs[d].axes for d in gi[1:] if d < len(spec.dim_specs))
-            if (not others_sharded and in_shape[lead_i] % shards == 0 and out_shape[lead_j] % shards == 0
-                    and (in_shape[lead_i] // shards) * math.prod(in_shape[d] for d in gi[1:])
-                    == (out_shape[lead_j] // shards) * math.prod(out_shape[d] for d in gj[1:])):
+            others_sharded = spec is not None and any(spec.dim_specs[d].axes for d in gi
+                                                       if d != lead_i and d < len(spec.dim_specs))
+            # dims before the leads must be 1 so that the leads stay the major part
+            major_ok = all(in_shape[d] == 1 for d in gi if d < lead_i) and all(out_shape[d] == 1 for d in gj if d < lead_j)
+            if (not others_sharded and major_ok and in_shape[lead_i] % shards == 0 and out_shape[lead_j] % shards == 0
+                    and (in_shape[lead_i] // shards) * math.prod(in_shape[d] for d in gi if d != lead_i)
+                    == (out_shape[lead_j] // shards) * math.prod(out_shape[d] for d in gj if d != lead_j)):
                 ins[lead_i] = [f"g{lead_i}"]
                 outs[lead_j] = [f"g{lead_i}"]
         return ins, outs
