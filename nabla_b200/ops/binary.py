@@ -96,19 +96,26 @@ class PowOp(BinaryOperation):
     def torch_fn(self, a, b):
         return torch.pow(a, b)
 
-    def vjp_rule(self, primals, cot, outputs, kwargs):
+    @staticmethod
+    def _safe_log(a):
+        # d/db a^b = a^b log a is only defined for a > 0; elsewhere contribute 0 instead of NaN
+        from .comparison import greater
+        from .control_flow import where
+        from .creation import ones_like, zeros_like
         from .unary import log
 
+        pos = greater(a, 0.0)
+        return where(pos, log(where(pos, a, ones_like(a))), zeros_like(a))
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
         a, b = primals
         da = cot * b * pow(a, b - 1.0)
-        db = cot * outputs * log(a)
+        db = cot * outputs * self._safe_log(a)
         return (da, db)
 
     def jvp_rule(self, primals, tangents, outputs, kwargs):
-        from .unary import log
-
         a, b = primals
-        return tangents[0] * b * pow(a, b - 1.0) + tangents[1] * outputs * log(a)
+        return tangents[0] * b * pow(a, b - 1.0) + tangents[1] * outputs * self._safe_log(a)
 
 
 class OuterOp(Operation):

@@ -30,12 +30,10 @@ def constant(value, *, dtype=None, device=None) -> Tensor:
         t = value
     else:
         arr = np.asarray(value)
-        if dtype is None:
-            if arr.dtype == np.float64:
-                arr = arr.astype(np.float32)
-            elif arr.dtype == np.int64 and isinstance(value, (int, list, tuple)) and False:
-                pass
-        t = torch.from_numpy(np.ascontiguousarray(arr))
+        if dtype is None and arr.dtype == np.float64:
+            arr = arr.astype(np.float32)
+        # np.ascontiguousarray promotes a 0-d array to 1-d: restore the shape
+        t = torch.from_numpy(np.ascontiguousarray(arr)).reshape(arr.shape)
     dt, dev = defaults(dtype if dtype is not None else DType.from_torch(t.dtype), device)
     t = t.to(device=dev.to_torch(), dtype=dt.to_torch())
     return Tensor(buffers=[t])

@@ -614,8 +614,10 @@ class LsePickBwdOp(Operation):
 
 # ================================================================ optimizers
 class AdamWStepOp(Operation):
-    """One AdamW update: (p, g, m, v) -> (p', m', v'). ``step`` may be a python int (baked) or
-    a 0-d tensor (so compiled steps do not retrace when it advances)."""
+    """One AdamW update: (p, g, m, v[, hyper]) -> (p', m', v'). The step count is either a
+    python int baked into the op (``step_value``) or enters through the device vector
+    ``hyper`` = [lr, 1-b1^t, 1-b2^t, 1] built by ``AdamHyperOp`` from a 0-d step tensor, so a
+    compiled training step does not retrace when the counter advances."""
 
     def kernel(self, p, g, m, v, step=None, *, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float,
                step_value: int | None = None, bias_correction: bool = True):
@@ -623,11 +625,7 @@ class AdamWStepOp(Operation):
                 and g.dtype in (torch.bfloat16, torch.float32):
             from ..native import kernels
 
-            hyper = None
-            if step is not None and bias_correction:
-                s = step.reshape(()).float()
-                hyper = torch.stack([torch.full((), lr, device=p.device), 1 - beta1 ** s, 1 - beta2 ** s,
-                                     torch.ones((), device=p.device)]).float().contiguous()
+            hyper = step.contiguous() if (step is not None and bias_correction) else None
             return kernels.adamw(p, g, m, v, lr=lr, b1=beta1, b2=beta2, eps=eps, wd=weight_decay,
                                  step=step_value if bias_correction else None, hyper=hyper)
         gf, pf = g.float(), p.float()
@@ -635,8 +633,7 @@ class AdamWStepOp(Operation):
         vn = beta2 * v.float() + (1 - beta2) * gf * gf
         if bias_correction:
             if step is not None:
-                s = step.reshape(()).float()
-                bc1, bc2 = 1 - beta1 ** s, 1 - beta2 ** s
+                bc1, bc2 = step[1], step[2]
             else:
                 bc1, bc2 = 1 - beta1 ** step_value, 1 - beta2 ** step_value
         else:
@@ -829,9 +826,44 @@ def _as_values(t: Tensor, axes) -> Tensor:
     return relabel_spec(t, new)
 
 
+class AdamHyperOp(Operation):
+    """[lr, 1 - b1^t, 1 - b2^t, 1] as a device vector, computed once per step from the step
+    counter tensor and shared by every parameter's update kernel."""
+
+    def kernel(self, step, *, lr: float, beta1: float, beta2: float):
+        s = step.reshape(()).float()
+        one = torch.ones((), device=step.device)
+        return torch.stack([one * lr, 1 - beta1 ** s, 1 - beta2 ** s, one]).float()
+
+    def sharding_rule(self, input_shapes, output_shapes, **kw):
+        return OpShardingRule([{}], [{0: ["four"]}])
+
+
+_adam_hyper = AdamHyperOp()
+_hyper_cache: dict = {}
+
+
+def _hyper_for(step: Tensor, lr, beta1, beta2) -> Tensor:
+    key = (id(step._impl), lr, beta1, beta2)
+    hit = _hyper_cache.get(key)
+    if hit is not None and hit[0]() is step._impl:
+        return hit[1]
+    import weakref
+
+    h = _adam_hyper(step, lr=float(lr), beta1=float(beta1), beta2=float(beta2))
+    if len(_hyper_cache) > 64:
+        _hyper_cache.clear()
+    _hyper_cache[key] = (weakref.ref(step._impl), h)
+    return h
+
+
 def adamw_step_fused(p, g, m, v, step, *, lr, beta1, beta2, eps, weight_decay, bias_correction=True):
     if isinstance(step, Tensor):
-        return _adamw(p, g, m, v, step, lr=float(lr), beta1=float(beta1), beta2=float(beta2), eps=float(eps),
+        hyper = _hyper_for(step, lr, beta1, beta2) if bias_correction else None
+        if hyper is None:
+            return _adamw(p, g, m, v, lr=float(lr), beta1=float(beta1), beta2=float(beta2), eps=float(eps),
+                          weight_decay=float(weight_decay), step_value=1, bias_correction=False)
+        return _adamw(p, g, m, v, hyper, lr=float(lr), beta1=float(beta1), beta2=float(beta2), eps=float(eps),
                       weight_decay=float(weight_decay), step_value=None, bias_correction=bias_correction)
     return _adamw(p, g, m, v, lr=float(lr), beta1=float(beta1), beta2=float(beta2), eps=float(eps),
                   weight_decay=float(weight_decay), step_value=int(step), bias_correction=bias_correction)

@@ -38,10 +38,17 @@ class SplitOp(_SplitBase):
         return self._rule(len(input_shapes[0]), axis, len(sizes))
 
     def vjp_rule(self, primals, cot, outputs, kwargs):
-        from .creation import zeros_like
+        from .creation import zeros
         from .view import concatenate
 
-        cots = [c if c is not None else zeros_like(o) for c, o in zip(cot, outputs)]
+        x = primals[0]
+        shp = list(x._impl.global_shape)
+        ax = kwargs["axis"] + len(shp) if kwargs["axis"] < 0 else kwargs["axis"]
+        cots = []
+        for c, n in zip(cot, kwargs["sizes"]):
+            if c is None:   # this piece was not used downstream
+                c = zeros(tuple(shp[:ax] + [int(n)] + shp[ax + 1:]), dtype=x.dtype, device=x.device)
+            cots.append(c)
         return (concatenate(cots, axis=kwargs["axis"]),)
 
     def jvp_rule(self, primals, tangents, outputs, kwargs):
@@ -56,10 +63,14 @@ class UnbindOp(_SplitBase):
         return self._rule(len(input_shapes[0]), axis, input_shapes[0][axis], drop=True)
 
     def vjp_rule(self, primals, cot, outputs, kwargs):
-        from .creation import zeros_like
+        from .creation import zeros
         from .view import stack
 
-        cots = [c if c is not None else zeros_like(o) for c, o in zip(cot, outputs)]
+        x = primals[0]
+        shp = list(x._impl.global_shape)
+        ax = kwargs["axis"] + len(shp) if kwargs["axis"] < 0 else kwargs["axis"]
+        piece = tuple(shp[:ax] + shp[ax + 1:])
+        cots = [c if c is not None else zeros(piece, dtype=x.dtype, device=x.device) for c in cot]
         return (stack(cots, axis=kwargs["axis"]),)
 
     def jvp_rule(self, primals, tangents, outputs, kwargs):

@@ -13,6 +13,15 @@ from ..types import DType
 from .base import AxisOp, ReduceOperation, ensure_tensor
 
 
+def _empty_reduce(x, axis, keepdims, value):
+    shp = list(x.shape)
+    if keepdims:
+        shp[axis] = 1
+    else:
+        del shp[axis]
+    return torch.full(shp, value, dtype=x.dtype, device=x.device)
+
+
 class ReduceSumOp(ReduceOperation):
     def torch_reduce(self, x, axis, keepdims):
         if x.dtype == torch.bool:
@@ -32,13 +41,26 @@ class ReduceSumOp(ReduceOperation):
 
 
 class _ReduceExt(ReduceOperation):
+    def _global_extreme(self, y):
+        """The op's own output over a sharded axis is the per-shard extreme (labelled as a
+        pending reduction); the derivative needs the extreme over all shards."""
+        sp = y._impl.sharding
+        if sp is None or not sp.partial_sum_axes:
+            return y
+        from .communication import all_reduce, relabel_spec
+
+        axes = set(sp.partial_sum_axes)
+        plain = sp.clone()
+        plain.partial_sum_axes = set()
+        return all_reduce(relabel_spec(y, plain), reduce_axes=axes, reduce_op=self.collective_reduce_type)
+
     def vjp_rule(self, primals, cot, outputs, kwargs):
         from .comparison import equal
         from .unary import cast
         from .view import broadcast_to, unsqueeze
 
         x = primals[0]
-        y = outputs
+        y = self._global_extreme(outputs)
         if not kwargs.get("keepdims", False):
             cot = unsqueeze(cot, axis=kwargs["axis"])
             y = unsqueeze(y, axis=kwargs["axis"])
@@ -53,7 +75,8 @@ class _ReduceExt(ReduceOperation):
         from .view import broadcast_to, unsqueeze
 
         x = primals[0]
-        y = outputs if kwargs.get("keepdims", False) else unsqueeze(outputs, axis=kwargs["axis"])
+        y = self._global_extreme(outputs)
+        y = y if kwargs.get("keepdims", False) else unsqueeze(y, axis=kwargs["axis"])
         mask = cast(equal(x, broadcast_to(y, tuple(x._impl.global_shape))), x.dtype)
         count = _reduce_sum(mask, axis=kwargs["axis"], keepdims=True)
         return _reduce_sum(tangents[0] * mask / count, **kwargs)
@@ -63,6 +86,8 @@ class ReduceMaxOp(_ReduceExt):
     collective_reduce_type = "max"
 
     def torch_reduce(self, x, axis, keepdims):
+        if x.shape[axis] == 0:   # empty trailing shard: identity of max
+            return _empty_reduce(x, axis, keepdims, float("-inf"))
         return torch.amax(x, dim=axis, keepdim=keepdims)
 
 
@@ -70,6 +95,8 @@ class ReduceMinOp(_ReduceExt):
     collective_reduce_type = "min"
 
     def torch_reduce(self, x, axis, keepdims):
+        if x.shape[axis] == 0:
+            return _empty_reduce(x, axis, keepdims, float("inf"))
         return torch.amin(x, dim=axis, keepdim=keepdims)
 
 

@@ -226,7 +226,7 @@ def softmax(x: Tensor, axis: int = -1) -> Tensor:
     if _axis_is_sharded(x, axis):
         from .reduction import reduce_max, reduce_sum
 
-        m = reduce_max(x, axis=axis, keepdims=True)
+        m = stop_gradient(reduce_max(x, axis=axis, keepdims=True))   # shift only: derivative is exactly 0
         e = exp(x - m)
         return e / reduce_sum(e, axis=axis, keepdims=True)
     return _softmax(x, axis=axis)
@@ -237,7 +237,7 @@ def logsoftmax(x: Tensor, axis: int = -1) -> Tensor:
     if _axis_is_sharded(x, axis):
         from .reduction import reduce_max, reduce_sum
 
-        m = reduce_max(x, axis=axis, keepdims=True)
+        m = stop_gradient(reduce_max(x, axis=axis, keepdims=True))
         s = x - m
         return s - log(reduce_sum(exp(s), axis=axis, keepdims=True))
     return _logsoftmax(x, axis=axis)

@@ -29,6 +29,8 @@ class DType(enum.Enum):
     bfloat16 = "bf16"
     float32 = "f32"
     float64 = "f64"
+    complex64 = "c64"
+    complex128 = "c128"
 
     def __repr__(self) -> str:
         return f"DType.{self.name}"
@@ -81,13 +83,15 @@ _TO_TORCH = {
     DType.bool: torch.bool, DType.int8: torch.int8, DType.int16: torch.int16, DType.int32: torch.int32,
     DType.int64: torch.int64, DType.uint8: torch.uint8, DType.uint16: torch.uint16, DType.uint32: torch.uint32,
     DType.uint64: torch.uint64, DType.float16: torch.float16, DType.bfloat16: torch.bfloat16,
-    DType.float32: torch.float32, DType.float64: torch.float64,
+    DType.float32: torch.float32, DType.float64: torch.float64, DType.complex64: torch.complex64,
+    DType.complex128: torch.complex128,
 }
 _FROM_TORCH = {v: k for k, v in _TO_TORCH.items()}
 _TO_NUMPY = {
     DType.bool: "bool", DType.int8: "int8", DType.int16: "int16", DType.int32: "int32", DType.int64: "int64",
     DType.uint8: "uint8", DType.uint16: "uint16", DType.uint32: "uint32", DType.uint64: "uint64",
-    DType.float16: "float16", DType.float32: "float32", DType.float64: "float64",
+    DType.float16: "float16", DType.float32: "float32", DType.float64: "float64", DType.complex64: "complex64",
+    DType.complex128: "complex128",
 }
 _FROM_NUMPY = {v: k for k, v in _TO_NUMPY.items()}
 
