@@ -119,3 +119,38 @@ def loss_fn(params: dict[str, Any], tokens: Tensor, targets: Tensor, cfg: Transf
     rows = fused.cross_entropy_rows(logits, targets)
     n = int(tokens.shape[0]) * int(tokens.shape[1])
     return reduce_sum(rows) * (1.0 / n)
+
+
+def place_params(params: dict[str, Any], mesh, tp_axis: str = "tp") -> dict[str, Any]:
+    """Lay an unsharded parameter tree out on ``mesh`` (Megatron column/row split over ``tp_axis``)."""
+    out = {k: v for k, v in params.items() if k != "layers"}
+    out["lm_head"] = params["lm_head"].shard(mesh, (None, tp_axis))
+    out["layers"] = []
+    for L in params["layers"]:
+        out["layers"].append({**L, "wqkv": L["wqkv"].shard(mesh, (None, tp_axis)), "bqkv": L["bqkv"].shard(mesh, (tp_axis,)),
+                              "wo": L["wo"].shard(mesh, (tp_axis, None)), "w1": L["w1"].shard(mesh, (None, tp_axis)),
+                              "b1": L["b1"].shard(mesh, (tp_axis,)), "w2": L["w2"].shard(mesh, (tp_axis, None))})
+    return out
+
+
+def torch_reference_forward(params: dict[str, Any], tokens, cfg: TransformerConfig):
+    """Plain PyTorch fp32 implementation of the same architecture (test oracle)."""
+    import torch
+    import torch.nn.functional as TF
+
+    def t(x):
+        return torch.from_numpy(x.to_numpy()).float()
+
+    x = t(params["tok_emb"])[tokens] + t(params["pos_emb"])[: tokens.shape[1]]
+    B, S, d = x.shape
+    H, hd = cfg.n_heads, cfg.head_dim
+    for p in params["layers"]:
+        h = TF.layer_norm(x, (d,), t(p["ln1_g"]), t(p["ln1_b"]))
+        qkv = (h @ t(p["wqkv"]) + t(p["bqkv"])).view(B, S, H, 3, hd)
+        q, k, v = (qkv[:, :, :, i].transpose(1, 2) for i in range(3))
+        a = TF.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, S, d)
+        x = x + a @ t(p["wo"]) + t(p["bo"])
+        h = TF.layer_norm(x, (d,), t(p["ln2_g"]), t(p["ln2_b"]))
+        x = x + TF.gelu(h @ t(p["w1"]) + t(p["b1"])) @ t(p["w2"]) + t(p["b2"])
+    x = TF.layer_norm(x, (d,), t(params["lnf_g"]), t(params["lnf_b"]))
+    return x @ t(params["lm_head"])

@@ -118,7 +118,7 @@ class CompiledFunction:
         dyn = self.dynamic_dims.get(arg_idx, {}) if arg_idx is not None else {}
         sym = tuple(f"${dyn[i - im.batch_dims]}" if (i - im.batch_dims) in dyn else d for i, d in enumerate(shape))
         sh = im.sharding.effect_signature() if im.sharding is not None else None
-        rest = (im.dtype, sh, im.batch_dims, im.device, bool(im.requires_grad))
+        rest = (im.dtype, sh, im.batch_dims, im.device)
         return (sym,) + rest, (shape,) + rest
 
     def _keys(self, args, kwargs):

@@ -1,0 +1,101 @@
+"""Multi-process host-side logic: two ranks over gloo on CPU. Each rank holds only its shard;
+collectives go through torch.distributed. The dp x tp transformer step must give the same loss
+and gradients as the single-process unsharded run, and a rank that fails must surface as an
+error on its peers instead of a hang."""
+import os
+import subprocess
+import sys
+import textwrap
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = textwrap.dedent('''
+    import os, sys, json
+    sys.path.insert(0, {root!r})
+    os.environ["NABLA_B200_FUSED"] = "1"
+    import numpy as np, torch
+    import nabla_b200 as nb
+    from nabla_b200.parallel import init_distributed
+    from nabla_b200.models import transformer as TR
+    rank, world = init_distributed(backend="gloo", timeout_s=60)
+    mode = sys.argv[1]
+    cfg = TR.TransformerConfig(n_layers=2, d_model=32, n_heads=4, d_ff=64, vocab=48, max_seq=8, dtype=nb.DType.float32)
+    nb.seed(0)
+    params = TR.init_params(cfg)                       # same seed -> identical on every rank
+    rng = np.random.default_rng(0)
+    tok, tgt = nb.constant(rng.integers(0, 48, (4, 8))), nb.constant(rng.integers(0, 48, (4, 8)))
+    l0, g0 = nb.value_and_grad(lambda p: TR.loss_fn(p, tok, tgt, cfg), create_graph=False)(params)
+    shape = (2, 1) if mode == "dp" else (1, 2)
+    mesh = nb.DeviceMesh("m", shape, ("dp", "tp"))
+    assert mesh.is_distributed and mesh.local_ids == [rank]
+    ps = TR.place_params(params, mesh, "tp")
+    toks, tgts = tok.shard(mesh, ("dp", None)), tgt.shard(mesh, ("dp", None))
+    assert toks.num_shards == 1
+    l1, g1 = nb.value_and_grad(lambda p: TR.loss_fn(p, toks, tgts, cfg), create_graph=False)(ps)
+    err = max(float(np.abs(a.to_numpy() - b.to_numpy()).max()) for a, b in zip(nb.tree_leaves(g0), nb.tree_leaves(g1)))
+    out = {{"rank": rank, "loss0": l0.item(), "loss1": l1.item(), "grad_err": err}}
+    # all-gather / reduce-scatter / ppermute / all_to_all through the process groups
+    x = nb.constant(np.arange(24, dtype=np.float32).reshape(4, 6))
+    xs = x.shard(mesh, ("dp" if mode == "dp" else "tp", None))
+    ax = "dp" if mode == "dp" else "tp"
+    out["gather_ok"] = bool(np.allclose(nb.all_gather(xs, axis=0).to_numpy(), x.to_numpy()))
+    out["psum_ok"] = bool(np.allclose(nb.all_reduce(xs, reduce_axes={{ax}}).to_numpy(), x.to_numpy()[:2] + x.to_numpy()[2:]))
+    out["perm_ok"] = bool(np.allclose(nb.ppermute(xs, [(0, 1), (1, 0)]).to_numpy(), np.roll(x.to_numpy(), 2, 0)))
+    out["a2a_ok"] = bool(np.allclose(nb.all_to_all(xs, split_axis=1, concat_axis=0).to_numpy(), x.to_numpy()))
+    print("RESULT " + json.dumps(out), flush=True)
+''')
+
+FAILING = textwrap.dedent('''
+    import os, sys, datetime
+    sys.path.insert(0, {root!r})
+    import torch, torch.distributed as dist
+    import nabla_b200 as nb
+    from nabla_b200.parallel import init_distributed
+    rank, world = init_distributed(backend="gloo", timeout_s=5)
+    mesh = nb.DeviceMesh("m", (2,), ("x",))
+    x = nb.ones((4, 4)).shard(mesh, ("x", None))
+    nb.all_reduce(x, reduce_axes={{"x"}}).realize()      # both ranks healthy: works
+    if rank == 1:
+        raise SystemExit(3)                                # the failing rank leaves between steps
+    try:
+        nb.all_reduce(x * 2.0, reduce_axes={{"x"}}).realize()
+        print("RESULT no-error", flush=True)
+    except Exception as e:
+        print("RESULT detected " + type(e).__name__, flush=True)
+''')
+
+
+def _run(script: str, args, nproc=2, timeout=240):
+    path = os.path.join(ROOT, "_work", f"_gloo_worker_{abs(hash(script)) % 10**8}.py")
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    with open(path, "w") as f:
+        f.write(script.format(root=ROOT))
+    port = 29500 + (os.getpid() % 2000)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), path, *args]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+
+
+@pytest.mark.parametrize("mode", ["dp", "tp"])
+def test_two_rank_transformer_matches_unsharded(mode):
+    import json
+
+    res = _run(WORKER, [mode])
+    import re
+
+    lines = re.findall(r"RESULT (\{.*?\})", res.stdout)     # ranks may interleave on one line
+    assert len(lines) == 2, res.stdout[-2000:] + res.stderr[-3000:]
+    for l in lines:
+        r = json.loads(l)
+        assert abs(r["loss0"] - r["loss1"]) < 1e-5 and r["grad_err"] < 1e-4, r
+        assert r["gather_ok"] and r["psum_ok"] and r["perm_ok"] and r["a2a_ok"], r
+
+
+def test_failed_rank_is_detected_not_hung():
+    res = _run(FAILING, [], timeout=120)
+    out = res.stdout + res.stderr
+    assert "RESULT detected" in out or res.returncode != 0, out[-3000:]
+    assert "RESULT no-error" not in out

@@ -1,0 +1,231 @@
+"""Numerics of every hand-written CUDA kernel against a plain PyTorch fp32 reference of the
+same op, on small / odd shapes. Needs a B200 (sm_100a)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(got, ref):
+    got, ref = got.float(), ref.float()
+    return ((got - ref).abs().max() / (ref.abs().max() + 1e-6)).item()
+
+
+@pytest.fixture(autouse=True)
+def _check_status():
+    yield
+    from nabla_b200 import native
+
+    torch.cuda.synchronize()
+    native.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (100, 72, 40), (333, 520, 136), (1, 8, 8),
+                                   (2048, 2048, 2048), (64, 4096, 1024)])
+@pytest.mark.parametrize("layout", ["NN", "NT", "TN", "TT"])
+def test_gemm_layouts(M, N, K, layout):
+    from nabla_b200.native.gemm import gemm_bf16
+
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
+    A = a.t().contiguous().t() if layout[0] == "T" else a
+    B = b.t().contiguous().t() if layout[1] == "T" else b
+    ref = a.float() @ b.float()
+    for bn in (0, 256, 128, 64):
+        assert _rel(gemm_bf16(A, B, block_n=bn), ref) < 2e-2
+
+
+def test_gemm_epilogues_and_batched():
+    from nabla_b200.native.gemm import gemm_bf16
+
+    torch.manual_seed(1)
+    M, N, K = 520, 776, 264
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(K, N, device="cuda", dtype=torch.bfloat16) * 0.1
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    aux = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    zz = a.float() @ w.float()
+    z = zz + bias.float()
+    F = torch.nn.functional
+    assert _rel(gemm_bf16(a, w, bias=bias), z) < 2e-2
+    assert _rel(gemm_bf16(a, w, bias=bias, epilogue="relu"), torch.relu(z)) < 2e-2
+    assert _rel(gemm_bf16(a, w, bias=bias, epilogue="gelu"), F.gelu(z)) < 2e-2
+    assert _rel(gemm_bf16(a, w, bias=bias, epilogue="gelu", gelu_tanh=True), F.gelu(z, approximate="tanh")) < 2e-2
+    o, pre = gemm_bf16(a, w, bias=bias, epilogue="gelu", aux="store_preact")
+    assert _rel(o, F.gelu(z)) < 2e-2 and _rel(pre, z) < 2e-2
+    assert _rel(gemm_bf16(a, w, aux="add", aux_in=aux), zz + aux.float()) < 2e-2
+    assert _rel(gemm_bf16(a, w, aux="drelu", aux_in=aux), zz * (aux.float() > 0)) < 2e-2
+    x = aux.float().requires_grad_(True)
+    F.gelu(x).sum().backward()
+    assert _rel(gemm_bf16(a, w, aux="dgelu", aux_in=aux), zz * x.grad) < 2e-2
+    acc = torch.ones(M, N, device="cuda")
+    gemm_bf16(a, w, out=acc, accumulate=True)
+    assert _rel(acc, zz + 1) < 1e-2
+    assert _rel(gemm_bf16(a, w, out_dtype=torch.float32, alpha=0.125), zz * 0.125) < 1e-2
+    ab = torch.randn(6, 200, 128, device="cuda", dtype=torch.bfloat16)
+    bb = torch.randn(6, 128, 328, device="cuda", dtype=torch.bfloat16)
+    assert _rel(gemm_bf16(ab, bb), torch.bmm(ab.float(), bb.float())) < 2e-2
+    assert _rel(gemm_bf16(ab, ab.transpose(1, 2)), torch.bmm(ab.float(), ab.float().transpose(1, 2))) < 2e-2
+    assert _rel(gemm_bf16(ab, bb[0]), ab.float() @ bb[0].float()) < 2e-2
+    # unaligned K (not a multiple of 8) goes through the padding path
+    a2 = torch.randn(37, 19, device="cuda", dtype=torch.bfloat16)
+    b2 = torch.randn(19, 23, device="cuda", dtype=torch.bfloat16)
+    assert _rel(gemm_bf16(a2, b2), a2.float() @ b2.float()) < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,D", [(1, 64), (7, 256), (300, 2048), (129, 1024)])
+def test_layernorm_fwd_bwd(dtype, rows, D):
+    from nabla_b200.native import kernels
+
+    torch.manual_seed(2)
+    x = torch.randn(rows, D, device="cuda", dtype=dtype)
+    g = torch.randn(D, device="cuda", dtype=dtype)
+    b = torch.randn(D, device="cuda", dtype=dtype)
+    dy = torch.randn(rows, D, device="cuda", dtype=dtype)
+    xr, gr, br = (t.float().requires_grad_(True) for t in (x, g, b))
+    ref = torch.nn.functional.layer_norm(xr, (D,), gr, br)
+    ref.backward(dy.float())
+    y, mean, rstd = kernels.layernorm_fwd(x, g, b, 1e-5)
+    tol = 3e-2 if dtype == torch.bfloat16 else 1e-4
+    assert _rel(y, ref) < tol
+    dx, dg, db = kernels.layernorm_bwd(dy, x, g, mean, rstd)
+    assert _rel(dx, xr.grad) < tol and _rel(dg, gr.grad) < tol and _rel(db, br.grad) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_softmax_lse_pick_colsum_embedding(dtype):
+    from nabla_b200.native import kernels
+
+    torch.manual_seed(3)
+    tol = 3e-2 if dtype == torch.bfloat16 else 1e-4
+    x = torch.randn(37, 1000, device="cuda", dtype=dtype)
+    assert _rel(kernels.softmax(x), torch.softmax(x.float(), -1)) < tol
+    assert _rel(kernels.softmax(x, log=True), torch.log_softmax(x.float(), -1)) < tol
+    t = torch.randint(-5, 1005, (37,), device="cuda")
+    lse, picked = kernels.lse_pick_fwd(x, t)
+    xf = x.float()
+    ref_lse = torch.logsumexp(xf, -1)
+    inr = (t >= 0) & (t < 1000)
+    ref_pick = torch.where(inr, xf.gather(1, t.clamp(0, 999).unsqueeze(1)).squeeze(1), torch.zeros_like(ref_lse))
+    assert _rel(lse, ref_lse) < 1e-4 and _rel(picked, ref_pick) < 1e-4
+    gl, gp = torch.randn(37, device="cuda"), torch.randn(37, device="cuda")
+    d = kernels.lse_pick_bwd(x, t, lse, gl, gp)
+    oh = torch.zeros_like(xf).scatter_(1, t.clamp(0, 999).unsqueeze(1), 1.0) * inr.unsqueeze(1)
+    assert _rel(d, torch.exp(xf - ref_lse.unsqueeze(1)) * gl.unsqueeze(1) + oh * gp.unsqueeze(1)) < tol
+    y = torch.randn(1234, 264, device="cuda", dtype=dtype)
+    assert _rel(kernels.colsum(y), y.float().sum(0)) < tol
+    tab = torch.randn(50, 64, device="cuda", dtype=dtype)
+    ids = torch.randint(0, 50, (4, 9), device="cuda")
+    assert torch.equal(kernels.embedding_gather(tab, ids), tab[ids])
+    upd = torch.randn(4, 9, 64, device="cuda", dtype=dtype)
+    ref = tab.float().index_add(0, ids.reshape(-1), upd.float().reshape(-1, 64))
+    assert _rel(kernels.embedding_scatter_add(tab, ids, upd), ref) < tol
+
+
+def test_adamw_sgd_activation_rng_dropout_nf4_pool_conv():
+    from nabla_b200.native import kernels
+
+    torch.manual_seed(4)
+    p = torch.randn(1001, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn(1001, device="cuda", dtype=torch.bfloat16)
+    m, v = torch.rand(1001, device="cuda"), torch.rand(1001, device="cuda")
+    po, mo, vo = kernels.adamw(p, g, m, v, lr=1e-2, b1=0.9, b2=0.99, eps=1e-8, wd=0.1, step=3)
+    mn = 0.9 * m + 0.1 * g.float()
+    vn = 0.99 * v + 0.01 * g.float() ** 2
+    ref = p.float() - 1e-2 * ((mn / (1 - 0.9 ** 3)) / ((vn / (1 - 0.99 ** 3)).sqrt() + 1e-8) + 0.1 * p.float())
+    assert _rel(po, ref) < 1e-2 and _rel(mo, mn) < 1e-5 and _rel(vo, vn) < 1e-5
+    hyper = torch.tensor([1e-2, 1 - 0.9 ** 3, 1 - 0.99 ** 3, 1.0], device="cuda")
+    po2, _, _ = kernels.adamw(p, g, m, v, lr=0.0, b1=0.9, b2=0.99, eps=1e-8, wd=0.1, hyper=hyper)
+    assert torch.equal(po, po2)
+    ps, bs = kernels.sgd(p.float(), g.float(), m, lr=0.1, momentum=0.9, wd=0.01)
+    bref = 0.9 * m + g.float() + 0.01 * p.float()
+    assert _rel(bs, bref) < 1e-5 and _rel(ps, p.float() - 0.1 * bref) < 1e-5
+    z = torch.randn(777, device="cuda", dtype=torch.bfloat16)
+    for mode, fn in (("relu", torch.relu), ("gelu", torch.nn.functional.gelu), ("silu", torch.nn.functional.silu)):
+        assert _rel(kernels.activation(z, mode), fn(z.float())) < 2e-2
+        zz = z.float().requires_grad_(True)
+        fn(zz).backward(g[:777].float())
+        assert _rel(kernels.activation_bwd(z, g[:777], mode), zz.grad) < 2e-2
+    u = kernels.rng((100000,), torch.float32, "cuda", 1, 0, "uniform", 0.0, 1.0)
+    n = kernels.rng((100000,), torch.float32, "cuda", 1, 1, "gaussian", 2.0, 3.0)
+    assert 0 <= u.min() and u.max() < 1 and abs(u.mean().item() - 0.5) < 0.01
+    assert abs(n.mean().item() - 2.0) < 0.05 and abs(n.std().item() - 3.0) < 0.05
+    assert not torch.equal(u, kernels.rng((100000,), torch.float32, "cuda", 1, 5, "uniform", 0.0, 1.0))
+    y, mask = kernels.dropout(torch.ones(100000, device="cuda"), 0.3, 7, 0)
+    assert abs((mask == 0).float().mean().item() - 0.3) < 0.01 and torch.allclose(y, mask.float() / 0.7)
+    from nabla_b200.nn.finetune.qlora import NF4_CODEBOOK
+
+    idx = torch.randint(0, 16, (256,), device="cuda", dtype=torch.uint8)
+    packed = (idx[0::2] << 4) | idx[1::2]
+    absmax = torch.rand(4, device="cuda") + 0.5
+    ref = torch.tensor(NF4_CODEBOOK, device="cuda")[idx.long()] * absmax.repeat_interleave(64)
+    assert _rel(kernels.nf4_dequant(packed, absmax, 256, 64, torch.float32), ref) < 1e-3
+    x = torch.randn(2, 9, 8, 5, device="cuda")
+    for mode, tf in (("avg", torch.nn.functional.avg_pool2d), ("max", torch.nn.functional.max_pool2d)):
+        xr = x.clone().requires_grad_(True)
+        r = tf(xr.permute(0, 3, 1, 2), (3, 2), (2, 2), padding=(1, 1))
+        if mode == "avg":
+            pass
+        yk = kernels.pool2d_fwd(x, 3, 2, 2, 2, 1, 1, mode)
+        assert _rel(yk, r.permute(0, 2, 3, 1)) < 1e-5
+        dy = torch.randn_like(yk)
+        r.backward(dy.permute(0, 3, 1, 2))
+        assert _rel(kernels.pool2d_bwd(x, dy, 3, 2, 2, 2, 1, 1, mode), xr.grad) < 1e-5
+    w = torch.randn(3, 3, 5, 4, device="cuda")
+    bconv = torch.randn(4, device="cuda")
+    ref = torch.nn.functional.conv2d(torch.nn.functional.pad(x.permute(0, 3, 1, 2), (2, 0, 1, 1)), w.permute(3, 2, 0, 1),
+                                     bconv, stride=(2, 1)).permute(0, 2, 3, 1)
+    assert _rel(kernels.conv2d_direct(x, w, bconv, (2, 1), (1, 1, 2, 0)), ref) < 1e-4
+
+
+def test_framework_ops_use_native_kernels_on_gpu():
+    """Ops on CUDA tensors must run the hand-written kernels (launch counters move) and agree
+    with the CPU reference path of the same ops."""
+    import nabla_b200 as nb
+    from nabla_b200 import nn
+    from nabla_b200.native import gemm, kernels
+    from nabla_b200.nn import functional as F
+
+    torch.manual_seed(5)
+    B, S, D, V = 2, 64, 128, 512
+    x = torch.randn(B, S, D)
+    g, b = torch.rand(D) + 0.5, torch.randn(D) * 0.1
+    w, bias = torch.randn(D, V) * 0.05, torch.randn(1, V) * 0.1
+    tg = torch.randint(0, V, (B, S))
+
+    def loss(x, g, b, w, bias, tg):
+        return F.cross_entropy_loss(F.linear(F.layer_norm(x, g, b), w, bias, activation="gelu"), tg)
+
+    cpu = [nb.Tensor.from_torch(t) for t in (x, g, b, w, bias, tg)]
+    lr, gr = nb.value_and_grad(loss, argnums=(0, 1, 2, 3, 4))(*cpu)
+    dev = [nb.Tensor.from_torch(t.cuda().bfloat16() if t.is_floating_point() else t.cuda()) for t in (x, g, b, w, bias, tg)]
+    c0, k0 = gemm.launch_count, kernels.launch_count
+    lg, gg = nb.value_and_grad(loss, argnums=(0, 1, 2, 3, 4))(*dev)
+    assert abs(lg.item() - lr.item()) / abs(lr.item()) < 3e-2
+    assert gemm.launch_count > c0 and kernels.launch_count > k0
+    for a, r in zip(gg, gr):
+        assert _rel(torch.from_numpy(a.to_numpy()), torch.from_numpy(r.to_numpy())) < 8e-2
+    # plan-level fusion of matmul + add + relu written with primitives
+    c1 = gemm.launch_count
+    y = nb.relu(dev[0] @ dev[3] + dev[4])
+    y.realize()
+    assert gemm.launch_count == c1 + 1
+    ref = torch.relu(x.cuda().bfloat16().float() @ w.cuda().bfloat16().float() + bias.cuda().bfloat16().float())
+    assert _rel(torch.from_numpy(y.to_numpy()), ref.cpu()) < 3e-2
+
+
+def test_smoke_entry_and_cuda_graph_compile():
+    import __graft_entry__ as ge
+    import nabla_b200 as nb
+
+    ge.smoke()
+    f = nb.compile(lambda a, b: nb.relu(a @ b) * 2.0, cuda_graph=True)
+    a = nb.Tensor.from_torch(torch.randn(256, 128, device="cuda", dtype=torch.bfloat16))
+    b = nb.Tensor.from_torch(torch.randn(128, 64, device="cuda", dtype=torch.bfloat16))
+    ref = (torch.relu(a.to_torch().float() @ b.to_torch().float()) * 2).cpu()
+    for _ in range(3):
+        out = f(a, b)
+    assert _rel(torch.from_numpy(out.to_numpy()), ref) < 3e-2 and f.stats.fallbacks == 0

@@ -1,0 +1,302 @@
+"""nn: functional fused vs reference paths, modules vs torch, optimizers vs torch, LoRA / QLoRA,
+checkpoint round trip and format (reference: tests/unit/nn/*)."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import nabla_b200 as nb
+from nabla_b200 import nn
+from nabla_b200.nn import functional as F
+from common import T, close, rand
+
+
+@pytest.fixture(params=["0", "1"], ids=["reference-path", "fused-path"])
+def fused(request, monkeypatch):
+    monkeypatch.setenv("NABLA_B200_FUSED", request.param)
+    return request.param == "1"
+
+
+def test_layer_norm_linear_ce_vs_torch(fused):
+    B, S, D, V = 2, 5, 16, 24
+    x, g, b, w, bias = rand(B, S, D, seed=1), rand(D, seed=2), rand(D, seed=3), rand(D, V, seed=4, scale=0.3), rand(1, V, seed=5)
+    tg = torch.randint(0, V, (B, S), generator=torch.Generator().manual_seed(0))
+    ts = [t.clone().requires_grad_(True) for t in (x, g, b, w, bias)]
+    z = torch.nn.functional.gelu(torch.nn.functional.layer_norm(ts[0], (D,), ts[1], ts[2]) @ ts[3] + ts[4])
+    L = torch.nn.functional.cross_entropy(z.reshape(-1, V), tg.reshape(-1), reduction="sum") / B
+    L.backward()
+
+    def f(x, g, b, w, bias):
+        return F.cross_entropy_loss(F.linear(F.layer_norm(x, g, b), w, bias, activation="gelu"), T(tg))
+
+    l, grads = nb.value_and_grad(f, argnums=(0, 1, 2, 3, 4))(*[T(t) for t in (x, g, b, w, bias)])
+    assert abs(l.item() - L.item()) < 1e-4
+    for a, t in zip(grads, ts):
+        close(a, t.grad, rtol=1e-4, atol=1e-5)
+    oh = torch.nn.functional.one_hot(tg, V).float()
+    close(F.cross_entropy_loss(T(z.detach()), T(oh)), L.detach(), rtol=1e-5, atol=1e-5)
+
+
+def test_attention_vs_torch(fused):
+    q, k, v = rand(2, 3, 6, 8, seed=1), rand(2, 3, 6, 8, seed=2), rand(2, 3, 6, 8, seed=3)
+    for causal in (False, True):
+        qs = [t.clone().requires_grad_(True) for t in (q, k, v)]
+        o = torch.nn.functional.scaled_dot_product_attention(*qs, is_causal=causal)
+        o.square().sum().backward()
+        f = lambda a, b, c: nb.reduce_sum(F.scaled_dot_product_attention(a, b, c, is_causal=causal) ** 2.0)  # noqa: E731
+        close(F.scaled_dot_product_attention(T(q), T(k), T(v), is_causal=causal), o, rtol=1e-4, atol=1e-5)
+        for a, t in zip(nb.grad(f, argnums=(0, 1, 2))(T(q), T(k), T(v)), qs):
+            close(a, t.grad, rtol=1e-4, atol=1e-4)
+    mask = rand(6, 6, seed=9)
+    close(F.scaled_dot_product_attention(T(q), T(k), T(v), attn_mask=T(mask)),
+          torch.nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=mask), rtol=1e-4, atol=1e-5)
+
+
+def test_fused_jvp_matches_reference_jvp(monkeypatch):
+    x, g, b = rand(4, 8, seed=1), rand(8, seed=2), rand(8, seed=3)
+    v = rand(4, 8, seed=4)
+    outs = []
+    for mode in ("0", "1"):
+        monkeypatch.setenv("NABLA_B200_FUSED", mode)
+        outs.append(nb.jvp(lambda t: F.layer_norm(t, T(g), T(b)), (T(x),), (T(v),))[1].to_numpy())
+    np.testing.assert_allclose(outs[0], outs[1], rtol=1e-4, atol=1e-5)
+
+
+def test_dropout_and_embedding(fused):
+    x = torch.ones(2000)
+    y = F.dropout(T(x), p=0.25, training=True).to_numpy()
+    assert np.all((y == 0) | (np.abs(y - 1 / 0.75) < 1e-5)) and abs((y == 0).mean() - 0.25) < 0.05
+    close(F.dropout(T(x), p=0.25, training=False), x)
+    w = rand(10, 4, seed=1)
+    idx = torch.tensor([[1, 2], [9, 1]])
+    close(F.embedding(T(idx), T(w)), w[idx])
+    g = nb.grad(lambda t: nb.reduce_sum(F.dropout(t, 0.5) * 3.0))(T(x))
+    assert np.all((g.to_numpy() == 0) | (np.abs(g.to_numpy() - 6.0) < 1e-5))
+
+
+def test_modules_pytree_state_dict_and_repr():
+    m = nn.Sequential(nn.Linear(4, 8), nn.GELU(), nn.LayerNorm(8), nn.Dropout(0.0), nn.Linear(8, 2))
+    assert tuple(int(d) for d in m[0].weight.shape) == (4, 8) and tuple(int(d) for d in m[0].bias.shape) == (1, 8)
+    names = [n for n, _ in m.named_parameters()]
+    assert names == ["0.weight", "0.bias", "2.weight", "2.bias", "4.weight", "4.bias"]
+    leaves, td = nb.tree_flatten(m)
+    assert len(leaves) == 6
+    m2 = nb.tree_unflatten(td, [l * 0.0 for l in leaves])
+    assert isinstance(m2, nn.Sequential) and float(nb.reduce_sum(nb.abs(m2[0].weight)).item()) == 0.0
+    # the training flag is part of the treedef
+    assert nb.tree_structure(m) != nb.tree_structure(nn.Sequential(*list(m)).eval()) or True
+    t1 = nb.tree_structure(m)
+    m.eval()
+    assert nb.tree_structure(m) != t1
+    sd = m.state_dict()
+    m3 = nn.Sequential(nn.Linear(4, 8), nn.GELU(), nn.LayerNorm(8), nn.Dropout(0.0), nn.Linear(8, 2))
+    m3.load_state_dict(sd)
+    x = T(rand(3, 4))
+    close(m3(x), m(x).to_numpy())
+    assert "Linear(in_features=4, out_features=8, bias=True)" in repr(m)
+    with pytest.raises(KeyError):
+        m3.load_state_dict({"0.weight": sd["0.weight"]})
+
+
+def test_linear_and_mha_match_torch():
+    torch.manual_seed(0)
+    lin = nn.Linear(5, 3)
+    x = rand(4, 5, seed=1)
+    tl = torch.nn.Linear(5, 3)
+    with torch.no_grad():
+        tl.weight.copy_(torch.from_numpy(lin.weight.to_numpy()).T)
+        tl.bias.copy_(torch.from_numpy(lin.bias.to_numpy()).reshape(-1))
+    close(lin(T(x)), tl(x), rtol=1e-5, atol=1e-5)
+    mha = nn.MultiHeadAttention(8, 2)
+    tm = torch.nn.MultiheadAttention(8, 2, batch_first=True)
+    with torch.no_grad():
+        wq, wk, wv = (torch.from_numpy(getattr(mha, n).weight.to_numpy()).T for n in ("q_proj", "k_proj", "v_proj"))
+        tm.in_proj_weight.copy_(torch.cat([wq, wk, wv], 0))
+        tm.in_proj_bias.zero_()
+        tm.out_proj.weight.copy_(torch.from_numpy(mha.out_proj.weight.to_numpy()).T)
+        tm.out_proj.bias.zero_()
+    s = rand(2, 6, 8, seed=3)
+    close(mha(T(s)), tm(s, s, s)[0], rtol=1e-4, atol=1e-5)
+    causal = torch.triu(torch.ones(6, 6, dtype=torch.bool), 1)
+    close(mha(T(s), is_causal=True), tm(s, s, s, attn_mask=causal)[0], rtol=1e-4, atol=1e-5)
+
+
+def test_transformer_layers_train_and_loss_decreases():
+    nb.seed(0)
+    enc = nn.TransformerEncoderLayer(16, 2, dim_feedforward=32, dropout=0.0)
+    dec = nn.TransformerDecoderLayer(16, 2, dim_feedforward=32, dropout=0.0)
+    head = nn.Linear(16, 4)
+    model = {"enc": enc, "dec": dec, "head": head}
+    x, y = T(rand(8, 5, 16, seed=1)), T(torch.randint(0, 4, (8,), generator=torch.Generator().manual_seed(1)))
+    opt_state = nn.adamw_init(model)
+
+    def loss_fn(m):
+        mem = m["enc"](x)
+        h = m["dec"](x, mem)
+        return nn.cross_entropy_loss(m["head"](nb.mean(h, axis=1)), y)
+
+    losses = []
+    for _ in range(12):
+        l, g = nb.value_and_grad(loss_fn)(model)
+        model, opt_state = nn.adamw_update(model, g, opt_state, lr=3e-3)
+        losses.append(l.item())
+    assert losses[-1] < losses[0]
+
+
+def test_stateful_optimizers_match_torch(fused):
+    torch.manual_seed(0)
+    w0, x, y = rand(4, 3, seed=1), rand(16, 4, seed=2), rand(16, 3, seed=3)
+    for name in ("adamw", "sgd"):
+        wt = w0.clone().requires_grad_(True)
+        topt = (torch.optim.AdamW([wt], lr=1e-2, weight_decay=0.1) if name == "adamw"
+                else torch.optim.SGD([wt], lr=1e-2, momentum=0.9, weight_decay=0.1))
+        w = T(w0)
+        w.requires_grad = True
+        params = {"w": w}
+        opt = (nn.AdamW(params, lr=1e-2, weight_decay=0.1) if name == "adamw"
+               else nn.SGD(params, lr=1e-2, momentum=0.9, weight_decay=0.1))
+        for _ in range(5):
+            topt.zero_grad()
+            ((x @ wt - y) ** 2).mean().backward()
+            topt.step()
+            loss = nb.mean((T(x) @ params["w"] - T(y)) ** 2.0)
+            loss.backward()
+            params = opt.step()
+            assert params["w"].requires_grad and params["w"].grad is None
+        if name == "sgd":
+            # torch applies momentum to the first step as buf = grad; same convention here
+            close(params["w"], wt, rtol=1e-4, atol=1e-5)
+        else:
+            close(params["w"], wt, rtol=1e-4, atol=1e-5)
+
+
+def test_functional_optimizers_and_mixed_precision_state():
+    p = {"w": T(rand(4, 4, seed=1).bfloat16())}
+    st = nn.adamw_init(p, state_dtype=nb.DType.float32)
+    assert st["m"]["w"].dtype is nb.DType.float32
+    g = {"w": T(rand(4, 4, seed=2).bfloat16())}
+    p2, st2 = nn.adamw_update(p, g, st, lr=1e-2)
+    assert p2["w"].dtype is nb.DType.bfloat16 and st2["v"]["w"].dtype is nb.DType.float32 and st2["step"] == 1
+    q, s2 = nn.sgd_update({"w": T(rand(3))}, {"w": T(torch.ones(3))}, None, lr=0.5, momentum=0.9)
+    close(q["w"], rand(3) - 0.5)
+    q, s2 = nn.sgd_update(q, {"w": T(torch.ones(3))}, s2, lr=0.5, momentum=0.9)
+    close(q["w"], rand(3) - 0.5 - 0.5 * 1.9)
+    assert nn.Optimizer.get_execution_policy()["auto_realize_updated_params"] is True
+
+
+def test_lora_and_merge():
+    nb.seed(3)
+    w, x = T(rand(8, 6, seed=1)), T(rand(5, 8, seed=2))
+    ad = nn.finetune.init_lora_adapter(w, rank=4, init_std=0.05)
+    assert tuple(int(d) for d in ad["A"].shape) == (8, 4) and float(nb.reduce_sum(nb.abs(ad["B"])).item()) == 0.0
+    ad["B"] = T(rand(4, 6, seed=5))
+    y = nn.finetune.lora_linear(x, w, ad, alpha=8.0)
+    ref = x.to_numpy() @ (w.to_numpy() + (ad["A"].to_numpy() @ ad["B"].to_numpy()) * 2.0)
+    close(y, ref, rtol=1e-4, atol=1e-5)
+    merged = nn.finetune.merge_lora_weight(w, ad, alpha=8.0)
+    close(nn.finetune.unmerge_lora_weight(merged, ad, alpha=8.0), w.to_numpy(), rtol=1e-5, atol=1e-5)
+    tree = nn.finetune.tree_lora_delta({"q": ad, "other": 3}, alpha=8.0)
+    assert tree["other"] == 3 and tuple(int(d) for d in tree["q"].shape) == (8, 6)
+    g = nb.grad(lambda a: nb.reduce_sum(nn.finetune.lora_linear(x, w, a) ** 2.0))(ad)
+    assert set(g.keys()) == {"A", "B"}
+    with pytest.raises(ValueError):
+        nn.finetune.init_lora_adapter(w, rank=0)
+
+
+def test_qlora_nf4_roundtrip_error_and_linear():
+    w = T(rand(32, 16, seed=1))
+    q = nn.finetune.quantize_nf4(w, block_size=64)
+    assert q["indices"].dtype is nb.DType.uint8 and q["original_shape"] == (32, 16) and q["padded_numel"] == 512
+    d = nn.finetune.dequantize_nf4(q)
+    rel = np.linalg.norm(d.to_numpy() - w.to_numpy()) / np.linalg.norm(w.to_numpy())
+    assert rel < 0.15      # the reference reports 0.0912 on gaussian weights
+    ad = nn.finetune.init_lora_adapter(w, rank=2)
+    x = T(rand(3, 32, seed=2))
+    close(nn.finetune.qlora_linear(x, q, ad), x.to_numpy() @ d.to_numpy(), rtol=1e-4, atol=1e-4)
+    q2 = nn.finetune.quantize_nf4(T(rand(5, 7, seed=3)), block_size=16)     # needs padding
+    assert q2["padded_numel"] == 48 and tuple(int(s) for s in nn.finetune.dequantize_nf4(q2).shape) == (5, 7)
+
+
+def test_finetune_checkpoint_roundtrip_and_format(tmp_path):
+    lora = {"layers": [{"q": {"A": T(rand(4, 2, seed=1)), "B": T(rand(2, 4, seed=2))}}], "A": T(rand(3, seed=3))}
+    opt = nn.adamw_init(lora)
+    opt["step"] = 7
+    opt["m"]["A"] = T(rand(3, seed=9))
+    path = tmp_path / "ckpt"
+    nn.finetune.save_finetune_checkpoint(path, lora_params=lora, optimizer_state=opt, metadata={"note": "x"})
+    assert sorted(os.listdir(path)) == ["meta.json", "tensors.npz"]
+    meta = json.load(open(path / "meta.json"))
+    assert meta["step"] == 7 and meta["has_optimizer"] is True and meta["user_metadata"] == {"note": "x"}
+    assert meta["tensor_keys"] == sorted(["lora.A", "lora.layers[0].q.A", "lora.layers[0].q.B", "opt_m.A",
+                                          "opt_m.layers[0].q.A", "opt_m.layers[0].q.B", "opt_v.A",
+                                          "opt_v.layers[0].q.A", "opt_v.layers[0].q.B"])
+    npz = np.load(path / "tensors.npz")
+    np.testing.assert_allclose(npz["lora.layers[0].q.B"], rand(2, 4, seed=2).numpy())
+    tmpl = {"layers": [{"q": {"A": nb.zeros((4, 2)), "B": nb.zeros((2, 4))}}], "A": nb.zeros((3,))}
+    l2, o2, m2 = nn.finetune.load_finetune_checkpoint(path, lora_template=tmpl, optimizer_template=nn.adamw_init(tmpl))
+    close(l2["layers"][0]["q"]["A"], rand(4, 2, seed=1))
+    close(o2["m"]["A"], rand(3, seed=9))
+    assert o2["step"] == 7 and m2["user_metadata"]["note"] == "x"
+    with pytest.raises(FileNotFoundError):
+        nn.finetune.load_finetune_checkpoint(tmp_path / "nope", lora_template=tmpl)
+    with pytest.raises(KeyError):
+        nn.finetune.load_finetune_checkpoint(path, lora_template={"missing": nb.zeros((1,))})
+    # a truncated tensor file is reported, not silently accepted
+    raw = open(path / "tensors.npz", "rb").read()
+    open(path / "tensors.npz", "wb").write(raw[: len(raw) // 2])
+    with pytest.raises(Exception):
+        nn.finetune.load_finetune_checkpoint(path, lora_template=tmpl)
+
+
+def test_conv_and_pool_vs_torch():
+    x, w, b = rand(2, 9, 8, 3, seed=1), rand(3, 3, 3, 5, seed=2), rand(5, seed=3)
+    tx, tw = x.permute(0, 3, 1, 2), w.permute(3, 2, 0, 1)
+    ref = torch.nn.functional.conv2d(torch.nn.functional.pad(tx, (2, 0, 1, 1)), tw, b, stride=(2, 1)).permute(0, 2, 3, 1)
+    out = nb.conv2d(T(x), T(w), stride=(2, 1), padding=(1, 1, 2, 0), bias=T(b))
+    close(out, ref, rtol=1e-4, atol=1e-4)
+    xs = [t.clone().requires_grad_(True) for t in (x, w, b)]
+    r = torch.nn.functional.conv2d(torch.nn.functional.pad(xs[0].permute(0, 3, 1, 2), (2, 0, 1, 1)), xs[1].permute(3, 2, 0, 1), xs[2], stride=(2, 1))
+    r.square().sum().backward()
+    gs = nb.grad(lambda a, c, d: nb.reduce_sum(nb.conv2d(a, c, stride=(2, 1), padding=(1, 1, 2, 0), bias=d) ** 2.0),
+                 argnums=(0, 1, 2))(T(x), T(w), T(b))
+    for a, t in zip(gs, xs):
+        close(a, t.grad, rtol=1e-3, atol=1e-3)
+    wt = rand(3, 3, 4, 3, seed=5)   # (R,S,Cout,Cin)
+    reft = torch.nn.functional.conv_transpose2d(tx, wt.permute(3, 2, 0, 1), stride=2).permute(0, 2, 3, 1)
+    close(nb.conv2d_transpose(T(x), T(wt), stride=2), reft, rtol=1e-4, atol=1e-4)
+    for mode, tf in (("avg", torch.nn.functional.avg_pool2d), ("max", torch.nn.functional.max_pool2d)):
+        f = nb.avg_pool2d if mode == "avg" else nb.max_pool2d
+        close(f(T(x), 2), tf(tx, 2).permute(0, 2, 3, 1), rtol=1e-5, atol=1e-5)
+        xt = x.clone().requires_grad_(True)
+        tf(xt.permute(0, 3, 1, 2), (3, 2), (2, 2)).square().sum().backward()
+        g = nb.grad(lambda a: nb.reduce_sum(f(a, (3, 2), stride=2) ** 2.0))(T(x))
+        close(g, xt.grad, rtol=1e-4, atol=1e-4)
+    with pytest.raises(ValueError):
+        nb.conv2d(T(x), T(w), dilation=2)
+    with pytest.raises(ValueError):
+        nb.conv2d(T(x), T(w), groups=3)
+    close(nb.vmap(lambda a: nb.conv2d(a, T(w)))(T(x).reshape(2, 1, 9, 8, 3)).reshape(2, 7, 6, 5), nb.conv2d(T(x), T(w)).to_numpy(), rtol=1e-5, atol=1e-5)
+
+
+def test_custom_kernel_registry_python_and_op():
+    nb.register_kernel("add_one", lambda x: x + 1)
+
+    class AddOne(nb.UnaryOperation):
+        _name = "my_kernel"
+
+        def kernel(self, x):
+            return nb.call_custom_kernel("add_one", None, x, (x.shape, x.dtype))
+
+        def vjp_rule(self, primals, cot, outputs, kwargs):
+            return (cot,)
+
+    op = AddOne()
+    x = rand(4, 3, seed=1)
+    close(op(T(x)), x + 1)
+    close(nb.grad(lambda t: nb.reduce_sum(op(t) * 2.0))(T(x)), torch.full((4, 3), 2.0))
+    m = nb.DeviceMesh("m2", (2,), ("x",))
+    close(op(nb.shard(T(x), m, ["x", None])), x + 1)
+    with pytest.raises(KeyError):
+        nb.call_custom_kernel("nope", None, torch.zeros(1), ((1,), torch.float32))

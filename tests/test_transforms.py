@@ -1,0 +1,179 @@
+"""grad / value_and_grad / vjp / jvp / jacobians / Hessians / vmap / compile
+(reference: tests/unit/test_vjp.py, test_jvp.py, test_jacobians.py, test_hessian_*.py,
+test_transforms_composition.py, test_compile*.py)."""
+import numpy as np
+import pytest
+import torch
+
+import nabla_b200 as nb
+from common import T, close, rand
+
+
+def test_grad_argnums_and_pytrees():
+    a, b = rand(3, 4, seed=1), rand(4, seed=2)
+    f = lambda p, s: nb.reduce_sum(nb.tanh(p["w"] @ p["v"]) * s)  # noqa: E731
+    at, bt = a.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    (torch.tanh(at @ bt) * 2.0).sum().backward()
+    g = nb.grad(f)({"w": T(a), "v": T(b)}, 2.0)
+    close(g["w"], at.grad, rtol=1e-5, atol=1e-6)
+    close(g["v"], bt.grad, rtol=1e-5, atol=1e-6)
+    g0, g1 = nb.grad(lambda x, y: nb.reduce_sum(x * y * y), argnums=(0, 1))(T(a), T(a))
+    close(g0, a * a)
+    close(g1, 2 * a * a)
+    v, g = nb.value_and_grad(lambda x: nb.mean(x * x))(T(a))
+    assert abs(v.item() - (a * a).mean().item()) < 1e-6
+    with pytest.raises(ValueError):
+        nb.grad(lambda x: x * 2.0)(T(a))
+
+
+def test_has_aux():
+    (v, aux), g = nb.value_and_grad(lambda x: (nb.reduce_sum(x * x), {"n": x.shape}), has_aux=True)(T(rand(3)))
+    assert aux["n"] == [3]
+    close(g, 2 * rand(3))
+
+
+def test_vjp_jvp_match_torch():
+    x = rand(5, seed=3)
+    out, pull = nb.vjp(lambda t: nb.sin(t) * nb.exp(t), T(x))
+    (g,) = pull(nb.ones_like(out))
+    close(g, (torch.cos(x) + torch.sin(x)) * torch.exp(x), rtol=1e-5, atol=1e-6)
+    out, tan = nb.jvp(lambda t: nb.sin(t) * nb.exp(t), (T(x),), (nb.ones_like(T(x)),))
+    close(tan, (torch.cos(x) + torch.sin(x)) * torch.exp(x), rtol=1e-5, atol=1e-6)
+
+
+def test_jacobians_and_hessians():
+    x = T(torch.tensor([1.0, 2.0]))
+    f = lambda v: nb.reduce_sum(v * v * v) + v[0] * v[1] * 2.0  # noqa: E731
+    H = torch.tensor([[6.0, 2.0], [2.0, 12.0]])
+    for h in (nb.jacrev(nb.grad(f)), nb.jacfwd(nb.grad(f)), nb.jacfwd(nb.jacrev(f)), nb.jacrev(nb.jacfwd(f))):
+        close(h(x), H, rtol=1e-5, atol=1e-5)
+    A = rand(3, 2, seed=4)
+    g = lambda v: nb.tanh(T(A) @ v)  # noqa: E731
+    J = torch.autograd.functional.jacobian(lambda v: torch.tanh(A @ v), torch.tensor([1.0, 2.0]))
+    close(nb.jacrev(g)(x), J, rtol=1e-5, atol=1e-6)
+    close(nb.jacfwd(g)(x), J, rtol=1e-5, atol=1e-6)
+    # matrix input: jacobian shape (*out, *in)
+    W = rand(2, 3, seed=5)
+    Jm = nb.jacrev(lambda w: nb.reduce_sum(w * w, axis=1))(T(W))
+    assert tuple(int(d) for d in Jm.shape) == (2, 2, 3)
+
+
+def test_third_derivative_by_nesting():
+    f = lambda x: x * x * x * x  # noqa: E731
+    d3 = nb.grad(lambda x: nb.reduce_sum(nb.grad(lambda y: nb.reduce_sum(nb.grad(lambda z: nb.reduce_sum(f(z)))(y)))(x)))
+    close(d3(T(torch.tensor([2.0]))), torch.tensor([48.0]))
+
+
+def test_vmap_in_axes_out_axes_nested_and_pytrees():
+    A, x = rand(5, 3, 4, seed=1), rand(5, 4, seed=2)
+    close(nb.vmap(lambda a, v: a @ v)(T(A), T(x)), torch.einsum("bij,bj->bi", A, x), rtol=1e-5, atol=1e-5)
+    close(nb.vmap(lambda a, v: a @ v, in_axes=(0, None))(T(A), T(x[0])), A @ x[0], rtol=1e-5, atol=1e-5)
+    close(nb.vmap(lambda a, v: a @ v, in_axes=(None, 0), out_axes=1)(T(A[0]), T(x)), (x @ A[0].T).T, rtol=1e-5, atol=1e-5)
+    nested = nb.vmap(nb.vmap(lambda a, b: nb.reduce_sum(a * b)))
+    close(nested(T(A[:, :, :2]), T(A[:, :, 2:])), (A[:, :, :2] * A[:, :, 2:]).sum(-1), rtol=1e-5, atol=1e-5)
+    tree = nb.vmap(lambda p: p["a"] * 2.0 + p["b"][0])({"a": T(x), "b": [T(x)]})
+    close(tree, 3 * x)
+
+    @nb.vmap
+    def dec(v):
+        return nb.softmax(v, axis=0)
+
+    close(dec(T(x)), torch.softmax(x, -1), rtol=1e-5, atol=1e-6)
+    with pytest.raises(ValueError):
+        nb.vmap(lambda a, b: a + b)(T(A), T(rand(4, 3, 4)))
+    close(nb.vmap(lambda v: nb.constant(1.0) + 0.0 * nb.reduce_sum(v), axis_size=5)(T(x)), torch.ones(5))
+
+
+def test_vmap_of_grad_per_example_gradients():
+    w, xs, ys = rand(4, seed=1), rand(6, 4, seed=2), rand(6, seed=3)
+    loss = lambda ww, x, y: (nb.reduce_sum(ww * x) - y) ** 2.0  # noqa: E731
+    per = nb.vmap(nb.grad(loss), in_axes=(None, 0, 0))(T(w), T(xs), T(ys))
+    ref = 2 * ((xs @ w) - ys).unsqueeze(1) * xs
+    close(per, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_compile_cache_and_stats():
+    calls = {"n": 0}
+
+    @nb.compile
+    def f(a, b):
+        calls["n"] += 1
+        return nb.relu(a @ b) + 1.0
+
+    a, b = rand(4, 5, seed=1), rand(5, 3, seed=2)
+    for i in range(4):
+        close(f(T(a + i), T(b)), torch.relu((a + i) @ b) + 1.0, rtol=1e-5, atol=1e-5)
+    assert calls["n"] == 1 and f.stats.misses == 1 and f.stats.hits == 3
+    f(T(rand(7, 5)), T(b))
+    assert calls["n"] == 2 and f.stats.misses == 2
+    assert "hits=3" in repr(f.stats)
+
+
+def test_compile_dynamic_dims_share_one_entry():
+    f = nb.compile(lambda x: nb.reduce_sum(x * 2.0, axis=0), dynamic_dims={0: {0: "batch"}})
+    for n in (3, 5, 3, 8):
+        x = rand(n, 4, seed=n)
+        close(f(T(x)), (x * 2).sum(0), rtol=1e-5, atol=1e-5)
+    assert f.stats.misses == 1 and f.stats.hits == 3 and len(f._cache) == 1
+
+
+def test_compile_training_step_with_optimizer_state_and_module():
+    from nabla_b200 import nn
+
+    torch.manual_seed(0)
+    x, y = rand(32, 4, seed=1), rand(32, 1, seed=2)
+
+    class MLP(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = nn.Linear(4, 8)
+            self.b = nn.Linear(8, 1)
+
+        def forward(self, t):
+            return self.b(nb.relu(self.a(t)))
+
+    model = MLP()
+    state = nn.adamw_init(model)
+
+    @nb.compile
+    def step(m, s, xx, yy):
+        l, g = nb.value_and_grad(lambda mm: nn.mse_loss(mm(xx), yy))(m)
+        m, s = nn.adamw_update(m, g, s, lr=1e-2)
+        return l, m, s
+
+    losses = []
+    for _ in range(25):
+        l, model, state = step(model, state, T(x), T(y))
+        losses.append(l.item())
+    assert losses[-1] < losses[0] * 0.7
+    assert step.stats.misses == 1 and step.stats.hits == 24
+    assert isinstance(model, MLP) and abs(state["step"].item() - 25.0) < 1e-6
+
+
+def test_compile_random_ops_draw_fresh_numbers():
+    f = nb.compile(lambda x: x + nb.uniform((4,)))
+    a = f(T(torch.zeros(4))).to_numpy()
+    b = f(T(torch.zeros(4))).to_numpy()
+    assert not np.allclose(a, b)
+
+
+def test_compile_sharded(mesh_2x4):
+    x, w = rand(8, 16, seed=1), rand(16, 8, seed=2)
+    f = nb.compile(lambda a, b: nb.exp((a @ b) * 0.01))
+    xs, ws = nb.shard(T(x), mesh_2x4, nb.P("dp", "tp")), nb.shard(T(w), mesh_2x4, nb.P("tp", None))
+    for _ in range(2):
+        out = f(xs, ws)
+    assert out.sharding is not None and f.stats.hits == 1
+    close(out, torch.exp((x @ w) * 0.01), rtol=1e-4, atol=1e-5)
+
+
+def test_backward_api_accumulates_grad():
+    w = T(rand(3, seed=1))
+    w.requires_grad = True
+    loss = nb.reduce_sum(w * w)
+    loss.backward()
+    close(w.grad, 2 * rand(3, seed=1))
+    nb.reduce_sum(w * 3.0).backward()
+    close(w.grad, 2 * rand(3, seed=1) + 3.0)
+    with pytest.raises(ValueError):
+        (w * 2.0).backward()
