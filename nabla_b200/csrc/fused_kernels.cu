@@ -140,73 +140,95 @@ __global__ void __launch_bounds__(128) layernorm_fwd_kernel(const T* __restrict_
   }
 }
 
-// Backward: dx per row (one warp per row); dgamma/dbeta partial sums per block are written to
-// `partial` ([gridDim.x][2][D] fp32) and folded by colsum_partials_kernel.
+// Backward, part 1: dx. One warp per row, the row stays in registers (like the forward).
 template <typename T, int VPL>
-__global__ void __launch_bounds__(128) layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
-                                                           const T* __restrict__ gamma, const float* __restrict__ mean,
-                                                           const float* __restrict__ rstd, T* __restrict__ dx,
-                                                           float* __restrict__ partial, int rows, int D,
-                                                           int rows_per_block) {
+__global__ void __launch_bounds__(128) layernorm_bwd_dx_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                                              const T* __restrict__ gamma, const float* __restrict__ mean,
+                                                              const float* __restrict__ rstd, T* __restrict__ dx,
+                                                              int rows, int D) {
   constexpr int V = Vec<T>::N;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  extern __shared__ float sh[];   // [4 warps][2][D]
-  float* my_dg = sh + (size_t)warp * 2 * D;
-  float* my_db = my_dg + D;
-  for (int c = lane; c < D; c += 32) { my_dg[c] = 0.f; my_db[c] = 0.f; }
-  __syncwarp();
-  const int r0 = blockIdx.x * rows_per_block;
-  const int r1 = min(rows, r0 + rows_per_block);
-  for (int row = r0 + warp; row < r1; row += 4) {
-    const T* xr = x + (size_t)row * D;
-    const T* dyr = dy + (size_t)row * D;
-    const float mu = mean[row], rs = rstd[row];
-    float xh[VPL][V], g[VPL][V];
-    float s1 = 0.f, s2 = 0.f;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const T* xr = x + (size_t)row * D;
+  const T* dyr = dy + (size_t)row * D;
+  const float mu = mean[row], rs = rstd[row];
+  float xh[VPL][V], g[VPL][V];
+  float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < VPL; ++i) {
-      const int c = (i * 32 + lane) * V;
-      if (c < D) {
-        float xv[V], dv[V], gm[V];
-        load_vec<T>(xr + c, xv);
-        load_vec<T>(dyr + c, dv);
-        if (gamma) load_vec<T>(gamma + c, gm);
+  for (int i = 0; i < VPL; ++i) {
+    const int c = (i * 32 + lane) * V;
+    if (c < D) {
+      float xv[V], dv[V], gm[V];
+      load_vec<T>(xr + c, xv);
+      load_vec<T>(dyr + c, dv);
+      if (gamma) load_vec<T>(gamma + c, gm);
 #pragma unroll
-        for (int j = 0; j < V; ++j) {
-          xh[i][j] = (xv[j] - mu) * rs;
-          my_dg[c + j] += dv[j] * xh[i][j];
-          my_db[c + j] += dv[j];
-          g[i][j] = dv[j] * (gamma ? gm[j] : 1.f);
-          s1 += g[i][j];
-          s2 += g[i][j] * xh[i][j];
-        }
-      }
-    }
-    s1 = warp_sum(s1) / D;
-    s2 = warp_sum(s2) / D;
-    T* dxr = dx + (size_t)row * D;
-#pragma unroll
-    for (int i = 0; i < VPL; ++i) {
-      const int c = (i * 32 + lane) * V;
-      if (c < D) {
-        float o[V];
-#pragma unroll
-        for (int j = 0; j < V; ++j) o[j] = (g[i][j] - s1 - xh[i][j] * s2) * rs;
-        store_vec<T>(dxr + c, o);
+      for (int j = 0; j < V; ++j) {
+        xh[i][j] = (xv[j] - mu) * rs;
+        g[i][j] = dv[j] * (gamma ? gm[j] : 1.f);
+        s1 += g[i][j];
+        s2 += g[i][j] * xh[i][j];
       }
     }
   }
+  s1 = warp_sum(s1) / D;
+  s2 = warp_sum(s2) / D;
+  T* dxr = dx + (size_t)row * D;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = (i * 32 + lane) * V;
+    if (c < D) {
+      float o[V];
+#pragma unroll
+      for (int j = 0; j < V; ++j) o[j] = (g[i][j] - s1 - xh[i][j] * s2) * rs;
+      store_vec<T>(dxr + c, o);
+    }
+  }
+}
+
+// Backward, part 2: dgamma = sum_rows dy * xhat, dbeta = sum_rows dy. Block = 32*V columns x a
+// slab of rows; 8 warps stride over the slab's rows with register accumulators; partial sums go
+// to `partial` ([gridDim.y][2][D] fp32) and are folded by colsum_partials_kernel.
+template <typename T>
+__global__ void __launch_bounds__(256) layernorm_bwd_dgb_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                                               const float* __restrict__ mean,
+                                                               const float* __restrict__ rstd,
+                                                               float* __restrict__ partial, int rows, int D,
+                                                               int rows_per_block) {
+  constexpr int V = Vec<T>::N;
+  __shared__ float sh[2][8][32 * V];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = (blockIdx.x * 32 + lane) * V;
+  const int r0 = blockIdx.y * rows_per_block, r1 = min(rows, r0 + rows_per_block);
+  float ag[V], ab[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) { ag[j] = 0.f; ab[j] = 0.f; }
+  if (c < D) {
+    for (int r = r0 + warp; r < r1; r += 8) {
+      float xv[V], dv[V];
+      load_vec<T>(x + (size_t)r * D + c, xv);
+      load_vec<T>(dy + (size_t)r * D + c, dv);
+      const float mu = mean[r], rs = rstd[r];
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        ag[j] += dv[j] * (xv[j] - mu) * rs;
+        ab[j] += dv[j];
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j) { sh[0][warp][lane * V + j] = ag[j]; sh[1][warp][lane * V + j] = ab[j]; }
   __syncthreads();
-  float* pg = partial + (size_t)blockIdx.x * 2 * D;
-  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+  for (int i = threadIdx.x; i < 32 * V; i += blockDim.x) {
     float a = 0.f, b = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      a += sh[(size_t)w * 2 * D + c];
-      b += sh[(size_t)w * 2 * D + D + c];
+    for (int w = 0; w < 8; ++w) { a += sh[0][w][i]; b += sh[1][w][i]; }
+    const int col = blockIdx.x * 32 * V + i;
+    if (col < D) {
+      partial[(size_t)blockIdx.y * 2 * D + col] = a;
+      partial[(size_t)blockIdx.y * 2 * D + D + col] = b;
     }
-    pg[c] = a;
-    pg[D + c] = b;
   }
 }
 
@@ -363,6 +385,27 @@ __global__ void __launch_bounds__(256) lse_pick_bwd_kernel(const T* __restrict__
 // AdamW with decoupled weight decay; P/G may be bf16 or fp32, moments fp32.
 // step-dependent bias corrections are passed as bc1 = 1 - b1^t, bc2 = 1 - b2^t via device scalars
 // when `hyper` is non-null: hyper = {lr, bc1, bc2, grad_scale}.
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float* out);
+template <>
+__device__ __forceinline__ void load8<bf16>(const bf16* p, float* out) { load_vec<bf16>(p, out); }
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float* out) {
+  load_vec<float>(p, out);
+  load_vec<float>(p + 4, out + 4);
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float* in);
+template <>
+__device__ __forceinline__ void store8<bf16>(bf16* p, const float* in) { store_vec<bf16>(p, in); }
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float* in) {
+  store_vec<float>(p, in);
+  store_vec<float>(p + 4, in + 4);
+}
+
+// 8 elements per thread with 16-byte accesses (all tensors come from the caching allocator and
+// are at least 16-byte aligned); the ragged tail is handled element-wise.
 template <typename TP, typename TG>
 __global__ void __launch_bounds__(256) adamw_kernel(const TP* __restrict__ p, const TG* __restrict__ g,
                                                    const float* __restrict__ m, const float* __restrict__ v,
@@ -371,23 +414,45 @@ __global__ void __launch_bounds__(256) adamw_kernel(const TP* __restrict__ p, co
                                                    float eps, float wd, float bc1, float bc2, float grad_scale,
                                                    const float* __restrict__ hyper) {
   if (hyper) { lr = hyper[0]; bc1 = hyper[1]; bc2 = hyper[2]; grad_scale = hyper[3]; }
-  const size_t i0 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
-  const size_t stride = (size_t)gridDim.x * blockDim.x * 4;
+  const float ibc1 = 1.f / bc1, ibc2 = 1.f / bc2;
+  const size_t i0 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const size_t stride = (size_t)gridDim.x * blockDim.x * 8;
   for (size_t i = i0; i < n; i += stride) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const size_t k = i + j;
-      if (k < n) {
-        const float gr = to_f<TG>(g[k]) * grad_scale;
-        const float pm = to_f<TP>(p[k]);
-        const float mn = b1 * m[k] + (1.f - b1) * gr;
-        const float vn = b2 * v[k] + (1.f - b2) * gr * gr;
-        const float mh = mn / bc1, vh = vn / bc2;
-        const float upd = mh / (sqrtf(vh) + eps) + wd * pm;
-        p_out[k] = from_f<TP>(pm - lr * upd);
-        m_out[k] = mn;
-        v_out[k] = vn;
+    float pv[8], gv[8], mv[8], vv[8];
+    const bool full = i + 8 <= n;
+    if (full) {
+      load8<TP>(p + i, pv);
+      load8<TG>(g + i, gv);
+      load8<float>(m + i, mv);
+      load8<float>(v + i, vv);
+    } else {
+      for (int j = 0; j < 8; ++j) {
+        const bool ok = i + j < n;
+        pv[j] = ok ? to_f<TP>(p[i + j]) : 0.f;
+        gv[j] = ok ? to_f<TG>(g[i + j]) : 0.f;
+        mv[j] = ok ? m[i + j] : 0.f;
+        vv[j] = ok ? v[i + j] : 0.f;
       }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gr = gv[j] * grad_scale;
+      mv[j] = b1 * mv[j] + (1.f - b1) * gr;
+      vv[j] = b2 * vv[j] + (1.f - b2) * gr * gr;
+      const float upd = (mv[j] * ibc1) / (sqrtf(vv[j] * ibc2) + eps) + wd * pv[j];
+      pv[j] -= lr * upd;
+    }
+    if (full) {
+      store8<TP>(p_out + i, pv);
+      store8<float>(m_out + i, mv);
+      store8<float>(v_out + i, vv);
+    } else {
+      for (int j = 0; j < 8; ++j)
+        if (i + j < n) {
+          p_out[i + j] = from_f<TP>(pv[j]);
+          m_out[i + j] = mv[j];
+          v_out[i + j] = vv[j];
+        }
     }
   }
 }
@@ -721,8 +786,8 @@ int nb_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y
 
 // Number of row slabs (= rows of the `partial` scratch buffer, each 2*D floats).
 int nb_layernorm_bwd_nblocks(int rows) {
-  int nb = (rows + 127) / 128;
-  if (nb > 148 * 2) nb = 148 * 2;
+  int nb = (rows + 255) / 256;
+  if (nb > 128) nb = 128;
   return nb < 1 ? 1 : nb;
 }
 
@@ -734,18 +799,19 @@ int nb_layernorm_bwd(const void* dy, const void* x, const void* gamma, const flo
   const int vpl = (D / V + 31) / 32;
   const int nb = nb_layernorm_bwd_nblocks(rows);
   const int rpb = (rows + nb - 1) / nb;
-  const size_t smem = (size_t)4 * 2 * D * sizeof(float);
-  if (smem > 200 * 1024) return -3;
-#define LN_BWD(T, VPL)                                                                                               \
-  {                                                                                                                  \
-    cudaFuncSetAttribute(layernorm_bwd_kernel<T, VPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-    layernorm_bwd_kernel<T, VPL><<<nb, 128, smem, STREAM>>>((const T*)dy, (const T*)x, (const T*)gamma, mean, rstd,  \
-                                                             (T*)dx, partial, rows, D, rpb);                         \
-    colsum_partials_kernel<T><<<(D + 255) / 256, 256, 0, STREAM>>>(partial, (T*)dgamma, (T*)dbeta, nb, D);           \
+  dim3 grid_dx((rows + 3) / 4);
+  dim3 grid_gb((D + 32 * V - 1) / (32 * V), nb);
+#define LN_BWD(T, VPL)                                                                                                \
+  {                                                                                                                   \
+    layernorm_bwd_dx_kernel<T, VPL><<<grid_dx, 128, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)gamma, mean,    \
+                                                                  rstd, (T*)dx, rows, D);                            \
+    layernorm_bwd_dgb_kernel<T><<<grid_gb, 256, 0, STREAM>>>((const T*)dy, (const T*)x, mean, rstd, partial, rows, D, \
+                                                              rpb);                                                   \
+    colsum_partials_kernel<T><<<(D + 255) / 256, 256, 0, STREAM>>>(partial, (T*)dgamma, (T*)dbeta, nb, D);            \
   }
   if (dtype) {
     if (vpl <= 1) LN_BWD(bf16, 1) else if (vpl <= 2) LN_BWD(bf16, 2) else if (vpl <= 4) LN_BWD(bf16, 4)
-    else if (vpl <= 8) LN_BWD(bf16, 8) else return -3;
+    else if (vpl <= 8) LN_BWD(bf16, 8) else if (vpl <= 16) LN_BWD(bf16, 16) else return -3;
   } else {
     if (vpl <= 1) LN_BWD(float, 1) else if (vpl <= 2) LN_BWD(float, 2) else if (vpl <= 4) LN_BWD(float, 4)
     else if (vpl <= 8) LN_BWD(float, 8) else if (vpl <= 16) LN_BWD(float, 16) else return -3;
@@ -804,7 +870,7 @@ int nb_adamw(const void* p, const void* g, const float* m, const float* v, void*
              long long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale,
              const float* hyper, int p_dtype, int g_dtype, void* stream) {
   if (n <= 0) return 0;
-  const int grid = grid_for((size_t)n, 256 * 4);
+  const int grid = grid_for((size_t)n, 256 * 8, 148 * 8);
 #define ADAMW(TP, TG) adamw_kernel<TP, TG><<<grid, 256, 0, STREAM>>>((const TP*)p, (const TG*)g, m, v, (TP*)p_out, m_out, v_out, (size_t)n, lr, b1, b2, eps, wd, bc1, bc2, grad_scale, hyper)
   if (p_dtype && g_dtype) ADAMW(bf16, bf16);
   else if (p_dtype) ADAMW(bf16, float);

@@ -165,15 +165,14 @@ def test_adamw_sgd_activation_rng_dropout_nf4_pool_conv():
     assert _rel(kernels.nf4_dequant(packed, absmax, 256, 64, torch.float32), ref) < 1e-3
     x = torch.randn(2, 9, 8, 5, device="cuda")
     for mode, tf in (("avg", torch.nn.functional.avg_pool2d), ("max", torch.nn.functional.max_pool2d)):
-        xr = x.clone().requires_grad_(True)
-        r = tf(xr.permute(0, 3, 1, 2), (3, 2), (2, 2), padding=(1, 1))
-        if mode == "avg":
-            pass
+        # oracle on the CPU in NCHW-contiguous fp32
+        xr = x.cpu().permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+        r = tf(xr, (3, 2), (2, 2), padding=(1, 1))
         yk = kernels.pool2d_fwd(x, 3, 2, 2, 2, 1, 1, mode)
-        assert _rel(yk, r.permute(0, 2, 3, 1)) < 1e-5
+        assert _rel(yk.cpu(), r.permute(0, 2, 3, 1)) < 1e-5
         dy = torch.randn_like(yk)
-        r.backward(dy.permute(0, 3, 1, 2))
-        assert _rel(kernels.pool2d_bwd(x, dy, 3, 2, 2, 2, 1, 1, mode), xr.grad) < 1e-5
+        r.backward(dy.cpu().permute(0, 3, 1, 2).contiguous())
+        assert _rel(kernels.pool2d_bwd(x, dy, 3, 2, 2, 2, 1, 1, mode).cpu(), xr.grad.permute(0, 2, 3, 1)) < 1e-5
     w = torch.randn(3, 3, 5, 4, device="cuda")
     bconv = torch.randn(4, device="cuda")
     ref = torch.nn.functional.conv2d(torch.nn.functional.pad(x.permute(0, 3, 1, 2), (2, 0, 1, 1)), w.permute(3, 2, 0, 1),
