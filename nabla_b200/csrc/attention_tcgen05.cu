@@ -341,6 +341,420 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+// ====================================================================== backward
+// One CTA per (batch, head, 128 keys). K_j and V_j stay in shared memory; the CTA walks over the
+// query tiles (64 rows) that see these keys. Per query tile, on the tensor cores:
+//   S^T  = K_j Q_i^T            (128 x 64, TMEM)       dP^T = V_j dO_i^T        (128 x 64, TMEM)
+//   P^T  = exp2(S^T * c - lse_i),  dS^T = P^T * (dP^T - delta_i) * scale      (softmax warps,
+//          thread = key row; both written as bf16 A operands into swizzled smem)
+//   dV  += P^T dO_i   dK += dS^T Q_i   (128 x 128 accumulators in TMEM for the whole loop)
+//   dQ_i^T = K_j^T dS^T (128 x 64)  -> fp32 vector reductions into a [B][H][D][Sq_pad] scratch
+// Two small kernels bracket it: delta_i = rowsum(dO_i * O_i), and the conversion of the dQ
+// scratch (transposed, fp32) to the caller's bf16 layout.
+constexpr int BQ = 64;
+
+struct BwdArgs {
+  int B, H, Sq, Skv, Sq_pad;
+  float scale, scale_log2;
+  int causal;
+  const float* lse;     // [B][H][Sq] natural log
+  const float* delta;   // [B][H][Sq]
+  float* dq_acc;        // [B][H][128][Sq_pad]
+  __nv_bfloat16 *dK, *dV;
+  long long dk_sb, dk_sh, dk_ss, dv_sb, dv_sh, dv_ss;
+  int* status;
+};
+
+struct BwdSmem {
+  static constexpr int HD = 128;
+  static constexpr int KV_BYTES = BN * HD * 2;        // 32 KB
+  static constexpr int QT_BYTES = BQ * HD * 2;        // 16 KB
+  static constexpr int XY_BYTES = BN * BQ * 2;        // 16 KB
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = OFF_K + KV_BYTES;
+  static constexpr int OFF_Q = OFF_V + KV_BYTES;      // 2 stages
+  static constexpr int OFF_DO = OFF_Q + 2 * QT_BYTES;
+  static constexpr int OFF_X = OFF_DO + 2 * QT_BYTES;
+  static constexpr int OFF_Y = OFF_X + XY_BYTES;
+  static constexpr int OFF_STAT = OFF_Y + XY_BYTES;   // lse2[2][64], delta[2][64]
+  static constexpr int OFF_BAR = OFF_STAT + 4 * BQ * 4;
+  static constexpr int TOTAL = OFF_BAR + 16 * 8 + 16 + 1024;
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                const BwdArgs args) {
+  using L = BwdSmem;
+  constexpr int HD = 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem + L::OFF_K;
+  uint8_t* sV = smem + L::OFF_V;
+  uint8_t* sQ = smem + L::OFF_Q;
+  uint8_t* sDO = smem + L::OFF_DO;
+  uint8_t* sX = smem + L::OFF_X;
+  uint8_t* sY = smem + L::OFF_Y;
+  float* s_lse2 = reinterpret_cast<float*>(smem + L::OFF_STAT);   // [2][64]
+  float* s_delta = s_lse2 + 2 * BQ;                               // [2][64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* qdo_full = bars + 1;    // [2]
+  uint64_t* qdo_empty = bars + 3;   // [2]
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* xy_full = bars + 6;
+  uint64_t* g2_done = bars + 7;
+  uint64_t* dq_free = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nkt = (args.Skv + BN - 1) / BN;
+  int bid = blockIdx.x;
+  const int jt = bid % nkt;
+  bid /= nkt;
+  const int h = bid % args.H;
+  const int b = bid / args.H;
+  const int k0 = jt * BN;
+  const int off = args.Skv - args.Sq;
+  const int nqt = (args.Sq + BQ - 1) / BQ;
+  int i_start = 0;
+  if (args.causal) {
+    const int first_q = k0 - off;             // first query row that sees key k0
+    i_start = first_q <= 0 ? 0 : first_q / BQ;
+  }
+  const int n_it = max(0, nqt - i_start);
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmDO);
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qdo_full[i], 1);
+      mbar_init(&qdo_empty[i], 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(xy_full, 128);
+    mbar_init(g2_done, 1);
+    mbar_init(dq_free, 128);
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_s = tmem_base, t_dp = tmem_base + 64, t_dq = tmem_base + 128, t_dv = tmem_base + 256,
+                 t_dk = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0 && n_it > 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * L::KV_BYTES);
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c) {
+        tma_load_4d(sK + c * (BN * 128), &tmK, kv_full, c * 64, k0, h, b);
+        tma_load_4d(sV + c * (BN * 128), &tmV, kv_full, c * 64, k0, h, b);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it & 1;
+        if (!mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1)) {
+          atomicExch(args.status, NB_ERR_TIMEOUT_PRODUCER);
+          break;
+        }
+        mbar_arrive_expect_tx(&qdo_full[st], 2 * L::QT_BYTES);
+        const int q0 = (i_start + it) * BQ;
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c) {
+          tma_load_4d(sQ + st * L::QT_BYTES + c * (BQ * 128), &tmQ, &qdo_full[st], c * 64, q0, h, b);
+          tma_load_4d(sDO + st * L::QT_BYTES + c * (BQ * 128), &tmDO, &qdo_full[st], c * 64, q0, h, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_it > 0) {
+      const uint32_t id_g1 = make_idesc_bf16(128, BQ, 0, 0);    // S^T, dP^T : A K-major, B K-major
+      const uint32_t id_g2 = make_idesc_bf16(128, HD, 0, 1);    // dV, dK    : A K-major, B MN-major
+      const uint32_t id_dq = make_idesc_bf16(128, BQ, 1, 1);    // dQ^T      : A MN-major, B MN-major
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aX = smem_u32(sX), aY = smem_u32(sY);
+      auto g1 = [&](int it) {
+        const int st = it & 1;
+        const uint32_t bq = smem_u32(sQ + st * L::QT_BYTES), bdo = smem_u32(sDO + st * L::QT_BYTES);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t ko = (k >> 2) * (BN * 128) + (k & 3) * 32;     // K/V chunk + in-row offset
+          const uint32_t qo = (k >> 2) * (BQ * 128) + (k & 3) * 32;
+          umma_f16_ss(t_s, make_smem_desc_sw128(aK + ko, 16, 1024), make_smem_desc_sw128(bq + qo, 16, 1024), id_g1,
+                      k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t ko = (k >> 2) * (BN * 128) + (k & 3) * 32;
+          const uint32_t qo = (k >> 2) * (BQ * 128) + (k & 3) * 32;
+          umma_f16_ss(t_dp, make_smem_desc_sw128(aV + ko, 16, 1024), make_smem_desc_sw128(bdo + qo, 16, 1024), id_g1,
+                      k != 0);
+        }
+        umma_commit(sdp_full);
+      };
+      bool ok = mbar_wait(kv_full, 0) && mbar_wait(&qdo_full[0], 0);
+      if (ok) {
+        tc_fence_after();
+        g1(0);
+      }
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int st = it & 1;
+        if (!mbar_wait(xy_full, it & 1)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t bq = smem_u32(sQ + st * L::QT_BYTES), bdo = smem_u32(sDO + st * L::QT_BYTES);
+        // dV += P^T dO_i ; dK += dS^T Q_i   (K = 64 query rows -> 4 k-steps)
+#pragma unroll
+        for (int k = 0; k < BQ / 16; ++k) {
+          const uint64_t da = make_smem_desc_sw128(aX + k * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(bdo + k * (16 * 128), BQ * 128, 1024);
+          umma_f16_ss(t_dv, da, db, id_g2, (it | k) != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < BQ / 16; ++k) {
+          const uint64_t da = make_smem_desc_sw128(aY + k * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(bq + k * (16 * 128), BQ * 128, 1024);
+          umma_f16_ss(t_dk, da, db, id_g2, (it | k) != 0);
+        }
+        if (it > 0) {
+          if (!mbar_wait(dq_free, (it - 1) & 1)) { ok = false; break; }
+          tc_fence_after();
+        }
+        // dQ_i^T = K_j^T dS^T : M = head dim, N = 64 queries, K = 128 keys
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k) {
+          const uint64_t da = make_smem_desc_sw128(aK + k * (16 * 128), BN * 128, 1024);
+          const uint64_t db = make_smem_desc_sw128(aY + k * (16 * 128), BN * 128, 1024);
+          umma_f16_ss(t_dq, da, db, id_dq, k != 0);
+        }
+        umma_commit(&qdo_empty[st]);
+        umma_commit(g2_done);
+        if (it + 1 < n_it) {
+          if (!mbar_wait(&qdo_full[(it + 1) & 1], ((it + 1) >> 1) & 1)) { ok = false; break; }
+          tc_fence_after();
+          g1(it + 1);
+        }
+      }
+      if (!ok) atomicExch(args.status, NB_ERR_TIMEOUT_MMA);
+    }
+  } else if (warp >= 4) {
+    const int wq = warp & 3;
+    const int r = wq * 32 + lane;           // key row inside the tile / head-dim row for dQ^T
+    const int et = threadIdx.x - 128;
+    const int key = k0 + r;
+    const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;
+    const long long bh = (long long)b * args.H + h;
+    bool ok = true;
+    auto drain_dq = [&](int it) {
+      // dQ^T tile: this thread holds head-dim row r, 64 consecutive queries
+      const int q0 = (i_start + it) * BQ;
+      float* dst = args.dq_acc + (bh * HD + r) * (long long)args.Sq_pad + q0;
+#pragma unroll
+      for (int c = 0; c < BQ / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_dq + lane_addr + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          red_add_v4(dst + c * 32 + u * 4, __uint_as_float(v[u * 4]), __uint_as_float(v[u * 4 + 1]),
+                     __uint_as_float(v[u * 4 + 2]), __uint_as_float(v[u * 4 + 3]));
+      }
+    };
+    for (int it = 0; it < n_it; ++it) {
+      const int q0 = (i_start + it) * BQ;
+      const int pb = it & 1;
+      // stage the per-query statistics of this tile
+      {
+        const int qi = q0 + (et & 63);
+        const bool inr = qi < args.Sq;
+        if (et < 64) s_lse2[pb * BQ + et] = inr ? args.lse[bh * args.Sq + qi] * 1.4426950408889634f : INFINITY;
+        else s_delta[pb * BQ + (et - 64)] = inr ? args.delta[bh * args.Sq + qi] : 0.f;
+      }
+      named_bar_sync(1, 128);
+      if (ok && !mbar_wait(sdp_full, it & 1)) {
+        atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      float p[BQ], ds[BQ];
+#pragma unroll
+      for (int c = 0; c < BQ / 32; ++c) {
+        uint32_t v[32], w[32];
+        tmem_ld_32x32(t_s + lane_addr + c * 32, v);
+        tmem_ld_32x32(t_dp + lane_addr + c * 32, w);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          p[c * 32 + i] = __uint_as_float(v[i]);
+          ds[c * 32 + i] = __uint_as_float(w[i]);
+        }
+      }
+      const bool need_mask = args.causal && (k0 + BN - 1 > q0 + off);
+      const bool key_ok = key < args.Skv;
+#pragma unroll
+      for (int c = 0; c < BQ; ++c) {
+        float pv = exp2f(p[c] * args.scale_log2 - s_lse2[pb * BQ + c]);
+        if (!key_ok || (need_mask && key > q0 + c + off)) pv = 0.f;
+        p[c] = pv;
+        ds[c] = pv * (ds[c] - s_delta[pb * BQ + c]) * args.scale;
+      }
+      if (it > 0) {
+        if (!mbar_wait(g2_done, (it - 1) & 1)) {
+          atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
+          ok = false;
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      // X = P^T, Y = dS^T as bf16, one 128-byte swizzled row per key
+      {
+        uint8_t* xr = sX + r * 128;
+        uint8_t* yr = sY + r * 128;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          uint4 px, py;
+          uint32_t* wx = reinterpret_cast<uint32_t*>(&px);
+          uint32_t* wy = reinterpret_cast<uint32_t*>(&py);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 a = __floats2bfloat162_rn(p[u * 8 + 2 * e], p[u * 8 + 2 * e + 1]);
+            __nv_bfloat162 d2 = __floats2bfloat162_rn(ds[u * 8 + 2 * e], ds[u * 8 + 2 * e + 1]);
+            wx[e] = *reinterpret_cast<uint32_t*>(&a);
+            wy[e] = *reinterpret_cast<uint32_t*>(&d2);
+          }
+          const int sw = (u ^ (r & 7)) << 4;
+          *reinterpret_cast<uint4*>(xr + sw) = px;
+          *reinterpret_cast<uint4*>(yr + sw) = py;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(xy_full);
+      if (it > 0) {
+        drain_dq(it - 1);
+        tc_fence_before();
+        mbar_arrive(dq_free);
+      }
+    }
+    if (ok && n_it > 0) {
+      if (!mbar_wait(g2_done, (n_it - 1) & 1)) {
+        atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tc_fence_after();
+        drain_dq(n_it - 1);
+      }
+    }
+    if (ok) {
+      // dK, dV rows of this key
+      __nv_bfloat16* dkr = args.dK + (long long)b * args.dk_sb + (long long)h * args.dk_sh + (long long)key * args.dk_ss;
+      __nv_bfloat16* dvr = args.dV + (long long)b * args.dv_sb + (long long)h * args.dv_sh + (long long)key * args.dv_ss;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* dst = which ? dvr : dkr;
+        const uint32_t src = which ? t_dv : t_dk;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t v[32];
+          if (n_it > 0) {
+            tmem_ld_32x32(src + lane_addr + c * 32, v);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0;
+          }
+          if (key < args.Skv) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint4 pk;
+              uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(v[u * 8 + 2 * e]), __uint_as_float(v[u * 8 + 2 * e + 1]));
+                pw[e] = *reinterpret_cast<uint32_t*>(&hh);
+              }
+              *reinterpret_cast<uint4*>(dst + c * 32 + u * 8) = pk;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[b][h][q] = sum_d dO * O ; one warp per row, head dim 128 (4 elements per lane)
+__global__ void __launch_bounds__(128) attn_delta_kernel(const __nv_bfloat16* __restrict__ dO,
+                                                        const __nv_bfloat16* __restrict__ O, float* __restrict__ delta,
+                                                        int B, int H, int Sq, int D, long long do_sb, long long do_sh,
+                                                        long long do_ss, long long o_sb, long long o_sh, long long o_ss) {
+  const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= (long long)B * H * Sq) return;
+  const int q = row % Sq;
+  const int h = (row / Sq) % H;
+  const int b = row / ((long long)Sq * H);
+  const __nv_bfloat16* a = dO + b * do_sb + h * do_sh + q * do_ss;
+  const __nv_bfloat16* c = O + b * o_sb + h * o_sh + q * o_ss;
+  float acc = 0.f;
+  for (int d = lane * 4; d < D; d += 128) {
+    const uint2 ra = *reinterpret_cast<const uint2*>(a + d);
+    const uint2 rc = *reinterpret_cast<const uint2*>(c + d);
+    const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ra);
+    const __nv_bfloat162* pc = reinterpret_cast<const __nv_bfloat162*>(&rc);
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const float2 x = __bfloat1622float2(pa[e]), y = __bfloat1622float2(pc[e]);
+      acc += x.x * y.x + x.y * y.y;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) delta[row] = acc;
+}
+
+// dq[b][h][q][d] (bf16, strided) = dq_acc[b][h][d][q] (fp32): 32 x 32 transposing tiles
+__global__ void __launch_bounds__(256) attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
+                                                             int H, int Sq, int Sq_pad, int D, long long sb, long long sh,
+                                                             long long ss) {
+  __shared__ float tile[32][33];
+  const int bh = blockIdx.z;
+  const int b = bh / H, h = bh % H;
+  const int q0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+  for (int i = ty; i < 32; i += 8) {
+    const int d = d0 + i, q = q0 + tx;
+    tile[i][tx] = (d < D && q < Sq) ? acc[((long long)bh * D + d) * Sq_pad + q] : 0.f;
+  }
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8) {
+    const int q = q0 + i, d = d0 + tx;
+    if (q < Sq && d < D) dq[b * sb + h * sh + q * ss + d] = __float2bfloat16(tile[tx][i]);
+  }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -423,3 +837,56 @@ extern "C" int nb_attn_fwd(const void* q, const void* k, const void* v, void* o,
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return D == 128 ? launch_fwd<128>(tq, tk, tv, a, s) : launch_fwd<64>(tq, tk, tv, a, s);
 }
+
+// Backward. All tensors are (B, H, S, 128) bf16 views with the head dim contiguous (element strides
+// given per tensor); lse fp32 [B][H][Sq] from the forward; dq_acc: zeroed fp32 scratch of
+// B*H*128*Sq_pad elements (Sq_pad = Sq rounded up to 64); delta: fp32 scratch [B][H][Sq].
+extern "C" int nb_attn_bwd(const void* dO, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                           void* dq, void* dk, void* dv, float* dq_acc, int B, int H, int Sq, int Skv, int D,
+                           long long q_sb, long long q_sh, long long q_ss, long long k_sb, long long k_sh, long long k_ss,
+                           long long v_sb, long long v_sh, long long v_ss, long long do_sb, long long do_sh,
+                           long long do_ss, long long o_sb, long long o_sh, long long o_ss, long long dq_sb,
+                           long long dq_sh, long long dq_ss, long long dk_sb, long long dk_sh, long long dk_ss,
+                           long long dv_sb, long long dv_sh, long long dv_ss, float scale, int causal, float* delta,
+                           int* status, void* stream) {
+  using namespace nba;
+  if (D != 128) return -10;
+  if (B <= 0 || H <= 0 || Sq <= 0 || Skv <= 0) return 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const long long st[] = {q_sb, q_sh, q_ss, k_sb, k_sh, k_ss, v_sb, v_sh, v_ss, do_sb, do_sh, do_ss,
+                          o_sb, o_sh, o_ss, dq_sb, dq_sh, dq_ss, dk_sb, dk_sh, dk_ss, dv_sb, dv_sh, dv_ss};
+  for (long long x : st)
+    if (x & 7) return -12;
+  const int Sq_pad = (Sq + BQ - 1) / BQ * BQ;
+  const long long rows = (long long)B * H * Sq;
+  attn_delta_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(
+      reinterpret_cast<const __nv_bfloat16*>(dO), reinterpret_cast<const __nv_bfloat16*>(o), delta, B, H, Sq, D, do_sb,
+      do_sh, do_ss, o_sb, o_sh, o_ss);
+  CUtensorMap tq, tk, tv, tdo;
+  int r;
+  if ((r = make_map4(&tq, q, B, H, Sq, D, q_sb, q_sh, q_ss, BQ))) return r;
+  if ((r = make_map4(&tdo, dO, B, H, Sq, D, do_sb, do_sh, do_ss, BQ))) return r;
+  if ((r = make_map4(&tk, k, B, H, Skv, D, k_sb, k_sh, k_ss, BN))) return r;
+  if ((r = make_map4(&tv, v, B, H, Skv, D, v_sb, v_sh, v_ss, BN))) return r;
+  BwdArgs a;
+  a.B = B; a.H = H; a.Sq = Sq; a.Skv = Skv; a.Sq_pad = Sq_pad;
+  a.scale = scale; a.scale_log2 = scale * 1.4426950408889634f;
+  a.causal = causal;
+  a.lse = lse; a.delta = delta; a.dq_acc = dq_acc;
+  a.dK = reinterpret_cast<__nv_bfloat16*>(dk); a.dV = reinterpret_cast<__nv_bfloat16*>(dv);
+  a.dk_sb = dk_sb; a.dk_sh = dk_sh; a.dk_ss = dk_ss; a.dv_sb = dv_sb; a.dv_sh = dv_sh; a.dv_ss = dv_ss;
+  a.status = status;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL) != cudaSuccess)
+      return -2;
+    configured = true;
+  }
+  const int nkt = (Skv + BN - 1) / BN;
+  attn_bwd_kernel<<<(unsigned)((long long)nkt * H * B), NTHREADS, BwdSmem::TOTAL, s>>>(tq, tk, tv, tdo, a);
+  dim3 grid((Sq + 31) / 32, (D + 31) / 32, B * H);
+  attn_dq_convert_kernel<<<grid, 256, 0, s>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), H, Sq, Sq_pad, D, dq_sb, dq_sh,
+                                              dq_ss);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+

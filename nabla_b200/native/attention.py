@@ -34,7 +34,7 @@ def _lib():
             if hasattr(lib, "nb_attn_bwd"):
                 g = lib.nb_attn_bwd
                 g.restype = c_int
-                g.argtypes = [c_vp] * 10 + [c_int] * 5 + [c_ll] * 24 + [c_f, c_int, c_vp, c_vp]
+                g.argtypes = [c_vp] * 10 + [c_int] * 5 + [c_ll] * 24 + [c_f, c_int, c_vp, c_vp, c_vp]
                 _bwd = g
     return _fwd
 
@@ -95,24 +95,28 @@ def sdpa_bwd(do, q, k, v, o, lse, *, causal: bool, scale: float, out=None):
     global launch_count
     from . import ptr, status_word, stream_ptr
 
+    _lib()
     q, k, v, do, o = _prep(q), _prep(k), _prep(v), _prep(do), _prep(o)
     B, H, Sq, D = q.shape
     Skv = k.shape[2]
+    if D != 128:
+        raise ValueError("native attention backward supports head_dim 128")
     if out is None:
         dq = torch.empty((B, Sq, H, D), dtype=q.dtype, device=q.device).permute(0, 2, 1, 3)
         dk = torch.empty((B, Skv, H, D), dtype=q.dtype, device=q.device).permute(0, 2, 1, 3)
         dv = torch.empty((B, Skv, H, D), dtype=q.dtype, device=q.device).permute(0, 2, 1, 3)
     else:
         dq, dk, dv = out
-    # fp32 scratch: dQ accumulator and delta = rowsum(dO * O)
-    dq_acc = torch.zeros((B, H, Sq, D), dtype=torch.float32, device=q.device)
+    # fp32 scratch: transposed dQ accumulator [B][H][D][Sq_pad] and delta = rowsum(dO * O)
+    sq_pad = (Sq + 63) // 64 * 64
+    dq_acc = torch.zeros((B, H, D, sq_pad), dtype=torch.float32, device=q.device)
     delta = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
     st = status_word(q.device)
     args = [ptr(do), ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse.contiguous()), ptr(dq), ptr(dk), ptr(dv), ptr(dq_acc)]
     strides = []
     for t in (q, k, v, do, o, dq, dk, dv):
         strides += [t.stride(0), t.stride(1), t.stride(2)]
-    rc = _bwd(*args, B, H, Sq, Skv, D, *strides, float(scale), int(causal), ptr(delta), stream_ptr())
+    rc = _bwd(*args, B, H, Sq, Skv, D, *strides, float(scale), int(causal), ptr(delta), ptr(st), stream_ptr())
     if rc != 0:
         raise RuntimeError(f"nb_attn_bwd failed with code {rc}")
     launch_count += 3
