@@ -83,6 +83,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  {
+    __shared__ int s_abort;   // an earlier bounded wait on this device already failed: leave (uniformly)
+    if (threadIdx.x == 0) s_abort = *reinterpret_cast<volatile int*>(args.status);
+    __syncthreads();
+    if (s_abort != 0) return;
+  }
   const int nqt = (args.Sq + BM - 1) / BM;
   int bid = blockIdx.x;
   const int qt = nqt - 1 - (bid % nqt);   // heavy (late) causal tiles first
@@ -412,6 +418,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  {
+    __shared__ int s_abort;   // an earlier bounded wait on this device already failed: leave (uniformly)
+    if (threadIdx.x == 0) s_abort = *reinterpret_cast<volatile int*>(args.status);
+    __syncthreads();
+    if (s_abort != 0) return;
+  }
   const int nkt = (args.Skv + BN - 1) / BN;
   int bid = blockIdx.x;
   const int jt = bid % nkt;

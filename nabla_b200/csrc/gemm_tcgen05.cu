@@ -89,6 +89,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // a previous bounded wait failed on this device: do not pile more waits on top of it
+  {
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) s_abort = *reinterpret_cast<volatile int*>(args.status);
+    __syncthreads();
+    if (s_abort != 0) return;   // uniform for the whole CTA
+  }
 
   const int num_m = (args.M + BLOCK_M - 1) / BLOCK_M;
   const int num_n = (args.N + BN - 1) / BN;

@@ -1,0 +1,307 @@
+// Collectives over NVLink 5 / NVSwitch peer memory for one-process-per-GPU groups.
+//
+// Every rank of a group owns a *symmetric workspace*: the same allocation size on every GPU,
+// mapped into all peers (torch symmetric memory does the exchange of handles), optionally
+// bound to an NVSwitch multicast object. Layout of a workspace:
+//
+//   [0, 8 KB)      barrier flags   u32 [MAX_BLOCKS][MAX_WORLD]   (monotonic epochs, never reset)
+//   [16 KB, 48 KB) tile flags      u32 [8192]                    (fused GEMM + all-reduce)
+//   [56 KB, 64 KB) done counters   u32
+//   [64 KB, ...)   data
+//
+// Kernels here: cross-rank barrier, all-reduce (one-shot P2P loads, two-shot reduce-scatter +
+// all-gather, NVLS multimem.ld_reduce + multimem.st), all-gather, reduce-scatter, all-to-all and
+// broadcast as peer loads. They replace the MAX graph collectives the reference calls
+// (nabla/ops/communication/all_reduce.py:94-108, all_gather.py:189-199,
+// reduce_scatter.py:167-170, broadcast.py:56-80), and, unlike those, take the device group of
+// a mesh axis, so reductions along 'tp' of a ('dp','tp') mesh stay inside each tp group.
+//
+// Every wait is bounded (2 s): on expiry the kernel writes NB_ERR_TIMEOUT_PEER to the status
+// word and returns, so a lost peer surfaces as an error on the host instead of a hang.
+#include "sm100_ptx.cuh"
+
+namespace nbc {
+using namespace nb;
+
+constexpr int MAX_WORLD = 8;
+constexpr int MAX_BLOCKS = 256;
+constexpr int FLAG_BYTES = 64 * 1024;
+constexpr int TILE_FLAG_OFFSET = 16 * 1024;
+constexpr int DONE_OFFSET = 56 * 1024;
+
+struct Group {
+  void* const* bufs;   // device array [world] of peer base pointers of the workspace
+  void* mc;            // multicast base pointer of the workspace (nullptr: no NVLS)
+  int rank, world;
+  unsigned epoch;      // increases by one per collective call on this workspace
+  int* status;
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool wait_ge(const unsigned* p, unsigned target, int* status) {
+  if ((int)(ld_acquire_sys(p) - target) >= 0) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  unsigned spins = 0;
+  while (true) {
+    if ((int)(ld_acquire_sys(p) - target) >= 0) return true;
+    if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+      atomicExch(status, NB_ERR_TIMEOUT_PEER);
+      return false;
+    }
+  }
+}
+
+// All threads of the block call this. Block b of every rank meets block b of every other rank.
+// `phase` distinguishes several barriers inside one kernel (epoch * 4 + phase is the value).
+__device__ __forceinline__ bool block_barrier(const Group& g, int phase) {
+  __syncthreads();
+  bool ok = true;
+  const unsigned val = g.epoch * 4u + (unsigned)phase;
+  if (threadIdx.x < g.world) {
+    const int peer = threadIdx.x;
+    __threadfence_system();
+    unsigned* remote = reinterpret_cast<unsigned*>(g.bufs[peer]) + (blockIdx.x * MAX_WORLD + g.rank);
+    st_release_sys(remote, val);
+    const unsigned* mine = reinterpret_cast<const unsigned*>(g.bufs[g.rank]) + (blockIdx.x * MAX_WORLD + peer);
+    ok = wait_ge(mine, val, g.status);
+  }
+  return __syncthreads_and(ok);
+}
+
+// ---------------------------------------------------------------- 16-byte vector helpers
+struct alignas(16) V4 { unsigned x, y, z, w; };
+
+template <typename T> struct Acc;
+template <> struct Acc<float> {
+  static constexpr int N = 4;
+  __device__ static void unpack(const V4& v, float* f) {
+    f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+  }
+  __device__ static V4 pack(const float* f) {
+    return {__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3])};
+  }
+};
+template <> struct Acc<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void unpack(const V4& v, float* f) {
+    const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  __device__ static V4 pack(const float* f) {
+    unsigned w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<unsigned*>(&h);
+    }
+    return {w[0], w[1], w[2], w[3]};
+  }
+};
+
+__device__ __forceinline__ float combine(float a, float b, int op) {
+  return op == 0 ? a + b : op == 1 ? fmaxf(a, b) : op == 2 ? fminf(a, b) : a * b;
+}
+
+__device__ __forceinline__ V4 ld_peer(const void* p) {
+  V4 v;
+  asm volatile("ld.global.relaxed.sys.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+template <typename T> __device__ __forceinline__ V4 mc_ld_reduce(const void* p);
+template <> __device__ __forceinline__ V4 mc_ld_reduce<__nv_bfloat16>(const void* p) {
+  V4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+template <> __device__ __forceinline__ V4 mc_ld_reduce<float>(const void* p) {
+  V4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void mc_st(void* p, const V4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// ---------------------------------------------------------------- all-reduce
+// The caller has copied its contribution into the workspace data region (offset `off` bytes).
+// algo 0: one-shot   every rank reads all peers and reduces everything          (small messages)
+// algo 1: two-shot   rank r reduces chunk r in place, then everyone reads all chunks (large)
+// algo 2: multimem   rank r: ld_reduce chunk r through the switch, multimem.st it back to all
+// Result is written to `out` (ordinary memory, n elements).
+template <typename T>
+__global__ void __launch_bounds__(512) allreduce_kernel(Group g, long long off, T* __restrict__ out, long long n,
+                                                       int algo, int op) {
+  constexpr int N = Acc<T>::N;
+  const long long nvec = n / N;                       // n is padded to a multiple of N * world by the host
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  if (!block_barrier(g, 0)) return;
+  const char* mine = reinterpret_cast<const char*>(g.bufs[g.rank]) + FLAG_BYTES + off;
+  if (algo == 0) {
+    for (long long i = tid; i < nvec; i += nthreads) {
+      float acc[N];
+      Acc<T>::unpack(ld_peer(mine + i * 16), acc);
+      for (int p = 1; p < g.world; ++p) {
+        const int peer = (g.rank + p) % g.world;
+        float v[N];
+        Acc<T>::unpack(ld_peer(reinterpret_cast<const char*>(g.bufs[peer]) + FLAG_BYTES + off + i * 16), v);
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[j] = combine(acc[j], v[j], op);
+      }
+      reinterpret_cast<V4*>(out)[i] = Acc<T>::pack(acc);
+    }
+    block_barrier(g, 1);      // nobody may overwrite its buffer while peers still read it
+    return;
+  }
+  const long long chunk = nvec / g.world;
+  const long long c0 = chunk * g.rank;
+  if (algo == 1) {
+    for (long long i = tid; i < chunk; i += nthreads) {
+      float acc[N];
+      Acc<T>::unpack(ld_peer(mine + (c0 + i) * 16), acc);
+      for (int p = 1; p < g.world; ++p) {
+        const int peer = (g.rank + p) % g.world;
+        float v[N];
+        Acc<T>::unpack(ld_peer(reinterpret_cast<const char*>(g.bufs[peer]) + FLAG_BYTES + off + (c0 + i) * 16), v);
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[j] = combine(acc[j], v[j], op);
+      }
+      *reinterpret_cast<V4*>(const_cast<char*>(mine) + (c0 + i) * 16) = Acc<T>::pack(acc);
+    }
+    if (!block_barrier(g, 1)) return;
+    for (long long i = tid; i < nvec; i += nthreads) {
+      const int owner = (int)min((long long)(g.world - 1), i / chunk);
+      reinterpret_cast<V4*>(out)[i] =
+          ld_peer(reinterpret_cast<const char*>(g.bufs[owner]) + FLAG_BYTES + off + i * 16);
+    }
+    block_barrier(g, 2);
+    return;
+  }
+  // multimem (sum only)
+  char* mc = reinterpret_cast<char*>(g.mc) + FLAG_BYTES + off;
+  for (long long i = tid; i < chunk; i += nthreads) {
+    const V4 v = mc_ld_reduce<T>(mc + (c0 + i) * 16);
+    mc_st(mc + (c0 + i) * 16, v);
+  }
+  if (!block_barrier(g, 1)) return;
+  for (long long i = tid; i < nvec; i += nthreads) reinterpret_cast<V4*>(out)[i] = ld_peer(mine + i * 16);
+  block_barrier(g, 2);
+}
+
+// ---------------------------------------------------------------- gather-style collectives
+// mode 0 all_gather    : out[p * chunk + i] = peer p's data[i]                  (chunk bytes each)
+// mode 1 reduce_scatter: out[i] = sum_p peer p's data[rank * chunk + i]
+// mode 2 all_to_all    : out[p * chunk + i] = peer p's data[rank * chunk + i]
+// mode 3 broadcast     : out[i] = root's data[i]            (root in `op`)
+template <typename T>
+__global__ void __launch_bounds__(512) gather_kernel(Group g, long long off, T* __restrict__ out, long long chunk_elems,
+                                                    int mode, int op) {
+  constexpr int N = Acc<T>::N;
+  const long long cvec = chunk_elems / N;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  if (!block_barrier(g, 0)) return;
+  if (mode == 1) {
+    for (long long i = tid; i < cvec; i += nthreads) {
+      float acc[N];
+#pragma unroll
+      for (int j = 0; j < N; ++j) acc[j] = 0.f;
+      for (int p = 0; p < g.world; ++p) {
+        const int peer = (g.rank + p) % g.world;
+        float v[N];
+        Acc<T>::unpack(ld_peer(reinterpret_cast<const char*>(g.bufs[peer]) + FLAG_BYTES + off + (g.rank * cvec + i) * 16), v);
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[j] += v[j];
+      }
+      reinterpret_cast<V4*>(out)[i] = Acc<T>::pack(acc);
+    }
+  } else if (mode == 3) {
+    for (long long i = tid; i < cvec; i += nthreads)
+      reinterpret_cast<V4*>(out)[i] = ld_peer(reinterpret_cast<const char*>(g.bufs[op]) + FLAG_BYTES + off + i * 16);
+  } else {
+    for (int p = 0; p < g.world; ++p) {
+      const int peer = (g.rank + p) % g.world;
+      const char* src = reinterpret_cast<const char*>(g.bufs[peer]) + FLAG_BYTES + off + (mode == 2 ? g.rank * cvec * 16 : 0);
+      for (long long i = tid; i < cvec; i += nthreads) reinterpret_cast<V4*>(out)[peer * cvec + i] = ld_peer(src + i * 16);
+    }
+  }
+  block_barrier(g, 1);
+}
+
+__global__ void barrier_kernel(Group g) { block_barrier(g, 0); }
+
+// A wait on a flag that nobody sets: exercises the bounded-wait error path without any fault.
+__global__ void wait_flag_kernel(const unsigned* flag, unsigned target, int* status, unsigned long long limit_ns) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    while ((int)(ld_acquire_sys(flag) - target) < 0) {
+      if (globaltimer_ns() - t0 > limit_ns) {
+        atomicExch(status, NB_ERR_TIMEOUT_PEER);
+        break;
+      }
+    }
+  }
+}
+
+}  // namespace nbc
+
+using namespace nbc;
+#define STREAM reinterpret_cast<cudaStream_t>(stream)
+
+static Group make_group(void* const* bufs, void* mc, int rank, int world, unsigned epoch, int* status) {
+  Group g;
+  g.bufs = bufs; g.mc = mc; g.rank = rank; g.world = world; g.epoch = epoch; g.status = status;
+  return g;
+}
+
+extern "C" {
+
+int nb_comm_flag_bytes() { return FLAG_BYTES; }
+int nb_comm_tile_flag_offset() { return TILE_FLAG_OFFSET; }
+int nb_comm_done_offset() { return DONE_OFFSET; }
+
+int nb_comm_barrier(void* const* bufs, int rank, int world, unsigned epoch, int* status, void* stream) {
+  barrier_kernel<<<1, 32, 0, STREAM>>>(make_group(bufs, nullptr, rank, world, epoch, status));
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// n must be a multiple of (16 / sizeof(T)) * world; dtype 0 fp32, 1 bf16; op 0 sum 1 max 2 min 3 prod.
+int nb_comm_allreduce(void* const* bufs, void* mc, int rank, int world, unsigned epoch, long long off, void* out,
+                      long long n, int dtype, int algo, int op, int blocks, int* status, void* stream) {
+  if (world > MAX_WORLD || blocks > MAX_BLOCKS) return -2;
+  if (algo == 2 && (mc == nullptr || op != 0)) return -3;
+  Group g = make_group(bufs, mc, rank, world, epoch, status);
+  if (dtype) allreduce_kernel<__nv_bfloat16><<<blocks, 512, 0, STREAM>>>(g, off, (__nv_bfloat16*)out, n, algo, op);
+  else allreduce_kernel<float><<<blocks, 512, 0, STREAM>>>(g, off, (float*)out, n, algo, op);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int nb_comm_gather(void* const* bufs, int rank, int world, unsigned epoch, long long off, void* out, long long chunk_elems,
+                   int dtype, int mode, int op, int blocks, int* status, void* stream) {
+  if (world > MAX_WORLD || blocks > MAX_BLOCKS) return -2;
+  Group g = make_group(bufs, nullptr, rank, world, epoch, status);
+  if (dtype) gather_kernel<__nv_bfloat16><<<blocks, 512, 0, STREAM>>>(g, off, (__nv_bfloat16*)out, chunk_elems, mode, op);
+  else gather_kernel<float><<<blocks, 512, 0, STREAM>>>(g, off, (float*)out, chunk_elems, mode, op);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int nb_comm_wait_flag(const unsigned* flag, unsigned target, int* status, unsigned long long limit_ns, void* stream) {
+  wait_flag_kernel<<<1, 32, 0, STREAM>>>(flag, target, status, limit_ns);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+}  // extern "C"

@@ -22,7 +22,7 @@ enum : int {
   NB_ERR_TIMEOUT_PEER = 4,
 };
 
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+constexpr unsigned long long WAIT_LIMIT_NS = 500000000ull;  // 0.5 s
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

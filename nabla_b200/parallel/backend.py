@@ -58,6 +58,11 @@ def all_gather(buf: torch.Tensor, mesh, axes: Sequence[str], dim: int, sizes: Se
         return buf
     buf = buf.contiguous()
     even = sizes is None or len(set(sizes)) == 1
+    nat = _native()
+    if nat is not None and even and dim == 0 and nat.supports(buf) and (buf.numel() * buf.element_size()) % 16 == 0 \
+            and buf.numel() * buf.element_size() * n + 4096 <= nat.DEFAULT_BYTES - 65536:
+        stats["native_calls"] += 1
+        return nat.all_gather_dim0(buf, mesh, tuple(axes))
     stats["nccl_calls"] += 1
     if even:
         if dim == 0:
@@ -87,6 +92,11 @@ def reduce_scatter(buf: torch.Tensor, mesh, axes: Sequence[str], dim: int) -> to
     if buf.shape[dim] % n != 0:
         return None
     x = buf.movedim(dim, 0).contiguous() if dim != 0 else buf.contiguous()
+    nat = _native()
+    if nat is not None and nat.supports(x) and (x.numel() // n * x.element_size()) % 16 == 0:
+        stats["native_calls"] += 1
+        out = nat.reduce_scatter_dim0(x, mesh, tuple(axes))
+        return out.movedim(0, dim) if dim != 0 else out
     out = torch.empty((x.shape[0] // n,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
     stats["nccl_calls"] += 1
     dist.reduce_scatter_tensor(out, x, group=pg)

@@ -1,0 +1,220 @@
+"""Symmetric workspaces over NVLink peer memory and the native collective entry points.
+
+One workspace per device group (= the ranks spanned by a set of mesh axes): the same
+allocation on every GPU of the group, mapped into every peer and, where the fabric supports it,
+bound to an NVSwitch multicast object (NVLS). torch's symmetric-memory allocator does the handle
+exchange; the kernels that read and write the peers' memory are ours
+(``csrc/peer_collectives.cu``, and the fused GEMM + all-reduce in ``csrc/gemm_tcgen05.cu``).
+
+``NABLA_B200_COMM=nccl`` disables this path (NCCL baseline); ``NABLA_B200_NVLS=0`` keeps the
+kernels on plain peer loads/stores (used by the failure-detection tests).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+_workspaces: dict = {}
+_lib = None
+_enabled: bool | None = None
+launch_count = 0
+DEFAULT_BYTES = int(os.environ.get("NABLA_B200_SYMM_MB", "640")) * 1024 * 1024
+c_int, c_ll, c_vp, c_uint, c_ull = ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_uint, ctypes.c_ulonglong
+
+
+def _L():
+    global _lib
+    if _lib is None:
+        from ..native import load
+
+        lib = load("libnb_comm.so")
+        lib.nb_comm_flag_bytes.restype = c_int
+        lib.nb_comm_allreduce.restype = c_int
+        lib.nb_comm_allreduce.argtypes = [c_vp, c_vp, c_int, c_int, c_uint, c_ll, c_vp, c_ll, c_int, c_int, c_int, c_int,
+                                          c_vp, c_vp]
+        lib.nb_comm_gather.restype = c_int
+        lib.nb_comm_gather.argtypes = [c_vp, c_int, c_int, c_uint, c_ll, c_vp, c_ll, c_int, c_int, c_int, c_int, c_vp, c_vp]
+        lib.nb_comm_barrier.restype = c_int
+        lib.nb_comm_barrier.argtypes = [c_vp, c_int, c_int, c_uint, c_vp, c_vp]
+        lib.nb_comm_wait_flag.restype = c_int
+        lib.nb_comm_wait_flag.argtypes = [c_vp, c_uint, c_vp, c_ull, c_vp]
+        _lib = lib
+    return _lib
+
+
+class Workspace:
+    """Symmetric buffer of one device group plus its epoch counter."""
+
+    def __init__(self, pg, ranks: list[int], nbytes: int):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.pg, self.ranks = pg, ranks
+        self.world = len(ranks)
+        self.rank = ranks.index(dist.get_rank())
+        self.flag_bytes = _L().nb_comm_flag_bytes()
+        self.nbytes = int(nbytes)
+        self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+        self.buf.zero_()
+        self.hdl = symm_mem.rendezvous(self.buf, group=pg)
+        self.ptrs_dev = int(self.hdl.buffer_ptrs_dev)
+        use_nvls = os.environ.get("NABLA_B200_NVLS", "1") != "0"
+        mc = 0
+        try:
+            mc = int(self.hdl.multicast_ptr) if use_nvls else 0
+        except Exception:
+            mc = 0
+        self.mc_ptr = mc
+        self.epoch = 0
+        self.data = self.buf[self.flag_bytes:]
+        self.data_bytes = self.nbytes - self.flag_bytes
+        torch.cuda.synchronize()
+        dist.barrier(group=pg)
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    def stage(self, x: torch.Tensor, offset: int = 0) -> None:
+        """Copy ``x`` (contiguous) into the data region at byte ``offset``."""
+        n = x.numel() * x.element_size()
+        self.data[offset:offset + n].view(x.dtype).view(x.shape).copy_(x)
+
+
+def is_ready() -> bool:
+    global _enabled
+    if _enabled is None:
+        _enabled = False
+        if (os.environ.get("NABLA_B200_COMM", "native") != "nccl" and dist.is_available() and dist.is_initialized()
+                and torch.cuda.is_available() and dist.get_backend() != "gloo"):
+            try:
+                from ..native import available
+
+                _enabled = available("libnb_comm.so")
+                if _enabled:
+                    _L()
+            except Exception:
+                _enabled = False
+    return _enabled
+
+
+def disable() -> None:
+    global _enabled
+    _enabled = False
+
+
+def workspace(mesh, axes) -> Workspace:
+    key = (id(mesh), tuple(axes))
+    ws = _workspaces.get(key)
+    if ws is None:
+        pg, ranks = mesh.process_group(tuple(axes))
+        ws = Workspace(pg, ranks, DEFAULT_BYTES)
+        _workspaces[key] = ws
+    return ws
+
+
+def supports(buf: torch.Tensor) -> bool:
+    return (buf.is_cuda and buf.dtype in (torch.bfloat16, torch.float32)
+            and buf.numel() * buf.element_size() + 4096 <= DEFAULT_BYTES - 65536)
+
+
+def _status():
+    from ..native import status_word
+
+    return status_word(torch.device("cuda", torch.cuda.current_device()))
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def all_reduce(buf: torch.Tensor, mesh, axes, op: str = "sum", algo: str | None = None) -> torch.Tensor:
+    """Sum (or max/min/prod) over the device group of ``axes`` with peer-memory kernels."""
+    global launch_count
+    ws = workspace(mesh, axes)
+    x = buf.contiguous()
+    n = x.numel()
+    vec = 16 // x.element_size()
+    unit = vec * ws.world
+    n_pad = (n + unit - 1) // unit * unit
+    flat = x.view(-1)
+    region = ws.data[: n_pad * x.element_size()].view(x.dtype)
+    region[:n].copy_(flat)
+    if n_pad != n:
+        region[n:].zero_()
+    out = torch.empty(n_pad, dtype=x.dtype, device=x.device)
+    nbytes = n_pad * x.element_size()
+    opi = {"sum": 0, "max": 1, "min": 2, "prod": 3}[op]
+    if algo is None:
+        algo = os.environ.get("NABLA_B200_AR_ALGO", "auto")
+    if algo == "auto":
+        if nbytes <= 512 * 1024 or opi != 0:
+            algo = "oneshot"
+        else:
+            algo = "multimem" if ws.mc_ptr else "twoshot"
+    if algo == "multimem" and (not ws.mc_ptr or opi != 0):
+        algo = "twoshot" if opi == 0 else "oneshot"
+    ai = {"oneshot": 0, "twoshot": 1, "multimem": 2}[algo]
+    blocks = 8 if nbytes <= 256 * 1024 else (32 if nbytes <= 8 * 1024 * 1024 else 64)
+    rc = _L().nb_comm_allreduce(ws.ptrs_dev, ws.mc_ptr, ws.rank, ws.world, ws.next_epoch(), 0, out.data_ptr(), n_pad,
+                                1 if x.dtype == torch.bfloat16 else 0, ai, opi, blocks, _status().data_ptr(), _stream())
+    if rc != 0:
+        raise RuntimeError(f"nb_comm_allreduce failed with code {rc}")
+    launch_count += 1
+    return out[:n].view(x.shape)
+
+
+def _gather_call(x: torch.Tensor, mesh, axes, mode: int, chunk_elems: int, out_elems: int, root: int = 0) -> torch.Tensor:
+    global launch_count
+    ws = workspace(mesh, axes)
+    flat = x.contiguous().view(-1)
+    ws.data[: flat.numel() * x.element_size()].view(x.dtype).copy_(flat)
+    out = torch.empty(out_elems, dtype=x.dtype, device=x.device)
+    nbytes = out_elems * x.element_size()
+    blocks = 8 if nbytes <= 256 * 1024 else (32 if nbytes <= 8 * 1024 * 1024 else 64)
+    rc = _L().nb_comm_gather(ws.ptrs_dev, ws.rank, ws.world, ws.next_epoch(), 0, out.data_ptr(), chunk_elems,
+                             1 if x.dtype == torch.bfloat16 else 0, mode, root, blocks, _status().data_ptr(), _stream())
+    if rc != 0:
+        raise RuntimeError(f"nb_comm_gather failed with code {rc}")
+    launch_count += 1
+    return out
+
+
+def all_gather_dim0(x: torch.Tensor, mesh, axes) -> torch.Tensor:
+    """Concatenate equal-size shards along dim 0 (numel a multiple of 16 bytes)."""
+    ws = workspace(mesh, axes)
+    out = _gather_call(x, mesh, axes, 0, x.numel(), x.numel() * ws.world)
+    return out.view((x.shape[0] * ws.world,) + tuple(x.shape[1:]))
+
+
+def reduce_scatter_dim0(x: torch.Tensor, mesh, axes) -> torch.Tensor:
+    ws = workspace(mesh, axes)
+    chunk = x.numel() // ws.world
+    out = _gather_call(x, mesh, axes, 1, chunk, chunk)
+    return out.view((x.shape[0] // ws.world,) + tuple(x.shape[1:]))
+
+
+def all_to_all_dim0(x: torch.Tensor, mesh, axes) -> torch.Tensor:
+    ws = workspace(mesh, axes)
+    chunk = x.numel() // ws.world
+    return _gather_call(x, mesh, axes, 2, chunk, x.numel()).view(x.shape)
+
+
+def broadcast(x: torch.Tensor, mesh, axes, root: int = 0) -> torch.Tensor:
+    return _gather_call(x, mesh, axes, 3, x.numel(), x.numel(), root).view(x.shape)
+
+
+def wait_flag_timeout_probe(limit_ms: float = 50.0) -> int:
+    """Launch a bounded wait on a flag nobody sets; returns the status code the kernel reported
+    (NB_ERR_TIMEOUT_PEER = 4). The CUDA context stays usable: this is how lost-peer detection is
+    tested without faulting or hanging a GPU."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    flag = torch.zeros(4, dtype=torch.int32, device=dev)
+    st = torch.zeros(4, dtype=torch.int32, device=dev)
+    rc = _L().nb_comm_wait_flag(flag.data_ptr(), 1, st.data_ptr(), int(limit_ms * 1e6), _stream())
+    if rc != 0:
+        raise RuntimeError("wait_flag launch failed")
+    torch.cuda.synchronize()
+    return int(st[0].item())
