@@ -1,0 +1,131 @@
+"""Worker run under torchrun by tests/test_gpu_multi.py (one rank per GPU, NCCL).
+
+Checks, on every rank: the peer-memory collectives against NCCL results, the sharded transformer
+step against the unsharded one, and (mode 'lost_peer') that a rank which leaves between steps
+is reported to the others as an error. Prints one ``RESULT {json}`` line per rank.
+"""
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+import nabla_b200 as nb
+from nabla_b200.parallel import init_distributed
+
+
+def main():
+    mode = sys.argv[1] if len(sys.argv) > 1 else "collectives"
+    rank, world = init_distributed(timeout_s=20 if mode == "lost_peer" else 120)
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    out = {"rank": rank, "world": world, "mode": mode}
+    if mode == "collectives":
+        from nabla_b200 import native
+        from nabla_b200.parallel import backend, symm
+
+        mesh = nb.DeviceMesh("m", (world,), ("x",))
+        out["symm_ready"] = symm.is_ready()
+        ws = symm.workspace(mesh, ("x",))
+        out["nvls"] = bool(ws.mc_ptr)
+        errs = {}
+        for dtype in (torch.bfloat16, torch.float32):
+            for n in (1000, 4096, 1 << 20, (1 << 22) + 24):
+                torch.manual_seed(100 + rank)
+                x = torch.randn(n, device=dev, dtype=dtype)
+                ref = x.clone().float()
+                dist.all_reduce(ref)
+                algos = ["oneshot", "twoshot"] + (["multimem"] if ws.mc_ptr else [])
+                for algo in algos:
+                    y = symm.all_reduce(x, mesh, ("x",), "sum", algo=algo)
+                    e = ((y.float() - ref).abs().max() / (ref.abs().max() + 1e-6)).item()
+                    errs[f"ar_{algo}_{str(dtype)[6:]}_{n}"] = e
+            xm = torch.randn(4096, device=dev, dtype=dtype)
+            rm = xm.clone()
+            dist.all_reduce(rm, op=dist.ReduceOp.MAX)
+            errs[f"max_{str(dtype)[6:]}"] = (symm.all_reduce(xm, mesh, ("x",), "max").float() - rm.float()).abs().max().item()
+        x = torch.randn(64, 256, device=dev, dtype=torch.bfloat16)
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x)
+        errs["all_gather"] = (symm.all_gather_dim0(x, mesh, ("x",)).float() - torch.cat(parts).float()).abs().max().item()
+        big = torch.randn(64 * world, 256, device=dev, dtype=torch.float32)
+        rs_ref = torch.empty(64, 256, device=dev)
+        dist.reduce_scatter_tensor(rs_ref, big.clone())
+        errs["reduce_scatter"] = (symm.reduce_scatter_dim0(big, mesh, ("x",)) - rs_ref).abs().max().item()
+        a2a_ref = torch.empty_like(big)
+        dist.all_to_all_single(a2a_ref, big.clone())
+        errs["all_to_all"] = (symm.all_to_all_dim0(big, mesh, ("x",)) - a2a_ref).abs().max().item()
+        bc = big.clone()
+        dist.broadcast(bc, src=0)
+        errs["broadcast"] = (symm.broadcast(big, mesh, ("x",), 0) - bc).abs().max().item()
+        torch.cuda.synchronize()
+        native.check_status()
+        out["max_err"] = max(errs.values())
+        out["errs"] = {k: v for k, v in errs.items() if v > 1e-2}
+        out["timeout_probe_status"] = symm.wait_flag_timeout_probe(20.0)
+        # bandwidth of the large all-reduce (device time, max over ranks)
+        x = torch.randn(64 * 1024 * 1024, device=dev, dtype=torch.bfloat16)
+        for name, fn in (("native", lambda: symm.all_reduce(x, mesh, ("x",))), ("nccl", lambda: dist.all_reduce(x.clone()))):
+            for _ in range(3):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(5):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / 5], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            out[f"ar128MB_{name}_ms"] = t.item()
+    elif mode == "transformer":
+        from nabla_b200.models import transformer as TR
+        from nabla_b200.parallel import backend
+
+        cfg = TR.TransformerConfig(n_layers=2, d_model=256, n_heads=2, d_ff=512, vocab=512, max_seq=256)
+        with nb.default_device(nb.Accelerator(dev.index)):
+            nb.seed(0)
+            params = TR.init_params(cfg, device=nb.Accelerator(dev.index))
+            rng = np.random.default_rng(0)
+            tok = nb.constant(rng.integers(0, 512, (4, 256)), device=nb.Accelerator(dev.index))
+            tgt = nb.constant(rng.integers(0, 512, (4, 256)), device=nb.Accelerator(dev.index))
+            l0, g0 = nb.value_and_grad(lambda p: TR.loss_fn(p, tok, tgt, cfg), create_graph=False)(params)
+            tp = 2 if world % 2 == 0 else 1
+            mesh = nb.DeviceMesh("m", (world // tp, tp), ("dp", "tp"))
+            ps = TR.place_params(params, mesh, "tp")
+            toks, tgts = tok.shard(mesh, ("dp", None)), tgt.shard(mesh, ("dp", None))
+            l1, g1 = nb.value_and_grad(lambda p: TR.loss_fn(p, toks, tgts, cfg), create_graph=False)(ps)
+            rel = []
+            for a, b in zip(nb.tree_leaves(g0), nb.tree_leaves(g1)):
+                ta, tb = torch.from_numpy(a.to_numpy()).float(), torch.from_numpy(b.to_numpy()).float()
+                rel.append(((ta - tb).norm() / (ta.norm() + 1e-6)).item())
+            out.update(loss0=l0.item(), loss1=l1.item(), grad_rel_err=max(rel), backend=dict(backend.stats))
+    elif mode == "lost_peer":
+        mesh = nb.DeviceMesh("m", (world,), ("x",))
+        x = nb.Tensor.from_torch(torch.ones(4, 4, device=dev)).shard(mesh, ("x", None))
+        nb.all_reduce(x, reduce_axes={"x"}).realize()
+        torch.cuda.synchronize()
+        if rank == world - 1:
+            print("RESULT " + json.dumps({"rank": rank, "left": True}), flush=True)
+            os._exit(0)                                   # leaves between steps, nothing in flight
+        try:
+            nb.all_reduce(x * 2.0, reduce_axes={"x"}).realize()
+            torch.cuda.synchronize()
+            out["detected"] = False
+        except Exception as e:
+            out["detected"] = True
+            out["error"] = type(e).__name__
+    print("RESULT " + json.dumps(out), flush=True)
+    if mode == "lost_peer":
+        os._exit(0)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
