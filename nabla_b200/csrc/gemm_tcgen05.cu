@@ -71,10 +71,25 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& b,
   n = rr / gsz;
 }
 
-template <int BN>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                         const GemmArgs args) {
+// Fused GEMM + all-reduce: where the tiles go and how ranks tell each other about them.
+struct CommArgs {
+  void* const* bufs;        // device array [world]: peer base pointers of the symmetric workspace
+  char* mc;                 // multicast base of the workspace (nullptr: plain peer loads/stores)
+  long long data_off;       // byte offset of the C matrix inside the workspace
+  int flag_off, done_off;   // byte offsets of the tile flags / done counter inside the workspace
+  int rank, world;
+  unsigned tile_target;     // value a tile flag reaches when every rank has written the tile
+  unsigned done_target;     // value the done counter reaches when every CTA of every rank is through
+  int* ticket;              // device int, zeroed before the launch: next reduce job of this rank
+};
+
+// One CTA's share of the GEMM. `cta` / `nctas` replace blockIdx / gridDim so that the fused
+// kernel can dedicate some CTAs to communication. Returns false if the CTA left early.
+template <int BN, bool FUSED>
+__device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensorMap* tmBp, const GemmArgs& args,
+                                         const CommArgs& comm, const int cta, const int nctas) {
+  const CUtensorMap& tmA = *tmAp;
+  const CUtensorMap& tmB = *tmBp;
   using L = SmemLayout<BN>;
   constexpr int STAGES = L::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -94,7 +109,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     __shared__ int s_abort;
     if (threadIdx.x == 0) s_abort = *reinterpret_cast<volatile int*>(args.status);
     __syncthreads();
-    if (s_abort != 0) return;   // uniform for the whole CTA
+    if (s_abort != 0) return false;   // uniform for the whole CTA
   }
 
   const int num_m = (args.M + BLOCK_M - 1) / BLOCK_M;
@@ -131,7 +146,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = cta; t < num_tiles && ok; t += nctas) {
         int b, tm, tn;
         tile_coords(t, num_m, num_n, b, tm, tn);
         const int m0 = tm * BLOCK_M, n0 = tn * BN;
@@ -177,7 +192,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      for (int t = cta; t < num_tiles && ok; t += nctas, ++it) {
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1)) {
@@ -215,7 +230,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     const int et = threadIdx.x - 128;        // 0..127
     bool ok = true;
     int it = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+    for (int t = cta; t < num_tiles; t += nctas, ++it) {
       int b, tm, tn;
       tile_coords(t, num_m, num_n, b, tm, tn);
       const int m0 = tm * BLOCK_M, n0 = tn * BN;
@@ -376,6 +391,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       }
       tc_fence_before();
       mbar_arrive(&tmem_empty[buf]);
+      if (FUSED) {
+        // the tile is in this rank's workspace: make it visible system-wide, then count it on
+        // the rank that reduces this tile (tile t belongs to rank t % world)
+        __threadfence_system();
+        named_bar_sync(2, EPI_THREADS);
+        if (et == 0)
+          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(reinterpret_cast<char*>(comm.bufs[t % comm.world]) +
+                                                                         comm.flag_off + 4ll * t),
+                       "r"(1u)
+                       : "memory");
+      }
     }
   }
 
@@ -385,6 +411,161 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     tc_fence_after();
     tmem_dealloc(tmem_base, 2 * BN);
   }
+  return true;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const GemmArgs args) {
+  CommArgs none{};
+  gemm_cta<BN, false>(&tmA, &tmB, args, none, blockIdx.x, gridDim.x);
+}
+
+// ------------------------------------------------------------------ fused GEMM + all-reduce
+// CTAs [0, n_gemm) compute tiles of this rank's partial product into the symmetric workspace and
+// raise per-tile flags on all ranks. Every CTA (the dedicated communication CTAs from the start,
+// the GEMM CTAs once they run out of tiles) then takes reduce jobs from a ticket counter: job k of
+// rank r is tile r + k * world. A job waits until all ranks have written the tile, sums the
+// copies (multimem.ld_reduce in the switch, or peer loads) and writes the sum into every rank's
+// workspace (multimem.st, or peer stores). The kernel leaves once every CTA of every rank is
+// through, so the next kernel on the stream finds the reduced matrix in the local workspace.
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool wait_flag_ge(const unsigned* p, unsigned target) {
+  if ((int)(ld_acquire_sys_u32(p) - target) >= 0) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  unsigned spins = 0;
+  while (true) {
+    if ((int)(ld_acquire_sys_u32(p) - target) >= 0) return true;
+    if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
+  }
+}
+
+template <int BN>
+__device__ __forceinline__ void reduce_jobs(const GemmArgs& args, const CommArgs& comm) {
+  __shared__ int s_job;
+  __shared__ int s_ok;
+  const int num_m = (args.M + BLOCK_M - 1) / BLOCK_M;
+  const int num_n = (args.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n * args.batch;
+  char* local = reinterpret_cast<char*>(comm.bufs[comm.rank]);
+  const unsigned* flags = reinterpret_cast<const unsigned*>(local + comm.flag_off);
+  while (true) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int k = atomicAdd(comm.ticket, 1);
+      const int t = comm.rank + k * comm.world;
+      s_job = t;
+      s_ok = 1;
+      if (t < num_tiles) {
+        if (!wait_flag_ge(flags + t, comm.tile_target)) {
+          atomicExch(args.status, NB_ERR_TIMEOUT_PEER);
+          s_ok = 0;
+        } else {
+          // every rank has counted: nobody touches this flag again before the closing
+          // barrier, so it can go back to zero for the next call
+          *const_cast<volatile unsigned*>(flags + t) = 0u;
+        }
+      }
+    }
+    __syncthreads();
+    const int t = s_job;
+    if (t >= num_tiles || !s_ok) break;
+    int b, tm, tn;
+    tile_coords(t, num_m, num_n, b, tm, tn);
+    const int m0 = tm * BLOCK_M, n0 = tn * BN;
+    const int rows = min(BLOCK_M, args.M - m0);
+    const int vpr = (min(BN, args.N - n0) * 2) / 16;       // 16-byte vectors per tile row (N % 8 == 0)
+    const long long base = comm.data_off + ((long long)b * args.stride_c + (long long)m0 * args.ldc + n0) * 2;
+    const int total = rows * vpr;
+    if (comm.mc != nullptr) {
+      for (int i = threadIdx.x; i < total; i += 4 * NUM_THREADS) {
+        uint4 v[4];
+        long long off[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int idx = i + u * NUM_THREADS;
+          off[u] = base + ((long long)(idx / vpr) * args.ldc) * 2 + (idx % vpr) * 16;
+          if (idx < total)
+            asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                         : "l"(comm.mc + off[u])
+                         : "memory");
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (i + u * NUM_THREADS < total)
+            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(comm.mc + off[u]), "r"(v[u].x),
+                         "r"(v[u].y), "r"(v[u].z), "r"(v[u].w)
+                         : "memory");
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < total; idx += NUM_THREADS) {
+        const long long off = base + ((long long)(idx / vpr) * args.ldc) * 2 + (idx % vpr) * 16;
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int p = 0; p < comm.world; ++p) {
+          uint4 v;
+          asm volatile("ld.global.relaxed.sys.v4.u32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                       : "l"(reinterpret_cast<char*>(comm.bufs[p]) + off)
+                       : "memory");
+          const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[2 * j] += __uint_as_float(w[j] << 16);
+            acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+          }
+        }
+        uint4 o;
+        unsigned* ow = reinterpret_cast<unsigned*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+          ow[j] = *reinterpret_cast<unsigned*>(&h);
+        }
+        for (int p = 0; p < comm.world; ++p)
+          *reinterpret_cast<uint4*>(reinterpret_cast<char*>(comm.bufs[p]) + off) = o;
+      }
+    }
+  }
+  // this CTA is through: tell every rank, and let the last CTA wait for everybody
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (comm.mc != nullptr) {
+      asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(comm.mc + comm.done_off), "r"(1u) : "memory");
+    } else {
+      for (int p = 0; p < comm.world; ++p)
+        asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(reinterpret_cast<char*>(comm.bufs[p]) + comm.done_off),
+                     "r"(1u)
+                     : "memory");
+    }
+    if (blockIdx.x == gridDim.x - 1) {
+      if (!wait_flag_ge(reinterpret_cast<const unsigned*>(local + comm.done_off), comm.done_target))
+        atomicExch(args.status, NB_ERR_TIMEOUT_PEER);
+    }
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_allreduce_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                            const GemmArgs args, const CommArgs comm, const int n_gemm) {
+  if ((int)blockIdx.x < n_gemm) {
+    if (!gemm_cta<BN, true>(&tmA, &tmB, args, comm, blockIdx.x, n_gemm)) return;
+  } else {
+    __shared__ int s_abort2;
+    if (threadIdx.x == 0) s_abort2 = *reinterpret_cast<volatile int*>(args.status);
+    __syncthreads();
+    if (s_abort2 != 0) return;
+  }
+  reduce_jobs<BN>(args, comm);
 }
 
 // ------------------------------------------------------------------ host side
@@ -506,4 +687,66 @@ extern "C" int nb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   if (bn == 256) return launch<256>(ta, tb, g, max_ctas, s);
   if (bn == 128) return launch<128>(ta, tb, g, max_ctas, s);
   return launch<64>(ta, tb, g, max_ctas, s);
+}
+
+// Fused row-parallel GEMM + all-reduce over a symmetric workspace.
+//   ws_local      this rank's workspace base pointer;  ws_bufs  device array [world] of all bases
+//   mc            multicast base of the workspace or null;  data_off  byte offset of C (M x N bf16)
+//   call_index    1, 2, 3, ... counts the fused calls on this workspace (flags are monotonic)
+//   ticket        device int used as job counter (zeroed here on `stream`)
+// After the kernel, every rank's workspace holds sum_r A_r @ B_r at data_off.
+extern "C" int nb_gemm_allreduce_bf16(const void* A, const void* B, void* ws_local, void* const* ws_bufs, void* mc,
+                                      long long data_off, int flag_off, int done_off, int M, int N, int K, long long lda,
+                                      long long ldb, int a_mn, int b_mn, int rank, int world, unsigned call_index,
+                                      int n_comm_ctas, int* ticket, int* status, void* stream) {
+  using namespace nb;
+  constexpr int BN = 256;
+  if (M <= 0 || N <= 0 || K <= 0) return -10;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (data_off & 15)) return -11;
+  if ((lda & 7) || (ldb & 7) || (N & 7)) return -12;
+  const int num_m = (M + BLOCK_M - 1) / BLOCK_M, num_n = (N + BN - 1) / BN;
+  const long long tiles = (long long)num_m * num_n;
+  if (tiles > 8192) return -13;   // tile-flag region holds 8192 flags
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  if (n_comm_ctas < 1) n_comm_ctas = 1;
+  if (n_comm_ctas > g_num_sms / 2) n_comm_ctas = g_num_sms / 2;
+  const int grid = g_num_sms;                 // every rank must launch the same grid
+  const int n_gemm = grid - n_comm_ctas;
+  CUtensorMap ta, tb;
+  int r;
+  if (!a_mn) r = make_map(&ta, A, K, M, 1, lda, 0, BLOCK_M);
+  else       r = make_map(&ta, A, M, K, 1, lda, 0, BLOCK_K);
+  if (r) return r;
+  if (!b_mn) r = make_map(&tb, B, K, N, 1, ldb, 0, BN);
+  else       r = make_map(&tb, B, N, K, 1, ldb, 0, BLOCK_K);
+  if (r) return r;
+  GemmArgs g{};
+  g.M = M; g.N = N; g.K = K; g.batch = 1;
+  g.out = reinterpret_cast<char*>(ws_local) + data_off;
+  g.bias = nullptr; g.aux_in = nullptr; g.aux_out = nullptr;
+  g.ldc = N; g.stride_c = (long long)M * N; g.ld_aux = 0; g.stride_aux = 0;
+  g.a_mn = a_mn; g.b_mn = b_mn; g.out_fp32 = 0; g.bias_fp32 = 0;
+  g.epi = EPI_NONE; g.aux = AUX_NONE; g.accumulate = 0; g.gelu_tanh = 0;
+  g.vec_ok = 1; g.alpha = 1.0f; g.status = status;
+  CommArgs c{};
+  c.bufs = ws_bufs; c.mc = reinterpret_cast<char*>(mc); c.data_off = data_off;
+  c.flag_off = flag_off; c.done_off = done_off; c.rank = rank; c.world = world;
+  c.tile_target = (unsigned)world;
+  c.done_target = (unsigned)world * (unsigned)grid * call_index;
+  c.ticket = ticket;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_allreduce_fused_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SmemLayout<BN>::TOTAL) != cudaSuccess)
+      return -2;
+    configured = true;
+  }
+  if (cudaMemsetAsync(ticket, 0, sizeof(int), s) != cudaSuccess) return -4;
+  gemm_allreduce_fused_kernel<BN><<<grid, NUM_THREADS, SmemLayout<BN>::TOTAL, s>>>(ta, tb, g, c, n_gemm);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

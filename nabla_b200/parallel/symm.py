@@ -32,6 +32,8 @@ def _L():
 
         lib = load("libnb_comm.so")
         lib.nb_comm_flag_bytes.restype = c_int
+        lib.nb_comm_tile_flag_offset.restype = c_int
+        lib.nb_comm_done_offset.restype = c_int
         lib.nb_comm_allreduce.restype = c_int
         lib.nb_comm_allreduce.argtypes = [c_vp, c_vp, c_int, c_int, c_uint, c_ll, c_vp, c_ll, c_int, c_int, c_int, c_int,
                                           c_vp, c_vp]
@@ -164,6 +166,71 @@ def all_reduce(buf: torch.Tensor, mesh, axes, op: str = "sum", algo: str | None 
         raise RuntimeError(f"nb_comm_allreduce failed with code {rc}")
     launch_count += 1
     return out[:n].view(x.shape)
+
+
+_gemm_fn = None
+FUSED_COMM_CTAS = int(os.environ.get("NABLA_B200_FUSED_COMM_CTAS", "20"))
+
+
+def _gemm_ar_fn():
+    global _gemm_fn
+    if _gemm_fn is None:
+        from ..native import load
+
+        fn = load("libnb_gemm.so").nb_gemm_allreduce_bf16
+        fn.restype = c_int
+        fn.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_ll, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll, c_int, c_int,
+                       c_int, c_int, c_uint, c_int, c_vp, c_vp, c_vp]
+        _gemm_fn = fn
+    return _gemm_fn
+
+
+def gemm_all_reduce_supported(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """Shapes the fused kernel takes: 2-D bf16 operands, N a multiple of 8, at most 8192 output
+    tiles of 128 x 256, output fitting the workspace."""
+    if not (a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and b.dim() == 2 and a.dim() >= 2):
+        return False
+    m = a.numel() // a.shape[-1]
+    n = b.shape[1]
+    if n % 8 or m == 0 or a.shape[-1] == 0:
+        return False
+    if ((m + 127) // 128) * ((n + 255) // 256) > 8192:
+        return False
+    return m * n * 2 + 4096 <= DEFAULT_BYTES - 65536
+
+
+def gemm_all_reduce(a: torch.Tensor, b: torch.Tensor, mesh, axes) -> torch.Tensor:
+    """``sum over the group of (a_r @ b_r)`` in ONE kernel: the tcgen05 GEMM writes each output
+    tile into the symmetric workspace and counts it on the tile's owner; reduction CTAs of the
+    same launch sum finished tiles through the switch (``multimem.ld_reduce`` + ``multimem.st``)
+    or over plain peer loads/stores while later tiles are still being multiplied.
+
+    Returns a VIEW of the workspace (M x N bf16): consume or copy it before the next collective
+    on this group."""
+    global launch_count
+    from ..native.gemm import _prep
+
+    ws = workspace(mesh, axes)
+    a2 = a.reshape(-1, a.shape[-1])
+    M, K = a2.shape
+    N = b.shape[1]
+    a3, akind, lda, _ = _prep(a2.unsqueeze(0))
+    b3, bkind, ldb, _ = _prep(b.unsqueeze(0))
+    a_mn = 0 if akind == "row" else 1
+    b_mn = 1 if bkind == "row" else 0
+    if not hasattr(ws, "ticket"):
+        ws.ticket = torch.zeros(4, dtype=torch.int32, device=a.device)
+        ws.fused_calls = 0
+    ws.fused_calls += 1
+    lib = _L()
+    rc = _gemm_ar_fn()(a3.data_ptr(), b3.data_ptr(), ws.buf.data_ptr(), ws.ptrs_dev, ws.mc_ptr, ws.flag_bytes,
+                       lib.nb_comm_tile_flag_offset(), lib.nb_comm_done_offset(), M, N, K, lda, ldb, a_mn, b_mn,
+                       ws.rank, ws.world, ws.fused_calls, FUSED_COMM_CTAS, ws.ticket.data_ptr(), _status().data_ptr(),
+                       _stream())
+    if rc != 0:
+        raise RuntimeError(f"nb_gemm_allreduce_bf16 failed with code {rc} for {tuple(a.shape)} @ {tuple(b.shape)}")
+    launch_count += 1
+    return ws.data[: M * N * 2].view(torch.bfloat16).view(M, N)
 
 
 def _gather_call(x: torch.Tensor, mesh, axes, mode: int, chunk_elems: int, out_elems: int, root: int = 0) -> torch.Tensor:

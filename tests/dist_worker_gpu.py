@@ -83,6 +83,57 @@ def main():
             t = torch.tensor([e0.elapsed_time(e1) / 5], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             out[f"ar128MB_{name}_ms"] = t.item()
+    elif mode == "fused_gemm":
+        from nabla_b200 import native
+        from nabla_b200.native.gemm import gemm_bf16
+        from nabla_b200.parallel import symm
+
+        mesh = nb.DeviceMesh("m", (world,), ("x",))
+        ws = symm.workspace(mesh, ("x",))
+        out["nvls"] = bool(ws.mc_ptr)
+        errs = {}
+        shapes = [(256, 512, 256), (1000, 264, 328), (4096, 2048, 1024), (300, 2048, 72)]
+        for (M, N, K) in shapes:
+            for b_t in (False, True):
+                torch.manual_seed(7 + rank)
+                a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+                b = torch.randn(N, K, device=dev, dtype=torch.bfloat16).t() if b_t else \
+                    torch.randn(K, N, device=dev, dtype=torch.bfloat16)
+                ref = a.float() @ b.float()
+                dist.all_reduce(ref)
+                for rep in range(2):          # the flags and counters must be reusable
+                    y = symm.gemm_all_reduce(a, b, mesh, ("x",)).clone()
+                    torch.cuda.synchronize()
+                    errs[f"{M}x{N}x{K}_{int(b_t)}_{rep}"] = ((y.float() - ref).abs().max() / ref.abs().max()).item()
+        native.check_status()
+        out["max_err"] = max(errs.values())
+        out["errs"] = {k: v for k, v in errs.items() if v > 2e-2}
+        # row-parallel projection of the benchmark model: tokens x d_model, K = d_ff / world
+        M, N, K = 16384, 2048, 8192 // world
+        a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        b = torch.randn(K, N, device=dev, dtype=torch.bfloat16)
+
+        def unfused():
+            y = gemm_bf16(a, b)
+            dist.all_reduce(y)
+            return y
+
+        for name, fn in (("fused", lambda: symm.gemm_all_reduce(a, b, mesh, ("x",))), ("gemm_then_nccl", unfused),
+                         ("gemm_only", lambda: gemm_bf16(a, b))):
+            for _ in range(3):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(10):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / 10], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            out[f"{name}_ms"] = t.item()
+        native.check_status()
     elif mode == "transformer":
         from nabla_b200.models import transformer as TR
         from nabla_b200.parallel import backend

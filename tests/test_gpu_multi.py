@@ -23,7 +23,13 @@ def _run(mode, n, env=None, timeout=300):
     e = dict(os.environ)
     e.update(env or {})
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=e)
-    found = [json.loads(m) for m in re.findall(r"RESULT (\{.*?\})\s*$", res.stdout, flags=re.M)]
+    found = []
+    dec = json.JSONDecoder()
+    for m in re.finditer(r"RESULT ", res.stdout):      # ranks may interleave on one line
+        try:
+            found.append(dec.raw_decode(res.stdout[m.end():])[0])
+        except json.JSONDecodeError:
+            pass
     return res, found
 
 
@@ -34,6 +40,15 @@ def test_peer_collectives_match_nccl():
     for r in rs:
         assert r["symm_ready"] and r["max_err"] < 2e-2 and not r["errs"], r
         assert r["timeout_probe_status"] == 4      # the bounded wait reported NB_ERR_TIMEOUT_PEER, context alive
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("nvls", ["1", "0"])
+def test_fused_gemm_all_reduce_matches_nccl(nvls):
+    res, rs = _run("fused_gemm", 2, env={"NABLA_B200_NVLS": nvls})
+    assert len(rs) == 2, res.stdout[-2000:] + res.stderr[-3000:]
+    for r in rs:
+        assert r["max_err"] < 2e-2 and not r["errs"], r
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
