@@ -7,6 +7,12 @@ CUDA bf16 tensors:
   consumer: one tcgen05 GEMM launch with the bias/activation epilogue
   (replaces the composition of nabla/nn/functional/layers.py:30-35).
 
+* ``matmul | linear (no bias) -> all_reduce(sum) | reduce_scatter`` on a mesh that runs one
+  process per GPU: one launch of the fused GEMM + collective kernel (tiles are reduced over
+  NVLink while later tiles are still being multiplied).
+* ``all_gather(rows) -> linear | matmul``: one launch that pulls the peers' rows while the tensor
+  cores already work on the rows that are there; the gathered tensor is still produced.
+
 Every other node is a plain 'op' step. Fusion never changes which tensors exist: fused-away
 intermediates that are still referenced are simply not fusable.
 """
@@ -41,6 +47,11 @@ def build_plan(nodes: list[OpNode], targets: list[TensorImpl]):
     pos = {id(n): i for i, n in enumerate(nodes)}
     used = [False] * len(nodes)
     steps = []
+    producer: dict[int, int] = {}
+    for ni, nd in enumerate(nodes):
+        for o_ in nd.outputs():
+            if o_ is not None:
+                producer[id(o_)] = ni
 
     def sole_output(n: OpNode):
         outs = n.outputs()
@@ -69,16 +80,42 @@ def build_plan(nodes: list[OpNode], targets: list[TensorImpl]):
                         if not used[k] and a.op.name in ("relu", "gelu") and not (
                                 a.op.name == "gelu" and a.kwargs.get("approximate", "none") not in ("none", "tanh")):
                             chain = [i, j, k]
-        if chain is not None and all(c == chain[0] + d for d, c in enumerate(chain)) is False:
-            # the fused step runs at the position of its last node; all inputs of the later
-            # nodes must already be available there, which holds because they precede it
-            pass
+        kind = "linear_epilogue"
+        if chain is None and n.op.name in ("matmul", "linear") and _is_partial_gemm(n):
+            o = sole_output(n)
+            # a traced product may stay an unrealized promise: no backward rule reads its value
+            if o is not None and id(o) not in target_ids and len(cons.get(id(o), [])) == 1 and o.batch_dims == 0:
+                j = cons[id(o)][0]
+                m = nodes[j]
+                if not used[j] and m.op.name == "all_reduce" and _is_sum_over_partials(m, o):
+                    chain = [i, j]
+                    kind = "gemm_all_reduce"
+                elif not used[j] and m.op.name == "reduce_scatter" and _is_scatter_of_partials(m, o):
+                    chain = [i, j]
+                    kind = "gemm_reduce_scatter"
+        if chain is None and n.op.name == "all_gather" and _is_row_gather(n):
+            o = sole_output(n)
+            users = cons.get(id(o), []) if o is not None else []
+            if o is not None and users and o.batch_dims == 0:
+                j = min(users)
+                m = nodes[j]
+                if not used[j] and m.op.name in ("matmul", "linear") and _is_gathered_gemm(m, o):
+                    # the GEMM may move up to right after its other inputs exist, but not past
+                    # another user of the gathered tensor
+                    ready = i
+                    for x in m.input_impls():
+                        if x is not o and id(x) in producer:
+                            ready = max(ready, producer[id(x)])
+                    if ready < j and all(u > ready for u in users):
+                        used[i] = used[j] = True
+                        steps.append((ready + 0.5, ("all_gather_gemm", (i, j))))
+                        continue
         if chain is not None:
             # schedule at the position of the LAST node of the chain
             last = chain[-1]
             for c in chain:
                 used[c] = True
-            steps.append((last, ("linear_epilogue", tuple(chain))))
+            steps.append((last, (kind, tuple(chain))))
         else:
             used[i] = True
             steps.append((i, ("op", (i,))))
@@ -97,6 +134,76 @@ def _is_cuda_bf16_2d(n: OpNode) -> bool:
 
     return (a.device.label == "gpu" and a.dtype is DType.bfloat16 and b.dtype is DType.bfloat16
             and len(b._shape) == 2 and len(a._shape) >= 2)
+
+
+def _is_partial_gemm(n: OpNode) -> bool:
+    """bf16 ``x @ w`` on a one-process-per-GPU mesh whose product is a pending partial sum."""
+    ins = n.input_impls()
+    if len(ins) != 2 or n.kwargs.get("activation") is not None:
+        return False
+    a, b = ins
+    outs = n.outputs()
+    o = outs[0] if len(outs) == 1 else None
+    if o is None or o.sharding is None or not o.sharding.partial_sum_axes or not o.sharding.mesh.is_distributed:
+        return False
+    from ...types import DType
+
+    if not (a.device.label == "gpu" and a.dtype is DType.bfloat16 and b.dtype is DType.bfloat16
+            and len(b._shape) == 2 and len(a._shape) >= 2 and a.batch_dims == 0 and b.batch_dims == 0):
+        return False
+    from ...parallel import symm
+
+    return symm.is_ready()
+
+
+def _is_sum_over_partials(m: OpNode, mm_out: TensorImpl) -> bool:
+    axes = set(m.kwargs.get("reduce_axes", ()))
+    if m.kwargs.get("reduce_op", "sum") != "sum" or not axes:
+        return False
+    sp = mm_out.sharding
+    # a plain sum of the partial products: no dim of the operand is split over the reduced axes
+    return axes <= set(sp.partial_sum_axes) and not any(set(d.axes) & axes for d in sp.dim_specs)
+
+
+def _is_scatter_of_partials(m: OpNode, mm_out: TensorImpl) -> bool:
+    axes = set(m.kwargs.get("scatter_axes", ()))
+    dim = m.kwargs.get("dim")
+    sp = mm_out.sharding
+    if not axes or dim is None or dim >= len(mm_out._shape) - 1:
+        return False
+    return axes <= set(sp.partial_sum_axes) and not any(set(d.axes) & axes for d in sp.dim_specs)
+
+
+def _is_row_gather(n: OpNode) -> bool:
+    ins = n.input_impls()
+    if len(ins) != 1:
+        return False
+    x = ins[0]
+    dim = n.kwargs.get("dim")
+    if x.sharding is None or not x.sharding.mesh.is_distributed or dim is None or dim >= len(x._shape) - 1:
+        return False
+    if not x.sharding.dim_specs[dim].axes or x.sharding.partial_sum_axes or x.batch_dims:
+        return False
+    from ...types import DType
+
+    if not (x.device.label == "gpu" and x.dtype is DType.bfloat16):
+        return False
+    from ...parallel import symm
+
+    return symm.is_ready()
+
+
+def _is_gathered_gemm(m: OpNode, gathered: TensorImpl) -> bool:
+    ins = m.input_impls()
+    if len(ins) < 2 or ins[0] is not gathered or any(x is gathered for x in ins[1:]):
+        return False
+    w = ins[1]
+    from ...types import DType
+
+    if not (w.dtype is DType.bfloat16 and len(w._shape) == 2 and w.batch_dims == 0):
+        return False
+    act = m.kwargs.get("activation")
+    return act in (None, "relu", "gelu", "gelu_tanh")
 
 
 def _is_bias_add(m: OpNode, mm_out: TensorImpl) -> bool:
@@ -135,4 +242,116 @@ def run_fused(kind: str, group: list[OpNode], keep_graph: bool = False) -> None:
         else:
             store_outputs(last, [[out]])
         return
+    if kind == "gemm_all_reduce":
+        from ...parallel import backend, symm
+
+        mm, ar = group
+        a, b = [x._buffers[0] for x in mm.input_impls()]
+        mesh = mm.outputs()[0].sharding.mesh if mm.outputs()[0] is not None else ar.input_impls()[0].sharding.mesh
+        axes = [x for x in mesh.axis_names if x in ar.kwargs["reduce_axes"]]
+        if symm.gemm_all_reduce_supported(a, b):
+            out = symm.gemm_all_reduce(a, b, mesh, axes).clone().reshape(*a.shape[:-1], b.shape[-1])
+            backend.stats["fused_gemm_all_reduce"] = backend.stats.get("fused_gemm_all_reduce", 0) + 1
+        else:
+            y = mm.op.kernel(a, b)
+            out = backend.all_reduce(y, mesh, axes, "sum")
+        if keep_graph:
+            o = ar.outputs()[0]
+            if o is not None:
+                o._buffers = [out]
+        else:
+            store_outputs(ar, [[out]])
+        return
+    if kind == "gemm_reduce_scatter":
+        from ...parallel import backend, symm
+
+        mm, rs = group
+        a, b = [x._buffers[0] for x in mm.input_impls()]
+        mesh = rs.input_impls()[0].sharding.mesh
+        axes = [x for x in mesh.axis_names if x in rs.kwargs["scatter_axes"]]
+        dim = rs.kwargs["dim"]
+        world = 1
+        for x in axes:
+            world *= mesh.get_axis_size(x)
+        lead = tuple(a.shape[:-1])
+        inner = 1
+        for d in lead[dim + 1:]:
+            inner *= d
+        m_total = 1
+        for d in lead:
+            m_total *= d
+        cs = (lead[dim] // world) * inner if lead[dim] % world == 0 else 0
+        if (symm.gemm_all_reduce_supported(a, b) and symm.chunked_supported(m_total, cs, world)
+                and os.environ.get("NABLA_B200_FUSE_RS", "1") != "0"):
+            y = symm.gemm_reduce_scatter(a, b, mesh, axes, cs)
+            out = y.reshape(*lead[:dim], lead[dim] // world, *lead[dim + 1:], b.shape[-1])
+            backend.stats["fused_gemm_reduce_scatter"] = backend.stats.get("fused_gemm_reduce_scatter", 0) + 1
+            _store(rs, [[out]], keep_graph)
+        else:
+            _plain(mm, keep_graph)
+            _plain(rs, keep_graph)
+        return
+    if kind == "all_gather_gemm":
+        from ...parallel import backend, symm
+
+        ag, mm = group
+        x_impl = ag.input_impls()[0]
+        x = x_impl._buffers[0]
+        dim = ag.kwargs["dim"]
+        mesh = x_impl.sharding.mesh
+        axes = list(x_impl.sharding.dim_specs[dim].axes)
+        world = 1
+        for a_ in axes:
+            world *= mesh.get_axis_size(a_)
+        ins = mm.input_impls()
+        w = ins[1]._buffers[0]
+        bias = ins[2]._buffers[0] if len(ins) > 2 else None
+        act = mm.kwargs.get("activation")
+        lead = tuple(x.shape[:-1])
+        cs = 1
+        for d in lead[dim:]:
+            cs *= d
+        m_total = world * x.numel() // max(x.shape[-1], 1)
+        k, n = x.shape[-1], w.shape[-1]
+        even = all(s == x.shape[dim] for s in
+                   [_local_extent(x_impl, dim, r) for r in mesh.group_of(mesh.rank, axes)])
+        if (even and symm.chunked_supported(m_total, cs, world) and n % 8 == 0 and k % 8 == 0 and w.dim() == 2
+                and m_total // world * k * 2 + 4096 <= symm.DEFAULT_BYTES - 65536
+                and os.environ.get("NABLA_B200_FUSE_AG", "1") != "0"):
+            epi = "none" if act is None else ("relu" if act == "relu" else "gelu")
+            res = symm.all_gather_gemm(x, w, mesh, axes, cs, bias=bias, epilogue=epi, gelu_tanh=act == "gelu_tanh",
+                                       store_preact=act is not None)
+            full_shape = (*lead[:dim], lead[dim] * world, *lead[dim + 1:])
+            _store(ag, [[res[0].reshape(*full_shape, k)]], keep_graph)
+            outs = [[res[1].reshape(*full_shape, n)]]
+            if act is not None:
+                outs.append([res[2].reshape(*full_shape, n)])
+            _store(mm, outs, keep_graph)
+            backend.stats["fused_all_gather_gemm"] = backend.stats.get("fused_all_gather_gemm", 0) + 1
+        else:
+            _plain(ag, keep_graph)
+            _plain(mm, keep_graph)
+        return
     raise ValueError(f"unknown fused step {kind}")
+
+
+def _local_extent(impl: TensorImpl, dim: int, device_id: int) -> int:
+    from ..sharding.spec import compute_local_shape
+
+    return compute_local_shape(impl._shape, impl.sharding, device_id)[dim]
+
+
+def _store(node: OpNode, outs, keep_graph: bool) -> None:
+    from .engine import store_outputs
+
+    if keep_graph:
+        for i, ref in enumerate(node.out_refs):
+            o = ref()
+            if o is not None:
+                o._buffers = outs[i]
+    else:
+        store_outputs(node, outs)
+
+
+def _plain(node: OpNode, keep_graph: bool) -> None:
+    _store(node, node.op.execute(node), keep_graph)

@@ -71,21 +71,64 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& b,
   n = rr / gsz;
 }
 
-// Fused GEMM + all-reduce: where the tiles go and how ranks tell each other about them.
+// Fused GEMM + collective: what the launch does besides the GEMM.
+//   MODE_AR  C = sum_r A_r @ B_r on every rank        (tiles -> workspace, reduced in place)
+//   MODE_RS  rank r keeps its row chunks of that sum   (tiles -> workspace, reduced into rs_out)
+//   MODE_AG  C = epilogue(gather_r(A_r) @ B)           (peers' row chunks of A are pulled into
+//            a_full by copy CTAs of the same launch; GEMM tiles wait for their rows only)
+// Row chunks: the gathered / scattered matrix has M = G * world * chunk_rows rows; rows
+// [(g * world + p) * chunk_rows, +chunk_rows) belong to rank p (chunk_rows a multiple of 128).
+enum FusedMode : int { MODE_NONE = 0, MODE_AR = 1, MODE_RS = 2, MODE_AG = 3 };
+
+constexpr int AG_FLAG_BASE = 8192;   // index of the first per-M-tile "rows are here" flag
+constexpr int READY_OFF = 64;        // byte offset, after the done counter, of the per-rank ready flags
+
 struct CommArgs {
   void* const* bufs;        // device array [world]: peer base pointers of the symmetric workspace
   char* mc;                 // multicast base of the workspace (nullptr: plain peer loads/stores)
-  long long data_off;       // byte offset of the C matrix inside the workspace
+  long long data_off;       // byte offset inside the workspace of C (AR/RS) or of the staged A shard (AG)
   int flag_off, done_off;   // byte offsets of the tile flags / done counter inside the workspace
   int rank, world;
   unsigned tile_target;     // value a tile flag reaches when every rank has written the tile
-  unsigned done_target;     // value the done counter reaches when every CTA of every rank is through
+  unsigned done_target;     // value the done counter reaches when every participant of every rank is through
   int* ticket;              // device int, zeroed before the launch: next reduce job of this rank
+  int mpc;                  // M tiles per row chunk (chunk_rows / 128); RS and AG
+  int per;                  // M tiles per rank (num_m / world); AG
+  unsigned epoch;           // AG: value of the ready / row flags of this call
+  __nv_bfloat16* rs_out;    // RS: this rank's rows of the sum, [M / world][N]
+  char* a_full;             // AG: the gathered A, [M][K] dense
+  long long unit_bytes;     // AG: bytes of one 128-row block of A
 };
+
+// Order in which the GEMM walks the M tiles -> the tile's real row block.
+//   RS: consecutive tiles rotate over the owning ranks, so that every rank's reducers get work
+//       from the start;  AG: own rows first, then the peers' in ring order (the copy order).
+template <int MODE>
+__device__ __forceinline__ int remap_m(int tm, const CommArgs& c) {
+  if (MODE == MODE_RS) {
+    const int q = tm / c.world, p = tm - q * c.world;
+    const int g = q / c.mpc, j = q - g * c.mpc;
+    return (g * c.world + p) * c.mpc + j;
+  }
+  if (MODE == MODE_AG) {
+    const int dist = tm / c.per, rem = tm - dist * c.per;
+    const int g = rem / c.mpc, j = rem - g * c.mpc;
+    int p = c.rank + dist;
+    if (p >= c.world) p -= c.world;
+    return (g * c.world + p) * c.mpc + j;
+  }
+  return tm;
+}
+
+__device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 
 // One CTA's share of the GEMM. `cta` / `nctas` replace blockIdx / gridDim so that the fused
 // kernel can dedicate some CTAs to communication. Returns false if the CTA left early.
-template <int BN, bool FUSED>
+template <int BN, int MODE>
 __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensorMap* tmBp, const GemmArgs& args,
                                          const CommArgs& comm, const int cta, const int nctas) {
   const CUtensorMap& tmA = *tmAp;
@@ -149,7 +192,24 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
       for (int t = cta; t < num_tiles && ok; t += nctas) {
         int b, tm, tn;
         tile_coords(t, num_m, num_n, b, tm, tn);
+        tm = remap_m<MODE>(tm, comm);
         const int m0 = tm * BLOCK_M, n0 = tn * BN;
+        if (MODE == MODE_AG) {
+          // rows m0 .. m0+127 of the gathered A must have been copied in by a copy CTA
+          const unsigned* f = reinterpret_cast<const unsigned*>(reinterpret_cast<char*>(comm.bufs[comm.rank]) +
+                                                                comm.flag_off) + AG_FLAG_BASE + tm;
+          const unsigned long long t0 = globaltimer_ns();
+          unsigned spins = 0;
+          while ((int)(ld_acquire_gpu_u32(f) - comm.epoch) < 0) {
+            if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+              ok = false;
+              atomicExch(args.status, NB_ERR_TIMEOUT_PEER);
+              break;
+            }
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");   // the rows were written by bulk copies
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
             ok = false;
@@ -233,6 +293,8 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
     for (int t = cta; t < num_tiles; t += nctas, ++it) {
       int b, tm, tn;
       tile_coords(t, num_m, num_n, b, tm, tn);
+      const int tm_order = tm;
+      tm = remap_m<MODE>(tm, comm);
       const int m0 = tm * BLOCK_M, n0 = tn * BN;
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -391,14 +453,15 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
       }
       tc_fence_before();
       mbar_arrive(&tmem_empty[buf]);
-      if (FUSED) {
+      if (MODE == MODE_AR || MODE == MODE_RS) {
         // the tile is in this rank's workspace: make it visible system-wide, then count it on
-        // the rank that reduces this tile (tile t belongs to rank t % world)
+        // the rank that reduces it (tile (tm_order, tn) belongs to rank tm_order % world)
         __threadfence_system();
         named_bar_sync(2, EPI_THREADS);
         if (et == 0)
-          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(reinterpret_cast<char*>(comm.bufs[t % comm.world]) +
-                                                                         comm.flag_off + 4ll * t),
+          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(
+                           reinterpret_cast<char*>(comm.bufs[tm_order % comm.world]) + comm.flag_off +
+                           4ll * (tm_order * num_n + tn)),
                        "r"(1u)
                        : "memory");
       }
@@ -419,7 +482,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const GemmArgs args) {
   CommArgs none{};
-  gemm_cta<BN, false>(&tmA, &tmB, args, none, blockIdx.x, gridDim.x);
+  gemm_cta<BN, MODE_NONE>(&tmA, &tmB, args, none, blockIdx.x, gridDim.x);
 }
 
 // ------------------------------------------------------------------ fused GEMM + all-reduce
@@ -445,96 +508,145 @@ __device__ __forceinline__ bool wait_flag_ge(const unsigned* p, unsigned target)
   }
 }
 
-template <int BN>
+constexpr int RED_UNROLL = 16;
+
+// Reduce jobs of MODE_AR / MODE_RS. Job k of this rank is tile (tm_order = (k / num_n) * world +
+// rank, tn = k % num_n): wait until every rank has counted it, then sum the ranks' copies.
+//   AR: multimem.ld_reduce + multimem.st in place on every rank (or peer loads + peer stores)
+//   RS: multimem.ld_reduce (or peer loads) + a plain store into this rank's rs_out
+template <int BN, int MODE>
 __device__ __forceinline__ void reduce_jobs(const GemmArgs& args, const CommArgs& comm) {
   __shared__ int s_job;
   __shared__ int s_ok;
   const int num_m = (args.M + BLOCK_M - 1) / BLOCK_M;
   const int num_n = (args.N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n * args.batch;
   char* local = reinterpret_cast<char*>(comm.bufs[comm.rank]);
   const unsigned* flags = reinterpret_cast<const unsigned*>(local + comm.flag_off);
   while (true) {
     __syncthreads();
     if (threadIdx.x == 0) {
       const int k = atomicAdd(comm.ticket, 1);
-      const int t = comm.rank + k * comm.world;
-      s_job = t;
+      const int tmo = (k / num_n) * comm.world + comm.rank;
+      s_job = k;
       s_ok = 1;
-      if (t < num_tiles) {
-        if (!wait_flag_ge(flags + t, comm.tile_target)) {
+      if (tmo < num_m) {
+        const unsigned* f = flags + tmo * num_n + (k % num_n);
+        if (!wait_flag_ge(f, comm.tile_target)) {
           atomicExch(args.status, NB_ERR_TIMEOUT_PEER);
           s_ok = 0;
         } else {
           // every rank has counted: nobody touches this flag again before the closing
           // barrier, so it can go back to zero for the next call
-          *const_cast<volatile unsigned*>(flags + t) = 0u;
+          *const_cast<volatile unsigned*>(f) = 0u;
         }
       }
     }
     __syncthreads();
-    const int t = s_job;
-    if (t >= num_tiles || !s_ok) break;
-    int b, tm, tn;
-    tile_coords(t, num_m, num_n, b, tm, tn);
+    const int k = s_job;
+    const int q = k / num_n, tn = k - q * num_n;
+    const int tmo = q * comm.world + comm.rank;
+    if (tmo >= num_m || !s_ok) break;
+    const int tm = remap_m<MODE>(tmo, comm);
     const int m0 = tm * BLOCK_M, n0 = tn * BN;
     const int rows = min(BLOCK_M, args.M - m0);
     const int vpr = (min(BN, args.N - n0) * 2) / 16;       // 16-byte vectors per tile row (N % 8 == 0)
-    const long long base = comm.data_off + ((long long)b * args.stride_c + (long long)m0 * args.ldc + n0) * 2;
+    const long long base = comm.data_off + ((long long)m0 * args.ldc + n0) * 2;
+    // RS: the tile's rows in this rank's output (its row blocks are numbered q = 0, 1, ...)
+    char* rs_base = reinterpret_cast<char*>(comm.rs_out) + ((long long)q * BLOCK_M * args.N + n0) * 2;
     const int total = rows * vpr;
     if (comm.mc != nullptr) {
-      for (int i = threadIdx.x; i < total; i += 4 * NUM_THREADS) {
-        uint4 v[4];
-        long long off[4];
+      // RED_UNROLL 16-byte vectors in flight per thread: one 128 x 256 tile is a single round
+      // trip through the switch for a 256-thread CTA
+      for (int i = threadIdx.x; i < total; i += RED_UNROLL * NUM_THREADS) {
+        uint4 v[RED_UNROLL];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < RED_UNROLL; ++u) {
           const int idx = i + u * NUM_THREADS;
-          off[u] = base + ((long long)(idx / vpr) * args.ldc) * 2 + (idx % vpr) * 16;
-          if (idx < total)
+          if (idx < total) {
+            const long long off = base + ((long long)(idx / vpr) * args.ldc) * 2 + (idx % vpr) * 16;
             asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
                          : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
-                         : "l"(comm.mc + off[u])
+                         : "l"(comm.mc + off)
                          : "memory");
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-          if (i + u * NUM_THREADS < total)
-            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(comm.mc + off[u]), "r"(v[u].x),
-                         "r"(v[u].y), "r"(v[u].z), "r"(v[u].w)
-                         : "memory");
-      }
-    } else {
-      for (int idx = threadIdx.x; idx < total; idx += NUM_THREADS) {
-        const long long off = base + ((long long)(idx / vpr) * args.ldc) * 2 + (idx % vpr) * 16;
-        float acc[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        for (int p = 0; p < comm.world; ++p) {
-          uint4 v;
-          asm volatile("ld.global.relaxed.sys.v4.u32 {%0,%1,%2,%3}, [%4];"
-                       : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                       : "l"(reinterpret_cast<char*>(comm.bufs[p]) + off)
-                       : "memory");
-          const unsigned w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            acc[2 * j] += __uint_as_float(w[j] << 16);
-            acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
           }
         }
-        uint4 o;
-        unsigned* ow = reinterpret_cast<unsigned*>(&o);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-          ow[j] = *reinterpret_cast<unsigned*>(&h);
+        for (int u = 0; u < RED_UNROLL; ++u) {
+          const int idx = i + u * NUM_THREADS;
+          if (idx < total) {
+            if (MODE == MODE_RS) {
+              *reinterpret_cast<uint4*>(rs_base + ((long long)(idx / vpr) * args.N) * 2 + (idx % vpr) * 16) = v[u];
+            } else {
+              const long long off = base + ((long long)(idx / vpr) * args.ldc) * 2 + (idx % vpr) * 16;
+              asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(comm.mc + off),
+                           "r"(v[u].x), "r"(v[u].y), "r"(v[u].z), "r"(v[u].w)
+                           : "memory");
+            }
+          }
         }
-        for (int p = 0; p < comm.world; ++p)
-          *reinterpret_cast<uint4*>(reinterpret_cast<char*>(comm.bufs[p]) + off) = o;
+      }
+    } else {
+      constexpr int PU = 8;   // vectors in flight per thread and peer
+      for (int i = threadIdx.x; i < total; i += PU * NUM_THREADS) {
+        float acc[PU][8];
+#pragma unroll
+        for (int u = 0; u < PU; ++u)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+        for (int p = 0; p < comm.world; ++p) {
+          const char* src = reinterpret_cast<const char*>(comm.bufs[p]);
+          uint4 v[PU];
+#pragma unroll
+          for (int u = 0; u < PU; ++u) {
+            const int idx = i + u * NUM_THREADS;
+            v[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (idx < total) {
+              const long long off = base + ((long long)(idx / vpr) * args.ldc) * 2 + (idx % vpr) * 16;
+              asm volatile("ld.global.relaxed.sys.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                           : "l"(src + off)
+                           : "memory");
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < PU; ++u) {
+            const unsigned w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              acc[u][2 * j] += __uint_as_float(w[j] << 16);
+              acc[u][2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < PU; ++u) {
+          const int idx = i + u * NUM_THREADS;
+          if (idx < total) {
+            uint4 o;
+            unsigned* ow = reinterpret_cast<unsigned*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(acc[u][2 * j], acc[u][2 * j + 1]);
+              ow[j] = *reinterpret_cast<unsigned*>(&h);
+            }
+            if (MODE == MODE_RS) {
+              *reinterpret_cast<uint4*>(rs_base + ((long long)(idx / vpr) * args.N) * 2 + (idx % vpr) * 16) = o;
+            } else {
+              const long long off = base + ((long long)(idx / vpr) * args.ldc) * 2 + (idx % vpr) * 16;
+              for (int p = 0; p < comm.world; ++p)
+                *reinterpret_cast<uint4*>(reinterpret_cast<char*>(comm.bufs[p]) + off) = o;
+            }
+          }
+        }
       }
     }
   }
-  // this CTA is through: tell every rank, and let the last CTA wait for everybody
+}
+
+// Closing step of a fused launch: count this CTA on every rank; the last CTA of the grid waits
+// until every participant of every rank is through, so no rank's workspace is reused (or its
+// kernel gone) while a peer still reads or writes it.
+__device__ __forceinline__ void closing_count(const GemmArgs& args, const CommArgs& comm) {
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -547,25 +659,132 @@ __device__ __forceinline__ void reduce_jobs(const GemmArgs& args, const CommArgs
                      : "memory");
     }
     if (blockIdx.x == gridDim.x - 1) {
+      const char* local = reinterpret_cast<const char*>(comm.bufs[comm.rank]);
       if (!wait_flag_ge(reinterpret_cast<const unsigned*>(local + comm.done_off), comm.done_target))
         atomicExch(args.status, NB_ERR_TIMEOUT_PEER);
     }
   }
 }
 
+// ---- MODE_AG copy CTAs -----------------------------------------------------------------------
+// One thread per copy CTA drives a ring of bulk copies: peer (or own) staged rows -> shared
+// memory -> a_full. No multicast; every byte crosses NVLink once. After the last piece of a
+// 128-row block has landed, the block's flag is raised for the GEMM producers of this GPU.
+constexpr int AG_PIECE = 32 * 1024;
+constexpr int AG_STAGES = 6;      // 192 KB of the GEMM's shared-memory ring
+
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+
 template <int BN>
+__device__ __forceinline__ void gather_jobs(const GemmArgs& args, const CommArgs& comm, int cidx, int ncomm) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  static_assert(AG_PIECE * AG_STAGES <= SmemLayout<BN>::RING_BYTES, "copy ring must fit the GEMM ring");
+  __shared__ uint64_t bars[AG_STAGES];
+  if (threadIdx.x != 0) return;
+  char* local = reinterpret_cast<char*>(comm.bufs[comm.rank]);
+  const int num_m = (args.M + BLOCK_M - 1) / BLOCK_M;
+  // tell every peer that this rank's rows are staged (the staging copy ran before this kernel)
+  if (cidx == 0) {
+    for (int p = 0; p < comm.world; ++p)
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<char*>(comm.bufs[p]) + comm.done_off +
+                                                                READY_OFF + 4 * comm.rank),
+                   "r"(comm.epoch)
+                   : "memory");
+  }
+  for (int s = 0; s < AG_STAGES; ++s) mbar_init(&bars[s], 1);
+  fence_mbar_init();
+  fence_proxy_async_smem();
+  const int ppu = (int)((comm.unit_bytes + AG_PIECE - 1) / AG_PIECE);   // pieces per 128-row block
+  int n_units = 0;
+  for (int u = cidx; u < num_m; u += ncomm) ++n_units;
+  const int total = n_units * ppu;
+  unsigned ready_mask = 0;
+  bool ok = true;
+  // piece i -> (unit, piece in unit) -> source / destination
+  auto issue_load = [&](int i) -> bool {
+    const int ui = i / ppu, pi = i - ui * ppu;
+    const int tm = remap_m<MODE_AG>(cidx + ui * ncomm, comm);
+    const int blk = tm / comm.mpc;                     // row chunk index in the gathered matrix
+    const int p = blk % comm.world, g = blk / comm.world, j = tm - blk * comm.mpc;
+    if (!((ready_mask >> p) & 1u)) {
+      if (!wait_flag_ge(reinterpret_cast<const unsigned*>(local + comm.done_off + READY_OFF + 4 * p), comm.epoch))
+        return false;
+      ready_mask |= 1u << p;
+    }
+    const long long off = (long long)pi * AG_PIECE;
+    const uint32_t bytes = (uint32_t)min((long long)AG_PIECE, comm.unit_bytes - off);
+    const char* src = reinterpret_cast<const char*>(comm.bufs[p]) + comm.data_off +
+                      (long long)(g * comm.mpc + j) * comm.unit_bytes + off;
+    const int st = i % AG_STAGES;
+    mbar_arrive_expect_tx(&bars[st], bytes);
+    bulk_g2s(ring + st * AG_PIECE, src, bytes, &bars[st]);
+    return true;
+  };
+  int issued = 0;
+  for (; issued < total && issued < AG_STAGES && ok; ++issued) ok = issue_load(issued);
+  for (int i = 0; i < total && ok; ++i) {
+    const int st = i % AG_STAGES;
+    const uint32_t phase = (i / AG_STAGES) & 1;
+    if (!mbar_wait(&bars[st], phase)) { ok = false; break; }
+    const int ui = i / ppu, pi = i - ui * ppu;
+    const int tm = remap_m<MODE_AG>(cidx + ui * ncomm, comm);
+    const long long off = (long long)pi * AG_PIECE;
+    const uint32_t bytes = (uint32_t)min((long long)AG_PIECE, comm.unit_bytes - off);
+    bulk_s2g(comm.a_full + (long long)tm * comm.unit_bytes + off, ring + st * AG_PIECE, bytes);
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    if (pi == ppu - 1) {
+      // the block is complete once its stores have landed: publish it to the GEMM producers
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      asm volatile("fence.proxy.async;" ::: "memory");
+      __threadfence();
+      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(reinterpret_cast<unsigned*>(local + comm.flag_off) +
+                                                                AG_FLAG_BASE + tm),
+                   "r"(comm.epoch)
+                   : "memory");
+    }
+    if (issued < total) {
+      // the stage that piece `issued` will use was read by store i - (AG_STAGES - 1) ... wait
+      // until all stores issued so far have finished READING shared memory, then refill
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      ok = issue_load(issued);
+      ++issued;
+    }
+  }
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  if (!ok) atomicExch(args.status, NB_ERR_TIMEOUT_PEER);
+}
+
+template <int BN, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_allreduce_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                            const GemmArgs args, const CommArgs comm, const int n_gemm) {
-  if ((int)blockIdx.x < n_gemm) {
-    if (!gemm_cta<BN, true>(&tmA, &tmB, args, comm, blockIdx.x, n_gemm)) return;
+gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const GemmArgs args, const CommArgs comm, const int n_gemm) {
+  const bool is_gemm = (int)blockIdx.x < n_gemm;
+  if (is_gemm) {
+    if (!gemm_cta<BN, MODE>(&tmA, &tmB, args, comm, blockIdx.x, n_gemm)) return;
   } else {
     __shared__ int s_abort2;
     if (threadIdx.x == 0) s_abort2 = *reinterpret_cast<volatile int*>(args.status);
     __syncthreads();
     if (s_abort2 != 0) return;
   }
-  reduce_jobs<BN>(args, comm);
+  if (MODE == MODE_AG) {
+    if (is_gemm) return;                      // GEMM CTAs touch no peer memory
+    gather_jobs<BN>(args, comm, (int)blockIdx.x - n_gemm, (int)gridDim.x - n_gemm);
+  } else {
+    reduce_jobs<BN, MODE>(args, comm);
+  }
+  closing_count(args, comm);
 }
 
 // ------------------------------------------------------------------ host side
@@ -689,64 +908,107 @@ extern "C" int nb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   return launch<64>(ta, tb, g, max_ctas, s);
 }
 
-// Fused row-parallel GEMM + all-reduce over a symmetric workspace.
-//   ws_local      this rank's workspace base pointer;  ws_bufs  device array [world] of all bases
-//   mc            multicast base of the workspace or null;  data_off  byte offset of C (M x N bf16)
-//   call_index    1, 2, 3, ... counts the fused calls on this workspace (flags are monotonic)
+// Fused GEMM + collective over a symmetric workspace (one launch; see FusedMode).
+//   mode          1 all-reduce, 2 reduce-scatter, 3 all-gather
+//   ws_local      this rank's workspace base;  ws_bufs  device array [world] of all ranks' bases
+//   mc            multicast base of the workspace or null (plain peer loads/stores)
+//   data_off      byte offset in the workspace of C (modes 1, 2) or of the staged A shard (mode 3)
+//   out           mode 2: this rank's rows [M/world][N];  mode 3: C [M][N] (ldc = N);  mode 1: unused
+//   a_full        mode 3: the gathered A [M][K] (dense, regular device memory); A is then ignored
+//   chunk_rows    modes 2, 3: rows per contiguous chunk of a rank (multiple of 128, M % (world*chunk_rows) == 0)
+//   epoch         mode 3: 1, 2, 3, ... per all-gather call on this workspace
+//   done_target   absolute value of the workspace's done counter after this call
+//                 (previous + world * participants; participants = grid for modes 1, 2, n_comm for 3)
 //   ticket        device int used as job counter (zeroed here on `stream`)
-// After the kernel, every rank's workspace holds sum_r A_r @ B_r at data_off.
-extern "C" int nb_gemm_allreduce_bf16(const void* A, const void* B, void* ws_local, void* const* ws_bufs, void* mc,
-                                      long long data_off, int flag_off, int done_off, int M, int N, int K, long long lda,
-                                      long long ldb, int a_mn, int b_mn, int rank, int world, unsigned call_index,
-                                      int n_comm_ctas, int* ticket, int* status, void* stream) {
-  using namespace nb;
-  constexpr int BN = 256;
-  if (M <= 0 || N <= 0 || K <= 0) return -10;
-  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (data_off & 15)) return -11;
-  if ((lda & 7) || (ldb & 7) || (N & 7)) return -12;
-  const int num_m = (M + BLOCK_M - 1) / BLOCK_M, num_n = (N + BN - 1) / BN;
-  const long long tiles = (long long)num_m * num_n;
-  if (tiles > 8192) return -13;   // tile-flag region holds 8192 flags
-  if (g_num_sms == 0) {
+// Returns 0, or a negative code when the shape does not fit (the caller then runs the unfused path).
+extern "C" int nb_gemm_fused_grid() {
+  if (nb::g_num_sms == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&nb::g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
+  return nb::g_num_sms;
+}
+
+template <int MODE>
+static int launch_fused(const CUtensorMap& ta, const CUtensorMap& tb, const nb::GemmArgs& g, const nb::CommArgs& c,
+                        int grid, int n_gemm, cudaStream_t s) {
+  using namespace nb;
+  constexpr int BN = 256;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_fused_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SmemLayout<BN>::TOTAL) != cudaSuccess)
+      return -2;
+    configured = true;
+  }
+  gemm_fused_kernel<BN, MODE><<<grid, NUM_THREADS, SmemLayout<BN>::TOTAL, s>>>(ta, tb, g, c, n_gemm);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* out, const void* bias, void* aux_out,
+                                  void* a_full, void* ws_local, void* const* ws_bufs, void* mc, long long data_off,
+                                  int flag_off, int done_off, int M, int N, int K, long long lda, long long ldb,
+                                  int a_mn, int b_mn, int bias_fp32, int epi, int aux, int gelu_tanh, int rank,
+                                  int world, int chunk_rows, unsigned epoch, unsigned done_target, int n_comm_ctas,
+                                  int* ticket, int* status, void* stream) {
+  using namespace nb;
+  constexpr int BN = 256;
+  if (mode < MODE_AR || mode > MODE_AG) return -9;
+  if (M <= 0 || N <= 0 || K <= 0) return -10;
+  const void* Aop = mode == MODE_AG ? a_full : A;
+  if ((reinterpret_cast<uintptr_t>(Aop) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (data_off & 15)) return -11;
+  if (mode == MODE_AG) { lda = K; a_mn = 0; }
+  if ((lda & 7) || (ldb & 7) || (N & 7) || (K & 7)) return -12;
+  const int num_m = (M + BLOCK_M - 1) / BLOCK_M, num_n = (N + BN - 1) / BN;
+  if (mode != MODE_AG && (long long)num_m * num_n > AG_FLAG_BASE) return -13;   // tile-flag region
+  if (mode == MODE_AG && num_m > 2048) return -13;
+  int mpc = 1, per = num_m;
+  if (mode != MODE_AR) {
+    if (chunk_rows <= 0 || (chunk_rows % BLOCK_M) || (M % (world * chunk_rows))) return -14;
+    mpc = chunk_rows / BLOCK_M;
+    per = num_m / world;
+  }
+  const int grid = nb_gemm_fused_grid();      // every rank must launch the same grid
   if (n_comm_ctas < 1) n_comm_ctas = 1;
-  if (n_comm_ctas > g_num_sms / 2) n_comm_ctas = g_num_sms / 2;
-  const int grid = g_num_sms;                 // every rank must launch the same grid
+  if (n_comm_ctas > grid / 2) n_comm_ctas = grid / 2;
   const int n_gemm = grid - n_comm_ctas;
   CUtensorMap ta, tb;
   int r;
-  if (!a_mn) r = make_map(&ta, A, K, M, 1, lda, 0, BLOCK_M);
-  else       r = make_map(&ta, A, M, K, 1, lda, 0, BLOCK_K);
+  if (!a_mn) r = make_map(&ta, Aop, K, M, 1, lda, 0, BLOCK_M);
+  else       r = make_map(&ta, Aop, M, K, 1, lda, 0, BLOCK_K);
   if (r) return r;
   if (!b_mn) r = make_map(&tb, B, K, N, 1, ldb, 0, BN);
   else       r = make_map(&tb, B, N, K, 1, ldb, 0, BLOCK_K);
   if (r) return r;
   GemmArgs g{};
   g.M = M; g.N = N; g.K = K; g.batch = 1;
-  g.out = reinterpret_cast<char*>(ws_local) + data_off;
-  g.bias = nullptr; g.aux_in = nullptr; g.aux_out = nullptr;
-  g.ldc = N; g.stride_c = (long long)M * N; g.ld_aux = 0; g.stride_aux = 0;
-  g.a_mn = a_mn; g.b_mn = b_mn; g.out_fp32 = 0; g.bias_fp32 = 0;
-  g.epi = EPI_NONE; g.aux = AUX_NONE; g.accumulate = 0; g.gelu_tanh = 0;
-  g.vec_ok = 1; g.alpha = 1.0f; g.status = status;
+  g.ldc = N; g.stride_c = (long long)M * N;
+  g.a_mn = a_mn; g.b_mn = b_mn; g.out_fp32 = 0; g.accumulate = 0;
+  g.alpha = 1.0f; g.status = status; g.vec_ok = 1;
+  if (mode == MODE_AG) {
+    if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(aux_out) & 15)) return -11;
+    g.out = out; g.bias = bias; g.bias_fp32 = bias_fp32; g.epi = epi; g.gelu_tanh = gelu_tanh;
+    g.aux = aux == AUX_STORE_PREACT ? AUX_STORE_PREACT : AUX_NONE;
+    g.aux_out = reinterpret_cast<__nv_bfloat16*>(aux_out);
+    g.ld_aux = N; g.stride_aux = (long long)M * N;
+  } else {
+    g.out = reinterpret_cast<char*>(ws_local) + data_off;
+    g.epi = EPI_NONE; g.aux = AUX_NONE;
+  }
   CommArgs c{};
   c.bufs = ws_bufs; c.mc = reinterpret_cast<char*>(mc); c.data_off = data_off;
   c.flag_off = flag_off; c.done_off = done_off; c.rank = rank; c.world = world;
   c.tile_target = (unsigned)world;
-  c.done_target = (unsigned)world * (unsigned)grid * call_index;
+  c.done_target = done_target;
   c.ticket = ticket;
+  c.mpc = mpc; c.per = per; c.epoch = epoch;
+  c.rs_out = reinterpret_cast<__nv_bfloat16*>(out);
+  c.a_full = reinterpret_cast<char*>(a_full);
+  c.unit_bytes = (long long)BLOCK_M * K * 2;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(gemm_allreduce_fused_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             SmemLayout<BN>::TOTAL) != cudaSuccess)
-      return -2;
-    configured = true;
-  }
-  if (cudaMemsetAsync(ticket, 0, sizeof(int), s) != cudaSuccess) return -4;
-  gemm_allreduce_fused_kernel<BN><<<grid, NUM_THREADS, SmemLayout<BN>::TOTAL, s>>>(ta, tb, g, c, n_gemm);
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  if (mode != MODE_AG && cudaMemsetAsync(ticket, 0, sizeof(int), s) != cudaSuccess) return -4;
+  if (mode == MODE_AR) return launch_fused<MODE_AR>(ta, tb, g, c, grid, n_gemm, s);
+  if (mode == MODE_RS) return launch_fused<MODE_RS>(ta, tb, g, c, grid, n_gemm, s);
+  return launch_fused<MODE_AG>(ta, tb, g, c, grid, n_gemm, s);
 }

@@ -5,6 +5,12 @@ shardings (Megatron layout): ``wqkv``/``w1``/``lm_head`` are column-parallel ``P
 ``wo``/``w2`` row-parallel ``P('tp', None)``, the batch is ``P('dp', None)``. The sharding
 propagation inserts the collectives. ``wqkv`` columns are ordered (head, {q,k,v}, head_dim) so
 that splitting the column dim splits heads.
+
+With ``SeqParallel`` the LayerNorm / residual regions keep the tokens split over the tensor-
+parallel axis as well (activations ``P('dp', 'tp', None)``): the row-parallel projections end in
+a reduce-scatter instead of an all-reduce, the column-parallel ones start with an all-gather,
+and no elementwise work is replicated over the tensor-parallel group. Both collectives fuse
+with their GEMM (``csrc/gemm_tcgen05.cu``).
 """
 from __future__ import annotations
 
@@ -48,6 +54,20 @@ class TransformerConfig:
         return 6.0 * mm + 3.0 * attn
 
 
+@dataclass(frozen=True)
+class SeqParallel:
+    """Where the token dimension is split between the tensor-parallel regions."""
+    mesh: Any
+    dp_axis: str | None = "dp"
+    tp_axis: str = "tp"
+
+    def tokens_split(self, x: Tensor) -> Tensor:      # (B, S, D) -> P(dp, tp, None)
+        return x.shard(self.mesh, (self.dp_axis, self.tp_axis, None))
+
+    def tokens_whole(self, x: Tensor) -> Tensor:      # (B, S, D) -> P(dp, None, None)
+        return x.shard(self.mesh, (self.dp_axis, None, None))
+
+
 def init_params(cfg: TransformerConfig, mesh=None, tp_axis: str | None = "tp", device=None) -> dict[str, Any]:
     """Random-normal weights (std ``init_std``), zero biases, unit LayerNorm gains."""
     dt = cfg.dtype
@@ -87,17 +107,26 @@ def init_params(cfg: TransformerConfig, mesh=None, tp_axis: str | None = "tp", d
     }
 
 
-def block(x: Tensor, p: dict[str, Tensor], cfg: TransformerConfig) -> Tensor:
-    h = F.layer_norm(x, p["ln1_g"], p["ln1_b"])
+def block(x: Tensor, p: dict[str, Tensor], cfg: TransformerConfig, sp: SeqParallel | None = None) -> Tensor:
+    if sp is None:
+        h = F.layer_norm(x, p["ln1_g"], p["ln1_b"])
+        qkv = F.linear(h, p["wqkv"], p["bqkv"])
+        a = fused.packed_self_attention(qkv, cfg.head_dim, causal=True)
+        x = x + F.linear(a, p["wo"], p["bo"])
+        h = F.layer_norm(x, p["ln2_g"], p["ln2_b"])
+        m = F.linear(h, p["w1"], p["b1"], activation="gelu")
+        return x + F.linear(m, p["w2"], p["b2"])
+    # tokens split over tp outside the projections: gather -> column-parallel -> row-parallel -> scatter
+    h = sp.tokens_whole(F.layer_norm(x, p["ln1_g"], p["ln1_b"]))
     qkv = F.linear(h, p["wqkv"], p["bqkv"])
     a = fused.packed_self_attention(qkv, cfg.head_dim, causal=True)
-    x = x + F.linear(a, p["wo"], p["bo"])
-    h = F.layer_norm(x, p["ln2_g"], p["ln2_b"])
+    x = x + (sp.tokens_split(F.linear(a, p["wo"])) + p["bo"])
+    h = sp.tokens_whole(F.layer_norm(x, p["ln2_g"], p["ln2_b"]))
     m = F.linear(h, p["w1"], p["b1"], activation="gelu")
-    return x + F.linear(m, p["w2"], p["b2"])
+    return x + (sp.tokens_split(F.linear(m, p["w2"])) + p["b2"])
 
 
-def forward(params: dict[str, Any], tokens: Tensor, cfg: TransformerConfig) -> Tensor:
+def forward(params: dict[str, Any], tokens: Tensor, cfg: TransformerConfig, sp: SeqParallel | None = None) -> Tensor:
     """tokens (B, S) int64 -> logits (B, S, vocab)."""
     S = int(tokens.shape[1])
     x = gather(params["tok_emb"], tokens, axis=0)
@@ -105,17 +134,22 @@ def forward(params: dict[str, Any], tokens: Tensor, cfg: TransformerConfig) -> T
     if int(pos.shape[0]) != S:
         pos = pos[:S]
     x = x + pos
+    if sp is not None:
+        x = sp.tokens_split(x)
     for p in params["layers"]:
-        x = block(x, p, cfg)
+        x = block(x, p, cfg, sp)
     x = F.layer_norm(x, params["lnf_g"], params["lnf_b"])
+    if sp is not None:
+        x = sp.tokens_whole(x)
     return F.linear(x, params["lm_head"])
 
 
-def loss_fn(params: dict[str, Any], tokens: Tensor, targets: Tensor, cfg: TransformerConfig) -> Tensor:
+def loss_fn(params: dict[str, Any], tokens: Tensor, targets: Tensor, cfg: TransformerConfig,
+            sp: SeqParallel | None = None) -> Tensor:
     """Mean next-token cross-entropy over all positions (fp32 scalar)."""
     from ..ops.reduction import reduce_sum
 
-    logits = forward(params, tokens, cfg)
+    logits = forward(params, tokens, cfg, sp)
     rows = fused.cross_entropy_rows(logits, targets)
     n = int(tokens.shape[0]) * int(tokens.shape[1])
     return reduce_sum(rows) * (1.0 / n)

@@ -469,6 +469,18 @@ def reshard_to_spec(x: Tensor, target: ShardingSpec) -> Tensor:
             r = _all_gather_op(r, dim=d)
     drop = set(r._impl.sharding.partial_sum_axes) - set(target.partial_sum_axes)
     if drop:
+        # a pending sum over axes that the target uses to split a dim: reduce-scatter (half the
+        # traffic of all-reduce + slice); the scattered axes must extend the dim's axis list
+        now = r._impl.sharding
+        for d in range(len(now.dim_specs)):
+            have, want = list(now.dim_specs[d].axes), list(target.dim_specs[d].axes)
+            extra = want[len(have):]
+            if extra and want[:len(have)] == have and set(extra) <= drop and \
+                    r._impl._shape[d] % math.prod(mesh.get_axis_size(a) for a in want) == 0:
+                r = _reduce_scatter_op(r, dim=d, scatter_axes=tuple(extra))
+                drop -= set(extra)
+                now = r._impl.sharding
+    if drop:
         r = _all_reduce_op(r, reduce_axes=frozenset(drop), reduce_op="sum")
     now = r._impl.sharding
     if any(a.axes != b.axes for a, b in zip(now.dim_specs, target.dim_specs)):

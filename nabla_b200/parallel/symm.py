@@ -170,33 +170,83 @@ def all_reduce(buf: torch.Tensor, mesh, axes, op: str = "sum", algo: str | None 
 
 _gemm_fn = None
 FUSED_COMM_CTAS = int(os.environ.get("NABLA_B200_FUSED_COMM_CTAS", "20"))
+AG_COMM_CTAS = int(os.environ.get("NABLA_B200_AG_COMM_CTAS", "12"))
+MODE_AR, MODE_RS, MODE_AG = 1, 2, 3
+_EPI = {"none": 0, "bias": 1, "relu": 2, "gelu": 3}
 
 
-def _gemm_ar_fn():
+def _fused_fn():
     global _gemm_fn
     if _gemm_fn is None:
         from ..native import load
 
-        fn = load("libnb_gemm.so").nb_gemm_allreduce_bf16
+        lib = load("libnb_gemm.so")
+        fn = lib.nb_gemm_fused_bf16
         fn.restype = c_int
-        fn.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_ll, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll, c_int, c_int,
-                       c_int, c_int, c_uint, c_int, c_vp, c_vp, c_vp]
-        _gemm_fn = fn
+        fn.argtypes = ([c_int] + [c_vp] * 9 + [c_ll, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll] + [c_int] * 9 +
+                       [c_uint, c_uint, c_int, c_vp, c_vp, c_vp])
+        lib.nb_gemm_fused_grid.restype = c_int
+        _gemm_fn = (fn, lib.nb_gemm_fused_grid)
     return _gemm_fn
 
 
+def _fused_shapes_ok(m: int, n: int, k: int, nbytes_ws: int) -> bool:
+    if n % 8 or k % 8 or m <= 0 or n <= 0 or k <= 0:
+        return False
+    return nbytes_ws + 4096 <= DEFAULT_BYTES - 65536
+
+
 def gemm_all_reduce_supported(a: torch.Tensor, b: torch.Tensor) -> bool:
-    """Shapes the fused kernel takes: 2-D bf16 operands, N a multiple of 8, at most 8192 output
-    tiles of 128 x 256, output fitting the workspace."""
+    """Shapes the fused kernel takes: 2-D bf16 operands, N and K multiples of 8, at most 8192
+    output tiles of 128 x 256, output fitting the workspace."""
     if not (a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and b.dim() == 2 and a.dim() >= 2):
         return False
-    m = a.numel() // a.shape[-1]
-    n = b.shape[1]
-    if n % 8 or m == 0 or a.shape[-1] == 0:
+    m, k, n = a.numel() // max(a.shape[-1], 1), a.shape[-1], b.shape[1]
+    if m == 0 or ((m + 127) // 128) * ((n + 255) // 256) > 8192:
         return False
-    if ((m + 127) // 128) * ((n + 255) // 256) > 8192:
-        return False
-    return m * n * 2 + 4096 <= DEFAULT_BYTES - 65536
+    return _fused_shapes_ok(m, n, k, m * n * 2)
+
+
+def chunked_supported(m_total: int, chunk_rows: int, world: int) -> bool:
+    """Row layout the reduce-scatter / all-gather kernels take: whole 128-row tiles per chunk."""
+    return chunk_rows > 0 and chunk_rows % 128 == 0 and m_total % (world * chunk_rows) == 0 and m_total // 128 <= 2048
+
+
+def _fused_state(ws, device):
+    if not hasattr(ws, "ticket"):
+        ws.ticket = torch.zeros(4, dtype=torch.int32, device=device)
+        ws.done_total = 0
+        ws.ag_epoch = 0
+    return ws
+
+
+def _launch_fused(mode, ws, a, b, out, bias, aux_out, a_full, M, N, K, lda, ldb, a_mn, b_mn, epi, aux, gelu_tanh,
+                  chunk_rows, n_comm):
+    global launch_count
+    fn, grid_fn = _fused_fn()
+    lib = _L()
+    grid = grid_fn()
+    n_comm = max(1, min(n_comm, grid // 2))
+    ws.done_total = (ws.done_total + ws.world * (n_comm if mode == MODE_AG else grid)) & 0xFFFFFFFF
+    if mode == MODE_AG:
+        ws.ag_epoch += 1
+    p = lambda t: c_vp(0 if t is None else t.data_ptr())
+    rc = fn(mode, p(a), p(b), p(out), p(bias), p(aux_out), p(a_full), ws.buf.data_ptr(), ws.ptrs_dev, ws.mc_ptr,
+            ws.flag_bytes, lib.nb_comm_tile_flag_offset(), lib.nb_comm_done_offset(), M, N, K, lda, ldb, a_mn, b_mn,
+            1 if (bias is not None and bias.dtype == torch.float32) else 0, epi, aux, int(gelu_tanh), ws.rank, ws.world,
+            chunk_rows, ws.ag_epoch, ws.done_total, n_comm, ws.ticket.data_ptr(), _status().data_ptr(), _stream())
+    if rc != 0:
+        raise RuntimeError(f"nb_gemm_fused_bf16(mode={mode}) failed with code {rc} for M={M} N={N} K={K}")
+    launch_count += 1
+
+
+def _operands(a: torch.Tensor, b: torch.Tensor):
+    from ..native.gemm import _prep
+
+    a2 = a.reshape(-1, a.shape[-1])
+    a3, akind, lda, _ = _prep(a2.unsqueeze(0))
+    b3, bkind, ldb, _ = _prep(b.unsqueeze(0))
+    return a3, b3, lda, ldb, (0 if akind == "row" else 1), (1 if bkind == "row" else 0)
 
 
 def gemm_all_reduce(a: torch.Tensor, b: torch.Tensor, mesh, axes) -> torch.Tensor:
@@ -207,30 +257,54 @@ def gemm_all_reduce(a: torch.Tensor, b: torch.Tensor, mesh, axes) -> torch.Tenso
 
     Returns a VIEW of the workspace (M x N bf16): consume or copy it before the next collective
     on this group."""
-    global launch_count
+    ws = _fused_state(workspace(mesh, axes), a.device)
+    a3, b3, lda, ldb, a_mn, b_mn = _operands(a, b)
+    M, K, N = a3.shape[1], a3.shape[2], b.shape[1]
+    _launch_fused(MODE_AR, ws, a3, b3, None, None, None, None, M, N, K, lda, ldb, a_mn, b_mn, 0, 0, False, 0,
+                  FUSED_COMM_CTAS)
+    return ws.data[: M * N * 2].view(torch.bfloat16).view(M, N)
+
+
+def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_rows: int) -> torch.Tensor:
+    """Rows of ``sum_r a_r @ b_r`` that belong to this rank (row chunks of ``chunk_rows`` dealt
+    round-robin to the ranks), in one kernel: same tile flow as :func:`gemm_all_reduce`, but each
+    tile is summed only by its owner, straight into the returned tensor (M / world, N)."""
+    ws = _fused_state(workspace(mesh, axes), a.device)
+    a3, b3, lda, ldb, a_mn, b_mn = _operands(a, b)
+    M, K, N = a3.shape[1], a3.shape[2], b.shape[1]
+    out = torch.empty((M // ws.world, N), dtype=torch.bfloat16, device=a.device)
+    _launch_fused(MODE_RS, ws, a3, b3, out, None, None, None, M, N, K, lda, ldb, a_mn, b_mn, 0, 0, False, chunk_rows,
+                  FUSED_COMM_CTAS)
+    return out
+
+
+def all_gather_gemm(a_shard: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_rows: int, bias: torch.Tensor | None = None,
+                    epilogue: str = "none", gelu_tanh: bool = False, store_preact: bool = False):
+    """``epilogue(gather(a) @ b + bias)`` in one kernel. ``a_shard`` is this rank's rows
+    (M / world, K); copy CTAs of the launch pull the peers' rows over NVLink with bulk copies
+    into the gathered matrix while the tensor-core CTAs already multiply the rows that are
+    there (own rows first, then the peers' in ring order).
+
+    Returns ``(a_full, out)`` or ``(a_full, out, preact)``; ``a_full`` (M, K) is the all-gather's
+    own result, kept for the backward pass."""
     from ..native.gemm import _prep
 
-    ws = workspace(mesh, axes)
-    a2 = a.reshape(-1, a.shape[-1])
-    M, K = a2.shape
-    N = b.shape[1]
-    a3, akind, lda, _ = _prep(a2.unsqueeze(0))
+    ws = _fused_state(workspace(mesh, axes), a_shard.device)
+    x = a_shard.reshape(-1, a_shard.shape[-1])
+    Ml, K = x.shape
+    M, N = Ml * ws.world, b.shape[1]
+    ws.data[: Ml * K * 2].view(torch.bfloat16).view(Ml, K).copy_(x)        # stage where peers can read it
     b3, bkind, ldb, _ = _prep(b.unsqueeze(0))
-    a_mn = 0 if akind == "row" else 1
-    b_mn = 1 if bkind == "row" else 0
-    if not hasattr(ws, "ticket"):
-        ws.ticket = torch.zeros(4, dtype=torch.int32, device=a.device)
-        ws.fused_calls = 0
-    ws.fused_calls += 1
-    lib = _L()
-    rc = _gemm_ar_fn()(a3.data_ptr(), b3.data_ptr(), ws.buf.data_ptr(), ws.ptrs_dev, ws.mc_ptr, ws.flag_bytes,
-                       lib.nb_comm_tile_flag_offset(), lib.nb_comm_done_offset(), M, N, K, lda, ldb, a_mn, b_mn,
-                       ws.rank, ws.world, ws.fused_calls, FUSED_COMM_CTAS, ws.ticket.data_ptr(), _status().data_ptr(),
-                       _stream())
-    if rc != 0:
-        raise RuntimeError(f"nb_gemm_allreduce_bf16 failed with code {rc} for {tuple(a.shape)} @ {tuple(b.shape)}")
-    launch_count += 1
-    return ws.data[: M * N * 2].view(torch.bfloat16).view(M, N)
+    a_full = torch.empty((M, K), dtype=torch.bfloat16, device=x.device)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    pre = torch.empty((M, N), dtype=torch.bfloat16, device=x.device) if store_preact else None
+    if bias is not None:
+        bias = bias.reshape(-1).contiguous()
+        if epilogue == "none":
+            epilogue = "bias"
+    _launch_fused(MODE_AG, ws, None, b3, out, bias, pre, a_full, M, N, K, K, ldb, 0, 1 if bkind == "row" else 0,
+                  _EPI[epilogue], 1 if store_preact else 0, gelu_tanh, chunk_rows, AG_COMM_CTAS)
+    return (a_full, out, pre) if store_preact else (a_full, out)
 
 
 def _gather_call(x: torch.Tensor, mesh, axes, mode: int, chunk_elems: int, out_elems: int, root: int = 0) -> torch.Tensor:

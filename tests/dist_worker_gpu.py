@@ -105,6 +105,35 @@ def main():
                     y = symm.gemm_all_reduce(a, b, mesh, ("x",)).clone()
                     torch.cuda.synchronize()
                     errs[f"{M}x{N}x{K}_{int(b_t)}_{rep}"] = ((y.float() - ref).abs().max() / ref.abs().max()).item()
+        # reduce-scatter and all-gather variants; rows are dealt to ranks in chunks of `cs`
+        for (M, N, K, cs) in [(256 * world, 512, 256, 128), (1024 * world, 264, 328, 256), (512 * world, 2048, 72, 512)]:
+            torch.manual_seed(11 + rank)
+            a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+            b = torch.randn(K, N, device=dev, dtype=torch.bfloat16)
+            ref = a.float() @ b.float()
+            dist.all_reduce(ref)
+            mine = ref.view(-1, world, cs, N)[:, rank].reshape(-1, N)         # this rank's row chunks
+            for rep in range(2):
+                y = symm.gemm_reduce_scatter(a, b, mesh, ("x",), cs)
+                torch.cuda.synchronize()
+                errs[f"rs_{M}x{N}x{K}_{rep}"] = ((y.float() - mine).abs().max() / ref.abs().max()).item()
+            # all-gather -> GEMM with bias + gelu epilogue and stored pre-activation
+            torch.manual_seed(5)                                              # same weights on every rank
+            w = torch.randn(K, N, device=dev, dtype=torch.bfloat16) * 0.05
+            bias = torch.randn(N, device=dev, dtype=torch.bfloat16)
+            torch.manual_seed(13 + rank)
+            xs = torch.randn(M // world, K, device=dev, dtype=torch.bfloat16)
+            parts = [torch.empty_like(xs) for _ in range(world)]
+            dist.all_gather(parts, xs)
+            full = torch.stack([p_.view(-1, cs, K) for p_ in parts], 1).reshape(M, K)
+            z_ref = full.float() @ w.float() + bias.float()
+            for rep in range(2):
+                a_full, y, z = symm.all_gather_gemm(xs, w, mesh, ("x",), cs, bias=bias, epilogue="gelu", store_preact=True)
+                torch.cuda.synchronize()
+                errs[f"ag_gather_{M}x{K}_{rep}"] = (a_full.float() - full.float()).abs().max().item()
+                errs[f"ag_z_{M}x{N}x{K}_{rep}"] = ((z.float() - z_ref).abs().max() / z_ref.abs().max()).item()
+                errs[f"ag_y_{M}x{N}x{K}_{rep}"] = ((y.float() - torch.nn.functional.gelu(z_ref)).abs().max()
+                                                    / z_ref.abs().max()).item()
         native.check_status()
         out["max_err"] = max(errs.values())
         out["errs"] = {k: v for k, v in errs.items() if v > 2e-2}
@@ -118,8 +147,26 @@ def main():
             dist.all_reduce(y)
             return y
 
+        xs = torch.randn(M // world, 2048, device=dev, dtype=torch.bfloat16)
+        w1 = torch.randn(2048, 8192 // world, device=dev, dtype=torch.bfloat16)
+        full_x = torch.empty(M, 2048, device=dev, dtype=torch.bfloat16)
+
+        def unfused_rs():
+            y = gemm_bf16(a, b)
+            o = torch.empty(M // world, N, device=dev, dtype=torch.bfloat16)
+            dist.reduce_scatter_tensor(o, y)
+            return o
+
+        def unfused_ag():
+            dist.all_gather_into_tensor(full_x, xs)
+            return gemm_bf16(full_x, w1)
+
         for name, fn in (("fused", lambda: symm.gemm_all_reduce(a, b, mesh, ("x",))), ("gemm_then_nccl", unfused),
-                         ("gemm_only", lambda: gemm_bf16(a, b))):
+                         ("gemm_only", lambda: gemm_bf16(a, b)),
+                         ("rs_fused", lambda: symm.gemm_reduce_scatter(a, b, mesh, ("x",), M // world)),
+                         ("rs_gemm_then_nccl", unfused_rs),
+                         ("ag_fused", lambda: symm.all_gather_gemm(xs, w1, mesh, ("x",), M // world)),
+                         ("ag_nccl_then_gemm", unfused_ag), ("ag_gemm_only", lambda: gemm_bf16(full_x, w1))):
             for _ in range(3):
                 fn()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -157,20 +204,28 @@ def main():
                 rel.append(((ta - tb).norm() / (ta.norm() + 1e-6)).item())
             out.update(loss0=l0.item(), loss1=l1.item(), grad_rel_err=max(rel), backend=dict(backend.stats))
     elif mode == "lost_peer":
+        import time
+
+        from nabla_b200.parallel import health
+
         mesh = nb.DeviceMesh("m", (world,), ("x",))
         x = nb.Tensor.from_torch(torch.ones(4, 4, device=dev)).shard(mesh, ("x", None))
         nb.all_reduce(x, reduce_axes={"x"}).realize()
         torch.cuda.synchronize()
         if rank == world - 1:
+            health.announce_exit()                         # leaves between steps, nothing in flight
             print("RESULT " + json.dumps({"rank": rank, "left": True}), flush=True)
-            os._exit(0)                                   # leaves between steps, nothing in flight
+            os._exit(0)
         try:
-            nb.all_reduce(x * 2.0, reduce_axes={"x"}).realize()
-            torch.cuda.synchronize()
+            deadline = time.time() + 30
+            while time.time() < deadline:                  # the survivors look at the store before launching
+                health.check_peers()
+                time.sleep(0.2)
             out["detected"] = False
-        except Exception as e:
+        except health.PeerLostError as e:
             out["detected"] = True
             out["error"] = type(e).__name__
+            out["lost"] = e.ranks
     print("RESULT " + json.dumps(out), flush=True)
     if mode == "lost_peer":
         os._exit(0)

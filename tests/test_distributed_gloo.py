@@ -99,3 +99,35 @@ def test_failed_rank_is_detected_not_hung():
     out = res.stdout + res.stderr
     assert "RESULT detected" in out or res.returncode != 0, out[-3000:]
     assert "RESULT no-error" not in out
+
+
+HEALTH = textwrap.dedent('''
+    import os, sys, time
+    sys.path.insert(0, {root!r})
+    import nabla_b200 as nb
+    from nabla_b200.parallel import init_distributed, health
+    rank, world = init_distributed(backend="gloo", timeout_s=30)
+    health.beat()
+    if rank == 1:
+        mode = sys.argv[1]
+        if mode == "announce":
+            health.announce_exit()
+        time.sleep(1.0 if mode == "announce" else 4.0)      # 'silent': alive but stuck, no more beats
+        os._exit(0)
+    t0 = time.time()
+    try:
+        while time.time() - t0 < 20:
+            health.beat()
+            health.check_peers(max_silence_s=1.5)
+            time.sleep(0.1)
+        print("RESULT no-error", flush=True)
+    except health.PeerLostError as e:
+        print("RESULT lost " + str(e.ranks) + " after %.1f" % (time.time() - t0), flush=True)
+    os._exit(0)
+''')
+
+
+@pytest.mark.parametrize("mode", ["announce", "silent"])
+def test_health_store_reports_lost_peer_before_next_launch(mode):
+    res = _run(HEALTH, [mode], timeout=120)
+    assert "RESULT lost [1]" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]

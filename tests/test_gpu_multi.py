@@ -62,10 +62,11 @@ def test_sharded_transformer_step_matches_unsharded(comm):
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_lost_peer_is_reported_not_hung():
-    # NVLS off and NCCL baseline: a rank leaves between steps; the other's next collective errors out
-    res, rs = _run("lost_peer", 2, env={"NCCL_NVLS_ENABLE": "0", "NABLA_B200_NVLS": "0", "NABLA_B200_COMM": "nccl",
-                                         "TORCH_NCCL_ASYNC_ERROR_HANDLING": "1"}, timeout=180)
+    # NVLS off, own kernels off: a rank leaves between steps and says so on the host; the others
+    # learn of it from the store before their next launch and enter no further collective
+    res, rs = _run("lost_peer", 2, env={"NCCL_NVLS_ENABLE": "0", "NABLA_B200_NVLS": "0", "NABLA_B200_COMM": "nccl"},
+                   timeout=180)
     left = [r for r in rs if r.get("left")]
     others = [r for r in rs if not r.get("left")]
-    assert left, res.stdout[-2000:] + res.stderr[-2000:]
-    assert all(r.get("detected") for r in others) or res.returncode != 0
+    assert left and others, res.stdout[-2000:] + res.stderr[-2000:]
+    assert all(r.get("detected") and r.get("lost") == [1] for r in others), others
