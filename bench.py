@@ -91,6 +91,12 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(self.rows)}
 
 
+def _collective_stats():
+    from nabla_b200.parallel import backend
+
+    return dict(backend.stats)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -115,6 +121,10 @@ def main() -> None:
     from nabla_b200.parallel import init_distributed
 
     rank, world = init_distributed()
+    if os.environ.get("NABLA_B200_BENCH_DEBUG"):
+        import faulthandler
+
+        faulthandler.dump_traceback_later(int(os.environ["NABLA_B200_BENCH_DEBUG"]), exit=False, file=sys.stderr)
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
     n = world
@@ -127,6 +137,10 @@ def main() -> None:
     mesh = nb.DeviceMesh("mesh", (dp, tp), ("dp", "tp")) if n > 1 else None
     global_batch = args.seqs_per_gpu * n
     seq = cfg.max_seq
+    # tokens stay split over 'tp' between the projections (reduce-scatter / all-gather fused
+    # with their GEMMs) unless NABLA_B200_SEQ_PARALLEL=0 asks for the all-reduce layout
+    sp = T.SeqParallel(mesh, "dp", "tp") if (mesh is not None and tp > 1
+                                              and os.environ.get("NABLA_B200_SEQ_PARALLEL", "1") != "0") else None
 
     with nb.default_device(dev):
         nb.seed(1234)
@@ -135,9 +149,13 @@ def main() -> None:
         state = nn.adamw_init(params, state_dtype=nb.DType.float32)
         nb.realize_all(*nb.tensor_leaves(state))
 
-        @nb.compile
+        # the whole step (forward, backward, AdamW) is recorded once, captured into one CUDA graph
+        # and replayed; params and optimizer state are donated, so AdamW updates them in place
+        use_graph = os.environ.get("NABLA_B200_CUDA_GRAPH", "1") != "0"
+
+        @nb.compile(cuda_graph=use_graph, donate_argnums=(0, 1))
         def train_step(params, state, tokens, targets):
-            loss, grads = nb.value_and_grad(lambda p: T.loss_fn(p, tokens, targets, cfg), create_graph=False)(params)
+            loss, grads = nb.value_and_grad(lambda p: T.loss_fn(p, tokens, targets, cfg, sp), create_graph=False)(params)
             params, state = nn.adamw_update(params, grads, state, lr=1e-4, weight_decay=0.01, realize=False)
             return loss, params, state
 
@@ -178,7 +196,7 @@ def main() -> None:
             from nabla_b200.native import attention, gemm, kernels
             from nabla_b200.parallel import backend
 
-            return gemm.launch_count + kernels.launch_count + attention.launch_count + backend.stats["native_calls"]
+            return native.total_launches()
 
         # ---- warm-up (includes the one trace)
         it = iter(host)
@@ -196,11 +214,15 @@ def main() -> None:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(local) as clk:
             e0.record()
+            t_issue0 = time.perf_counter()
             for tok, tgt in staged:
                 loss, params, state = train_step(params, state, tok, tgt)
             e1.record()
+            host_issue_ms = 1e3 * (time.perf_counter() - t_issue0)     # host time to enqueue the K steps
             sync()
         launches = counters() - c0
+        if train_step.stats.cuda_graphs:
+            launches = train_step.stats.launches_per_graph * args.steps     # replayed from the captured graph
         ms = e0.elapsed_time(e1)
         t = torch.tensor([ms], device=tdev)
         if world > 1:
@@ -244,22 +266,30 @@ def main() -> None:
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids ~U[0,32000), random-init weights",
             "config": {"model": f"decoder-only transformer {cfg.n_layers}L d{cfg.d_model} h{cfg.n_heads} ff{cfg.d_ff} "
                                 f"vocab{cfg.vocab} pre-LN gelu, bf16 params + fp32 Adam state",
-                       "global_batch": global_batch, "seq_len": seq, "parallelism": f"dp{dp}xtp{tp}",
+                       "global_batch": global_batch, "seq_len": seq, "parallelism": f"dp{dp}xtp{tp}" + ("+sp" if sp is not None else ""),
                        "l2": "inputs larger than L2 (per-step working set is tens of GB)",
-                       "optimizer": "AdamW fused kernel, inside the timed step"},
+                       "optimizer": "AdamW fused kernel, inside the timed step",
+                       "cuda_graph": bool(train_step.stats.cuda_graphs)},
             "clocks": clk.summary(),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms_total / args.steps,
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches),
+            "host_issue_ms_per_step": host_issue_ms / args.steps,
             "final_loss": last,
             "model_tflops_per_gpu": flops / (ms_total / args.steps / 1e3) / 1e12 / n,
             "mfu_of_measured_sustained": flops / (ms_total / args.steps / 1e3) / 1e12 / n / sustained,
             "impl": "ours",
+            "collectives": _collective_stats(),
         }
         print(json.dumps(out))
     if world > 1:
         torch.distributed.barrier()
-        torch.distributed.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        # captured CUDA graphs hold NCCL kernels; tearing the communicator down under them can
+        # block, so the ranks leave together without the teardown
+        os._exit(0)
 
 
 if __name__ == "__main__":

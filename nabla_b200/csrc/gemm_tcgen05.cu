@@ -94,7 +94,10 @@ struct CommArgs {
   int* ticket;              // device int, zeroed before the launch: next reduce job of this rank
   int mpc;                  // M tiles per row chunk (chunk_rows / 128); RS and AG
   int per;                  // M tiles per rank (num_m / world); AG
-  unsigned epoch;           // AG: value of the ready / row flags of this call
+  unsigned epoch;           // AG: value of the ready / row flags of this call (relative to ctr[1])
+  const unsigned* ctr;      // device counters of the workspace: [1] all-gather calls so far, [2] done
+                            // counts so far; epoch and done_target are relative to them, and a
+                            // one-thread kernel advances them after the launch (CUDA-graph replay safe)
   __nv_bfloat16* rs_out;    // RS: this rank's rows of the sum, [M / world][N]
   char* a_full;             // AG: the gathered A, [M][K] dense
   long long unit_bytes;     // AG: bytes of one 128-row block of A
@@ -768,7 +771,10 @@ __device__ __forceinline__ void gather_jobs(const GemmArgs& args, const CommArgs
 template <int BN, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const GemmArgs args, const CommArgs comm, const int n_gemm) {
+                  const GemmArgs args, const CommArgs comm_in, const int n_gemm) {
+  CommArgs comm = comm_in;
+  comm.epoch += *reinterpret_cast<const volatile unsigned*>(comm_in.ctr + 1);
+  comm.done_target += *reinterpret_cast<const volatile unsigned*>(comm_in.ctr + 2);
   const bool is_gemm = (int)blockIdx.x < n_gemm;
   if (is_gemm) {
     if (!gemm_cta<BN, MODE>(&tmA, &tmB, args, comm, blockIdx.x, n_gemm)) return;
@@ -916,9 +922,9 @@ extern "C" int nb_gemm_bf16(const void* A, const void* B, void* C, const void* b
 //   out           mode 2: this rank's rows [M/world][N];  mode 3: C [M][N] (ldc = N);  mode 1: unused
 //   a_full        mode 3: the gathered A [M][K] (dense, regular device memory); A is then ignored
 //   chunk_rows    modes 2, 3: rows per contiguous chunk of a rank (multiple of 128, M % (world*chunk_rows) == 0)
-//   epoch         mode 3: 1, 2, 3, ... per all-gather call on this workspace
-//   done_target   absolute value of the workspace's done counter after this call
-//                 (previous + world * participants; participants = grid for modes 1, 2, n_comm for 3)
+//   ctr           device counters of the workspace (unsigned[4], zero at creation): the kernel
+//                 takes its all-gather epoch and done target relative to them and a one-thread
+//                 kernel advances them afterwards, so replaying the launches from a CUDA graph works
 //   ticket        device int used as job counter (zeroed here on `stream`)
 // Returns 0, or a negative code when the shape does not fit (the caller then runs the unfused path).
 extern "C" int nb_gemm_fused_grid() {
@@ -928,6 +934,11 @@ extern "C" int nb_gemm_fused_grid() {
     cudaDeviceGetAttribute(&nb::g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
   return nb::g_num_sms;
+}
+
+__global__ void bump_fused_kernel(unsigned* ctr, unsigned add_epoch, unsigned add_done) {
+  ctr[1] += add_epoch;
+  ctr[2] += add_done;
 }
 
 template <int MODE>
@@ -943,6 +954,7 @@ static int launch_fused(const CUtensorMap& ta, const CUtensorMap& tb, const nb::
     configured = true;
   }
   gemm_fused_kernel<BN, MODE><<<grid, NUM_THREADS, SmemLayout<BN>::TOTAL, s>>>(ta, tb, g, c, n_gemm);
+  bump_fused_kernel<<<1, 1, 0, s>>>(const_cast<unsigned*>(c.ctr), MODE == nb::MODE_AG ? 1u : 0u, c.done_target);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -950,8 +962,8 @@ extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* 
                                   void* a_full, void* ws_local, void* const* ws_bufs, void* mc, long long data_off,
                                   int flag_off, int done_off, int M, int N, int K, long long lda, long long ldb,
                                   int a_mn, int b_mn, int bias_fp32, int epi, int aux, int gelu_tanh, int rank,
-                                  int world, int chunk_rows, unsigned epoch, unsigned done_target, int n_comm_ctas,
-                                  int* ticket, int* status, void* stream) {
+                                  int world, int chunk_rows, unsigned* ctr, int n_comm_ctas, int* ticket, int* status,
+                                  void* stream) {
   using namespace nb;
   constexpr int BN = 256;
   if (mode < MODE_AR || mode > MODE_AG) return -9;
@@ -1000,9 +1012,9 @@ extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* 
   c.bufs = ws_bufs; c.mc = reinterpret_cast<char*>(mc); c.data_off = data_off;
   c.flag_off = flag_off; c.done_off = done_off; c.rank = rank; c.world = world;
   c.tile_target = (unsigned)world;
-  c.done_target = done_target;
+  c.done_target = (unsigned)world * (unsigned)(mode == MODE_AG ? n_comm_ctas : grid);   // + ctr[2] on the device
   c.ticket = ticket;
-  c.mpc = mpc; c.per = per; c.epoch = epoch;
+  c.mpc = mpc; c.per = per; c.epoch = 1u; c.ctr = ctr;
   c.rs_out = reinterpret_cast<__nv_bfloat16*>(out);
   c.a_full = reinterpret_cast<char*>(a_full);
   c.unit_bytes = (long long)BLOCK_M * K * 2;

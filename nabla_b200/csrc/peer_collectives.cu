@@ -33,7 +33,10 @@ struct Group {
   void* const* bufs;   // device array [world] of peer base pointers of the workspace
   void* mc;            // multicast base pointer of the workspace (nullptr: no NVLS)
   int rank, world;
-  unsigned epoch;      // increases by one per collective call on this workspace
+  unsigned epoch;      // this call's number relative to *epoch_ctr (1 = the next one)
+  const unsigned* epoch_ctr;   // device counter of the calls made so far on this workspace; a
+                               // one-thread kernel after each collective advances it, so a launch
+                               // sequence replayed from a CUDA graph keeps counting
   int* status;
 };
 
@@ -63,7 +66,7 @@ __device__ __forceinline__ bool wait_ge(const unsigned* p, unsigned target, int*
 __device__ __forceinline__ bool block_barrier(const Group& g, int phase) {
   __syncthreads();
   bool ok = true;
-  const unsigned val = g.epoch * 4u + (unsigned)phase;
+  const unsigned val = (g.epoch + *reinterpret_cast<const volatile unsigned*>(g.epoch_ctr)) * 4u + (unsigned)phase;
   if (threadIdx.x < g.world) {
     const int peer = threadIdx.x;
     __threadfence_system();
@@ -262,11 +265,13 @@ __global__ void wait_flag_kernel(const unsigned* flag, unsigned target, int* sta
 using namespace nbc;
 #define STREAM reinterpret_cast<cudaStream_t>(stream)
 
-static Group make_group(void* const* bufs, void* mc, int rank, int world, unsigned epoch, int* status) {
+static Group make_group(void* const* bufs, void* mc, int rank, int world, unsigned* epoch_ctr, int* status) {
   Group g;
-  g.bufs = bufs; g.mc = mc; g.rank = rank; g.world = world; g.epoch = epoch; g.status = status;
+  g.bufs = bufs; g.mc = mc; g.rank = rank; g.world = world; g.epoch = 1u; g.epoch_ctr = epoch_ctr; g.status = status;
   return g;
 }
+
+__global__ void bump_kernel(unsigned* ctr, unsigned inc) { *ctr += inc; }
 
 extern "C" {
 
@@ -274,28 +279,32 @@ int nb_comm_flag_bytes() { return FLAG_BYTES; }
 int nb_comm_tile_flag_offset() { return TILE_FLAG_OFFSET; }
 int nb_comm_done_offset() { return DONE_OFFSET; }
 
-int nb_comm_barrier(void* const* bufs, int rank, int world, unsigned epoch, int* status, void* stream) {
-  barrier_kernel<<<1, 32, 0, STREAM>>>(make_group(bufs, nullptr, rank, world, epoch, status));
+// `epoch_ctr`: device counter owned by the workspace (zero at creation); advanced here after the kernel.
+int nb_comm_barrier(void* const* bufs, int rank, int world, unsigned* epoch_ctr, int* status, void* stream) {
+  barrier_kernel<<<1, 32, 0, STREAM>>>(make_group(bufs, nullptr, rank, world, epoch_ctr, status));
+  bump_kernel<<<1, 1, 0, STREAM>>>(epoch_ctr, 1u);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
 // n must be a multiple of (16 / sizeof(T)) * world; dtype 0 fp32, 1 bf16; op 0 sum 1 max 2 min 3 prod.
-int nb_comm_allreduce(void* const* bufs, void* mc, int rank, int world, unsigned epoch, long long off, void* out,
+int nb_comm_allreduce(void* const* bufs, void* mc, int rank, int world, unsigned* epoch_ctr, long long off, void* out,
                       long long n, int dtype, int algo, int op, int blocks, int* status, void* stream) {
   if (world > MAX_WORLD || blocks > MAX_BLOCKS) return -2;
   if (algo == 2 && (mc == nullptr || op != 0)) return -3;
-  Group g = make_group(bufs, mc, rank, world, epoch, status);
+  Group g = make_group(bufs, mc, rank, world, epoch_ctr, status);
   if (dtype) allreduce_kernel<__nv_bfloat16><<<blocks, 512, 0, STREAM>>>(g, off, (__nv_bfloat16*)out, n, algo, op);
   else allreduce_kernel<float><<<blocks, 512, 0, STREAM>>>(g, off, (float*)out, n, algo, op);
+  bump_kernel<<<1, 1, 0, STREAM>>>(epoch_ctr, 1u);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
-int nb_comm_gather(void* const* bufs, int rank, int world, unsigned epoch, long long off, void* out, long long chunk_elems,
+int nb_comm_gather(void* const* bufs, int rank, int world, unsigned* epoch_ctr, long long off, void* out, long long chunk_elems,
                    int dtype, int mode, int op, int blocks, int* status, void* stream) {
   if (world > MAX_WORLD || blocks > MAX_BLOCKS) return -2;
-  Group g = make_group(bufs, nullptr, rank, world, epoch, status);
+  Group g = make_group(bufs, nullptr, rank, world, epoch_ctr, status);
   if (dtype) gather_kernel<__nv_bfloat16><<<blocks, 512, 0, STREAM>>>(g, off, (__nv_bfloat16*)out, chunk_elems, mode, op);
   else gather_kernel<float><<<blocks, 512, 0, STREAM>>>(g, off, (float*)out, chunk_elems, mode, op);
+  bump_kernel<<<1, 1, 0, STREAM>>>(epoch_ctr, 1u);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -94,3 +94,17 @@ def check_status(device: torch.device | None = None) -> None:
 
 
 from .gemm import gemm_bf16, gemm_supported  # noqa: E402,F401
+
+
+def total_launches() -> int:
+    """Number of launches of this package's own kernels issued so far by this process
+    (GEMM, attention, fused kernels, peer-memory collectives and fused GEMM+collective)."""
+    import sys
+
+    n = 0
+    for name in ("nabla_b200.native.gemm", "nabla_b200.native.kernels", "nabla_b200.native.attention",
+                 "nabla_b200.parallel.symm"):
+        m = sys.modules.get(name)
+        if m is not None:
+            n += getattr(m, "launch_count", 0)
+    return n

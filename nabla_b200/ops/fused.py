@@ -629,15 +629,18 @@ class AdamWStepOp(Operation):
     ``hyper`` = [lr, 1-b1^t, 1-b2^t, 1] built by ``AdamHyperOp`` from a 0-d step tensor, so a
     compiled training step does not retrace when the counter advances."""
 
+    inplace_inputs = (0, 2, 3)     # p, m, v may be overwritten when a compiled function was given them
+
     def kernel(self, p, g, m, v, step=None, *, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float,
-               step_value: int | None = None, bias_correction: bool = True):
+               step_value: int | None = None, bias_correction: bool = True, inplace: bool = False):
         if p.device.type != "meta" and _native(p) and p.numel() and m.dtype == torch.float32 and v.dtype == torch.float32 \
                 and g.dtype in (torch.bfloat16, torch.float32):
             from ..native import kernels
 
             hyper = step.contiguous() if (step is not None and bias_correction) else None
             return kernels.adamw(p, g, m, v, lr=lr, b1=beta1, b2=beta2, eps=eps, wd=weight_decay,
-                                 step=step_value if bias_correction else None, hyper=hyper)
+                                 step=step_value if bias_correction else None, hyper=hyper,
+                                 inplace=inplace and p.is_contiguous() and m.is_contiguous() and v.is_contiguous())
         gf, pf = g.float(), p.float()
         mn = beta1 * m.float() + (1 - beta1) * gf
         vn = beta2 * v.float() + (1 - beta2) * gf * gf
@@ -649,6 +652,11 @@ class AdamWStepOp(Operation):
         else:
             bc1 = bc2 = 1.0
         upd = (mn / bc1) / (torch.sqrt(vn / bc2) + eps) + weight_decay * pf
+        if inplace:
+            p.copy_(pf - lr * upd)
+            m.copy_(mn)
+            v.copy_(vn)
+            return p, m, v
         return (pf - lr * upd).to(p.dtype), mn.to(m.dtype), vn.to(v.dtype)
 
     def sharding_rule(self, input_shapes, output_shapes, **kw):

@@ -35,12 +35,12 @@ def _L():
         lib.nb_comm_tile_flag_offset.restype = c_int
         lib.nb_comm_done_offset.restype = c_int
         lib.nb_comm_allreduce.restype = c_int
-        lib.nb_comm_allreduce.argtypes = [c_vp, c_vp, c_int, c_int, c_uint, c_ll, c_vp, c_ll, c_int, c_int, c_int, c_int,
+        lib.nb_comm_allreduce.argtypes = [c_vp, c_vp, c_int, c_int, c_vp, c_ll, c_vp, c_ll, c_int, c_int, c_int, c_int,
                                           c_vp, c_vp]
         lib.nb_comm_gather.restype = c_int
-        lib.nb_comm_gather.argtypes = [c_vp, c_int, c_int, c_uint, c_ll, c_vp, c_ll, c_int, c_int, c_int, c_int, c_vp, c_vp]
+        lib.nb_comm_gather.argtypes = [c_vp, c_int, c_int, c_vp, c_ll, c_vp, c_ll, c_int, c_int, c_int, c_int, c_vp, c_vp]
         lib.nb_comm_barrier.restype = c_int
-        lib.nb_comm_barrier.argtypes = [c_vp, c_int, c_int, c_uint, c_vp, c_vp]
+        lib.nb_comm_barrier.argtypes = [c_vp, c_int, c_int, c_vp, c_vp, c_vp]
         lib.nb_comm_wait_flag.restype = c_int
         lib.nb_comm_wait_flag.argtypes = [c_vp, c_uint, c_vp, c_ull, c_vp]
         _lib = lib
@@ -69,15 +69,12 @@ class Workspace:
         except Exception:
             mc = 0
         self.mc_ptr = mc
-        self.epoch = 0
+        # device-side call counters: [0] collectives, [1] fused all-gathers, [2] fused done counts
+        self.ctr = torch.zeros(8, dtype=torch.int32, device=self.buf.device)
         self.data = self.buf[self.flag_bytes:]
         self.data_bytes = self.nbytes - self.flag_bytes
         torch.cuda.synchronize()
         dist.barrier(group=pg)
-
-    def next_epoch(self) -> int:
-        self.epoch += 1
-        return self.epoch
 
     def stage(self, x: torch.Tensor, offset: int = 0) -> None:
         """Copy ``x`` (contiguous) into the data region at byte ``offset``."""
@@ -112,7 +109,11 @@ def workspace(mesh, axes) -> Workspace:
     ws = _workspaces.get(key)
     if ws is None:
         pg, ranks = mesh.process_group(tuple(axes))
-        ws = Workspace(pg, ranks, DEFAULT_BYTES)
+        # one workspace per set of ranks: ('tp',) and ('dp', 'tp') of a dp=1 mesh share theirs
+        ws = _workspaces.get(tuple(ranks))
+        if ws is None:
+            ws = Workspace(pg, ranks, DEFAULT_BYTES)
+            _workspaces[tuple(ranks)] = ws
         _workspaces[key] = ws
     return ws
 
@@ -160,7 +161,7 @@ def all_reduce(buf: torch.Tensor, mesh, axes, op: str = "sum", algo: str | None 
         algo = "twoshot" if opi == 0 else "oneshot"
     ai = {"oneshot": 0, "twoshot": 1, "multimem": 2}[algo]
     blocks = 8 if nbytes <= 256 * 1024 else (32 if nbytes <= 8 * 1024 * 1024 else 64)
-    rc = _L().nb_comm_allreduce(ws.ptrs_dev, ws.mc_ptr, ws.rank, ws.world, ws.next_epoch(), 0, out.data_ptr(), n_pad,
+    rc = _L().nb_comm_allreduce(ws.ptrs_dev, ws.mc_ptr, ws.rank, ws.world, ws.ctr.data_ptr(), 0, out.data_ptr(), n_pad,
                                 1 if x.dtype == torch.bfloat16 else 0, ai, opi, blocks, _status().data_ptr(), _stream())
     if rc != 0:
         raise RuntimeError(f"nb_comm_allreduce failed with code {rc}")
@@ -184,7 +185,7 @@ def _fused_fn():
         fn = lib.nb_gemm_fused_bf16
         fn.restype = c_int
         fn.argtypes = ([c_int] + [c_vp] * 9 + [c_ll, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll] + [c_int] * 9 +
-                       [c_uint, c_uint, c_int, c_vp, c_vp, c_vp])
+                       [c_vp, c_int, c_vp, c_vp, c_vp])
         lib.nb_gemm_fused_grid.restype = c_int
         _gemm_fn = (fn, lib.nb_gemm_fused_grid)
     return _gemm_fn
@@ -215,8 +216,6 @@ def chunked_supported(m_total: int, chunk_rows: int, world: int) -> bool:
 def _fused_state(ws, device):
     if not hasattr(ws, "ticket"):
         ws.ticket = torch.zeros(4, dtype=torch.int32, device=device)
-        ws.done_total = 0
-        ws.ag_epoch = 0
     return ws
 
 
@@ -227,14 +226,11 @@ def _launch_fused(mode, ws, a, b, out, bias, aux_out, a_full, M, N, K, lda, ldb,
     lib = _L()
     grid = grid_fn()
     n_comm = max(1, min(n_comm, grid // 2))
-    ws.done_total = (ws.done_total + ws.world * (n_comm if mode == MODE_AG else grid)) & 0xFFFFFFFF
-    if mode == MODE_AG:
-        ws.ag_epoch += 1
     p = lambda t: c_vp(0 if t is None else t.data_ptr())
     rc = fn(mode, p(a), p(b), p(out), p(bias), p(aux_out), p(a_full), ws.buf.data_ptr(), ws.ptrs_dev, ws.mc_ptr,
             ws.flag_bytes, lib.nb_comm_tile_flag_offset(), lib.nb_comm_done_offset(), M, N, K, lda, ldb, a_mn, b_mn,
             1 if (bias is not None and bias.dtype == torch.float32) else 0, epi, aux, int(gelu_tanh), ws.rank, ws.world,
-            chunk_rows, ws.ag_epoch, ws.done_total, n_comm, ws.ticket.data_ptr(), _status().data_ptr(), _stream())
+            chunk_rows, ws.ctr.data_ptr(), n_comm, ws.ticket.data_ptr(), _status().data_ptr(), _stream())
     if rc != 0:
         raise RuntimeError(f"nb_gemm_fused_bf16(mode={mode}) failed with code {rc} for M={M} N={N} K={K}")
     launch_count += 1
@@ -315,7 +311,7 @@ def _gather_call(x: torch.Tensor, mesh, axes, mode: int, chunk_elems: int, out_e
     out = torch.empty(out_elems, dtype=x.dtype, device=x.device)
     nbytes = out_elems * x.element_size()
     blocks = 8 if nbytes <= 256 * 1024 else (32 if nbytes <= 8 * 1024 * 1024 else 64)
-    rc = _L().nb_comm_gather(ws.ptrs_dev, ws.rank, ws.world, ws.next_epoch(), 0, out.data_ptr(), chunk_elems,
+    rc = _L().nb_comm_gather(ws.ptrs_dev, ws.rank, ws.world, ws.ctr.data_ptr(), 0, out.data_ptr(), chunk_elems,
                              1 if x.dtype == torch.bfloat16 else 0, mode, root, blocks, _status().data_ptr(), _stream())
     if rc != 0:
         raise RuntimeError(f"nb_comm_gather failed with code {rc}")

@@ -5,7 +5,14 @@ recording a private graph of ``OpNode``s; later calls skip the Python function a
 pipeline (no shape inference, no sharding propagation): they bind the new input buffers to
 the placeholders and replay the recorded, fused schedule, freeing every intermediate right
 after its last use. With ``cuda_graph=True`` the replay is captured into a CUDA graph so a
-launch-bound step (small pipeline ticks) costs one graph launch.
+launch-bound step costs one graph launch.
+
+``donate_argnums=(i, ...)`` hands the buffers of those arguments to the function: optimizer-step
+ops that are the last reader of a donated parameter / moment update it in place, so the returned
+parameters ARE the argument's buffers (no 3x parameter-size allocation per step, and under
+``cuda_graph=True`` no copy in or out: feed the returned tree back in). The caller must not use
+a donated argument after the call. Outputs of a CUDA-graph replay that do not alias a donated
+input are copied out of the graph's memory; those that do are returned as they are.
 
 Cache key = (pytree structure, per-tensor (shape, dtype, sharding signature), static values);
 dimensions named in ``dynamic_dims={arg_idx: {dim_idx: "name"}}`` enter the key as ``"$name"``
@@ -39,6 +46,8 @@ class CompilationStats:
     replay_time_s: float = 0.0
     graph_nodes: int = 0
     graph_steps: int = 0
+    cuda_graphs: int = 0
+    launches_per_graph: int = 0      # this package's kernels inside the last captured CUDA graph
 
     @property
     def hit_rate(self) -> float:
@@ -64,6 +73,7 @@ class _Recorded:
         self.out_static: list[Any] = []
         self.out_treedef = None
         self.cuda_graph = None
+        self.donated: list[bool] = []               # per placeholder
         self.static_inputs: list[list[torch.Tensor]] | None = None
         self.static_outputs: list[list[torch.Tensor]] | None = None
 
@@ -93,8 +103,10 @@ def _normalize_step_scalars(tree: Any) -> Any:
 
 class CompiledFunction:
     def __init__(self, fn: Callable, *, fullgraph: bool = False, max_cache_size: int = 64,
-                 dynamic_dims: dict[int, dict[int, str]] | None = None, cuda_graph: bool = False):
+                 dynamic_dims: dict[int, dict[int, str]] | None = None, cuda_graph: bool = False,
+                 donate_argnums: tuple[int, ...] | int = ()):
         self.fn = fn
+        self.donate_argnums = (donate_argnums,) if isinstance(donate_argnums, int) else tuple(donate_argnums)
         self.fullgraph = fullgraph
         self.max_cache_size = int(max_cache_size)
         self.dynamic_dims = dynamic_dims or {}
@@ -140,6 +152,7 @@ class CompiledFunction:
                 f = ("static", _freeze(leaf))
                 sym.append(f)
                 conc.append(f)
+        self._last_owner = owner
         return (td, tuple(sym)), tuple(conc), leaves, td
 
     # ---- call
@@ -183,7 +196,8 @@ class CompiledFunction:
     def _trace(self, leaves: list, td) -> tuple[_Recorded, Any]:
         rec = _Recorded()
         ph_leaves = []
-        for l in leaves:
+        owner = getattr(self, "_last_owner", [None] * len(leaves))
+        for li, l in enumerate(leaves):
             if isinstance(l, Tensor):
                 im = l._impl
                 ph = TensorImpl(list(im._buffers), shape=im._shape, dtype=im.dtype, device=im.device,
@@ -191,6 +205,7 @@ class CompiledFunction:
                 ph.requires_grad = im.requires_grad
                 ph.is_traced = im.requires_grad
                 rec.placeholders.append(ph)
+                rec.donated.append(owner[li] in self.donate_argnums if owner[li] is not None else False)
                 ph_leaves.append(Tensor(impl=ph))
             else:
                 ph_leaves.append(l)
@@ -214,17 +229,25 @@ class CompiledFunction:
         rec.keep = [[o for o in n.outputs() if o is not None] for n in nodes]
         plan = fusion.build_plan(nodes, targets) if fusion.enabled() else None
         rec.steps = plan.steps if plan is not None else [("op", (i,)) for i in range(len(nodes))]
+        if any(rec.donated):
+            rec.steps = _optimizer_steps_last(rec.steps, nodes)
         # liveness: free an intermediate after the last step that reads it
         out_ids = {id(i) for i in rec.out_impls if i is not None}
         produced = {id(o): o for outs in rec.keep for o in outs}
         last_use: dict[int, int] = {}
+        ph_ids = {id(p) for p in rec.placeholders}
+        ph_last_use: dict[int, int] = {}
         for si, (kind, idxs) in enumerate(rec.steps):
             for ni in idxs:
                 for a in nodes[ni].input_impls():
                     if id(a) in produced:
                         last_use[id(a)] = si
+                    elif id(a) in ph_ids:
+                        ph_last_use[id(a)] = si
                 for o in rec.keep[ni]:
                     last_use.setdefault(id(o), si)
+        if any(rec.donated):
+            _mark_inplace_updates(rec, ph_last_use)
         rec.free_after = [[] for _ in rec.steps]
         for k, si in last_use.items():
             if k not in out_ids:
@@ -281,29 +304,33 @@ class CompiledFunction:
 
     def _replay_cuda_graph(self, rec: _Recorded, tensors: list[Tensor]) -> Any:
         if rec.cuda_graph is None:
+            # the graph owns its inputs: replays read (and, for donated arguments, update) them
             rec.static_inputs = [[b.clone() for b in t._impl._buffers] for t in tensors]
             for ph, bufs in zip(rec.placeholders, rec.static_inputs):
                 ph._buffers = bufs
-            s = torch.cuda.Stream()
-            s.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(s):
-                self._run(rec)       # warm-up on the side stream (allocator, lazy inits)
-                for impl in rec.out_impls:
-                    if impl is not None and impl.output_refs is not None:
-                        impl._buffers = None
-            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()      # the graph gets its own pool; hand cached blocks back first
             g = torch.cuda.CUDAGraph()
             try:
-                with torch.cuda.graph(g):
+                from ..native import total_launches
+
+                n0 = total_launches()
+                with torch.cuda.graph(g, capture_error_mode="thread_local"):
                     self._run(rec)
                     rec.static_outputs = [list(i._buffers) if i is not None else None for i in rec.out_impls]
-            except Exception:
+            except Exception as e:
+                import warnings
+
+                warnings.warn(f"CUDA graph capture failed ({type(e).__name__}: {e}); replaying without a graph")
                 self._stats.fallbacks += 1
                 self.use_cuda_graph = False
                 for ph in rec.placeholders:
                     ph._buffers = None
                 return self._replay(rec, tensors)
             rec.cuda_graph = g
+            self._stats.cuda_graphs += 1
+            self._stats.launches_per_graph = total_launches() - n0
+            rec.static_ptrs = {b.data_ptr() for bufs in rec.static_inputs for b in bufs}
         for bufs, t in zip(rec.static_inputs, tensors):
             for dst, src in zip(bufs, t._impl._buffers):
                 if dst.data_ptr() != src.data_ptr():
@@ -314,17 +341,55 @@ class CompiledFunction:
             if impl is None:
                 outs.append(static)
             else:
-                new = TensorImpl([b.clone() for b in bufs], shape=impl._shape, dtype=impl.dtype, device=impl.device,
+                # results that live in a donated input's buffer are handed back as they are
+                res = [b if b.data_ptr() in rec.static_ptrs else b.clone() for b in bufs]
+                new = TensorImpl(res, shape=impl._shape, dtype=impl.dtype, device=impl.device,
                                  sharding=impl.sharding, batch_dims=impl.batch_dims)
                 outs.append(Tensor(impl=new))
         return pytree.tree_unflatten(rec.out_treedef, outs)
 
 
+def _optimizer_steps_last(steps: list, nodes: list[OpNode]) -> list:
+    """Move in-place-capable update ops whose results feed no other node to the end of the
+    schedule, so that they are the last readers of the parameters they overwrite."""
+    consumed = set()
+    for n in nodes:
+        for a in n.input_impls():
+            consumed.add(id(a))
+    head, tail = [], []
+    for st in steps:
+        kind, idxs = st
+        n = nodes[idxs[0]]
+        if kind == "op" and getattr(n.op, "inplace_inputs", None) and \
+                not any(o is not None and id(o) in consumed for o in n.outputs()):
+            tail.append(st)
+        else:
+            head.append(st)
+    return head + tail
+
+
+def _mark_inplace_updates(rec: _Recorded, last_use: dict[int, int]) -> None:
+    donated = {id(ph) for ph, d in zip(rec.placeholders, rec.donated) if d}
+    for si, (kind, idxs) in enumerate(rec.steps):
+        if kind != "op":
+            continue
+        n = rec.nodes[idxs[0]]
+        which = getattr(n.op, "inplace_inputs", None)
+        if not which:
+            continue
+        ins = n.input_impls()
+        targets = [ins[i] for i in which if i < len(ins)]
+        # in place only when every overwritten input was donated and nothing reads it later
+        if targets and all(id(t) in donated and last_use.get(id(t), si) <= si for t in targets):
+            n.kwargs = dict(n.kwargs, inplace=True)
+
+
 def compile(fn: Callable | None = None, *, fullgraph: bool = False, max_cache_size: int = 64,
-            dynamic_dims: dict[int, dict[int, str]] | None = None, cuda_graph: bool = False):
+            dynamic_dims: dict[int, dict[int, str]] | None = None, cuda_graph: bool = False,
+            donate_argnums: tuple[int, ...] | int = ()):
     """Decorator / wrapper: ``@compile`` or ``compile(fn, dynamic_dims={0: {0: "batch"}})``."""
     if fn is None:
         return lambda f: CompiledFunction(f, fullgraph=fullgraph, max_cache_size=max_cache_size,
-                                          dynamic_dims=dynamic_dims, cuda_graph=cuda_graph)
+                                          dynamic_dims=dynamic_dims, cuda_graph=cuda_graph, donate_argnums=donate_argnums)
     return CompiledFunction(fn, fullgraph=fullgraph, max_cache_size=max_cache_size, dynamic_dims=dynamic_dims,
-                            cuda_graph=cuda_graph)
+                            cuda_graph=cuda_graph, donate_argnums=donate_argnums)

@@ -151,6 +151,9 @@ def main():
         w1 = torch.randn(2048, 8192 // world, device=dev, dtype=torch.bfloat16)
         full_x = torch.empty(M, 2048, device=dev, dtype=torch.bfloat16)
 
+        y_c = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+        o_c = torch.empty(M // world, N, device=dev, dtype=torch.bfloat16)
+
         def unfused_rs():
             y = gemm_bf16(a, b)
             o = torch.empty(M // world, N, device=dev, dtype=torch.bfloat16)
@@ -166,7 +169,10 @@ def main():
                          ("rs_fused", lambda: symm.gemm_reduce_scatter(a, b, mesh, ("x",), M // world)),
                          ("rs_gemm_then_nccl", unfused_rs),
                          ("ag_fused", lambda: symm.all_gather_gemm(xs, w1, mesh, ("x",), M // world)),
-                         ("ag_nccl_then_gemm", unfused_ag), ("ag_gemm_only", lambda: gemm_bf16(full_x, w1))):
+                         ("ag_nccl_then_gemm", unfused_ag), ("ag_gemm_only", lambda: gemm_bf16(full_x, w1)),
+                         ("nccl_ar_only", lambda: dist.all_reduce(y_c)),
+                         ("nccl_rs_only", lambda: dist.reduce_scatter_tensor(o_c, y_c)),
+                         ("nccl_ag_only", lambda: dist.all_gather_into_tensor(full_x, xs))):
             for _ in range(3):
                 fn()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
