@@ -249,6 +249,18 @@ def main() -> None:
         e2e_ms_total = float(t2.item())
         native.check_status()
 
+        if os.environ.get("NABLA_B200_PROFILE_OPS") and not train_step.stats.cuda_graphs:
+            # per-op device time of one more step (event pair around every replayed op), rank 0 -> stderr
+            train_step.profile_ops = True
+            tok, tgt = to_device(host[0])
+            loss, params, state = train_step(params, state, tok, tgt)
+            train_step.profile_ops = False
+            if rank == 0:
+                tot = sum(v[1] for v in train_step.op_profile.values())
+                print(f"op profile (rank 0, {tot:.1f} ms summed):", file=sys.stderr)
+                for k, v in sorted(train_step.op_profile.items(), key=lambda kv: -kv[1][1])[:40]:
+                    print(f"  {v[1]:9.2f} ms {100 * v[1] / tot:5.1f}%  x{v[0]:4d}  {k}", file=sys.stderr)
+
     tokens_per_step = global_batch * seq
     value = tokens_per_step * args.steps / (ms_total / 1e3)
     e2e_value = tokens_per_step * args.steps / (e2e_ms_total / 1e3)

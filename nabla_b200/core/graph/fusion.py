@@ -93,6 +93,19 @@ def build_plan(nodes: list[OpNode], targets: list[TensorImpl]):
                 elif not used[j] and m.op.name == "reduce_scatter" and _is_scatter_of_partials(m, o):
                     chain = [i, j]
                     kind = "gemm_reduce_scatter"
+                    # + bias row and + residual fold into the pass that sums the partial row blocks
+                    cur = sole_output(m)
+                    for want in ("bias", "residual"):
+                        if cur is None or id(cur) in target_ids or len(cons.get(id(cur), [])) != 1 or cur.batch_dims:
+                            break
+                        k = cons[id(cur)][0]
+                        a = nodes[k]
+                        if used[k] or a.op.name != "add" or _rs_addend(a, cur) != want:
+                            if want == "bias":
+                                continue          # no bias: the next add may still be the residual
+                            break
+                        chain.append(k)
+                        cur = sole_output(a)
         if chain is None and n.op.name == "all_gather" and _is_row_gather(n):
             o = sole_output(n)
             users = cons.get(id(o), []) if o is not None else []
@@ -161,17 +174,45 @@ def _is_sum_over_partials(m: OpNode, mm_out: TensorImpl) -> bool:
     if m.kwargs.get("reduce_op", "sum") != "sum" or not axes:
         return False
     sp = mm_out.sharding
+    if _group_size(sp.mesh, axes) <= 1:
+        return False           # a group of one rank: the all-reduce is the identity, keep the plain GEMM
     # a plain sum of the partial products: no dim of the operand is split over the reduced axes
     return axes <= set(sp.partial_sum_axes) and not any(set(d.axes) & axes for d in sp.dim_specs)
+
+
+def _group_size(mesh, axes) -> int:
+    n = 1
+    for a in axes:
+        n *= mesh.get_axis_size(a)
+    return n
 
 
 def _is_scatter_of_partials(m: OpNode, mm_out: TensorImpl) -> bool:
     axes = set(m.kwargs.get("scatter_axes", ()))
     dim = m.kwargs.get("dim")
     sp = mm_out.sharding
-    if not axes or dim is None or dim >= len(mm_out._shape) - 1:
+    if not axes or dim is None or dim >= len(mm_out._shape) - 1 or _group_size(sp.mesh, axes) <= 1:
         return False
     return axes <= set(sp.partial_sum_axes) and not any(set(d.axes) & axes for d in sp.dim_specs)
+
+
+def _rs_addend(add: OpNode, x: TensorImpl) -> str | None:
+    """What ``add`` adds to the reduce-scatter result ``x``: 'bias' (one row, no split dims),
+    'residual' (same shape and layout) or None."""
+    ins = add.input_impls()
+    if len(ins) != 2:
+        return None
+    other = ins[1] if ins[0] is x else ins[0] if ins[1] is x else None
+    if other is None or other.batch_dims or other.dtype is not x.dtype:
+        return None
+    split = [tuple(d.axes) for d in other.sharding.dim_specs] if other.sharding is not None else []
+    if len(other._shape) >= 1 and other._shape[-1] == x._shape[-1] and all(d == 1 for d in other._shape[:-1]) \
+            and not any(split):
+        return "bias"
+    if tuple(other._shape) == tuple(x._shape) and other.sharding is not None and x.sharding is not None and \
+            split == [tuple(d.axes) for d in x.sharding.dim_specs] and not other.sharding.partial_sum_axes:
+        return "residual"
+    return None
 
 
 def _is_row_gather(n: OpNode) -> bool:
@@ -183,6 +224,8 @@ def _is_row_gather(n: OpNode) -> bool:
     if x.sharding is None or not x.sharding.mesh.is_distributed or dim is None or dim >= len(x._shape) - 1:
         return False
     if not x.sharding.dim_specs[dim].axes or x.sharding.partial_sum_axes or x.batch_dims:
+        return False
+    if _group_size(x.sharding.mesh, x.sharding.dim_specs[dim].axes) <= 1:
         return False
     from ...types import DType
 
@@ -265,8 +308,17 @@ def run_fused(kind: str, group: list[OpNode], keep_graph: bool = False) -> None:
     if kind == "gemm_reduce_scatter":
         from ...parallel import backend, symm
 
-        mm, rs = group
+        mm, rs = group[0], group[1]
         a, b = [x._buffers[0] for x in mm.input_impls()]
+        bias = resid = None
+        cur = rs.outputs()[0]
+        for add in group[2:]:
+            other = [x for x in add.input_impls() if x is not cur][0]
+            if _rs_addend(add, cur) == "bias":
+                bias = other._buffers[0]
+            else:
+                resid = other._buffers[0]
+            cur = add.outputs()[0]
         mesh = rs.input_impls()[0].sharding.mesh
         axes = [x for x in mesh.axis_names if x in rs.kwargs["scatter_axes"]]
         dim = rs.kwargs["dim"]
@@ -283,13 +335,13 @@ def run_fused(kind: str, group: list[OpNode], keep_graph: bool = False) -> None:
         cs = (lead[dim] // world) * inner if lead[dim] % world == 0 else 0
         if (symm.gemm_all_reduce_supported(a, b) and symm.chunked_supported(m_total, cs, world)
                 and os.environ.get("NABLA_B200_FUSE_RS", "1") != "0"):
-            y = symm.gemm_reduce_scatter(a, b, mesh, axes, cs)
+            y = symm.gemm_reduce_scatter(a, b, mesh, axes, cs, bias=bias, residual=resid)
             out = y.reshape(*lead[:dim], lead[dim] // world, *lead[dim + 1:], b.shape[-1])
             backend.stats["fused_gemm_reduce_scatter"] = backend.stats.get("fused_gemm_reduce_scatter", 0) + 1
-            _store(rs, [[out]], keep_graph)
+            _store(group[-1], [[out]], keep_graph)
         else:
-            _plain(mm, keep_graph)
-            _plain(rs, keep_graph)
+            for n_ in group:
+                _plain(n_, keep_graph)
         return
     if kind == "all_gather_gemm":
         from ...parallel import backend, symm

@@ -54,7 +54,11 @@ struct SmemLayout {
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int BIAS_BYTES = BN * 4;
   static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
-  static constexpr int TOTAL = RING_BYTES + BIAS_BYTES + BAR_BYTES + 1024;  // + alignment slack
+  // per epilogue warp: 32 rows x 64 bf16 (+16 B pad) used to turn row-per-lane accumulators into
+  // 128-byte row segments before they are stored to a peer (reduce-scatter push)
+  static constexpr int OUT_ROW_BYTES = 64 * 2 + 16;
+  static constexpr int OUT_STAGE_BYTES = 4 * 32 * OUT_ROW_BYTES;
+  static constexpr int TOTAL = RING_BYTES + BIAS_BYTES + BAR_BYTES + 112 + OUT_STAGE_BYTES + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& b, int& m, int& n) {
@@ -133,7 +137,8 @@ __device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
 // kernel can dedicate some CTAs to communication. Returns false if the CTA left early.
 template <int BN, int MODE>
 __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensorMap* tmBp, const GemmArgs& args,
-                                         const CommArgs& comm, const int cta, const int nctas) {
+                                         const CommArgs& comm, const int cta, const int nctas,
+                                         const CUtensorMap* tmAownp = nullptr) {
   const CUtensorMap& tmA = *tmAp;
   const CUtensorMap& tmB = *tmBp;
   using L = SmemLayout<BN>;
@@ -147,6 +152,7 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
   uint64_t* tmem_full = empty_bar + STAGES;   // [2]
   uint64_t* tmem_empty = tmem_full + 2;       // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint8_t* out_stage = smem + ((L::RING_BYTES + L::BIAS_BYTES + L::BAR_BYTES + 127) & ~127);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -197,7 +203,19 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
         tile_coords(t, num_m, num_n, b, tm, tn);
         tm = remap_m<MODE>(tm, comm);
         const int m0 = tm * BLOCK_M, n0 = tn * BN;
+        // MODE_AG: this rank's own rows are read from its shard directly (no copy to wait for)
+        const CUtensorMap* tmAuse = tmAp;
+        int ma0 = m0;
+        bool own = false;
         if (MODE == MODE_AG) {
+          const int blk = tm / comm.mpc;
+          own = (blk % comm.world) == comm.rank;
+          if (own) {
+            tmAuse = tmAownp;
+            ma0 = ((blk / comm.world) * comm.mpc + (tm - blk * comm.mpc)) * BLOCK_M;
+          }
+        }
+        if (MODE == MODE_AG && !own) {
           // rows m0 .. m0+127 of the gathered A must have been copied in by a copy CTA
           const unsigned* f = reinterpret_cast<const unsigned*>(reinterpret_cast<char*>(comm.bufs[comm.rank]) +
                                                                 comm.flag_off) + AG_FLAG_BASE + tm;
@@ -224,7 +242,7 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
           mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
           const int k0 = kb * BLOCK_K;
           if (!args.a_mn) {
-            tma_load_3d(sA, &tmA, &full_bar[stage], k0, m0, b);
+            tma_load_3d(sA, tmAuse, &full_bar[stage], k0, ma0, b);
           } else {
 #pragma unroll
             for (int j = 0; j < BLOCK_M / 64; ++j)
@@ -322,7 +340,15 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
       const int row = m0 + wq * 32 + lane;
       const bool row_ok = row < args.M;
       const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(wq * 32) << 16);
-      const long long out_off = static_cast<long long>(b) * args.stride_c + static_cast<long long>(row) * args.ldc;
+      long long out_off = static_cast<long long>(b) * args.stride_c + static_cast<long long>(row) * args.ldc;
+      void* out_ptr = args.out;
+      if (MODE == MODE_RS) {
+        // push: the tile goes straight into the memory of the rank that owns these rows, into
+        // the slot of this rank ([world][M / world][N] at data_off of the owner's workspace)
+        const int q = tm_order / comm.world, p = tm_order - q * comm.world;
+        out_ptr = reinterpret_cast<char*>(comm.bufs[p]) + comm.data_off;
+        out_off = (static_cast<long long>(comm.rank) * (args.M / comm.world) + q * BLOCK_M + wq * 32 + lane) * args.N;
+      }
       const long long aux_off =
           static_cast<long long>(b) * args.stride_aux + static_cast<long long>(row) * args.ld_aux;
 #pragma unroll 1
@@ -405,7 +431,42 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
           }
         }
         // ---- store
-        if (row_ok) {
+        if (MODE == MODE_RS) {
+          // to a peer: stage two 32-column chunks per warp in shared memory, then write whole
+          // 128-byte row segments (4 rows per warp instruction) instead of 16-byte pieces of
+          // 32 different rows, which NVLink would carry as 32 small packets
+          uint8_t* mine = out_stage + wq * (32 * L::OUT_ROW_BYTES);
+          uint8_t* rowp = mine + lane * L::OUT_ROW_BYTES + (c & 1) * 64;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 pk;
+            uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(f[q * 8 + 2 * j], f[q * 8 + 2 * j + 1]);
+              pw[j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(rowp + q * 16) = pk;
+          }
+          const bool last_chunk = (c == BN / 32 - 1) || (nb0 + 32 >= args.N);
+          if ((c & 1) || last_chunk) {
+            __syncwarp();
+            const int col0 = n0 + (c & ~1) * 32;               // first column held in the stage
+            const int sub = lane >> 3, piece = lane & 7;       // 4 rows x 8 pieces of 16 bytes
+            __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(out_ptr) + (out_off - (long long)lane * args.N);
+#pragma unroll
+            for (int it8 = 0; it8 < 8; ++it8) {
+              const int r = it8 * 4 + sub;
+              const int col = col0 + piece * 8;
+              const bool have = ((c & 1) || piece < 4) && col < args.N;
+              if (have) {
+                const uint4 v = *reinterpret_cast<const uint4*>(mine + r * L::OUT_ROW_BYTES + piece * 16);
+                *reinterpret_cast<uint4*>(base + (long long)r * args.N + col) = v;
+              }
+            }
+            __syncwarp();
+          }
+        } else if (row_ok) {
           if (args.out_fp32) {
             float* op = reinterpret_cast<float*>(args.out) + out_off + nb0;
             if (full) {
@@ -423,7 +484,7 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
                 if (nb0 + j < args.N) op[j] = args.accumulate ? op[j] + f[j] : f[j];
             }
           } else {
-            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(args.out) + out_off + nb0;
+            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(out_ptr) + out_off + nb0;
             if (full) {
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
@@ -456,7 +517,7 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
       }
       tc_fence_before();
       mbar_arrive(&tmem_empty[buf]);
-      if (MODE == MODE_AR || MODE == MODE_RS) {
+      if (MODE == MODE_AR) {
         // the tile is in this rank's workspace: make it visible system-wide, then count it on
         // the rank that reduces it (tile (tm_order, tn) belongs to rank tm_order % world)
         __threadfence_system();
@@ -688,6 +749,14 @@ __device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint3
                : "memory");
 }
 
+// Copy order of the 128-row blocks: the peers' rows first (ring order, as the GEMM will ask for
+// them), this rank's own rows last (the GEMM reads those from the shard; the copy only completes
+// the gathered matrix for later use).
+__device__ __forceinline__ int ag_unit(int u, int num_m, const CommArgs& c) {
+  u += c.per;
+  return u >= num_m ? u - num_m : u;
+}
+
 template <int BN>
 __device__ __forceinline__ void gather_jobs(const GemmArgs& args, const CommArgs& comm, int cidx, int ncomm) {
   extern __shared__ uint8_t smem_raw[];
@@ -717,7 +786,7 @@ __device__ __forceinline__ void gather_jobs(const GemmArgs& args, const CommArgs
   // piece i -> (unit, piece in unit) -> source / destination
   auto issue_load = [&](int i) -> bool {
     const int ui = i / ppu, pi = i - ui * ppu;
-    const int tm = remap_m<MODE_AG>(cidx + ui * ncomm, comm);
+    const int tm = remap_m<MODE_AG>(ag_unit(cidx + ui * ncomm, num_m, comm), comm);
     const int blk = tm / comm.mpc;                     // row chunk index in the gathered matrix
     const int p = blk % comm.world, g = blk / comm.world, j = tm - blk * comm.mpc;
     if (!((ready_mask >> p) & 1u)) {
@@ -734,6 +803,21 @@ __device__ __forceinline__ void gather_jobs(const GemmArgs& args, const CommArgs
     bulk_g2s(ring + st * AG_PIECE, src, bytes, &bars[st]);
     return true;
   };
+  auto publish = [&](int i) {   // piece i has landed in a_full; raise its block's flag if it was the last piece
+    const int ui = i / ppu, pi = i - ui * ppu;
+    if (pi != ppu - 1) return;
+    const int tm = remap_m<MODE_AG>(ag_unit(cidx + ui * ncomm, num_m, comm), comm);
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __threadfence();
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(reinterpret_cast<unsigned*>(local + comm.flag_off) +
+                                                              AG_FLAG_BASE + tm),
+                 "r"(comm.epoch)
+                 : "memory");
+  };
+  // Ring of AG_STAGES pieces. Stores trail loads by AG_LAG groups: after committing store i only
+  // stores up to i - AG_LAG are awaited, so loads and stores of several pieces are in flight and
+  // neither the peer's latency nor the store's is paid per piece.
+  constexpr int AG_LAG = 2;
   int issued = 0;
   for (; issued < total && issued < AG_STAGES && ok; ++issued) ok = issue_load(issued);
   for (int i = 0; i < total && ok; ++i) {
@@ -741,43 +825,37 @@ __device__ __forceinline__ void gather_jobs(const GemmArgs& args, const CommArgs
     const uint32_t phase = (i / AG_STAGES) & 1;
     if (!mbar_wait(&bars[st], phase)) { ok = false; break; }
     const int ui = i / ppu, pi = i - ui * ppu;
-    const int tm = remap_m<MODE_AG>(cidx + ui * ncomm, comm);
+    const int tm = remap_m<MODE_AG>(ag_unit(cidx + ui * ncomm, num_m, comm), comm);
     const long long off = (long long)pi * AG_PIECE;
     const uint32_t bytes = (uint32_t)min((long long)AG_PIECE, comm.unit_bytes - off);
     bulk_s2g(comm.a_full + (long long)tm * comm.unit_bytes + off, ring + st * AG_PIECE, bytes);
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-    if (pi == ppu - 1) {
-      // the block is complete once its stores have landed: publish it to the GEMM producers
-      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-      asm volatile("fence.proxy.async;" ::: "memory");
-      __threadfence();
-      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(reinterpret_cast<unsigned*>(local + comm.flag_off) +
-                                                                AG_FLAG_BASE + tm),
-                   "r"(comm.epoch)
-                   : "memory");
-    }
-    if (issued < total) {
-      // the stage that piece `issued` will use was read by store i - (AG_STAGES - 1) ... wait
-      // until all stores issued so far have finished READING shared memory, then refill
-      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-      ok = issue_load(issued);
-      ++issued;
+    if (i >= AG_LAG) {
+      asm volatile("cp.async.bulk.wait_group %0;" ::"n"(AG_LAG) : "memory");   // stores <= i - AG_LAG are complete
+      publish(i - AG_LAG);
+      if (issued < total) {          // piece `issued` reuses the stage of piece i - AG_LAG (AG_STAGES apart)
+        ok = issue_load(issued);
+        ++issued;
+      }
     }
   }
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  if (ok)
+    for (int i = max(0, total - AG_LAG); i < total; ++i) publish(i);
   if (!ok) atomicExch(args.status, NB_ERR_TIMEOUT_PEER);
 }
 
 template <int BN, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const GemmArgs args, const CommArgs comm_in, const int n_gemm) {
+                  const __grid_constant__ CUtensorMap tmAown, const GemmArgs args, const CommArgs comm_in,
+                  const int n_gemm) {
   CommArgs comm = comm_in;
   comm.epoch += *reinterpret_cast<const volatile unsigned*>(comm_in.ctr + 1);
   comm.done_target += *reinterpret_cast<const volatile unsigned*>(comm_in.ctr + 2);
   const bool is_gemm = (int)blockIdx.x < n_gemm;
   if (is_gemm) {
-    if (!gemm_cta<BN, MODE>(&tmA, &tmB, args, comm, blockIdx.x, n_gemm)) return;
+    if (!gemm_cta<BN, MODE>(&tmA, &tmB, args, comm, blockIdx.x, n_gemm, &tmAown)) return;
   } else {
     __shared__ int s_abort2;
     if (threadIdx.x == 0) s_abort2 = *reinterpret_cast<volatile int*>(args.status);
@@ -787,9 +865,11 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   if (MODE == MODE_AG) {
     if (is_gemm) return;                      // GEMM CTAs touch no peer memory
     gather_jobs<BN>(args, comm, (int)blockIdx.x - n_gemm, (int)gridDim.x - n_gemm);
-  } else {
+  } else if (MODE == MODE_AR) {
     reduce_jobs<BN, MODE>(args, comm);
   }
+  // MODE_RS: the tiles were pushed by the epilogue; once every CTA of every rank has counted,
+  // all partial sums of this rank's rows are in its workspace and rs_reduce_kernel adds them up
   closing_count(args, comm);
 }
 
@@ -920,7 +1000,10 @@ extern "C" int nb_gemm_bf16(const void* A, const void* B, void* C, const void* b
 //   mc            multicast base of the workspace or null (plain peer loads/stores)
 //   data_off      byte offset in the workspace of C (modes 1, 2) or of the staged A shard (mode 3)
 //   out           mode 2: this rank's rows [M/world][N];  mode 3: C [M][N] (ldc = N);  mode 1: unused
-//   a_full        mode 3: the gathered A [M][K] (dense, regular device memory); A is then ignored
+//   bias, aux_out mode 2: optional bias[N] (bf16) and residual [M/world][N] added while the partial
+//                 sums are folded;  mode 3: GEMM epilogue bias and stored pre-activation
+//   a_full        mode 3: the gathered A [M][K] (dense, regular device memory); A = this rank's own rows
+//                 [M / world][K], dense (the same data that was staged at data_off for the peers)
 //   chunk_rows    modes 2, 3: rows per contiguous chunk of a rank (multiple of 128, M % (world*chunk_rows) == 0)
 //   ctr           device counters of the workspace (unsigned[4], zero at creation): the kernel
 //                 takes its all-gather epoch and done target relative to them and a one-thread
@@ -936,14 +1019,64 @@ extern "C" int nb_gemm_fused_grid() {
   return nb::g_num_sms;
 }
 
+// Sum of the `world` partial row blocks that the peers pushed into this rank's workspace
+// ([world][rows][N] bf16), plus optional bias[N] and residual[rows][N]: out = sum_s part[s] + bias + res.
+__global__ void __launch_bounds__(256) rs_reduce_kernel(const __nv_bfloat16* __restrict__ parts, int world,
+                                                        long long n_vec, int n_cols_vec, long long slot_vec,
+                                                        const __nv_bfloat16* __restrict__ bias,
+                                                        const __nv_bfloat16* __restrict__ residual,
+                                                        __nv_bfloat16* __restrict__ out) {
+  const uint4* pv = reinterpret_cast<const uint4*>(parts);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int s = 0; s < world; ++s) {
+      const uint4 v = pv[s * slot_vec + i];
+      const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += __uint_as_float(w[j] << 16);
+        acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+      }
+    }
+    if (bias != nullptr) {
+      const uint4 v = reinterpret_cast<const uint4*>(bias)[i % n_cols_vec];
+      const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += __uint_as_float(w[j] << 16);
+        acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+      }
+    }
+    if (residual != nullptr) {
+      const uint4 v = reinterpret_cast<const uint4*>(residual)[i];
+      const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += __uint_as_float(w[j] << 16);
+        acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+      }
+    }
+    uint4 o;
+    unsigned* ow = reinterpret_cast<unsigned*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      ow[j] = *reinterpret_cast<unsigned*>(&h);
+    }
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
 __global__ void bump_fused_kernel(unsigned* ctr, unsigned add_epoch, unsigned add_done) {
   ctr[1] += add_epoch;
   ctr[2] += add_done;
 }
 
 template <int MODE>
-static int launch_fused(const CUtensorMap& ta, const CUtensorMap& tb, const nb::GemmArgs& g, const nb::CommArgs& c,
-                        int grid, int n_gemm, cudaStream_t s) {
+static int launch_fused(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ta_own, const nb::GemmArgs& g,
+                        const nb::CommArgs& c, int grid, int n_gemm, cudaStream_t s) {
   using namespace nb;
   constexpr int BN = 256;
   static bool configured = false;
@@ -953,7 +1086,7 @@ static int launch_fused(const CUtensorMap& ta, const CUtensorMap& tb, const nb::
       return -2;
     configured = true;
   }
-  gemm_fused_kernel<BN, MODE><<<grid, NUM_THREADS, SmemLayout<BN>::TOTAL, s>>>(ta, tb, g, c, n_gemm);
+  gemm_fused_kernel<BN, MODE><<<grid, NUM_THREADS, SmemLayout<BN>::TOTAL, s>>>(ta, tb, ta_own, g, c, n_gemm);
   bump_fused_kernel<<<1, 1, 0, s>>>(const_cast<unsigned*>(c.ctr), MODE == nb::MODE_AG ? 1u : 0u, c.done_target);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
@@ -984,6 +1117,7 @@ extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* 
   const int grid = nb_gemm_fused_grid();      // every rank must launch the same grid
   if (n_comm_ctas < 1) n_comm_ctas = 1;
   if (n_comm_ctas > grid / 2) n_comm_ctas = grid / 2;
+  if (mode == MODE_RS) n_comm_ctas = 0;        // the epilogue pushes the tiles; no communication CTAs
   const int n_gemm = grid - n_comm_ctas;
   CUtensorMap ta, tb;
   int r;
@@ -1020,7 +1154,23 @@ extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* 
   c.unit_bytes = (long long)BLOCK_M * K * 2;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (mode != MODE_AG && cudaMemsetAsync(ticket, 0, sizeof(int), s) != cudaSuccess) return -4;
-  if (mode == MODE_AR) return launch_fused<MODE_AR>(ta, tb, g, c, grid, n_gemm, s);
-  if (mode == MODE_RS) return launch_fused<MODE_RS>(ta, tb, g, c, grid, n_gemm, s);
-  return launch_fused<MODE_AG>(ta, tb, g, c, grid, n_gemm, s);
+  if (mode == MODE_AR) return launch_fused<MODE_AR>(ta, tb, ta, g, c, grid, n_gemm, s);
+  if (mode == MODE_RS) {
+    r = launch_fused<MODE_RS>(ta, tb, ta, g, c, grid, n_gemm, s);
+    if (r) return r;
+    const long long rows = M / world;
+    const long long n_vec = rows * N / 8;
+    const int blocks = (int)((n_vec + 255) / 256 < 148 * 8 ? (n_vec + 255) / 256 : 148 * 8);
+    rs_reduce_kernel<<<blocks, 256, 0, s>>>(
+        reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<char*>(ws_local) + data_off), world, n_vec, N / 8, n_vec,
+        reinterpret_cast<const __nv_bfloat16*>(bias), reinterpret_cast<const __nv_bfloat16*>(aux_out),
+        reinterpret_cast<__nv_bfloat16*>(out));
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  }
+  // mode 3: A = this rank's own rows (dense [M / world][K]); the GEMM reads them in place
+  CUtensorMap ta_own;
+  if ((reinterpret_cast<uintptr_t>(A) & 15)) return -11;
+  r = make_map(&ta_own, A, K, M / world, 1, K, 0, BLOCK_M);
+  if (r) return r;
+  return launch_fused<MODE_AG>(ta, tb, ta_own, g, c, grid, n_gemm, s);
 }

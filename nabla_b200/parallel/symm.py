@@ -194,7 +194,7 @@ def _fused_fn():
 def _fused_shapes_ok(m: int, n: int, k: int, nbytes_ws: int) -> bool:
     if n % 8 or k % 8 or m <= 0 or n <= 0 or k <= 0:
         return False
-    return nbytes_ws + 4096 <= DEFAULT_BYTES - 65536
+    return nbytes_ws + 4096 <= (DEFAULT_BYTES - 65536) // 2       # the data region is used in two halves
 
 
 def gemm_all_reduce_supported(a: torch.Tensor, b: torch.Tensor) -> bool:
@@ -221,19 +221,31 @@ def _fused_state(ws, device):
 
 def _launch_fused(mode, ws, a, b, out, bias, aux_out, a_full, M, N, K, lda, ldb, a_mn, b_mn, epi, aux, gelu_tanh,
                   chunk_rows, n_comm):
+    """Returns the byte offset (inside the workspace) of the region the call used."""
     global launch_count
     fn, grid_fn = _fused_fn()
     lib = _L()
     grid = grid_fn()
     n_comm = max(1, min(n_comm, grid // 2))
+    data_off = ws.flag_bytes
+    if mode != MODE_AG:
+        # calls that write into the peers' workspaces alternate between two halves: the local
+        # fold of call n (which runs after the kernel's closing barrier) may still be reading its
+        # half when a faster peer already pushes tiles of call n + 1
+        half = ((ws.nbytes - ws.flag_bytes) // 2) & ~1023
+        if M * N * 2 > half:
+            raise RuntimeError(f"fused GEMM+collective output ({M}x{N}) does not fit half of the workspace")
+        ws.parity = 1 - getattr(ws, "parity", 1)
+        data_off += ws.parity * half
     p = lambda t: c_vp(0 if t is None else t.data_ptr())
     rc = fn(mode, p(a), p(b), p(out), p(bias), p(aux_out), p(a_full), ws.buf.data_ptr(), ws.ptrs_dev, ws.mc_ptr,
-            ws.flag_bytes, lib.nb_comm_tile_flag_offset(), lib.nb_comm_done_offset(), M, N, K, lda, ldb, a_mn, b_mn,
+            data_off, lib.nb_comm_tile_flag_offset(), lib.nb_comm_done_offset(), M, N, K, lda, ldb, a_mn, b_mn,
             1 if (bias is not None and bias.dtype == torch.float32) else 0, epi, aux, int(gelu_tanh), ws.rank, ws.world,
             chunk_rows, ws.ctr.data_ptr(), n_comm, ws.ticket.data_ptr(), _status().data_ptr(), _stream())
     if rc != 0:
         raise RuntimeError(f"nb_gemm_fused_bf16(mode={mode}) failed with code {rc} for M={M} N={N} K={K}")
     launch_count += 1
+    return data_off
 
 
 def _operands(a: torch.Tensor, b: torch.Tensor):
@@ -256,26 +268,35 @@ def gemm_all_reduce(a: torch.Tensor, b: torch.Tensor, mesh, axes) -> torch.Tenso
     ws = _fused_state(workspace(mesh, axes), a.device)
     a3, b3, lda, ldb, a_mn, b_mn = _operands(a, b)
     M, K, N = a3.shape[1], a3.shape[2], b.shape[1]
-    _launch_fused(MODE_AR, ws, a3, b3, None, None, None, None, M, N, K, lda, ldb, a_mn, b_mn, 0, 0, False, 0,
-                  FUSED_COMM_CTAS)
-    return ws.data[: M * N * 2].view(torch.bfloat16).view(M, N)
+    off = _launch_fused(MODE_AR, ws, a3, b3, None, None, None, None, M, N, K, lda, ldb, a_mn, b_mn, 0, 0, False, 0,
+                        FUSED_COMM_CTAS)
+    return ws.buf[off: off + M * N * 2].view(torch.bfloat16).view(M, N)
 
 
-def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_rows: int) -> torch.Tensor:
-    """Rows of ``sum_r a_r @ b_r`` that belong to this rank (row chunks of ``chunk_rows`` dealt
-    round-robin to the ranks), in one kernel: same tile flow as :func:`gemm_all_reduce`, but each
-    tile is summed only by its owner, straight into the returned tensor (M / world, N)."""
+def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_rows: int,
+                        bias: torch.Tensor | None = None, residual: torch.Tensor | None = None) -> torch.Tensor:
+    """Rows of ``sum_r a_r @ b_r`` (+ ``bias`` + ``residual``) that belong to this rank (row
+    chunks of ``chunk_rows`` dealt round-robin to the ranks). The GEMM's epilogue stores every
+    output tile straight into the memory of the rank that owns its rows (peer stores over NVLink,
+    overlapped with the next tile's MMAs; no SM is set aside for communication); after the
+    launch's closing barrier a local pass folds the ``world`` partial row blocks, the bias and
+    the residual into the returned (M / world, N) tensor."""
     ws = _fused_state(workspace(mesh, axes), a.device)
     a3, b3, lda, ldb, a_mn, b_mn = _operands(a, b)
     M, K, N = a3.shape[1], a3.shape[2], b.shape[1]
     out = torch.empty((M // ws.world, N), dtype=torch.bfloat16, device=a.device)
-    _launch_fused(MODE_RS, ws, a3, b3, out, None, None, None, M, N, K, lda, ldb, a_mn, b_mn, 0, 0, False, chunk_rows,
-                  FUSED_COMM_CTAS)
+    if bias is not None:
+        bias = bias.reshape(-1).to(torch.bfloat16).contiguous()
+    if residual is not None:
+        residual = residual.reshape(M // ws.world, N).contiguous()
+    _launch_fused(MODE_RS, ws, a3, b3, out, bias, residual, None, M, N, K, lda, ldb, a_mn, b_mn, 0, 0, False,
+                  chunk_rows, 1)
     return out
 
 
 def all_gather_gemm(a_shard: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_rows: int, bias: torch.Tensor | None = None,
-                    epilogue: str = "none", gelu_tanh: bool = False, store_preact: bool = False):
+                    epilogue: str = "none", gelu_tanh: bool = False, store_preact: bool = False,
+                    comm_ctas: int | None = None):
     """``epilogue(gather(a) @ b + bias)`` in one kernel. ``a_shard`` is this rank's rows
     (M / world, K); copy CTAs of the launch pull the peers' rows over NVLink with bulk copies
     into the gathered matrix while the tensor-core CTAs already multiply the rows that are
@@ -298,8 +319,9 @@ def all_gather_gemm(a_shard: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_ro
         bias = bias.reshape(-1).contiguous()
         if epilogue == "none":
             epilogue = "bias"
-    _launch_fused(MODE_AG, ws, None, b3, out, bias, pre, a_full, M, N, K, K, ldb, 0, 1 if bkind == "row" else 0,
-                  _EPI[epilogue], 1 if store_preact else 0, gelu_tanh, chunk_rows, AG_COMM_CTAS)
+    x = x.contiguous()
+    _launch_fused(MODE_AG, ws, x, b3, out, bias, pre, a_full, M, N, K, K, ldb, 0, 1 if bkind == "row" else 0,
+                  _EPI[epilogue], 1 if store_preact else 0, gelu_tanh, chunk_rows, comm_ctas or AG_COMM_CTAS)
     return (a_full, out, pre) if store_preact else (a_full, out)
 
 

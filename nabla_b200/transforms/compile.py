@@ -111,6 +111,8 @@ class CompiledFunction:
         self.max_cache_size = int(max_cache_size)
         self.dynamic_dims = dynamic_dims or {}
         self.use_cuda_graph = bool(cuda_graph)
+        self.profile_ops = False        # set True to time every step of the replay with CUDA events
+        self.op_profile: dict[str, list] = {}
         self._cache: "OrderedDict[Any, dict[Any, _Recorded]]" = OrderedDict()
         self._stats = CompilationStats()
         self.__name__ = getattr(fn, "__name__", "compiled")
@@ -261,6 +263,8 @@ class CompiledFunction:
     def _run(self, rec: _Recorded) -> None:
         nodes = rec.nodes
         _STATS["nodes_executed"] += len(nodes)
+        if self.profile_ops and not torch.cuda.is_current_stream_capturing():
+            return self._run_profiled(rec)
         for si, (kind, idxs) in enumerate(rec.steps):
             if kind == "op":
                 n = nodes[idxs[0]]
@@ -273,6 +277,35 @@ class CompiledFunction:
                 fusion.run_fused(kind, [nodes[i] for i in idxs], keep_graph=True)
             for dead in rec.free_after[si]:
                 dead._buffers = None
+
+    def _run_profiled(self, rec: _Recorded) -> None:
+        """Same as ``_run`` with a CUDA event pair around every step; device time per step kind
+        accumulates in ``self.op_profile`` ({name: [calls, ms]}), read it after a synchronize."""
+        nodes = rec.nodes
+        marks = []
+        for si, (kind, idxs) in enumerate(rec.steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            if kind == "op":
+                n = nodes[idxs[0]]
+                outs = n.op.execute(n)
+                for i, ref in enumerate(n.out_refs):
+                    o = ref()
+                    if o is not None:
+                        o._buffers = outs[i]
+                name = n.op.name
+            else:
+                fusion.run_fused(kind, [nodes[i] for i in idxs], keep_graph=True)
+                name = kind + ":" + nodes[idxs[-1]].op.name
+            e1.record()
+            marks.append((name, e0, e1))
+            for dead in rec.free_after[si]:
+                dead._buffers = None
+        torch.cuda.synchronize()
+        for name, e0, e1 in marks:
+            ent = self.op_profile.setdefault(name, [0, 0.0])
+            ent[0] += 1
+            ent[1] += e0.elapsed_time(e1)
 
     def _collect(self, rec: _Recorded) -> Any:
         outs = []

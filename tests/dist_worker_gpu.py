@@ -113,10 +113,16 @@ def main():
             ref = a.float() @ b.float()
             dist.all_reduce(ref)
             mine = ref.view(-1, world, cs, N)[:, rank].reshape(-1, N)         # this rank's row chunks
-            for rep in range(2):
+            for rep in range(3):
                 y = symm.gemm_reduce_scatter(a, b, mesh, ("x",), cs)
                 torch.cuda.synchronize()
                 errs[f"rs_{M}x{N}x{K}_{rep}"] = ((y.float() - mine).abs().max() / ref.abs().max()).item()
+            rb = torch.randn(N, device=dev, dtype=torch.bfloat16)
+            rr = torch.randn(M // world, N, device=dev, dtype=torch.bfloat16)
+            y = symm.gemm_reduce_scatter(a, b, mesh, ("x",), cs, bias=rb, residual=rr)
+            torch.cuda.synchronize()
+            errs[f"rs_bias_res_{M}x{N}x{K}"] = ((y.float() - (mine + rb.float() + rr.float())).abs().max()
+                                                 / ref.abs().max()).item()
             # all-gather -> GEMM with bias + gelu epilogue and stored pre-activation
             torch.manual_seed(5)                                              # same weights on every rank
             w = torch.randn(K, N, device=dev, dtype=torch.bfloat16) * 0.05
@@ -186,6 +192,45 @@ def main():
             t = torch.tensor([e0.elapsed_time(e1) / 10], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             out[f"{name}_ms"] = t.item()
+        native.check_status()
+    elif mode == "fused_sweep":
+        # timing sweep of the fused kernels over the number of communication CTAs (bench shapes)
+        from nabla_b200.native.gemm import gemm_bf16
+        from nabla_b200.parallel import symm
+
+        mesh = nb.DeviceMesh("m", (world,), ("x",))
+        M = 16384 * world
+        a = torch.randn(M, 8192 // world, device=dev, dtype=torch.bfloat16)
+        b = torch.randn(8192 // world, 2048, device=dev, dtype=torch.bfloat16)
+        xs = torch.randn(M // world, 2048, device=dev, dtype=torch.bfloat16)
+        w1 = torch.randn(2048, 8192 // world, device=dev, dtype=torch.bfloat16)
+        w8 = torch.randn(2048, 8, device=dev, dtype=torch.bfloat16)
+        full_x = torch.randn(M, 2048, device=dev, dtype=torch.bfloat16)
+
+        def timed(fn):
+            for _ in range(3):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(10):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / 10], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return round(t.item(), 4)
+
+        out["rs_gemm_only"] = timed(lambda: gemm_bf16(a, b))
+        out["ag_gemm_only"] = timed(lambda: gemm_bf16(full_x, w1))
+        out["nccl_ag"] = timed(lambda: dist.all_gather_into_tensor(full_x, xs))
+        out["rs_fused"] = timed(lambda: symm.gemm_reduce_scatter(a, b, mesh, ("x",), M // world))
+        for c in (4, 6, 8, 12, 16, 24):
+            out[f"ag_{c}"] = timed(lambda: symm.all_gather_gemm(xs, w1, mesh, ("x",), M // world, comm_ctas=c))
+            out[f"agcopy_{c}"] = timed(lambda: symm.all_gather_gemm(xs, w8, mesh, ("x",), M // world, comm_ctas=c))
+        native_ok = True
+        from nabla_b200 import native
         native.check_status()
     elif mode == "transformer":
         from nabla_b200.models import transformer as TR
