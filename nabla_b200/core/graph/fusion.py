@@ -261,7 +261,9 @@ def _is_bias_add(m: OpNode, mm_out: TensorImpl) -> bool:
     return len(shp) >= 1 and shp[-1] == n and all(d == 1 for d in shp[:-1]) and other.dtype is mm_out.dtype
 
 
-def run_fused(kind: str, group: list[OpNode], keep_graph: bool = False) -> None:
+def run_fused(kind: str, group: list[OpNode], keep_graph: bool = False, arena_blocks: dict | None = None) -> None:
+    """``arena_blocks`` (compiled replays only): {id(impl): (arena, offset)} of gathered tensors
+    that live in a symmetric arena; the replay frees them after their last use."""
     from .engine import store_outputs
 
     if kind == "linear_epilogue":
@@ -371,8 +373,16 @@ def run_fused(kind: str, group: list[OpNode], keep_graph: bool = False) -> None:
                 and m_total // world * k * 2 + 4096 <= symm.DEFAULT_BYTES - 65536
                 and os.environ.get("NABLA_B200_FUSE_AG", "1") != "0"):
             epi = "none" if act is None else ("relu" if act == "relu" else "gelu")
+            off = None
+            ag_out = ag.outputs()[0]
+            if arena_blocks is not None and ag_out is not None and os.environ.get("NABLA_B200_AG_PUSH", "1") != "0":
+                ar = symm.arena(mesh, axes)
+                if ar is not None:
+                    off = ar.alloc(m_total * k * 2)
+                    if off is not None:
+                        arena_blocks[id(ag_out)] = (ar, off)
             res = symm.all_gather_gemm(x, w, mesh, axes, cs, bias=bias, epilogue=epi, gelu_tanh=act == "gelu_tanh",
-                                       store_preact=act is not None)
+                                       store_preact=act is not None, arena_off=off)
             full_shape = (*lead[:dim], lead[dim] * world, *lead[dim + 1:])
             _store(ag, [[res[0].reshape(*full_shape, k)]], keep_graph)
             outs = [[res[1].reshape(*full_shape, n)]]

@@ -105,6 +105,11 @@ struct CommArgs {
   __nv_bfloat16* rs_out;    // RS: this rank's rows of the sum, [M / world][N]
   char* a_full;             // AG: the gathered A, [M][K] dense
   long long unit_bytes;     // AG: bytes of one 128-row block of A
+  // AG push variant: the gathered A of every rank lives at the same offset of a symmetric arena;
+  // copy CTAs read this rank's own rows and store them into every rank's gathered A
+  void* const* abufs;       // device array [world] of arena base pointers (nullptr: pull variant)
+  long long a_off;          // byte offset of the gathered A inside the arena
+  const char* own_src;      // this rank's own rows, [M / world][K] dense
 };
 
 // Order in which the GEMM walks the M tiles -> the tile's real row block.
@@ -125,6 +130,12 @@ __device__ __forceinline__ int remap_m(int tm, const CommArgs& c) {
     return (g * c.world + p) * c.mpc + j;
   }
   return tm;
+}
+
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
 }
 
 __device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
@@ -221,7 +232,7 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
                                                                 comm.flag_off) + AG_FLAG_BASE + tm;
           const unsigned long long t0 = globaltimer_ns();
           unsigned spins = 0;
-          while ((int)(ld_acquire_gpu_u32(f) - comm.epoch) < 0) {
+          while ((int)(ld_acquire_sys_u32(f) - comm.epoch) < 0) {
             if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
               ok = false;
               atomicExch(args.status, NB_ERR_TIMEOUT_PEER);
@@ -557,11 +568,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 // copies (multimem.ld_reduce in the switch, or peer loads) and writes the sum into every rank's
 // workspace (multimem.st, or peer stores). The kernel leaves once every CTA of every rank is
 // through, so the next kernel on the stream finds the reduced matrix in the local workspace.
-__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 __device__ __forceinline__ bool wait_flag_ge(const unsigned* p, unsigned target) {
   if ((int)(ld_acquire_sys_u32(p) - target) >= 0) return true;
   const unsigned long long t0 = globaltimer_ns();
@@ -749,9 +755,9 @@ __device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint3
                : "memory");
 }
 
-// Copy order of the 128-row blocks: the peers' rows first (ring order, as the GEMM will ask for
-// them), this rank's own rows last (the GEMM reads those from the shard; the copy only completes
-// the gathered matrix for later use).
+// Copy order of the 128-row blocks: the peers' rows in ring order, as the GEMM will ask for them.
+// This rank's own rows (the last num_m / world positions of this order) are not copied here: the
+// GEMM reads them from the shard, and the caller writes them into the gathered matrix itself.
 __device__ __forceinline__ int ag_unit(int u, int num_m, const CommArgs& c) {
   u += c.per;
   return u >= num_m ? u - num_m : u;
@@ -779,7 +785,7 @@ __device__ __forceinline__ void gather_jobs(const GemmArgs& args, const CommArgs
   fence_proxy_async_smem();
   const int ppu = (int)((comm.unit_bytes + AG_PIECE - 1) / AG_PIECE);   // pieces per 128-row block
   int n_units = 0;
-  for (int u = cidx; u < num_m; u += ncomm) ++n_units;
+  for (int u = cidx; u < num_m - comm.per; u += ncomm) ++n_units;     // the peers' blocks; own rows are the caller's
   const int total = n_units * ppu;
   unsigned ready_mask = 0;
   bool ok = true;
@@ -845,6 +851,72 @@ __device__ __forceinline__ void gather_jobs(const GemmArgs& args, const CommArgs
   if (!ok) atomicExch(args.status, NB_ERR_TIMEOUT_PEER);
 }
 
+// Push variant of the MODE_AG copy CTAs: all threads read this rank's own rows (local memory,
+// short latency) and store them into the gathered A of every rank. The peer stores are posted:
+// nothing waits for a round trip, so a few CTAs keep the link busy. After each 128-row block a
+// barrier and one release store per peer raise the block's flag there. A peer is written only
+// after it announced (ready flag) that its gathered A may be overwritten.
+template <int BN>
+__device__ __forceinline__ void push_jobs(const GemmArgs& args, const CommArgs& comm, int cidx, int ncomm) {
+  __shared__ int s_ok;
+  char* local = reinterpret_cast<char*>(comm.bufs[comm.rank]);
+  if (threadIdx.x == 0) {
+    if (cidx == 0) {
+      for (int p = 0; p < comm.world; ++p)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<char*>(comm.bufs[p]) + comm.done_off +
+                                                                  READY_OFF + 4 * comm.rank),
+                     "r"(comm.epoch)
+                     : "memory");
+    }
+    bool ok = true;
+    for (int p = 0; p < comm.world && ok; ++p)
+      ok = wait_flag_ge(reinterpret_cast<const unsigned*>(local + comm.done_off + READY_OFF + 4 * p), comm.epoch);
+    if (!ok) atomicExch(args.status, NB_ERR_TIMEOUT_PEER);
+    s_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  constexpr int PU = 16;                                   // 16-byte vectors in flight per thread
+  const long long nvec = comm.unit_bytes / 16;
+  for (int v = cidx; v < comm.per; v += ncomm) {           // this CTA's own 128-row blocks
+    const int g = v / comm.mpc, j = v - g * comm.mpc;
+    const int tm = (g * comm.world + comm.rank) * comm.mpc + j;   // the block's place in the gathered A
+    const uint4* src = reinterpret_cast<const uint4*>(comm.own_src + (long long)v * comm.unit_bytes);
+    const long long dst_off = comm.a_off + (long long)tm * comm.unit_bytes;
+    for (long long base = 0; base < nvec; base += (long long)PU * NUM_THREADS) {
+      uint4 val[PU];
+#pragma unroll
+      for (int u = 0; u < PU; ++u) {
+        const long long idx = base + u * NUM_THREADS + threadIdx.x;
+        if (idx < nvec) val[u] = src[idx];
+      }
+      for (int d = 1; d < comm.world; ++d) {               // the peers in ring order (the own copy is the caller's)
+        int q = comm.rank + d;
+        if (q >= comm.world) q -= comm.world;
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(comm.abufs[q]) + dst_off);
+#pragma unroll
+        for (int u = 0; u < PU; ++u) {
+          const long long idx = base + u * NUM_THREADS + threadIdx.x;
+          if (idx < nvec) dst[idx] = val[u];
+        }
+      }
+    }
+    __syncthreads();                                       // every thread's stores precede the flags
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      for (int d = 1; d < comm.world; ++d) {
+        int q = comm.rank + d;
+        if (q >= comm.world) q -= comm.world;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<unsigned*>(
+                                                                      reinterpret_cast<char*>(comm.bufs[q]) + comm.flag_off) +
+                                                                  AG_FLAG_BASE + tm),
+                     "r"(comm.epoch)
+                     : "memory");
+      }
+    }
+  }
+}
+
 template <int BN, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -864,6 +936,12 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
   if (MODE == MODE_AG) {
     if (is_gemm) return;                      // GEMM CTAs touch no peer memory
+    if (comm.abufs != nullptr) {
+      // push: nobody reads this rank's memory, and the GEMM has waited for every block that was
+      // pushed to it, so no closing barrier is needed
+      push_jobs<BN>(args, comm, (int)blockIdx.x - n_gemm, (int)gridDim.x - n_gemm);
+      return;
+    }
     gather_jobs<BN>(args, comm, (int)blockIdx.x - n_gemm, (int)gridDim.x - n_gemm);
   } else if (MODE == MODE_AR) {
     reduce_jobs<BN, MODE>(args, comm);
@@ -1005,6 +1083,8 @@ extern "C" int nb_gemm_bf16(const void* A, const void* B, void* C, const void* b
 //   a_full        mode 3: the gathered A [M][K] (dense, regular device memory); A = this rank's own rows
 //                 [M / world][K], dense (the same data that was staged at data_off for the peers)
 //   chunk_rows    modes 2, 3: rows per contiguous chunk of a rank (multiple of 128, M % (world*chunk_rows) == 0)
+//   arena_bufs    mode 3, push variant: device array [world] of the base pointers of a symmetric arena
+//                 in which a_full sits at byte offset a_off on EVERY rank (null: pull variant)
 //   ctr           device counters of the workspace (unsigned[4], zero at creation): the kernel
 //                 takes its all-gather epoch and done target relative to them and a one-thread
 //                 kernel advances them afterwards, so replaying the launches from a CUDA graph works
@@ -1096,7 +1176,7 @@ extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* 
                                   int flag_off, int done_off, int M, int N, int K, long long lda, long long ldb,
                                   int a_mn, int b_mn, int bias_fp32, int epi, int aux, int gelu_tanh, int rank,
                                   int world, int chunk_rows, unsigned* ctr, int n_comm_ctas, int* ticket, int* status,
-                                  void* stream) {
+                                  void* const* arena_bufs, long long a_off, void* stream) {
   using namespace nb;
   constexpr int BN = 256;
   if (mode < MODE_AR || mode > MODE_AG) return -9;
@@ -1152,6 +1232,10 @@ extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* 
   c.rs_out = reinterpret_cast<__nv_bfloat16*>(out);
   c.a_full = reinterpret_cast<char*>(a_full);
   c.unit_bytes = (long long)BLOCK_M * K * 2;
+  c.abufs = mode == MODE_AG ? arena_bufs : nullptr;
+  c.a_off = a_off;
+  c.own_src = reinterpret_cast<const char*>(A);
+  if (mode == MODE_AG && arena_bufs != nullptr) c.done_target = 0;   // push: no closing barrier, nothing counted
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (mode != MODE_AG && cudaMemsetAsync(ticket, 0, sizeof(int), s) != cudaSuccess) return -4;
   if (mode == MODE_AR) return launch_fused<MODE_AR>(ta, tb, ta, g, c, grid, n_gemm, s);

@@ -82,6 +82,71 @@ class Workspace:
         self.data[offset:offset + n].view(x.dtype).view(x.shape).copy_(x)
 
 
+class Arena:
+    """Symmetric memory that outlives one collective: the gathered activations of the push
+    variant of all-gather + GEMM live here, at the same offset on every rank, so that a peer can
+    store its rows straight into them. First-fit free list; every rank performs the same sequence
+    of ``alloc`` / ``free`` calls (they come from the same recorded schedule), which keeps the
+    offsets identical without any exchange."""
+
+    ALIGN = 1 << 20
+
+    def __init__(self, pg, nbytes: int):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.nbytes = int(nbytes)
+        self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+        self.hdl = symm_mem.rendezvous(self.buf, group=pg)
+        self.ptrs_dev = int(self.hdl.buffer_ptrs_dev)
+        self.free_list: list[list[int]] = [[0, self.nbytes]]      # [offset, size], sorted by offset
+        self.live: dict[int, int] = {}
+        torch.cuda.synchronize()
+        dist.barrier(group=pg)
+
+    def alloc(self, nbytes: int) -> int | None:
+        need = (int(nbytes) + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+        for i, (off, size) in enumerate(self.free_list):
+            if size >= need:
+                if size == need:
+                    self.free_list.pop(i)
+                else:
+                    self.free_list[i] = [off + need, size - need]
+                self.live[off] = need
+                return off
+        return None
+
+    def free(self, off: int) -> None:
+        size = self.live.pop(off)
+        fl = self.free_list
+        i = 0
+        while i < len(fl) and fl[i][0] < off:
+            i += 1
+        fl.insert(i, [off, size])
+        if i + 1 < len(fl) and fl[i][0] + fl[i][1] == fl[i + 1][0]:
+            fl[i][1] += fl[i + 1][1]
+            fl.pop(i + 1)
+        if i > 0 and fl[i - 1][0] + fl[i - 1][1] == fl[i][0]:
+            fl[i - 1][1] += fl[i][1]
+            fl.pop(i)
+
+
+ARENA_BYTES = int(float(os.environ.get("NABLA_B200_SYMM_ARENA_GB", "20")) * (1 << 30))
+
+
+def arena(mesh, axes) -> Arena | None:
+    """The symmetric arena of the device group (created on first use; ``None`` when disabled with
+    ``NABLA_B200_SYMM_ARENA_GB=0`` or when the allocation fails)."""
+    ws = workspace(mesh, axes)
+    if not hasattr(ws, "arena"):
+        ws.arena = None
+        if ARENA_BYTES > 0:
+            try:
+                ws.arena = Arena(ws.pg, ARENA_BYTES)
+            except Exception:      # not enough memory, or symmetric allocation unsupported
+                ws.arena = None
+    return ws.arena
+
+
 def is_ready() -> bool:
     global _enabled
     if _enabled is None:
@@ -172,6 +237,7 @@ def all_reduce(buf: torch.Tensor, mesh, axes, op: str = "sum", algo: str | None 
 _gemm_fn = None
 FUSED_COMM_CTAS = int(os.environ.get("NABLA_B200_FUSED_COMM_CTAS", "20"))
 AG_COMM_CTAS = int(os.environ.get("NABLA_B200_AG_COMM_CTAS", "12"))
+PUSH_COMM_CTAS = int(os.environ.get("NABLA_B200_PUSH_COMM_CTAS", "8"))
 MODE_AR, MODE_RS, MODE_AG = 1, 2, 3
 _EPI = {"none": 0, "bias": 1, "relu": 2, "gelu": 3}
 
@@ -185,7 +251,7 @@ def _fused_fn():
         fn = lib.nb_gemm_fused_bf16
         fn.restype = c_int
         fn.argtypes = ([c_int] + [c_vp] * 9 + [c_ll, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll] + [c_int] * 9 +
-                       [c_vp, c_int, c_vp, c_vp, c_vp])
+                       [c_vp, c_int, c_vp, c_vp, c_vp, c_ll, c_vp])
         lib.nb_gemm_fused_grid.restype = c_int
         _gemm_fn = (fn, lib.nb_gemm_fused_grid)
     return _gemm_fn
@@ -213,6 +279,17 @@ def chunked_supported(m_total: int, chunk_rows: int, world: int) -> bool:
     return chunk_rows > 0 and chunk_rows % 128 == 0 and m_total % (world * chunk_rows) == 0 and m_total // 128 <= 2048
 
 
+_side_streams: dict = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    st = _side_streams.get(device)
+    if st is None:
+        st = torch.cuda.Stream(device=device)
+        _side_streams[device] = st
+    return st
+
+
 def _fused_state(ws, device):
     if not hasattr(ws, "ticket"):
         ws.ticket = torch.zeros(4, dtype=torch.int32, device=device)
@@ -220,7 +297,7 @@ def _fused_state(ws, device):
 
 
 def _launch_fused(mode, ws, a, b, out, bias, aux_out, a_full, M, N, K, lda, ldb, a_mn, b_mn, epi, aux, gelu_tanh,
-                  chunk_rows, n_comm):
+                  chunk_rows, n_comm, arena_ptrs: int = 0, a_off: int = 0):
     """Returns the byte offset (inside the workspace) of the region the call used."""
     global launch_count
     fn, grid_fn = _fused_fn()
@@ -241,7 +318,8 @@ def _launch_fused(mode, ws, a, b, out, bias, aux_out, a_full, M, N, K, lda, ldb,
     rc = fn(mode, p(a), p(b), p(out), p(bias), p(aux_out), p(a_full), ws.buf.data_ptr(), ws.ptrs_dev, ws.mc_ptr,
             data_off, lib.nb_comm_tile_flag_offset(), lib.nb_comm_done_offset(), M, N, K, lda, ldb, a_mn, b_mn,
             1 if (bias is not None and bias.dtype == torch.float32) else 0, epi, aux, int(gelu_tanh), ws.rank, ws.world,
-            chunk_rows, ws.ctr.data_ptr(), n_comm, ws.ticket.data_ptr(), _status().data_ptr(), _stream())
+            chunk_rows, ws.ctr.data_ptr(), n_comm, ws.ticket.data_ptr(), _status().data_ptr(), arena_ptrs, a_off,
+            _stream())
     if rc != 0:
         raise RuntimeError(f"nb_gemm_fused_bf16(mode={mode}) failed with code {rc} for M={M} N={N} K={K}")
     launch_count += 1
@@ -296,32 +374,60 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_rows
 
 def all_gather_gemm(a_shard: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_rows: int, bias: torch.Tensor | None = None,
                     epilogue: str = "none", gelu_tanh: bool = False, store_preact: bool = False,
-                    comm_ctas: int | None = None):
+                    comm_ctas: int | None = None, arena_off: int | None = None):
     """``epilogue(gather(a) @ b + bias)`` in one kernel. ``a_shard`` is this rank's rows
-    (M / world, K); copy CTAs of the launch pull the peers' rows over NVLink with bulk copies
-    into the gathered matrix while the tensor-core CTAs already multiply the rows that are
-    there (own rows first, then the peers' in ring order).
+    (M / world, K). The tensor-core CTAs start on the own rows (read in place) while copy CTAs of
+    the same launch move the other rows over NVLink; each later tile waits only for its own
+    128-row block.
+
+    Two copy directions. With ``arena_off`` (an offset in the group's symmetric :class:`Arena`,
+    the same on every rank) the gathered matrix lives in the arena and every rank PUSHES its rows
+    into all peers' copies with posted bulk stores: no round trip to wait for, a handful of copy
+    CTAs keep the link busy, and nothing has to be staged. Without it the rows are staged in the
+    workspace and PULLED by the consumer (bulk loads through shared memory).
 
     Returns ``(a_full, out)`` or ``(a_full, out, preact)``; ``a_full`` (M, K) is the all-gather's
     own result, kept for the backward pass."""
     from ..native.gemm import _prep
 
     ws = _fused_state(workspace(mesh, axes), a_shard.device)
-    x = a_shard.reshape(-1, a_shard.shape[-1])
+    x = a_shard.reshape(-1, a_shard.shape[-1]).contiguous()
     Ml, K = x.shape
     M, N = Ml * ws.world, b.shape[1]
-    ws.data[: Ml * K * 2].view(torch.bfloat16).view(Ml, K).copy_(x)        # stage where peers can read it
     b3, bkind, ldb, _ = _prep(b.unsqueeze(0))
-    a_full = torch.empty((M, K), dtype=torch.bfloat16, device=x.device)
+    push = arena_off is not None
+    if push:
+        ar = ws.arena
+        a_full = ar.buf[arena_off: arena_off + M * K * 2].view(torch.bfloat16).view(M, K)
+    else:
+        ws.data[: Ml * K * 2].view(torch.bfloat16).view(Ml, K).copy_(x)        # stage where peers can read it
+        a_full = torch.empty((M, K), dtype=torch.bfloat16, device=x.device)
     out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     pre = torch.empty((M, N), dtype=torch.bfloat16, device=x.device) if store_preact else None
     if bias is not None:
         bias = bias.reshape(-1).contiguous()
         if epilogue == "none":
             epilogue = "bias"
-    x = x.contiguous()
+    # this rank's own rows of the gathered matrix (the kernel moves only the peers' rows): a plain
+    # copy on a side stream, issued first so that it runs under the fused kernel (which reads the
+    # own rows from ``x``, not from here); the streams join again right after the launch
+    cs = chunk_rows
+    cur = torch.cuda.current_stream()
+    side = _side_stream(x.device)
+    side.wait_stream(cur)
+    with torch.cuda.stream(side):
+        a_full.view(M // (ws.world * cs), ws.world, cs, K)[:, ws.rank].copy_(x.view(-1, cs, K))
+    # copy CTAs: an SM moves about 32 GB/s (pull) to 38 GB/s (push); take as many as it needs to move
+    # the peers' rows within the GEMM's own time, up to what saturates the link
+    if comm_ctas is None:
+        gemm_s = 2.0 * M * N * K / 1.3e15
+        need = (M - Ml) * K * 2 / max(gemm_s, 1e-6) / (38e9 if push else 32e9)
+        comm_ctas = int(min(20, max(4, need + 1.5)))
+    n_comm = comm_ctas
     _launch_fused(MODE_AG, ws, x, b3, out, bias, pre, a_full, M, N, K, K, ldb, 0, 1 if bkind == "row" else 0,
-                  _EPI[epilogue], 1 if store_preact else 0, gelu_tanh, chunk_rows, comm_ctas or AG_COMM_CTAS)
+                  _EPI[epilogue], 1 if store_preact else 0, gelu_tanh, chunk_rows, n_comm,
+                  ws.arena.ptrs_dev if push else 0, arena_off or 0)
+    cur.wait_stream(side)
     return (a_full, out, pre) if store_preact else (a_full, out)
 
 

@@ -73,6 +73,8 @@ class _Recorded:
         self.out_static: list[Any] = []
         self.out_treedef = None
         self.cuda_graph = None
+        self.arena_blocks: dict[int, tuple] = {}    # gathered tensors living in a symmetric arena
+        self.arena_ok: set[int] = set()             # ids of impls that may live there (never returned)
         self.donated: list[bool] = []               # per placeholder
         self.static_inputs: list[list[torch.Tensor]] | None = None
         self.static_outputs: list[list[torch.Tensor]] | None = None
@@ -274,9 +276,22 @@ class CompiledFunction:
                     if o is not None:
                         o._buffers = outs[i]
             else:
-                fusion.run_fused(kind, [nodes[i] for i in idxs], keep_graph=True)
+                fusion.run_fused(kind, [nodes[i] for i in idxs], keep_graph=True, arena_blocks=rec.arena_blocks)
             for dead in rec.free_after[si]:
                 dead._buffers = None
+                blk = rec.arena_blocks.pop(id(dead), None)
+                if blk is not None:
+                    blk[0].free(blk[1])
+        self._release_arena(rec)
+
+    @staticmethod
+    def _release_arena(rec: _Recorded) -> None:
+        """Results that are handed to the caller must not stay in the symmetric arena."""
+        for impl in rec.out_impls:
+            blk = rec.arena_blocks.pop(id(impl), None) if impl is not None else None
+            if blk is not None:
+                impl._buffers = [b.clone() for b in impl._buffers]
+                blk[0].free(blk[1])
 
     def _run_profiled(self, rec: _Recorded) -> None:
         """Same as ``_run`` with a CUDA event pair around every step; device time per step kind
@@ -295,12 +310,15 @@ class CompiledFunction:
                         o._buffers = outs[i]
                 name = n.op.name
             else:
-                fusion.run_fused(kind, [nodes[i] for i in idxs], keep_graph=True)
+                fusion.run_fused(kind, [nodes[i] for i in idxs], keep_graph=True, arena_blocks=rec.arena_blocks)
                 name = kind + ":" + nodes[idxs[-1]].op.name
             e1.record()
             marks.append((name, e0, e1))
             for dead in rec.free_after[si]:
                 dead._buffers = None
+                blk = rec.arena_blocks.pop(id(dead), None)
+                if blk is not None:
+                    blk[0].free(blk[1])
         torch.cuda.synchronize()
         for name, e0, e1 in marks:
             ent = self.op_profile.setdefault(name, [0, 0.0])

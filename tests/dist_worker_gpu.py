@@ -133,9 +133,17 @@ def main():
             dist.all_gather(parts, xs)
             full = torch.stack([p_.view(-1, cs, K) for p_ in parts], 1).reshape(M, K)
             z_ref = full.float() @ w.float() + bias.float()
-            for rep in range(2):
-                a_full, y, z = symm.all_gather_gemm(xs, w, mesh, ("x",), cs, bias=bias, epilogue="gelu", store_preact=True)
+            ar = symm.arena(mesh, ("x",))
+            out["arena"] = ar is not None
+            for rep in range(4):
+                off = ar.alloc(M * K * 2) if (ar is not None and rep >= 2) else None      # reps 2, 3: push variant
+                a_full, y, z = symm.all_gather_gemm(xs, w, mesh, ("x",), cs, bias=bias, epilogue="gelu", store_preact=True,
+                                                    arena_off=off)
                 torch.cuda.synchronize()
+                if off is not None:
+                    a_full = a_full.clone()
+                    dist.barrier()
+                    ar.free(off)
                 errs[f"ag_gather_{M}x{K}_{rep}"] = (a_full.float() - full.float()).abs().max().item()
                 errs[f"ag_z_{M}x{N}x{K}_{rep}"] = ((z.float() - z_ref).abs().max() / z_ref.abs().max()).item()
                 errs[f"ag_y_{M}x{N}x{K}_{rep}"] = ((y.float() - torch.nn.functional.gelu(z_ref)).abs().max()
@@ -226,9 +234,15 @@ def main():
         out["ag_gemm_only"] = timed(lambda: gemm_bf16(full_x, w1))
         out["nccl_ag"] = timed(lambda: dist.all_gather_into_tensor(full_x, xs))
         out["rs_fused"] = timed(lambda: symm.gemm_reduce_scatter(a, b, mesh, ("x",), M // world))
-        for c in (4, 6, 8, 12, 16, 24):
+        for c in (8, 12, 16):
             out[f"ag_{c}"] = timed(lambda: symm.all_gather_gemm(xs, w1, mesh, ("x",), M // world, comm_ctas=c))
             out[f"agcopy_{c}"] = timed(lambda: symm.all_gather_gemm(xs, w8, mesh, ("x",), M // world, comm_ctas=c))
+        ar = symm.arena(mesh, ("x",))
+        off = ar.alloc(M * 2048 * 2)
+        for c in (2, 4, 6, 8, 12):
+            out[f"agpush_{c}"] = timed(lambda: symm.all_gather_gemm(xs, w1, mesh, ("x",), M // world, comm_ctas=c, arena_off=off))
+            out[f"agpushcopy_{c}"] = timed(lambda: symm.all_gather_gemm(xs, w8, mesh, ("x",), M // world, comm_ctas=c,
+                                                                        arena_off=off))
         native_ok = True
         from nabla_b200 import native
         native.check_status()
