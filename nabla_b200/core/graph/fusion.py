@@ -10,7 +10,9 @@ CUDA bf16 tensors:
 * ``matmul | linear (no bias) -> all_reduce(sum) | reduce_scatter`` on a mesh that runs one
   process per GPU: one launch of the fused GEMM + collective kernel (tiles are reduced over
   NVLink while later tiles are still being multiplied).
-* ``all_gather(rows) -> linear | matmul``: one launch that pulls the peers' rows while the tensor
+* ``matmul -> dact_mul`` (backward of linear + relu/gelu): the activation derivative is applied in
+  the GEMM epilogue.
+* ``all_gather(rows) -> linear | matmul [-> dact_mul]``: one launch that pulls the peers' rows while the tensor
   cores already work on the rows that are there; the gathered tensor is still produced.
 
 Every other node is a plain 'op' step. Fusion never changes which tensors exist: fused-away
@@ -81,6 +83,11 @@ def build_plan(nodes: list[OpNode], targets: list[TensorImpl]):
                                 a.op.name == "gelu" and a.kwargs.get("approximate", "none") not in ("none", "tanh")):
                             chain = [i, j, k]
         kind = "linear_epilogue"
+        if chain is None and n.op.name == "matmul" and _is_local_gemm(n):
+            dk = _dact_consumer(n, nodes, cons, target_ids, used)
+            if dk is not None:
+                chain = [i, dk]
+                kind = "gemm_dact"
         if chain is None and n.op.name in ("matmul", "linear") and _is_partial_gemm(n):
             o = sole_output(n)
             # a traced product may stay an unrealized promise: no backward rule reads its value
@@ -119,9 +126,18 @@ def build_plan(nodes: list[OpNode], targets: list[TensorImpl]):
                     for x in m.input_impls():
                         if x is not o and id(x) in producer:
                             ready = max(ready, producer[id(x)])
+                    idxs = [i, j]
+                    dk = _dact_consumer(m, nodes, cons, target_ids, used)
+                    if dk is not None:
+                        z = nodes[dk].input_impls()[1]
+                        zr = producer.get(id(z), -1)
+                        if max(ready, zr) < j:
+                            ready = max(ready, zr)
+                            idxs.append(dk)
                     if ready < j and all(u > ready for u in users):
-                        used[i] = used[j] = True
-                        steps.append((ready + 0.5, ("all_gather_gemm", (i, j))))
+                        for c_ in idxs:
+                            used[c_] = True
+                        steps.append((ready + 0.5, ("all_gather_gemm", tuple(idxs))))
                         continue
         if chain is not None:
             # schedule at the position of the LAST node of the chain
@@ -147,6 +163,40 @@ def _is_cuda_bf16_2d(n: OpNode) -> bool:
 
     return (a.device.label == "gpu" and a.dtype is DType.bfloat16 and b.dtype is DType.bfloat16
             and len(b._shape) == 2 and len(a._shape) >= 2)
+
+
+def _is_local_gemm(n: OpNode) -> bool:
+    """bf16 GPU ``x @ w`` (w 2-D) whose product needs no collective."""
+    ins = n.input_impls()
+    if len(ins) != 2:
+        return False
+    a, b = ins
+    outs = n.outputs()
+    o = outs[0] if len(outs) == 1 else None
+    if o is None or (o.sharding is not None and o.sharding.partial_sum_axes):
+        return False
+    from ...types import DType
+
+    return (a.device.label == "gpu" and a.dtype is DType.bfloat16 and b.dtype is DType.bfloat16
+            and len(b._shape) == 2 and len(a._shape) >= 2 and a.batch_dims == 0 and b.batch_dims == 0)
+
+
+def _dact_consumer(mm: OpNode, nodes, cons, target_ids, used) -> int | None:
+    """Index of the ``dact_mul`` node that is the only reader of ``mm``'s product, if any."""
+    outs = mm.outputs()
+    o = outs[0] if len(outs) == 1 else None
+    if o is None or id(o) in target_ids or o.batch_dims or len(cons.get(id(o), [])) != 1:
+        return None
+    if mm.kwargs.get("activation") is not None or len(mm.input_impls()) != 2:
+        return None
+    k = cons[id(o)][0]
+    d = nodes[k]
+    if used[k] or d.op.name != "dact_mul" or d.kwargs.get("activation") not in ("relu", "gelu", "gelu_tanh"):
+        return None
+    ins = d.input_impls()
+    if len(ins) != 2 or ins[0] is not o or ins[1] is o or tuple(ins[1]._shape) != tuple(o._shape):
+        return None
+    return k
 
 
 def _is_partial_gemm(n: OpNode) -> bool:
@@ -287,6 +337,22 @@ def run_fused(kind: str, group: list[OpNode], keep_graph: bool = False, arena_bl
         else:
             store_outputs(last, [[out]])
         return
+    if kind == "gemm_dact":
+        from ...native.gemm import gemm_bf16
+
+        mm, da = group
+        a, b = [x._buffers[0] for x in mm.input_impls()]
+        z = da.input_impls()[1]._buffers[0]
+        act = da.kwargs["activation"]
+        if a.is_cuda and a.numel() and b.numel():
+            n_out = b.shape[-1]
+            out = gemm_bf16(a.reshape(-1, a.shape[-1]), b, aux="drelu" if act == "relu" else "dgelu",
+                            aux_in=z.reshape(-1, n_out), gelu_tanh=act == "gelu_tanh").reshape(*a.shape[:-1], n_out)
+            _store(da, [[out]], keep_graph)
+        else:
+            _plain(mm, keep_graph)
+            _plain(da, keep_graph)
+        return
     if kind == "gemm_all_reduce":
         from ...parallel import backend, symm
 
@@ -348,7 +414,8 @@ def run_fused(kind: str, group: list[OpNode], keep_graph: bool = False, arena_bl
     if kind == "all_gather_gemm":
         from ...parallel import backend, symm
 
-        ag, mm = group
+        ag, mm = group[0], group[1]
+        da = group[2] if len(group) > 2 else None
         x_impl = ag.input_impls()[0]
         x = x_impl._buffers[0]
         dim = ag.kwargs["dim"]
@@ -381,18 +448,21 @@ def run_fused(kind: str, group: list[OpNode], keep_graph: bool = False, arena_bl
                     off = ar.alloc(m_total * k * 2)
                     if off is not None:
                         arena_blocks[id(ag_out)] = (ar, off)
+            dact = None
+            if da is not None:
+                dact = (da.input_impls()[1]._buffers[0], da.kwargs["activation"])
             res = symm.all_gather_gemm(x, w, mesh, axes, cs, bias=bias, epilogue=epi, gelu_tanh=act == "gelu_tanh",
-                                       store_preact=act is not None, arena_off=off)
+                                       store_preact=act is not None, arena_off=off, dact=dact)
             full_shape = (*lead[:dim], lead[dim] * world, *lead[dim + 1:])
             _store(ag, [[res[0].reshape(*full_shape, k)]], keep_graph)
             outs = [[res[1].reshape(*full_shape, n)]]
             if act is not None:
                 outs.append([res[2].reshape(*full_shape, n)])
-            _store(mm, outs, keep_graph)
+            _store(da if da is not None else mm, outs, keep_graph)
             backend.stats["fused_all_gather_gemm"] = backend.stats.get("fused_all_gather_gemm", 0) + 1
         else:
-            _plain(ag, keep_graph)
-            _plain(mm, keep_graph)
+            for n_ in group:
+                _plain(n_, keep_graph)
         return
     raise ValueError(f"unknown fused step {kind}")
 

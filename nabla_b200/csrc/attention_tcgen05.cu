@@ -357,7 +357,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 //   dQ_i^T = K_j^T dS^T (128 x 64)  -> fp32 vector reductions into a [B][H][D][Sq_pad] scratch
 // Two small kernels bracket it: delta_i = rowsum(dO_i * O_i), and the conversion of the dQ
 // scratch (transposed, fp32) to the caller's bf16 layout.
+//
+// Two query tiles are in flight: math group 0 (warps 4-7) owns the even tiles, group 1 (warps
+// 8-11) the odd ones, each with its own S^T / dP^T columns in TMEM and its own P^T / dS^T buffers
+// in shared memory, so the tensor pipe works on one tile's five MMAs while the other tile's
+// exponentials and dS are computed. dQ_i^T is written over tile i's dP^T columns (which the math
+// threads have consumed by then): 2 x (64 + 64) + 128 + 128 = 512 TMEM columns.
 constexpr int BQ = 64;
+constexpr int BWD_THREADS = 384;
 
 struct BwdArgs {
   int B, H, Sq, Skv, Sq_pad;
@@ -380,18 +387,18 @@ struct BwdSmem {
   static constexpr int OFF_V = OFF_K + KV_BYTES;
   static constexpr int OFF_Q = OFF_V + KV_BYTES;      // 2 stages
   static constexpr int OFF_DO = OFF_Q + 2 * QT_BYTES;
-  static constexpr int OFF_X = OFF_DO + 2 * QT_BYTES;
-  static constexpr int OFF_Y = OFF_X + XY_BYTES;
-  static constexpr int OFF_STAT = OFF_Y + XY_BYTES;   // lse2[2][64], delta[2][64]
+  static constexpr int OFF_X = OFF_DO + 2 * QT_BYTES;  // 2 buffers (one per math group)
+  static constexpr int OFF_Y = OFF_X + 2 * XY_BYTES;   // 2 buffers
+  static constexpr int OFF_STAT = OFF_Y + 2 * XY_BYTES;   // lse2[2][64], delta[2][64]
   static constexpr int OFF_BAR = OFF_STAT + 4 * BQ * 4;
-  static constexpr int TOTAL = OFF_BAR + 16 * 8 + 16 + 1024;
+  static constexpr int TOTAL = OFF_BAR + 24 * 8 + 16 + 1024;
 };
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                 const BwdArgs args) {
@@ -409,13 +416,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   float* s_delta = s_lse2 + 2 * BQ;                               // [2][64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* kv_full = bars + 0;
-  uint64_t* qdo_full = bars + 1;    // [2]
-  uint64_t* qdo_empty = bars + 3;   // [2]
-  uint64_t* sdp_full = bars + 5;
-  uint64_t* xy_full = bars + 6;
-  uint64_t* g2_done = bars + 7;
-  uint64_t* dq_free = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* qdo_full = bars + 1;    // [2]  Q_i / dO_i landed in stage i & 1
+  uint64_t* qdo_empty = bars + 3;   // [2]  the MMAs that read the stage have retired
+  uint64_t* sdp_full = bars + 5;    // [2]  S^T and dP^T of the group's tile are in TMEM
+  uint64_t* xy_full = bars + 7;     // [2]  P^T and dS^T of the group's tile are in shared memory (128 arrivals)
+  uint64_t* g2_done = bars + 9;     // [2]  dV / dK / dQ^T MMAs of the group's tile have retired
+  uint64_t* dq_free = bars + 11;    // [2]  dQ^T of the group's tile has been drained (128 arrivals)
+  uint64_t* all_done = bars + 13;   //      every MMA of the CTA has retired
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   {
@@ -449,11 +457,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     for (int i = 0; i < 2; ++i) {
       mbar_init(&qdo_full[i], 1);
       mbar_init(&qdo_empty[i], 1);
+      mbar_init(&sdp_full[i], 1);
+      mbar_init(&xy_full[i], 128);
+      mbar_init(&g2_done[i], 1);
+      mbar_init(&dq_free[i], 128);
     }
-    mbar_init(sdp_full, 1);
-    mbar_init(xy_full, 128);
-    mbar_init(g2_done, 1);
-    mbar_init(dq_free, 128);
+    mbar_init(all_done, 1);
     fence_mbar_init();
     fence_proxy_async_smem();
   }
@@ -465,8 +474,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t t_s = tmem_base, t_dp = tmem_base + 64, t_dq = tmem_base + 128, t_dv = tmem_base + 256,
-                 t_dk = tmem_base + 384;
+  const uint32_t t_dv = tmem_base + 256, t_dk = tmem_base + 384;
+  // group g: S^T at columns g*128 .. +63, dP^T (later dQ^T) at g*128 + 64 .. +127
 
   if (warp == 0) {
     if (lane == 0 && n_it > 0) {
@@ -496,112 +505,116 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t id_g1 = make_idesc_bf16(128, BQ, 0, 0);    // S^T, dP^T : A K-major, B K-major
       const uint32_t id_g2 = make_idesc_bf16(128, HD, 0, 1);    // dV, dK    : A K-major, B MN-major
       const uint32_t id_dq = make_idesc_bf16(128, BQ, 1, 1);    // dQ^T      : A MN-major, B MN-major
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aX = smem_u32(sX), aY = smem_u32(sY);
-      auto g1 = [&](int it) {
-        const int st = it & 1;
-        const uint32_t bq = smem_u32(sQ + st * L::QT_BYTES), bdo = smem_u32(sDO + st * L::QT_BYTES);
+      // Descriptors are built once; inside the loops an operand advances by adding a constant to
+      // the descriptor's start-address field (16-byte units), so the issuing thread spends a few
+      // instructions per MMA and keeps ahead of the tensor pipe (the MMAs are only 128 x 64 x 16).
+      const uint64_t dK_k = make_smem_desc_sw128(smem_u32(sK), 16, 1024);            // K as K-major A
+      const uint64_t dV_k = make_smem_desc_sw128(smem_u32(sV), 16, 1024);
+      const uint64_t dK_mn = make_smem_desc_sw128(smem_u32(sK), BN * 128, 1024);     // K as MN-major A (dQ^T)
+      // stage / group 1 operands sit a fixed distance after stage / group 0: one add selects them
+      const uint64_t dQ_k0 = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+      const uint64_t dDO_k0 = make_smem_desc_sw128(smem_u32(sDO), 16, 1024);
+      const uint64_t dQ_mn0 = make_smem_desc_sw128(smem_u32(sQ), BQ * 128, 1024);
+      const uint64_t dDO_mn0 = make_smem_desc_sw128(smem_u32(sDO), BQ * 128, 1024);
+      const uint64_t dX0 = make_smem_desc_sw128(smem_u32(sX), 16, 1024);
+      const uint64_t dY_k0 = make_smem_desc_sw128(smem_u32(sY), 16, 1024);
+      const uint64_t dY_mn0 = make_smem_desc_sw128(smem_u32(sY), BN * 128, 1024);
+      auto g1 = [&](int it) {       // S^T and dP^T of tile `it` into its group's columns
+        const int g = it & 1;
+        const uint32_t t_s = tmem_base + g * 128, t_dp = t_s + 64;
+        const uint64_t bq = dQ_k0 + (uint64_t)(g * (L::QT_BYTES >> 4)), bdo = dDO_k0 + (uint64_t)(g * (L::QT_BYTES >> 4));
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t ko = (k >> 2) * (BN * 128) + (k & 3) * 32;     // K/V chunk + in-row offset
-          const uint32_t qo = (k >> 2) * (BQ * 128) + (k & 3) * 32;
-          umma_f16_ss(t_s, make_smem_desc_sw128(aK + ko, 16, 1024), make_smem_desc_sw128(bq + qo, 16, 1024), id_g1,
-                      k != 0);
+          const uint64_t ko = (uint64_t)(((k >> 2) * (BN * 128) + (k & 3) * 32) >> 4);     // K/V chunk + in-row offset
+          const uint64_t qo = (uint64_t)(((k >> 2) * (BQ * 128) + (k & 3) * 32) >> 4);
+          umma_f16_ss(t_s, dK_k + ko, bq + qo, id_g1, k != 0);
         }
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t ko = (k >> 2) * (BN * 128) + (k & 3) * 32;
-          const uint32_t qo = (k >> 2) * (BQ * 128) + (k & 3) * 32;
-          umma_f16_ss(t_dp, make_smem_desc_sw128(aV + ko, 16, 1024), make_smem_desc_sw128(bdo + qo, 16, 1024), id_g1,
-                      k != 0);
+          const uint64_t ko = (uint64_t)(((k >> 2) * (BN * 128) + (k & 3) * 32) >> 4);
+          const uint64_t qo = (uint64_t)(((k >> 2) * (BQ * 128) + (k & 3) * 32) >> 4);
+          umma_f16_ss(t_dp, dV_k + ko, bdo + qo, id_g1, k != 0);
         }
-        umma_commit(sdp_full);
+        umma_commit(&sdp_full[g]);
       };
-      bool ok = mbar_wait(kv_full, 0) && mbar_wait(&qdo_full[0], 0);
-      if (ok) {
-        tc_fence_after();
-        g1(0);
+      bool ok = mbar_wait(kv_full, 0);
+      for (int t = 0; t < 2 && t < n_it && ok; ++t) {
+        ok = mbar_wait(&qdo_full[t], 0);
+        if (ok) {
+          tc_fence_after();
+          g1(t);
+        }
       }
       for (int it = 0; it < n_it && ok; ++it) {
-        const int st = it & 1;
-        if (!mbar_wait(xy_full, it & 1)) { ok = false; break; }
+        const int g = it & 1;
+        if (!mbar_wait(&xy_full[g], (it >> 1) & 1)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t bq = smem_u32(sQ + st * L::QT_BYTES), bdo = smem_u32(sDO + st * L::QT_BYTES);
+        const uint64_t gq = (uint64_t)(g * (L::QT_BYTES >> 4)), gx = (uint64_t)(g * (L::XY_BYTES >> 4));
+        const uint64_t dXg = dX0 + gx, dYkg = dY_k0 + gx, dYmng = dY_mn0 + gx;
+        const uint64_t dQmng = dQ_mn0 + gq, dDOmng = dDO_mn0 + gq;
         // dV += P^T dO_i ; dK += dS^T Q_i   (K = 64 query rows -> 4 k-steps)
 #pragma unroll
-        for (int k = 0; k < BQ / 16; ++k) {
-          const uint64_t da = make_smem_desc_sw128(aX + k * 32, 16, 1024);
-          const uint64_t db = make_smem_desc_sw128(bdo + k * (16 * 128), BQ * 128, 1024);
-          umma_f16_ss(t_dv, da, db, id_g2, (it | k) != 0);
-        }
+        for (int k = 0; k < BQ / 16; ++k)
+          umma_f16_ss(t_dv, dXg + (uint64_t)((k * 32) >> 4), dDOmng + (uint64_t)((k * 16 * 128) >> 4), id_g2,
+                      (it | k) != 0);
 #pragma unroll
-        for (int k = 0; k < BQ / 16; ++k) {
-          const uint64_t da = make_smem_desc_sw128(aY + k * 32, 16, 1024);
-          const uint64_t db = make_smem_desc_sw128(bq + k * (16 * 128), BQ * 128, 1024);
-          umma_f16_ss(t_dk, da, db, id_g2, (it | k) != 0);
-        }
-        if (it > 0) {
-          if (!mbar_wait(dq_free, (it - 1) & 1)) { ok = false; break; }
-          tc_fence_after();
-        }
-        // dQ_i^T = K_j^T dS^T : M = head dim, N = 64 queries, K = 128 keys
+        for (int k = 0; k < BQ / 16; ++k)
+          umma_f16_ss(t_dk, dYkg + (uint64_t)((k * 32) >> 4), dQmng + (uint64_t)((k * 16 * 128) >> 4), id_g2,
+                      (it | k) != 0);
+        // dQ_i^T = K_j^T dS^T : M = head dim, N = 64 queries, K = 128 keys; over the tile's dP^T columns
+        const uint32_t t_dq = tmem_base + g * 128 + 64;
 #pragma unroll
-        for (int k = 0; k < BN / 16; ++k) {
-          const uint64_t da = make_smem_desc_sw128(aK + k * (16 * 128), BN * 128, 1024);
-          const uint64_t db = make_smem_desc_sw128(aY + k * (16 * 128), BN * 128, 1024);
-          umma_f16_ss(t_dq, da, db, id_dq, k != 0);
-        }
-        umma_commit(&qdo_empty[st]);
-        umma_commit(g2_done);
-        if (it + 1 < n_it) {
-          if (!mbar_wait(&qdo_full[(it + 1) & 1], ((it + 1) >> 1) & 1)) { ok = false; break; }
+        for (int k = 0; k < BN / 16; ++k)
+          umma_f16_ss(t_dq, dK_mn + (uint64_t)((k * 16 * 128) >> 4), dYmng + (uint64_t)((k * 16 * 128) >> 4), id_dq,
+                      k != 0);
+        umma_commit(&qdo_empty[g]);
+        umma_commit(&g2_done[g]);
+        if (it >= 1 && it + 1 < n_it) {
+          // tile it + 1 belongs to the other group: its columns are free once dQ of tile it - 1 is drained
+          const int o = g ^ 1;
+          if (!mbar_wait(&dq_free[o], ((it - 1) >> 1) & 1)) { ok = false; break; }
+          if (!mbar_wait(&qdo_full[o], ((it + 1) >> 1) & 1)) { ok = false; break; }
           tc_fence_after();
           g1(it + 1);
         }
       }
-      if (!ok) atomicExch(args.status, NB_ERR_TIMEOUT_MMA);
+      if (ok) umma_commit(all_done);
+      else atomicExch(args.status, NB_ERR_TIMEOUT_MMA);
     }
   } else if (warp >= 4) {
-    const int wq = warp & 3;
+    const int grp = (warp - 4) >> 2;        // math group: 0 = even query tiles, 1 = odd ones
+    const int wq = warp & 3;                // TMEM lane quarter this warp may read
     const int r = wq * 32 + lane;           // key row inside the tile / head-dim row for dQ^T
-    const int et = threadIdx.x - 128;
+    const int et = (threadIdx.x - 128) & 127;
     const int key = k0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;
+    const uint32_t t_s = tmem_base + grp * 128, t_dp = t_s + 64;
     const long long bh = (long long)b * args.H + h;
+    uint8_t* xr = sX + grp * L::XY_BYTES + r * 128;
+    uint8_t* yr = sY + grp * L::XY_BYTES + r * 128;
+    const bool key_ok = key < args.Skv;
     bool ok = true;
-    auto drain_dq = [&](int it) {
-      // dQ^T tile: this thread holds head-dim row r, 64 consecutive queries
+    for (int it = grp; it < n_it; it += 2) {
       const int q0 = (i_start + it) * BQ;
-      float* dst = args.dq_acc + (bh * HD + r) * (long long)args.Sq_pad + q0;
-#pragma unroll
-      for (int c = 0; c < BQ / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_dq + lane_addr + c * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-          red_add_v4(dst + c * 32 + u * 4, __uint_as_float(v[u * 4]), __uint_as_float(v[u * 4 + 1]),
-                     __uint_as_float(v[u * 4 + 2]), __uint_as_float(v[u * 4 + 3]));
-      }
-    };
-    for (int it = 0; it < n_it; ++it) {
-      const int q0 = (i_start + it) * BQ;
-      const int pb = it & 1;
-      // stage the per-query statistics of this tile
+      const uint32_t ph = (it >> 1) & 1;
+      // stage the per-query statistics of this tile (the group's previous tile is fully consumed)
       {
         const int qi = q0 + (et & 63);
         const bool inr = qi < args.Sq;
-        if (et < 64) s_lse2[pb * BQ + et] = inr ? args.lse[bh * args.Sq + qi] * 1.4426950408889634f : INFINITY;
-        else s_delta[pb * BQ + (et - 64)] = inr ? args.delta[bh * args.Sq + qi] : 0.f;
+        if (et < 64) s_lse2[grp * BQ + et] = inr ? args.lse[bh * args.Sq + qi] * 1.4426950408889634f : INFINITY;
+        else s_delta[grp * BQ + (et - 64)] = inr ? args.delta[bh * args.Sq + qi] : 0.f;
       }
-      named_bar_sync(1, 128);
-      if (ok && !mbar_wait(sdp_full, it & 1)) {
+      named_bar_sync(1 + grp, 128);
+      if (ok && !mbar_wait(&sdp_full[grp], ph)) {
         atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
         ok = false;
       }
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      float p[BQ], ds[BQ];
+      const bool need_mask = args.causal && (k0 + BN - 1 > q0 + off);
+      // the MMAs that read this group's P^T / dS^T buffers belong to its previous tile; their
+      // retirement was awaited before that tile's dQ was drained, so the buffers are free
 #pragma unroll
       for (int c = 0; c < BQ / 32; ++c) {
         uint32_t v[32], w[32];
@@ -610,99 +623,93 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          p[c * 32 + i] = __uint_as_float(v[i]);
-          ds[c * 32 + i] = __uint_as_float(w[i]);
+          const int qc = c * 32 + i;
+          float pv = exp2f(__uint_as_float(v[i]) * args.scale_log2 - s_lse2[grp * BQ + qc]);
+          if (!key_ok || (need_mask && key > q0 + qc + off)) pv = 0.f;
+          const float dsv = pv * (__uint_as_float(w[i]) - s_delta[grp * BQ + qc]) * args.scale;
+          v[i] = __float_as_uint(pv);
+          w[i] = __float_as_uint(dsv);
         }
-      }
-      const bool need_mask = args.causal && (k0 + BN - 1 > q0 + off);
-      const bool key_ok = key < args.Skv;
+        // X = P^T, Y = dS^T as bf16, one 128-byte swizzled row per key (4 x 16 bytes per 32 queries)
 #pragma unroll
-      for (int c = 0; c < BQ; ++c) {
-        float pv = exp2f(p[c] * args.scale_log2 - s_lse2[pb * BQ + c]);
-        if (!key_ok || (need_mask && key > q0 + c + off)) pv = 0.f;
-        p[c] = pv;
-        ds[c] = pv * (ds[c] - s_delta[pb * BQ + c]) * args.scale;
-      }
-      if (it > 0) {
-        if (!mbar_wait(g2_done, (it - 1) & 1)) {
-          atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
-          ok = false;
-        }
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-      }
-      // X = P^T, Y = dS^T as bf16, one 128-byte swizzled row per key
-      {
-        uint8_t* xr = sX + r * 128;
-        uint8_t* yr = sY + r * 128;
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < 4; ++u) {
           uint4 px, py;
           uint32_t* wx = reinterpret_cast<uint32_t*>(&px);
           uint32_t* wy = reinterpret_cast<uint32_t*>(&py);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            __nv_bfloat162 a = __floats2bfloat162_rn(p[u * 8 + 2 * e], p[u * 8 + 2 * e + 1]);
-            __nv_bfloat162 d2 = __floats2bfloat162_rn(ds[u * 8 + 2 * e], ds[u * 8 + 2 * e + 1]);
+            __nv_bfloat162 a = __floats2bfloat162_rn(__uint_as_float(v[u * 8 + 2 * e]), __uint_as_float(v[u * 8 + 2 * e + 1]));
+            __nv_bfloat162 d2 = __floats2bfloat162_rn(__uint_as_float(w[u * 8 + 2 * e]), __uint_as_float(w[u * 8 + 2 * e + 1]));
             wx[e] = *reinterpret_cast<uint32_t*>(&a);
             wy[e] = *reinterpret_cast<uint32_t*>(&d2);
           }
-          const int sw = (u ^ (r & 7)) << 4;
+          const int sw = ((c * 4 + u) ^ (r & 7)) << 4;
           *reinterpret_cast<uint4*>(xr + sw) = px;
           *reinterpret_cast<uint4*>(yr + sw) = py;
         }
       }
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(xy_full);
-      if (it > 0) {
-        drain_dq(it - 1);
-        tc_fence_before();
-        mbar_arrive(dq_free);
-      }
-    }
-    if (ok && n_it > 0) {
-      if (!mbar_wait(g2_done, (n_it - 1) & 1)) {
+      mbar_arrive(&xy_full[grp]);
+      // dQ^T of this tile: wait for its MMAs, then reduce it into the fp32 scratch
+      if (!mbar_wait(&g2_done[grp], ph)) {
         atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
         ok = false;
       }
       ok = __all_sync(0xffffffffu, ok);
-      if (ok) {
-        tc_fence_after();
-        drain_dq(n_it - 1);
+      if (!ok) break;
+      tc_fence_after();
+      {
+        float* dst = args.dq_acc + (bh * HD + r) * (long long)args.Sq_pad + q0;
+#pragma unroll
+        for (int c = 0; c < BQ / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_dp + lane_addr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            red_add_v4(dst + c * 32 + u * 4, __uint_as_float(v[u * 4]), __uint_as_float(v[u * 4 + 1]),
+                       __uint_as_float(v[u * 4 + 2]), __uint_as_float(v[u * 4 + 3]));
+        }
       }
+      tc_fence_before();
+      mbar_arrive(&dq_free[grp]);
+    }
+    if (ok && n_it > 0) {
+      if (!mbar_wait(all_done, 0)) {
+        atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) tc_fence_after();
     }
     if (ok) {
-      // dK, dV rows of this key
-      __nv_bfloat16* dkr = args.dK + (long long)b * args.dk_sb + (long long)h * args.dk_sh + (long long)key * args.dk_ss;
-      __nv_bfloat16* dvr = args.dV + (long long)b * args.dv_sb + (long long)h * args.dv_sh + (long long)key * args.dv_ss;
+      // group 0 writes this key's dK row, group 1 its dV row
+      __nv_bfloat16* dst = grp == 0
+          ? args.dK + (long long)b * args.dk_sb + (long long)h * args.dk_sh + (long long)key * args.dk_ss
+          : args.dV + (long long)b * args.dv_sb + (long long)h * args.dv_sh + (long long)key * args.dv_ss;
+      const uint32_t src = grp == 0 ? t_dk : t_dv;
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        __nv_bfloat16* dst = which ? dvr : dkr;
-        const uint32_t src = which ? t_dv : t_dk;
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t v[32];
+        if (n_it > 0) {
+          tmem_ld_32x32(src + lane_addr + c * 32, v);
+          tmem_ld_wait();
+        } else {
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t v[32];
-          if (n_it > 0) {
-            tmem_ld_32x32(src + lane_addr + c * 32, v);
-            tmem_ld_wait();
-          } else {
+          for (int i = 0; i < 32; ++i) v[i] = 0;
+        }
+        if (key_ok) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0;
-          }
-          if (key < args.Skv) {
+          for (int u = 0; u < 4; ++u) {
+            uint4 pk;
+            uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              uint4 pk;
-              uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(v[u * 8 + 2 * e]), __uint_as_float(v[u * 8 + 2 * e + 1]));
-                pw[e] = *reinterpret_cast<uint32_t*>(&hh);
-              }
-              *reinterpret_cast<uint4*>(dst + c * 32 + u * 8) = pk;
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(v[u * 8 + 2 * e]), __uint_as_float(v[u * 8 + 2 * e + 1]));
+              pw[e] = *reinterpret_cast<uint32_t*>(&hh);
             }
+            *reinterpret_cast<uint4*>(dst + c * 32 + u * 8) = pk;
           }
         }
       }
@@ -895,7 +902,7 @@ extern "C" int nb_attn_bwd(const void* dO, const void* q, const void* k, const v
     configured = true;
   }
   const int nkt = (Skv + BN - 1) / BN;
-  attn_bwd_kernel<<<(unsigned)((long long)nkt * H * B), NTHREADS, BwdSmem::TOTAL, s>>>(tq, tk, tv, tdo, a);
+  attn_bwd_kernel<<<(unsigned)((long long)nkt * H * B), BWD_THREADS, BwdSmem::TOTAL, s>>>(tq, tk, tv, tdo, a);
   dim3 grid((Sq + 31) / 32, (D + 31) / 32, B * H);
   attn_dq_convert_kernel<<<grid, 256, 0, s>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), H, Sq, Sq_pad, D, dq_sb, dq_sh,
                                               dq_ss);

@@ -140,7 +140,16 @@ __global__ void __launch_bounds__(128) layernorm_fwd_kernel(const T* __restrict_
   }
 }
 
-// Backward, part 1: dx. One warp per row, the row stays in registers (like the forward).
+// Backward, part 1: dx. One warp per row. The row's x and dy stay in registers in their packed
+// 16-byte form (half the registers of keeping them as floats, so twice as many rows are in flight
+// per SM for this bandwidth-bound pass) and are unpacked once for the two sums and once for dx.
+template <typename T>
+__device__ __forceinline__ void unpack_vec(const uint4& raw, float* out) {
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < Vec<T>::N; ++i) out[i] = to_f<T>(e[i]);
+}
+
 template <typename T, int VPL>
 __global__ void __launch_bounds__(128) layernorm_bwd_dx_kernel(const T* __restrict__ dy, const T* __restrict__ x,
                                                               const T* __restrict__ gamma, const float* __restrict__ mean,
@@ -152,23 +161,30 @@ __global__ void __launch_bounds__(128) layernorm_bwd_dx_kernel(const T* __restri
   if (row >= rows) return;
   const T* xr = x + (size_t)row * D;
   const T* dyr = dy + (size_t)row * D;
+  uint4 xraw[VPL], draw[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = (i * 32 + lane) * V;
+    if (c < D) {
+      xraw[i] = *reinterpret_cast<const uint4*>(xr + c);
+      draw[i] = *reinterpret_cast<const uint4*>(dyr + c);
+    }
+  }
   const float mu = mean[row], rs = rstd[row];
-  float xh[VPL][V], g[VPL][V];
   float s1 = 0.f, s2 = 0.f;
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     const int c = (i * 32 + lane) * V;
     if (c < D) {
       float xv[V], dv[V], gm[V];
-      load_vec<T>(xr + c, xv);
-      load_vec<T>(dyr + c, dv);
+      unpack_vec<T>(xraw[i], xv);
+      unpack_vec<T>(draw[i], dv);
       if (gamma) load_vec<T>(gamma + c, gm);
 #pragma unroll
       for (int j = 0; j < V; ++j) {
-        xh[i][j] = (xv[j] - mu) * rs;
-        g[i][j] = dv[j] * (gamma ? gm[j] : 1.f);
-        s1 += g[i][j];
-        s2 += g[i][j] * xh[i][j];
+        const float g = dv[j] * (gamma ? gm[j] : 1.f);
+        s1 += g;
+        s2 += g * (xv[j] - mu) * rs;
       }
     }
   }
@@ -179,9 +195,15 @@ __global__ void __launch_bounds__(128) layernorm_bwd_dx_kernel(const T* __restri
   for (int i = 0; i < VPL; ++i) {
     const int c = (i * 32 + lane) * V;
     if (c < D) {
-      float o[V];
+      float xv[V], dv[V], gm[V], o[V];
+      unpack_vec<T>(xraw[i], xv);
+      unpack_vec<T>(draw[i], dv);
+      if (gamma) load_vec<T>(gamma + c, gm);
 #pragma unroll
-      for (int j = 0; j < V; ++j) o[j] = (g[i][j] - s1 - xh[i][j] * s2) * rs;
+      for (int j = 0; j < V; ++j) {
+        const float g = dv[j] * (gamma ? gm[j] : 1.f);
+        o[j] = (g - s1 - (xv[j] - mu) * rs * s2) * rs;
+      }
       store_vec<T>(dxr + c, o);
     }
   }

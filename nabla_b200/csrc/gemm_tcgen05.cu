@@ -1215,8 +1215,11 @@ extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* 
   if (mode == MODE_AG) {
     if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(aux_out) & 15)) return -11;
     g.out = out; g.bias = bias; g.bias_fp32 = bias_fp32; g.epi = epi; g.gelu_tanh = gelu_tanh;
-    g.aux = aux == AUX_STORE_PREACT ? AUX_STORE_PREACT : AUX_NONE;
+    // aux 1: aux_out receives the pre-activation; aux 2 / 3: aux_out holds z and the result is
+    // multiplied by relu'(z) / gelu'(z) (activation backward fused into the epilogue)
+    g.aux = (aux == AUX_STORE_PREACT || aux == AUX_MUL_DRELU || aux == AUX_MUL_DGELU) ? aux : AUX_NONE;
     g.aux_out = reinterpret_cast<__nv_bfloat16*>(aux_out);
+    g.aux_in = reinterpret_cast<const __nv_bfloat16*>(aux_out);
     g.ld_aux = N; g.stride_aux = (long long)M * N;
   } else {
     g.out = reinterpret_cast<char*>(ws_local) + data_off;

@@ -374,7 +374,7 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_rows
 
 def all_gather_gemm(a_shard: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_rows: int, bias: torch.Tensor | None = None,
                     epilogue: str = "none", gelu_tanh: bool = False, store_preact: bool = False,
-                    comm_ctas: int | None = None, arena_off: int | None = None):
+                    comm_ctas: int | None = None, arena_off: int | None = None, dact: tuple | None = None):
     """``epilogue(gather(a) @ b + bias)`` in one kernel. ``a_shard`` is this rank's rows
     (M / world, K). The tensor-core CTAs start on the own rows (read in place) while copy CTAs of
     the same launch move the other rows over NVLink; each later tile waits only for its own
@@ -385,6 +385,9 @@ def all_gather_gemm(a_shard: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_ro
     into all peers' copies with posted bulk stores: no round trip to wait for, a handful of copy
     CTAs keep the link busy, and nothing has to be staged. Without it the rows are staged in the
     workspace and PULLED by the consumer (bulk loads through shared memory).
+
+    ``dact=(z, activation)`` multiplies the product by ``activation'(z)`` in the epilogue (the
+    backward of a fused linear + activation; ``z`` is (M, N)).
 
     Returns ``(a_full, out)`` or ``(a_full, out, preact)``; ``a_full`` (M, K) is the all-gather's
     own result, kept for the backward pass."""
@@ -424,8 +427,14 @@ def all_gather_gemm(a_shard: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_ro
         need = (M - Ml) * K * 2 / max(gemm_s, 1e-6) / (38e9 if push else 32e9)
         comm_ctas = int(min(20, max(4, need + 1.5)))
     n_comm = comm_ctas
-    _launch_fused(MODE_AG, ws, x, b3, out, bias, pre, a_full, M, N, K, K, ldb, 0, 1 if bkind == "row" else 0,
-                  _EPI[epilogue], 1 if store_preact else 0, gelu_tanh, chunk_rows, n_comm,
+    aux_code, aux_t = (1 if store_preact else 0), pre
+    if dact is not None:
+        z, act = dact
+        aux_t = z.reshape(M, N).contiguous()
+        aux_code = 2 if act == "relu" else 3
+        gelu_tanh = act == "gelu_tanh"
+    _launch_fused(MODE_AG, ws, x, b3, out, bias, aux_t, a_full, M, N, K, K, ldb, 0, 1 if bkind == "row" else 0,
+                  _EPI[epilogue], aux_code, gelu_tanh, chunk_rows, n_comm,
                   ws.arena.ptrs_dev if push else 0, arena_off or 0)
     cur.wait_stream(side)
     return (a_full, out, pre) if store_preact else (a_full, out)
