@@ -105,6 +105,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=24, help="debug only: a run with fewer layers is not a valid number")
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
+    ap.add_argument("--tp", type=int, default=0, help="debug only: tensor-parallel width (default min(N, 4), the benchmark's mesh)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -132,7 +133,7 @@ def main() -> None:
     dev = nb.Accelerator(local)
     tdev = dev.to_torch()
     cfg = T.TransformerConfig(n_layers=args.layers)
-    tp = min(n, 4)
+    tp = args.tp if args.tp > 0 else min(n, 4)
     dp = n // tp
     mesh = nb.DeviceMesh("mesh", (dp, tp), ("dp", "tp")) if n > 1 else None
     global_batch = args.seqs_per_gpu * n

@@ -12,6 +12,10 @@ CUDA bf16 tensors:
   NVLink while later tiles are still being multiplied).
 * ``matmul -> dact_mul`` (backward of linear + relu/gelu): the activation derivative is applied in
   the GEMM epilogue.
+* compiled replays with donated optimizer state: ``matmul -> all_reduce(dp) -> adam_wstep`` becomes a
+  GEMM that writes its (unreduced) weight gradient into a symmetric arena plus one kernel that sums
+  the ranks' gradients while reading them and applies AdamW in place (``gemm_to_arena`` /
+  ``adamw_reduce`` steps, set up by ``transforms/compile.py``).
 * ``all_gather(rows) -> linear | matmul [-> dact_mul]``: one launch that pulls the peers' rows while the tensor
   cores already work on the rows that are there; the gathered tensor is still produced.
 
@@ -352,6 +356,47 @@ def run_fused(kind: str, group: list[OpNode], keep_graph: bool = False, arena_bl
         else:
             _plain(mm, keep_graph)
             _plain(da, keep_graph)
+        return
+    if kind == "gemm_to_arena":
+        # weight gradient of a data-parallel replica group: keep it unreduced, in the arena; the
+        # matching adamw_reduce step sums it over the group while it reads it
+        from ...native.gemm import gemm_bf16
+        from ...parallel import symm
+
+        mm, ar = group
+        a, b = [x._buffers[0] for x in mm.input_impls()]
+        ar_out = ar.outputs()[0]
+        mesh = ar.input_impls()[0].sharding.mesh
+        axes = [x for x in mesh.axis_names if x in ar.kwargs["reduce_axes"]]
+        arena = symm.arena(mesh, axes) if arena_blocks is not None else None
+        m_rows = a.numel() // max(a.shape[-1], 1)
+        nbytes = m_rows * b.shape[-1] * 2
+        off = arena.alloc(nbytes) if (arena is not None and ar_out is not None and a.dim() == 2
+                                      and os.environ.get("NABLA_B200_FUSE_DP_ADAMW", "0") == "1") else None
+        if off is None:
+            return run_fused("gemm_all_reduce", group, keep_graph, arena_blocks)
+        out = arena.buf[off: off + nbytes].view(torch.bfloat16).view(m_rows, b.shape[-1])
+        gemm_bf16(a, b, out=out)
+        arena_blocks[id(ar_out)] = (arena, off)
+        _store(ar, [[out]], keep_graph)
+        return
+    if kind == "adamw_reduce":
+        from ...parallel import backend, symm
+
+        (ad,) = group
+        ins = ad.input_impls()
+        blk = arena_blocks.get(id(ins[1])) if arena_blocks is not None else None
+        if blk is None:
+            return _plain(ad, keep_graph)
+        kw = ad.kwargs
+        p_, m_, v_ = ins[0]._buffers[0], ins[2]._buffers[0], ins[3]._buffers[0]
+        hyper = ins[4]._buffers[0].contiguous() if (len(ins) > 4 and kw.get("bias_correction", True)) else None
+        mesh, axes = arena_blocks[("dp_group", id(ad))]
+        symm.adamw_reduce(p_, m_, v_, blk[1], mesh, axes, lr=kw["lr"], b1=kw["beta1"], b2=kw["beta2"], eps=kw["eps"],
+                          wd=kw["weight_decay"], step=kw.get("step_value") if kw.get("bias_correction", True) else None,
+                          hyper=hyper)
+        backend.stats["fused_dp_adamw"] = backend.stats.get("fused_dp_adamw", 0) + 1
+        _store(ad, [[p_], [m_], [v_]], keep_graph)
         return
     if kind == "gemm_all_reduce":
         from ...parallel import backend, symm

@@ -247,6 +247,94 @@ __global__ void __launch_bounds__(512) gather_kernel(Group g, long long off, T* 
 
 __global__ void barrier_kernel(Group g) { block_barrier(g, 0); }
 
+// ---------------------------------------------------------------- gradient all-reduce + AdamW
+// One kernel for the data-parallel update of one parameter: every rank's gradient (bf16) sits at
+// the same offset of a symmetric arena; after a barrier (all gradients written) each rank sums them
+// (multimem.ld_reduce through the switch, or one load per peer), scales, and applies AdamW to its
+// own copy of p / m / v in place; a closing barrier keeps the gradients alive until every peer has
+// read them. No reduced gradient is ever written to memory, and the replicas stay bit-identical
+// because every rank adds the same values in the same order.
+//   hyper = [lr, 1 - b1^t, 1 - b2^t, grad_scale] (device) overrides the scalar arguments.
+__global__ void __launch_bounds__(256) adamw_reduce_kernel(Group g, void* const* grad_bufs, const char* grad_mc,
+                                                          long long grad_off, __nv_bfloat16* p, float* m, float* v,
+                                                          long long n, float lr, float b1, float b2, float eps, float wd,
+                                                          float bc1, float bc2, float grad_scale, const float* hyper) {
+  if (!block_barrier(g, 0)) return;
+  if (hyper) { lr = hyper[0]; bc1 = hyper[1]; bc2 = hyper[2]; grad_scale = hyper[3]; }
+  const float ibc1 = 1.f / bc1, ibc2 = 1.f / bc2;
+  const long long nv = n / 8;                                  // 16-byte vectors of bf16 (n % 8 == 0)
+  constexpr int U = 4;                                         // vectors per thread in flight per peer
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthr = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = tid; i0 < nv; i0 += nthr * U) {
+    float gr[U][8];
+    if (grad_mc != nullptr) {
+      V4 r[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * nthr;
+        if (i < nv)
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(r[u].x), "=r"(r[u].y), "=r"(r[u].z), "=r"(r[u].w)
+                       : "l"(grad_mc + grad_off + i * 16)
+                       : "memory");
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) Acc<__nv_bfloat16>::unpack(r[u], gr[u]);
+    } else {
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) gr[u][j] = 0.f;
+      for (int q = 0; q < g.world; ++q) {
+        const char* src = reinterpret_cast<const char*>(grad_bufs[q]) + grad_off;
+        V4 r[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * nthr;
+          r[u] = V4{0u, 0u, 0u, 0u};
+          if (i < nv)
+            asm volatile("ld.global.relaxed.sys.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(r[u].x), "=r"(r[u].y), "=r"(r[u].z), "=r"(r[u].w)
+                         : "l"(src + i * 16)
+                         : "memory");
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          float f[8];
+          Acc<__nv_bfloat16>::unpack(r[u], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) gr[u][j] += f[j];
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * nthr;
+      if (i >= nv) break;
+      float pv[8], mv[8], vv[8];
+      Acc<__nv_bfloat16>::unpack(reinterpret_cast<const V4*>(p)[i], pv);
+      const float4 m0 = reinterpret_cast<const float4*>(m)[2 * i], m1 = reinterpret_cast<const float4*>(m)[2 * i + 1];
+      const float4 v0 = reinterpret_cast<const float4*>(v)[2 * i], v1 = reinterpret_cast<const float4*>(v)[2 * i + 1];
+      mv[0] = m0.x; mv[1] = m0.y; mv[2] = m0.z; mv[3] = m0.w; mv[4] = m1.x; mv[5] = m1.y; mv[6] = m1.z; mv[7] = m1.w;
+      vv[0] = v0.x; vv[1] = v0.y; vv[2] = v0.z; vv[3] = v0.w; vv[4] = v1.x; vv[5] = v1.y; vv[6] = v1.z; vv[7] = v1.w;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float gj = gr[u][j] * grad_scale;
+        mv[j] = b1 * mv[j] + (1.f - b1) * gj;
+        vv[j] = b2 * vv[j] + (1.f - b2) * gj * gj;
+        pv[j] -= lr * ((mv[j] * ibc1) / (sqrtf(vv[j] * ibc2) + eps) + wd * pv[j]);
+      }
+      reinterpret_cast<V4*>(p)[i] = Acc<__nv_bfloat16>::pack(pv);
+      reinterpret_cast<float4*>(m)[2 * i] = make_float4(mv[0], mv[1], mv[2], mv[3]);
+      reinterpret_cast<float4*>(m)[2 * i + 1] = make_float4(mv[4], mv[5], mv[6], mv[7]);
+      reinterpret_cast<float4*>(v)[2 * i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+      reinterpret_cast<float4*>(v)[2 * i + 1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+    }
+  }
+  block_barrier(g, 1);
+}
+
 // A wait on a flag that nobody sets: exercises the bounded-wait error path without any fault.
 __global__ void wait_flag_kernel(const unsigned* flag, unsigned target, int* status, unsigned long long limit_ns) {
   if (threadIdx.x == 0 && blockIdx.x == 0) {
@@ -304,6 +392,24 @@ int nb_comm_gather(void* const* bufs, int rank, int world, unsigned* epoch_ctr, 
   Group g = make_group(bufs, nullptr, rank, world, epoch_ctr, status);
   if (dtype) gather_kernel<__nv_bfloat16><<<blocks, 512, 0, STREAM>>>(g, off, (__nv_bfloat16*)out, chunk_elems, mode, op);
   else gather_kernel<float><<<blocks, 512, 0, STREAM>>>(g, off, (float*)out, chunk_elems, mode, op);
+  bump_kernel<<<1, 1, 0, STREAM>>>(epoch_ctr, 1u);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// Fused data-parallel gradient all-reduce + AdamW step (see adamw_reduce_kernel). `grad_bufs`:
+// device array [world] of the arena base pointers, `grad_mc`: the arena's multicast base or null,
+// `grad_off`: byte offset of this parameter's bf16 gradient in the arena; n must be a multiple of 8;
+// p bf16, m / v fp32, all 16-byte aligned, updated in place.
+int nb_comm_adamw_reduce(void* const* bufs, int rank, int world, unsigned* epoch_ctr, void* const* grad_bufs,
+                         void* grad_mc, long long grad_off, void* p, float* m, float* v, long long n, float lr,
+                         float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale,
+                         const float* hyper, int blocks, int* status, void* stream) {
+  if (world > MAX_WORLD || blocks > MAX_BLOCKS || blocks < 1) return -2;
+  if ((n & 7) || (grad_off & 15)) return -12;
+  Group g = make_group(bufs, nullptr, rank, world, epoch_ctr, status);
+  adamw_reduce_kernel<<<blocks, 256, 0, STREAM>>>(g, grad_bufs, reinterpret_cast<const char*>(grad_mc), grad_off,
+                                                  reinterpret_cast<__nv_bfloat16*>(p), m, v, n, lr, b1, b2, eps, wd, bc1,
+                                                  bc2, grad_scale, hyper);
   bump_kernel<<<1, 1, 0, STREAM>>>(epoch_ctr, 1u);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -33,6 +33,11 @@ def _stage_fn(x, w, b):
     return relu(matmul(x, w) + b)
 
 
+def _stage_fn2(x, w1, b1, w2, b2):
+    """Two Linear + relu per stage (the PP x DP configuration)."""
+    return relu(matmul(relu(matmul(x, w1) + b1), w2) + b2)
+
+
 def _stage_mask(n_stages: int, index: int, like: Tensor, mesh, stage_axis: str) -> Tensor:
     """(S,1,1) boolean selecting one stage, laid out over the stage axis."""
     m = np.zeros((n_stages, 1, 1), dtype=bool)
@@ -52,12 +57,18 @@ def _perm(mesh, stage_axis: str) -> list[tuple[int, int]]:
     return perm
 
 
-def gpipe_forward(w: Tensor, b: Tensor, xs: Tensor, mesh, stage_axis: str = "stage", dp_axis: str | None = None) -> Tensor:
+def gpipe_forward(w, b, xs: Tensor, mesh, stage_axis: str = "stage", dp_axis: str | None = None) -> Tensor:
     """Run ``xs`` (micro_batches, batch, dim) through the S-stage pipe; returns the last stage's
-    outputs, shape (micro_batches, batch, dim)."""
+    outputs, shape (micro_batches, batch, dim). ``w`` / ``b`` are the stacked (S, ...) stage
+    parameters, or pairs ``(w1, w2)`` / ``(b1, b2)`` for stages of two Linear + relu."""
     S = mesh.get_axis_size(stage_axis)
     MB, B, D = (int(d) for d in xs.shape)
-    step = vmap(_stage_fn, in_axes=(0, 0, 0), spmd_axis_name=stage_axis, mesh=mesh)
+    two = isinstance(w, (tuple, list))
+    if two:
+        step2 = vmap(_stage_fn2, in_axes=(0, 0, 0, 0, 0), spmd_axis_name=stage_axis, mesh=mesh)
+        step = lambda x_, w_, b_: step2(x_, w[0], unsqueeze(b[0], axis=1), w[1], unsqueeze(b[1], axis=1))
+    else:
+        step = vmap(_stage_fn, in_axes=(0, 0, 0), spmd_axis_name=stage_axis, mesh=mesh)
     state_spec = (stage_axis, dp_axis, None)
     state = shard(zeros((S, B, D), dtype=xs.dtype, device=xs.device), mesh, state_spec)
     first = _stage_mask(S, 0, xs, mesh, stage_axis)
@@ -69,7 +80,7 @@ def gpipe_forward(w: Tensor, b: Tensor, xs: Tensor, mesh, stage_axis: str = "sta
         fresh = xs[t] if t < MB else zero_x
         fresh = shard(broadcast_to(unsqueeze(fresh, axis=0), (S, B, D)), mesh, state_spec)
         inp = where(first, fresh, state)
-        computed = step(inp, w, unsqueeze(b, axis=1))
+        computed = step(inp, w, None if two else unsqueeze(b, axis=1))
         if t >= S - 1:
             # the last stage's row, extracted by masking and summing over the stage axis
             outs.append(reduce_sum(where(last, computed, zeros_like_state(computed)), axis=0))
@@ -83,7 +94,7 @@ def zeros_like_state(t: Tensor) -> Tensor:
     return zeros_like(t)
 
 
-def gpipe_loss(w: Tensor, b: Tensor, xs: Tensor, ys: Tensor, mesh, stage_axis: str = "stage",
+def gpipe_loss(w, b, xs: Tensor, ys: Tensor, mesh, stage_axis: str = "stage",
                dp_axis: str | None = None) -> Tensor:
     out = gpipe_forward(w, b, xs, mesh, stage_axis, dp_axis)
     d = out - ys

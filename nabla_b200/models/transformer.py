@@ -107,7 +107,42 @@ def init_params(cfg: TransformerConfig, mesh=None, tp_axis: str | None = "tp", d
     }
 
 
-def block(x: Tensor, p: dict[str, Tensor], cfg: TransformerConfig, sp: SeqParallel | None = None) -> Tensor:
+def init_lora(params: dict[str, Any], cfg: TransformerConfig, rank: int = 16, init_std: float = 0.02, mesh=None,
+              tp_axis: str | None = "tp") -> list[dict[str, Any]]:
+    """Rank-``rank`` adapters (A ~ N(0, init_std), B = 0) on the q/k/v (packed) and o projections of
+    every layer. With a mesh the adapters follow their frozen weight's split: for the column-parallel
+    ``wqkv`` B is split over ``tp_axis``, for the row-parallel ``wo`` A is."""
+    from ..nn.finetune.lora import init_lora_adapter
+
+    out = []
+    for L in params["layers"]:
+        qkv = init_lora_adapter(L["wqkv"], rank, init_std)
+        o = init_lora_adapter(L["wo"], rank, init_std)
+        if mesh is not None and tp_axis:
+            qkv = {"A": qkv["A"].shard(mesh, (None, None)), "B": qkv["B"].shard(mesh, (None, tp_axis))}
+            o = {"A": o["A"].shard(mesh, (tp_axis, None)), "B": o["B"].shard(mesh, (None, None))}
+        out.append({"qkv": qkv, "o": o})
+    return out
+
+
+def _lora_linear(x: Tensor, w: Tensor, b: Tensor | None, ad: dict[str, Tensor] | None, alpha: float) -> Tensor:
+    y = F.linear(x, w, b)
+    if ad is None:
+        return y
+    A, B = ad["A"], ad["B"]
+    return y + ((x @ A) @ B) * (alpha / float(int(A.shape[1])))
+
+
+def block(x: Tensor, p: dict[str, Tensor], cfg: TransformerConfig, sp: SeqParallel | None = None,
+          lora: dict[str, Any] | None = None, lora_alpha: float = 16.0) -> Tensor:
+    if lora is not None:
+        h = F.layer_norm(x, p["ln1_g"], p["ln1_b"])
+        qkv = _lora_linear(h, p["wqkv"], p["bqkv"], lora["qkv"], lora_alpha)
+        a = fused.packed_self_attention(qkv, cfg.head_dim, causal=True)
+        x = x + _lora_linear(a, p["wo"], p["bo"], lora["o"], lora_alpha)
+        h = F.layer_norm(x, p["ln2_g"], p["ln2_b"])
+        m = F.linear(h, p["w1"], p["b1"], activation="gelu")
+        return x + F.linear(m, p["w2"], p["b2"])
     if sp is None:
         h = F.layer_norm(x, p["ln1_g"], p["ln1_b"])
         qkv = F.linear(h, p["wqkv"], p["bqkv"])
@@ -126,7 +161,8 @@ def block(x: Tensor, p: dict[str, Tensor], cfg: TransformerConfig, sp: SeqParall
     return x + (sp.tokens_split(F.linear(m, p["w2"])) + p["b2"])
 
 
-def forward(params: dict[str, Any], tokens: Tensor, cfg: TransformerConfig, sp: SeqParallel | None = None) -> Tensor:
+def forward(params: dict[str, Any], tokens: Tensor, cfg: TransformerConfig, sp: SeqParallel | None = None,
+            lora: list[dict[str, Any]] | None = None) -> Tensor:
     """tokens (B, S) int64 -> logits (B, S, vocab)."""
     S = int(tokens.shape[1])
     x = gather(params["tok_emb"], tokens, axis=0)
@@ -136,8 +172,8 @@ def forward(params: dict[str, Any], tokens: Tensor, cfg: TransformerConfig, sp: 
     x = x + pos
     if sp is not None:
         x = sp.tokens_split(x)
-    for p in params["layers"]:
-        x = block(x, p, cfg, sp)
+    for li, p in enumerate(params["layers"]):
+        x = block(x, p, cfg, sp, lora[li] if lora is not None else None)
     x = F.layer_norm(x, params["lnf_g"], params["lnf_b"])
     if sp is not None:
         x = sp.tokens_whole(x)
@@ -145,11 +181,11 @@ def forward(params: dict[str, Any], tokens: Tensor, cfg: TransformerConfig, sp: 
 
 
 def loss_fn(params: dict[str, Any], tokens: Tensor, targets: Tensor, cfg: TransformerConfig,
-            sp: SeqParallel | None = None) -> Tensor:
+            sp: SeqParallel | None = None, lora: list[dict[str, Any]] | None = None) -> Tensor:
     """Mean next-token cross-entropy over all positions (fp32 scalar)."""
     from ..ops.reduction import reduce_sum
 
-    logits = forward(params, tokens, cfg, sp)
+    logits = forward(params, tokens, cfg, sp, lora)
     rows = fused.cross_entropy_rows(logits, targets)
     n = int(tokens.shape[0]) * int(tokens.shape[1])
     return reduce_sum(rows) * (1.0 / n)

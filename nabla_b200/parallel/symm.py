@@ -41,6 +41,9 @@ def _L():
         lib.nb_comm_gather.argtypes = [c_vp, c_int, c_int, c_vp, c_ll, c_vp, c_ll, c_int, c_int, c_int, c_int, c_vp, c_vp]
         lib.nb_comm_barrier.restype = c_int
         lib.nb_comm_barrier.argtypes = [c_vp, c_int, c_int, c_vp, c_vp, c_vp]
+        lib.nb_comm_adamw_reduce.restype = c_int
+        lib.nb_comm_adamw_reduce.argtypes = ([c_vp, c_int, c_int, c_vp, c_vp, c_vp, c_ll, c_vp, c_vp, c_vp, c_ll] +
+                                             [ctypes.c_float] * 8 + [c_vp, c_int, c_vp, c_vp])
         lib.nb_comm_wait_flag.restype = c_int
         lib.nb_comm_wait_flag.argtypes = [c_vp, c_uint, c_vp, c_ull, c_vp]
         _lib = lib
@@ -98,6 +101,12 @@ class Arena:
         self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
         self.hdl = symm_mem.rendezvous(self.buf, group=pg)
         self.ptrs_dev = int(self.hdl.buffer_ptrs_dev)
+        self.mc_ptr = 0
+        if os.environ.get("NABLA_B200_NVLS", "1") != "0":
+            try:
+                self.mc_ptr = int(self.hdl.multicast_ptr)
+            except Exception:
+                self.mc_ptr = 0
         self.free_list: list[list[int]] = [[0, self.nbytes]]      # [offset, size], sorted by offset
         self.live: dict[int, int] = {}
         torch.cuda.synchronize()
@@ -438,6 +447,31 @@ def all_gather_gemm(a_shard: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_ro
                   ws.arena.ptrs_dev if push else 0, arena_off or 0)
     cur.wait_stream(side)
     return (a_full, out, pre) if store_preact else (a_full, out)
+
+
+def adamw_reduce(p: torch.Tensor, m: torch.Tensor, v: torch.Tensor, grad_off: int, mesh, axes, *, lr: float, b1: float,
+                 b2: float, eps: float, wd: float, step: int | None = None, hyper: torch.Tensor | None = None,
+                 grad_scale: float = 1.0) -> None:
+    """Data-parallel AdamW step of one parameter in ONE kernel: the ranks' bf16 gradients sit at
+    ``grad_off`` of the group's symmetric :class:`Arena`; the kernel sums them over NVLink while it
+    reads them (``multimem.ld_reduce`` or one load per peer), applies scale + AdamW to ``p`` (bf16),
+    ``m``, ``v`` (fp32) in place, and brackets itself with the two barriers that keep the gradients
+    valid. Replaces all-reduce + cast + AdamW (reference: nabla/nn/optim/functional.py:116-162 after
+    the partial-sum all-reduce of nabla/core/autograd/backward.py:72-80)."""
+    global launch_count
+    ws = _fused_state(workspace(mesh, axes), p.device)
+    ar = ws.arena
+    n = p.numel()
+    bc1 = 1.0 - b1 ** step if step is not None else 1.0
+    bc2 = 1.0 - b2 ** step if step is not None else 1.0
+    blocks = int(max(1, min(256, (n // 8 + 255) // 256)))
+    rc = _L().nb_comm_adamw_reduce(ws.ptrs_dev, ws.rank, ws.world, ws.ctr.data_ptr(), ar.ptrs_dev, ar.mc_ptr, grad_off,
+                                   p.data_ptr(), m.data_ptr(), v.data_ptr(), n, float(lr), float(b1), float(b2),
+                                   float(eps), float(wd), float(bc1), float(bc2), float(grad_scale),
+                                   c_vp(0 if hyper is None else hyper.data_ptr()), blocks, _status().data_ptr(), _stream())
+    if rc != 0:
+        raise RuntimeError(f"nb_comm_adamw_reduce failed with code {rc}")
+    launch_count += 1
 
 
 def _gather_call(x: torch.Tensor, mesh, axes, mode: int, chunk_elems: int, out_elems: int, root: int = 0) -> torch.Tensor:

@@ -252,6 +252,7 @@ class CompiledFunction:
                     last_use.setdefault(id(o), si)
         if any(rec.donated):
             _mark_inplace_updates(rec, ph_last_use)
+            _fuse_dp_grad_updates(rec)
         rec.free_after = [[] for _ in rec.steps]
         for k, si in last_use.items():
             if k not in out_ids:
@@ -417,6 +418,55 @@ def _optimizer_steps_last(steps: list, nodes: list[OpNode]) -> list:
         else:
             head.append(st)
     return head + tail
+
+
+def _fuse_dp_grad_updates(rec: _Recorded) -> None:
+    """``matmul -> all_reduce(sum over replica axes) -> in-place AdamW`` on bf16 parameters: the
+    all-reduce moves into the optimizer kernel (see fusion.run_fused 'gemm_to_arena' / 'adamw_reduce')."""
+    from ..types import DType
+
+    nodes = rec.nodes
+    readers: dict[int, list[int]] = {}
+    for ni, n in enumerate(nodes):
+        for a in n.input_impls():
+            readers.setdefault(id(a), []).append(ni)
+    adam_step = {idxs[0]: si for si, (kind, idxs) in enumerate(rec.steps)
+                 if kind == "op" and nodes[idxs[0]].op.name == "adam_wstep" and nodes[idxs[0]].kwargs.get("inplace")}
+    out_ids = {id(i) for i in rec.out_impls if i is not None}
+    for si, (kind, idxs) in enumerate(rec.steps):
+        if kind != "gemm_all_reduce":
+            continue
+        ar = nodes[idxs[1]]
+        g = ar.outputs()[0]
+        if g is None or id(g) in out_ids or len(readers.get(id(g), [])) != 1:
+            continue
+        k = readers[id(g)][0]
+        if k not in adam_step:
+            continue
+        ad = nodes[k]
+        ins = ad.input_impls()
+        if len(ins) < 4 or ins[1] is not g:
+            continue
+        p_, m_, v_ = ins[0], ins[2], ins[3]
+        n_el = 1
+        for d in (p_.sharding and compute_local(p_) or p_._shape):
+            n_el *= int(d)
+        if not (p_.dtype is DType.bfloat16 and g.dtype is DType.bfloat16 and m_.dtype is DType.float32
+                and v_.dtype is DType.float32 and n_el % 8 == 0 and len(g._shape) == 2):
+            continue
+        mesh = g.sharding.mesh if g.sharding is not None else None
+        if mesh is None:
+            continue
+        rec.arena_blocks[("dp_group", id(ad))] = (mesh, [x for x in mesh.axis_names if x in ar.kwargs["reduce_axes"]])
+        rec.steps[si] = ("gemm_to_arena", idxs)
+        rec.steps[adam_step[k]] = ("adamw_reduce", (k,))
+
+
+def compute_local(impl) -> tuple:
+    from ..core.sharding.spec import compute_local_shape
+
+    mesh = impl.sharding.mesh
+    return compute_local_shape(impl._shape, impl.sharding, mesh.local_ids[0])
 
 
 def _mark_inplace_updates(rec: _Recorded, last_use: dict[int, int]) -> None:

@@ -148,6 +148,31 @@ def main():
                 errs[f"ag_z_{M}x{N}x{K}_{rep}"] = ((z.float() - z_ref).abs().max() / z_ref.abs().max()).item()
                 errs[f"ag_y_{M}x{N}x{K}_{rep}"] = ((y.float() - torch.nn.functional.gelu(z_ref)).abs().max()
                                                     / z_ref.abs().max()).item()
+        # data-parallel gradient all-reduce fused into AdamW: gradients stay unreduced in the arena
+        from nabla_b200.native import kernels as NK
+
+        if ar is not None:
+            for n_el in (4096, 1 << 20, (1 << 21) + 4096):
+                torch.manual_seed(3)
+                p0 = torch.randn(n_el, device=dev, dtype=torch.bfloat16)
+                m0 = torch.rand(n_el, device=dev) * 0.1
+                v0 = torch.rand(n_el, device=dev) * 0.01
+                torch.manual_seed(50 + rank)
+                g = torch.randn(n_el, device=dev, dtype=torch.bfloat16)
+                gsum = g.float().clone()
+                dist.all_reduce(gsum)
+                pr, mr, vr = NK.adamw(p0.clone(), gsum, m0.clone(), v0.clone(), lr=1e-2, b1=0.9, b2=0.999, eps=1e-8,
+                                      wd=0.01, step=3)
+                for rep in range(2):
+                    off = ar.alloc(n_el * 2)
+                    ar.buf[off: off + n_el * 2].view(torch.bfloat16).copy_(g)
+                    p1, m1, v1 = p0.clone(), m0.clone(), v0.clone()
+                    symm.adamw_reduce(p1, m1, v1, off, mesh, ("x",), lr=1e-2, b1=0.9, b2=0.999, eps=1e-8, wd=0.01, step=3)
+                    torch.cuda.synchronize()
+                    ar.free(off)
+                    errs[f"dp_adamw_p_{n_el}_{rep}"] = (p1.float() - pr.float()).abs().max().item()
+                    errs[f"dp_adamw_m_{n_el}_{rep}"] = ((m1 - mr).abs().max() / mr.abs().max()).item()
+                    errs[f"dp_adamw_v_{n_el}_{rep}"] = ((v1 - vr).abs().max() / vr.abs().max()).item()
         native.check_status()
         out["max_err"] = max(errs.values())
         out["errs"] = {k: v for k, v in errs.items() if v > 2e-2}
