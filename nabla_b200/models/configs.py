@@ -28,6 +28,11 @@ import numpy as np
 import torch
 
 
+def _graph() -> bool:
+    """Replay the recorded step from one CUDA graph (default) unless NABLA_B200_CUDA_GRAPH=0."""
+    return os.environ.get("NABLA_B200_CUDA_GRAPH", "1") != "0"
+
+
 def _timed(step_fn, warmup: int, steps: int, world: int, dev) -> float:
     for _ in range(warmup):
         out = step_fn()
@@ -58,7 +63,7 @@ def run_gpipe(nb, rank, world, dev, tdev, steps, warmup, dim=4096, micro=32, bat
     ys = nb.gaussian((micro, batch, dim), 0.0, 1.0, dtype=nb.DType.bfloat16, device=dev)
     nb.realize_all(w, b, xs, ys)
 
-    @nb.compile
+    @nb.compile(cuda_graph=_graph())
     def step(w, b, xs, ys):
         loss, (gw, gb) = nb.value_and_grad(lambda w_, b_: P.gpipe_loss(w_, b_, xs, ys, mesh), argnums=(0, 1))(w, b)
         return loss, w - gw * 1e-3, b - gb * 1e-3
@@ -97,7 +102,7 @@ def run_pp_dp(nb, rank, world, dev, tdev, steps, warmup, dim=8192, micro=16, bat
     state = nn.adamw_init(params, state_dtype=nb.DType.float32)
     nb.realize_all(*nb.tensor_leaves(state))
 
-    @nb.compile
+    @nb.compile(cuda_graph=_graph(), donate_argnums=(0, 1))
     def step(params, state, xs, ys):
         loss, grads = nb.value_and_grad(
             lambda p: P.gpipe_loss((p["w1"], p["w2"]), (p["b1"], p["b2"]), xs, ys, mesh, "stage",
@@ -135,7 +140,7 @@ def run_lora(nb, rank, world, dev, tdev, steps, warmup, layers=24, batch=32, seq
     if mesh is not None:
         tok, tgt = tok.shard(mesh, (None, None)), tgt.shard(mesh, (None, None))
 
-    @nb.compile
+    @nb.compile(cuda_graph=_graph(), donate_argnums=(0, 1))
     def step(lora, state, tok, tgt):
         loss, grads = nb.value_and_grad(lambda a: T.loss_fn(params, tok, tgt, cfg, None, a), create_graph=False)(lora)
         lora, state = nn.adamw_update(lora, grads, state, lr=1e-4, weight_decay=0.0, realize=False)
@@ -179,7 +184,7 @@ def main() -> None:
             kw = dict(layers=2, batch=4, seq=256) if args.small else {}
             out = run_lora(nb, rank, world, dev, tdev, args.steps, args.warmup, **kw)
         native.check_status()
-    out.update(n_gpus=world, steps=args.steps, warmup=args.warmup, small=bool(args.small))
+    out.update(n_gpus=world, steps=args.steps, warmup=args.warmup, small=bool(args.small), cuda_graph=_graph())
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
