@@ -7,6 +7,10 @@
 * ``lora``   LoRA fine-tuning of the 24-layer d=2048 transformer: frozen bf16 base, rank-16 adapters on
   q/k/v/o, tensor parallel over all GPUs, seq 2048, batch 32; only adapter gradients exist.
 
+* ``cpu_mlp``  the CPU training configuration: fp32 MLP 64 -> 256 -> 256 -> 256 -> 1 with relu, x (512, 64)
+  ~ U(0, 1) from seed 0, y = sin(2 pi mean(x, axis=1)), MSE, Adam lr 1e-3, 100 steps, one device
+  (``python -m nabla_b200.models.configs cpu_mlp``; no torchrun, no GPU).
+
 Run under torchrun, one rank per GPU::
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \\
@@ -157,13 +161,63 @@ def run_lora(nb, rank, world, dev, tdev, steps, warmup, layers=24, batch=32, seq
             "tokens_per_s": batch * seq / (ms / 1e3), "loss": float(loss.item())}
 
 
+def run_cpu_mlp(steps: int = 100) -> dict:
+    import time
+
+    import nabla_b200 as nb
+    from nabla_b200 import nn
+
+    rng = np.random.default_rng(0)
+    x_np = rng.uniform(0.0, 1.0, (512, 64)).astype(np.float32)
+    y_np = np.sin(2 * np.pi * x_np.mean(axis=1, keepdims=True)).astype(np.float32)
+    sizes = [64, 256, 256, 256, 1]
+    with nb.default_device(nb.CPU()):
+        x, y = nb.constant(x_np), nb.constant(y_np)
+        params = []
+        for fi, fo in zip(sizes[:-1], sizes[1:]):
+            params.append({"w": nb.constant(rng.normal(0.0, fi ** -0.5, (fi, fo)).astype(np.float32)),
+                           "b": nb.constant(np.zeros((1, fo), np.float32))})
+        state = nn.adamw_init(params)
+
+        def loss_fn(ps):
+            h = x
+            for i, p in enumerate(ps):
+                h = h @ p["w"] + p["b"]
+                if i + 1 < len(ps):
+                    h = nb.relu(h)
+            d = h - y
+            return nb.mean(d * d)
+
+        @nb.compile
+        def step(params, state):
+            loss, grads = nb.value_and_grad(loss_fn)(params)
+            params, state = nn.adamw_update(params, grads, state, lr=1e-3, weight_decay=0.0, realize=False)
+            return loss, params, state
+
+        first = None
+        t0 = time.perf_counter()
+        for i in range(steps):
+            loss, params, state = step(params, state)
+            if i == 0:
+                first = float(loss.item())
+                t1 = time.perf_counter()          # the first call records the graph
+        last = float(loss.item())
+        t2 = time.perf_counter()
+    return {"config": "cpu_mlp", "steps": steps, "first_loss": first, "final_loss": last,
+            "steps_per_s_after_first": (steps - 1) / (t2 - t1), "total_s": t2 - t0}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("config", choices=["gpipe", "pp_dp", "lora"])
+    ap.add_argument("config", choices=["gpipe", "pp_dp", "lora", "cpu_mlp"])
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--small", action="store_true", help="reduced sizes (functional check, not a benchmark number)")
     args = ap.parse_args()
+
+    if args.config == "cpu_mlp":
+        print(json.dumps(run_cpu_mlp(100 if args.steps == 5 else args.steps)), flush=True)
+        return
 
     import nabla_b200 as nb
     from nabla_b200 import native
