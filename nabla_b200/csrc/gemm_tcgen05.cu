@@ -362,12 +362,29 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
       }
       const long long aux_off =
           static_cast<long long>(b) * args.stride_aux + static_cast<long long>(row) * args.ld_aux;
+      // the auxiliary input (z for the activation backward, or the residual) does not depend on
+      // the MMAs: its 64 bytes per row and chunk are fetched one chunk ahead of their use
+      const bool aux_reads = args.aux >= AUX_MUL_DRELU && row_ok && args.vec_ok;
+      uint4 anext[4];
+      if (aux_reads && n0 + 32 <= args.N) {
+        const uint4* ap0 = reinterpret_cast<const uint4*>(args.aux_in + aux_off + n0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) anext[q] = ap0[q];
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int nb0 = n0 + c * 32;
         if (nb0 >= args.N) break;   // warp-uniform
         uint32_t v[32];
         tmem_ld_32x32(taddr + c * 32, v);
+        uint4 acur[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acur[q] = anext[q];
+        if (aux_reads && c + 1 < BN / 32 && nb0 + 64 <= args.N) {
+          const uint4* apn = reinterpret_cast<const uint4*>(args.aux_in + aux_off + nb0 + 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) anext[q] = apn[q];
+        }
         tmem_ld_wait();
         float f[32];
 #pragma unroll
@@ -413,7 +430,7 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
           if (full) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              uint4 pk = reinterpret_cast<const uint4*>(ap)[q];
+              const uint4 pk = acur[q];
               const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&pk);
 #pragma unroll
               for (int j = 0; j < 4; ++j) {

@@ -1,4 +1,4 @@
-"""GPipe-style pipeline parallel MLP (BASELINE configs 2 and 4; reference recipe:
+"""GPipe-style pipeline parallel MLP (the GPipe and PP x DP configurations; reference recipe:
 examples/07_mlp_pipeline_parallel.ipynb, examples/08_mlp_pp_dp_training.ipynb).
 
 Per-stage weights are stacked on a leading axis split over the ``stage`` mesh axis;

@@ -1,5 +1,5 @@
 """Workload-level tests on CPU: the benchmark transformer (unsharded == dp x tp sharded, compiled
-training step decreases the loss), the BASELINE CPU MLP, GPipe via vmap(spmd_axis_name) +
+training step decreases the loss), the CPU MLP configuration, GPipe via vmap(spmd_axis_name) +
 ppermute against a sequential oracle, PP x DP."""
 import numpy as np
 import pytest
@@ -61,7 +61,7 @@ def test_transformer_compiled_training_loss_decreases(monkeypatch):
 
 
 def test_baseline_cpu_mlp_config_trains():
-    """BASELINE config 1: fp32 MLP 64-256-256-256-1 relu, x (512,64) ~U(0,1), y = sin(2 pi mean x),
+    """CPU MLP configuration: fp32 MLP 64-256-256-256-1 relu, x (512,64) ~U(0,1), y = sin(2 pi mean x),
     MSE, Adam lr 1e-3 (shortened to 40 steps)."""
     rng = np.random.default_rng(0)
     xn = rng.random((512, 64), dtype=np.float32)
