@@ -108,3 +108,59 @@ def total_launches() -> int:
         if m is not None:
             n += getattr(m, "launch_count", 0)
     return n
+
+
+# ---------------------------------------------------------------- status watchdog (C++ thread)
+def _rt():
+    lib = load("libnb_runtime.so")
+    lib.nb_rt_watch_start.restype = ctypes.c_int
+    lib.nb_rt_watch_start.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int]
+    lib.nb_rt_watch_stop.argtypes = [ctypes.c_int]
+    lib.nb_rt_watch_last.restype = ctypes.c_int
+    lib.nb_rt_watch_last.argtypes = [ctypes.c_int]
+    lib.nb_rt_watch_polls.restype = ctypes.c_longlong
+    lib.nb_rt_watch_polls.argtypes = [ctypes.c_int]
+    lib.nb_rt_watch_stalled_ms.restype = ctypes.c_double
+    lib.nb_rt_watch_stalled_ms.argtypes = [ctypes.c_int]
+    lib.nb_rt_watch_clear.argtypes = [ctypes.c_int]
+    return lib
+
+
+def watchdog_start(device: torch.device | None = None, interval_ms: int = 50, word: torch.Tensor | None = None) -> None:
+    """Start the C++ watchdog thread of ``device``: it copies the device's status word (or
+    ``word``, an int32 CUDA tensor) to pinned host memory on its own stream every ``interval_ms``
+    without holding the GIL, so that a failed bounded wait is noticed while Python is busy or
+    blocked, and without a device synchronisation in the training loop."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    w = word if word is not None else status_word(device)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if _rt().nb_rt_watch_start(idx, ctypes.c_void_p(w.data_ptr()), int(interval_ms)) != 0:
+        raise RuntimeError("could not start the status watchdog")
+    _watched[idx] = w
+
+
+def watchdog_stop(device: torch.device | None = None) -> None:
+    idx = (device.index if device is not None and device.index is not None else torch.cuda.current_device())
+    _rt().nb_rt_watch_stop(idx)
+    _watched.pop(idx, None)
+
+
+def watchdog_poll(device: torch.device | None = None) -> dict:
+    """What the watchdog has seen so far, without touching the device: ``code`` (first non-zero
+    status, 0 if none), ``polls`` (completed copies) and ``stalled_ms`` (age of a copy that has not
+    come back yet: a device that stopped answering shows up here)."""
+    idx = (device.index if device is not None and device.index is not None else torch.cuda.current_device())
+    lib = _rt()
+    return {"code": int(lib.nb_rt_watch_last(idx)), "polls": int(lib.nb_rt_watch_polls(idx)),
+            "stalled_ms": float(lib.nb_rt_watch_stalled_ms(idx))}
+
+
+def watchdog_check(device: torch.device | None = None) -> None:
+    """Raise ``KernelStatusError`` if the watchdog has recorded a failed bounded wait."""
+    idx = (device.index if device is not None and device.index is not None else torch.cuda.current_device())
+    code = int(_rt().nb_rt_watch_last(idx))
+    if code > 0:
+        raise KernelStatusError(f"cuda:{idx}: kernel status {code}: {_STATUS_NAMES.get(code, 'unknown')} (seen by the watchdog)")
+
+
+_watched: dict = {}

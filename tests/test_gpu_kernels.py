@@ -290,3 +290,31 @@ def test_transformer_block_on_gpu_matches_cpu_reference():
     for a, b in zip(nb.tree_leaves(g_dev), nb.tree_leaves(g_ref)):
         ga, gb = torch.from_numpy(a.to_numpy()).float(), torch.from_numpy(b.to_numpy()).float()
         assert ((ga - gb).norm() / (gb.norm() + 1e-6)).item() < 0.1
+
+
+@pytest.mark.skipif(not torch.cuda.is_available(), reason="needs a GPU")
+def test_status_watchdog_thread_reports_without_synchronising():
+    """The C++ watchdog copies a status word to the host on its own stream: a non-zero code written
+    on the device shows up in `watchdog_poll` although Python never reads the tensor."""
+    import time
+
+    from nabla_b200 import native
+
+    dev = torch.device("cuda", 0)
+    word = torch.zeros(4, dtype=torch.int32, device=dev)
+    native.watchdog_start(dev, interval_ms=10, word=word)
+    try:
+        time.sleep(0.2)
+        before = native.watchdog_poll(dev)
+        assert before["code"] == 0 and before["polls"] > 0
+        native.watchdog_check(dev)                      # nothing recorded: no exception
+        word[0] = 4                                     # what a timed-out peer wait would store
+        torch.cuda.synchronize()
+        deadline = time.time() + 5.0
+        while native.watchdog_poll(dev)["code"] == 0 and time.time() < deadline:
+            time.sleep(0.02)
+        assert native.watchdog_poll(dev)["code"] == 4
+        with pytest.raises(native.KernelStatusError):
+            native.watchdog_check(dev)
+    finally:
+        native.watchdog_stop(dev)
