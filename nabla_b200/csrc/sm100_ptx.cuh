@@ -206,7 +206,27 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, int a_mn, i
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
-__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+// erf(t) and exp(-t*t) together (Abramowitz & Stegun 7.1.26, |error| < 1.5e-7): one approximate
+// reciprocal, one ex2 and a degree-5 polynomial -- about half the instructions of erff() plus a
+// separate expf(), which matters because the exact-gelu epilogues run on four warps per CTA next
+// to the MMAs. The exponential is also the Gaussian density that d-gelu needs.
+__device__ __forceinline__ float erf_with_gauss(float t, float& gauss) {
+  const float at = fabsf(t);
+  float k;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(k) : "f"(fmaf(0.3275911f, at, 1.0f)));
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * at * at));
+  gauss = e;
+  float p = fmaf(k, 1.061405429f, -1.453152027f);
+  p = fmaf(k, p, 1.421413741f);
+  p = fmaf(k, p, -0.284496736f);
+  p = fmaf(k, p, 0.254829592f);
+  return copysignf(fmaf(-p * k, e, 1.0f), t);
+}
+__device__ __forceinline__ float gelu_erf(float x) {
+  float g;
+  return 0.5f * x * (1.0f + erf_with_gauss(x * 0.70710678118654752f, g));
+}
 __device__ __forceinline__ float gelu_tanh(float x) {
   float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
   float t;
@@ -214,9 +234,9 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   return 0.5f * x * (1.0f + t);
 }
 __device__ __forceinline__ float dgelu_erf(float x) {
-  float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752f));
-  float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
+  float g;                                                 // exp(-x*x/2)
+  const float cdf = 0.5f * (1.0f + erf_with_gauss(x * 0.70710678118654752f, g));
+  return fmaf(x * 0.3989422804014327f, g, cdf);
 }
 __device__ __forceinline__ float dgelu_tanh(float x) {
   float x2 = x * x;
