@@ -2,12 +2,16 @@
 //
 //   D[b] = epilogue( A[b] (M x K)  *  B[b] (K x N) )        fp32 accumulation in TMEM
 //
-// Structure (one persistent CTA per SM, 256 threads):
-//   warp 0      TMA producer: cp.async.bulk.tensor loads of A/B tiles into a shared-memory ring
-//   warp 1      MMA issuer:   one thread issues tcgen05.mma (128 x BN x 16) from smem descriptors
-//   warp 2      TMEM allocator (2 accumulator buffers of BN columns each)
-//   warps 4..7  epilogue: tcgen05.ld the accumulator, bias / relu / gelu / d-activation /
-//               residual add, cast and store; overlaps the next tile's MMAs (double-buffered TMEM)
+// Structure (one persistent CTA per SM, 384 threads):
+//   warp 0       TMA producer: cp.async.bulk.tensor loads of A/B tiles into a shared-memory ring
+//   warp 1       MMA issuer:   one thread issues tcgen05.mma (128 x BN x 16) from smem descriptors
+//   warp 2       TMEM allocator (2 accumulator buffers of BN columns each)
+//   warps 4..11  epilogue, two groups of four warps (a warp reads the TMEM lane quarter warp % 4):
+//                tcgen05.ld the accumulator, bias / relu / gelu / d-activation / residual add, cast
+//                and store. For the erf-gelu and d-gelu epilogues the groups take alternate
+//                64-column pairs of the tile, which keeps them shorter than the tile's MMAs; plain
+//                epilogues run on group 0 alone. The epilogue overlaps the next tile's MMAs
+//                (double-buffered TMEM).
 //
 // Both operands may be K-major (row = M or N index, K contiguous) or MN-major (row = K index,
 // M or N contiguous), so x@W, dY@W^T and X^T@dY all run without materialising a transpose.
@@ -23,8 +27,8 @@ namespace nb {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;   // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int NUM_THREADS = 256;
-constexpr int EPI_THREADS = 128;
+constexpr int NUM_THREADS = 384;   // warps 0-3: TMA / MMA / TMEM alloc / idle; warps 4-11: two epilogue groups
+constexpr int EPI_THREADS = 256;
 
 enum Epi : int { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_RELU = 2, EPI_BIAS_GELU = 3 };
 enum Aux : int { AUX_NONE = 0, AUX_STORE_PREACT = 1, AUX_MUL_DRELU = 2, AUX_MUL_DGELU = 3, AUX_ADD = 4 };
@@ -319,7 +323,11 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
   } else if (warp >= 4) {
     // ------------------------------------------------------------ epilogue
     const int wq = warp & 3;                 // TMEM lane quarter this warp may read
-    const int et = threadIdx.x - 128;        // 0..127
+    const int et = threadIdx.x - 128;        // 0..255
+    // two epilogue groups share every tile: group g takes the 64-column pairs with (pair & 1) == g,
+    // so the per-element math of the gelu / d-gelu epilogues fits under the tile's MMAs
+    const int grp = (warp - 4) >> 2;
+    const bool heavy = args.epi == EPI_BIAS_GELU || args.aux == AUX_MUL_DGELU;
     bool ok = true;
     int it = 0;
     for (int t = cta; t < num_tiles; t += nctas, ++it) {
@@ -362,29 +370,20 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
       }
       const long long aux_off =
           static_cast<long long>(b) * args.stride_aux + static_cast<long long>(row) * args.ld_aux;
-      // the auxiliary input (z for the activation backward, or the residual) does not depend on
-      // the MMAs: its 64 bytes per row and chunk are fetched one chunk ahead of their use
-      const bool aux_reads = args.aux >= AUX_MUL_DRELU && row_ok && args.vec_ok;
-      uint4 anext[4];
-      if (aux_reads && n0 + 32 <= args.N) {
-        const uint4* ap0 = reinterpret_cast<const uint4*>(args.aux_in + aux_off + n0);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) anext[q] = ap0[q];
-      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int nb0 = n0 + c * 32;
         if (nb0 >= args.N) break;   // warp-uniform
+        // epilogues with per-element transcendental math are split between the two groups by
+        // 64-column pairs; the plain ones (and the peer-store path, whose staging buffers exist
+        // once per lane quarter) stay with group 0, whose warps then stream the whole tile
+        if (MODE != MODE_RS && heavy) {
+          if (((c >> 1) & 1) != grp) continue;
+        } else if (grp != 0) {
+          break;
+        }
         uint32_t v[32];
         tmem_ld_32x32(taddr + c * 32, v);
-        uint4 acur[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) acur[q] = anext[q];
-        if (aux_reads && c + 1 < BN / 32 && nb0 + 64 <= args.N) {
-          const uint4* apn = reinterpret_cast<const uint4*>(args.aux_in + aux_off + nb0 + 32);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) anext[q] = apn[q];
-        }
         tmem_ld_wait();
         float f[32];
 #pragma unroll
@@ -430,7 +429,7 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
           if (full) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              const uint4 pk = acur[q];
+              const uint4 pk = reinterpret_cast<const uint4*>(ap)[q];
               const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&pk);
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
