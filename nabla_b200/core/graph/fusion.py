@@ -357,6 +357,23 @@ def run_fused(kind: str, group: list[OpNode], keep_graph: bool = False, arena_bl
             _plain(mm, keep_graph)
             _plain(da, keep_graph)
         return
+    if kind == "all_reduce_bucket":
+        # many small partial sums over the same device group: one flat all-reduce
+        from ...parallel import backend
+
+        first = group[0]
+        mesh = first.input_impls()[0].sharding.mesh
+        axes = [x for x in mesh.axis_names if x in first.kwargs["reduce_axes"]]
+        xs = [n_.input_impls()[0]._buffers[0] for n_ in group]
+        flat = torch.cat([x.reshape(-1) for x in xs])
+        red = backend.all_reduce(flat, mesh, axes, "sum")
+        off = 0
+        for n_, x in zip(group, xs):
+            k = x.numel()
+            _store(n_, [[red[off: off + k].view(x.shape)]], keep_graph)
+            off += k
+        backend.stats["bucketed_all_reduce"] = backend.stats.get("bucketed_all_reduce", 0) + len(group)
+        return
     if kind == "gemm_to_arena":
         # weight gradient of a data-parallel replica group: keep it unreduced, in the arena; the
         # matching adamw_reduce step sums it over the group while it reads it

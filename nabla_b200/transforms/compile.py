@@ -235,6 +235,7 @@ class CompiledFunction:
         rec.steps = plan.steps if plan is not None else [("op", (i,)) for i in range(len(nodes))]
         if any(rec.donated):
             rec.steps = _optimizer_steps_last(rec.steps, nodes)
+            rec.steps = _bucket_small_all_reduces(rec.steps, nodes)
         # liveness: free an intermediate after the last step that reads it
         out_ids = {id(i) for i in rec.out_impls if i is not None}
         produced = {id(o): o for outs in rec.keep for o in outs}
@@ -418,6 +419,58 @@ def _optimizer_steps_last(steps: list, nodes: list[OpNode]) -> list:
         else:
             head.append(st)
     return head + tail
+
+
+def _bucket_small_all_reduces(steps: list, nodes: list[OpNode], max_elems: int = 1 << 20) -> list:
+    """Gradients of small parameters (biases, LayerNorm gains) each need their own all-reduce
+    before the optimizer: hundreds of launches that move a few KB. Those whose only reader is an
+    optimizer step at the end of the schedule are taken out of line and reduced together, one
+    flat buffer per (axes, dtype), right before the optimizer steps."""
+    readers: dict[int, list[int]] = {}
+    for ni, n in enumerate(nodes):
+        for a in n.input_impls():
+            readers.setdefault(id(a), []).append(ni)
+    tail_nodes = set()
+    tail_start = len(steps)
+    for si in range(len(steps) - 1, -1, -1):
+        kind, idxs = steps[si]
+        if kind == "op" and getattr(nodes[idxs[0]].op, "inplace_inputs", None):
+            tail_nodes.add(idxs[0])
+            tail_start = si
+        else:
+            break
+    if not tail_nodes:
+        return steps
+    groups: dict[tuple, list[int]] = {}
+    for si, (kind, idxs) in enumerate(steps[:tail_start]):
+        if kind != "op":
+            continue
+        n = nodes[idxs[0]]
+        if n.op.name != "all_reduce" or n.kwargs.get("reduce_op", "sum") != "sum":
+            continue
+        x = n.input_impls()[0]
+        o = n.outputs()[0]
+        sp = x.sharding
+        if o is None or sp is None or not sp.mesh.is_distributed or x.batch_dims:
+            continue
+        axes = set(n.kwargs.get("reduce_axes", ()))
+        if not axes or not axes <= set(sp.partial_sum_axes) or any(set(d.axes) & axes for d in sp.dim_specs):
+            continue
+        rd = readers.get(id(o), [])
+        if len(rd) != 1 or rd[0] not in tail_nodes:
+            continue
+        numel = 1
+        for d in compute_local(x):
+            numel *= int(d)
+        if numel > max_elems:
+            continue
+        groups.setdefault((tuple(sorted(axes)), x.dtype, id(sp.mesh)), []).append(si)
+    taken = {si for g in groups.values() if len(g) >= 2 for si in g}
+    if not taken:
+        return steps
+    head = [st for si, st in enumerate(steps[:tail_start]) if si not in taken]
+    buckets = [("all_reduce_bucket", tuple(steps[si][1][0] for si in g)) for g in groups.values() if len(g) >= 2]
+    return head + buckets + steps[tail_start:]
 
 
 def _fuse_dp_grad_updates(rec: _Recorded) -> None:

@@ -131,3 +131,61 @@ HEALTH = textwrap.dedent('''
 def test_health_store_reports_lost_peer_before_next_launch(mode):
     res = _run(HEALTH, [mode], timeout=120)
     assert "RESULT lost [1]" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+BUCKET = textwrap.dedent('''
+    import os, sys, json
+    os.environ["NABLA_B200_FUSED"] = "1"      # fused optimizer / layer ops also on CPU (torch implementations)
+    sys.path.insert(0, {root!r})
+    import numpy as np
+    import nabla_b200 as nb
+    from nabla_b200 import nn
+    from nabla_b200.models import transformer as T
+    from nabla_b200.parallel import init_distributed, backend
+    rank, world = init_distributed(backend="gloo", timeout_s=60)
+    cfg = T.TransformerConfig(n_layers=2, d_model=32, n_heads=4, d_ff=64, vocab=48, max_seq=16, dtype=nb.DType.float32)
+    rng = np.random.default_rng(0)
+    tok_np, tgt_np = rng.integers(0, 48, (4, 16)), rng.integers(0, 48, (4, 16))
+
+    def run(mesh):
+        nb.seed(0)
+        params = T.init_params(cfg)
+        if mesh is not None:
+            params = T.place_params(params, mesh, "tp")
+        nb.realize_all(*nb.tensor_leaves(params))
+        state = nn.adamw_init(params, state_dtype=nb.DType.float32)
+        nb.realize_all(*nb.tensor_leaves(state))
+        sp = T.SeqParallel(mesh, None, "tp") if mesh is not None else None
+        tok, tgt = nb.constant(tok_np), nb.constant(tgt_np)
+        if mesh is not None:
+            tok, tgt = tok.shard(mesh, (None, None)), tgt.shard(mesh, (None, None))
+
+        def step(params, state, tokens, targets):
+            loss, grads = nb.value_and_grad(lambda p: T.loss_fn(p, tokens, targets, cfg, sp), create_graph=False)(params)
+            params, state = nn.adamw_update(params, grads, state, lr=1e-2, weight_decay=0.01, realize=False)
+            return loss, params, state
+
+        f = nb.compile(step, donate_argnums=(0, 1))
+        out = []
+        for _ in range(3):
+            loss, params, state = f(params, state, tok, tgt)
+            out.append(float(loss.item()))
+        return out
+
+    ref = run(None)
+    got = run(nb.DeviceMesh("m", (2,), ("tp",)))
+    print("RESULT " + json.dumps({{"ref": ref, "got": got, "bucketed": backend.stats.get("bucketed_all_reduce", 0)}}), flush=True)
+''')
+
+
+def test_compiled_sequence_parallel_step_buckets_small_gradient_reductions():
+    import json
+    import re
+
+    res = _run(BUCKET, [], timeout=240)
+    lines = re.findall(r"RESULT (\{.*?\})", res.stdout)
+    assert len(lines) == 2, res.stdout[-2000:] + res.stderr[-3000:]
+    for l in lines:
+        r = json.loads(l)
+        assert r["bucketed"] > 0, r
+        assert all(abs(a - b) < 2e-4 for a, b in zip(r["ref"], r["got"])), r
