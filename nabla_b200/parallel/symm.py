@@ -22,6 +22,7 @@ _lib = None
 _enabled: bool | None = None
 launch_count = 0
 DEFAULT_BYTES = int(os.environ.get("NABLA_B200_SYMM_MB", "640")) * 1024 * 1024
+CANARY_BYTES, CANARY_VALUE = 4096, 0xA5
 c_int, c_ll, c_vp, c_uint, c_ull = ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_uint, ctypes.c_ulonglong
 
 
@@ -76,8 +77,33 @@ class Workspace:
         self.ctr = torch.zeros(8, dtype=torch.int32, device=self.buf.device)
         self.data = self.buf[self.flag_bytes:]
         self.data_bytes = self.nbytes - self.flag_bytes
+        # guard bytes at the very end of the allocation: no kernel is ever given an extent that
+        # reaches them (`supports`, the fused launchers' size checks), so `check_canary` finding
+        # them changed means some kernel wrote past its region
+        self.buf[-CANARY_BYTES:].fill_(CANARY_VALUE)
         torch.cuda.synchronize()
         dist.barrier(group=pg)
+        self.validate()
+
+    def validate(self) -> None:
+        """Host-side check of the peer pointer table and the flag pad before first use: one
+        non-null, distinct base pointer per rank, this rank's entry equal to its own buffer, and a
+        flag region that starts out zero."""
+        try:
+            ptrs = [int(self.hdl.buffer_ptrs[r]) for r in range(self.world)]
+        except Exception:          # handle without a host-side pointer list: nothing to check here
+            ptrs = None
+        if ptrs is not None:
+            if any(p == 0 for p in ptrs) or len(set(ptrs)) != self.world:
+                raise RuntimeError(f"symmetric workspace: bad peer pointer table {ptrs}")
+            if ptrs[self.rank] != self.buf.data_ptr():
+                raise RuntimeError("symmetric workspace: this rank's table entry is not its own buffer")
+        if int(self.buf[: self.flag_bytes].view(torch.int32).abs().max().item()) != 0:
+            raise RuntimeError("symmetric workspace: flag region is not zero at creation")
+
+    def check_canary(self) -> bool:
+        """True while the guard bytes at the end of the workspace are intact."""
+        return bool((self.buf[-CANARY_BYTES:] == CANARY_VALUE).all().item())
 
     def stage(self, x: torch.Tensor, offset: int = 0) -> None:
         """Copy ``x`` (contiguous) into the data region at byte ``offset``."""
@@ -194,7 +220,7 @@ def workspace(mesh, axes) -> Workspace:
 
 def supports(buf: torch.Tensor) -> bool:
     return (buf.is_cuda and buf.dtype in (torch.bfloat16, torch.float32)
-            and buf.numel() * buf.element_size() + 4096 <= DEFAULT_BYTES - 65536)
+            and buf.numel() * buf.element_size() + 8192 <= DEFAULT_BYTES - 65536)
 
 
 def _status():

@@ -36,6 +36,11 @@ from ..core.tensor.api import Tensor
 from ..core.tensor.impl import TensorImpl
 
 
+import os as _os
+
+_NVTX = _os.environ.get("NABLA_B200_NVTX", "0") == "1"
+
+
 @dataclass
 class CompilationStats:
     hits: int = 0
@@ -126,6 +131,23 @@ class CompiledFunction:
 
     def clear_cache(self) -> None:
         self._cache.clear()
+
+    def dump_plan(self, file=None) -> str:
+        """Text listing of every recorded schedule: one line per step with its kind (``op`` or
+        the name of a fused step), the op names it covers and the output shapes."""
+        lines = []
+        for entry in self._cache.values():
+            for rec in entry.values():
+                lines.append(f"plan: {len(rec.nodes)} nodes, {len(rec.steps)} steps, "
+                             f"{sum(rec.donated)} donated inputs, cuda_graph={rec.cuda_graph is not None}")
+                for si, (kind, idxs) in enumerate(rec.steps):
+                    names = "+".join(rec.nodes[i].op.name for i in idxs)
+                    outs = [tuple(o._shape) for o in rec.keep[idxs[-1]]] if idxs[-1] < len(rec.keep) else []
+                    lines.append(f"  {si:5d} {kind:20s} {names:40s} -> {outs}")
+        text = "\n".join(lines)
+        if file is not None:
+            print(text, file=file)
+        return text
 
     # ---- keys
     def _signature(self, t: Tensor, arg_idx: int | None) -> tuple[tuple, tuple]:
@@ -269,7 +291,10 @@ class CompiledFunction:
         _STATS["nodes_executed"] += len(nodes)
         if self.profile_ops and not torch.cuda.is_current_stream_capturing():
             return self._run_profiled(rec)
+        nvtx = _NVTX and torch.cuda.is_available()
         for si, (kind, idxs) in enumerate(rec.steps):
+            if nvtx:       # one range per plan step (NABLA_B200_NVTX=1), visible in timeline profilers
+                torch.cuda.nvtx.range_push(kind if kind != "op" else nodes[idxs[0]].op.name)
             if kind == "op":
                 n = nodes[idxs[0]]
                 outs = n.op.execute(n)
@@ -279,6 +304,8 @@ class CompiledFunction:
                         o._buffers = outs[i]
             else:
                 fusion.run_fused(kind, [nodes[i] for i in idxs], keep_graph=True, arena_blocks=rec.arena_blocks)
+            if nvtx:
+                torch.cuda.nvtx.range_pop()
             for dead in rec.free_after[si]:
                 dead._buffers = None
                 blk = rec.arena_blocks.pop(id(dead), None)

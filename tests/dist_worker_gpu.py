@@ -67,6 +67,7 @@ def main():
         out["max_err"] = max(errs.values())
         out["errs"] = {k: v for k, v in errs.items() if v > 1e-2}
         out["timeout_probe_status"] = symm.wait_flag_timeout_probe(20.0)
+        out["canary_ok"] = ws.check_canary()        # nothing wrote past the end of the workspace
         # bandwidth of the large all-reduce (device time, max over ranks)
         x = torch.randn(64 * 1024 * 1024, device=dev, dtype=torch.bfloat16)
         for name, fn in (("native", lambda: symm.all_reduce(x, mesh, ("x",))), ("nccl", lambda: dist.all_reduce(x.clone()))):

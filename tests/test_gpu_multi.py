@@ -40,6 +40,7 @@ def test_peer_collectives_match_nccl():
     for r in rs:
         assert r["symm_ready"] and r["max_err"] < 2e-2 and not r["errs"], r
         assert r["timeout_probe_status"] == 4      # the bounded wait reported NB_ERR_TIMEOUT_PEER, context alive
+        assert r["canary_ok"]
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
