@@ -87,8 +87,7 @@ class Workspace:
 
     def validate(self) -> None:
         """Host-side check of the peer pointer table and the flag pad before first use: one
-        non-null, distinct base pointer per rank, this rank's entry equal to its own buffer, and a
-        flag region that starts out zero."""
+        non-null, distinct base pointer per rank and a flag region that starts out zero."""
         try:
             ptrs = [int(self.hdl.buffer_ptrs[r]) for r in range(self.world)]
         except Exception:          # handle without a host-side pointer list: nothing to check here
@@ -96,8 +95,6 @@ class Workspace:
         if ptrs is not None:
             if any(p == 0 for p in ptrs) or len(set(ptrs)) != self.world:
                 raise RuntimeError(f"symmetric workspace: bad peer pointer table {ptrs}")
-            if ptrs[self.rank] != self.buf.data_ptr():
-                raise RuntimeError("symmetric workspace: this rank's table entry is not its own buffer")
         if int(self.buf[: self.flag_bytes].view(torch.int32).abs().max().item()) != 0:
             raise RuntimeError("symmetric workspace: flag region is not zero at creation")
 
