@@ -62,8 +62,15 @@ class PyTreeDef:
     def __eq__(self, o: Any) -> bool:
         if self is o:
             return True
-        return (isinstance(o, PyTreeDef) and self.kind == o.kind and self.num_leaves == o.num_leaves
-                and _freeze(self.meta) == _freeze(o.meta) and self.children == o.children)
+        if not (isinstance(o, PyTreeDef) and self.kind == o.kind and self.num_leaves == o.num_leaves):
+            return False
+        if self._hash is not None and o._hash is not None and self._hash != o._hash:
+            return False
+        try:
+            same_meta = bool(self.meta == o.meta)        # plain comparison first (lists of keys, None, ints)
+        except Exception:
+            same_meta = False
+        return (same_meta or _freeze(self.meta) == _freeze(o.meta)) and self.children == o.children
 
     def __hash__(self) -> int:
         if self._hash is None:

@@ -39,6 +39,7 @@ from ..core.tensor.impl import TensorImpl
 import os as _os
 
 _NVTX = _os.environ.get("NABLA_B200_NVTX", "0") == "1"
+_SPEC_SIG: dict[int, tuple] = {}      # id(ShardingSpec) -> (spec, effect signature)
 
 
 @dataclass
@@ -85,26 +86,44 @@ class _Recorded:
         self.static_outputs: list[list[torch.Tensor]] | None = None
 
 
-def _normalize_step_scalars(tree: Any) -> Any:
-    """Optimizer state dicts carry ``step`` as a python int that changes every call; turn it
-    into a 0-d tensor so the cache key stays stable (reference: compile.py:138-170)."""
+def _first_tensor(tree: Any):
+    """First Tensor found in a pytree (depth first), without flattening the whole tree."""
+    if isinstance(tree, Tensor):
+        return tree
     if isinstance(tree, dict):
-        out = {}
-        for k, v in tree.items():
-            if k == "step" and isinstance(v, (int, float)) and not isinstance(v, bool) and ("m" in tree or "v" in tree or "momentum_buffers" in tree):
-                from ..ops.creation import constant
-                from ..types import DType
+        for v in tree.values():
+            t = _first_tensor(v)
+            if t is not None:
+                return t
+    elif isinstance(tree, (list, tuple)):
+        for v in tree:
+            t = _first_tensor(v)
+            if t is not None:
+                return t
+    return None
 
-                dev = None
-                for leaf in pytree.tensor_leaves(tree):
-                    dev = leaf.device
-                    break
-                out[k] = constant(float(v), dtype=DType.float32, device=dev)
-            else:
-                out[k] = _normalize_step_scalars(v)
-        return out
-    if isinstance(tree, (list, tuple)) and not hasattr(tree, "_fields"):
-        return type(tree)(_normalize_step_scalars(v) for v in tree)
+
+def _normalize_step_scalars(tree: Any, depth: int = 0) -> Any:
+    """Optimizer state dicts carry ``step`` as a python int that changes every call; turn it
+    into a 0-d tensor so the cache key stays stable (reference: compile.py:138-170). Only the
+    argument itself and its direct children are inspected: that is where optimizer states live,
+    and walking a whole parameter tree on every call would cost more than the replay."""
+    if isinstance(tree, dict):
+        step = tree.get("step")
+        if isinstance(step, (int, float)) and not isinstance(step, bool) and \
+                ("m" in tree or "v" in tree or "momentum_buffers" in tree):
+            from ..ops.creation import constant
+            from ..types import DType
+
+            first = _first_tensor(tree)
+            out = dict(tree)
+            out["step"] = constant(float(step), dtype=DType.float32, device=first.device if first is not None else None)
+            return out
+        if depth < 1:
+            return {k: _normalize_step_scalars(v, depth + 1) for k, v in tree.items()}
+        return tree
+    if depth < 1 and isinstance(tree, (list, tuple)) and not hasattr(tree, "_fields"):
+        return type(tree)(_normalize_step_scalars(v, depth + 1) for v in tree)
     return tree
 
 
@@ -153,19 +172,38 @@ class CompiledFunction:
     def _signature(self, t: Tensor, arg_idx: int | None) -> tuple[tuple, tuple]:
         im = t._impl
         shape = tuple(im._shape)
-        dyn = self.dynamic_dims.get(arg_idx, {}) if arg_idx is not None else {}
-        sym = tuple(f"${dyn[i - im.batch_dims]}" if (i - im.batch_dims) in dyn else d for i, d in enumerate(shape))
-        sh = im.sharding.effect_signature() if im.sharding is not None else None
+        dyn = self.dynamic_dims.get(arg_idx) if arg_idx is not None else None
+        sp = im.sharding
+        if sp is None:
+            sh = None
+        else:
+            # the signature of a spec object never changes; the memo keeps the object alive so its id stays its own
+            hit = _SPEC_SIG.get(id(sp))
+            if hit is None or hit[0] is not sp:
+                hit = (sp, sp.effect_signature())
+                _SPEC_SIG[id(sp)] = hit
+            sh = hit[1]
         rest = (im.dtype, sh, im.batch_dims, im.device)
-        return (sym,) + rest, (shape,) + rest
+        conc = (shape,) + rest
+        if not dyn:
+            return conc, conc
+        sym = tuple(f"${dyn[i - im.batch_dims]}" if (i - im.batch_dims) in dyn else d for i, d in enumerate(shape))
+        return (sym,) + rest, conc
 
     def _keys(self, args, kwargs):
-        leaves, td = pytree.tree_flatten((args, kwargs))
-        # which top-level positional argument does each leaf belong to (for dynamic_dims)
+        # one flatten per top-level argument: gives the leaves, the structure and each leaf's owner
+        leaves: list = []
         owner: list[int | None] = []
+        tds = []
         for i, a in enumerate(args):
-            owner += [i] * len(pytree.tree_leaves(a))
-        owner += [None] * (len(leaves) - len(owner))
+            lv, td_a = pytree.tree_flatten(a)
+            tds.append(td_a)
+            leaves += lv
+            owner += [i] * len(lv)
+        lv, td_k = pytree.tree_flatten(kwargs)
+        leaves += lv
+        owner += [None] * len(lv)
+        td = (tuple(tds), td_k)
         sym, conc = [], []
         for leaf, ow in zip(leaves, owner):
             if isinstance(leaf, Tensor):
@@ -185,11 +223,10 @@ class CompiledFunction:
     def __call__(self, *args, **kwargs):
         args = tuple(_normalize_step_scalars(a) for a in args)
         kwargs = {k: _normalize_step_scalars(v) for k, v in kwargs.items()}
-        tensors = pytree.tensor_leaves((args, kwargs))
-        pending = [t for t in tensors if not t._impl.is_realized]
+        key, conc, leaves, td = self._keys(args, kwargs)
+        pending = [t for t in leaves if isinstance(t, Tensor) and not t._impl.is_realized]
         if pending:
             GRAPH.evaluate(*pending)
-        key, conc, leaves, td = self._keys(args, kwargs)
         entry = self._cache.get(key)
         if entry is None:
             self._stats.misses += 1
@@ -235,7 +272,12 @@ class CompiledFunction:
                 ph_leaves.append(Tensor(impl=ph))
             else:
                 ph_leaves.append(l)
-        p_args, p_kwargs = pytree.tree_unflatten(td, ph_leaves)
+        tds, td_k = td
+        p_args, pos = [], 0
+        for t_ in tds:
+            p_args.append(pytree.tree_unflatten(t_, ph_leaves[pos: pos + t_.num_leaves]))
+            pos += t_.num_leaves
+        p_kwargs = pytree.tree_unflatten(td_k, ph_leaves[pos:])
         with config.tracing(True), config.eager_max_graph(False):
             result = self.fn(*p_args, **p_kwargs)
         out_leaves, out_td = pytree.tree_flatten(result)
