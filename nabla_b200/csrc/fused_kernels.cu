@@ -82,7 +82,16 @@ __device__ __forceinline__ float block_max(float v, float* sh) {
 }
 
 // ============================================================== LayerNorm
-// One warp per row. The row is read once into registers when D <= 32 * VPL * Vec::N.
+template <typename T>
+__device__ __forceinline__ void unpack_vec(const uint4& raw, float* out) {
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < Vec<T>::N; ++i) out[i] = to_f<T>(e[i]);
+}
+
+// One warp per row. The row is read once and stays in registers in its packed 16-byte form
+// (D <= 32 * VPL * Vec::N); it is unpacked for the mean, the variance and the output, which keeps
+// the register count low enough for the number of rows in flight that a bandwidth-bound pass needs.
 template <typename T, int VPL>
 __global__ void __launch_bounds__(128) layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
                                                            const T* __restrict__ beta, T* __restrict__ y,
@@ -93,15 +102,21 @@ __global__ void __launch_bounds__(128) layernorm_fwd_kernel(const T* __restrict_
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
   const T* xr = x + (size_t)row * D;
-  float v[VPL][V];
+  uint4 raw[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = (i * 32 + lane) * V;
+    if (c < D) raw[i] = *reinterpret_cast<const uint4*>(xr + c);
+  }
   float s = 0.f;
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     const int c = (i * 32 + lane) * V;
     if (c < D) {
-      load_vec<T>(xr + c, v[i]);
+      float v[V];
+      unpack_vec<T>(raw[i], v);
 #pragma unroll
-      for (int j = 0; j < V; ++j) s += v[i][j];
+      for (int j = 0; j < V; ++j) s += v[j];
     }
   }
   const float mu = warp_sum(s) / D;
@@ -110,9 +125,11 @@ __global__ void __launch_bounds__(128) layernorm_fwd_kernel(const T* __restrict_
   for (int i = 0; i < VPL; ++i) {
     const int c = (i * 32 + lane) * V;
     if (c < D) {
+      float v[V];
+      unpack_vec<T>(raw[i], v);
 #pragma unroll
       for (int j = 0; j < V; ++j) {
-        const float d = v[i][j] - mu;
+        const float d = v[j] - mu;
         q += d * d;
       }
     }
@@ -127,12 +144,13 @@ __global__ void __launch_bounds__(128) layernorm_fwd_kernel(const T* __restrict_
   for (int i = 0; i < VPL; ++i) {
     const int c = (i * 32 + lane) * V;
     if (c < D) {
-      float g[V], b[V], o[V];
+      float g[V], b[V], o[V], v[V];
+      unpack_vec<T>(raw[i], v);
       if (gamma) load_vec<T>(gamma + c, g);
       if (beta) load_vec<T>(beta + c, b);
 #pragma unroll
       for (int j = 0; j < V; ++j) {
-        float n = (v[i][j] - mu) * rs;
+        float n = (v[j] - mu) * rs;
         o[j] = n * (gamma ? g[j] : 1.f) + (beta ? b[j] : 0.f);
       }
       store_vec<T>(yr + c, o);
@@ -143,13 +161,6 @@ __global__ void __launch_bounds__(128) layernorm_fwd_kernel(const T* __restrict_
 // Backward, part 1: dx. One warp per row. The row's x and dy stay in registers in their packed
 // 16-byte form (half the registers of keeping them as floats, so twice as many rows are in flight
 // per SM for this bandwidth-bound pass) and are unpacked once for the two sums and once for dx.
-template <typename T>
-__device__ __forceinline__ void unpack_vec(const uint4& raw, float* out) {
-  const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-  for (int i = 0; i < Vec<T>::N; ++i) out[i] = to_f<T>(e[i]);
-}
-
 template <typename T, int VPL>
 __global__ void __launch_bounds__(128) layernorm_bwd_dx_kernel(const T* __restrict__ dy, const T* __restrict__ x,
                                                               const T* __restrict__ gamma, const float* __restrict__ mean,
