@@ -433,9 +433,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (s_abort != 0) return;
   }
   const int nkt = (args.Skv + BN - 1) / BN;
+  // key tile 0 sees every query tile, the last one only a few: tile index slowest, so that the
+  // long CTAs start first and the short ones fill the end of the grid
   int bid = blockIdx.x;
-  const int jt = bid % nkt;
-  bid /= nkt;
+  const int bh = args.H * args.B;
+  const int jt = bid / bh;
+  bid -= jt * bh;
   const int h = bid % args.H;
   const int b = bid / args.H;
   const int k0 = jt * BN;
