@@ -10,6 +10,7 @@ CUDA bf16 tensors:
 * ``matmul | linear (no bias) -> all_reduce(sum) | reduce_scatter`` on a mesh that runs one
   process per GPU: one launch of the fused GEMM + collective kernel (tiles are reduced over
   NVLink while later tiles are still being multiplied).
+* ``linear (+bias) -> add(residual)``: the residual is added in the GEMM epilogue.
 * ``matmul -> dact_mul`` (backward of linear + relu/gelu): the activation derivative is applied in
   the GEMM epilogue.
 * compiled replays with donated optimizer state: ``matmul -> all_reduce(dp) -> adam_wstep`` becomes a
@@ -30,6 +31,9 @@ import torch
 
 from ..tensor.impl import TensorImpl
 from .tracing import OpNode
+
+
+_FUSE_RESIDUAL = os.environ.get("NABLA_B200_FUSE_RESIDUAL", "0") == "1"
 
 
 def enabled() -> bool:
@@ -92,6 +96,17 @@ def build_plan(nodes: list[OpNode], targets: list[TensorImpl]):
             if dk is not None:
                 chain = [i, dk]
                 kind = "gemm_dact"
+        if chain is None and _FUSE_RESIDUAL and n.op.name == "linear" and n.kwargs.get("activation") is None \
+                and _is_local_linear(n):
+            # y = x @ w + b followed by "+ residual" of the same shape: the residual is added in the epilogue
+            o = sole_output(n)
+            if (o is not None and id(o) not in target_ids and len(cons.get(id(o), [])) == 1 and o.batch_dims == 0
+                    and not (o.sharding is not None and o.sharding.partial_sum_axes)):
+                k = cons[id(o)][0]
+                a_ = nodes[k]
+                if not used[k] and a_.op.name == "add" and _same_layout_addend(a_, o):
+                    chain = [i, k]
+                    kind = "gemm_residual"
         if chain is None and n.op.name in ("matmul", "linear") and _is_partial_gemm(n):
             o = sole_output(n)
             # a traced product may stay an unrealized promise: no backward rule reads its value
@@ -183,6 +198,31 @@ def _is_local_gemm(n: OpNode) -> bool:
 
     return (a.device.label == "gpu" and a.dtype is DType.bfloat16 and b.dtype is DType.bfloat16
             and len(b._shape) == 2 and len(a._shape) >= 2 and a.batch_dims == 0 and b.batch_dims == 0)
+
+
+def _is_local_linear(n: OpNode) -> bool:
+    ins = n.input_impls()
+    if len(ins) not in (2, 3):
+        return False
+    a, b = ins[0], ins[1]
+    from ...types import DType
+
+    return (a.device.label == "gpu" and a.dtype is DType.bfloat16 and b.dtype is DType.bfloat16
+            and len(b._shape) == 2 and len(a._shape) >= 2 and a.batch_dims == 0 and b.batch_dims == 0)
+
+
+def _same_layout_addend(add: OpNode, x: TensorImpl) -> bool:
+    ins = add.input_impls()
+    if len(ins) != 2:
+        return False
+    other = ins[1] if ins[0] is x else ins[0] if ins[1] is x else None
+    if other is None or other is x or other.batch_dims or other.dtype is not x.dtype or tuple(other._shape) != tuple(x._shape):
+        return False
+    sa = [tuple(d.axes) for d in other.sharding.dim_specs] if other.sharding is not None else None
+    sb = [tuple(d.axes) for d in x.sharding.dim_specs] if x.sharding is not None else None
+    if sa != sb:
+        return False
+    return not (other.sharding is not None and other.sharding.partial_sum_axes)
 
 
 def _dact_consumer(mm: OpNode, nodes, cons, target_ids, used) -> int | None:
@@ -340,6 +380,24 @@ def run_fused(kind: str, group: list[OpNode], keep_graph: bool = False, arena_bl
                 o._buffers = [out]
         else:
             store_outputs(last, [[out]])
+        return
+    if kind == "gemm_residual":
+        from ...native.gemm import gemm_bf16
+
+        lin, add = group
+        ins = lin.input_impls()
+        a, b = ins[0]._buffers[0], ins[1]._buffers[0]
+        bias = ins[2]._buffers[0] if len(ins) > 2 else None
+        lin_out = lin.outputs()[0]
+        res = [x for x in add.input_impls() if x is not lin_out][0]._buffers[0]
+        if a.is_cuda and a.numel() and b.numel():
+            n_out = b.shape[-1]
+            out = gemm_bf16(a.reshape(-1, a.shape[-1]), b, bias=bias, aux="add",
+                            aux_in=res.reshape(-1, n_out)).reshape(*a.shape[:-1], n_out)
+            _store(add, [[out]], keep_graph)
+        else:
+            _plain(lin, keep_graph)
+            _plain(add, keep_graph)
         return
     if kind == "gemm_dact":
         from ...native.gemm import gemm_bf16
