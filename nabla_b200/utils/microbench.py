@@ -51,6 +51,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--block-n", type=int, default=0, help="gemm: force the tile width (256, 128 or 64)")
     a = ap.parse_args()
 
     from nabla_b200 import native
@@ -67,7 +68,7 @@ def main() -> None:
         w = torch.randn(a.k, a.n, device=dev, dtype=bf)
         b = torch.randn(a.n, device=dev, dtype=bf)
         if a.kernel == "gemm":
-            fn = lambda: gemm_bf16(x, w)
+            fn = lambda: gemm_bf16(x, w, block_n=a.block_n)
         else:
             fn = lambda: gemm_bf16(x, w, bias=b, epilogue="gelu", aux="store_preact")
         flops = 2.0 * a.m * a.n * a.k
