@@ -82,6 +82,7 @@ class _Recorded:
         self.arena_blocks: dict[int, tuple] = {}    # gathered tensors living in a symmetric arena
         self.arena_ok: set[int] = set()             # ids of impls that may live there (never returned)
         self.donated: list[bool] = []               # per placeholder
+        self.out_cached: list | None = None         # Tensor objects of outputs that alias donated inputs
         self.static_inputs: list[list[torch.Tensor]] | None = None
         self.static_outputs: list[list[torch.Tensor]] | None = None
 
@@ -458,12 +459,24 @@ class CompiledFunction:
                 if dst.data_ptr() != src.data_ptr():
                     dst.copy_(src)
         rec.cuda_graph.replay()
+        if rec.out_cached is None:
+            # results that live entirely in a donated input's buffers are the same storage on
+            # every replay: their Tensor objects are built once and handed back as they are
+            rec.out_cached = []
+            for impl, bufs in zip(rec.out_impls, rec.static_outputs):
+                if impl is not None and all(b.data_ptr() in rec.static_ptrs for b in bufs):
+                    rec.out_cached.append(Tensor(impl=TensorImpl(list(bufs), shape=impl._shape, dtype=impl.dtype,
+                                                                device=impl.device, sharding=impl.sharding,
+                                                                batch_dims=impl.batch_dims)))
+                else:
+                    rec.out_cached.append(None)
         outs = []
-        for impl, static, bufs in zip(rec.out_impls, rec.out_static, rec.static_outputs):
+        for impl, static, bufs, cached in zip(rec.out_impls, rec.out_static, rec.static_outputs, rec.out_cached):
             if impl is None:
                 outs.append(static)
+            elif cached is not None:
+                outs.append(cached)
             else:
-                # results that live in a donated input's buffer are handed back as they are
                 res = [b if b.data_ptr() in rec.static_ptrs else b.clone() for b in bufs]
                 new = TensorImpl(res, shape=impl._shape, dtype=impl.dtype, device=impl.device,
                                  sharding=impl.sharding, batch_dims=impl.batch_dims)
