@@ -1,31 +1,43 @@
 // Flash attention for sm_100a on tcgen05 tensor cores with TMEM accumulators.
 //
-//   O = softmax(Q K^T * scale [+ causal mask]) V        per (batch, head), never materialising
-//                                                       the (seq_q, seq_k) score matrix
+//   O = softmax(Q K^T * scale [+ mask] [+ causal mask]) V     per (batch, head), never materialising
+//                                                             the (seq_q, seq_k) score matrix
 //
 // Replaces the reference's composed attention (matmul, mul, tril, where, softmax, matmul:
 // nabla/nn/functional/layers.py:106-153), whose memory is O(seq^2).
 //
-// Forward: one CTA per (batch, head, 128 query rows), 256 threads:
-//   warp 0     TMA producer: Q once, K/V tiles (128 keys) into a 2-stage ring (4-D tensor maps
-//              over strided (B, H, S, D) views, so packed qkv projections are read in place)
-//   warp 1     MMA issuer: S_j = Q K_j^T into one of two TMEM score buffers, O += P_j V_j
-//   warp 2     TMEM allocator
-//   warps 4-7  softmax: thread r owns query row r (TMEM lane r): scale, mask, online max/sum in
-//              the log2 domain, P (bf16) to swizzled smem as the A operand of the second MMA,
-//              lazy rescaling of the O accumulator in TMEM, final normalisation and store
-// S is double buffered so the tensor core computes S_{j+1} while the softmax works on S_j.
+// Three kernels, all with the same warp roles (384 threads, one CTA per SM):
+//   warp 0      TMA producer (4-D tensor maps over strided (B, H, S, D) views, so q/k/v sliced out
+//               of a packed projection are read in place)
+//   warp 1      MMA issuer (one elected thread)
+//   warp 2      TMEM allocator
+//   warps 4-11  two math warpgroups of 128 threads; thread r of a group owns TMEM lane r
 //
-// Backward: see attn_bwd_* below (dK/dV per key tile with tensor-core GEMMs for S^T, dP^T,
-// dV, dK and dQ; dQ accumulated with fp32 reductions).
+// The probabilities never touch shared memory: the math threads write P (bf16, two values per
+// 32-bit TMEM column) over the score columns they have just read, and the second MMA takes its A
+// operand from TMEM. Shared memory then only feeds Q / K / V / dO, which halves the operand
+// traffic of the PV-type products.
+//
+// forward (attn_fwd_kernel): one CTA owns TWO query tiles (2 x 128 rows) that share the K / V
+//   stream. Group A works on the softmax of tile A while the tensor core runs tile B's products
+//   and vice versa (S_A, S_B, O_A, O_B = 512 TMEM columns at head_dim 128).
+// backward, dK / dV (attn_bwd_dkdv_kernel): one CTA owns 128 keys and walks over the query
+//   tiles: S^T = K Q^T, dP^T = V dO^T, P^T and dS^T written back into TMEM as A operands of
+//   dV += P^T dO and dK += dS^T Q. The two groups split the 128 query columns of a tile.
+// backward, dQ (attn_bwd_dq_kernel): one CTA owns 128 queries and walks over the key tiles:
+//   S = Q K^T (double buffered), dP = dO V^T, dS into TMEM, dQ += dS K accumulated in TMEM and
+//   stored once as bf16: no atomics, no fp32 scratch, deterministic.
+// A small kernel before the backward computes delta = rowsum(dO * O) and log2-domain row
+// statistics padded to whole tiles.
 #include "sm100_ptx.cuh"
+#include <stdlib.h>
 
 namespace nba {
 using namespace nb;
 
-constexpr int BM = 128;
-constexpr int BN = 128;
-constexpr int NTHREADS = 256;
+constexpr int BT = 128;          // tile edge, queries and keys
+constexpr int NTHREADS = 384;
+constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2,
                                             int c3) {
@@ -37,7 +49,83 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
         "r"(c3)
       : "memory");
 }
+// Untiled bulk copy global -> shared; both addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      :
+      : "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+// tcgen05.wait::ld that names the 32 loaded registers as in/out operands: everything that reads
+// them afterwards depends on the wait, so the compiler cannot schedule a use above it. This lets a
+// loop issue the load of the next chunk before it works on the current one.
+__device__ __forceinline__ void tmem_ld_wait32(uint32_t (&v)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                 "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+                 "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]),
+                 "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+               :
+               : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ float2 f2(uint32_t a, uint32_t b) { return make_float2(__uint_as_float(a), __uint_as_float(b)); }
 
+// D[128 x 128] = A[128 x HD] B[128 x HD]^T : both operands K-major tiles of HD / 64 swizzled chunks.
+template <int HD>
+__device__ __forceinline__ void mma_scores(uint32_t d_tmem, uint32_t a0, uint32_t b0) {
+  constexpr uint32_t idesc = make_idesc_bf16(BT, BT, 0, 0);
+#pragma unroll
+  for (int k = 0; k < HD / 16; ++k) {
+    const uint64_t da = make_smem_desc_sw128(a0 + (k >> 2) * (BT * 128) + (k & 3) * 32, 16, 1024);
+    const uint64_t db = make_smem_desc_sw128(b0 + (k >> 2) * (BT * 128) + (k & 3) * 32, 16, 1024);
+    umma_f16_ss(d_tmem, da, db, idesc, k != 0);
+  }
+}
+// D[128 x HD] (+)= A[128 x 128] B[128 x HD] : A (bf16 pairs) in TMEM, B in shared memory with the
+// reduction index as rows and HD contiguous. `split`: the A columns of k-steps 4-7 start 64 TMEM
+// columns after those of k-steps 0-3 (each math group writes inside the columns it has read).
+template <int HD>
+__device__ __forceinline__ void mma_accum(uint32_t d_tmem, uint32_t a_tmem, bool split, uint32_t b0, bool accumulate) {
+  constexpr uint32_t idesc = make_idesc_bf16(BT, HD, 0, 1);
+#pragma unroll
+  for (int k = 0; k < BT / 16; ++k) {
+    const uint64_t db = make_smem_desc_sw128(b0 + k * (16 * 128), BT * 128, 1024);
+    const uint32_t a = a_tmem + (split ? 64 * (k >> 2) + 8 * (k & 3) : 8 * k);
+    umma_f16_ts(d_tmem, a, db, idesc, (accumulate || k != 0) ? 1u : 0u);
+  }
+}
+
+// Optional additive mask (fp32, natural-log domain), element (b, h, q, key) at
+// mask[b * sb + h * sh + q * sq + key]; strides of 0 broadcast.
+struct MaskArg {
+  const float* ptr;
+  long long sb, sh, sq;
+};
+
+// ====================================================================== forward
 struct FwdArgs {
   int B, H, Sq, Skv;
   float scale_log2;   // softmax scale * log2(e)
@@ -45,21 +133,20 @@ struct FwdArgs {
   __nv_bfloat16* O;
   long long o_sb, o_sh, o_ss;   // element strides of O for batch, head, row
   float* lse;                   // [B][H][Sq]
+  MaskArg mask;
   int* status;
+  int dbg;
 };
 
 template <int HD>
 struct FwdSmem {
-  static constexpr int Q_BYTES = BM * HD * 2;
-  static constexpr int KV_BYTES = BN * HD * 2;
-  static constexpr int P_BYTES = BM * BN * 2;
-  static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = OFF_Q + Q_BYTES;
-  static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
-  static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int TILE_BYTES = BT * HD * 2;
+  static constexpr int OFF_Q = 0;                          // 2 query tiles
+  static constexpr int OFF_K = OFF_Q + 2 * TILE_BYTES;     // 2 stages
+  static constexpr int OFF_V = OFF_K + 2 * TILE_BYTES;     // 2 stages
+  static constexpr int OFF_BAR = OFF_V + 2 * TILE_BYTES;
   static constexpr int RAW = OFF_BAR + 16 * 8 + 16 + 1024;
-  static constexpr int TOTAL = RAW < 120 * 1024 ? 120 * 1024 : RAW;   // keep one CTA per SM (TMEM)
+  static constexpr int TOTAL = RAW < 120 * 1024 ? 120 * 1024 : RAW;   // one CTA per SM (it takes all of TMEM)
 };
 
 template <int HD>
@@ -72,15 +159,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* sQ = smem + L::OFF_Q;
   uint8_t* sK = smem + L::OFF_K;
   uint8_t* sV = smem + L::OFF_V;
-  uint8_t* sP = smem + L::OFF_P;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
-  uint64_t* q_full = bars + 0;
-  uint64_t* kv_full = bars + 1;    // [2]
-  uint64_t* kv_empty = bars + 3;   // [2]
-  uint64_t* s_full = bars + 5;     // [2]
-  uint64_t* p_full = bars + 7;
-  uint64_t* pv_done = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* q_full = bars + 0;     // [2] per query tile
+  uint64_t* k_full = bars + 2;     // [2]
+  uint64_t* k_empty = bars + 4;    // [2]
+  uint64_t* v_full = bars + 6;     // [2]
+  uint64_t* v_empty = bars + 8;    // [2]
+  uint64_t* s_full = bars + 10;    // [2] per query tile: scores of the next key tile are in TMEM
+  uint64_t* p_full = bars + 12;    // [2] per query tile: probabilities are in TMEM (128 arrivals)
+  uint64_t* o_done = bars + 14;    // [2] per query tile: last PV product has retired
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   {
@@ -89,32 +177,41 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __syncthreads();
     if (s_abort != 0) return;
   }
-  const int nqt = (args.Sq + BM - 1) / BM;
+  const int nqt = (args.Sq + 2 * BT - 1) / (2 * BT);
   int bid = blockIdx.x;
   const int qt = nqt - 1 - (bid % nqt);   // heavy (late) causal tiles first
   bid /= nqt;
   const int h = bid % args.H;
   const int b = bid / args.H;
-  const int q0 = qt * BM;
+  const int q0 = qt * 2 * BT;
   const int off = args.Skv - args.Sq;     // causal: row i sees keys <= i + off
-  int n_tiles = (args.Skv + BN - 1) / BN;
-  if (args.causal) {
-    const int last_key = min(args.Skv - 1, q0 + BM - 1 + off);
-    n_tiles = last_key < 0 ? 0 : last_key / BN + 1;
+  int n_t[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int q0t = q0 + t * BT;
+    int n = (args.Skv + BT - 1) / BT;
+    if (args.causal) {
+      const int last_key = min(args.Skv - 1, q0t + BT - 1 + off);
+      n = last_key < 0 ? 0 : last_key / BT + 1;
+    }
+    n_t[t] = q0t < args.Sq ? n : 0;
   }
+  const int n_max = max(n_t[0], n_t[1]);
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
-    mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&q_full[i], 1);
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 128);
+      mbar_init(&o_done[i], 1);
     }
-    mbar_init(p_full, 128);
-    mbar_init(pv_done, 1);
     fence_mbar_init();
     fence_proxy_async_smem();
   }
@@ -126,193 +223,199 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 256;
+  // tile t: scores (and P over their first 64 columns) at t * 128, output accumulator at 256 + t * HD
 
   if (warp == 0) {
-    if (lane == 0 && n_tiles > 0) {
-      mbar_arrive_expect_tx(q_full, L::Q_BYTES);
+    if (lane == 0 && n_max > 0) {
+      for (int t = 0; t < 2; ++t) {
+        if (n_t[t] == 0) continue;
+        mbar_arrive_expect_tx(&q_full[t], L::TILE_BYTES);
 #pragma unroll
-      for (int c = 0; c < HD / 64; ++c) tma_load_4d(sQ + c * (BM * 128), &tmQ, q_full, c * 64, q0, h, b);
-      for (int j = 0; j < n_tiles; ++j) {
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_4d(sQ + t * L::TILE_BYTES + c * (BT * 128), &tmQ, &q_full[t], c * 64, q0 + t * BT, h, b);
+      }
+      for (int j = 0; j < n_max; ++j) {
         const int st = j & 1;
-        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1)) {
-          atomicExch(args.status, NB_ERR_TIMEOUT_PRODUCER);
-          break;
-        }
-        mbar_arrive_expect_tx(&kv_full[st], 2 * L::KV_BYTES);
+        const uint32_t ph = ((j >> 1) & 1) ^ 1;
+        if (!mbar_wait(&k_empty[st], ph)) { atomicExch(args.status, NB_ERR_TIMEOUT_PRODUCER); break; }
+        mbar_arrive_expect_tx(&k_full[st], L::TILE_BYTES);
 #pragma unroll
-        for (int c = 0; c < HD / 64; ++c) {
-          tma_load_4d(sK + st * L::KV_BYTES + c * (BN * 128), &tmK, &kv_full[st], c * 64, j * BN, h, b);
-          tma_load_4d(sV + st * L::KV_BYTES + c * (BN * 128), &tmV, &kv_full[st], c * 64, j * BN, h, b);
-        }
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_4d(sK + st * L::TILE_BYTES + c * (BT * 128), &tmK, &k_full[st], c * 64, j * BT, h, b);
+        if (!mbar_wait(&v_empty[st], ph)) { atomicExch(args.status, NB_ERR_TIMEOUT_PRODUCER); break; }
+        mbar_arrive_expect_tx(&v_full[st], L::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_4d(sV + st * L::TILE_BYTES + c * (BT * 128), &tmV, &v_full[st], c * 64, j * BT, h, b);
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && n_tiles > 0) {
-      const uint32_t idesc_qk = make_idesc_bf16(BM, BN, 0, 0);
-      const uint32_t idesc_pv = make_idesc_bf16(BM, HD, 0, 1);
-      bool ok = mbar_wait(q_full, 0);
-      auto issue_qk = [&](int j) {
-        const int st = j & 1;
-        const uint32_t a0 = smem_u32(sQ), b0 = smem_u32(sK + st * L::KV_BYTES);
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const uint64_t da = make_smem_desc_sw128(a0 + (k >> 2) * (BM * 128) + (k & 3) * 32, 16, 1024);
-          const uint64_t db = make_smem_desc_sw128(b0 + (k >> 2) * (BN * 128) + (k & 3) * 32, 16, 1024);
-          umma_f16_ss(tmem_base + (j & 1) * BN, da, db, idesc_qk, k != 0);
-        }
-        umma_commit(&s_full[j & 1]);
+    if (lane == 0 && n_max > 0) {
+      bool ok = true;
+      auto qk = [&](int t, int j) {
+        if (!(args.dbg & 2)) mma_scores<HD>(tmem_base + t * BT, smem_u32(sQ + t * L::TILE_BYTES), smem_u32(sK + (j & 1) * L::TILE_BYTES));
+        umma_commit(&s_full[t]);
       };
-      auto issue_pv = [&](int j) {
-        const int st = j & 1;
-        const uint32_t a0 = smem_u32(sP), b0 = smem_u32(sV + st * L::KV_BYTES);
-#pragma unroll
-        for (int k = 0; k < BN / 16; ++k) {
-          const uint64_t da = make_smem_desc_sw128(a0 + (k >> 2) * (BM * 128) + (k & 3) * 32, 16, 1024);
-          const uint64_t db = make_smem_desc_sw128(b0 + k * (16 * 128), BN * 128, 1024);
-          umma_f16_ss(tmem_o, da, db, idesc_pv, (j | k) != 0);
-        }
-        umma_commit(&kv_empty[st]);   // K_j / V_j slot reusable once these MMAs retire
-        umma_commit(pv_done);
+      auto pv = [&](int t, int j) {
+        if (!(args.dbg & 4)) mma_accum<HD>(tmem_base + 256 + t * HD, tmem_base + t * BT, false, smem_u32(sV + (j & 1) * L::TILE_BYTES), j != 0);
+        if (j == n_t[t] - 1) umma_commit(&o_done[t]);
       };
-      if (!ok) atomicExch(args.status, NB_ERR_TIMEOUT_MMA);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (!mbar_wait(&kv_full[j & 1], (j >> 1) & 1)) { ok = false; break; }
-        tc_fence_after();
-        issue_qk(j);
-        if (j > 0) {
-          if (!mbar_wait(p_full, (j - 1) & 1)) { ok = false; break; }
-          tc_fence_after();
-          issue_pv(j - 1);
-        }
-      }
+      for (int t = 0; t < 2 && ok; ++t)
+        if (n_t[t] > 0) ok = mbar_wait(&q_full[t], 0);
+      ok = ok && mbar_wait(&k_full[0], 0);
       if (ok) {
-        if (mbar_wait(p_full, (n_tiles - 1) & 1)) {
-          tc_fence_after();
-          issue_pv(n_tiles - 1);
-        } else {
-          ok = false;
+        tc_fence_after();
+        if (n_t[0] > 0) qk(0, 0);
+        if (n_t[1] > 0) qk(1, 0);
+        umma_commit(&k_empty[0]);
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const bool more = j + 1 < n_max;
+        if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1)) { ok = false; break; }
+        if (more && !mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1)) { ok = false; break; }
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (j < n_t[t]) {
+            if (!mbar_wait(&p_full[t], j & 1)) { ok = false; break; }
+            tc_fence_after();
+            pv(t, j);
+          }
+          if (t == 1) umma_commit(&v_empty[j & 1]);
+          if (j + 1 < n_t[t]) qk(t, j + 1);
         }
+        if (!ok) break;
+        if (more) umma_commit(&k_empty[(j + 1) & 1]);
       }
       if (!ok) atomicExch(args.status, NB_ERR_TIMEOUT_MMA);
     }
   } else if (warp >= 4) {
+    const int t = (warp - 4) >> 2;          // query tile of this math group
     const int wq = warp & 3;
     const int r = wq * 32 + lane;
-    const int q_idx = q0 + r;
+    const int q_idx = q0 + t * BT + r;
+    const int n = n_t[t];
     const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;
+    const uint32_t t_s = tmem_base + t * BT + lane_addr;
+    const uint32_t t_o = tmem_base + 256 + t * HD + lane_addr;
+    const float* mrow = nullptr;
+    if (args.mask.ptr != nullptr && q_idx < args.Sq)
+      mrow = args.mask.ptr + b * args.mask.sb + h * args.mask.sh + (long long)q_idx * args.mask.sq;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int sb = j & 1;
-      if (ok && !mbar_wait(&s_full[sb], (j >> 1) & 1)) {
+    for (int j = 0; j < n; ++j) {
+      if (ok && !mbar_wait(&s_full[t], j & 1)) {
         atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
         ok = false;
       }
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      float s[BN];
-#pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_base + sb * BN + lane_addr + c * 32, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[i]);
-      }
-      tmem_ld_wait();
-      const int kv0 = j * BN;
-      const bool need_mask = (kv0 + BN > args.Skv) || (args.causal && (kv0 + BN - 1 > q0 + off));
-      float mx = -INFINITY;
-      if (need_mask) {
+      if (args.dbg & 1) { tc_fence_before(); mbar_arrive(&p_full[t]); continue; }
+      const int kv0 = j * BT;
+      const bool general = (kv0 + BT > args.Skv) || (args.causal && (kv0 + BT - 1 > q0 + t * BT + off)) ||
+                           (args.mask.ptr != nullptr);
+      if (general) {
+        // masked tile (diagonal, tail or user mask): rewrite the scores in place, -inf where a key is
+        // not visible, so that the two passes below carry no mask logic
         const int lim = args.causal ? min(args.Skv - 1, q_idx + off) : args.Skv - 1;
+        const float mask_mul = LOG2E / args.scale_log2;
+#pragma unroll 1
+        for (int c = 0; c < BT / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_s + c * 32, v);
+          tmem_ld_wait32(v);
 #pragma unroll
-        for (int c = 0; c < BN; ++c) {
-          const float x = (kv0 + c <= lim) ? s[c] * args.scale_log2 : -INFINITY;
-          s[c] = x;
-          mx = fmaxf(mx, x);
+          for (int i = 0; i < 32; ++i) {
+            const int kc = kv0 + c * 32 + i;
+            float x = __uint_as_float(v[i]);
+            if (mrow != nullptr && kc < args.Skv) x = fmaf(mrow[kc], mask_mul, x);
+            v[i] = __float_as_uint(kc <= lim ? x : -INFINITY);
+          }
+          tmem_st_32x32(t_s + c * 32, v);
         }
-      } else {
-#pragma unroll
-        for (int c = 0; c < BN; ++c) {
-          s[c] *= args.scale_log2;
-          mx = fmaxf(mx, s[c]);
-        }
+        tmem_st_wait();
       }
+      // pass 1: row maximum. The load of the next 32 columns is in flight while the current ones
+      // are reduced (four independent chains of three-input max).
+      uint32_t va[32], vb[32];
+      tmem_ld_32x32(t_s, va);
+      float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < BT / 32; ++c) {
+        uint32_t (&v)[32] = (c & 1) ? vb : va;
+        uint32_t (&nx)[32] = (c & 1) ? va : vb;
+        tmem_ld_wait32(v);
+        tmem_ld_32x32(t_s + ((c + 1) & 3) * 32, nx);       // after the last chunk: chunk 0 again, for pass 2
+#pragma unroll
+        for (int i = 0; i < 16; ++i) mxa[i & 3] = max3(mxa[i & 3], __uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+      }
+      const float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])) * args.scale_log2;
       // lazy rescale: keep the old reference maximum unless the new one exceeds it by 2^8
       float alpha = 1.f;
       bool resc = false;
-      if (j == 0) {
-        m_used = (mx == -INFINITY) ? 0.f : mx;
+      if (m_used == -INFINITY) {
+        m_used = mx;                       // may stay -inf: every key so far is masked for this row
       } else if (mx > m_used + 8.f) {
-        alpha = exp2f(m_used - mx);
+        alpha = ex2(m_used - mx);
         m_used = mx;
         resc = true;
       }
-      float sum = 0.f;
+      const float m_sub = m_used == -INFINITY ? 0.f : m_used;
+      if (__any_sync(0xffffffffu, resc)) {
+        // s_full of this tile also tracks the previous PV product: O is not being written now
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_o + c * 32, v);
+          tmem_ld_wait32(v);
 #pragma unroll
-      for (int c = 0; c < BN; ++c) {
-        s[c] = exp2f(s[c] - m_used);
-        sum += s[c];
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_st_32x32(t_o + c * 32, v);
+        }
       }
+      // pass 2: probabilities (bf16 pairs) written over the first 64 score columns; packed fp32x2
+      // arithmetic: per pair one FFMA2, two EX2, one FADD2, one pack
+      const float2 sc2 = make_float2(args.scale_log2, args.scale_log2), nm2 = make_float2(-m_sub, -m_sub);
+      float2 acc[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+      for (int c = 0; c < BT / 32; ++c) {
+        uint32_t (&v)[32] = (c & 1) ? vb : va;
+        uint32_t (&nx)[32] = (c & 1) ? va : vb;
+        tmem_ld_wait32(v);
+        if (c + 1 < BT / 32) tmem_ld_32x32(t_s + (c + 1) * 32, nx);
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float2 x = __ffma2_rn(f2(v[2 * i], v[2 * i + 1]), sc2, nm2);
+          const float2 pr = make_float2(ex2(x.x), ex2(x.y));
+          acc[i & 1] = __fadd2_rn(acc[i & 1], pr);
+          pk[i] = pack_bf16(pr.x, pr.y);
+        }
+        tmem_st_32x16(t_s + c * 16, pk);
+      }
+      const float sum = (acc[0].x + acc[0].y) + (acc[1].x + acc[1].y);
       l = l * alpha + sum;
-      if (j > 0) {
-        if (!mbar_wait(pv_done, (j - 1) & 1)) {
-          atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
-          ok = false;
-        }
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, resc)) {
-#pragma unroll
-          for (int c = 0; c < HD / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st_32x32(tmem_o + lane_addr + c * 32, v);
-          }
-          tmem_st_wait();
-        }
-      }
-      // P (bf16) into the K-major SWIZZLE_128B layout the second MMA reads
-#pragma unroll
-      for (int cc = 0; cc < BN / 64; ++cc) {
-        uint8_t* rowp = sP + cc * (BM * 128) + r * 128;
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          uint4 pk;
-          uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            __nv_bfloat162 hh = __floats2bfloat162_rn(s[cc * 64 + u * 8 + 2 * e], s[cc * 64 + u * 8 + 2 * e + 1]);
-            pw[e] = *reinterpret_cast<uint32_t*>(&hh);
-          }
-          *reinterpret_cast<uint4*>(rowp + ((u ^ (r & 7)) << 4)) = pk;
-        }
-      }
-      fence_proxy_async_smem();
+      tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[t]);
     }
-    if (ok && n_tiles > 0) {
-      if (!mbar_wait(pv_done, (n_tiles - 1) & 1)) {
+    if (ok && n > 0) {
+      if (!mbar_wait(&o_done[t], 0)) {
         atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
         ok = false;
       }
       ok = __all_sync(0xffffffffu, ok);
     }
-    if (ok) {
+    if (ok && q0 + t * BT < args.Sq) {
       tc_fence_after();
-      const float inv = (n_tiles > 0 && l > 0.f) ? 1.f / l : 0.f;
+      const bool have = n > 0 && l > 0.f;
+      const float inv = have ? 1.f / l : 0.f;
       __nv_bfloat16* orow = args.O + (long long)b * args.o_sb + (long long)h * args.o_sh + (long long)q_idx * args.o_ss;
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t v[32];
-        if (n_tiles > 0) {
-          tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
+        if (n > 0) {
+          tmem_ld_32x32(t_o + c * 32, v);
           tmem_ld_wait();
         } else {
 #pragma unroll
@@ -324,18 +427,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             uint4 pk;
             uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(v[u * 8 + 2 * e]) * inv,
-                                                        __uint_as_float(v[u * 8 + 2 * e + 1]) * inv);
-              pw[e] = *reinterpret_cast<uint32_t*>(&hh);
-            }
+            for (int e = 0; e < 4; ++e)
+              pw[e] = pack_bf16(__uint_as_float(v[u * 8 + 2 * e]) * inv, __uint_as_float(v[u * 8 + 2 * e + 1]) * inv);
             *reinterpret_cast<uint4*>(orow + c * 32 + u * 8) = pk;
           }
         }
       }
       if (q_idx < args.Sq)
         args.lse[((long long)b * args.H + h) * args.Sq + q_idx] =
-            (n_tiles > 0 && l > 0.f) ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+            have ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
     }
   }
 
@@ -348,108 +448,84 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 }
 
 // ====================================================================== backward
-// One CTA per (batch, head, 128 keys). K_j and V_j stay in shared memory; the CTA walks over the
-// query tiles (64 rows) that see these keys. Per query tile, on the tensor cores:
-//   S^T  = K_j Q_i^T            (128 x 64, TMEM)       dP^T = V_j dO_i^T        (128 x 64, TMEM)
-//   P^T  = exp2(S^T * c - lse_i),  dS^T = P^T * (dP^T - delta_i) * scale      (softmax warps,
-//          thread = key row; both written as bf16 A operands into swizzled smem)
-//   dV  += P^T dO_i   dK += dS^T Q_i   (128 x 128 accumulators in TMEM for the whole loop)
-//   dQ_i^T = K_j^T dS^T (128 x 64)  -> fp32 vector reductions into a [B][H][D][Sq_pad] scratch
-// Two small kernels bracket it: delta_i = rowsum(dO_i * O_i), and the conversion of the dQ
-// scratch (transposed, fp32) to the caller's bf16 layout.
-//
-// Two query tiles are in flight: math group 0 (warps 4-7) owns the even tiles, group 1 (warps
-// 8-11) the odd ones, each with its own S^T / dP^T columns in TMEM and its own P^T / dS^T buffers
-// in shared memory, so the tensor pipe works on one tile's five MMAs while the other tile's
-// exponentials and dS are computed. dQ_i^T is written over tile i's dP^T columns (which the math
-// threads have consumed by then): 2 x (64 + 64) + 128 + 128 = 512 TMEM columns.
-constexpr int BQ = 64;
-constexpr int BWD_THREADS = 384;
-
 struct BwdArgs {
   int B, H, Sq, Skv, Sq_pad;
   float scale, scale_log2;
   int causal;
-  const float* lse;     // [B][H][Sq] natural log
-  const float* delta;   // [B][H][Sq]
-  float* dq_acc;        // [B][H][128][Sq_pad]
-  __nv_bfloat16 *dK, *dV;
-  long long dk_sb, dk_sh, dk_ss, dv_sb, dv_sh, dv_ss;
+  const float* nlse2;   // [B][H][Sq_pad]  -(log-sum-exp) in the log2 domain; -inf on padding rows and rows without keys
+  const float* ndelta;  // [B][H][Sq_pad]  -rowsum(dO * O), 0 on padding rows
+  __nv_bfloat16 *dQ, *dK, *dV;
+  long long dq_sb, dq_sh, dq_ss, dk_sb, dk_sh, dk_ss, dv_sb, dv_sh, dv_ss;
+  MaskArg mask;
   int* status;
 };
 
-struct BwdSmem {
-  static constexpr int HD = 128;
-  static constexpr int KV_BYTES = BN * HD * 2;        // 32 KB
-  static constexpr int QT_BYTES = BQ * HD * 2;        // 16 KB
-  static constexpr int XY_BYTES = BN * BQ * 2;        // 16 KB
+// ---------------------------------------------------------------------- dK / dV
+template <int HD>
+struct DkvSmem {
+  static constexpr int TILE_BYTES = BT * HD * 2;
   static constexpr int OFF_K = 0;
-  static constexpr int OFF_V = OFF_K + KV_BYTES;
-  static constexpr int OFF_Q = OFF_V + KV_BYTES;      // 2 stages
-  static constexpr int OFF_DO = OFF_Q + 2 * QT_BYTES;
-  static constexpr int OFF_X = OFF_DO + 2 * QT_BYTES;  // 2 buffers (one per math group)
-  static constexpr int OFF_Y = OFF_X + 2 * XY_BYTES;   // 2 buffers
-  static constexpr int OFF_STAT = OFF_Y + 2 * XY_BYTES;   // lse2[2][64], delta[2][64]
-  static constexpr int OFF_BAR = OFF_STAT + 4 * BQ * 4;
-  static constexpr int TOTAL = OFF_BAR + 24 * 8 + 16 + 1024;
+  static constexpr int OFF_V = OFF_K + TILE_BYTES;
+  static constexpr int OFF_Q = OFF_V + TILE_BYTES;        // 2 stages
+  static constexpr int OFF_DO = OFF_Q + 2 * TILE_BYTES;   // 2 stages
+  static constexpr int OFF_STAT = OFF_DO + 2 * TILE_BYTES;   // lse2[2][128], delta[2][128]
+  static constexpr int OFF_BAR = OFF_STAT + 4 * BT * 4;
+  static constexpr int RAW = OFF_BAR + 24 * 8 + 16 + 1024;
+  static constexpr int TOTAL = RAW < 120 * 1024 ? 120 * 1024 : RAW;
 };
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
-__global__ void __launch_bounds__(BWD_THREADS, 1)
-attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
-                const BwdArgs args) {
-  using L = BwdSmem;
-  constexpr int HD = 128;
+template <int HD>
+__global__ void __launch_bounds__(NTHREADS, 1)
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                     const BwdArgs args) {
+  using L = DkvSmem<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem + L::OFF_K;
   uint8_t* sV = smem + L::OFF_V;
   uint8_t* sQ = smem + L::OFF_Q;
   uint8_t* sDO = smem + L::OFF_DO;
-  uint8_t* sX = smem + L::OFF_X;
-  uint8_t* sY = smem + L::OFF_Y;
-  float* s_lse2 = reinterpret_cast<float*>(smem + L::OFF_STAT);   // [2][64]
-  float* s_delta = s_lse2 + 2 * BQ;                               // [2][64]
+  float* s_nlse2 = reinterpret_cast<float*>(smem + L::OFF_STAT);   // [2][128]
+  float* s_ndelta = s_nlse2 + 2 * BT;                              // [2][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* kv_full = bars + 0;
-  uint64_t* qdo_full = bars + 1;    // [2]  Q_i / dO_i landed in stage i & 1
-  uint64_t* qdo_empty = bars + 3;   // [2]  the MMAs that read the stage have retired
-  uint64_t* sdp_full = bars + 5;    // [2]  S^T and dP^T of the group's tile are in TMEM
-  uint64_t* xy_full = bars + 7;     // [2]  P^T and dS^T of the group's tile are in shared memory (128 arrivals)
-  uint64_t* g2_done = bars + 9;     // [2]  dV / dK / dQ^T MMAs of the group's tile have retired
-  uint64_t* dq_free = bars + 11;    // [2]  dQ^T of the group's tile has been drained (128 arrivals)
-  uint64_t* all_done = bars + 13;   //      every MMA of the CTA has retired
+  uint64_t* q_full = bars + 1;     // [2]  Q_i and its lse2 landed in stage i & 1
+  uint64_t* q_empty = bars + 3;    // [2]
+  uint64_t* do_full = bars + 5;    // [2]  dO_i and its delta landed
+  uint64_t* do_empty = bars + 7;   // [2]
+  uint64_t* s_full = bars + 9;     //      S^T of the current tile is in TMEM
+  uint64_t* dp_full = bars + 10;   //      dP^T of the current tile is in TMEM
+  uint64_t* p_full = bars + 11;    //      P^T written back (256 arrivals)
+  uint64_t* ds_full = bars + 12;   //      dS^T written back (256 arrivals)
+  uint64_t* all_done = bars + 13;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   {
-    __shared__ int s_abort;   // an earlier bounded wait on this device already failed: leave (uniformly)
+    __shared__ int s_abort;
     if (threadIdx.x == 0) s_abort = *reinterpret_cast<volatile int*>(args.status);
     __syncthreads();
     if (s_abort != 0) return;
   }
-  const int nkt = (args.Skv + BN - 1) / BN;
   // key tile 0 sees every query tile, the last one only a few: tile index slowest, so that the
   // long CTAs start first and the short ones fill the end of the grid
   int bid = blockIdx.x;
-  const int bh = args.H * args.B;
-  const int jt = bid / bh;
-  bid -= jt * bh;
+  const int nbh = args.H * args.B;
+  const int jt = bid / nbh;
+  bid -= jt * nbh;
   const int h = bid % args.H;
   const int b = bid / args.H;
-  const int k0 = jt * BN;
+  const int k0 = jt * BT;
   const int off = args.Skv - args.Sq;
-  const int nqt = (args.Sq + BQ - 1) / BQ;
+  const int nqt = (args.Sq + BT - 1) / BT;
   int i_start = 0;
   if (args.causal) {
     const int first_q = k0 - off;             // first query row that sees key k0
-    i_start = first_q <= 0 ? 0 : first_q / BQ;
+    i_start = first_q <= 0 ? 0 : first_q / BT;
   }
   const int n_it = max(0, nqt - i_start);
+  const long long bh = (long long)b * args.H + h;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmQ);
@@ -458,13 +534,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tma_prefetch_desc(&tmDO);
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&qdo_full[i], 1);
-      mbar_init(&qdo_empty[i], 1);
-      mbar_init(&sdp_full[i], 1);
-      mbar_init(&xy_full[i], 128);
-      mbar_init(&g2_done[i], 1);
-      mbar_init(&dq_free[i], 128);
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+      mbar_init(&do_full[i], 1);
+      mbar_init(&do_empty[i], 1);
     }
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(p_full, 256);
+    mbar_init(ds_full, 256);
     mbar_init(all_done, 1);
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -477,206 +555,164 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t t_dv = tmem_base + 256, t_dk = tmem_base + 384;
-  // group g: S^T at columns g*128 .. +63, dP^T (later dQ^T) at g*128 + 64 .. +127
+  const uint32_t t_st = tmem_base, t_dpt = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 256 + HD;
 
   if (warp == 0) {
     if (lane == 0 && n_it > 0) {
-      mbar_arrive_expect_tx(kv_full, 2 * L::KV_BYTES);
+      mbar_arrive_expect_tx(kv_full, 2 * L::TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < HD / 64; ++c) {
-        tma_load_4d(sK + c * (BN * 128), &tmK, kv_full, c * 64, k0, h, b);
-        tma_load_4d(sV + c * (BN * 128), &tmV, kv_full, c * 64, k0, h, b);
+        tma_load_4d(sK + c * (BT * 128), &tmK, kv_full, c * 64, k0, h, b);
+        tma_load_4d(sV + c * (BT * 128), &tmV, kv_full, c * 64, k0, h, b);
       }
       for (int it = 0; it < n_it; ++it) {
         const int st = it & 1;
-        if (!mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1)) {
-          atomicExch(args.status, NB_ERR_TIMEOUT_PRODUCER);
-          break;
-        }
-        mbar_arrive_expect_tx(&qdo_full[st], 2 * L::QT_BYTES);
-        const int q0 = (i_start + it) * BQ;
+        const uint32_t ph = ((it >> 1) & 1) ^ 1;
+        const int q0 = (i_start + it) * BT;
+        if (!mbar_wait(&q_empty[st], ph)) { atomicExch(args.status, NB_ERR_TIMEOUT_PRODUCER); break; }
+        mbar_arrive_expect_tx(&q_full[st], L::TILE_BYTES + BT * 4);
 #pragma unroll
-        for (int c = 0; c < HD / 64; ++c) {
-          tma_load_4d(sQ + st * L::QT_BYTES + c * (BQ * 128), &tmQ, &qdo_full[st], c * 64, q0, h, b);
-          tma_load_4d(sDO + st * L::QT_BYTES + c * (BQ * 128), &tmDO, &qdo_full[st], c * 64, q0, h, b);
-        }
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_4d(sQ + st * L::TILE_BYTES + c * (BT * 128), &tmQ, &q_full[st], c * 64, q0, h, b);
+        bulk_load_1d(s_nlse2 + st * BT, args.nlse2 + bh * args.Sq_pad + q0, BT * 4, &q_full[st]);
+        if (!mbar_wait(&do_empty[st], ph)) { atomicExch(args.status, NB_ERR_TIMEOUT_PRODUCER); break; }
+        mbar_arrive_expect_tx(&do_full[st], L::TILE_BYTES + BT * 4);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_4d(sDO + st * L::TILE_BYTES + c * (BT * 128), &tmDO, &do_full[st], c * 64, q0, h, b);
+        bulk_load_1d(s_ndelta + st * BT, args.ndelta + bh * args.Sq_pad + q0, BT * 4, &do_full[st]);
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && n_it > 0) {
-      const uint32_t id_g1 = make_idesc_bf16(128, BQ, 0, 0);    // S^T, dP^T : A K-major, B K-major
-      const uint32_t id_g2 = make_idesc_bf16(128, HD, 0, 1);    // dV, dK    : A K-major, B MN-major
-      const uint32_t id_dq = make_idesc_bf16(128, BQ, 1, 1);    // dQ^T      : A MN-major, B MN-major
-      // Descriptors are built once; inside the loops an operand advances by adding a constant to
-      // the descriptor's start-address field (16-byte units), so the issuing thread spends a few
-      // instructions per MMA and keeps ahead of the tensor pipe (the MMAs are only 128 x 64 x 16).
-      const uint64_t dK_k = make_smem_desc_sw128(smem_u32(sK), 16, 1024);            // K as K-major A
-      const uint64_t dV_k = make_smem_desc_sw128(smem_u32(sV), 16, 1024);
-      const uint64_t dK_mn = make_smem_desc_sw128(smem_u32(sK), BN * 128, 1024);     // K as MN-major A (dQ^T)
-      // stage / group 1 operands sit a fixed distance after stage / group 0: one add selects them
-      const uint64_t dQ_k0 = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
-      const uint64_t dDO_k0 = make_smem_desc_sw128(smem_u32(sDO), 16, 1024);
-      const uint64_t dQ_mn0 = make_smem_desc_sw128(smem_u32(sQ), BQ * 128, 1024);
-      const uint64_t dDO_mn0 = make_smem_desc_sw128(smem_u32(sDO), BQ * 128, 1024);
-      const uint64_t dX0 = make_smem_desc_sw128(smem_u32(sX), 16, 1024);
-      const uint64_t dY_k0 = make_smem_desc_sw128(smem_u32(sY), 16, 1024);
-      const uint64_t dY_mn0 = make_smem_desc_sw128(smem_u32(sY), BN * 128, 1024);
-      auto g1 = [&](int it) {       // S^T and dP^T of tile `it` into its group's columns
-        const int g = it & 1;
-        const uint32_t t_s = tmem_base + g * 128, t_dp = t_s + 64;
-        const uint64_t bq = dQ_k0 + (uint64_t)(g * (L::QT_BYTES >> 4)), bdo = dDO_k0 + (uint64_t)(g * (L::QT_BYTES >> 4));
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const uint64_t ko = (uint64_t)(((k >> 2) * (BN * 128) + (k & 3) * 32) >> 4);     // K/V chunk + in-row offset
-          const uint64_t qo = (uint64_t)(((k >> 2) * (BQ * 128) + (k & 3) * 32) >> 4);
-          umma_f16_ss(t_s, dK_k + ko, bq + qo, id_g1, k != 0);
-        }
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const uint64_t ko = (uint64_t)(((k >> 2) * (BN * 128) + (k & 3) * 32) >> 4);
-          const uint64_t qo = (uint64_t)(((k >> 2) * (BQ * 128) + (k & 3) * 32) >> 4);
-          umma_f16_ss(t_dp, dV_k + ko, bdo + qo, id_g1, k != 0);
-        }
-        umma_commit(&sdp_full[g]);
-      };
-      bool ok = mbar_wait(kv_full, 0);
-      for (int t = 0; t < 2 && t < n_it && ok; ++t) {
-        ok = mbar_wait(&qdo_full[t], 0);
-        if (ok) {
-          tc_fence_after();
-          g1(t);
-        }
+      bool ok = mbar_wait(kv_full, 0) && mbar_wait(&q_full[0], 0);
+      if (ok) {
+        tc_fence_after();
+        mma_scores<HD>(t_st, smem_u32(sK), smem_u32(sQ));            // S^T_0 = K Q_0^T
+        umma_commit(s_full);
+        ok = mbar_wait(&do_full[0], 0);
+      }
+      if (ok) {
+        tc_fence_after();
+        mma_scores<HD>(t_dpt, smem_u32(sV), smem_u32(sDO));          // dP^T_0 = V dO_0^T
+        umma_commit(dp_full);
       }
       for (int it = 0; it < n_it && ok; ++it) {
-        const int g = it & 1;
-        if (!mbar_wait(&xy_full[g], (it >> 1) & 1)) { ok = false; break; }
+        const int st = it & 1;
+        const bool more = it + 1 < n_it;
+        if (!mbar_wait(p_full, it & 1)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t gq = (uint64_t)(g * (L::QT_BYTES >> 4)), gx = (uint64_t)(g * (L::XY_BYTES >> 4));
-        const uint64_t dXg = dX0 + gx, dYkg = dY_k0 + gx, dYmng = dY_mn0 + gx;
-        const uint64_t dQmng = dQ_mn0 + gq, dDOmng = dDO_mn0 + gq;
-        // dV += P^T dO_i ; dK += dS^T Q_i   (K = 64 query rows -> 4 k-steps)
-#pragma unroll
-        for (int k = 0; k < BQ / 16; ++k)
-          umma_f16_ss(t_dv, dXg + (uint64_t)((k * 32) >> 4), dDOmng + (uint64_t)((k * 16 * 128) >> 4), id_g2,
-                      (it | k) != 0);
-#pragma unroll
-        for (int k = 0; k < BQ / 16; ++k)
-          umma_f16_ss(t_dk, dYkg + (uint64_t)((k * 32) >> 4), dQmng + (uint64_t)((k * 16 * 128) >> 4), id_g2,
-                      (it | k) != 0);
-        // dQ_i^T = K_j^T dS^T : M = head dim, N = 64 queries, K = 128 keys; over the tile's dP^T columns
-        const uint32_t t_dq = tmem_base + g * 128 + 64;
-#pragma unroll
-        for (int k = 0; k < BN / 16; ++k)
-          umma_f16_ss(t_dq, dK_mn + (uint64_t)((k * 16 * 128) >> 4), dYmng + (uint64_t)((k * 16 * 128) >> 4), id_dq,
-                      k != 0);
-        umma_commit(&qdo_empty[g]);
-        umma_commit(&g2_done[g]);
-        if (it >= 1 && it + 1 < n_it) {
-          // tile it + 1 belongs to the other group: its columns are free once dQ of tile it - 1 is drained
-          const int o = g ^ 1;
-          if (!mbar_wait(&dq_free[o], ((it - 1) >> 1) & 1)) { ok = false; break; }
-          if (!mbar_wait(&qdo_full[o], ((it + 1) >> 1) & 1)) { ok = false; break; }
+        mma_accum<HD>(t_dv, t_st, true, smem_u32(sDO + st * L::TILE_BYTES), it != 0);     // dV += P^T dO_i
+        umma_commit(&do_empty[st]);
+        if (more) {
+          if (!mbar_wait(&q_full[st ^ 1], ((it + 1) >> 1) & 1)) { ok = false; break; }
           tc_fence_after();
-          g1(it + 1);
+          mma_scores<HD>(t_st, smem_u32(sK), smem_u32(sQ + (st ^ 1) * L::TILE_BYTES));
+          umma_commit(s_full);
+        }
+        if (!mbar_wait(ds_full, it & 1)) { ok = false; break; }
+        tc_fence_after();
+        mma_accum<HD>(t_dk, t_dpt, true, smem_u32(sQ + st * L::TILE_BYTES), it != 0);     // dK += dS^T Q_i
+        umma_commit(&q_empty[st]);
+        if (more) {
+          if (!mbar_wait(&do_full[st ^ 1], ((it + 1) >> 1) & 1)) { ok = false; break; }
+          tc_fence_after();
+          mma_scores<HD>(t_dpt, smem_u32(sV), smem_u32(sDO + (st ^ 1) * L::TILE_BYTES));
+          umma_commit(dp_full);
         }
       }
       if (ok) umma_commit(all_done);
       else atomicExch(args.status, NB_ERR_TIMEOUT_MMA);
     }
   } else if (warp >= 4) {
-    const int grp = (warp - 4) >> 2;        // math group: 0 = even query tiles, 1 = odd ones
-    const int wq = warp & 3;                // TMEM lane quarter this warp may read
-    const int r = wq * 32 + lane;           // key row inside the tile / head-dim row for dQ^T
-    const int et = (threadIdx.x - 128) & 127;
+    const int grp = (warp - 4) >> 2;        // query columns [64 grp, 64 grp + 64) of every tile
+    const int wq = warp & 3;
+    const int r = wq * 32 + lane;           // key row inside the tile
     const int key = k0 + r;
-    const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;
-    const uint32_t t_s = tmem_base + grp * 128, t_dp = t_s + 64;
-    const long long bh = (long long)b * args.H + h;
-    uint8_t* xr = sX + grp * L::XY_BYTES + r * 128;
-    uint8_t* yr = sY + grp * L::XY_BYTES + r * 128;
     const bool key_ok = key < args.Skv;
+    const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;
+    const uint32_t a_s = t_st + lane_addr + grp * 64, a_dp = t_dpt + lane_addr + grp * 64;
+    const float* mbase = args.mask.ptr == nullptr ? nullptr : args.mask.ptr + b * args.mask.sb + h * args.mask.sh + key;
     bool ok = true;
-    for (int it = grp; it < n_it; it += 2) {
-      const int q0 = (i_start + it) * BQ;
-      const uint32_t ph = (it >> 1) & 1;
-      // stage the per-query statistics of this tile (the group's previous tile is fully consumed)
-      {
-        const int qi = q0 + (et & 63);
-        const bool inr = qi < args.Sq;
-        if (et < 64) s_lse2[grp * BQ + et] = inr ? args.lse[bh * args.Sq + qi] * 1.4426950408889634f : INFINITY;
-        else s_delta[grp * BQ + (et - 64)] = inr ? args.delta[bh * args.Sq + qi] : 0.f;
-      }
-      named_bar_sync(1 + grp, 128);
-      if (ok && !mbar_wait(&sdp_full[grp], ph)) {
+    for (int it = 0; it < n_it; ++it) {
+      const int st = it & 1;
+      const int q0 = (i_start + it) * BT + grp * 64;
+      if (ok && !(mbar_wait(&q_full[st], (it >> 1) & 1) && mbar_wait(s_full, it & 1))) {
         atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
         ok = false;
       }
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const bool need_mask = args.causal && (k0 + BN - 1 > q0 + off);
-      // the MMAs that read this group's P^T / dS^T buffers belong to its previous tile; their
-      // retirement was awaited before that tile's dQ was drained, so the buffers are free
-#pragma unroll
-      for (int c = 0; c < BQ / 32; ++c) {
-        uint32_t v[32], w[32];
-        tmem_ld_32x32(t_s + lane_addr + c * 32, v);
-        tmem_ld_32x32(t_dp + lane_addr + c * 32, w);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int qc = c * 32 + i;
-          float pv = exp2f(__uint_as_float(v[i]) * args.scale_log2 - s_lse2[grp * BQ + qc]);
-          if (!key_ok || (need_mask && key > q0 + qc + off)) pv = 0.f;
-          const float dsv = pv * (__uint_as_float(w[i]) - s_delta[grp * BQ + qc]) * args.scale;
-          v[i] = __float_as_uint(pv);
-          w[i] = __float_as_uint(dsv);
-        }
-        // X = P^T, Y = dS^T as bf16, one 128-byte swizzled row per key (4 x 16 bytes per 32 queries)
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint4 px, py;
-          uint32_t* wx = reinterpret_cast<uint32_t*>(&px);
-          uint32_t* wy = reinterpret_cast<uint32_t*>(&py);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            __nv_bfloat162 a = __floats2bfloat162_rn(__uint_as_float(v[u * 8 + 2 * e]), __uint_as_float(v[u * 8 + 2 * e + 1]));
-            __nv_bfloat162 d2 = __floats2bfloat162_rn(__uint_as_float(w[u * 8 + 2 * e]), __uint_as_float(w[u * 8 + 2 * e + 1]));
-            wx[e] = *reinterpret_cast<uint32_t*>(&a);
-            wy[e] = *reinterpret_cast<uint32_t*>(&d2);
-          }
-          const int sw = ((c * 4 + u) ^ (r & 7)) << 4;
-          *reinterpret_cast<uint4*>(xr + sw) = px;
-          *reinterpret_cast<uint4*>(yr + sw) = py;
-        }
-      }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(&xy_full[grp]);
-      // dQ^T of this tile: wait for its MMAs, then reduce it into the fp32 scratch
-      if (!mbar_wait(&g2_done[grp], ph)) {
-        atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
-        ok = false;
-      }
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      {
-        float* dst = args.dq_acc + (bh * HD + r) * (long long)args.Sq_pad + q0;
-#pragma unroll
-        for (int c = 0; c < BQ / 32; ++c) {
+      const bool general = (args.causal && (k0 + BT - 1 > q0 + off)) || (k0 + BT > args.Skv) || (mbase != nullptr);
+      if (general) {
+        // masked tile: rewrite S^T in place with -inf where (key, query) is not visible
+        const float mask_mul = LOG2E / args.scale_log2;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
           uint32_t v[32];
-          tmem_ld_32x32(t_dp + lane_addr + c * 32, v);
-          tmem_ld_wait();
+          tmem_ld_32x32(a_s + c * 32, v);
+          tmem_ld_wait32(v);
 #pragma unroll
-          for (int u = 0; u < 8; ++u)
-            red_add_v4(dst + c * 32 + u * 4, __uint_as_float(v[u * 4]), __uint_as_float(v[u * 4 + 1]),
-                       __uint_as_float(v[u * 4 + 2]), __uint_as_float(v[u * 4 + 3]));
+          for (int i = 0; i < 32; ++i) {
+            const int q = q0 + c * 32 + i;
+            float x = __uint_as_float(v[i]);
+            if (mbase != nullptr && key_ok && q < args.Sq) x = fmaf(mbase[(long long)q * args.mask.sq], mask_mul, x);
+            if (!key_ok || (args.causal && key > q + off)) x = -INFINITY;
+            v[i] = __float_as_uint(x);
+          }
+          tmem_st_32x32(a_s + c * 32, v);
         }
+        tmem_st_wait();
       }
+      const float2* nl2 = reinterpret_cast<const float2*>(s_nlse2 + st * BT + grp * 64);
+      const float2 sc2 = make_float2(args.scale_log2, args.scale_log2);
+      float2 p[32];
+      uint32_t va[32], vb[32];
+      tmem_ld_32x32(a_s, va);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t (&v)[32] = c ? vb : va;
+        tmem_ld_wait32(v);
+        if (c == 0) tmem_ld_32x32(a_s + 32, vb);
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float2 x = __ffma2_rn(f2(v[2 * i], v[2 * i + 1]), sc2, nl2[c * 16 + i]);
+          p[c * 16 + i] = make_float2(ex2(x.x), ex2(x.y));
+          pk[i] = pack_bf16(p[c * 16 + i].x, p[c * 16 + i].y);
+        }
+        tmem_st_32x16(a_s + c * 16, pk);
+      }
+      tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&dq_free[grp]);
+      mbar_arrive(p_full);
+      if (!(mbar_wait(&do_full[st], (it >> 1) & 1) && mbar_wait(dp_full, it & 1))) {
+        atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const float2* nd2 = reinterpret_cast<const float2*>(s_ndelta + st * BT + grp * 64);
+      tmem_ld_32x32(a_dp, va);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t (&v)[32] = c ? vb : va;
+        tmem_ld_wait32(v);
+        if (c == 0) tmem_ld_32x32(a_dp + 32, vb);
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          // dS^T / scale = P^T * (dP^T - delta); the scale is applied once, to dK, in the epilogue
+          const float2 d = __fmul2_rn(p[c * 16 + i], __fadd2_rn(f2(v[2 * i], v[2 * i + 1]), nd2[c * 16 + i]));
+          pk[i] = pack_bf16(d.x, d.y);
+        }
+        tmem_st_32x16(a_dp + c * 16, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(ds_full);
     }
     if (ok && n_it > 0) {
       if (!mbar_wait(all_done, 0)) {
@@ -691,12 +727,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       __nv_bfloat16* dst = grp == 0
           ? args.dK + (long long)b * args.dk_sb + (long long)h * args.dk_sh + (long long)key * args.dk_ss
           : args.dV + (long long)b * args.dv_sb + (long long)h * args.dv_sh + (long long)key * args.dv_ss;
-      const uint32_t src = grp == 0 ? t_dk : t_dv;
+      const uint32_t src = (grp == 0 ? t_dk : t_dv) + lane_addr;
+      const float mul = grp == 0 ? args.scale : 1.f;
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t v[32];
         if (n_it > 0) {
-          tmem_ld_32x32(src + lane_addr + c * 32, v);
+          tmem_ld_32x32(src + c * 32, v);
           tmem_ld_wait();
         } else {
 #pragma unroll
@@ -708,10 +745,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             uint4 pk;
             uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(v[u * 8 + 2 * e]), __uint_as_float(v[u * 8 + 2 * e + 1]));
-              pw[e] = *reinterpret_cast<uint32_t*>(&hh);
-            }
+            for (int e = 0; e < 4; ++e)
+              pw[e] = pack_bf16(__uint_as_float(v[u * 8 + 2 * e]) * mul, __uint_as_float(v[u * 8 + 2 * e + 1]) * mul);
             *reinterpret_cast<uint4*>(dst + c * 32 + u * 8) = pk;
           }
         }
@@ -727,53 +762,339 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-// delta[b][h][q] = sum_d dO * O ; one warp per row, head dim 128 (4 elements per lane)
-__global__ void __launch_bounds__(128) attn_delta_kernel(const __nv_bfloat16* __restrict__ dO,
-                                                        const __nv_bfloat16* __restrict__ O, float* __restrict__ delta,
-                                                        int B, int H, int Sq, int D, long long do_sb, long long do_sh,
-                                                        long long do_ss, long long o_sb, long long o_sh, long long o_ss) {
-  const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= (long long)B * H * Sq) return;
-  const int q = row % Sq;
-  const int h = (row / Sq) % H;
-  const int b = row / ((long long)Sq * H);
-  const __nv_bfloat16* a = dO + b * do_sb + h * do_sh + q * do_ss;
-  const __nv_bfloat16* c = O + b * o_sb + h * o_sh + q * o_ss;
+// ---------------------------------------------------------------------- dQ
+template <int HD>
+struct DqSmem {
+  static constexpr int TILE_BYTES = BT * HD * 2;
+  static constexpr int KST = 3;                             // K stages (a K tile is held until its dQ product retires)
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_DO = OFF_Q + TILE_BYTES;
+  static constexpr int OFF_K = OFF_DO + TILE_BYTES;
+  static constexpr int OFF_V = OFF_K + KST * TILE_BYTES;    // 2 stages
+  static constexpr int OFF_BAR = OFF_V + 2 * TILE_BYTES;
+  static constexpr int RAW = OFF_BAR + 24 * 8 + 16 + 1024;
+  static constexpr int TOTAL = RAW < 120 * 1024 ? 120 * 1024 : RAW;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(NTHREADS, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                   const BwdArgs args) {
+  using L = DqSmem<HD>;
+  constexpr int KST = L::KST;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + L::OFF_Q;
+  uint8_t* sDO = smem + L::OFF_DO;
+  uint8_t* sK = smem + L::OFF_K;
+  uint8_t* sV = smem + L::OFF_V;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* qdo_full = bars + 0;
+  uint64_t* k_full = bars + 1;     // [3]
+  uint64_t* k_empty = bars + 4;    // [3]
+  uint64_t* v_full = bars + 7;     // [2]
+  uint64_t* v_empty = bars + 9;    // [2]
+  uint64_t* s_full = bars + 11;    // [2]  score buffer j & 1 holds S_j
+  uint64_t* dp_full = bars + 13;   //      dP_j is in TMEM
+  uint64_t* ds_full = bars + 14;   //      dS_j written back (256 arrivals)
+  uint64_t* dq_done = bars + 15;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  {
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) s_abort = *reinterpret_cast<volatile int*>(args.status);
+    __syncthreads();
+    if (s_abort != 0) return;
+  }
+  const int nqt = (args.Sq + BT - 1) / BT;
+  int bid = blockIdx.x;
+  const int qt = nqt - 1 - (bid % nqt);   // heavy (late) causal tiles first
+  bid /= nqt;
+  const int h = bid % args.H;
+  const int b = bid / args.H;
+  const int q0 = qt * BT;
+  const int off = args.Skv - args.Sq;
+  int n = (args.Skv + BT - 1) / BT;
+  if (args.causal) {
+    const int last_key = min(args.Skv - 1, q0 + BT - 1 + off);
+    n = last_key < 0 ? 0 : last_key / BT + 1;
+  }
+  const long long bh = (long long)b * args.H + h;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmDO);
+    mbar_init(qdo_full, 1);
+    for (int i = 0; i < KST; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+    }
+    mbar_init(dp_full, 1);
+    mbar_init(ds_full, 256);
+    mbar_init(dq_done, 1);
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_dp = tmem_base + 256, t_dq = tmem_base + 384;   // S buffers at 0 and 128
+
+  if (warp == 0) {
+    if (lane == 0 && n > 0) {
+      mbar_arrive_expect_tx(qdo_full, 2 * L::TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c) {
+        tma_load_4d(sQ + c * (BT * 128), &tmQ, qdo_full, c * 64, q0, h, b);
+        tma_load_4d(sDO + c * (BT * 128), &tmDO, qdo_full, c * 64, q0, h, b);
+      }
+      for (int j = 0; j < n; ++j) {
+        const int ks = j % KST, vs = j & 1;
+        if (!mbar_wait(&k_empty[ks], ((j / KST) & 1) ^ 1)) { atomicExch(args.status, NB_ERR_TIMEOUT_PRODUCER); break; }
+        mbar_arrive_expect_tx(&k_full[ks], L::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_4d(sK + ks * L::TILE_BYTES + c * (BT * 128), &tmK, &k_full[ks], c * 64, j * BT, h, b);
+        if (!mbar_wait(&v_empty[vs], ((j >> 1) & 1) ^ 1)) { atomicExch(args.status, NB_ERR_TIMEOUT_PRODUCER); break; }
+        mbar_arrive_expect_tx(&v_full[vs], L::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_4d(sV + vs * L::TILE_BYTES + c * (BT * 128), &tmV, &v_full[vs], c * 64, j * BT, h, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n > 0) {
+      auto scores = [&](int j) {          // S_j = Q K_j^T into buffer j & 1
+        mma_scores<HD>(tmem_base + (j & 1) * BT, smem_u32(sQ), smem_u32(sK + (j % KST) * L::TILE_BYTES));
+        umma_commit(&s_full[j & 1]);
+      };
+      auto dprobs = [&](int j) {          // dP_j = dO V_j^T
+        mma_scores<HD>(t_dp, smem_u32(sDO), smem_u32(sV + (j & 1) * L::TILE_BYTES));
+        umma_commit(dp_full);
+        umma_commit(&v_empty[j & 1]);
+      };
+      bool ok = mbar_wait(qdo_full, 0) && mbar_wait(&k_full[0], 0);
+      if (ok) {
+        tc_fence_after();
+        scores(0);
+        ok = mbar_wait(&v_full[0], 0);
+      }
+      if (ok) {
+        tc_fence_after();
+        dprobs(0);
+        if (n > 1) {
+          ok = mbar_wait(&k_full[1], 0);
+          if (ok) {
+            tc_fence_after();
+            scores(1);
+          }
+        }
+      }
+      for (int j = 0; j < n && ok; ++j) {
+        if (!mbar_wait(ds_full, j & 1)) { ok = false; break; }
+        tc_fence_after();
+        mma_accum<HD>(t_dq, t_dp, true, smem_u32(sK + (j % KST) * L::TILE_BYTES), j != 0);   // dQ += dS_j K_j
+        umma_commit(&k_empty[j % KST]);
+        if (j + 1 < n) {
+          if (!mbar_wait(&v_full[(j + 1) & 1], ((j + 1) >> 1) & 1)) { ok = false; break; }
+          tc_fence_after();
+          dprobs(j + 1);
+        }
+        if (j + 2 < n) {
+          if (!mbar_wait(&k_full[(j + 2) % KST], ((j + 2) / KST) & 1)) { ok = false; break; }
+          tc_fence_after();
+          scores(j + 2);
+        }
+      }
+      if (ok) umma_commit(dq_done);
+      else atomicExch(args.status, NB_ERR_TIMEOUT_MMA);
+    }
+  } else if (warp >= 4) {
+    const int grp = (warp - 4) >> 2;        // key columns [64 grp, 64 grp + 64) of every tile
+    const int wq = warp & 3;
+    const int r = wq * 32 + lane;
+    const int q_idx = q0 + r;
+    const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;
+    const uint32_t a_dp = t_dp + lane_addr + grp * 64;
+    const float nlse2 = args.nlse2[bh * args.Sq_pad + q_idx];      // padded: always in range
+    const float ndelta = args.ndelta[bh * args.Sq_pad + q_idx];
+    const float* mrow = nullptr;
+    if (args.mask.ptr != nullptr && q_idx < args.Sq)
+      mrow = args.mask.ptr + b * args.mask.sb + h * args.mask.sh + (long long)q_idx * args.mask.sq;
+    const int lim = args.causal ? min(args.Skv - 1, q_idx + off) : args.Skv - 1;
+    bool ok = true;
+    for (int j = 0; j < n; ++j) {
+      if (ok && !mbar_wait(&s_full[j & 1], (j >> 1) & 1)) {
+        atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int kv0 = j * BT + grp * 64;
+      const bool general = (kv0 + 64 > args.Skv) || (args.causal && (kv0 + 63 > q0 + off)) || (args.mask.ptr != nullptr);
+      const uint32_t a_s = tmem_base + (j & 1) * BT + lane_addr + grp * 64;
+      if (general) {
+        // masked tile: rewrite the scores in place with -inf where the key is not visible
+        const float mask_mul = LOG2E / args.scale_log2;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(a_s + c * 32, v);
+          tmem_ld_wait32(v);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kc = kv0 + c * 32 + i;
+            float x = __uint_as_float(v[i]);
+            if (mrow != nullptr && kc < args.Skv) x = fmaf(mrow[kc], mask_mul, x);
+            v[i] = __float_as_uint(kc <= lim ? x : -INFINITY);
+          }
+          tmem_st_32x32(a_s + c * 32, v);
+        }
+        tmem_st_wait();
+      }
+      const float2 sc2 = make_float2(args.scale_log2, args.scale_log2), nl2 = make_float2(nlse2, nlse2);
+      float2 p[32];
+      uint32_t va[32], vb[32];
+      tmem_ld_32x32(a_s, va);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t (&v)[32] = c ? vb : va;
+        tmem_ld_wait32(v);
+        if (c == 0) tmem_ld_32x32(a_s + 32, vb);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float2 x = __ffma2_rn(f2(v[2 * i], v[2 * i + 1]), sc2, nl2);
+          p[c * 16 + i] = make_float2(ex2(x.x), ex2(x.y));
+        }
+      }
+      if (!mbar_wait(dp_full, j & 1)) {
+        atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const float2 nd2 = make_float2(ndelta, ndelta);
+      tmem_ld_32x32(a_dp, va);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t (&v)[32] = c ? vb : va;
+        tmem_ld_wait32(v);
+        if (c == 0) tmem_ld_32x32(a_dp + 32, vb);
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          // dS / scale = P * (dP - delta); the scale is applied once, to dQ, in the epilogue
+          const float2 d = __fmul2_rn(p[c * 16 + i], __fadd2_rn(f2(v[2 * i], v[2 * i + 1]), nd2));
+          pk[i] = pack_bf16(d.x, d.y);
+        }
+        tmem_st_32x16(a_dp + c * 16, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(ds_full);
+    }
+    if (ok && n > 0) {
+      if (!mbar_wait(dq_done, 0)) {
+        atomicExch(args.status, NB_ERR_TIMEOUT_EPILOGUE);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) tc_fence_after();
+    }
+    if (ok) {
+      // each group stores half of the head dim of its query row
+      constexpr int HALF = HD / 2;
+      __nv_bfloat16* dst = args.dQ + (long long)b * args.dq_sb + (long long)h * args.dq_sh + (long long)q_idx * args.dq_ss +
+                           grp * HALF;
+#pragma unroll
+      for (int c = 0; c < HALF / 32; ++c) {
+        uint32_t v[32];
+        if (n > 0) {
+          tmem_ld_32x32(t_dq + lane_addr + grp * HALF + c * 32, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0;
+        }
+        if (q_idx < args.Sq) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 pk;
+            uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              pw[e] = pack_bf16(__uint_as_float(v[u * 8 + 2 * e]) * args.scale, __uint_as_float(v[u * 8 + 2 * e + 1]) * args.scale);
+            *reinterpret_cast<uint4*>(dst + c * 32 + u * 8) = pk;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ndelta[b][h][q] = -sum_d dO * O and nlse2 = -lse * log2(e), both padded to Sq_pad rows per
+// (b, h): padding rows and rows whose lse is -inf (no visible key) get nlse2 = -inf (probability 0)
+// and ndelta = 0. D / 8 lanes per row, 16-byte loads.
+__global__ void __launch_bounds__(256) attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ dO,
+                                                           const __nv_bfloat16* __restrict__ O,
+                                                           const float* __restrict__ lse, float* __restrict__ ndelta,
+                                                           float* __restrict__ nlse2, int B, int H, int Sq, int Sq_pad, int D,
+                                                           long long do_sb, long long do_sh, long long do_ss,
+                                                           long long o_sb, long long o_sh, long long o_ss) {
+  const int lpr = D / 8;                                  // lanes per row: 16 (D = 128) or 8 (D = 64)
+  const int rows_per_block = 256 / lpr;
+  const long long row = (long long)blockIdx.x * rows_per_block + threadIdx.x / lpr;
+  const int sub = threadIdx.x % lpr;
+  const bool in_range = row < (long long)B * H * Sq_pad;
+  const int q = in_range ? (int)(row % Sq_pad) : 0;
+  const long long bh = in_range ? row / Sq_pad : 0;
+  const int h = bh % H;
+  const int b = bh / H;
   float acc = 0.f;
-  for (int d = lane * 4; d < D; d += 128) {
-    const uint2 ra = *reinterpret_cast<const uint2*>(a + d);
-    const uint2 rc = *reinterpret_cast<const uint2*>(c + d);
+  if (in_range && q < Sq) {
+    const uint4 ra = *reinterpret_cast<const uint4*>(dO + b * do_sb + h * do_sh + q * do_ss + sub * 8);
+    const uint4 rc = *reinterpret_cast<const uint4*>(O + b * o_sb + h * o_sh + q * o_ss + sub * 8);
     const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ra);
     const __nv_bfloat162* pc = reinterpret_cast<const __nv_bfloat162*>(&rc);
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
+    for (int e = 0; e < 4; ++e) {
       const float2 x = __bfloat1622float2(pa[e]), y = __bfloat1622float2(pc[e]);
       acc += x.x * y.x + x.y * y.y;
     }
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) delta[row] = acc;
-}
-
-// dq[b][h][q][d] (bf16, strided) = dq_acc[b][h][d][q] (fp32): 32 x 32 transposing tiles
-__global__ void __launch_bounds__(256) attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
-                                                             int H, int Sq, int Sq_pad, int D, long long sb, long long sh,
-                                                             long long ss) {
-  __shared__ float tile[32][33];
-  const int bh = blockIdx.z;
-  const int b = bh / H, h = bh % H;
-  const int q0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
-  for (int i = ty; i < 32; i += 8) {
-    const int d = d0 + i, q = q0 + tx;
-    tile[i][tx] = (d < D && q < Sq) ? acc[((long long)bh * D + d) * Sq_pad + q] : 0.f;
-  }
-  __syncthreads();
-  for (int i = ty; i < 32; i += 8) {
-    const int q = q0 + i, d = d0 + tx;
-    if (q < Sq && d < D) dq[b * sb + h * sh + q * ss + d] = __float2bfloat16(tile[tx][i]);
+  for (int o = lpr / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (in_range && sub == 0) {
+    if (q < Sq) {
+      const float l = lse[bh * Sq + q];
+      ndelta[row] = -acc;
+      nlse2[row] = (l == -INFINITY) ? -INFINITY : -l * LOG2E;
+    } else {
+      ndelta[row] = 0.f;
+      nlse2[row] = -INFINITY;
+    }
   }
 }
 
@@ -793,19 +1114,24 @@ static EncodeTiledFn get_encode_fn() {
   }
   return fn;
 }
-// (B, H, S, D) bf16 view with D contiguous; element strides sb, sh, ss. Box = 64 x rows x 1 x 1.
+// (B, H, S, D) bf16 view with D contiguous; element strides sb, sh, ss. Box = 64 x 128 rows x 1 x 1.
 static int make_map4(CUtensorMap* map, const void* ptr, int B, int H, int S, int D, long long sb, long long sh,
-                     long long ss, int box_rows) {
+                     long long ss) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return -1;
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
   cuuint64_t strides[3] = {(cuuint64_t)ss * 2, (cuuint64_t)(H > 1 ? sh : ss * S) * 2, (cuuint64_t)(B > 1 ? sb : sh * H) * 2};
-  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t box[4] = {64, (cuuint32_t)BT, 1, 1};
   cuuint32_t es[4] = {1, 1, 1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, es,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -(int)r - 100;
+}
+
+template <typename K>
+static int set_smem(K kernel, int bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess ? 0 : -2;
 }
 
 template <int HD>
@@ -814,14 +1140,29 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   using L = FwdSmem<HD>;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
-      return -2;
+    if (set_smem(attn_fwd_kernel<HD>, L::TOTAL)) return -2;
     configured = true;
   }
-  const int nqt = (a.Sq + BM - 1) / BM;
+  const int nqt = (a.Sq + 2 * BT - 1) / (2 * BT);
   const long long grid = (long long)nqt * a.H * a.B;
   if (grid <= 0) return 0;
   attn_fwd_kernel<HD><<<(unsigned)grid, NTHREADS, L::TOTAL, stream>>>(tq, tk, tv, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+template <int HD>
+static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                      const BwdArgs& a, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    if (set_smem(attn_bwd_dkdv_kernel<HD>, DkvSmem<HD>::TOTAL)) return -2;
+    if (set_smem(attn_bwd_dq_kernel<HD>, DqSmem<HD>::TOTAL)) return -2;
+    configured = true;
+  }
+  const long long bh = (long long)a.H * a.B;
+  const int nkt = (a.Skv + BT - 1) / BT, nqt = (a.Sq + BT - 1) / BT;
+  attn_bwd_dkdv_kernel<HD><<<(unsigned)(nkt * bh), NTHREADS, DkvSmem<HD>::TOTAL, stream>>>(tq, tk, tv, tdo, a);
+  attn_bwd_dq_kernel<HD><<<(unsigned)(nqt * bh), NTHREADS, DqSmem<HD>::TOTAL, stream>>>(tq, tk, tv, tdo, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -829,13 +1170,16 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 
 // q, k, v: bf16 (B, H, S, D) views, D contiguous, strides in elements (multiples of 8, 16-byte
 // aligned bases). o: bf16 with its own strides. lse: fp32 [B][H][Sq]. D in {64, 128}.
+// mask: optional fp32 additive mask (null = none), element strides m_sb, m_sh, m_sq (0 = broadcast),
+// key stride 1.
 extern "C" int nb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H, int Sq,
                            int Skv, int D, long long q_sb, long long q_sh, long long q_ss, long long k_sb,
                            long long k_sh, long long k_ss, long long v_sb, long long v_sh, long long v_ss,
-                           long long o_sb, long long o_sh, long long o_ss, float scale, int causal, int* status,
-                           void* stream) {
+                           long long o_sb, long long o_sh, long long o_ss, float scale, int causal, const float* mask,
+                           long long m_sb, long long m_sh, long long m_sq, int* status, void* stream) {
   using namespace nba;
   if (D != 64 && D != 128) return -10;
+  if (!(scale > 0.f)) return -13;
   if (B <= 0 || H <= 0 || Sq <= 0) return 0;
   const long long strides[] = {q_sb, q_sh, q_ss, k_sb, k_sh, k_ss, v_sb, v_sh, v_ss, o_ss, o_sh, o_sb};
   for (long long s : strides)
@@ -845,70 +1189,71 @@ extern "C" int nb_attn_fwd(const void* q, const void* k, const void* v, void* o,
     return -11;
   CUtensorMap tq, tk, tv;
   int r;
-  if ((r = make_map4(&tq, q, B, H, Sq, D, q_sb, q_sh, q_ss, BM))) return r;
-  if ((r = make_map4(&tk, k, B, H, Skv, D, k_sb, k_sh, k_ss, BN))) return r;
-  if ((r = make_map4(&tv, v, B, H, Skv, D, v_sb, v_sh, v_ss, BN))) return r;
+  if ((r = make_map4(&tq, q, B, H, Sq, D, q_sb, q_sh, q_ss))) return r;
+  if ((r = make_map4(&tk, k, B, H, Skv, D, k_sb, k_sh, k_ss))) return r;
+  if ((r = make_map4(&tv, v, B, H, Skv, D, v_sb, v_sh, v_ss))) return r;
   FwdArgs a;
   a.B = B; a.H = H; a.Sq = Sq; a.Skv = Skv;
-  a.scale_log2 = scale * 1.4426950408889634f;
+  a.scale_log2 = scale * LOG2E;
   a.causal = causal;
   a.O = reinterpret_cast<__nv_bfloat16*>(o);
   a.o_sb = o_sb; a.o_sh = o_sh; a.o_ss = o_ss;
   a.lse = lse;
+  a.mask = MaskArg{mask, m_sb, m_sh, m_sq};
   a.status = status;
+  a.dbg = getenv("NB_ATTN_DBG") ? atoi(getenv("NB_ATTN_DBG")) : 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return D == 128 ? launch_fwd<128>(tq, tk, tv, a, s) : launch_fwd<64>(tq, tk, tv, a, s);
 }
 
-// Backward. All tensors are (B, H, S, 128) bf16 views with the head dim contiguous (element strides
-// given per tensor); lse fp32 [B][H][Sq] from the forward; dq_acc: zeroed fp32 scratch of
-// B*H*128*Sq_pad elements (Sq_pad = Sq rounded up to 64); delta: fp32 scratch [B][H][Sq].
+// Backward. All tensors are (B, H, S, D) bf16 views with the head dim contiguous (element strides
+// given per tensor), D in {64, 128}; lse fp32 [B][H][Sq] from the forward. `stats`: fp32 scratch of
+// 2 * B * H * Sq_pad elements (Sq_pad = Sq rounded up to 128), filled here (delta, then lse2).
 extern "C" int nb_attn_bwd(const void* dO, const void* q, const void* k, const void* v, const void* o, const float* lse,
-                           void* dq, void* dk, void* dv, float* dq_acc, int B, int H, int Sq, int Skv, int D,
+                           void* dq, void* dk, void* dv, float* stats, int B, int H, int Sq, int Skv, int D,
                            long long q_sb, long long q_sh, long long q_ss, long long k_sb, long long k_sh, long long k_ss,
                            long long v_sb, long long v_sh, long long v_ss, long long do_sb, long long do_sh,
                            long long do_ss, long long o_sb, long long o_sh, long long o_ss, long long dq_sb,
                            long long dq_sh, long long dq_ss, long long dk_sb, long long dk_sh, long long dk_ss,
-                           long long dv_sb, long long dv_sh, long long dv_ss, float scale, int causal, float* delta,
-                           int* status, void* stream) {
+                           long long dv_sb, long long dv_sh, long long dv_ss, float scale, int causal, const float* mask,
+                           long long m_sb, long long m_sh, long long m_sq, int* status, void* stream) {
   using namespace nba;
-  if (D != 128) return -10;
+  if (D != 64 && D != 128) return -10;
+  if (!(scale > 0.f)) return -13;
   if (B <= 0 || H <= 0 || Sq <= 0 || Skv <= 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const long long st[] = {q_sb, q_sh, q_ss, k_sb, k_sh, k_ss, v_sb, v_sh, v_ss, do_sb, do_sh, do_ss,
                           o_sb, o_sh, o_ss, dq_sb, dq_sh, dq_ss, dk_sb, dk_sh, dk_ss, dv_sb, dv_sh, dv_ss};
   for (long long x : st)
     if (x & 7) return -12;
-  const int Sq_pad = (Sq + BQ - 1) / BQ * BQ;
-  const long long rows = (long long)B * H * Sq;
-  attn_delta_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(
-      reinterpret_cast<const __nv_bfloat16*>(dO), reinterpret_cast<const __nv_bfloat16*>(o), delta, B, H, Sq, D, do_sb,
-      do_sh, do_ss, o_sb, o_sh, o_ss);
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(dO) | reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) |
+       reinterpret_cast<uintptr_t>(dv) | reinterpret_cast<uintptr_t>(stats) | reinterpret_cast<uintptr_t>(o)) & 15)
+    return -11;
+  const int Sq_pad = (Sq + BT - 1) / BT * BT;
+  const long long rows = (long long)B * H * Sq_pad;
+  float* ndelta = stats;
+  float* nlse2 = stats + rows;
+  const int rpb = 256 / (D / 8);
+  attn_bwd_prep_kernel<<<(unsigned)((rows + rpb - 1) / rpb), 256, 0, s>>>(
+      reinterpret_cast<const __nv_bfloat16*>(dO), reinterpret_cast<const __nv_bfloat16*>(o), lse, ndelta, nlse2, B, H, Sq,
+      Sq_pad, D, do_sb, do_sh, do_ss, o_sb, o_sh, o_ss);
   CUtensorMap tq, tk, tv, tdo;
   int r;
-  if ((r = make_map4(&tq, q, B, H, Sq, D, q_sb, q_sh, q_ss, BQ))) return r;
-  if ((r = make_map4(&tdo, dO, B, H, Sq, D, do_sb, do_sh, do_ss, BQ))) return r;
-  if ((r = make_map4(&tk, k, B, H, Skv, D, k_sb, k_sh, k_ss, BN))) return r;
-  if ((r = make_map4(&tv, v, B, H, Skv, D, v_sb, v_sh, v_ss, BN))) return r;
+  if ((r = make_map4(&tq, q, B, H, Sq, D, q_sb, q_sh, q_ss))) return r;
+  if ((r = make_map4(&tdo, dO, B, H, Sq, D, do_sb, do_sh, do_ss))) return r;
+  if ((r = make_map4(&tk, k, B, H, Skv, D, k_sb, k_sh, k_ss))) return r;
+  if ((r = make_map4(&tv, v, B, H, Skv, D, v_sb, v_sh, v_ss))) return r;
   BwdArgs a;
   a.B = B; a.H = H; a.Sq = Sq; a.Skv = Skv; a.Sq_pad = Sq_pad;
-  a.scale = scale; a.scale_log2 = scale * 1.4426950408889634f;
+  a.scale = scale; a.scale_log2 = scale * LOG2E;
   a.causal = causal;
-  a.lse = lse; a.delta = delta; a.dq_acc = dq_acc;
+  a.nlse2 = nlse2; a.ndelta = ndelta;
+  a.dQ = reinterpret_cast<__nv_bfloat16*>(dq);
   a.dK = reinterpret_cast<__nv_bfloat16*>(dk); a.dV = reinterpret_cast<__nv_bfloat16*>(dv);
+  a.dq_sb = dq_sb; a.dq_sh = dq_sh; a.dq_ss = dq_ss;
   a.dk_sb = dk_sb; a.dk_sh = dk_sh; a.dk_ss = dk_ss; a.dv_sb = dv_sb; a.dv_sh = dv_sh; a.dv_ss = dv_ss;
+  a.mask = MaskArg{mask, m_sb, m_sh, m_sq};
   a.status = status;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL) != cudaSuccess)
-      return -2;
-    configured = true;
-  }
-  const int nkt = (Skv + BN - 1) / BN;
-  attn_bwd_kernel<<<(unsigned)((long long)nkt * H * B), BWD_THREADS, BwdSmem::TOTAL, s>>>(tq, tk, tv, tdo, a);
-  dim3 grid((Sq + 31) / 32, (D + 31) / 32, B * H);
-  attn_dq_convert_kernel<<<grid, 256, 0, s>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), H, Sq, Sq_pad, D, dq_sb, dq_sh,
-                                              dq_ss);
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  return D == 128 ? launch_bwd<128>(tq, tk, tv, tdo, a, s) : launch_bwd<64>(tq, tk, tv, tdo, a, s);
 }
-

@@ -355,8 +355,8 @@ class SDPAOp(_Fused):
         if q.device.type != "meta" and _native(q):
             from ..native import attention
 
-            if attention.supported(q, k, v, mask, dropout_p):
-                return attention.sdpa_fwd(q, k, v, causal=causal, scale=sc)
+            if attention.supported(q, k, v, mask, dropout_p) and sc > 0:
+                return attention.sdpa_fwd(q, k, v, causal=causal, scale=sc, mask=mask)
         if q.is_cuda and q.dtype == torch.bfloat16 and mask is None and q.dim() == 4 and q.shape[-2] == k.shape[-2]:
             # library stand-in (torch flash attention) used only while the hand-written kernel
             # does not cover a shape; it is not counted as a native launch
@@ -414,8 +414,8 @@ class SDPABwdOp(Operation):
         if q.device.type != "meta" and _native(q):
             from ..native import attention
 
-            if attention.supported(q, k, v, mask, 0.0) and attention.bwd_available() and q.shape[-1] == 128:
-                return attention.sdpa_bwd(do, q, k, v, o, lse, causal=causal, scale=sc)
+            if attention.supported(q, k, v, mask, 0.0) and attention.bwd_available() and sc > 0:
+                return attention.sdpa_bwd(do, q, k, v, o, lse, causal=causal, scale=sc, mask=mask)
         if q.is_cuda and q.dtype == torch.bfloat16 and mask is None and q.dim() == 4 and q.shape[-2] == k.shape[-2]:
             with torch.enable_grad():
                 qr, kr, vr = (t.detach().requires_grad_(True) for t in (q, k, v))
@@ -516,7 +516,7 @@ class PackedSelfAttentionBwdOp(Operation):
         if _native(qkv):
             from ..native import attention
 
-            if attention.supported(q, k, v, None, 0.0) and attention.bwd_available() and head_dim == 128:
+            if attention.supported(q, k, v, None, 0.0) and attention.bwd_available():
                 attention.sdpa_bwd(do4, q, k, v, o4, lse, causal=causal, scale=sc,
                                    out=tuple(d5[:, :, :, i, :].permute(0, 2, 1, 3) for i in range(3)))
                 return dqkv

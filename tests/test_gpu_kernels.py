@@ -231,8 +231,10 @@ def test_smoke_entry_and_cuda_graph_compile():
 
 
 @pytest.mark.parametrize("B,H,S,D,causal", [(1, 1, 128, 128, False), (1, 2, 256, 128, True), (2, 2, 200, 128, True),
-                                            (2, 3, 384, 64, True), (1, 2, 333, 64, False)])
+                                            (2, 3, 384, 64, True), (1, 2, 333, 64, False), (1, 2, 520, 128, True),
+                                            (1, 2, 2048, 128, True), (1, 1, 1024, 64, False)])
 def test_flash_attention_forward(B, H, S, D, causal):
+    from nabla_b200 import native
     from nabla_b200.native import attention as A
 
     torch.manual_seed(6)
@@ -240,6 +242,7 @@ def test_flash_attention_forward(B, H, S, D, causal):
     k, v = torch.randn_like(q), torch.randn_like(q)
     assert A.supported(q, k, v, None, 0.0)
     o, lse = A.sdpa_fwd(q, k, v, causal=causal, scale=D ** -0.5)
+    native.check_status()
     ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float(), is_causal=causal)
     s = (q.float() @ k.float().transpose(-1, -2)) * D ** -0.5
     if causal:
@@ -248,20 +251,75 @@ def test_flash_attention_forward(B, H, S, D, causal):
     assert (lse - torch.logsumexp(s, -1)).abs().max().item() < 1e-2
 
 
-@pytest.mark.parametrize("B,H,S,causal", [(1, 1, 128, False), (1, 2, 256, True), (2, 2, 200, True), (1, 2, 320, False)])
-def test_flash_attention_backward_and_packed(B, H, S, causal):
+def test_flash_attention_cross_lengths():
+    """seq_q != seq_kv, causal aligned to the last key (row i sees keys <= i + Skv - Sq)."""
+    from nabla_b200.native import attention as A
+
+    torch.manual_seed(8)
+    B, H, Sq, Skv, D = 1, 2, 130, 300, 128
+    q = torch.randn(B, H, Sq, D, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(B, H, Skv, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn_like(k)
+    for causal in (False, True):
+        o, _ = A.sdpa_fwd(q, k, v, causal=causal, scale=D ** -0.5)
+        s = (q.float() @ k.float().transpose(-1, -2)) * D ** -0.5
+        if causal:
+            s = s.masked_fill(~torch.ones(Sq, Skv, dtype=torch.bool, device="cuda").tril(Skv - Sq), float("-inf"))
+        ref = torch.softmax(s, -1) @ v.float()
+        assert (o.float() - ref).abs().max().item() < 3e-2
+
+
+@pytest.mark.parametrize("B,H,S,D,causal", [(1, 1, 128, 128, False), (1, 2, 256, 128, True), (2, 2, 200, 128, True),
+                                            (1, 2, 320, 128, False), (1, 2, 2048, 128, True), (2, 2, 200, 64, True),
+                                            (1, 3, 384, 64, False), (1, 1, 1100, 128, True)])
+def test_flash_attention_backward_and_packed(B, H, S, D, causal):
+    from nabla_b200 import native
     from nabla_b200.native import attention as A
 
     torch.manual_seed(7)
-    D = 128
     qkv = torch.randn(B, S, H * 3 * D, device="cuda", dtype=torch.bfloat16)
     v5 = qkv.view(B, S, H, 3, D)
     q, k, v = (v5[:, :, :, i, :].permute(0, 2, 1, 3) for i in range(3))      # strided views, no copies
     do = torch.randn(B, H, S, D, device="cuda", dtype=torch.bfloat16)
     o, lse = A.sdpa_fwd(q, k, v, causal=causal, scale=D ** -0.5)
     dq, dk, dv = A.sdpa_bwd(do, q, k, v, o, lse, causal=causal, scale=D ** -0.5)
+    native.check_status()
     qs = [t.float().requires_grad_(True) for t in (q, k, v)]
     torch.nn.functional.scaled_dot_product_attention(*qs, is_causal=causal).backward(do.float())
+    for a, b in zip((dq, dk, dv), qs):
+        assert _rel(a, b.grad) < 4e-2
+
+
+@pytest.mark.parametrize("kind", ["float_bh", "bool_rows", "float_2d_causal"])
+def test_flash_attention_additive_mask(kind):
+    """Forward and backward with an additive / boolean mask against the fp32 composition."""
+    from nabla_b200.native import attention as A
+
+    torch.manual_seed(9)
+    B, H, S, D = 2, 2, 200, 128
+    q = torch.randn(B, H, S, D, device="cuda", dtype=torch.bfloat16)
+    k, v = torch.randn_like(q), torch.randn_like(q)
+    do = torch.randn_like(q)
+    causal = kind == "float_2d_causal"
+    if kind == "float_bh":
+        mask = torch.randn(B, H, S, S, device="cuda")
+    elif kind == "bool_rows":
+        mask = torch.rand(B, 1, 1, S, device="cuda") > 0.3          # key padding mask
+        mask[..., 0] = True
+    else:
+        mask = torch.randn(S, S, device="cuda")
+    assert A.supported(q, k, v, mask, 0.0)
+    o, lse = A.sdpa_fwd(q, k, v, causal=causal, scale=D ** -0.5, mask=mask)
+    dq, dk, dv = A.sdpa_bwd(do, q, k, v, o, lse, causal=causal, scale=D ** -0.5, mask=mask)
+    qs = [t.float().requires_grad_(True) for t in (q, k, v)]
+    s = (qs[0] @ qs[1].transpose(-1, -2)) * D ** -0.5
+    add = torch.zeros_like(s).masked_fill(~mask, float("-inf")) if mask.dtype == torch.bool else mask
+    s = s + add
+    if causal:
+        s = s.masked_fill(~torch.ones(S, S, dtype=torch.bool, device="cuda").tril(), float("-inf"))
+    ref = torch.softmax(s, -1) @ qs[2]
+    ref.backward(do.float())
+    assert (o.float() - ref).abs().max().item() < 3e-2
     for a, b in zip((dq, dk, dv), qs):
         assert _rel(a, b.grad) < 4e-2
 
