@@ -30,7 +30,6 @@
 // A small kernel before the backward computes delta = rowsum(dO * O) and log2-domain row
 // statistics padded to whole tiles.
 #include "sm100_ptx.cuh"
-#include <stdlib.h>
 
 namespace nba {
 using namespace nb;
@@ -135,7 +134,6 @@ struct FwdArgs {
   float* lse;                   // [B][H][Sq]
   MaskArg mask;
   int* status;
-  int dbg;
 };
 
 template <int HD>
@@ -253,11 +251,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (lane == 0 && n_max > 0) {
       bool ok = true;
       auto qk = [&](int t, int j) {
-        if (!(args.dbg & 2)) mma_scores<HD>(tmem_base + t * BT, smem_u32(sQ + t * L::TILE_BYTES), smem_u32(sK + (j & 1) * L::TILE_BYTES));
+        mma_scores<HD>(tmem_base + t * BT, smem_u32(sQ + t * L::TILE_BYTES), smem_u32(sK + (j & 1) * L::TILE_BYTES));
         umma_commit(&s_full[t]);
       };
       auto pv = [&](int t, int j) {
-        if (!(args.dbg & 4)) mma_accum<HD>(tmem_base + 256 + t * HD, tmem_base + t * BT, false, smem_u32(sV + (j & 1) * L::TILE_BYTES), j != 0);
+        mma_accum<HD>(tmem_base + 256 + t * HD, tmem_base + t * BT, false, smem_u32(sV + (j & 1) * L::TILE_BYTES), j != 0);
         if (j == n_t[t] - 1) umma_commit(&o_done[t]);
       };
       for (int t = 0; t < 2 && ok; ++t)
@@ -310,7 +308,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      if (args.dbg & 1) { tc_fence_before(); mbar_arrive(&p_full[t]); continue; }
       const int kv0 = j * BT;
       const bool general = (kv0 + BT > args.Skv) || (args.causal && (kv0 + BT - 1 > q0 + t * BT + off)) ||
                            (args.mask.ptr != nullptr);
@@ -1201,7 +1198,6 @@ extern "C" int nb_attn_fwd(const void* q, const void* k, const void* v, void* o,
   a.lse = lse;
   a.mask = MaskArg{mask, m_sb, m_sh, m_sq};
   a.status = status;
-  a.dbg = getenv("NB_ATTN_DBG") ? atoi(getenv("NB_ATTN_DBG")) : 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return D == 128 ? launch_fwd<128>(tq, tk, tv, a, s) : launch_fwd<64>(tq, tk, tv, a, s);
 }
