@@ -23,6 +23,9 @@ _EAGER = ContextVar("nabla_eager_max_graph", default=_env("EAGER_MAX_GRAPH") or 
 _VERIFY = ContextVar("nabla_verify_eager_shapes",
                      default=_env("VERIFY_EAGER_SHAPES") or _env("NABLA_VERIFY_EAGER_SHAPES"))
 _TRACING = ContextVar("nabla_tracing", default=False)
+# set by compile(cuda_graph=True) while it traces: ops that would need a host decision at replay
+# (cond) pick a lowering that stays on the device
+_CAPTURABLE = ContextVar("nabla_capturable_trace", default=False)
 
 _FLAGS = {"EAGER_MAX_GRAPH": _EAGER, "VERIFY_EAGER_SHAPES": _VERIFY, "TRACING": _TRACING}
 
@@ -69,3 +72,11 @@ def verify_eager_shapes(v: bool = True):
 
 def tracing(v: bool = True):
     return _scoped(_TRACING, v)
+
+
+def capturable_trace(v: bool = True):
+    return _scoped(_CAPTURABLE, v)
+
+
+def is_capturable_trace() -> bool:
+    return _CAPTURABLE.get()

@@ -116,11 +116,13 @@ class ComputeGraph:
         self.epoch = 0
         self.seed = 0
         self.rng_counter = 0
+        self.seed_epoch = 0          # bumped by set_seed: device-resident stream states re-read (seed, counter)
 
     # ---- RNG: counter-based, carried by the engine across evaluations
     def set_seed(self, seed: int) -> None:
         self.seed = int(seed)
         self.rng_counter = 0
+        self.seed_epoch += 1
 
     def next_rng(self) -> tuple[int, int]:
         c = self.rng_counter

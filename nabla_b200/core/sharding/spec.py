@@ -336,6 +336,19 @@ def shard_index(spec: ShardingSpec, dim: int, device_id: int) -> tuple[int, int]
     return idx, total
 
 
+def shard_salt(spec: "ShardingSpec | None", device_id: int) -> int:
+    """Linear index of this device's shard over the SHARDED dimensions only: copies of a replicated
+    (or partially replicated) tensor get the same value on every device that holds the same piece,
+    so random ops draw identical numbers for identical pieces and replicas do not diverge."""
+    if spec is None:
+        return 0
+    idx = 0
+    for d in range(len(spec.dim_specs)):
+        i, total = shard_index(spec, d, device_id)
+        idx = idx * total + i
+    return idx
+
+
 def local_slice(global_len: int, idx: int, total: int) -> tuple[int, int]:
     """Ceil-div chunk ``idx`` of ``total``: (start, length); trailing chunks may be short/empty."""
     chunk = math.ceil(global_len / total) if total else global_len

@@ -628,12 +628,26 @@ struct Philox {
 };
 __device__ __forceinline__ float u01(uint32_t x) { return ((x >> 8) + 0.5f) * (1.0f / 16777216.0f); }
 
+// Random streams. With `state` (device memory: [0] seed, [1] number of draws made so far on this
+// device) the Philox key and offset come from there and `seed` is only a salt that tells the shards
+// of one tensor apart; the launcher advances state[1] with a one-thread kernel afterwards. Because
+// the kernel reads the state when it RUNS, a launch replayed from a CUDA graph draws fresh numbers
+// every time (reference: the seed threaded graph-in -> graph-out, nabla/core/graph/engine.py:80-88).
+__device__ __forceinline__ void rng_resolve(const unsigned long long* state, uint64_t& seed, uint64_t& offset) {
+  if (state != nullptr) {
+    seed = state[0] * 1000003ull + seed;
+    offset = state[1] << 32;
+  }
+}
+__global__ void rng_bump_kernel(unsigned long long* state) { state[1] += 1ull; }
+
 // mode 0: uniform in [a, b); mode 1: gaussian mean a std b
 template <typename T>
 __global__ void __launch_bounds__(256) rng_kernel(T* __restrict__ out, size_t n, uint64_t seed, uint64_t offset,
-                                                 int mode, float a, float b) {
+                                                 int mode, float a, float b, const unsigned long long* state) {
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t nthreads = (size_t)gridDim.x * blockDim.x;
+  rng_resolve(state, seed, offset);
   Philox ph(seed, tid, offset);
   for (size_t i = tid * 4; i < n; i += nthreads * 4) {
     const uint4 r = ph.next();
@@ -655,9 +669,10 @@ __global__ void __launch_bounds__(256) rng_kernel(T* __restrict__ out, size_t n,
 template <typename T>
 __global__ void __launch_bounds__(256) dropout_kernel(const T* __restrict__ x, T* __restrict__ y,
                                                      uint8_t* __restrict__ mask, size_t n, float p, uint64_t seed,
-                                                     uint64_t offset) {
+                                                     uint64_t offset, const unsigned long long* state) {
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t nthreads = (size_t)gridDim.x * blockDim.x;
+  rng_resolve(state, seed, offset);
   Philox ph(seed, tid, offset);
   const float keep_scale = 1.f / (1.f - p);
   for (size_t i = tid * 4; i < n; i += nthreads * 4) {
@@ -971,16 +986,39 @@ int nb_rng(void* out, long long n, unsigned long long seed, unsigned long long o
            int dtype, void* stream) {
   if (n <= 0) return 0;
   const int grid = grid_for((size_t)n, 256 * 4, 148 * 8);
-  if (dtype) rng_kernel<bf16><<<grid, 256, 0, STREAM>>>((bf16*)out, (size_t)n, seed, offset, mode, a, b);
-  else rng_kernel<float><<<grid, 256, 0, STREAM>>>((float*)out, (size_t)n, seed, offset, mode, a, b);
+  if (dtype) rng_kernel<bf16><<<grid, 256, 0, STREAM>>>((bf16*)out, (size_t)n, seed, offset, mode, a, b, nullptr);
+  else rng_kernel<float><<<grid, 256, 0, STREAM>>>((float*)out, (size_t)n, seed, offset, mode, a, b, nullptr);
   return CHECK_LAUNCH();
 }
 int nb_dropout(const void* x, void* y, unsigned char* mask, long long n, float p, unsigned long long seed,
                unsigned long long offset, int dtype, void* stream) {
   if (n <= 0) return 0;
   const int grid = grid_for((size_t)n, 256 * 4, 148 * 8);
-  if (dtype) dropout_kernel<bf16><<<grid, 256, 0, STREAM>>>((const bf16*)x, (bf16*)y, mask, (size_t)n, p, seed, offset);
-  else dropout_kernel<float><<<grid, 256, 0, STREAM>>>((const float*)x, (float*)y, mask, (size_t)n, p, seed, offset);
+  if (dtype) dropout_kernel<bf16><<<grid, 256, 0, STREAM>>>((const bf16*)x, (bf16*)y, mask, (size_t)n, p, seed, offset, nullptr);
+  else dropout_kernel<float><<<grid, 256, 0, STREAM>>>((const float*)x, (float*)y, mask, (size_t)n, p, seed, offset, nullptr);
+  return CHECK_LAUNCH();
+}
+// Variants whose stream position lives on the device: `state` = [seed, draws so far] (two 64-bit
+// words of device memory), `salt` distinguishes the shards of one tensor. The draw counter is
+// advanced here, after the kernel, by a one-thread launch on the same stream.
+int nb_rng_dev(void* out, long long n, unsigned long long* state, unsigned long long salt, int mode, float a, float b,
+               int dtype, void* stream) {
+  if (n > 0) {
+    const int grid = grid_for((size_t)n, 256 * 4, 148 * 8);
+    if (dtype) rng_kernel<bf16><<<grid, 256, 0, STREAM>>>((bf16*)out, (size_t)n, salt, 0, mode, a, b, state);
+    else rng_kernel<float><<<grid, 256, 0, STREAM>>>((float*)out, (size_t)n, salt, 0, mode, a, b, state);
+  }
+  rng_bump_kernel<<<1, 1, 0, STREAM>>>(state);
+  return CHECK_LAUNCH();
+}
+int nb_dropout_dev(const void* x, void* y, unsigned char* mask, long long n, float p, unsigned long long* state,
+                   unsigned long long salt, int dtype, void* stream) {
+  if (n > 0) {
+    const int grid = grid_for((size_t)n, 256 * 4, 148 * 8);
+    if (dtype) dropout_kernel<bf16><<<grid, 256, 0, STREAM>>>((const bf16*)x, (bf16*)y, mask, (size_t)n, p, salt, 0, state);
+    else dropout_kernel<float><<<grid, 256, 0, STREAM>>>((const float*)x, (float*)y, mask, (size_t)n, p, salt, 0, state);
+  }
+  rng_bump_kernel<<<1, 1, 0, STREAM>>>(state);
   return CHECK_LAUNCH();
 }
 

@@ -16,8 +16,10 @@
 // reduce_scatter.py:167-170, broadcast.py:56-80), and, unlike those, take the device group of
 // a mesh axis, so reductions along 'tp' of a ('dp','tp') mesh stay inside each tp group.
 //
-// Every wait is bounded (2 s): on expiry the kernel writes NB_ERR_TIMEOUT_PEER to the status
-// word and returns, so a lost peer surfaces as an error on the host instead of a hang.
+// Every wait is bounded (0.5 s, WAIT_LIMIT_NS): on expiry the kernel writes NB_ERR_TIMEOUT_PEER to
+// the status word and returns, so a lost peer surfaces as an error on the host instead of a hang.
+// While the status word is set every kernel of this file returns at its first barrier without
+// waiting, so the collectives queued behind a lost peer drain at once.
 #include "sm100_ptx.cuh"
 
 namespace nbc {
@@ -65,7 +67,8 @@ __device__ __forceinline__ bool wait_ge(const unsigned* p, unsigned target, int*
 // `phase` distinguishes several barriers inside one kernel (epoch * 4 + phase is the value).
 __device__ __forceinline__ bool block_barrier(const Group& g, int phase) {
   __syncthreads();
-  bool ok = true;
+  bool ok = *reinterpret_cast<const volatile int*>(g.status) == 0;   // an earlier wait on this device gave up
+  if (!__syncthreads_and(ok)) return false;
   const unsigned val = (g.epoch + *reinterpret_cast<const volatile unsigned*>(g.epoch_ctr)) * 4u + (unsigned)phase;
   if (threadIdx.x < g.world) {
     const int peer = threadIdx.x;
@@ -145,27 +148,51 @@ __device__ __forceinline__ void mc_st(void* p, const V4& v) {
 // algo 1: two-shot   rank r reduces chunk r in place, then everyone reads all chunks (large)
 // algo 2: multimem   rank r: ld_reduce chunk r through the switch, multimem.st it back to all
 // Result is written to `out` (ordinary memory, n elements).
+// Thread mapping of the chunked algorithms: element j of a chunk is always handled by the thread
+// with global index j mod nthreads, on every rank and in both phases. The per-block barrier pairs
+// block b of all ranks, so the thread that reads an element in phase 2 is covered by the barrier
+// its writer (same thread index on the owner rank) passed after phase 1, whatever the chunk size.
 template <typename T>
 __global__ void __launch_bounds__(512) allreduce_kernel(Group g, long long off, T* __restrict__ out, long long n,
                                                        int algo, int op) {
   constexpr int N = Acc<T>::N;
+  constexpr int U = 4;                                // 16-byte vectors in flight per thread and peer
   const long long nvec = n / N;                       // n is padded to a multiple of N * world by the host
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
   if (!block_barrier(g, 0)) return;
   const char* mine = reinterpret_cast<const char*>(g.bufs[g.rank]) + FLAG_BYTES + off;
   if (algo == 0) {
-    for (long long i = tid; i < nvec; i += nthreads) {
-      float acc[N];
-      Acc<T>::unpack(ld_peer(mine + i * 16), acc);
-      for (int p = 1; p < g.world; ++p) {
-        const int peer = (g.rank + p) % g.world;
-        float v[N];
-        Acc<T>::unpack(ld_peer(reinterpret_cast<const char*>(g.bufs[peer]) + FLAG_BYTES + off + i * 16), v);
+    for (long long i0 = tid; i0 < nvec; i0 += nthreads * U) {
+      float acc[U][N];
+      V4 r[U];
 #pragma unroll
-        for (int j = 0; j < N; ++j) acc[j] = combine(acc[j], v[j], op);
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * nthreads;
+        r[u] = i < nvec ? ld_peer(mine + i * 16) : V4{0u, 0u, 0u, 0u};
       }
-      reinterpret_cast<V4*>(out)[i] = Acc<T>::pack(acc);
+#pragma unroll
+      for (int u = 0; u < U; ++u) Acc<T>::unpack(r[u], acc[u]);
+      for (int p = 1; p < g.world; ++p) {
+        const char* src = reinterpret_cast<const char*>(g.bufs[(g.rank + p) % g.world]) + FLAG_BYTES + off;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * nthreads;
+          r[u] = i < nvec ? ld_peer(src + i * 16) : V4{0u, 0u, 0u, 0u};
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          float v[N];
+          Acc<T>::unpack(r[u], v);
+#pragma unroll
+          for (int j = 0; j < N; ++j) acc[u][j] = combine(acc[u][j], v[j], op);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * nthreads;
+        if (i < nvec) reinterpret_cast<V4*>(out)[i] = Acc<T>::pack(acc[u]);
+      }
     }
     block_barrier(g, 1);      // nobody may overwrite its buffer while peers still read it
     return;
@@ -173,35 +200,74 @@ __global__ void __launch_bounds__(512) allreduce_kernel(Group g, long long off, 
   const long long chunk = nvec / g.world;
   const long long c0 = chunk * g.rank;
   if (algo == 1) {
-    for (long long i = tid; i < chunk; i += nthreads) {
-      float acc[N];
-      Acc<T>::unpack(ld_peer(mine + (c0 + i) * 16), acc);
-      for (int p = 1; p < g.world; ++p) {
-        const int peer = (g.rank + p) % g.world;
-        float v[N];
-        Acc<T>::unpack(ld_peer(reinterpret_cast<const char*>(g.bufs[peer]) + FLAG_BYTES + off + (c0 + i) * 16), v);
+    // phase 1: reduce the own chunk in place
+    for (long long i0 = tid; i0 < chunk; i0 += nthreads * U) {
+      float acc[U][N];
 #pragma unroll
-        for (int j = 0; j < N; ++j) acc[j] = combine(acc[j], v[j], op);
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[u][j] = op == 0 ? 0.f : op == 1 ? -INFINITY : op == 2 ? INFINITY : 1.f;
+      for (int p = 0; p < g.world; ++p) {
+        const char* src = reinterpret_cast<const char*>(g.bufs[(g.rank + p) % g.world]) + FLAG_BYTES + off + c0 * 16;
+        V4 r[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * nthreads;
+          r[u] = i < chunk ? ld_peer(src + i * 16) : V4{0u, 0u, 0u, 0u};
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          float v[N];
+          Acc<T>::unpack(r[u], v);
+#pragma unroll
+          for (int j = 0; j < N; ++j) acc[u][j] = combine(acc[u][j], v[j], op);
+        }
       }
-      *reinterpret_cast<V4*>(const_cast<char*>(mine) + (c0 + i) * 16) = Acc<T>::pack(acc);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * nthreads;
+        if (i < chunk) *reinterpret_cast<V4*>(const_cast<char*>(mine) + (c0 + i) * 16) = Acc<T>::pack(acc[u]);
+      }
     }
-    if (!block_barrier(g, 1)) return;
-    for (long long i = tid; i < nvec; i += nthreads) {
-      const int owner = (int)min((long long)(g.world - 1), i / chunk);
-      reinterpret_cast<V4*>(out)[i] =
-          ld_peer(reinterpret_cast<const char*>(g.bufs[owner]) + FLAG_BYTES + off + i * 16);
+  } else {
+    // multimem (sum only): the switch adds the ranks' copies of the own chunk and stores the sum back to all
+    char* mc = reinterpret_cast<char*>(g.mc) + FLAG_BYTES + off + c0 * 16;
+    for (long long i0 = tid; i0 < chunk; i0 += nthreads * U) {
+      V4 r[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * nthreads;
+        if (i < chunk) r[u] = mc_ld_reduce<T>(mc + i * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * nthreads;
+        if (i < chunk) mc_st(mc + i * 16, r[u]);
+      }
     }
-    block_barrier(g, 2);
-    return;
-  }
-  // multimem (sum only)
-  char* mc = reinterpret_cast<char*>(g.mc) + FLAG_BYTES + off;
-  for (long long i = tid; i < chunk; i += nthreads) {
-    const V4 v = mc_ld_reduce<T>(mc + (c0 + i) * 16);
-    mc_st(mc + (c0 + i) * 16, v);
   }
   if (!block_barrier(g, 1)) return;
-  for (long long i = tid; i < nvec; i += nthreads) reinterpret_cast<V4*>(out)[i] = ld_peer(mine + i * 16);
+  // phase 2: collect every owner's reduced chunk with the SAME (thread <-> element of a chunk) mapping.
+  // After the multimem store every rank holds all chunks in its own buffer; the two-shot variant
+  // reads each chunk from its owner.
+  for (int q = 0; q < g.world; ++q) {
+    const int owner = (g.rank + q) % g.world;
+    const char* src = (algo == 1 ? reinterpret_cast<const char*>(g.bufs[owner]) + FLAG_BYTES + off : mine) + owner * chunk * 16;
+    V4* dst = reinterpret_cast<V4*>(out) + owner * chunk;
+    for (long long i0 = tid; i0 < chunk; i0 += nthreads * U) {
+      V4 r[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * nthreads;
+        if (i < chunk) r[u] = ld_peer(src + i * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * nthreads;
+        if (i < chunk) dst[i] = r[u];
+      }
+    }
+  }
   block_barrier(g, 2);
 }
 

@@ -37,6 +37,8 @@ def _L():
             "nb_activation": [c_vp] * 3 + [c_ll, c_int, c_int, c_int, c_vp],
             "nb_rng": [c_vp, c_ll, c_ull, c_ull, c_int, c_f, c_f, c_int, c_vp],
             "nb_dropout": [c_vp] * 3 + [c_ll, c_f, c_ull, c_ull, c_int, c_vp],
+            "nb_rng_dev": [c_vp, c_ll, c_vp, c_ull, c_int, c_f, c_f, c_int, c_vp],
+            "nb_dropout_dev": [c_vp] * 3 + [c_ll, c_f, c_vp, c_ull, c_int, c_vp],
             "nb_nf4_dequant": [c_vp] * 3 + [c_ll, c_int, c_int, c_vp],
             "nb_pool2d_fwd": [c_vp, c_vp] + [c_int] * 14 + [c_vp],
             "nb_pool2d_bwd": [c_vp] * 3 + [c_int] * 14 + [c_vp],
@@ -239,6 +241,51 @@ def activation_bwd(z: torch.Tensor, dy: torch.Tensor, mode: str) -> torch.Tensor
 
 
 # ---------------------------------------------------------------- RNG
+_rng_states: dict = {}      # device -> (int64[2] tensor [seed, draws so far], host epoch it was written for)
+
+
+def rng_state(device) -> torch.Tensor:
+    """This device's random-stream position ``[seed, draws so far]`` in device memory. The kernels
+    read it when they run and a one-thread kernel advances it after each draw, so a CUDA-graph replay
+    continues the stream instead of repeating it. Re-written from the host after every ``seed()``
+    call (never during stream capture: run one uncaptured step first, which ``compile`` does)."""
+    from ..core.graph.engine import GRAPH
+
+    device = torch.device(device)
+    epoch = (GRAPH.seed, getattr(GRAPH, "seed_epoch", 0))
+    ent = _rng_states.get(device)
+    if ent is None or ent[1] != epoch:
+        if torch.cuda.is_current_stream_capturing():
+            if ent is None:
+                raise RuntimeError("random op inside CUDA-graph capture before the device stream state exists")
+            return ent[0]
+        t = ent[0] if ent is not None else torch.zeros(2, dtype=torch.int64, device=device)
+        t.copy_(torch.tensor([GRAPH.seed & (2 ** 63 - 1), GRAPH.rng_counter], dtype=torch.int64))
+        ent = (t, epoch)
+        _rng_states[device] = ent
+    return ent[0]
+
+
+def rng_dev(shape, dtype: torch.dtype, device, salt: int, mode: str, a: float, b: float) -> torch.Tensor:
+    """Uniform / gaussian tensor from this device's stream (``rng_state``), Philox in one kernel."""
+    out = torch.empty(shape, dtype=dtype, device=device)
+    st = rng_state(out.device)
+    _ok(_L().nb_rng_dev(ptr(out), out.numel(), ptr(st), salt & (2 ** 64 - 1), 0 if mode == "uniform" else 1,
+                        float(a), float(b), _dt(out), stream_ptr()), "rng")
+    return out
+
+
+def dropout_dev(x: torch.Tensor, p: float, salt: int):
+    """Dropout whose mask comes from this device's stream (``rng_state``): ``(y, keep mask uint8)``."""
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    mask = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    st = rng_state(x.device)
+    _ok(_L().nb_dropout_dev(ptr(x), ptr(y), ptr(mask), x.numel(), float(p), ptr(st), salt & (2 ** 64 - 1), _dt(x),
+                            stream_ptr()), "dropout")
+    return y, mask
+
+
 def rng(shape, dtype: torch.dtype, device, seed: int, offset: int, mode: str, a: float, b: float) -> torch.Tensor:
     out = torch.empty(shape, dtype=dtype, device=device)
     _ok(_L().nb_rng(ptr(out), out.numel(), seed & (2 ** 64 - 1), offset & (2 ** 64 - 1), 0 if mode == "uniform" else 1,

@@ -1,14 +1,27 @@
 """Control flow (reference: nabla/ops/control_flow.py:21-507): ``where`` (differentiable),
-``cond`` and ``while_loop`` (data-dependent, host-evaluated predicate, not differentiable, as
-in the reference), ``scan`` (Python-unrolled, differentiable through its body)."""
+``cond`` and ``while_loop`` (data-dependent, not differentiable, as in the reference), ``scan``
+(Python-unrolled, differentiable through its body).
+
+Outside ``compile`` the predicate of ``cond`` / ``while_loop`` is read on the host and the chosen
+code runs right away. While ``compile`` traces, both become ONE recorded node (``CondOp`` /
+``WhileOp``) that keeps the branch / body functions: every replay reads the predicate of that
+call's data and runs the matching branch (or as many iterations as that call's data asks for), so
+a compiled function stays data dependent (reference: ops.cond / ops.while_loop lowered into the
+graph, control_flow.py:302-307, 444-446). These nodes read a device value on the host, so a step
+that contains one is replayed without CUDA-graph capture; under ``compile(cuda_graph=True)``
+``cond`` instead evaluates both branches and selects with ``where``, which stays on the device."""
 from __future__ import annotations
 
+import weakref
 from typing import Any, Callable
 
 import torch
 
+from .. import config
 from ..core.common import pytree
+from ..core.graph.tracing import OpNode
 from ..core.tensor.api import Tensor, realize_all
+from ..core.tensor.impl import TensorImpl
 from .base import Operation, _align_batch_dims, ensure_tensor
 
 
@@ -60,33 +73,176 @@ def where(condition, x, y) -> Tensor:
     return _where(condition, x, y)
 
 
+def _closure_tensors(*fns: Callable) -> list[Tensor]:
+    """Tensors a function closes over (one level, through containers): they become inputs of the
+    recorded node so that the replay realises them first and keeps them alive until it has run."""
+    found: list[Tensor] = []
+    seen: set[int] = set()
+    for fn in fns:
+        cells = getattr(fn, "__closure__", None) or ()
+        for c in cells:
+            try:
+                v = c.cell_contents
+            except ValueError:
+                continue
+            for leaf in pytree.tree_leaves(v) if isinstance(v, (Tensor, dict, list, tuple)) else ():
+                if isinstance(leaf, Tensor) and id(leaf._impl) not in seen:
+                    seen.add(id(leaf._impl))
+                    found.append(leaf)
+    return found
+
+
+def _fresh(impl: TensorImpl) -> Tensor:
+    """A new realized Tensor over the buffers an impl holds right now."""
+    return Tensor(impl=TensorImpl(list(impl._buffers), shape=impl._shape, dtype=impl.dtype, device=impl.device,
+                                  sharding=impl.sharding, batch_dims=impl.batch_dims))
+
+
+def _host_bool(x) -> bool:
+    if isinstance(x, Tensor):
+        return bool(x.item())
+    if isinstance(x, TensorImpl):
+        return bool(x._buffers[0].reshape(-1)[0].item())
+    return bool(x)
+
+
+class _HostControlOp(Operation):
+    """Base of the recorded control-flow nodes. ``host_sync`` tells ``compile`` that the node reads
+    a device value on the host (no CUDA-graph capture of a schedule that contains it)."""
+
+    host_sync = True
+    partial_policy = "none"
+
+    def build(self, inputs: list[Tensor], templates: list[Tensor], kwargs: dict) -> list[Tensor]:
+        _, td = pytree.tree_flatten(tuple(inputs))
+        node = OpNode(self, [t._impl for t in inputs], td, kwargs, kwargs)
+        outs = []
+        for i, t in enumerate(templates):
+            im = t._impl
+            impl = TensorImpl(None, shape=im._shape, dtype=im.dtype, device=im.device, sharding=im.sharding,
+                              batch_dims=im.batch_dims, is_traced=False)
+            impl.output_refs = node
+            impl.output_index = i
+            node.out_refs.append(weakref.ref(impl))
+            outs.append(Tensor(impl=impl))
+        _, node.out_treedef = pytree.tree_flatten(list(outs))
+        return outs
+
+    @staticmethod
+    def _result_buffers(tree: Any, n_expected: int, what: str) -> list[list[torch.Tensor]]:
+        leaves = [l for l in pytree.tree_leaves(tree) if isinstance(l, Tensor)]
+        if len(leaves) != n_expected:
+            raise ValueError(f"{what}: produced {len(leaves)} tensors, the recorded structure has {n_expected}")
+        realize_all(*leaves)
+        return [list(l._impl._buffers) for l in leaves]
+
+
+class CondOp(_HostControlOp):
+    """inputs: [pred, *operand tensors, *closed-over tensors]; kwargs keep the two functions and the
+    operand tree. Replays read ``pred`` and run the matching branch eagerly."""
+
+    def execute(self, node):
+        kw = node.kwargs
+        ins = node.input_impls()
+        n_op = kw["n_operands"]
+        it = iter(_fresh(i) for i in ins[1:1 + n_op])
+        leaves = [next(it) if is_t else v for is_t, v in kw["operand_leaves"]]
+        operands = pytree.tree_unflatten(kw["operand_treedef"], leaves)
+        with config.tracing(False):
+            take = _host_bool(ins[0])
+            out = (kw["true_fn"] if take else kw["false_fn"])(*operands)
+            return self._result_buffers(out, len(node.out_refs), "cond branch")
+
+
+class WhileOp(_HostControlOp):
+    """inputs: [*loop-state tensors, *closed-over tensors]. Replays run ``cond_fn`` / ``body_fn``
+    eagerly until the condition computed from that call's data turns false."""
+
+    def execute(self, node):
+        kw = node.kwargs
+        ins = node.input_impls()
+        n_st = kw["n_state"]
+        it = iter(_fresh(i) for i in ins[:n_st])
+        state = tuple(pytree.tree_unflatten(kw["state_treedef"], [next(it) if is_t else v for is_t, v in kw["state_leaves"]]))
+        with config.tracing(False):
+            state = _while_eager(kw["cond_fn"], kw["body_fn"], state, kw.get("max_iters"))
+            return self._result_buffers(state, len(node.out_refs), "while_loop body")
+
+
+_cond_op, _while_op = CondOp(), WhileOp()
+
+
+def _same_structure(a_leaves: list, b_leaves: list, what: str) -> None:
+    if len(a_leaves) != len(b_leaves):
+        raise ValueError(f"{what}: the two sides return different numbers of values")
+    for x, y in zip(a_leaves, b_leaves):
+        if isinstance(x, Tensor) != isinstance(y, Tensor):
+            raise ValueError(f"{what}: a value is a tensor on one side only")
+        if isinstance(x, Tensor) and (tuple(x._impl._shape) != tuple(y._impl._shape) or x.dtype is not y.dtype):
+            raise ValueError(f"{what}: shapes / dtypes differ: {tuple(x.shape)} {x.dtype} vs {tuple(y.shape)} {y.dtype}")
+
+
 def cond(pred, true_fn: Callable, false_fn: Callable, *operands: Any):
-    """Run ``true_fn(*operands)`` or ``false_fn(*operands)`` depending on the scalar ``pred``.
+    """Run ``true_fn(*operands)`` or ``false_fn(*operands)`` depending on the scalar ``pred``; both
+    branches must produce the same structure of shapes and dtypes.
 
-    The predicate is read on the host (one device->host sync), then only the taken branch is
-    traced and executed; both branches must produce the same structure of shapes and dtypes.
-    """
-    if isinstance(pred, Tensor):
-        p = bool(pred.item())
-    else:
-        p = bool(pred)
-    return true_fn(*operands) if p else false_fn(*operands)
+    Eagerly the predicate is read on the host (one device->host sync) and only the taken branch
+    runs. Inside ``compile`` the choice is made again on every call (module docstring)."""
+    if not (isinstance(pred, Tensor) and config.get_flag("TRACING")):
+        return true_fn(*operands) if _host_bool(pred) else false_fn(*operands)
+    # both branches are traced lazily to learn (and check) the output structure
+    t_out = true_fn(*operands)
+    f_out = false_fn(*operands)
+    t_leaves, out_td = pytree.tree_flatten(t_out)
+    f_leaves, _ = pytree.tree_flatten(f_out)
+    _same_structure(t_leaves, f_leaves, "cond")
+    if config.is_capturable_trace():
+        # stays on the device: both branches are part of the graph, `where` selects per call
+        sel = [where(pred, a, b) if isinstance(a, Tensor) else a for a, b in zip(t_leaves, f_leaves)]
+        return pytree.tree_unflatten(out_td, sel)
+    op_leaves, op_td = pytree.tree_flatten(tuple(operands))
+    op_tensors = [l for l in op_leaves if isinstance(l, Tensor)]
+    extra = [t for t in _closure_tensors(true_fn, false_fn) if all(t._impl is not o._impl for o in op_tensors)]
+    templates = [l for l in t_leaves if isinstance(l, Tensor)]
+    kwargs = {"true_fn": true_fn, "false_fn": false_fn, "operand_treedef": op_td, "n_operands": len(op_tensors),
+              "operand_leaves": [(isinstance(l, Tensor), None if isinstance(l, Tensor) else l) for l in op_leaves]}
+    outs = iter(_cond_op.build([pred, *op_tensors, *extra], templates, kwargs))
+    return pytree.tree_unflatten(out_td, [next(outs) if isinstance(l, Tensor) else l for l in t_leaves])
 
 
-def while_loop(cond_fn: Callable, body_fn: Callable, init_val: Any):
-    """``while cond_fn(*state): state = body_fn(*state)`` with a host-evaluated condition.
-    ``init_val`` may be a single value or a tuple; the loop state is realized every iteration
-    so the lazy graph does not grow with the trip count."""
-    is_tuple = isinstance(init_val, (tuple, list))
-    state = tuple(init_val) if is_tuple else (init_val,)
-    while True:
-        c = cond_fn(*state)
-        c = bool(c.item()) if isinstance(c, Tensor) else bool(c)
-        if not c:
-            break
+def _while_eager(cond_fn: Callable, body_fn: Callable, state: tuple, max_iters: int | None = None) -> tuple:
+    n = 0
+    while _host_bool(cond_fn(*state)):
         new = body_fn(*state)
         state = tuple(new) if isinstance(new, (tuple, list)) else (new,)
         realize_all(*pytree.tensor_leaves(state))
+        n += 1
+        if max_iters is not None and n >= max_iters:
+            break
+    return state
+
+
+def while_loop(cond_fn: Callable, body_fn: Callable, init_val: Any):
+    """``while cond_fn(*state): state = body_fn(*state)``. ``init_val`` may be a single value or a
+    tuple; the loop state is realized every iteration so the lazy graph does not grow with the trip
+    count. Inside ``compile`` the whole loop is one recorded node whose trip count follows each
+    call's data (module docstring)."""
+    is_tuple = isinstance(init_val, (tuple, list))
+    state = tuple(init_val) if is_tuple else (init_val,)
+    st_leaves, st_td = pytree.tree_flatten(state)
+    st_tensors = [l for l in st_leaves if isinstance(l, Tensor)]
+    if config.get_flag("TRACING") and st_tensors:
+        # one lazy application of the body checks that the state keeps its structure
+        probe = body_fn(*state)
+        probe = tuple(probe) if isinstance(probe, (tuple, list)) else (probe,)
+        _same_structure(st_leaves, pytree.tree_flatten(probe)[0], "while_loop")
+        extra = [t for t in _closure_tensors(cond_fn, body_fn) if all(t._impl is not o._impl for o in st_tensors)]
+        kwargs = {"cond_fn": cond_fn, "body_fn": body_fn, "state_treedef": st_td, "n_state": len(st_tensors),
+                  "state_leaves": [(isinstance(l, Tensor), None if isinstance(l, Tensor) else l) for l in st_leaves]}
+        outs = iter(_while_op.build([*st_tensors, *extra], st_tensors, kwargs))
+        state = tuple(pytree.tree_unflatten(st_td, [next(outs) if isinstance(l, Tensor) else l for l in st_leaves]))
+    else:
+        state = _while_eager(cond_fn, body_fn, state)
     return (type(init_val)(state) if isinstance(init_val, list) else state) if is_tuple else state[0]
 
 

@@ -46,11 +46,11 @@ class _LocalShapeMixin:
         out_impl = node.outputs()[0]
         if out_impl is None or out_impl.sharding is None:
             return kwargs
-        from ..core.sharding.spec import compute_local_shape
+        from ..core.sharding.spec import compute_local_shape, shard_salt
 
         kw = dict(kwargs)
         kw["shape"] = compute_local_shape(out_impl._shape, out_impl.sharding, device_id)
-        kw["_shard"] = device_id
+        kw["_shard"] = shard_salt(out_impl.sharding, device_id)
         return kw
 
 
@@ -100,9 +100,27 @@ class _RandomOp(_LocalShapeMixin, CreationOperation):
         return _generator(device, seed, counter, shard)
 
 
+def _native_rng(d: torch.device, shape, dtype: DType, shard: int, mode: str, a: float, b: float):
+    """Philox kernel on this device's own stream (``native.kernels.rng_state``); None when the
+    device is not a GPU or the library is missing."""
+    if d.type != "cuda":
+        return None
+    from ..native import kernels
+
+    if not kernels.has("nb_rng_dev"):
+        return None
+    td = dtype.to_torch()
+    out = kernels.rng_dev(tuple(int(x) for x in shape), td if td in (torch.float32, torch.bfloat16) else torch.float32,
+                          d, shard, mode, a, b)
+    return out if out.dtype == td else out.to(td)
+
+
 class UniformOp(_RandomOp):
     def kernel(self, *, shape, low, high, dtype: DType, device, _shard: int = 0):
         d = _dev(device)
+        nat = _native_rng(d, shape, dtype, _shard, "uniform", low, high)
+        if nat is not None:
+            return nat
         g = self._gen(d, _shard)
         u = torch.rand(shape, dtype=torch.float32, device=d, generator=g)
         return (u * (high - low) + low).to(dtype.to_torch())
@@ -111,6 +129,9 @@ class UniformOp(_RandomOp):
 class GaussianOp(_RandomOp):
     def kernel(self, *, shape, mean, std, dtype: DType, device, _shard: int = 0):
         d = _dev(device)
+        nat = _native_rng(d, shape, dtype, _shard, "gaussian", mean, std)
+        if nat is not None:
+            return nat
         g = self._gen(d, _shard)
         n = torch.randn(shape, dtype=torch.float32, device=d, generator=g)
         return (n * std + mean).to(dtype.to_torch())

@@ -699,14 +699,18 @@ class DropoutOp(Operation):
         return super().execute(node)
 
     def shard_kwargs(self, kwargs, node, shard_idx, device_id):
-        return {**kwargs, "_shard": device_id}
+        from ..core.sharding.spec import shard_salt
+
+        return {**kwargs, "_shard": shard_salt(node.input_impls()[0].sharding, device_id)}
 
     def kernel(self, x, *, p: float, _shard: int = 0):
         seed, counter = getattr(self, "_rng", (0, 0))
         if x.device.type != "meta" and _native(x) and x.numel():
             from ..native import kernels
 
-            return kernels.dropout(x, p, seed * 1000003 + _shard, counter << 32)
+            # the stream position lives on the device and is advanced there, so a step replayed
+            # from a CUDA graph gets a new mask every time
+            return kernels.dropout_dev(x, p, _shard)
         if x.device.type == "meta":
             return torch.empty_like(x), torch.empty(x.shape, dtype=torch.uint8, device="meta")
         from .creation import _generator

@@ -35,9 +35,15 @@ def _native():
         return None
 
 
+def _local_only() -> bool:
+    from . import symm
+
+    return symm.local_only()
+
+
 def all_reduce(buf: torch.Tensor, mesh, axes: Sequence[str], op: str = "sum") -> torch.Tensor:
     pg, ranks = _group(mesh, axes)
-    if len(ranks) == 1:
+    if len(ranks) == 1 or _local_only():
         return buf
     nat = _native()
     if nat is not None and op == "sum" and nat.supports(buf):
@@ -58,6 +64,8 @@ def all_gather(buf: torch.Tensor, mesh, axes: Sequence[str], dim: int, sizes: Se
         return buf
     buf = buf.contiguous()
     even = sizes is None or len(set(sizes)) == 1
+    if _local_only():
+        return torch.cat([buf] * n, dim=dim)
     nat = _native()
     if nat is not None and even and dim == 0 and nat.supports(buf) and (buf.numel() * buf.element_size()) % 16 == 0 \
             and buf.numel() * buf.element_size() * n + 4096 <= nat.DEFAULT_BYTES - 65536:
@@ -92,6 +100,10 @@ def reduce_scatter(buf: torch.Tensor, mesh, axes: Sequence[str], dim: int) -> to
     if buf.shape[dim] % n != 0:
         return None
     x = buf.movedim(dim, 0).contiguous() if dim != 0 else buf.contiguous()
+    if _local_only():
+        c = x.shape[0] // n
+        out = x[ranks.index(dist.get_rank()) * c:][:c].clone()
+        return out.movedim(0, dim) if dim != 0 else out
     nat = _native()
     if nat is not None and nat.supports(x) and (x.numel() // n * x.element_size()) % 16 == 0:
         stats["native_calls"] += 1
@@ -107,6 +119,8 @@ def permute(buf: torch.Tensor, mesh, perm: Sequence[tuple[int, int]]) -> torch.T
     """Point-to-point shift: rank ``src`` sends its shard to ``dst`` for every pair; ranks
     nobody sends to receive zeros. Grouped NCCL send/recv."""
     me = mesh.rank
+    if _local_only():
+        return buf.clone()
     ops = []
     out = torch.zeros_like(buf)
     send_to = [d for s, d in perm if s == me]
@@ -129,6 +143,8 @@ def permute(buf: torch.Tensor, mesh, perm: Sequence[tuple[int, int]]) -> torch.T
 
 def broadcast(buf: torch.Tensor, mesh, root: int = 0) -> torch.Tensor:
     out = buf.clone()
+    if _local_only():
+        return out
     stats["nccl_calls"] += 1
     dist.broadcast(out, src=root)
     return out

@@ -179,6 +179,24 @@ def arena(mesh, axes) -> Arena | None:
     return ws.arena
 
 
+_local_only = False
+
+
+def set_local_only(flag: bool) -> None:
+    """Measurement switch: while on, every collective of this module and of ``parallel.backend``
+    becomes its communication-free local counterpart with the same shapes (all-reduce = identity,
+    all-gather = the own shard repeated, reduce-scatter = the own chunk of the local partial sum,
+    fused GEMM + collective = the plain GEMM). A step recorded in this mode does the same math on
+    the same tile shapes and moves no byte between GPUs, so ``step time - local-only step time`` is
+    the communication a step fails to hide. The numbers it computes are meaningless."""
+    global _local_only
+    _local_only = bool(flag)
+
+
+def local_only() -> bool:
+    return _local_only
+
+
 def is_ready() -> bool:
     global _enabled
     if _enabled is None:
@@ -230,9 +248,22 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+def _blocks_for(nbytes: int) -> int:
+    """Grid of the standalone collectives: sized to the bytes NVLink needs in flight (about 2 MB per
+    direction at 770 GB/s and a few microseconds of latency; one block keeps 32 KB in flight), not to
+    the SM count, and small for latency-bound messages."""
+    if nbytes <= 256 * 1024:
+        return 8
+    if nbytes <= 8 * 1024 * 1024:
+        return 32
+    return 64 if nbytes <= 64 * 1024 * 1024 else 128
+
+
 def all_reduce(buf: torch.Tensor, mesh, axes, op: str = "sum", algo: str | None = None) -> torch.Tensor:
     """Sum (or max/min/prod) over the device group of ``axes`` with peer-memory kernels."""
     global launch_count
+    if _local_only:
+        return buf
     ws = workspace(mesh, axes)
     x = buf.contiguous()
     n = x.numel()
@@ -257,7 +288,7 @@ def all_reduce(buf: torch.Tensor, mesh, axes, op: str = "sum", algo: str | None 
     if algo == "multimem" and (not ws.mc_ptr or opi != 0):
         algo = "twoshot" if opi == 0 else "oneshot"
     ai = {"oneshot": 0, "twoshot": 1, "multimem": 2}[algo]
-    blocks = 8 if nbytes <= 256 * 1024 else (32 if nbytes <= 8 * 1024 * 1024 else 64)
+    blocks = _blocks_for(nbytes)
     rc = _L().nb_comm_allreduce(ws.ptrs_dev, ws.mc_ptr, ws.rank, ws.world, ws.ctr.data_ptr(), 0, out.data_ptr(), n_pad,
                                 1 if x.dtype == torch.bfloat16 else 0, ai, opi, blocks, _status().data_ptr(), _stream())
     if rc != 0:
@@ -375,6 +406,10 @@ def gemm_all_reduce(a: torch.Tensor, b: torch.Tensor, mesh, axes) -> torch.Tenso
 
     Returns a VIEW of the workspace (M x N bf16): consume or copy it before the next collective
     on this group."""
+    if _local_only:
+        from ..native.gemm import gemm_bf16
+
+        return gemm_bf16(a.reshape(-1, a.shape[-1]), b)
     ws = _fused_state(workspace(mesh, axes), a.device)
     a3, b3, lda, ldb, a_mn, b_mn = _operands(a, b)
     M, K, N = a3.shape[1], a3.shape[2], b.shape[1]
@@ -392,6 +427,17 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_rows
     launch's closing barrier a local pass folds the ``world`` partial row blocks, the bias and
     the residual into the returned (M / world, N) tensor."""
     ws = _fused_state(workspace(mesh, axes), a.device)
+    if _local_only:
+        from ..native.gemm import gemm_bf16
+
+        y = gemm_bf16(a.reshape(-1, a.shape[-1]), b)
+        M, N = y.shape
+        y = y.view(M // (ws.world * chunk_rows), ws.world, chunk_rows, N)[:, ws.rank].reshape(M // ws.world, N)
+        if bias is not None:
+            y = y + bias.reshape(-1).to(y.dtype)
+        if residual is not None:
+            y = y + residual.reshape(M // ws.world, N)
+        return y
     a3, b3, lda, ldb, a_mn, b_mn = _operands(a, b)
     M, K, N = a3.shape[1], a3.shape[2], b.shape[1]
     out = torch.empty((M // ws.world, N), dtype=torch.bfloat16, device=a.device)
@@ -429,6 +475,25 @@ def all_gather_gemm(a_shard: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_ro
     x = a_shard.reshape(-1, a_shard.shape[-1]).contiguous()
     Ml, K = x.shape
     M, N = Ml * ws.world, b.shape[1]
+    if _local_only:
+        from ..native.gemm import gemm_bf16
+
+        if arena_off is not None:
+            a_full = ws.arena.buf[arena_off: arena_off + M * K * 2].view(torch.bfloat16).view(M, K)
+        else:
+            a_full = torch.empty((M, K), dtype=torch.bfloat16, device=x.device)
+        a_full.view(M // (ws.world * chunk_rows), ws.world, chunk_rows, K)[:] = x.view(-1, 1, chunk_rows, K)
+        if bias is not None and epilogue == "none":
+            epilogue = "bias"
+        if dact is not None:
+            z, act = dact
+            o = gemm_bf16(a_full, b, aux="drelu" if act == "relu" else "dgelu", aux_in=z.reshape(M, N),
+                          gelu_tanh=act == "gelu_tanh")
+            return a_full, o
+        if store_preact:
+            o, pre = gemm_bf16(a_full, b, bias=bias, epilogue=epilogue, aux="store_preact", gelu_tanh=gelu_tanh)
+            return a_full, o, pre
+        return a_full, gemm_bf16(a_full, b, bias=bias, epilogue=epilogue, gelu_tanh=gelu_tanh)
     b3, bkind, ldb, _ = _prep(b.unsqueeze(0))
     push = arena_off is not None
     if push:
@@ -485,6 +550,12 @@ def adamw_reduce(p: torch.Tensor, m: torch.Tensor, v: torch.Tensor, grad_off: in
     ws = _fused_state(workspace(mesh, axes), p.device)
     ar = ws.arena
     n = p.numel()
+    if _local_only:
+        from ..native import kernels
+
+        g = ar.buf[grad_off: grad_off + n * 2].view(torch.bfloat16).view(p.shape)
+        kernels.adamw(p, g, m, v, lr=lr, b1=b1, b2=b2, eps=eps, wd=wd, step=step or 1, inplace=True)
+        return
     bc1 = 1.0 - b1 ** step if step is not None else 1.0
     bc2 = 1.0 - b2 ** step if step is not None else 1.0
     blocks = int(max(1, min(256, (n // 8 + 255) // 256)))
@@ -501,10 +572,16 @@ def _gather_call(x: torch.Tensor, mesh, axes, mode: int, chunk_elems: int, out_e
     global launch_count
     ws = workspace(mesh, axes)
     flat = x.contiguous().view(-1)
+    if _local_only:
+        if mode == 0:                                     # all-gather: the own shard repeated
+            return flat.repeat(ws.world)
+        if mode == 1:                                     # reduce-scatter: own chunk of the local partial sum
+            return flat[ws.rank * chunk_elems:(ws.rank + 1) * chunk_elems].clone()
+        return flat.clone()
     ws.data[: flat.numel() * x.element_size()].view(x.dtype).copy_(flat)
     out = torch.empty(out_elems, dtype=x.dtype, device=x.device)
     nbytes = out_elems * x.element_size()
-    blocks = 8 if nbytes <= 256 * 1024 else (32 if nbytes <= 8 * 1024 * 1024 else 64)
+    blocks = _blocks_for(nbytes)
     rc = _L().nb_comm_gather(ws.ptrs_dev, ws.rank, ws.world, ws.ctr.data_ptr(), 0, out.data_ptr(), chunk_elems,
                              1 if x.dtype == torch.bfloat16 else 0, mode, root, blocks, _status().data_ptr(), _stream())
     if rc != 0:

@@ -16,12 +16,27 @@ input are copied out of the graph's memory; those that do are returned as they a
 
 Cache key = (pytree structure, per-tensor (shape, dtype, sharding signature), static values);
 dimensions named in ``dynamic_dims={arg_idx: {dim_idx: "name"}}`` enter the key as ``"$name"``
-so all sizes share one entry (each concrete size is specialised lazily inside that entry).
+so all sizes share one entry. The first call of such an entry traces the Python function twice,
+once on the real inputs and once, without executing anything, on placeholders whose named
+dimensions are doubled; every integer that differs between the two recordings (reshape targets,
+slice bounds, creation shapes...) is an affine function of the named sizes. A later call with
+new sizes does not run the Python function: the recorded node list is instantiated for the new
+sizes (shape-valued arguments evaluated from those functions, output shapes re-inferred node by
+node) and planned again (reference: one executable with SymbolicDim inputs,
+nabla/transforms/compile.py:276-301). ``stats.retraces`` counts real re-runs of the Python
+function, ``stats.respecialisations`` the instantiations.
+
+``cond`` / ``while_loop`` inside the function become recorded nodes that decide again on every
+replay (``ops/control_flow.py``); a schedule that contains one is replayed without CUDA-graph
+capture. Random ops read a stream position that lives on the device, so replays (captured or not)
+draw fresh numbers.
 """
 from __future__ import annotations
 
 import time
+import weakref
 from collections import OrderedDict
+from fractions import Fraction
 from dataclasses import dataclass, field
 from typing import Any, Callable
 
@@ -48,6 +63,7 @@ class CompilationStats:
     misses: int = 0
     fallbacks: int = 0
     retraces: int = 0
+    respecialisations: int = 0       # new sizes of a dynamic_dims entry served without re-running the function
     compile_time_s: float = 0.0
     replay_time_s: float = 0.0
     graph_nodes: int = 0
@@ -66,10 +82,16 @@ class CompilationStats:
                 f"nodes={self.graph_nodes}, steps={self.graph_steps})")
 
 
+class _NotAffine(Exception):
+    """A recorded integer does not follow an affine function of the named sizes."""
+
+
 class _Recorded:
     """One specialisation: placeholder impls, ordered nodes, fused steps, output recipe."""
 
     def __init__(self):
+        self.targets: list[TensorImpl] = []
+        self.keep_alive: list[TensorImpl] = []
         self.placeholders: list[TensorImpl] = []
         self.nodes: list[OpNode] = []
         self.keep: list[list[TensorImpl]] = []      # strong refs to every node's outputs
@@ -85,6 +107,8 @@ class _Recorded:
         self.out_cached: list | None = None         # Tensor objects of outputs that alias donated inputs
         self.static_inputs: list[list[torch.Tensor]] | None = None
         self.static_outputs: list[list[torch.Tensor]] | None = None
+        self.host_sync = False                      # holds a node that reads a device value on the host
+        self.sizes: dict[str, int] = {}             # value of every named dynamic dimension in this recording
 
 
 def _first_tensor(tree: Any):
@@ -152,12 +176,31 @@ class CompiledFunction:
     def clear_cache(self) -> None:
         self._cache.clear()
 
+    def release(self) -> None:
+        """Drop every recorded schedule together with its CUDA graphs and the buffers they own.
+        Call it (then synchronise) before tearing down a process group whose collectives were
+        captured, so that no graph outlives the communicator it launches into."""
+        for entry in self._cache.values():
+            for rec in entry.values():
+                if not isinstance(rec, _Recorded):
+                    continue
+                rec.cuda_graph = None
+                rec.static_inputs = rec.static_outputs = rec.out_cached = None
+                for ph in rec.placeholders:
+                    ph._buffers = None
+                for outs in rec.keep:
+                    for o in outs:
+                        o._buffers = None
+        self._cache.clear()
+
     def dump_plan(self, file=None) -> str:
         """Text listing of every recorded schedule: one line per step with its kind (``op`` or
         the name of a fused step), the op names it covers and the output shapes."""
         lines = []
         for entry in self._cache.values():
             for rec in entry.values():
+                if not isinstance(rec, _Recorded):
+                    continue
                 lines.append(f"plan: {len(rec.nodes)} nodes, {len(rec.steps)} steps, "
                              f"{sum(rec.donated)} donated inputs, cuda_graph={rec.cuda_graph is not None}")
                 for si, (kind, idxs) in enumerate(rec.steps):
@@ -240,15 +283,28 @@ class CompiledFunction:
             self._stats.hits += 1
         rec = entry.get(conc)
         if rec is None:
-            if entry:
-                self._stats.retraces += 1
             t0 = time.perf_counter()
+            sym = entry.get("__symbolic__")
+            if sym is not None and sym is not False:
+                # a new size of a dynamic_dims entry: instantiate the recorded node list, no Python re-run
+                try:
+                    rec, result = self._respecialise(sym, leaves)
+                    self._stats.respecialisations += 1
+                    entry[conc] = rec
+                    self._stats.compile_time_s += time.perf_counter() - t0
+                    return result
+                except _NotAffine:
+                    entry["__symbolic__"] = False
+            if any(isinstance(r, _Recorded) for r in entry.values()):
+                self._stats.retraces += 1
             try:
                 rec, result = self._trace(leaves, td)
             except Exception:
                 self._stats.fallbacks += 1
                 raise
             entry[conc] = rec
+            if self.dynamic_dims and sym is None:
+                entry["__symbolic__"] = self._probe(rec, leaves, td)
             self._stats.compile_time_s += time.perf_counter() - t0
             return result
         t0 = time.perf_counter()
@@ -257,14 +313,37 @@ class CompiledFunction:
         return out
 
     # ---- trace
-    def _trace(self, leaves: list, td) -> tuple[_Recorded, Any]:
+    def _dyn_names(self, li: int, im: TensorImpl) -> dict[int, str]:
+        """{physical dim index: name} of the named dynamic dimensions of leaf ``li``."""
+        owner = getattr(self, "_last_owner", [])
+        ow = owner[li] if li < len(owner) else None
+        dyn = self.dynamic_dims.get(ow) if ow is not None else None
+        return {d + im.batch_dims: n for d, n in dyn.items()} if dyn else {}
+
+    def _record(self, leaves: list, td, scale: dict[str, int] | None = None) -> _Recorded:
+        """Run the Python function once on placeholders and keep the node list. With ``scale``
+        ({name: factor}) the placeholders are shape-only (meta buffers) and the named dimensions are
+        multiplied: nothing can execute, the recording only serves to see which integers move."""
         rec = _Recorded()
         ph_leaves = []
         owner = getattr(self, "_last_owner", [None] * len(leaves))
         for li, l in enumerate(leaves):
             if isinstance(l, Tensor):
                 im = l._impl
-                ph = TensorImpl(list(im._buffers), shape=im._shape, dtype=im.dtype, device=im.device,
+                shape = list(im._shape)
+                names = self._dyn_names(li, im)
+                for d, name in names.items():
+                    rec.sizes[name] = int(shape[d]) * (scale.get(name, 1) if scale else 1)
+                    shape[d] = rec.sizes[name]
+                if scale is None:
+                    bufs = list(im._buffers)
+                else:
+                    from ..core.sharding.spec import compute_local_shape
+
+                    ids = im.sharding.mesh.local_ids if im.sharding is not None else [0]
+                    bufs = [torch.empty(compute_local_shape(shape, im.sharding, i) if im.sharding is not None else shape,
+                                        dtype=im.dtype.to_torch(), device="meta") for i in ids]
+                ph = TensorImpl(bufs, shape=tuple(shape), dtype=im.dtype, device=im.device,
                                 sharding=im.sharding, batch_dims=im.batch_dims, is_traced=False)
                 ph.requires_grad = im.requires_grad
                 ph.is_traced = im.requires_grad
@@ -279,7 +358,7 @@ class CompiledFunction:
             p_args.append(pytree.tree_unflatten(t_, ph_leaves[pos: pos + t_.num_leaves]))
             pos += t_.num_leaves
         p_kwargs = pytree.tree_unflatten(td_k, ph_leaves[pos:])
-        with config.tracing(True), config.eager_max_graph(False):
+        with config.tracing(True), config.eager_max_graph(False), config.capturable_trace(self.use_cuda_graph):
             result = self.fn(*p_args, **p_kwargs)
         out_leaves, out_td = pytree.tree_flatten(result)
         rec.out_treedef = out_td
@@ -293,9 +372,15 @@ class CompiledFunction:
             else:
                 rec.out_impls.append(None)
                 rec.out_static.append(o)
-        nodes = topo_nodes(targets, lambda impl: impl.is_realized)
-        rec.nodes = nodes
-        rec.keep = [[o for o in n.outputs() if o is not None] for n in nodes]
+        rec.nodes = topo_nodes(targets, lambda impl: impl.is_realized)
+        rec.keep = [[o for o in n.outputs() if o is not None] for n in rec.nodes]
+        rec.targets = targets
+        return rec
+
+    def _plan(self, rec: _Recorded) -> None:
+        """Fused schedule, liveness and in-place marking of a recorded node list."""
+        nodes, targets = rec.nodes, rec.targets
+        rec.host_sync = any(getattr(n.op, "host_sync", False) for n in nodes)
         plan = fusion.build_plan(nodes, targets) if fusion.enabled() else None
         rec.steps = plan.steps if plan is not None else [("op", (i,)) for i in range(len(nodes))]
         if any(rec.donated):
@@ -325,8 +410,130 @@ class CompiledFunction:
                 rec.free_after[si].append(produced[k])
         self._stats.graph_nodes = len(nodes)
         self._stats.graph_steps = len(rec.steps)
+
+    def _trace(self, leaves: list, td) -> tuple[_Recorded, Any]:
+        rec = self._record(leaves, td)
+        self._plan(rec)
         self._run(rec)
         return rec, self._collect(rec)
+
+    # ---- dynamic dimensions
+    def _probe(self, rec: _Recorded, leaves: list, td):
+        """Second, shape-only recording with every named dimension doubled (one recording per name).
+        Returns the symbolic description used by ``_respecialise`` or False when the function cannot
+        be described that way (it needs data while tracing, or its structure depends on the size)."""
+        names = sorted(rec.sizes)
+        if not names:
+            return False
+        probes = {}
+        try:
+            for name in names:
+                other = self._record(leaves, td, scale={name: 2})
+                if len(other.nodes) != len(rec.nodes) or any(a.op is not b.op for a, b in zip(other.nodes, rec.nodes)):
+                    return False
+                probes[name] = other
+        except Exception:
+            return False
+        return {"base": rec, "probes": probes}
+
+    def _respecialise(self, sym: dict, leaves: list) -> tuple["_Recorded", Any]:
+        """Instantiate the base recording for the sizes of ``leaves``: same nodes, integers that moved
+        between the base and the probe recordings re-evaluated, output shapes re-inferred."""
+        base: _Recorded = sym["base"]
+        tensors = [(li, l) for li, l in enumerate(leaves) if isinstance(l, Tensor)]
+        sizes: dict[str, int] = {}
+        for (li, l) in tensors:
+            for d, name in self._dyn_names(li, l._impl).items():
+                v = int(l._impl._shape[d])
+                if sizes.setdefault(name, v) != v:
+                    raise ValueError(f"dynamic dimension '{name}' has two different sizes in one call ({sizes[name]}, {v})")
+        env = [(base.sizes[n], sym["probes"][n].sizes[n], sizes[n], sym["probes"][n]) for n in sorted(base.sizes)]
+
+        def value(path_get, v0):
+            """Integer at the same place in every recording -> its value for the new sizes."""
+            out = Fraction(v0)
+            for s0, s1, s_new, probe in env:
+                v1 = path_get(probe)
+                if type(v1) is not type(v0) and not (isinstance(v1, int) and isinstance(v0, int)):
+                    raise _NotAffine()
+                if v1 != v0:
+                    out += Fraction(v1 - v0, s1 - s0) * (s_new - s0)
+            if out.denominator != 1:
+                raise _NotAffine()
+            return int(out)
+
+        def subst(x0, getter):
+            """Rebuild a (nested) static argument, re-evaluating the integers that moved."""
+            if isinstance(x0, bool) or x0 is None or isinstance(x0, (str, float)):
+                return x0
+            if isinstance(x0, int):
+                return value(getter, x0)
+            if isinstance(x0, (tuple, list)):
+                for _, _, _, probe in env:
+                    x1 = getter(probe)
+                    if not isinstance(x1, (tuple, list)) or len(x1) != len(x0):
+                        raise _NotAffine()
+                return type(x0)(subst(v, (lambda i: lambda r: getter(r)[i])(i)) for i, v in enumerate(x0)) \
+                    if not hasattr(x0, "_fields") else x0
+            if isinstance(x0, dict):
+                return {k: subst(v, (lambda k: lambda r: getter(r)[k])(k)) for k, v in x0.items()}
+            return x0
+
+        new = _Recorded()
+        new.sizes = sizes
+        new.donated = list(base.donated)
+        new.out_static = list(base.out_static)
+        new.out_treedef = base.out_treedef
+        mapping: dict[int, TensorImpl] = {}
+        for ph0, (li, l) in zip(base.placeholders, tensors):
+            im = l._impl
+            ph = TensorImpl(list(im._buffers), shape=im._shape, dtype=im.dtype, device=im.device, sharding=im.sharding,
+                            batch_dims=im.batch_dims, is_traced=False)
+            ph.requires_grad = ph0.requires_grad
+            ph.is_traced = ph0.is_traced
+            new.placeholders.append(ph)
+            mapping[id(ph0)] = ph
+        for ni, n0 in enumerate(base.nodes):
+            leaves_new = []
+            for ai, a in enumerate(n0.arg_leaves):
+                if isinstance(a, TensorImpl):
+                    leaves_new.append(mapping.get(id(a), a))         # constants captured by the trace stay as they are
+                else:
+                    leaves_new.append(subst(a, (lambda ni, ai: lambda r: r.nodes[ni].arg_leaves[ai])(ni, ai)))
+            kw = subst(n0.kwargs, (lambda ni: lambda r: r.nodes[ni].kwargs)(ni))
+            okw = kw if n0.op_kwargs is n0.kwargs else subst(n0.op_kwargs, (lambda ni: lambda r: r.nodes[ni].op_kwargs)(ni))
+            node = OpNode(n0.op, leaves_new, n0.arg_treedef, kw, okw)
+            node.out_treedef = n0.out_treedef
+            outs0 = n0.outputs()
+            ins = [a for a in leaves_new if isinstance(a, TensorImpl)]
+            if getattr(n0.op, "host_sync", False):
+                # control-flow nodes keep the structure of their state: shapes follow the matching inputs
+                metas = None
+            else:
+                fake = [Tensor(impl=a) if isinstance(a, TensorImpl) else a for a in leaves_new]
+                metas, _ = n0.op.infer_outputs([(a._shape, a.dtype.to_torch()) for a in ins], fake, n0.arg_treedef, kw)
+            for oi, o0 in enumerate(outs0):
+                if o0 is None:
+                    node.out_refs.append(lambda: None)
+                    continue
+                if metas is not None:
+                    shape = tuple(int(x) for x in metas[oi][0])
+                else:
+                    shape = subst(tuple(int(x) for x in o0._shape), (lambda ni, oi: lambda r: tuple(int(x) for x in r.nodes[ni].outputs()[oi]._shape))(ni, oi))
+                impl = TensorImpl(None, shape=shape, dtype=o0.dtype, device=o0.device, sharding=o0.sharding,
+                                  batch_dims=o0.batch_dims, is_traced=o0.is_traced)
+                impl.output_refs = node
+                impl.output_index = oi
+                node.out_refs.append(weakref.ref(impl))
+                mapping[id(o0)] = impl
+                new.keep_alive.append(impl)
+            new.nodes.append(node)
+        new.keep = [[o for o in n.outputs() if o is not None] for n in new.nodes]
+        new.out_impls = [mapping.get(id(i), i) if i is not None else None for i in base.out_impls]
+        new.targets = [mapping[id(t)] for t in base.targets]
+        self._plan(new)
+        self._run(new)
+        return new, self._collect(new)
 
     # ---- execution of a recorded graph
     def _run(self, rec: _Recorded) -> None:
@@ -414,7 +621,7 @@ class CompiledFunction:
         return pytree.tree_unflatten(rec.out_treedef, outs)
 
     def _replay(self, rec: _Recorded, tensors: list[Tensor]) -> Any:
-        if self.use_cuda_graph and tensors and tensors[0]._impl.device.label == "gpu":
+        if self.use_cuda_graph and not rec.host_sync and tensors and tensors[0]._impl.device.label == "gpu":
             return self._replay_cuda_graph(rec, tensors)
         for ph, t in zip(rec.placeholders, tensors):
             ph._buffers = t._impl._buffers
@@ -453,7 +660,10 @@ class CompiledFunction:
             rec.cuda_graph = g
             self._stats.cuda_graphs += 1
             self._stats.launches_per_graph = total_launches() - n0
-            rec.static_ptrs = {b.data_ptr() for bufs in rec.static_inputs for b in bufs}
+            # only the graph's copies of DONATED arguments may be handed back as results: the caller gave
+            # those buffers up. The static copy of any other argument is overwritten by the next
+            # call's copy-in, so a result that aliases it is cloned out below.
+            rec.static_ptrs = {b.data_ptr() for bufs, d in zip(rec.static_inputs, rec.donated) if d for b in bufs}
         for bufs, t in zip(rec.static_inputs, tensors):
             for dst, src in zip(bufs, t._impl._buffers):
                 if dst.data_ptr() != src.data_ptr():

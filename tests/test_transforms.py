@@ -177,3 +177,96 @@ def test_backward_api_accumulates_grad():
     close(w.grad, 2 * rand(3, seed=1) + 3.0)
     with pytest.raises(ValueError):
         (w * 2.0).backward()
+
+
+# ---------------------------------------------------------------- compile: data-dependent control flow, RNG, dynamic dims
+def test_compiled_cond_follows_its_predicate():
+    """A compiled `cond` decides again on every call (reference: ops.cond lowered into the graph,
+    nabla/ops/control_flow.py:302-307); the branch taken while tracing is not baked in."""
+    g = nb.compile(lambda a: nb.cond(nb.reduce_sum(a) > 0, lambda x: x * 2, lambda x: x - 1, a))
+    pos = nb.constant(np.array([1., 2., 3.], dtype=np.float32))
+    neg = nb.constant(np.array([-1., -2., -3.], dtype=np.float32))
+    assert np.allclose(g(pos).to_numpy(), [2, 4, 6])
+    assert np.allclose(g(neg).to_numpy(), [-2, -3, -4])
+    assert np.allclose(g(pos).to_numpy(), [2, 4, 6])
+    assert g.stats.misses == 1 and g.stats.retraces == 0
+
+
+def test_compiled_cond_closure_and_select_lowering():
+    """Branches may close over tensors computed earlier in the traced function; with
+    cuda_graph=True the same function lowers to both branches + `where` and gives the same values."""
+    def f(a, b):
+        s = a + b
+        return nb.cond(nb.reduce_sum(a) > 0, lambda x: x * s, lambda x: x - s, a)
+    a1 = nb.constant(np.array([1., 2.], dtype=np.float32))
+    a2 = nb.constant(np.array([-1., -2.], dtype=np.float32))
+    b = nb.constant(np.array([10., 20.], dtype=np.float32))
+    for kw in ({}, {"cuda_graph": True}):
+        g = nb.compile(f, **kw)
+        assert np.allclose(g(a1, b).to_numpy(), [11, 44])
+        assert np.allclose(g(a2, b).to_numpy(), [-10, -20])
+        assert np.allclose(g(a1, b).to_numpy(), [11, 44])
+
+
+def test_compiled_cond_rejects_mismatched_branches():
+    g = nb.compile(lambda a: nb.cond(nb.reduce_sum(a) > 0, lambda x: x * 2, lambda x: nb.reduce_sum(x), a))
+    with pytest.raises(ValueError):
+        g(nb.constant(np.ones(3, dtype=np.float32)))
+
+
+def test_compiled_while_loop_trip_count_follows_the_input():
+    def f(x):
+        return nb.while_loop(lambda v, i: nb.reduce_sum(v) < 100.0, lambda v, i: (v * 2, i + 1),
+                             (x, nb.constant(np.float32(0))))
+    h = nb.compile(f)
+    for start, trips in ((1., 6), (10., 3), (40., 1), (200., 0), (1., 6)):
+        v, i = h(nb.constant(np.array([start, start], dtype=np.float32)))
+        assert int(i.to_numpy()) == trips
+        assert np.allclose(v.to_numpy(), start * 2 ** trips)
+    assert h.stats.misses == 1 and h.stats.retraces == 0
+
+
+def test_compiled_dropout_draws_a_new_mask_on_every_replay():
+    nb.seed(5)
+    g = nb.compile(lambda x: nb.nn.functional.dropout(x, p=0.5, training=True))
+    x = nb.constant(np.ones((64, 64), dtype=np.float32))
+    a, b, c = (g(x).to_numpy() for _ in range(3))
+    assert g.stats.hits == 2
+    assert (a != b).any() and (b != c).any()
+    assert set(np.unique(a)) <= {0.0, 2.0}
+
+
+def test_dynamic_dims_serves_new_sizes_without_rerunning_python():
+    """dynamic_dims: four sizes, the Python function runs for the first one only (plus one
+    shape-only probe); shape-valued arguments follow the size (reference: one executable with
+    symbolic dims, nabla/transforms/compile.py:276-301, tests/unit/test_compile.py:46)."""
+    calls = {"n": 0}
+
+    def f(x, w):
+        calls["n"] += 1
+        b = int(x.shape[0])
+        y = nb.reshape(nb.matmul(x, w), (b * 2, 4))
+        z = nb.concatenate([y, nb.zeros((b, 4), dtype=y.dtype, device=y.device)], axis=0)
+        return nb.reduce_sum(nb.relu(z), axis=0), z[: b // 2]
+
+    g = nb.compile(f, dynamic_dims={0: {0: "batch"}})
+    rng = np.random.default_rng(0)
+    w = rng.standard_normal((6, 8)).astype(np.float32)
+    for b in (4, 8, 2, 16, 8):
+        x = rng.standard_normal((b, 6)).astype(np.float32)
+        out, head = g(nb.constant(x), nb.constant(w))
+        z = np.concatenate([(x @ w).reshape(b * 2, 4), np.zeros((b, 4), np.float32)], 0)
+        assert np.allclose(out.to_numpy(), np.maximum(z, 0).sum(0), atol=1e-4)
+        assert np.allclose(head.to_numpy(), z[: b // 2], atol=1e-5)
+    assert calls["n"] == 2                      # the real trace and the shape-only probe
+    assert g.stats.retraces == 0 and g.stats.respecialisations == 3 and g.stats.misses == 1
+
+
+def test_dynamic_dims_falls_back_when_a_size_is_not_affine():
+    """b // 2 recorded at b = 4 and probed at b = 8 has slope 1/2: an odd size has no integer value
+    on that line, so that size is traced on its own and counted as a retrace."""
+    g = nb.compile(lambda x: x[: int(x.shape[0]) // 2] * 2.0, dynamic_dims={0: {0: "n"}})
+    for n in (4, 6, 5):
+        x = np.arange(n, dtype=np.float32)
+        assert np.allclose(g(nb.constant(x)).to_numpy(), x[: n // 2] * 2)
+    assert g.stats.respecialisations == 1 and g.stats.retraces == 1
