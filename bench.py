@@ -103,6 +103,9 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="transformer", choices=["transformer", "gpipe", "pp_dp", "lora"],
+                    help="transformer = the headline dp x tp benchmark; the others time the pipeline / LoRA "
+                         "configurations of nabla_b200.models.configs at their full sizes on the GPUs given")
     ap.add_argument("--layers", type=int, default=24, help="debug only: a run with fewer layers is not a valid number")
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--tp", type=int, default=0, help="debug only: tensor-parallel width (default min(N, 4), the benchmark's mesh)")
@@ -112,6 +115,9 @@ def main() -> None:
         return
     if args.warmup < 3:
         args.warmup = 3
+    if args.config != "transformer":
+        other_config(args)
+        return
 
     import numpy as np
     import torch
@@ -154,16 +160,17 @@ def main() -> None:
         # and replayed; params and optimizer state are donated, so AdamW updates them in place
         use_graph = os.environ.get("NABLA_B200_CUDA_GRAPH", "1") != "0"
 
-        @nb.compile(cuda_graph=use_graph, donate_argnums=(0, 1))
-        def train_step(params, state, tokens, targets):
+        def step_fn(params, state, tokens, targets):
             loss, grads = nb.value_and_grad(lambda p: T.loss_fn(p, tokens, targets, cfg, sp), create_graph=False)(params)
             params, state = nn.adamw_update(params, grads, state, lr=1e-4, weight_decay=0.01, realize=False)
             return loss, params, state
 
+        train_step = nb.compile(step_fn, cuda_graph=use_graph, donate_argnums=(0, 1))
+
         # synthetic data: every rank generates the same global batch (same seed) in pinned host
         # memory and keeps its dp slice; a fresh batch per step
         rng = np.random.default_rng(2024)
-        n_batches = args.warmup + 2 * args.steps
+        n_batches = 2 * args.warmup + 3 * args.steps
         rows = global_batch // dp
         dp_idx = (rank // tp) if mesh is not None else 0
         host = []
@@ -250,6 +257,42 @@ def main() -> None:
         e2e_ms_total = float(t2.item())
         native.check_status()
 
+        # ---- exposed communication: the same step recorded with every collective replaced by its
+        # communication-free local counterpart (same GEMM shapes, no byte crosses NVLink); the
+        # difference to the real step is what the step fails to hide. Runs last: its numbers are garbage.
+        exposed = None
+        graph_used = bool(train_step.stats.cuda_graphs)
+        launches_per_graph = train_step.stats.launches_per_graph
+        if world > 1 and os.environ.get("NABLA_B200_EXPOSED_COMM", "1") != "0":
+            from nabla_b200.parallel import symm
+
+            try:
+                train_step.release()
+                symm.set_local_only(True)
+                local_step = nb.compile(step_fn, cuda_graph=use_graph, donate_argnums=(0, 1))
+                for _ in range(args.warmup):
+                    tok, tgt = to_device(next(it))
+                    loss, params, state = local_step(params, state, tok, tgt)
+                staged = [to_device(next(it)) for _ in range(args.steps)]
+                sync()
+                e4, e5 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e4.record()
+                for tok, tgt in staged:
+                    loss, params, state = local_step(params, state, tok, tgt)
+                e5.record()
+                sync()
+                t3 = torch.tensor([e4.elapsed_time(e5)], device=tdev)
+                torch.distributed.all_reduce(t3, op=torch.distributed.ReduceOp.MAX)
+                local_ms = float(t3.item()) / args.steps
+                exposed = {"exposed_comm_ms_per_step": ms_total / args.steps - local_ms,
+                           "compute_only_ms_per_step": local_ms,
+                           "exposed_comm_fraction": (ms_total / args.steps - local_ms) / (ms_total / args.steps)}
+                local_step.release()
+            except Exception as e:      # the measurement is optional: never lose the headline numbers to it
+                exposed = {"exposed_comm_ms_per_step": None, "error": f"{type(e).__name__}: {str(e)[:160]}"}
+            finally:
+                symm.set_local_only(False)
+
         if os.environ.get("NABLA_B200_PROFILE_OPS") and not train_step.stats.cuda_graphs:
             # per-op device time of one more step (event pair around every replayed op), rank 0 -> stderr
             train_step.profile_ops = True
@@ -282,7 +325,7 @@ def main() -> None:
                        "global_batch": global_batch, "seq_len": seq, "parallelism": f"dp{dp}xtp{tp}" + ("+sp" if sp is not None else ""),
                        "l2": "inputs larger than L2 (per-step working set is tens of GB)",
                        "optimizer": "AdamW fused kernel, inside the timed step",
-                       "cuda_graph": bool(train_step.stats.cuda_graphs)},
+                       "cuda_graph": graph_used},
             "clocks": clk.summary(),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms_total / args.steps,
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4},
@@ -294,15 +337,45 @@ def main() -> None:
             "impl": "ours",
             "collectives": _collective_stats(),
         }
-        print(json.dumps(out))
-    if world > 1:
-        torch.distributed.barrier()
-        torch.cuda.synchronize()
-        sys.stdout.flush()
-        sys.stderr.flush()
-        # captured CUDA graphs hold NCCL kernels; tearing the communicator down under them can
-        # block, so the ranks leave together without the teardown
-        os._exit(0)
+        if exposed is not None:
+            out.update(exposed)
+        print(json.dumps(out), flush=True)
+    from nabla_b200.parallel import shutdown
+
+    del params, state, loss
+    shutdown(train_step)
+
+
+def other_config(args) -> None:
+    """`--config gpipe | pp_dp | lora`: the other multi-GPU configurations, same JSON contract."""
+    import torch
+
+    import nabla_b200 as nb
+    from nabla_b200 import native
+    from nabla_b200.models import configs
+    from nabla_b200.parallel import init_distributed
+
+    rank, world = init_distributed()
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = nb.Accelerator(local)
+    tdev = dev.to_torch()
+    run = {"gpipe": configs.run_gpipe, "pp_dp": configs.run_pp_dp, "lora": configs.run_lora}[args.config]
+    with nb.default_device(dev), ClockSampler(local) as clk:
+        res = run(nb, rank, world, dev, tdev, args.steps, args.warmup)
+        native.check_status()
+    if rank == 0:
+        unit = "tokens/s" if args.config == "lora" else "samples/s"
+        value = res.get("tokens_per_s", res.get("samples_per_s"))
+        metric = {"gpipe": "train samples/sec GPipe MLP (one bf16 Linear 4096 + relu per stage, 32 micro-batches of 64)",
+                  "pp_dp": "train samples/sec PP x DP MLP (2 bf16 Linear 8192 + relu per stage, 16 micro-batches of 128 per replica, AdamW)",
+                  "lora": "train tokens/sec LoRA rank 16 on q/k/v/o of the 24L d2048 transformer, tensor parallel, seq 2048 batch 32"}
+        print(json.dumps({"metric": metric[args.config], "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+                          "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+                          "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+                          "data": "synthetic N(0,1) activations / token ids ~U[0,32000), random-init weights",
+                          "config": res, "clocks": clk.summary(), "gpu_launches": int(native.total_launches()),
+                          "impl": "ours"}), flush=True)
+    configs.finish()
 
 
 if __name__ == "__main__":

@@ -158,6 +158,34 @@ def tree_leaves(tree: Any, is_leaf=None) -> list:
     return tree_flatten(tree, is_leaf)[0]
 
 
+def leaf_names(treedef: PyTreeDef, prefix: str = "") -> list[str]:
+    """One path string per leaf of ``treedef``, in flatten order: dict entries as ``.key``, items of
+    lists / tuples / registered containers as ``[i]`` (e.g. ``layers[2].attn.q``). With a prefix the
+    first dict key is joined with a dot (``lora.w``)."""
+    out: list[str] = []
+
+    def walk(td: PyTreeDef, path: str) -> None:
+        if td.kind == "leaf":
+            out.append(path)
+        elif td.kind == "none":
+            return
+        elif td.kind == "dict":
+            for k, c in zip(td.meta, td.children):
+                walk(c, f"{path}.{k}" if path else str(k))
+        else:
+            for i, c in enumerate(td.children):
+                walk(c, f"{path}[{i}]")
+
+    walk(treedef, prefix)
+    return out
+
+
+def tree_flatten_full(tree: Any, is_leaf=None) -> tuple[list, list[str], PyTreeDef]:
+    """``tree_flatten`` plus the path name of every leaf: ``(leaves, names, treedef)``."""
+    leaves, td = tree_flatten(tree, is_leaf)
+    return leaves, leaf_names(td), td
+
+
 def tree_structure(tree: Any, is_leaf=None) -> PyTreeDef:
     return tree_flatten(tree, is_leaf)[1]
 

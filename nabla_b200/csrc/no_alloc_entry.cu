@@ -92,9 +92,9 @@ float* scratch_for_current_device() {
 }
 
 int parts_for(int rows) {
-  int np = (rows + 511) / 512;
+  long long np = ((long long)rows + 511) / 512;      // 64-bit: rows close to INT_MAX must not wrap
   if (np > NB_NOALLOC_MAX_PARTS) np = NB_NOALLOC_MAX_PARTS;
-  return np < 1 ? 1 : np;
+  return np < 1 ? 1 : (int)np;
 }
 
 }  // namespace
@@ -111,13 +111,21 @@ extern "C" int nb_colsum_noalloc(const void* x, void* out, int rows, int N, int 
   if (scratch == nullptr) return NB_NOALLOC_ERR_SETUP;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int parts = parts_for(rows);
-  const int rows_per_part = (rows + parts - 1) / parts;
+  const int rows_per_part = (int)(((long long)rows + parts - 1) / parts);
   const dim3 grid((N + 32 * V - 1) / (32 * V), parts);
+  // cudaPeekAtLastError after each launch: it reports a failed launch of ours without clearing (and
+  // thereby swallowing) an error that the caller's earlier work may have left behind
   if (in_dtype) noalloc_colsum_slabs<bf16><<<grid, 256, 0, s>>>(static_cast<const bf16*>(x), scratch, rows, N, rows_per_part);
   else noalloc_colsum_slabs<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), scratch, rows, N, rows_per_part);
+  if (cudaPeekAtLastError() != cudaSuccess) return NB_NOALLOC_ERR_LAUNCH;
   if (out_dtype) noalloc_colsum_fold<bf16><<<(N + 255) / 256, 256, 0, s>>>(scratch, static_cast<bf16*>(out), parts, N);
   else noalloc_colsum_fold<float><<<(N + 255) / 256, 256, 0, s>>>(scratch, static_cast<float*>(out), parts, N);
-  return cudaGetLastError() == cudaSuccess ? NB_NOALLOC_OK : NB_NOALLOC_ERR_LAUNCH;
+  return cudaPeekAtLastError() == cudaSuccess ? NB_NOALLOC_OK : NB_NOALLOC_ERR_LAUNCH;
+}
+
+extern "C" void nb_noalloc_forget_devices(void) {
+  std::lock_guard<std::mutex> lock(g_setup_mutex);
+  for (int i = 0; i < MAX_DEVICES; ++i) g_scratch_addr[i] = nullptr;
 }
 
 extern "C" const char* nb_noalloc_strerror(int code) {

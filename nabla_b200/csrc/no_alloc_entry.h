@@ -25,7 +25,11 @@
 //     same call, so stale contents are never observed.
 //   * Set-up: the first call on each device looks up the device address of the array (with that
 //     device current) and caches it. Make that first call outside any stream capture; later
-//     calls only launch kernels.
+//     calls only launch kernels. With lazy module loading that first call is also the moment
+//     the driver loads this library's code and commits its 2 MiB data segment on the device, so
+//     make it while the device still has that much memory to spare, i.e. before the process
+//     fills the GPU. A host that resets the device (cudaDeviceReset) must call
+//     nb_noalloc_forget_devices() afterwards: the cached addresses belong to the old context.
 //   * The routine itself calls no cudaMalloc, cudaFree or other allocating routine, and takes
 //     nothing from torch.
 #pragma once
@@ -49,6 +53,10 @@ extern "C" {
  * `stream` is a cudaStream_t (null = the default stream). Returns NB_NOALLOC_OK or a negative
  * code; nothing is launched when the code is one of the argument errors. */
 int nb_colsum_noalloc(const void* x, void* out, int rows, int N, int in_dtype, int out_dtype, void* stream);
+
+/* Drop the cached per-device addresses of the scratch array; the next call on a device looks
+ * its address up again. Needed only after the host destroyed the device's context. */
+void nb_noalloc_forget_devices(void);
 
 /* A one-line description of a code returned by nb_colsum_noalloc. */
 const char* nb_noalloc_strerror(int code);

@@ -32,6 +32,17 @@ import numpy as np
 import torch
 
 
+_COMPILED: list = []      # compiled step functions of this process, released by `finish`
+
+
+def finish() -> None:
+    """Release the recorded steps (and their CUDA graphs) and leave the process group in order."""
+    from nabla_b200.parallel import shutdown
+
+    shutdown(*_COMPILED)
+    _COMPILED.clear()
+
+
 def _graph() -> bool:
     """Replay the recorded step from one CUDA graph (default) unless NABLA_B200_CUDA_GRAPH=0."""
     return os.environ.get("NABLA_B200_CUDA_GRAPH", "1") != "0"
@@ -73,6 +84,7 @@ def run_gpipe(nb, rank, world, dev, tdev, steps, warmup, dim=4096, micro=32, bat
         return loss, w - gw * 1e-3, b - gb * 1e-3
 
     state = [w, b]
+    _COMPILED.append(step)
 
     def one():
         loss, state[0], state[1] = step(state[0], state[1], xs, ys)
@@ -115,6 +127,7 @@ def run_pp_dp(nb, rank, world, dev, tdev, steps, warmup, dim=8192, micro=16, bat
         return loss, params, state
 
     box = [params, state]
+    _COMPILED.append(step)
 
     def one():
         loss, box[0], box[1] = step(box[0], box[1], xs, ys)
@@ -151,6 +164,7 @@ def run_lora(nb, rank, world, dev, tdev, steps, warmup, layers=24, batch=32, seq
         return loss, lora, state
 
     box = [lora, state]
+    _COMPILED.append(step)
 
     def one():
         loss, box[0], box[1] = step(box[0], box[1], tok, tgt)
@@ -241,11 +255,7 @@ def main() -> None:
     out.update(n_gpus=world, steps=args.steps, warmup=args.warmup, small=bool(args.small), cuda_graph=_graph())
     if rank == 0:
         print(json.dumps(out), flush=True)
-    if world > 1:
-        torch.distributed.barrier()
-        torch.cuda.synchronize()
-        sys.stdout.flush()
-        os._exit(0)
+    finish()
 
 
 if __name__ == "__main__":

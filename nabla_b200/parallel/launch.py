@@ -50,3 +50,47 @@ def init_distributed(backend: str | None = None, timeout_s: float = 600.0) -> tu
 
         set_default_device(Accelerator(local_rank()))
     return dist.get_rank(), dist.get_world_size()
+
+
+def shutdown(*compiled, timeout_s: float = 45.0) -> None:
+    """Orderly end of a (multi-rank) run: drop the recorded schedules and their CUDA graphs, wait for
+    the device, meet the other ranks, then destroy the process group and return normally, so the
+    interpreter's exit hooks run. Captured graphs hold NCCL and peer-memory launches; destroying the
+    communicator while such a graph is alive can block, which is why the graphs go first.
+
+    A daemon timer ends the process (exit code 0, streams flushed) if the teardown itself does not
+    come back within ``timeout_s``: a rank stuck in teardown must not keep the job's launcher alive."""
+    import gc
+    import sys
+    import threading
+
+    for c in compiled:
+        rel = getattr(c, "release", None)
+        if rel is not None:
+            rel()
+    gc.collect()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    if not (dist.is_available() and dist.is_initialized()):
+        return
+
+    def _bail():
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+    guard = threading.Timer(timeout_s, _bail)
+    guard.daemon = True
+    guard.start()
+    try:
+        dist.barrier()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+            from . import symm
+
+            symm.release_all()          # peer mappings go while every rank is still here
+            torch.cuda.synchronize()
+            dist.barrier()
+        dist.destroy_process_group()
+    finally:
+        guard.cancel()

@@ -219,6 +219,17 @@ def disable() -> None:
     _enabled = False
 
 
+def release_all() -> None:
+    """Drop every symmetric workspace and arena of this process (end of a run, all kernels done)."""
+    import gc
+
+    for ws in set(_workspaces.values()):
+        ws.arena = None
+    _workspaces.clear()
+    _side_streams.clear()
+    gc.collect()
+
+
 def workspace(mesh, axes) -> Workspace:
     key = (id(mesh), tuple(axes))
     ws = _workspaces.get(key)

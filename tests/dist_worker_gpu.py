@@ -1,8 +1,10 @@
 """Worker run under torchrun by tests/test_gpu_multi.py (one rank per GPU, NCCL).
 
-Checks, on every rank: the peer-memory collectives against NCCL results, the sharded transformer
-step against the unsharded one, and (mode 'lost_peer') that a rank which leaves between steps
-is reported to the others as an error. Prints one ``RESULT {json}`` line per rank.
+Checks, on every rank: the peer-memory collectives and the fused GEMM + collective kernels against
+NCCL results (mode 'grouped': on the tp and dp groups of a ('dp', 'tp') mesh, (2, 4) on 8 GPUs),
+the sharded transformer step against the unsharded one, and (mode 'lost_peer') that a rank which
+leaves between steps is reported to the others as an error. Prints one ``RESULT {json}`` line per
+rank. Timing sweeps live in ``nabla_b200.utils.microbench`` (comm_allreduce, comm_fused).
 """
 import json
 import os
@@ -68,22 +70,6 @@ def main():
         out["errs"] = {k: v for k, v in errs.items() if v > 1e-2}
         out["timeout_probe_status"] = symm.wait_flag_timeout_probe(20.0)
         out["canary_ok"] = ws.check_canary()        # nothing wrote past the end of the workspace
-        # bandwidth of the large all-reduce (device time, max over ranks)
-        x = torch.randn(64 * 1024 * 1024, device=dev, dtype=torch.bfloat16)
-        for name, fn in (("native", lambda: symm.all_reduce(x, mesh, ("x",))), ("nccl", lambda: dist.all_reduce(x.clone()))):
-            for _ in range(3):
-                fn()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            dist.barrier()
-            torch.cuda.synchronize()
-            e0.record()
-            for _ in range(5):
-                fn()
-            e1.record()
-            torch.cuda.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1) / 5], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            out[f"ar128MB_{name}_ms"] = t.item()
     elif mode == "fused_gemm":
         from nabla_b200 import native
         from nabla_b200.native.gemm import gemm_bf16
@@ -177,123 +163,114 @@ def main():
         native.check_status()
         out["max_err"] = max(errs.values())
         out["errs"] = {k: v for k, v in errs.items() if v > 2e-2}
-        # row-parallel projection of the benchmark model: tokens x d_model, K = d_ff / world
-        M, N, K = 16384, 2048, 8192 // world
-        a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
-        b = torch.randn(K, N, device=dev, dtype=torch.bfloat16)
-
-        def unfused():
-            y = gemm_bf16(a, b)
-            dist.all_reduce(y)
-            return y
-
-        xs = torch.randn(M // world, 2048, device=dev, dtype=torch.bfloat16)
-        w1 = torch.randn(2048, 8192 // world, device=dev, dtype=torch.bfloat16)
-        full_x = torch.empty(M, 2048, device=dev, dtype=torch.bfloat16)
-
-        y_c = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
-        o_c = torch.empty(M // world, N, device=dev, dtype=torch.bfloat16)
-
-        def unfused_rs():
-            y = gemm_bf16(a, b)
-            o = torch.empty(M // world, N, device=dev, dtype=torch.bfloat16)
-            dist.reduce_scatter_tensor(o, y)
-            return o
-
-        def unfused_ag():
-            dist.all_gather_into_tensor(full_x, xs)
-            return gemm_bf16(full_x, w1)
-
-        for name, fn in (("fused", lambda: symm.gemm_all_reduce(a, b, mesh, ("x",))), ("gemm_then_nccl", unfused),
-                         ("gemm_only", lambda: gemm_bf16(a, b)),
-                         ("rs_fused", lambda: symm.gemm_reduce_scatter(a, b, mesh, ("x",), M // world)),
-                         ("rs_gemm_then_nccl", unfused_rs),
-                         ("ag_fused", lambda: symm.all_gather_gemm(xs, w1, mesh, ("x",), M // world)),
-                         ("ag_nccl_then_gemm", unfused_ag), ("ag_gemm_only", lambda: gemm_bf16(full_x, w1)),
-                         ("nccl_ar_only", lambda: dist.all_reduce(y_c)),
-                         ("nccl_rs_only", lambda: dist.reduce_scatter_tensor(o_c, y_c)),
-                         ("nccl_ag_only", lambda: dist.all_gather_into_tensor(full_x, xs))):
-            for _ in range(3):
-                fn()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            dist.barrier()
-            torch.cuda.synchronize()
-            e0.record()
-            for _ in range(10):
-                fn()
-            e1.record()
-            torch.cuda.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1) / 10], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            out[f"{name}_ms"] = t.item()
-        native.check_status()
-    elif mode == "fused_sweep":
-        # timing sweep of the fused kernels over the number of communication CTAs (bench shapes)
-        from nabla_b200.native.gemm import gemm_bf16
+    elif mode == "grouped":
+        # the mesh of record: ('dp', 'tp') = (2, 4) on 8 GPUs ((2, 2) on 4): every collective and every
+        # fused GEMM + collective on the tp groups and on the dp groups, against NCCL on the same group
+        from nabla_b200 import native
         from nabla_b200.parallel import symm
 
-        mesh = nb.DeviceMesh("m", (world,), ("x",))
-        M = 16384 * world
-        a = torch.randn(M, 8192 // world, device=dev, dtype=torch.bfloat16)
-        b = torch.randn(8192 // world, 2048, device=dev, dtype=torch.bfloat16)
-        xs = torch.randn(M // world, 2048, device=dev, dtype=torch.bfloat16)
-        w1 = torch.randn(2048, 8192 // world, device=dev, dtype=torch.bfloat16)
-        w8 = torch.randn(2048, 8, device=dev, dtype=torch.bfloat16)
-        full_x = torch.randn(M, 2048, device=dev, dtype=torch.bfloat16)
-
-        def timed(fn):
-            for _ in range(3):
-                fn()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            dist.barrier()
+        tp = 4 if world >= 8 else 2
+        mesh = nb.DeviceMesh("m", (world // tp, tp), ("dp", "tp"))
+        errs = {}
+        out["groups"] = {}
+        for axes in (("tp",), ("dp",)):
+            pg, ranks = mesh.process_group(axes)
+            g = len(ranks)
+            if g == 1:
+                continue
+            gi = ranks.index(rank)
+            ws = symm.workspace(mesh, axes)
+            out["groups"]["+".join(axes)] = {"ranks": ranks, "nvls": bool(ws.mc_ptr)}
+            tag = axes[0]
+            for dtype in (torch.bfloat16, torch.float32):
+                for n in (4096, (1 << 20) + 8 * g, (1 << 22) + 24 * g):
+                    torch.manual_seed(100 + rank)
+                    x = torch.randn(n, device=dev, dtype=dtype)
+                    ref = x.clone().float()
+                    dist.all_reduce(ref, group=pg)
+                    for algo in ["oneshot", "twoshot"] + (["multimem"] if ws.mc_ptr else []):
+                        y = symm.all_reduce(x, mesh, axes, "sum", algo=algo)
+                        errs[f"{tag}_ar_{algo}_{str(dtype)[6:]}_{n}"] = ((y.float() - ref).abs().max() / (ref.abs().max() + 1e-6)).item()
+            x = torch.randn(64, 256, device=dev, dtype=torch.bfloat16)
+            parts = [torch.empty_like(x) for _ in range(g)]
+            dist.all_gather(parts, x, group=pg)
+            errs[f"{tag}_all_gather"] = (symm.all_gather_dim0(x, mesh, axes).float() - torch.cat(parts).float()).abs().max().item()
+            big = torch.randn(64 * g, 256, device=dev, dtype=torch.float32)
+            rs_ref = torch.empty(64, 256, device=dev)
+            dist.reduce_scatter_tensor(rs_ref, big.clone(), group=pg)
+            errs[f"{tag}_reduce_scatter"] = (symm.reduce_scatter_dim0(big, mesh, axes) - rs_ref).abs().max().item()
+            # fused GEMM -> all-reduce on this group
+            for (M, N, K) in [(1000, 264, 328), (2048, 2048, 512)]:
+                torch.manual_seed(7 + rank)
+                a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+                b = torch.randn(K, N, device=dev, dtype=torch.bfloat16)
+                ref = a.float() @ b.float()
+                dist.all_reduce(ref, group=pg)
+                for rep in range(2):
+                    y = symm.gemm_all_reduce(a, b, mesh, axes).clone()
+                    errs[f"{tag}_gemm_ar_{M}x{N}x{K}_{rep}"] = ((y.float() - ref).abs().max() / ref.abs().max()).item()
+            # fused GEMM -> reduce-scatter and all-gather -> GEMM on this group
+            for (M, N, K, cs) in [(256 * g, 512, 256, 128), (1024 * g, 264, 328, 256)]:
+                torch.manual_seed(11 + rank)
+                a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+                b = torch.randn(K, N, device=dev, dtype=torch.bfloat16)
+                ref = a.float() @ b.float()
+                dist.all_reduce(ref, group=pg)
+                mine = ref.view(-1, g, cs, N)[:, gi].reshape(-1, N)
+                for rep in range(2):
+                    y = symm.gemm_reduce_scatter(a, b, mesh, axes, cs)
+                    errs[f"{tag}_gemm_rs_{M}x{N}x{K}_{rep}"] = ((y.float() - mine).abs().max() / ref.abs().max()).item()
+                torch.manual_seed(5)
+                w = torch.randn(K, N, device=dev, dtype=torch.bfloat16) * 0.05
+                torch.manual_seed(13 + rank)
+                xs = torch.randn(M // g, K, device=dev, dtype=torch.bfloat16)
+                parts = [torch.empty_like(xs) for _ in range(g)]
+                dist.all_gather(parts, xs, group=pg)
+                full = torch.stack([p_.view(-1, cs, K) for p_ in parts], 1).reshape(M, K)
+                z_ref = full.float() @ w.float()
+                ar = symm.arena(mesh, axes)
+                for rep in range(3):
+                    off = ar.alloc(M * K * 2) if (ar is not None and rep >= 1) else None      # reps 1, 2: push variant
+                    a_full, y = symm.all_gather_gemm(xs, w, mesh, axes, cs, arena_off=off)
+                    torch.cuda.synchronize()
+                    errs[f"{tag}_ag_gather_{M}x{K}_{rep}"] = (a_full.float() - full.float()).abs().max().item()
+                    errs[f"{tag}_ag_gemm_{M}x{N}x{K}_{rep}"] = ((y.float() - z_ref).abs().max() / z_ref.abs().max()).item()
+                    if off is not None:
+                        dist.barrier(group=pg)
+                        ar.free(off)
             torch.cuda.synchronize()
-            e0.record()
-            for _ in range(10):
-                fn()
-            e1.record()
-            torch.cuda.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1) / 10], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            return round(t.item(), 4)
-
-        out["rs_gemm_only"] = timed(lambda: gemm_bf16(a, b))
-        out["ag_gemm_only"] = timed(lambda: gemm_bf16(full_x, w1))
-        out["nccl_ag"] = timed(lambda: dist.all_gather_into_tensor(full_x, xs))
-        out["rs_fused"] = timed(lambda: symm.gemm_reduce_scatter(a, b, mesh, ("x",), M // world))
-        for c in (8, 12, 16):
-            out[f"ag_{c}"] = timed(lambda: symm.all_gather_gemm(xs, w1, mesh, ("x",), M // world, comm_ctas=c))
-            out[f"agcopy_{c}"] = timed(lambda: symm.all_gather_gemm(xs, w8, mesh, ("x",), M // world, comm_ctas=c))
-        ar = symm.arena(mesh, ("x",))
-        off = ar.alloc(M * 2048 * 2)
-        for c in (2, 4, 6, 8, 12):
-            out[f"agpush_{c}"] = timed(lambda: symm.all_gather_gemm(xs, w1, mesh, ("x",), M // world, comm_ctas=c, arena_off=off))
-            out[f"agpushcopy_{c}"] = timed(lambda: symm.all_gather_gemm(xs, w8, mesh, ("x",), M // world, comm_ctas=c,
-                                                                        arena_off=off))
-        native_ok = True
-        from nabla_b200 import native
+            out.setdefault("canary_ok", True)
+            out["canary_ok"] = out["canary_ok"] and ws.check_canary()
         native.check_status()
+        out["max_err"] = max(errs.values())
+        out["n_checks"] = len(errs)
+        out["errs"] = {k: v for k, v in errs.items() if v > 2e-2}
     elif mode == "transformer":
         from nabla_b200.models import transformer as TR
         from nabla_b200.parallel import backend
 
-        cfg = TR.TransformerConfig(n_layers=2, d_model=256, n_heads=2, d_ff=512, vocab=512, max_seq=256)
+        tp = 4 if world >= 8 else (2 if world % 2 == 0 else 1)
+        cfg = TR.TransformerConfig(n_layers=2, d_model=512, n_heads=4, d_ff=1024, vocab=512, max_seq=256)
         with nb.default_device(nb.Accelerator(dev.index)):
             nb.seed(0)
             params = TR.init_params(cfg, device=nb.Accelerator(dev.index))
             rng = np.random.default_rng(0)
-            tok = nb.constant(rng.integers(0, 512, (4, 256)), device=nb.Accelerator(dev.index))
-            tgt = nb.constant(rng.integers(0, 512, (4, 256)), device=nb.Accelerator(dev.index))
+            tok = nb.constant(rng.integers(0, 512, (8, 256)), device=nb.Accelerator(dev.index))
+            tgt = nb.constant(rng.integers(0, 512, (8, 256)), device=nb.Accelerator(dev.index))
             l0, g0 = nb.value_and_grad(lambda p: TR.loss_fn(p, tok, tgt, cfg), create_graph=False)(params)
-            tp = 2 if world % 2 == 0 else 1
             mesh = nb.DeviceMesh("m", (world // tp, tp), ("dp", "tp"))
             ps = TR.place_params(params, mesh, "tp")
             toks, tgts = tok.shard(mesh, ("dp", None)), tgt.shard(mesh, ("dp", None))
-            l1, g1 = nb.value_and_grad(lambda p: TR.loss_fn(p, toks, tgts, cfg), create_graph=False)(ps)
+            # sequence-parallel layout (tokens split over 'tp' between the projections): this is what
+            # puts the fused GEMM -> reduce-scatter and all-gather -> GEMM kernels on the model's path
+            sp = TR.SeqParallel(mesh, "dp", "tp") if (tp > 1 and os.environ.get("NABLA_B200_SEQ_PARALLEL", "1") != "0") else None
+            l1, g1 = nb.value_and_grad(lambda p: TR.loss_fn(p, toks, tgts, cfg, sp), create_graph=False)(ps)
             rel = []
             for a, b in zip(nb.tree_leaves(g0), nb.tree_leaves(g1)):
                 ta, tb = torch.from_numpy(a.to_numpy()).float(), torch.from_numpy(b.to_numpy()).float()
                 rel.append(((ta - tb).norm() / (ta.norm() + 1e-6)).item())
-            out.update(loss0=l0.item(), loss1=l1.item(), grad_rel_err=max(rel), backend=dict(backend.stats))
+            out.update(loss0=l0.item(), loss1=l1.item(), grad_rel_err=max(rel), backend=dict(backend.stats),
+                       mesh=[world // tp, tp], seq_parallel=sp is not None)
     elif mode == "lost_peer":
         import time
 

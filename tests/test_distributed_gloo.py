@@ -68,8 +68,10 @@ FAILING = textwrap.dedent('''
 
 
 def _run(script: str, args, nproc=2, timeout=240):
-    path = os.path.join(ROOT, "_work", f"_gloo_worker_{abs(hash(script)) % 10**8}.py")
-    os.makedirs(os.path.dirname(path), exist_ok=True)
+    import tempfile
+
+    tmp = tempfile.mkdtemp(prefix="nb_gloo_")                 # worker scripts never live in the source tree
+    path = os.path.join(tmp, "worker.py")
     with open(path, "w") as f:
         f.write(script.format(root=ROOT))
     port = 29500 + (os.getpid() % 2000)
@@ -77,6 +79,49 @@ def _run(script: str, args, nproc=2, timeout=240):
            "--master-addr", "127.0.0.1", "--master-port", str(port), path, *args]
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
     return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+
+
+CHECKPOINT = textwrap.dedent('''
+    import os, sys, json
+    sys.path.insert(0, {root!r})
+    import numpy as np
+    import nabla_b200 as nb
+    from nabla_b200 import nn
+    from nabla_b200.nn.finetune import save_finetune_checkpoint, load_finetune_checkpoint
+    from nabla_b200.parallel import init_distributed
+    rank, world = init_distributed(backend="gloo", timeout_s=60)
+    out_dir = sys.argv[1]
+    mesh = nb.DeviceMesh("m", (2,), ("tp",))
+    rng = np.random.default_rng(0)
+    full = {{"A": rng.standard_normal((4, 6)).astype(np.float32), "B": rng.standard_normal((6, 4)).astype(np.float32)}}
+    lora = {{"q": {{"A": nb.constant(full["A"]).shard(mesh, (None, "tp")), "B": nb.constant(full["B"]).shard(mesh, ("tp", None))}}}}
+    state = nn.adamw_init(lora)
+    state = dict(state, step=7)
+    for _ in range(3):                                   # several saves in a row: every rank calls, rank 0 writes
+        save_finetune_checkpoint(out_dir, lora_params=lora, optimizer_state=state, metadata={{"tag": "t"}})
+    files = sorted(os.listdir(out_dir))
+    l2, s2, meta = load_finetune_checkpoint(out_dir, lora_template=lora, optimizer_template=state)
+    ok = bool(np.allclose(l2["q"]["A"].to_numpy(), full["A"]) and np.allclose(l2["q"]["B"].to_numpy(), full["B"]))
+    same_spec = l2["q"]["A"]._impl.sharding == lora["q"]["A"]._impl.sharding
+    print("RESULT " + json.dumps({{"rank": rank, "ok": ok, "spec": bool(same_spec), "files": files, "step": s2["step"],
+                                  "keys": meta["tensor_keys"]}}), flush=True)
+''')
+
+
+def test_two_rank_checkpoint_save_and_reload(tmp_path):
+    """Every rank calls save (the gather of sharded tensors is collective), only rank 0 writes, no
+    temporary file is left behind, and both ranks reload the sharded adapters."""
+    import json
+    import re
+
+    res = _run(CHECKPOINT, [str(tmp_path / "ckpt")])
+    lines = re.findall(r"RESULT (\{.*?\})\n", res.stdout)
+    assert len(lines) == 2, res.stdout[-2000:] + res.stderr[-3000:]
+    for l in lines:
+        r = json.loads(l)
+        assert r["ok"] and r["spec"] and r["step"] == 7, r
+        assert r["files"] == ["meta.json", "tensors.npz"], r
+        assert r["keys"] == ["lora.q.A", "lora.q.B", "opt_m.q.A", "opt_m.q.B", "opt_v.q.A", "opt_v.q.B"], r
 
 
 @pytest.mark.parametrize("mode", ["dp", "tp"])

@@ -52,13 +52,35 @@ def test_fused_gemm_all_reduce_matches_nccl(nvls):
         assert r["max_err"] < 2e-2 and not r["errs"], r
 
 
-@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def _need(n):
+    return pytest.mark.skipif(_ngpu() < n, reason=f"needs {n} GPUs")
+
+
+@pytest.mark.parametrize("n", [pytest.param(2, marks=_need(2)), pytest.param(4, marks=_need(4)),
+                               pytest.param(8, marks=_need(8))])
 @pytest.mark.parametrize("comm", ["native", "nccl"])
-def test_sharded_transformer_step_matches_unsharded(comm):
-    res, rs = _run("transformer", 2, env={"NABLA_B200_COMM": comm})
-    assert len(rs) == 2, res.stdout[-2000:] + res.stderr[-3000:]
+def test_sharded_transformer_step_matches_unsharded(comm, n):
+    """dp x tp (+ sequence parallel) transformer step against the unsharded one; 8 ranks run the mesh
+    of record, ('dp', 'tp') = (2, 4). Each rank is its own process; every device wait is bounded."""
+    res, rs = _run("transformer", n, env={"NABLA_B200_COMM": comm})
+    assert len(rs) == n, res.stdout[-2000:] + res.stderr[-3000:]
     for r in rs:
         assert abs(r["loss0"] - r["loss1"]) / r["loss0"] < 2e-2 and r["grad_rel_err"] < 0.1, r
+        if n == 8:
+            assert r["mesh"] == [2, 4]
+
+
+@pytest.mark.parametrize("n", [pytest.param(4, marks=_need(4)), pytest.param(8, marks=_need(8))])
+@pytest.mark.parametrize("nvls", ["1", "0"])
+def test_grouped_collectives_and_fused_gemms_on_dp_tp_mesh(nvls, n):
+    """All-reduce / all-gather / reduce-scatter and the three fused GEMM + collective kernels on the
+    tp groups and the dp groups of a ('dp', 'tp') mesh ((2, 4) on 8 GPUs), with the switch
+    reduction (NVLS) on and off, against NCCL on the same process group."""
+    res, rs = _run("grouped", n, env={"NABLA_B200_NVLS": nvls, "NABLA_B200_SYMM_ARENA_GB": "2"})
+    assert len(rs) == n, res.stdout[-2000:] + res.stderr[-3000:]
+    for r in rs:
+        assert r["max_err"] < 2e-2 and not r["errs"] and r["n_checks"] > 40 and r["canary_ok"], r
+        assert set(r["groups"]) == {"tp", "dp"}
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
