@@ -80,3 +80,16 @@ def capturable_trace(v: bool = True):
 
 def is_capturable_trace() -> bool:
     return _CAPTURABLE.get()
+
+
+_DEBUG_ON = ("1", "true", "TRUE", "True")
+
+
+def debug_stream(name: str) -> bool:
+    """True when the environment switches the debug print stream ``NABLA_DEBUG_<name>`` on. Read at
+    call time, so a test (or a debugging session) can flip it without re-importing anything.
+    Streams (names shared with the reference): OP_CALL (every op call with its operands'
+    shapes), PHYS (physical-shape decisions of reductions and shape inference), PHYS_VJP
+    (operands of reduction VJPs), COT_FLOW / COT_ACCUM (cotangents as the backward sweep creates,
+    adds, or fails to add them), NESTED_JVP (tangent attachment in forward mode)."""
+    return os.environ.get("NABLA_DEBUG_" + name, "0") in _DEBUG_ON

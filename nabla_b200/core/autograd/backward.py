@@ -86,11 +86,31 @@ class BackwardEngine:
             if c is not None:
                 self._accumulate(o, c if isinstance(c, Tensor) else Tensor.constant(c))
 
-    def _accumulate(self, impl: TensorImpl, g: Tensor) -> None:
+    def _accumulate(self, impl: TensorImpl, g: Tensor, op_name: str = "seed") -> None:
+        from ... import config
+
         k = id(impl)
         self.keep[k] = impl
         cur = self.cot.get(k)
-        self.cot[k] = g if cur is None else cur + g
+        if config.debug_stream("COT_FLOW"):
+            what = "init" if cur is None else "add"
+            extra = "" if cur is None else (f"existing_shape={tuple(cur._impl.global_shape)} "
+                                            f"existing_batch_dims={cur._impl.batch_dims} existing_phys={tuple(cur._impl._shape)} ")
+            print(f"[NABLA_DEBUG_COT_FLOW] {what} op={op_name} target_shape={tuple(impl.global_shape)} "
+                  f"target_batch_dims={impl.batch_dims} target_phys={tuple(impl._shape)} {extra}"
+                  f"cot_shape={tuple(g._impl.global_shape)} cot_batch_dims={g._impl.batch_dims} cot_phys={tuple(g._impl._shape)}")
+        if cur is None:
+            self.cot[k] = g
+            return
+        try:
+            self.cot[k] = cur + g
+        except Exception:
+            if config.debug_stream("COT_ACCUM"):
+                print(f"[NABLA_DEBUG_COT_ACCUM] add failed: target shape={tuple(impl.global_shape)} "
+                      f"batch_dims={impl.batch_dims} phys={tuple(impl._shape)} | existing shape={tuple(cur._impl.global_shape)} "
+                      f"batch_dims={cur._impl.batch_dims} phys={tuple(cur._impl._shape)} | incoming "
+                      f"shape={tuple(g._impl.global_shape)} batch_dims={g._impl.batch_dims} phys={tuple(g._impl._shape)}")
+            raise
 
     def run(self) -> dict[int, Tensor]:
         if self.create_graph:
@@ -118,9 +138,9 @@ class BackwardEngine:
                 raise NotImplementedError(f"backward through '{node.op.name}': {e}") from e
             if not isinstance(in_cots, (tuple, list)):
                 in_cots = (in_cots,)
-            self._scatter(primals, tuple(in_cots))
+            self._scatter(primals, tuple(in_cots), node.op.name)
 
-    def _scatter(self, primals: tuple, in_cots: tuple) -> None:
+    def _scatter(self, primals: tuple, in_cots: tuple, op_name: str = "?") -> None:
         for p, g in zip(primals, in_cots):
             if g is None:
                 continue
@@ -131,11 +151,11 @@ class BackwardEngine:
                     continue
                 if not p.dtype.is_float():
                     continue
-                self._accumulate(p._impl, _reduce_to_shape(g, p))
+                self._accumulate(p._impl, _reduce_to_shape(g, p), op_name)
             elif isinstance(p, (list, tuple)) and isinstance(g, (list, tuple)):
-                self._scatter(tuple(p), tuple(g))
+                self._scatter(tuple(p), tuple(g), op_name)
             elif isinstance(p, dict) and isinstance(g, dict):
-                self._scatter(tuple(p[k] for k in sorted(p)), tuple(g.get(k) for k in sorted(p)))
+                self._scatter(tuple(p[k] for k in sorted(p)), tuple(g.get(k) for k in sorted(p)), op_name)
 
     def finalize(self, wrt: list[TensorImpl]) -> dict[int, Tensor]:
         """Gradients for the requested inputs, laid out like the inputs."""

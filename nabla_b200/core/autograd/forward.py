@@ -7,6 +7,8 @@ An op without a JVP rule, or one that returns ``None``, contributes a zero tange
 """
 from __future__ import annotations
 
+from ... import config as _config
+
 from typing import Any
 
 from ..common import pytree
@@ -75,6 +77,8 @@ class ForwardEngine:
                         from ...ops.view import broadcast_to
 
                         t = broadcast_to(t, tuple(o.global_shape))
+                    if _config.debug_stream("NESTED_JVP"):
+                        print("[NABLA_DEBUG_NESTED_JVP]", node.op.name, "tangent_has_parent=", t._impl.output_refs is not None)
                     self.tan[id(o)] = t
 
     def output_tangents(self) -> list[Tensor | None]:

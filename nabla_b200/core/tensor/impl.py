@@ -117,6 +117,80 @@ class TensorImpl:
     def primary_buffer(self) -> torch.Tensor | None:
         return self._buffers[0] if self._buffers else None
 
+    # ---- graph introspection (reference: nabla/core/tensor/impl.py:157-187, 233-326)
+    @property
+    def op(self):
+        """The operation whose call produced this tensor (None for leaves)."""
+        return self.output_refs.op if self.output_refs is not None else None
+
+    @property
+    def op_kwargs(self) -> dict | None:
+        return self.output_refs.op_kwargs if self.output_refs is not None else None
+
+    @property
+    def op_name(self) -> str | None:
+        return self.output_refs.op.name if self.output_refs is not None else None
+
+    @property
+    def parents(self) -> list["TensorImpl"]:
+        """Tensor arguments of the producing op call, in argument order ([] for leaves)."""
+        return list(self.output_refs.input_impls()) if self.output_refs is not None else []
+
+    @property
+    def is_leaf(self) -> bool:
+        """True when no recorded op produced this tensor (inputs, constants, detached results)."""
+        return self.output_refs is None
+
+    @property
+    def ndim(self) -> int:
+        return len(self._shape) - self.batch_dims
+
+    @property
+    def physical_shape(self) -> tuple[int, ...]:
+        """Shape of the first locally held shard, batch dims included."""
+        return self.physical_local_shape(0)
+
+    @property
+    def local_shape(self) -> tuple[int, ...]:
+        return self.physical_local_shape(0)
+
+    @property
+    def logical_shape(self) -> tuple[int, ...]:
+        """Shape of the first locally held shard without the batch dims."""
+        return self.logical_local_shape(0)
+
+    def physical_local_shape_ints(self, shard_idx: int = 0) -> tuple[int, ...]:
+        return tuple(int(d) for d in self.physical_local_shape(shard_idx))
+
+    @property
+    def physical_global_shape_ints(self) -> tuple[int, ...]:
+        return tuple(int(d) for d in self._shape)
+
+    @property
+    def global_shape_ints(self) -> tuple[int, ...]:
+        return tuple(int(d) for d in self._shape[self.batch_dims:])
+
+    def get_unrealized_shape(self) -> tuple[int, ...]:
+        return self.global_shape
+
+    def get_unrealized_dtype(self) -> DType:
+        return self._dtype
+
+    def get_realized_shape(self) -> tuple[int, ...]:
+        if self._buffers is None:
+            raise RuntimeError("tensor is not realized")
+        return self.global_shape
+
+    def get_realized_dtype(self) -> DType:
+        if self._buffers is None:
+            raise RuntimeError("tensor is not realized")
+        return self._dtype
+
+    @property
+    def primary_value(self) -> torch.Tensor | None:
+        """The first local buffer (the reference returns its driver buffer / graph value here)."""
+        return self.primary_buffer()
+
     # ---- formatting: f32[8,4](<dp, *> | partial={'tp'})(local=[4,4])
     @staticmethod
     def _fmt_shape(shape, batch_dims: int) -> str:

@@ -710,6 +710,32 @@ __global__ void __launch_bounds__(256) nf4_dequant_kernel(const uint8_t* __restr
   }
 }
 
+// One code per byte (the layout of the QLoRA weight dict: `indices` uint8 [padded_numel], `scales`
+// fp32 per block) and the 16-entry codebook passed by the caller. 16 codes per thread: one 16-byte
+// load of codes, the block scale read once per run of codes in the same block.
+template <typename T>
+__global__ void __launch_bounds__(256) nf4_dequant_codes_kernel(const uint8_t* __restrict__ codes,
+                                                               const float* __restrict__ absmax,
+                                                               const float* __restrict__ codebook, T* __restrict__ out,
+                                                               size_t n, int block) {
+  __shared__ float cb[16];
+  if (threadIdx.x < 16) cb[threadIdx.x] = codebook[threadIdx.x];
+  __syncthreads();
+  const size_t stride = (size_t)gridDim.x * blockDim.x * 16;
+  for (size_t i0 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 16; i0 < n; i0 += stride) {
+    uint8_t c[16];
+    if (i0 + 16 <= n && (reinterpret_cast<uintptr_t>(codes + i0) & 15) == 0) {
+      *reinterpret_cast<uint4*>(c) = *reinterpret_cast<const uint4*>(codes + i0);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) c[j] = i0 + j < n ? codes[i0 + j] : 0;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      if (i0 + j < n) out[i0 + j] = from_f<T>(cb[c[j] & 15] * absmax[(i0 + j) / block]);
+  }
+}
+
 // ============================================================== pooling (NHWC)
 // mode 0 avg, 1 max. Backward: avg spreads dy/(kh*kw); max routes to the first arg-max.
 template <typename T>
@@ -796,6 +822,45 @@ __global__ void __launch_bounds__(128) conv2d_direct_kernel(const T* __restrict_
       }
     }
     y[i] = from_f<T>(acc);
+  }
+}
+
+// Filter gradient of the direct convolution (small channel counts, fp32 or bf16):
+//   dw[r,s,c,f] = sum_{n,oh,ow} x[n, oh*sh - pt + r, ow*sw - pl + s, c] * dy[n,oh,ow,f]
+// One block per (r, s, c) and tile of 32 output channels. Lane = output channel (coalesced reads
+// of dy, one broadcast read of x per position), the 8 warps split the N*OH*OW positions and are
+// summed through shared memory: plain stores, no atomics, deterministic.
+template <typename T>
+__global__ void __launch_bounds__(256) conv2d_wgrad_direct_kernel(const T* __restrict__ x, const T* __restrict__ dy,
+                                                                 T* __restrict__ dw, int N, int H, int W, int C, int R,
+                                                                 int S, int F, int OH, int OW, int sh, int sw, int pt,
+                                                                 int pl) {
+  __shared__ float part[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int f = blockIdx.y * 32 + lane;
+  int rsc = blockIdx.x;
+  const int c = rsc % C; rsc /= C;
+  const int s = rsc % S;
+  const int r = rsc / S;
+  const long long positions = (long long)N * OH * OW;
+  float acc = 0.f;
+  for (long long p = warp; p < positions; p += 8) {
+    const int ow = (int)(p % OW);
+    long long q = p / OW;
+    const int oh = (int)(q % OH);
+    const int n = (int)(q / OH);
+    const int ih = oh * sh - pt + r, iw = ow * sw - pl + s;
+    if (ih < 0 || ih >= H || iw < 0 || iw >= W) continue;
+    const float xv = to_f<T>(x[(((size_t)n * H + ih) * W + iw) * C + c]);
+    if (f < F) acc += xv * to_f<T>(dy[(size_t)p * F + f]);
+  }
+  part[warp][lane] = acc;
+  __syncthreads();
+  if (warp == 0 && f < F) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += part[i][lane];
+    dw[((size_t)(r * S + s) * C + c) * F + f] = from_f<T>(t);
   }
 }
 
@@ -1031,6 +1096,15 @@ int nb_nf4_dequant(const unsigned char* packed, const float* absmax, void* out, 
   return CHECK_LAUNCH();
 }
 
+int nb_nf4_dequant_codes(const unsigned char* codes, const float* absmax, const float* codebook, void* out, long long n,
+                         int block, int dtype, void* stream) {
+  if (n <= 0) return 0;
+  const int grid = grid_for((size_t)(n + 15) / 16, 256);
+  if (dtype) nf4_dequant_codes_kernel<bf16><<<grid, 256, 0, STREAM>>>(codes, absmax, codebook, (bf16*)out, (size_t)n, block);
+  else nf4_dequant_codes_kernel<float><<<grid, 256, 0, STREAM>>>(codes, absmax, codebook, (float*)out, (size_t)n, block);
+  return CHECK_LAUNCH();
+}
+
 int nb_pool2d_fwd(const void* x, void* y, int N, int H, int W, int C, int OH, int OW, int kh, int kw, int sh, int sw,
                   int ph, int pw, int mode, int dtype, void* stream) {
   const size_t total = (size_t)N * OH * OW * C;
@@ -1058,6 +1132,15 @@ int nb_conv2d_direct(const void* x, const void* w, const void* bias, void* y, in
   const int grid = grid_for(total, 128, 148 * 32);
   if (dtype) conv2d_direct_kernel<bf16><<<grid, 128, 0, STREAM>>>((const bf16*)x, (const bf16*)w, (const bf16*)bias, (bf16*)y, N, H, W, C, R, S, F, OH, OW, sh, sw, pt, pl);
   else conv2d_direct_kernel<float><<<grid, 128, 0, STREAM>>>((const float*)x, (const float*)w, (const float*)bias, (float*)y, N, H, W, C, R, S, F, OH, OW, sh, sw, pt, pl);
+  return CHECK_LAUNCH();
+}
+
+int nb_conv2d_wgrad_direct(const void* x, const void* dy, void* dw, int N, int H, int W, int C, int R, int S, int F,
+                           int OH, int OW, int sh, int sw, int pt, int pl, int dtype, void* stream) {
+  if ((size_t)R * S * C * F == 0) return 0;
+  const dim3 grid(R * S * C, (F + 31) / 32);
+  if (dtype) conv2d_wgrad_direct_kernel<bf16><<<grid, 256, 0, STREAM>>>((const bf16*)x, (const bf16*)dy, (bf16*)dw, N, H, W, C, R, S, F, OH, OW, sh, sw, pt, pl);
+  else conv2d_wgrad_direct_kernel<float><<<grid, 256, 0, STREAM>>>((const float*)x, (const float*)dy, (float*)dw, N, H, W, C, R, S, F, OH, OW, sh, sw, pt, pl);
   return CHECK_LAUNCH();
 }
 

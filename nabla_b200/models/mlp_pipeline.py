@@ -19,7 +19,8 @@ from ..ops.communication import ppermute, shard
 from ..ops.control_flow import where
 from ..ops.creation import constant, zeros
 from ..ops.reduction import mean, reduce_sum
-from ..ops.unary import relu
+from ..ops.unary import cast, relu
+from ..types import DType
 from ..ops.view import broadcast_to, reshape, stack, unsqueeze
 from ..transforms.vmap import vmap
 
@@ -96,6 +97,42 @@ def zeros_like_state(t: Tensor) -> Tensor:
 
 def gpipe_loss(w, b, xs: Tensor, ys: Tensor, mesh, stage_axis: str = "stage",
                dp_axis: str | None = None) -> Tensor:
-    out = gpipe_forward(w, b, xs, mesh, stage_axis, dp_axis)
-    d = out - ys
-    return mean(d * d)
+    """Mean squared error of the pipe's outputs against ``ys`` (micro_batches, batch, dim).
+
+    The outputs never leave the last stage: every tick the last stage's rows are compared with
+    their targets in place (a stage mask zeroes the other stages' rows) and the squared error is
+    accumulated per stage; ONE reduction over the stage (and replica) axes at the very end gives the
+    loss. The only communication of a tick is the ``ppermute`` shift, where the reference recipe
+    (examples/07_mlp_pipeline_parallel.ipynb) sums a masked (S, batch, dim) tensor over the stage
+    axis every tick."""
+    S = mesh.get_axis_size(stage_axis)
+    MB, B, D = (int(d) for d in xs.shape)
+    two = isinstance(w, (tuple, list))
+    if two:
+        step2 = vmap(_stage_fn2, in_axes=(0, 0, 0, 0, 0), spmd_axis_name=stage_axis, mesh=mesh)
+        step = lambda x_, w_, b_: step2(x_, w[0], unsqueeze(b[0], axis=1), w[1], unsqueeze(b[1], axis=1))
+    else:
+        step = vmap(_stage_fn, in_axes=(0, 0, 0), spmd_axis_name=stage_axis, mesh=mesh)
+    state_spec = (stage_axis, dp_axis, None)
+    state = shard(zeros((S, B, D), dtype=xs.dtype, device=xs.device), mesh, state_spec)
+    first = _stage_mask(S, 0, xs, mesh, stage_axis)
+    last = _stage_mask(S, S - 1, xs, mesh, stage_axis)
+    perm = _perm(mesh, stage_axis)
+    zero_x = zeros((B, D), dtype=xs.dtype, device=xs.device)
+    zero_s = None
+    acc = None
+    for t in range(MB + S - 1):
+        fresh = xs[t] if t < MB else zero_x
+        fresh = shard(broadcast_to(unsqueeze(fresh, axis=0), (S, B, D)), mesh, state_spec)
+        inp = where(first, fresh, state)
+        computed = step(inp, w, None if two else unsqueeze(b, axis=1))
+        if t >= S - 1:
+            target = shard(broadcast_to(unsqueeze(ys[t - (S - 1)], axis=0), (S, B, D)), mesh, state_spec)
+            if zero_s is None:
+                zero_s = zeros_like_state(computed)
+            d = where(last, computed - target, zero_s)
+            e = cast(reduce_sum(reduce_sum(d * d, axis=2), axis=1), DType.float32)   # (S,), one value per stage
+            acc = e if acc is None else acc + e
+        if t + 1 < MB + S - 1:
+            state = ppermute(computed, perm)
+    return reduce_sum(acc, axis=0) * (1.0 / float(MB * B * D))

@@ -40,9 +40,11 @@ def _L():
             "nb_rng_dev": [c_vp, c_ll, c_vp, c_ull, c_int, c_f, c_f, c_int, c_vp],
             "nb_dropout_dev": [c_vp] * 3 + [c_ll, c_f, c_vp, c_ull, c_int, c_vp],
             "nb_nf4_dequant": [c_vp] * 3 + [c_ll, c_int, c_int, c_vp],
+            "nb_nf4_dequant_codes": [c_vp] * 4 + [c_ll, c_int, c_int, c_vp],
             "nb_pool2d_fwd": [c_vp, c_vp] + [c_int] * 14 + [c_vp],
             "nb_pool2d_bwd": [c_vp] * 3 + [c_int] * 14 + [c_vp],
             "nb_conv2d_direct": [c_vp] * 4 + [c_int] * 14 + [c_vp],
+            "nb_conv2d_wgrad_direct": [c_vp] * 3 + [c_int] * 14 + [c_vp],
         }
         for name, args in sig.items():
             fn = getattr(lib, name)
@@ -346,3 +348,28 @@ def conv2d_direct(x, w, bias, stride, padding):
     _ok(_L().nb_conv2d_direct(ptr(x), ptr(w), ptr(b), ptr(y), N, H, W, C, R, S, F, OH, OW, stride[0], stride[1], pt, pl,
                               _dt(x), stream_ptr()), "conv2d_direct")
     return y
+
+
+def conv2d_wgrad_direct(x, dy, w_shape, stride, padding):
+    """Filter gradient of the NHWC x RSCF convolution: ``dw[r,s,c,f] = sum x[...] * dy[...]`` over
+    the batch and all output pixels (deterministic, no atomics)."""
+    x = x.contiguous()
+    dy = dy.contiguous().to(x.dtype)
+    N, H, W, C = x.shape
+    R, S, _, F = w_shape
+    OH, OW = dy.shape[1], dy.shape[2]
+    dw = torch.empty((R, S, C, F), dtype=x.dtype, device=x.device)
+    _ok(_L().nb_conv2d_wgrad_direct(ptr(x), ptr(dy), ptr(dw), N, H, W, C, R, S, F, OH, OW, stride[0], stride[1],
+                                    padding[0], padding[2], _dt(x), stream_ptr()), "conv2d_wgrad_direct")
+    return dw
+
+
+def nf4_dequant_codes(codes: torch.Tensor, absmax: torch.Tensor, codebook: torch.Tensor, n: int, block: int,
+                      dtype: torch.dtype) -> torch.Tensor:
+    """``out[i] = codebook[codes[i]] * absmax[i // block]`` for one-code-per-byte NF4 weights, in one
+    kernel; ``dtype`` fp32 or bf16."""
+    out = torch.empty(n, dtype=dtype, device=codes.device)
+    _ok(_L().nb_nf4_dequant_codes(ptr(codes.contiguous()), ptr(absmax.contiguous().float()),
+                                  ptr(codebook.contiguous().float()), ptr(out), n, block, _dt(out), stream_ptr()),
+        "nf4_dequant_codes")
+    return out

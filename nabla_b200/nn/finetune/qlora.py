@@ -47,12 +47,32 @@ def quantize_nf4(weight: Tensor, block_size: int = 64) -> dict[str, Any]:
             "original_shape": shape, "original_numel": n, "padded_numel": int(flat.size), "block_size": int(block_size)}
 
 
+_CODEBOOKS: dict = {}      # device -> the 16 codes as an fp32 device tensor
+
+
+def _codebook_on(device: torch.device) -> torch.Tensor:
+    t = _CODEBOOKS.get(device)
+    if t is None:
+        t = torch.tensor(NF4_CODEBOOK, dtype=torch.float32, device=device)
+        _CODEBOOKS[device] = t
+    return t
+
+
 class DequantizeNF4Op(Operation):
-    """codebook[indices] * scale_of_block -> dense weight (one kernel on GPU)."""
+    """``codebook[indices] * scale_of_block`` -> dense weight. On a GPU this is ONE launch of
+    ``nf4_dequant_codes_kernel`` (fp32 or bf16 output); elsewhere torch indexing."""
 
     def kernel(self, indices, scales, *, shape, numel: int, block_size: int, dtype: DType):
         td = dtype.to_torch()
-        code = torch.tensor(NF4_CODEBOOK, dtype=torch.float32, device=indices.device)
+        if indices.is_cuda and td in (torch.float32, torch.bfloat16) and indices.dtype == torch.uint8 and numel > 0:
+            from ... import native
+
+            if native.use_native(indices):
+                from ...native import kernels
+
+                return kernels.nf4_dequant_codes(indices.reshape(-1), scales.reshape(-1), _codebook_on(indices.device),
+                                                 int(numel), int(block_size), td).reshape(shape)
+        code = _codebook_on(indices.device) if indices.device.type != "meta" else torch.empty(16, device="meta")
         vals = code[indices.long()].reshape(-1, block_size) * scales.float().reshape(-1, 1)
         return vals.reshape(-1)[:numel].reshape(shape).to(td)
 

@@ -220,7 +220,15 @@ class Operation:
             arg_leaves, treedef = pytree.tree_flatten(args)
             tensors = [a for a in arg_leaves if isinstance(a, Tensor)]
         metas = [(t._impl._shape, t._impl.dtype.to_torch()) for t in tensors]
+        if config.debug_stream("OP_CALL"):
+            desc = "; ".join(f"arg{i}:shape={tuple(t._impl.global_shape)},batch_dims={t._impl.batch_dims},"
+                             f"physical={tuple(t._impl._shape)}" for i, t in enumerate(tensors))
+            print(f"[NABLA_DEBUG_OP_CALL] op={self.name} max_batch_dims={batch_dims} any_traced={traced} "
+                  f"any_sharded={mesh is not None} kwargs={kwargs} adapted_kwargs={phys_kwargs} args=[{desc}]")
         out_meta, out_td = self.infer_outputs(metas, arg_leaves, treedef, phys_kwargs)
+        if config.debug_stream("PHYS"):
+            print(f"[NABLA_DEBUG_PHYS] {self.name}.infer_outputs: in={[m[0] for m in metas]} kwargs={phys_kwargs} "
+                  f"out={[m[0] for m in out_meta]}")
         if mesh is not None:
             out_specs = out_specs_fn([m[0] for m in out_meta])
 

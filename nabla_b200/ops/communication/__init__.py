@@ -1,3 +1,32 @@
+"""Communication ops. Functions (``all_reduce``, ``shard``, ...) are the public API; the ``*_op``
+names are the op objects behind them, for code that inspects or extends ops
+(reference: nabla/ops/communication/__init__.py)."""
+from ..base import CollectiveOperation
 from .collectives import (accelerator, all_gather, all_reduce, all_to_all, axis_index, broadcast, cpu,
                           distributed_broadcast, gather_all_axes, gpu, pmean, ppermute, reduce_scatter, reshard,
                           reshard_tensor, reshard_to_spec, relabel_spec, shard, to_device, transfer_to)
+from .collectives import (_all_gather_op as all_gather_op, _all_reduce_op as all_reduce_op,
+                          _gather_all_op as gather_all_axes_op, _ppermute_op as ppermute_op,
+                          _reduce_scatter_op as reduce_scatter_op, _shard_op as shard_op)
+
+
+class _ComposedOp:
+    """Callable stand-in with a ``name`` for collectives that this framework builds from other ops
+    (a re-layout, or all-reduce + scale) instead of a dedicated op class."""
+
+    def __init__(self, name: str, fn):
+        self.name = name
+        self._fn = fn
+        self.__doc__ = fn.__doc__
+
+    def __call__(self, *args, **kwargs):
+        return self._fn(*args, **kwargs)
+
+    def __repr__(self) -> str:
+        return f"<composed op {self.name}>"
+
+
+pmean_op = _ComposedOp("pmean", pmean)
+all_to_all_op = _ComposedOp("all_to_all", all_to_all)
+distributed_broadcast_op = _ComposedOp("distributed_broadcast", distributed_broadcast)
+axis_index_op = _ComposedOp("axis_index", axis_index)

@@ -2,10 +2,19 @@
 
 ``conv2d``: NHWC input, HWIO (R,S,C,F) filter, stride, 4-way padding (top, bottom, left,
 right); dilation 1 and groups 1 only (as in the reference). ``conv2d_transpose``: filter
-(K_h, K_w, C_out, C_in), no output padding. On GPU the forward runs as im2col + the tcgen05
-GEMM for wide channels (C*R*S >= 64, bf16) or a direct kernel for narrow ones; gradients are
-convolutions again (dgrad = transposed conv, wgrad = correlation of input with cotangent).
-Leading vmap batch dims are folded into N.
+(K_h, K_w, C_out, C_in), no output padding. Leading vmap batch dims are folded into N.
+
+On GPU every piece runs on this package's kernels (no cuDNN call):
+  * forward: im2col + the tcgen05 GEMM for wide bf16 channels (C*R*S >= 64), a direct kernel
+    for narrow ones or fp32;
+  * input gradient: a convolution again - the cotangent, zero-dilated by the stride and padded to
+    "full", correlated with the spatially flipped, channel-transposed filter - so it goes through
+    the same forward paths (reference: nabla/ops/convolution.py:309-353);
+  * filter gradient: im2col(x)^T @ dy on the tcgen05 GEMM (fp32 output) for wide bf16 channels,
+    otherwise the direct reduction kernel ``conv2d_wgrad_direct`` (reference: :354-392);
+  * ``conv2d_transpose``: the input-gradient computation with the roles of data and cotangent
+    swapped (reference: :429-466).
+On CPU the same ops use torch's convolution functions.
 """
 from __future__ import annotations
 
@@ -69,10 +78,65 @@ def _conv_fwd(x, w, bias, stride, padding):
     return y.reshape(*lead, *y.shape[1:])
 
 
+def _own_kernels(t: torch.Tensor) -> bool:
+    from .. import native
+
+    return t.numel() > 0 and native.use_native(t) and t.dtype in (torch.bfloat16, torch.float32)
+
+
+def _dgrad_as_conv(dy4: torch.Tensor, w: torch.Tensor, out_hw, stride, padding) -> torch.Tensor:
+    """Input gradient of ``conv2d(x, w)`` for cotangent ``dy4`` (N, OH, OW, F), filter (R, S, C, F),
+    as a stride-1 convolution over the zero-dilated cotangent; result (N, H, W, C)."""
+    pt, pb, pl, pr = padding
+    H, W = out_hw
+    R, S, C, F = w.shape
+    N, OH, OW, _ = dy4.shape
+    sh, sw = stride
+    hz, wz = (OH - 1) * sh + 1, (OW - 1) * sw + 1
+    if sh > 1 or sw > 1:
+        z = torch.zeros((N, hz, wz, F), dtype=dy4.dtype, device=dy4.device)
+        z[:, ::sh, ::sw] = dy4
+    else:
+        z = dy4
+    # out[o] = sum_r' zpad[o + r'] wf[r'] with wf the flipped filter; o = 0 must be input row 0
+    top, left = R - 1 - pt, S - 1 - pl
+    bottom, right = H + R - 1 - top - hz, W + S - 1 - left - wz
+    if min(top, left, bottom, right) < 0:          # padding larger than the filter reach: crop instead
+        z = z[:, max(0, -top): hz - max(0, -bottom), max(0, -left): wz - max(0, -right)]
+        top, left, bottom, right = max(0, top), max(0, left), max(0, bottom), max(0, right)
+    wf = w.flip(0, 1).permute(0, 1, 3, 2).contiguous()      # (R, S, F, C): in-channels F, out-channels C
+    return _conv_fwd(z, wf, None, (1, 1), (top, bottom, left, right))
+
+
+def _wgrad_own(x4: torch.Tensor, dy4: torch.Tensor, w_shape, stride, padding) -> torch.Tensor:
+    from .. import native
+    from ..native import kernels
+
+    pt, pb, pl, pr = padding
+    R, S, C, F = w_shape
+    if x4.dtype == torch.bfloat16 and (C * R * S) % 8 == 0 and C * R * S >= 64 and F % 8 == 0:
+        xp = TF.pad(x4, (0, 0, pl, pr, pt, pb))
+        N = xp.shape[0]
+        OH, OW = dy4.shape[1], dy4.shape[2]
+        cols = xp.unfold(1, R, stride[0]).unfold(2, S, stride[1])[:, :OH, :OW]       # N,OH,OW,C,R,S
+        cols = cols.permute(0, 1, 2, 4, 5, 3).reshape(N * OH * OW, R * S * C)
+        dw = native.gemm_bf16(cols.t(), dy4.reshape(N * OH * OW, F).contiguous(), out_dtype=torch.float32)
+        return dw.reshape(R, S, C, F).to(x4.dtype)
+    return kernels.conv2d_wgrad_direct(x4, dy4, w_shape, stride, padding)
+
+
 def _conv_transpose_fwd(x, w, bias, stride, padding):
     """x (N,H,W,Cin), w (R,S,Cout,Cin) -> (N, (H-1)*s+R - pt - pb, ..., Cout)."""
     x4, lead = _fold(x)
     pt, pb, pl, pr = padding
+    if _own_kernels(x4):
+        R, S = w.shape[0], w.shape[1]
+        oh = (x4.shape[1] - 1) * stride[0] + R - pt - pb
+        ow = (x4.shape[2] - 1) * stride[1] + S - pl - pr
+        y = _dgrad_as_conv(x4, w.to(x4.dtype), (oh, ow), stride, padding)
+        if bias is not None:
+            y = y + bias.to(y.dtype)
+        return y.reshape(*lead, *y.shape[1:])
     y = TF.conv_transpose2d(x4.permute(0, 3, 1, 2), w.permute(3, 2, 0, 1).to(x4.dtype), stride=stride)
     y = y.permute(0, 2, 3, 1)
     H, W = y.shape[1], y.shape[2]
@@ -128,6 +192,8 @@ class ConvDgradOp(Operation):
         dy4, lead = _fold(dy)
         pt, pb, pl, pr = padding
         H, W, C = x_shape
+        if _own_kernels(dy4):
+            return _dgrad_as_conv(dy4, w.to(dy4.dtype), (H, W), stride, padding).reshape(*lead, H, W, C)
         g = torch.nn.grad.conv2d_input((dy4.shape[0], C, H + pt + pb, W + pl + pr), w.permute(3, 2, 0, 1).to(dy4.dtype),
                                        dy4.permute(0, 3, 1, 2), stride=stride)
         g = g[:, :, pt:pt + H, pl:pl + W].permute(0, 2, 3, 1).contiguous()
@@ -157,6 +223,8 @@ class ConvWgradOp(Operation):
         dy4, _ = _fold(dy)
         pt, pb, pl, pr = padding
         R, S, C, F = w_shape
+        if _own_kernels(x4):
+            return _wgrad_own(x4, dy4, tuple(w_shape), stride, padding)
         xp = TF.pad(x4.permute(0, 3, 1, 2), (pl, pr, pt, pb))
         g = torch.nn.grad.conv2d_weight(xp.float(), (F, C, R, S), dy4.permute(0, 3, 1, 2).float(), stride=stride)
         return g.permute(2, 3, 1, 0).contiguous().to(x.dtype)

@@ -29,9 +29,14 @@ class ReduceSumOp(ReduceOperation):
         return torch.sum(x, dim=axis, keepdim=keepdims)
 
     def vjp_rule(self, primals, cot, outputs, kwargs):
+        from .. import config
         from .view import broadcast_to, unsqueeze
 
         x = primals[0]
+        if config.debug_stream("PHYS_VJP"):
+            for tag, t in (("reduce_sum.vjp primal", x), ("reduce_sum.vjp cotangent", cot)):
+                print(f"[NABLA_DEBUG_PHYS_VJP] {tag}: shape={tuple(t._impl.global_shape)} "
+                      f"batch_dims={t._impl.batch_dims} phys={tuple(t._impl._shape)}")
         if not kwargs.get("keepdims", False):
             cot = unsqueeze(cot, axis=kwargs["axis"])
         return (broadcast_to(cot, tuple(x._impl.global_shape)),)

@@ -212,3 +212,48 @@ def test_complex_views():
     c = nb.as_interleaved_complex(T(x))
     back = nb.view_as_real_interleaved(c)
     close(back, x)
+
+
+# ---------------------------------------------------------------- further transform tiers
+# (reference: tests/unit/test_unified.py:306-381: vmap(jvp), jacrev, jacfwd per op)
+@pytest.mark.parametrize("name,fn,tfn,pos", VMAPPABLE, ids=[u[0] for u in VMAPPABLE])
+def test_unary_vmap_of_jvp(name, fn, tfn, pos):
+    """vmap(jvp(f)) with all-ones tangents against per-example torch forward mode."""
+    xb = rand(3, 4, 6, seed=12, positive=pos)
+
+    def tan_of(x):
+        return nb.jvp(fn, (x,), (nb.ones_like(x),))[1]
+
+    got = nb.vmap(tan_of)(T(xb))
+    ref = torch.stack([torch.autograd.functional.jvp(tfn, (xb[i],), (torch.ones_like(xb[i]),))[1] for i in range(3)])
+    close(got, ref, rtol=1e-4, atol=1e-5, msg=f"{name} vmap(jvp)")
+
+
+JAC_OPS = [u for u in UNARY if u[0] not in ("cast_f64",)]
+
+
+@pytest.mark.parametrize("name,fn,tfn,pos", JAC_OPS, ids=[u[0] for u in JAC_OPS])
+def test_unary_jacrev_and_jacfwd(name, fn, tfn, pos):
+    """Full Jacobians, reverse and forward mode, against torch.autograd.functional.jacobian."""
+    x = rand(4, 6, seed=13, positive=pos)
+    ref = torch.autograd.functional.jacobian(tfn, x)
+    close(nb.jacrev(fn)(T(x)), ref, rtol=1e-4, atol=1e-5, msg=f"{name} jacrev")
+    close(nb.jacfwd(fn)(T(x)), ref, rtol=1e-4, atol=1e-5, msg=f"{name} jacfwd")
+
+
+@pytest.mark.parametrize("name,fn,tfn", [b for b in BINARY if b[0] != "mod"], ids=[b[0] for b in BINARY if b[0] != "mod"])
+def test_binary_vmap_of_jvp_and_jacobians(name, fn, tfn):
+    a, b = rand(3, 4, 6, seed=14), rand(3, 4, 6, seed=15)
+
+    def tan_of(x, y):
+        return nb.jvp(fn, (x, y), (nb.ones_like(x), nb.ones_like(y)))[1]
+
+    got = nb.vmap(tan_of)(T(a), T(b))
+    ref = torch.stack([torch.autograd.functional.jvp(tfn, (a[i], b[i]), (torch.ones_like(a[i]), torch.ones_like(b[i])))[1]
+                       for i in range(3)])
+    close(got, ref, rtol=1e-4, atol=1e-4, msg=f"{name} vmap(jvp)")
+    ja, jb = torch.autograd.functional.jacobian(tfn, (a[0], b[0]))
+    r = nb.jacrev(fn, argnums=(0, 1))(T(a[0]), T(b[0]))
+    f = nb.jacfwd(fn, argnums=(0, 1))(T(a[0]), T(b[0]))
+    for got_j, ref_j in ((r[0], ja), (r[1], jb), (f[0], ja), (f[1], jb)):
+        close(got_j, ref_j, rtol=1e-4, atol=1e-4, msg=f"{name} jacobian")
