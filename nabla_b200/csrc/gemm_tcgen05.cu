@@ -114,11 +114,14 @@ struct CommArgs {
   void* const* abufs;       // device array [world] of arena base pointers (nullptr: pull variant)
   long long a_off;          // byte offset of the gathered A inside the arena
   const char* own_src;      // this rank's own rows, [M / world][K] dense
+  char* a_mc;               // multicast base of the arena (nullptr: one store per peer). With it a
+                            // single multimem.st reaches the gathered A of EVERY rank of the group
+                            // through the switch: the rows leave this GPU once instead of world - 1 times
 };
 
 // Order in which the GEMM walks the M tiles -> the tile's real row block.
 //   RS: consecutive tiles rotate over the owning ranks, so that every rank's reducers get work
-//       from the start;  AG: own rows first, then the peers' in ring order (the copy order).
+//       from the start;  AG: own rows first, then the peers' blocks in the order they arrive.
 template <int MODE>
 __device__ __forceinline__ int remap_m(int tm, const CommArgs& c) {
   if (MODE == MODE_RS) {
@@ -127,7 +130,17 @@ __device__ __forceinline__ int remap_m(int tm, const CommArgs& c) {
     return (g * c.world + p) * c.mpc + j;
   }
   if (MODE == MODE_AG) {
-    const int dist = tm / c.per, rem = tm - dist * c.per;
+    // own rows first; then the peers' blocks in ARRIVAL order. Every rank sends its block v to all
+    // peers at the same time, so the blocks with the same index v of all peers land together: the
+    // walk takes block 0 of peer +1, +2, ..., then block 1 of each, and so on. (Walking one peer's
+    // rows to the end before the next peer's would wait for the end of the whole exchange after the
+    // first quarter of the work.)
+    int dist = 0, rem = tm;
+    if (tm >= c.per) {
+      const int t2 = tm - c.per, nw = c.world - 1;
+      rem = t2 / nw;
+      dist = 1 + (t2 - rem * nw);
+    }
     const int g = rem / c.mpc, j = rem - g * c.mpc;
     int p = c.rank + dist;
     if (p >= c.world) p -= c.world;
@@ -906,14 +919,26 @@ __device__ __forceinline__ void push_jobs(const GemmArgs& args, const CommArgs& 
         const long long idx = base + u * NUM_THREADS + threadIdx.x;
         if (idx < nvec) val[u] = src[idx];
       }
-      for (int d = 1; d < comm.world; ++d) {               // the peers in ring order (the own copy is the caller's)
-        int q = comm.rank + d;
-        if (q >= comm.world) q -= comm.world;
-        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(comm.abufs[q]) + dst_off);
+      if (comm.a_mc != nullptr) {                          // one store, replicated by the switch (own copy included)
+        char* dst = comm.a_mc + dst_off;
 #pragma unroll
         for (int u = 0; u < PU; ++u) {
           const long long idx = base + u * NUM_THREADS + threadIdx.x;
-          if (idx < nvec) dst[idx] = val[u];
+          if (idx < nvec)
+            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + idx * 16),
+                         "r"(val[u].x), "r"(val[u].y), "r"(val[u].z), "r"(val[u].w)
+                         : "memory");
+        }
+      } else {
+        for (int d = 1; d < comm.world; ++d) {             // the peers in ring order (the own copy is the caller's)
+          int q = comm.rank + d;
+          if (q >= comm.world) q -= comm.world;
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(comm.abufs[q]) + dst_off);
+#pragma unroll
+          for (int u = 0; u < PU; ++u) {
+            const long long idx = base + u * NUM_THREADS + threadIdx.x;
+            if (idx < nvec) dst[idx] = val[u];
+          }
         }
       }
     }
@@ -1192,7 +1217,7 @@ extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* 
                                   int flag_off, int done_off, int M, int N, int K, long long lda, long long ldb,
                                   int a_mn, int b_mn, int bias_fp32, int epi, int aux, int gelu_tanh, int rank,
                                   int world, int chunk_rows, unsigned* ctr, int n_comm_ctas, int* ticket, int* status,
-                                  void* const* arena_bufs, long long a_off, void* stream) {
+                                  void* const* arena_bufs, long long a_off, void* arena_mc, void* stream) {
   using namespace nb;
   constexpr int BN = 256;
   if (mode < MODE_AR || mode > MODE_AG) return -9;
@@ -1253,6 +1278,7 @@ extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* 
   c.unit_bytes = (long long)BLOCK_M * K * 2;
   c.abufs = mode == MODE_AG ? arena_bufs : nullptr;
   c.a_off = a_off;
+  c.a_mc = (mode == MODE_AG && arena_bufs != nullptr) ? reinterpret_cast<char*>(arena_mc) : nullptr;
   c.own_src = reinterpret_cast<const char*>(A);
   if (mode == MODE_AG && arena_bufs != nullptr) c.done_target = 0;   // push: no closing barrier, nothing counted
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

@@ -325,7 +325,7 @@ def _fused_fn():
         fn = lib.nb_gemm_fused_bf16
         fn.restype = c_int
         fn.argtypes = ([c_int] + [c_vp] * 9 + [c_ll, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll] + [c_int] * 9 +
-                       [c_vp, c_int, c_vp, c_vp, c_vp, c_ll, c_vp])
+                       [c_vp, c_int, c_vp, c_vp, c_vp, c_ll, c_vp, c_vp])
         lib.nb_gemm_fused_grid.restype = c_int
         _gemm_fn = (fn, lib.nb_gemm_fused_grid)
     return _gemm_fn
@@ -371,7 +371,7 @@ def _fused_state(ws, device):
 
 
 def _launch_fused(mode, ws, a, b, out, bias, aux_out, a_full, M, N, K, lda, ldb, a_mn, b_mn, epi, aux, gelu_tanh,
-                  chunk_rows, n_comm, arena_ptrs: int = 0, a_off: int = 0):
+                  chunk_rows, n_comm, arena_ptrs: int = 0, a_off: int = 0, arena_mc: int = 0):
     """Returns the byte offset (inside the workspace) of the region the call used."""
     global launch_count
     fn, grid_fn = _fused_fn()
@@ -393,7 +393,7 @@ def _launch_fused(mode, ws, a, b, out, bias, aux_out, a_full, M, N, K, lda, ldb,
             data_off, lib.nb_comm_tile_flag_offset(), lib.nb_comm_done_offset(), M, N, K, lda, ldb, a_mn, b_mn,
             1 if (bias is not None and bias.dtype == torch.float32) else 0, epi, aux, int(gelu_tanh), ws.rank, ws.world,
             chunk_rows, ws.ctr.data_ptr(), n_comm, ws.ticket.data_ptr(), _status().data_ptr(), arena_ptrs, a_off,
-            _stream())
+            arena_mc, _stream())
     if rc != 0:
         raise RuntimeError(f"nb_gemm_fused_bf16(mode={mode}) failed with code {rc} for M={M} N={N} K={K}")
     launch_count += 1
@@ -443,12 +443,12 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_rows
 
         y = gemm_bf16(a.reshape(-1, a.shape[-1]), b)
         M, N = y.shape
-        y = y.view(M // (ws.world * chunk_rows), ws.world, chunk_rows, N)[:, ws.rank].reshape(M // ws.world, N)
+        own = y.view(M // (ws.world * chunk_rows), ws.world, chunk_rows, N)[:, ws.rank]     # strided view, no copy
+        # one pass like the real kernel's fold: own chunk (+ residual) -> contiguous, bias added in place
+        out = torch.add(own, residual.reshape(own.shape)) if residual is not None else own.contiguous()
         if bias is not None:
-            y = y + bias.reshape(-1).to(y.dtype)
-        if residual is not None:
-            y = y + residual.reshape(M // ws.world, N)
-        return y
+            out.add_(bias.reshape(-1).to(out.dtype))
+        return out.reshape(M // ws.world, N)
     a3, b3, lda, ldb, a_mn, b_mn = _operands(a, b)
     M, K, N = a3.shape[1], a3.shape[2], b.shape[1]
     out = torch.empty((M // ws.world, N), dtype=torch.bfloat16, device=a.device)
@@ -493,7 +493,8 @@ def all_gather_gemm(a_shard: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_ro
             a_full = ws.arena.buf[arena_off: arena_off + M * K * 2].view(torch.bfloat16).view(M, K)
         else:
             a_full = torch.empty((M, K), dtype=torch.bfloat16, device=x.device)
-        a_full.view(M // (ws.world * chunk_rows), ws.world, chunk_rows, K)[:] = x.view(-1, 1, chunk_rows, K)
+        # the gathered matrix is left as it is (stale or uninitialised rows): the GEMM reads the same bytes
+        # from the same place as in the real step, and no copy that the real step does not make is added
         if bias is not None and epilogue == "none":
             epilogue = "bias"
         if dact is not None:
@@ -519,21 +520,32 @@ def all_gather_gemm(a_shard: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_ro
         bias = bias.reshape(-1).contiguous()
         if epilogue == "none":
             epilogue = "bias"
-    # this rank's own rows of the gathered matrix (the kernel moves only the peers' rows): a plain
-    # copy on a side stream, issued first so that it runs under the fused kernel (which reads the
-    # own rows from ``x``, not from here); the streams join again right after the launch
+    # With a multicast binding of the arena one multimem.st per 16 bytes reaches the gathered matrix of
+    # every rank (this one included) through the switch: the rows leave the GPU once, not world - 1 times.
+    # Measured: with two ranks the multicast push wins (0.48 ms against 0.63 ms for 32768 x 4096 x 2048);
+    # with four the receiving side is the limit either way and plain peer stores from 16 copy CTAs are
+    # faster (0.43 ms against 0.57 ms for 65536 x 1536 x 2048), so multicast is the default for pairs only.
+    mm = os.environ.get("NABLA_B200_AG_MULTIMEM", "auto")
+    arena_mc = ws.arena.mc_ptr if (push and (mm == "1" or (mm == "auto" and ws.world == 2))) else 0
     cs = chunk_rows
     cur = torch.cuda.current_stream()
     side = _side_stream(x.device)
-    side.wait_stream(cur)
-    with torch.cuda.stream(side):
-        a_full.view(M // (ws.world * cs), ws.world, cs, K)[:, ws.rank].copy_(x.view(-1, cs, K))
+    if not arena_mc:
+        # this rank's own rows of the gathered matrix (the kernel moves only the peers' rows): a plain
+        # copy on a side stream, issued first so that it runs under the fused kernel (which reads the
+        # own rows from ``x``, not from here); the streams join again right after the launch
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            a_full.view(M // (ws.world * cs), ws.world, cs, K)[:, ws.rank].copy_(x.view(-1, cs, K))
     # copy CTAs: an SM moves about 32 GB/s (pull) to 38 GB/s (push); take as many as it needs to move
-    # the peers' rows within the GEMM's own time, up to what saturates the link
+    # its share within the GEMM's own time, up to what saturates the link
     if comm_ctas is None:
         gemm_s = 2.0 * M * N * K / 1.3e15
-        need = (M - Ml) * K * 2 / max(gemm_s, 1e-6) / (38e9 if push else 32e9)
-        comm_ctas = int(min(20, max(4, need + 1.5)))
+        out_bytes = Ml * K * 2 if arena_mc else (M - Ml) * K * 2
+        need = out_bytes / max(gemm_s, 1e-6) / (38e9 if push else 32e9)
+        # measured: below 8 copy CTAs a multicast push does not keep up with the GEMM (0.57 ms with 5,
+        # 0.48 ms with 8 or more for 32768 x 4096 x 2048 on two GPUs, GEMM alone 0.44 ms)
+        comm_ctas = int(min(20, max(8 if arena_mc else 4, need + 1.5)))
     n_comm = comm_ctas
     aux_code, aux_t = (1 if store_preact else 0), pre
     if dact is not None:
@@ -543,8 +555,9 @@ def all_gather_gemm(a_shard: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_ro
         gelu_tanh = act == "gelu_tanh"
     _launch_fused(MODE_AG, ws, x, b3, out, bias, aux_t, a_full, M, N, K, K, ldb, 0, 1 if bkind == "row" else 0,
                   _EPI[epilogue], aux_code, gelu_tanh, chunk_rows, n_comm,
-                  ws.arena.ptrs_dev if push else 0, arena_off or 0)
-    cur.wait_stream(side)
+                  ws.arena.ptrs_dev if push else 0, arena_off or 0, arena_mc)
+    if not arena_mc:
+        cur.wait_stream(side)
     return (a_full, out, pre) if store_preact else (a_full, out)
 
 

@@ -132,7 +132,19 @@ def comm_main(kind: str, tokens: int) -> None:
 
             r = {"path": name, "M": M, "N": N, "K": d_model,
                  "fused_ms": _rank_time(lambda: symm.all_gather_gemm(xs, w, mesh, ("x",), tokens, arena_off=off)),
-                 "nccl_then_gemm_ms": _rank_time(lib), "gemm_only_ms": _rank_time(lambda: gemm_bf16(full, w))}
+                 "nccl_then_gemm_ms": _rank_time(lib), "gemm_only_ms": _rank_time(lambda: gemm_bf16(full, w)),
+                 "nccl_all_gather_ms": _rank_time(lambda: dist.all_gather_into_tensor(full, xs)),
+                 "switch_multicast": bool(ar is not None and ar.mc_ptr)}
+            os.environ["NABLA_B200_AG_MULTIMEM"] = "1"          # one multicast store through the switch
+            for c in (4, 8, 12, 16):      # copy CTAs taken from the GEMM
+                r[f"fused_multicast_{c}ctas_ms"] = _rank_time(lambda: symm.all_gather_gemm(xs, w, mesh, ("x",), tokens, arena_off=off,
+                                                                               comm_ctas=c))
+            os.environ["NABLA_B200_AG_MULTIMEM"] = "0"          # one store per peer instead of one multicast store
+            r["fused_peer_stores_ms"] = _rank_time(lambda: symm.all_gather_gemm(xs, w, mesh, ("x",), tokens, arena_off=off))
+            for c in (8, 12, 16, 20):
+                r[f"fused_peer_stores_{c}ctas_ms"] = _rank_time(
+                    lambda: symm.all_gather_gemm(xs, w, mesh, ("x",), tokens, arena_off=off, comm_ctas=c))
+            os.environ["NABLA_B200_AG_MULTIMEM"] = "auto"
             r["roofline_ms"] = round(roof(2.0 * M * N * d_model, tokens * d_model * 2 * (world - 1)), 4)
             rows.append(r)
             if off is not None:

@@ -43,17 +43,19 @@ def test_peer_collectives_match_nccl():
         assert r["canary_ok"]
 
 
-@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("nvls", ["1", "0"])
-def test_fused_gemm_all_reduce_matches_nccl(nvls):
-    res, rs = _run("fused_gemm", 2, env={"NABLA_B200_NVLS": nvls})
-    assert len(rs) == 2, res.stdout[-2000:] + res.stderr[-3000:]
-    for r in rs:
-        assert r["max_err"] < 2e-2 and not r["errs"], r
-
-
 def _need(n):
     return pytest.mark.skipif(_ngpu() < n, reason=f"needs {n} GPUs")
+
+
+@pytest.mark.parametrize("n", [pytest.param(2, marks=_need(2)), pytest.param(4, marks=_need(4))])
+@pytest.mark.parametrize("nvls", ["1", "0"])
+def test_fused_gemm_all_reduce_matches_nccl(nvls, n):
+    """The three fused GEMM + collective kernels and the fused dp all-reduce + AdamW over ONE group of
+    n ranks (n = 4: the tensor-parallel width of the benchmark), switch reduction on and off."""
+    res, rs = _run("fused_gemm", n, env={"NABLA_B200_NVLS": nvls, "NABLA_B200_SYMM_ARENA_GB": "2"})
+    assert len(rs) == n, res.stdout[-2000:] + res.stderr[-3000:]
+    for r in rs:
+        assert r["max_err"] < 2e-2 and not r["errs"], r
 
 
 @pytest.mark.parametrize("n", [pytest.param(2, marks=_need(2)), pytest.param(4, marks=_need(4)),
