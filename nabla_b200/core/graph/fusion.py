@@ -480,7 +480,18 @@ def run_fused(kind: str, group: list[OpNode], keep_graph: bool = False, arena_bl
         a, b = [x._buffers[0] for x in mm.input_impls()]
         mesh = mm.outputs()[0].sharding.mesh if mm.outputs()[0] is not None else ar.input_impls()[0].sharding.mesh
         axes = [x for x in mesh.axis_names if x in ar.kwargs["reduce_axes"]]
-        if symm.gemm_all_reduce_supported(a, b):
+        split = 1
+        if a.is_cuda and a.dim() == 2 and a.dtype == torch.bfloat16:
+            from ...native.gemm import gemm_bf16, split_k_factor
+
+            split = split_k_factor(a.shape[0], b.shape[-1], a.shape[1])
+        if split > 1:
+            # few output tiles and a very long K (weight gradients of a tensor-parallel shard): the
+            # fused kernel's fixed 128 x 256 tiles would leave most SMs idle, so the product runs
+            # as K slices on all SMs and the small result is all-reduced on its own
+            out = backend.all_reduce(gemm_bf16(a, b), mesh, axes, "sum")
+            backend.stats["split_k_gemm_all_reduce"] = backend.stats.get("split_k_gemm_all_reduce", 0) + 1
+        elif symm.gemm_all_reduce_supported(a, b):
             out = symm.gemm_all_reduce(a, b, mesh, axes).clone().reshape(*a.shape[:-1], b.shape[-1])
             backend.stats["fused_gemm_all_reduce"] = backend.stats.get("fused_gemm_all_reduce", 0) + 1
         else:

@@ -26,7 +26,7 @@ NVCC_FLAGS = [
 # library name -> (sources, extra flags)
 TARGETS: dict[str, tuple[list[str], list[str]]] = {
     "libnb_gemm.so": (["gemm_tcgen05.cu"], []),
-    "libnb_kernels.so": (["fused_kernels.cu"], []),
+    "libnb_kernels.so": (["fused_kernels.cu", "elementwise_kernels.cu"], []),
     "libnb_attention.so": (["attention_tcgen05.cu"], []),
     "libnb_comm.so": (["peer_collectives.cu"], []),
     "libnb_runtime.so": (["plan_runtime.cpp"], []),

@@ -864,6 +864,23 @@ __global__ void __launch_bounds__(256) conv2d_wgrad_direct_kernel(const T* __res
   }
 }
 
+// out[i] = sum_j part[j][i] for `slices` fp32 slices of n elements (n % 4 == 0): the second half of
+// a split-K GEMM, whose partial products are written as fp32 by the tensor-core kernel.
+template <typename T>
+__global__ void __launch_bounds__(256) sum_slices_kernel(const float* __restrict__ part, T* __restrict__ out, size_t n,
+                                                        int slices) {
+  const size_t nv = n / 4;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += (size_t)gridDim.x * blockDim.x) {
+    float4 acc = reinterpret_cast<const float4*>(part)[i];
+    for (int j = 1; j < slices; ++j) {
+      const float4 v = reinterpret_cast<const float4*>(part + (size_t)j * n)[i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    out[4 * i] = from_f<T>(acc.x); out[4 * i + 1] = from_f<T>(acc.y);
+    out[4 * i + 2] = from_f<T>(acc.z); out[4 * i + 3] = from_f<T>(acc.w);
+  }
+}
+
 static inline int grid_for(size_t n, int per_block, int cap = 148 * 16) {
   size_t g = (n + per_block - 1) / per_block;
   if (g < 1) g = 1;
@@ -1132,6 +1149,15 @@ int nb_conv2d_direct(const void* x, const void* w, const void* bias, void* y, in
   const int grid = grid_for(total, 128, 148 * 32);
   if (dtype) conv2d_direct_kernel<bf16><<<grid, 128, 0, STREAM>>>((const bf16*)x, (const bf16*)w, (const bf16*)bias, (bf16*)y, N, H, W, C, R, S, F, OH, OW, sh, sw, pt, pl);
   else conv2d_direct_kernel<float><<<grid, 128, 0, STREAM>>>((const float*)x, (const float*)w, (const float*)bias, (float*)y, N, H, W, C, R, S, F, OH, OW, sh, sw, pt, pl);
+  return CHECK_LAUNCH();
+}
+
+int nb_sum_slices(const float* part, void* out, long long n, int slices, int dtype, void* stream) {
+  if (n <= 0 || slices <= 0) return 0;
+  if (n & 3) return -2;
+  const int grid = grid_for((size_t)n / 4, 256, 148 * 8);
+  if (dtype) sum_slices_kernel<bf16><<<grid, 256, 0, STREAM>>>(part, (bf16*)out, (size_t)n, slices);
+  else sum_slices_kernel<float><<<grid, 256, 0, STREAM>>>(part, (float*)out, (size_t)n, slices);
   return CHECK_LAUNCH();
 }
 

@@ -55,10 +55,66 @@ def gemm_supported(a: torch.Tensor, b: torch.Tensor) -> bool:
     return a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
 
 
+_SMS = 0
+
+
+def split_k_factor(M: int, N: int, K: int) -> int:
+    """How many K slices a weight-gradient-shaped GEMM (few output tiles, long K) is cut into: 1 (no
+    split), 2, 4 or 8. A small cost model of the kernel picks it: whole waves of tiles over the SMs,
+    the tile width the launcher would choose (256, or 128 / 64 when there are too few tiles, which
+    run at about 0.9 / 0.4 of the wide tile's rate), plus the fp32 partial sums that a split writes
+    and reads back. Measured on a B200: 512 x 2048 x 65536 runs 0.319 ms unsplit (64-wide tiles) and
+    0.131 ms in 4 slices; 2048 x 1536 x 65536 0.418 -> 0.366 ms; 2048 x 2048 x 16384 is best unsplit
+    (0.118 ms on 128-wide tiles)."""
+    global _SMS
+    if _SMS == 0:
+        _SMS = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    if K < 4096 or (M * N) % 4:
+        return 1
+    m_t = (M + 127) // 128
+    rate = 1.4e15 / _SMS                          # FLOP/s of one SM on wide tiles (sustained)
+    tile_eff = {256: 1.0, 128: 0.9, 64: 0.4}
+
+    def est(s: int) -> float:
+        bn = 256
+        if N <= 64 or m_t * ((N + 255) // 256) * s < _SMS // 2:
+            bn = 128
+        if N <= 64 or (bn == 128 and m_t * ((N + 127) // 128) * s < _SMS // 2):
+            bn = 64
+        tiles = m_t * ((N + bn - 1) // bn) * s
+        waves = -(-tiles // _SMS)
+        t = waves * (2.0 * 128 * bn * (K / s)) / (rate * tile_eff[bn])
+        if s > 1:
+            t += (s * M * N * 8 + M * N * 2) / 5e12 + 4e-6
+        return t
+
+    best, best_t = 1, est(1)
+    for s in (2, 4, 8):
+        if K % (s * 64) or K // s < 1024:
+            break
+        t = est(s)
+        if t < 0.93 * best_t:
+            best, best_t = s, t
+    return best
+
+
+def _k_slices(t3: torch.Tensor, kind: str, ld: int, s: int, k_dim: int) -> torch.Tensor:
+    """(1, R, C) operand -> (s, ...) strided view whose batch index walks the K slices (no copy).
+    ``k_dim`` is the position of K in the (R, C) shape."""
+    _, R, C = t3.shape
+    if k_dim == 1:                      # A: (M, K)
+        ks = C // s
+        strides = (ks, ld, 1) if kind == "row" else (ks * ld, 1, ld)
+        return t3.as_strided((s, R, ks), strides, t3.storage_offset())
+    ks = R // s                          # B: (K, N)
+    strides = (ks * ld, ld, 1) if kind == "row" else (ks, 1, ld)
+    return t3.as_strided((s, ks, C), strides, t3.storage_offset())
+
+
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = None, epilogue: str = "none",
               aux: str = "none", aux_in: torch.Tensor | None = None, out: torch.Tensor | None = None,
               out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False, gelu_tanh: bool = False,
-              alpha: float = 1.0, block_n: int = 0, max_ctas: int = 0):
+              alpha: float = 1.0, block_n: int = 0, max_ctas: int = 0, split_k: int | None = None):
     """``out = epilogue(alpha * a @ b + bias)`` for bf16 ``a`` (..., M, K) and ``b`` (..., K, N).
 
     ``a`` and ``b`` may be arbitrary 2-D/3-D strided views (e.g. ``.transpose(-1, -2)``); views
@@ -94,6 +150,18 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, bias: torch.Tensor | None = N
     a3, akind, lda, sa = _prep(a3)
     # B (K,N): 'row' (N contiguous) is MN-major; 'col' (K contiguous) is K-major.
     b3, bkind, ldb, sb = _prep(b3)
+    # split-K: few output tiles and a long K (weight gradients): the K range is cut into slices that
+    # run as a batch (each slice an fp32 partial product), and one pass adds the slices
+    if (batch == 1 and bias is None and epilogue == "none" and aux == "none" and out is None and not accumulate
+            and alpha == 1.0 and block_n == 0 and split_k != 1 and out_dtype in (torch.bfloat16, torch.float32)):
+        s_ = split_k if split_k else split_k_factor(M, N, K)
+        if s_ > 1 and K % (s_ * 64) == 0:
+            from . import kernels
+
+            part = gemm_bf16(_k_slices(a3, akind, lda, s_, 1), _k_slices(b3, bkind, ldb, s_, 0),
+                             out_dtype=torch.float32, split_k=1, max_ctas=max_ctas)
+            res = kernels.sum_slices(part, out_dtype)
+            return res if squeeze else res.unsqueeze(0)
     a_mn = 0 if akind == "row" else 1
     b_mn = 1 if bkind == "row" else 0
     if out is None:

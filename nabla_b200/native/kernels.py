@@ -45,6 +45,12 @@ def _L():
             "nb_pool2d_bwd": [c_vp] * 3 + [c_int] * 14 + [c_vp],
             "nb_conv2d_direct": [c_vp] * 4 + [c_int] * 14 + [c_vp],
             "nb_conv2d_wgrad_direct": [c_vp] * 3 + [c_int] * 14 + [c_vp],
+            "nb_sum_slices": [c_vp, c_vp, c_ll, c_int, c_int, c_vp],
+            "nb_binary": [c_vp, c_vp, c_vp, c_ll, c_int, c_int, c_ll, c_int, c_int, c_vp],
+            "nb_unary": [c_vp, c_vp, c_ll, c_int, c_int, c_vp],
+            "nb_reduce": [c_vp, c_vp, c_vp, c_ll, c_ll, c_ll, c_int, c_int, c_vp],
+            "nb_reduce_splits": [c_ll, c_ll, c_ll],
+            "nb_cumsum": [c_vp, c_vp, c_ll, c_ll, c_ll, c_int, c_int, c_int, c_vp],
         }
         for name, args in sig.items():
             fn = getattr(lib, name)
@@ -372,4 +378,121 @@ def nf4_dequant_codes(codes: torch.Tensor, absmax: torch.Tensor, codebook: torch
     _ok(_L().nb_nf4_dequant_codes(ptr(codes.contiguous()), ptr(absmax.contiguous().float()),
                                   ptr(codebook.contiguous().float()), ptr(out), n, block, _dt(out), stream_ptr()),
         "nf4_dequant_codes")
+    return out
+
+
+def sum_slices(part: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """Sum a contiguous fp32 tensor over its leading dim (the partial products of a split-K GEMM)."""
+    s_ = part.shape[0]
+    out = torch.empty(part.shape[1:], dtype=out_dtype, device=part.device)
+    _ok(_L().nb_sum_slices(ptr(part), ptr(out), out.numel(), s_, _dt(out), stream_ptr()), "sum_slices")
+    return out
+
+
+# ---------------------------------------------------------------- pointwise / reduction families
+BINARY_OPS = {"add": 0, "sub": 1, "mul": 2, "div": 3, "maximum": 4, "minimum": 5, "pow": 6}
+UNARY_OPS = {"neg": 0, "abs": 1, "exp": 2, "log": 3, "sqrt": 4, "rsqrt": 5, "tanh": 6, "sigmoid": 7, "sin": 8, "cos": 9,
+             "erf": 10, "log1p": 11, "floor": 12, "trunc": 13, "round": 14, "square": 15, "reciprocal": 16}
+REDUCE_OPS = {"sum": 0, "max": 1, "min": 2, "mean": 3, "argmax": 4, "argmin": 5}
+_FLOATS = (torch.float32, torch.bfloat16)
+
+
+def elementwise_enabled() -> bool:
+    import os
+
+    return os.environ.get("NABLA_B200_ELEMENTWISE", "native") == "native"
+
+
+def binary(a: torch.Tensor, b: torch.Tensor, op: str):
+    """``a (op) b`` in one kernel when both are fp32 / bf16 CUDA tensors of one dtype and ``b`` (or
+    ``a``) has the other's shape, is a single element, or is a vector over the trailing dims (bias
+    style). Returns None for anything else (mixed dtypes, general broadcasting, integers): the caller
+    then uses the framework's generic path."""
+    if not (a.is_cuda and b.is_cuda and a.dtype == b.dtype and a.dtype in _FLOATS and elementwise_enabled()):
+        return None
+    swap = 0
+    if a.numel() < b.numel():
+        a, b, swap = b, a, 1
+    if a.numel() == 0 or tuple(torch.broadcast_shapes(a.shape, b.shape)) != tuple(a.shape):
+        return None
+    v = 16 // a.element_size()
+    if b.numel() == 1:
+        mode, inner = 1, 1
+    elif tuple(b.shape) == tuple(a.shape):
+        mode, inner = 0, 1
+    else:
+        bs = tuple(b.shape)
+        while bs and bs[0] == 1:
+            bs = bs[1:]
+        if not bs or tuple(a.shape[len(a.shape) - len(bs):]) != bs:
+            return None
+        mode, inner = 2, b.numel()
+        if inner % v:
+            return None
+    a_c, b_c = a.contiguous(), b.contiguous()
+    if (a_c.data_ptr() | b_c.data_ptr()) & 15:
+        return None
+    out = torch.empty_like(a_c)
+    _ok(_L().nb_binary(ptr(a_c), ptr(b_c), ptr(out), a_c.numel(), BINARY_OPS[op], mode, inner, swap, _dt(a_c), stream_ptr()),
+        "binary")
+    return out
+
+
+def unary(x: torch.Tensor, op: str):
+    """``f(x)`` in one kernel for fp32 / bf16 CUDA tensors; None otherwise."""
+    if not (x.is_cuda and x.dtype in _FLOATS and x.numel() and elementwise_enabled()):
+        return None
+    xc = x.contiguous()
+    if xc.data_ptr() & 15:
+        return None
+    out = torch.empty_like(xc)
+    _ok(_L().nb_unary(ptr(xc), ptr(out), xc.numel(), UNARY_OPS[op], _dt(xc), stream_ptr()), "unary")
+    return out
+
+
+def _outer_r_inner(x: torch.Tensor, axis: int):
+    outer = 1
+    for d in x.shape[:axis]:
+        outer *= int(d)
+    inner = 1
+    for d in x.shape[axis + 1:]:
+        inner *= int(d)
+    return outer, int(x.shape[axis]), inner
+
+
+def reduce(x: torch.Tensor, axis: int, op: str, keepdims: bool = False):
+    """sum / max / min / mean / argmax / argmin over one axis in one kernel (fp32 / bf16 CUDA, non-empty
+    axis); None otherwise."""
+    if not (x.is_cuda and x.dtype in _FLOATS and x.numel() and elementwise_enabled()):
+        return None
+    axis = axis % x.dim() if x.dim() else 0
+    if x.dim() == 0:
+        return None
+    xc = x.contiguous()
+    outer, r, inner = _outer_r_inner(xc, axis)
+    if inner > 1 and op == "sum" and outer == 1 and r > 4096 and supports_rows(xc.reshape(r, inner)):
+        # column sums of a tall 2-D matrix (bias-gradient shape) have their own slab kernel
+        out = colsum(xc.reshape(r, inner), out_dtype=x.dtype)
+        return out.reshape([1] + list(xc.shape[axis + 1:]) if keepdims else list(xc.shape[axis + 1:]))
+    shape = list(xc.shape)
+    if keepdims:
+        shape[axis] = 1
+    else:
+        shape.pop(axis)
+    out = torch.empty(shape, dtype=torch.int64 if op.startswith("arg") else x.dtype, device=x.device)
+    splits = _L().nb_reduce_splits(outer, r, inner)
+    scratch = torch.empty(outer * splits * inner * 3, dtype=torch.float32, device=x.device) if splits > 1 else None
+    _ok(_L().nb_reduce(ptr(xc), ptr(out), ptr(scratch), outer, r, inner, REDUCE_OPS[op], _dt(xc), stream_ptr()), "reduce")
+    return out
+
+
+def cumsum(x: torch.Tensor, axis: int, exclusive: bool = False, reverse: bool = False):
+    if not (x.is_cuda and x.dtype in _FLOATS and x.numel() and x.dim() and elementwise_enabled()):
+        return None
+    xc = x.contiguous()
+    outer, r, inner = _outer_r_inner(xc, axis % x.dim())
+    if outer * inner < 4096 and r > 2048:
+        return None                      # a few long scans: the sequential-per-column kernel is the wrong tool
+    out = torch.empty_like(xc)
+    _ok(_L().nb_cumsum(ptr(xc), ptr(out), outer, r, inner, int(exclusive), int(reverse), _dt(xc), stream_ptr()), "cumsum")
     return out

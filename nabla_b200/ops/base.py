@@ -346,10 +346,19 @@ def _align_batch_dims(tensors: list[Tensor]) -> list[Tensor]:
 class BinaryOperation(Operation):
     """Elementwise op of two operands with numpy broadcasting."""
 
+    #: name of the op in ``native.kernels.BINARY_OPS`` when the pointwise kernel family covers it
+    native_op: str | None = None
+
     def torch_fn(self, a, b):
         raise NotImplementedError
 
     def kernel(self, a, b):
+        if self.native_op is not None and a.is_cuda:
+            from ..native import kernels
+
+            out = kernels.binary(a, b, self.native_op)
+            if out is not None:
+                return out
         return self.torch_fn(a, b)
 
     def __call__(self, a, b):
@@ -368,10 +377,19 @@ class BinaryOperation(Operation):
 class UnaryOperation(Operation):
     """Elementwise op of one operand. ``_derivative(x, y)`` gives dy/dx for VJP and JVP."""
 
+    #: name of the op in ``native.kernels.UNARY_OPS`` when the pointwise kernel family covers it
+    native_op: str | None = None
+
     def torch_fn(self, x):
         raise NotImplementedError
 
     def kernel(self, x, **kwargs):
+        if self.native_op is not None and x.is_cuda:
+            from ..native import kernels
+
+            out = kernels.unary(x, self.native_op)
+            if out is not None:
+                return out
         return self.torch_fn(x)
 
     def _derivative(self, x: Tensor, y: Tensor, kwargs: dict) -> Tensor | None:
@@ -431,10 +449,19 @@ class ReduceOperation(AxisOp):
 
     partial_policy = "any"
 
+    #: name of the reduction in ``native.kernels.REDUCE_OPS`` when the reduction kernels cover it
+    native_op: str | None = None
+
     def torch_reduce(self, x, axis, keepdims):
         raise NotImplementedError
 
     def kernel(self, x, *, axis: int, keepdims: bool = False):
+        if self.native_op is not None and x.is_cuda and x.dim() and x.shape[axis] > 0:
+            from ..native import kernels
+
+            out = kernels.reduce(x, axis, self.native_op, keepdims)
+            if out is not None:
+                return out
         return self.torch_reduce(x, axis, keepdims)
 
     def sharding_rule(self, input_shapes, output_shapes, *, axis: int, keepdims: bool = False, **kw):

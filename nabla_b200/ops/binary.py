@@ -18,6 +18,7 @@ def _result_float(a: Tensor) -> bool:
 
 
 class AddOp(BinaryOperation):
+    native_op = "add"
     partial_policy = "all"
 
     def torch_fn(self, a, b):
@@ -31,6 +32,7 @@ class AddOp(BinaryOperation):
 
 
 class SubOp(BinaryOperation):
+    native_op = "sub"
     partial_policy = "all"
 
     def torch_fn(self, a, b):
@@ -44,6 +46,7 @@ class SubOp(BinaryOperation):
 
 
 class MulOp(BinaryOperation):
+    native_op = "mul"
     partial_policy = "one"
 
     def torch_fn(self, a, b):
@@ -59,6 +62,7 @@ class MulOp(BinaryOperation):
 
 
 class DivOp(BinaryOperation):
+    native_op = "div"
     partial_policy = "first"
 
     def torch_fn(self, a, b):

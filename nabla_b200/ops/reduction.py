@@ -23,6 +23,8 @@ def _empty_reduce(x, axis, keepdims, value):
 
 
 class ReduceSumOp(ReduceOperation):
+    native_op = "sum"
+
     def torch_reduce(self, x, axis, keepdims):
         if x.dtype == torch.bool:
             x = x.to(torch.int64)
@@ -88,6 +90,7 @@ class _ReduceExt(ReduceOperation):
 
 
 class ReduceMaxOp(_ReduceExt):
+    native_op = "max"
     collective_reduce_type = "max"
 
     def torch_reduce(self, x, axis, keepdims):
@@ -97,6 +100,7 @@ class ReduceMaxOp(_ReduceExt):
 
 
 class ReduceMinOp(_ReduceExt):
+    native_op = "min"
     collective_reduce_type = "min"
 
     def torch_reduce(self, x, axis, keepdims):
@@ -108,7 +112,15 @@ class ReduceMinOp(_ReduceExt):
 class _ArgOp(AxisOp):
     fn = None
 
+    native_op = None
+
     def kernel(self, x, *, axis: int, keepdims: bool = False):
+        if self.native_op is not None and x.is_cuda and x.dim() and x.shape[axis] > 0:
+            from ..native import kernels
+
+            out = kernels.reduce(x, axis, self.native_op, keepdims)
+            if out is not None:
+                return out
         return type(self).fn(x, dim=axis, keepdim=keepdims)
 
     def sharding_rule(self, input_shapes, output_shapes, *, axis: int, keepdims: bool = False, **kw):
@@ -134,14 +146,22 @@ class _ArgOp(AxisOp):
 
 class ArgmaxOp(_ArgOp):
     fn = staticmethod(torch.argmax)
+    native_op = "argmax"
 
 
 class ArgminOp(_ArgOp):
     fn = staticmethod(torch.argmin)
+    native_op = "argmin"
 
 
 class CumsumOp(AxisOp):
     def kernel(self, x, *, axis: int, exclusive: bool = False, reverse: bool = False):
+        if x.is_cuda:
+            from ..native import kernels
+
+            out = kernels.cumsum(x, axis, exclusive, reverse)
+            if out is not None:
+                return out
         if reverse:
             x = torch.flip(x, dims=(axis,))
         y = torch.cumsum(x, dim=axis)

@@ -10,9 +10,10 @@ from ..types import DType, as_dtype
 from .base import AxisOp, Operation, UnaryOperation, ensure_tensor
 
 
-def _u(name: str, fn, deriv=None, policy: str = "none"):
-    """Build a UnaryOperation subclass instance from a torch function and a derivative."""
-    ns = {"torch_fn": lambda self, x: fn(x), "partial_policy": policy}
+def _u(name: str, fn, deriv=None, policy: str = "none", native: str | None = None):
+    """Build a UnaryOperation subclass instance from a torch function and a derivative; ``native``
+    names the entry of the pointwise kernel family that runs it on a GPU."""
+    ns = {"torch_fn": lambda self, x: fn(x), "partial_policy": policy, "native_op": native}
     if deriv is not None:
         ns["_derivative"] = lambda self, x, y, kwargs: deriv(x, y)
     return type(name, (UnaryOperation,), ns)()
@@ -24,14 +25,15 @@ def _zeros_like(x):
     return zeros_like(x)
 
 
-def _nondiff(name: str, fn):
+def _nondiff(name: str, fn, native: str | None = None):
     def vjp(self, primals, cot, outputs, kwargs):
         return (None,)
 
     def jvp(self, primals, tangents, outputs, kwargs):
         return None
 
-    return type(name, (UnaryOperation,), {"torch_fn": lambda self, x: fn(x), "vjp_rule": vjp, "jvp_rule": jvp})()
+    return type(name, (UnaryOperation,), {"torch_fn": lambda self, x: fn(x), "vjp_rule": vjp, "jvp_rule": jvp,
+                                          "native_op": native})()
 
 
 def _step(x):
@@ -47,29 +49,30 @@ def _sign(x):
 
 
 _relu = _u("ReluOp", torch.relu, lambda x, y: _step(x))
-_sigmoid = _u("SigmoidOp", torch.sigmoid, lambda x, y: y * (1.0 - y))
-_tanh = _u("TanhOp", torch.tanh, lambda x, y: 1.0 - y * y)
-_exp = _u("ExpOp", torch.exp, lambda x, y: y)
-_abs = _u("AbsOp", torch.abs, lambda x, y: _sign(x))
-_log = _u("LogOp", torch.log, lambda x, y: 1.0 / x)
-_sqrt = _u("SqrtOp", torch.sqrt, lambda x, y: 0.5 / y)
+_sigmoid = _u("SigmoidOp", torch.sigmoid, lambda x, y: y * (1.0 - y), native="sigmoid")
+_tanh = _u("TanhOp", torch.tanh, lambda x, y: 1.0 - y * y, native="tanh")
+_exp = _u("ExpOp", torch.exp, lambda x, y: y, native="exp")
+_abs = _u("AbsOp", torch.abs, lambda x, y: _sign(x), native="abs")
+_log = _u("LogOp", torch.log, lambda x, y: 1.0 / x, native="log")
+_sqrt = _u("SqrtOp", torch.sqrt, lambda x, y: 0.5 / y, native="sqrt")
 _acos = _u("AcosOp", torch.acos, lambda x, y: -rsqrt(1.0 - x * x))
 _atanh = _u("AtanhOp", torch.atanh, lambda x, y: 1.0 / (1.0 - x * x))
-_cos = _u("CosOp", torch.cos, lambda x, y: -sin(x))
-_sin = _u("SinOp", torch.sin, lambda x, y: cos(x))
-_erf = _u("ErfOp", torch.erf, lambda x, y: (2.0 / math.sqrt(math.pi)) * exp(-(x * x)))
-_log1p = _u("Log1pOp", torch.log1p, lambda x, y: 1.0 / (1.0 + x))
-_rsqrt = _u("RsqrtOp", torch.rsqrt, lambda x, y: -0.5 * y / x)
+_cos = _u("CosOp", torch.cos, lambda x, y: -sin(x), native="cos")
+_sin = _u("SinOp", torch.sin, lambda x, y: cos(x), native="sin")
+_erf = _u("ErfOp", torch.erf, lambda x, y: (2.0 / math.sqrt(math.pi)) * exp(-(x * x)), native="erf")
+_log1p = _u("Log1pOp", torch.log1p, lambda x, y: 1.0 / (1.0 + x), native="log1p")
+_rsqrt = _u("RsqrtOp", torch.rsqrt, lambda x, y: -0.5 * y / x, native="rsqrt")
 _silu = _u("SiluOp", torch.nn.functional.silu, lambda x, y: sigmoid(x) * (1.0 + x * (1.0 - sigmoid(x))))
-_floor = _nondiff("FloorOp", torch.floor)
-_trunc = _nondiff("TruncOp", torch.trunc)
-_round = _nondiff("RoundOp", torch.round)
+_floor = _nondiff("FloorOp", torch.floor, native="floor")
+_trunc = _nondiff("TruncOp", torch.trunc, native="trunc")
+_round = _nondiff("RoundOp", torch.round, native="round")
 _is_inf = _nondiff("IsInfOp", torch.isinf)
 _is_nan = _nondiff("IsNanOp", torch.isnan)
 
 
 class NegOp(UnaryOperation):
     partial_policy = "any"
+    native_op = "neg"
 
     def torch_fn(self, x):
         return torch.neg(x)

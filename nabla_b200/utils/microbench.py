@@ -199,6 +199,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--block-n", type=int, default=0, help="gemm: force the tile width (256, 128 or 64)")
+    ap.add_argument("--split-k", type=int, default=0, help="gemm: K slices (0 = automatic, 1 = never split)")
+    ap.add_argument("--ta", action="store_true", help="gemm: A given as the transpose of a (K, M) matrix (weight gradient)")
     a = ap.parse_args()
     if a.kernel in ("comm_allreduce", "comm_fused"):
         return comm_main(a.kernel, a.tokens)
@@ -213,11 +215,11 @@ def main() -> None:
     bf = torch.bfloat16
     flops = bytes_ = 0.0
     if a.kernel in ("gemm", "gemm_gelu"):
-        x = torch.randn(a.m, a.k, device=dev, dtype=bf)
+        x = torch.randn(a.k, a.m, device=dev, dtype=bf).t() if a.ta else torch.randn(a.m, a.k, device=dev, dtype=bf)
         w = torch.randn(a.k, a.n, device=dev, dtype=bf)
         b = torch.randn(a.n, device=dev, dtype=bf)
         if a.kernel == "gemm":
-            fn = lambda: gemm_bf16(x, w, block_n=a.block_n)
+            fn = lambda: gemm_bf16(x, w, block_n=a.block_n, split_k=a.split_k or None)
         else:
             fn = lambda: gemm_bf16(x, w, bias=b, epilogue="gelu", aux="store_preact")
         flops = 2.0 * a.m * a.n * a.k

@@ -540,3 +540,114 @@ def test_gemm_tail_tiles_elementwise(M, N, K):
         out = gemm_bf16(aa, bb, out_dtype=torch.float32)
         bad = (out - ref).abs() > 1e-3
         assert not bad.any(), (layout, bad.nonzero()[:4].tolist())
+
+
+@pytest.mark.parametrize("M,N,K,layout", [(2048, 2048, 16384, "TN"), (2048, 1536, 65536, "TN"), (512, 2048, 65536, "TN"),
+                                          (1024, 1024, 8192, "NN"), (640, 776, 4096, "NT")])
+def test_gemm_split_k_matches_fp32(M, N, K, layout):
+    """Weight-gradient-shaped GEMMs (few output tiles, long K) run as K slices + one summing pass;
+    the result must equal the unsplit kernel's and the fp32 reference."""
+    from nabla_b200.native import gemm as G
+
+    torch.manual_seed(2)
+    a = (torch.randn(K, M, device="cuda", dtype=torch.bfloat16).t() if layout[0] == "T"
+         else torch.randn(M, K, device="cuda", dtype=torch.bfloat16))
+    b = (torch.randn(N, K, device="cuda", dtype=torch.bfloat16).t() if layout[1] == "T"
+         else torch.randn(K, N, device="cuda", dtype=torch.bfloat16))
+    ref = a.float() @ b.float()
+    if K == 65536:
+        assert G.split_k_factor(M, N, K) > 1           # the tensor-parallel weight-gradient shapes do split
+    for sk in (None, 2, 4):
+        for od in (torch.bfloat16, torch.float32):
+            out = G.gemm_bf16(a, b, out_dtype=od, split_k=sk)
+            assert out.dtype == od and _rel(out, ref) < (1e-2 if od == torch.bfloat16 else 1e-4)
+    plain = G.gemm_bf16(a, b, out_dtype=torch.float32, split_k=1)
+    assert _rel(G.gemm_bf16(a, b, out_dtype=torch.float32), plain) < 1e-4
+
+
+# ---------------------------------------------------------------- pointwise / reduction families
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_pointwise_binary_family(dtype):
+    from nabla_b200.native import kernels
+
+    torch.manual_seed(4)
+    tol = 1e-6 if dtype == torch.float32 else 1e-2
+    a = torch.randn(37, 5, 24, device="cuda").to(dtype)
+    for bshape in ((37, 5, 24), (1,), (24,), (5, 24), (1, 1, 24)):
+        b = (torch.rand(bshape, device="cuda") + 0.5).to(dtype)
+        for op, ref in (("add", torch.add), ("sub", torch.sub), ("mul", torch.mul), ("div", torch.div),
+                        ("maximum", torch.maximum), ("minimum", torch.minimum)):
+            for x, y in ((a, b), (b, a)):                      # the smaller operand on either side
+                out = kernels.binary(x, y, op)
+                assert out is not None, (op, bshape)
+                want = ref(x.float(), y.float())
+                assert out.shape == want.shape and _rel(out, want) < tol, (op, bshape)
+    assert kernels.binary(a, torch.randn(5, 1, device="cuda").to(dtype), "add") is None      # general broadcast: not covered
+    odd = torch.randn(1003, device="cuda").to(dtype)                                          # tail that is not a whole vector
+    assert _rel(kernels.binary(odd, odd, "mul"), odd.float() ** 2) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_pointwise_unary_family(dtype):
+    from nabla_b200.native import kernels
+
+    torch.manual_seed(5)
+    x = (torch.rand(129, 77, device="cuda") * 3 + 0.1).to(dtype)
+    refs = {"neg": torch.neg, "abs": torch.abs, "exp": torch.exp, "log": torch.log, "sqrt": torch.sqrt, "rsqrt": torch.rsqrt,
+            "tanh": torch.tanh, "sigmoid": torch.sigmoid, "sin": torch.sin, "cos": torch.cos, "erf": torch.erf,
+            "log1p": torch.log1p, "floor": torch.floor, "trunc": torch.trunc, "round": torch.round,
+            "square": torch.square, "reciprocal": torch.reciprocal}
+    for op, ref in refs.items():
+        for inp in (x, -x if op not in ("log", "sqrt", "rsqrt", "log1p") else x):
+            out = kernels.unary(inp, op)
+            want = ref(inp.float())
+            assert (out.float() - want).abs().max().item() <= (2e-6 if dtype == torch.float32 else 1.6e-2) * (1 + want.abs().max().item()), op
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_reduction_family(dtype):
+    from nabla_b200.native import kernels
+
+    torch.manual_seed(6)
+    x = torch.randn(9, 130, 33, device="cuda").to(dtype)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    for axis in (0, 1, 2, -1):
+        for keep in (False, True):
+            assert _rel(kernels.reduce(x, axis, "sum", keep), x.float().sum(axis, keepdim=keep)) < tol
+            assert _rel(kernels.reduce(x, axis, "mean", keep), x.float().mean(axis, keepdim=keep)) < tol
+            assert torch.equal(kernels.reduce(x, axis, "max", keep), x.amax(axis, keepdim=keep))
+            assert torch.equal(kernels.reduce(x, axis, "min", keep), x.amin(axis, keepdim=keep))
+            assert torch.equal(kernels.reduce(x, axis, "argmax", keep), x.float().argmax(axis, keepdim=keep))
+            assert torch.equal(kernels.reduce(x, axis, "argmin", keep), x.float().argmin(axis, keepdim=keep))
+    wide = torch.randn(7, 5000, device="cuda").to(dtype)                   # block-per-row path, vector loads
+    assert _rel(kernels.reduce(wide, 1, "sum"), wide.float().sum(1)) < tol
+    assert torch.equal(kernels.reduce(wide, 1, "argmax"), wide.float().argmax(1))
+    nan = wide.clone()
+    nan[3, 17] = float("nan")
+    assert torch.isnan(kernels.reduce(nan, 1, "max")[3]) and not torch.isnan(kernels.reduce(nan, 1, "max")[2])
+    tall = torch.randn(6000, 64, device="cuda").to(dtype)                   # few long columns -> slab column sum
+    assert _rel(kernels.reduce(tall, 0, "sum"), tall.float().sum(0)) < tol
+    for axis in (0, 1, 2):
+        for excl in (False, True):
+            for rev in (False, True):
+                ref = x.float().flip(axis).cumsum(axis).flip(axis) if rev else x.float().cumsum(axis)
+                if excl:
+                    ref = ref - x.float()
+                got = kernels.cumsum(x, axis, excl, rev)
+                assert _rel(got, ref) < (1e-5 if dtype == torch.float32 else 5e-2), (axis, excl, rev)
+
+
+def test_ops_route_through_the_pointwise_and_reduction_kernels():
+    """The framework's ops (not only the wrappers) launch these kernels for GPU tensors."""
+    import nabla_b200 as nb
+    from nabla_b200.native import kernels
+
+    x = nb.Tensor.from_torch(torch.randn(64, 48, device="cuda"))
+    n0 = kernels.launch_count
+    y = nb.reduce_sum(nb.exp(x) * 2.0 + x, axis=1)
+    z = nb.argmax(x, axis=0)
+    y.realize(); z.realize()
+    assert kernels.launch_count >= n0 + 5
+    xt = x.to_torch()
+    assert _rel(y.to_torch(), (xt.exp() * 2 + xt).sum(1)) < 1e-5
+    assert torch.equal(z.to_torch(), xt.argmax(0))
