@@ -93,10 +93,10 @@ __device__ __forceinline__ void unpack_vec(const uint4& raw, float* out) {
 // (D <= 32 * VPL * Vec::N); it is unpacked for the mean, the variance and the output, which keeps
 // the register count low enough for the number of rows in flight that a bandwidth-bound pass needs.
 template <typename T, int VPL>
-__global__ void __launch_bounds__(128) layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
-                                                           const T* __restrict__ beta, T* __restrict__ y,
-                                                           float* __restrict__ mean, float* __restrict__ rstd,
-                                                           int rows, int D, float eps) {
+__global__ void __launch_bounds__(128, 8) layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
+                                                              const T* __restrict__ beta, T* __restrict__ y,
+                                                              float* __restrict__ mean, float* __restrict__ rstd,
+                                                              int rows, int D, float eps) {
   constexpr int V = Vec<T>::N;
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -108,19 +108,11 @@ __global__ void __launch_bounds__(128) layernorm_fwd_kernel(const T* __restrict_
     const int c = (i * 32 + lane) * V;
     if (c < D) raw[i] = *reinterpret_cast<const uint4*>(xr + c);
   }
-  float s = 0.f;
-#pragma unroll
-  for (int i = 0; i < VPL; ++i) {
-    const int c = (i * 32 + lane) * V;
-    if (c < D) {
-      float v[V];
-      unpack_vec<T>(raw[i], v);
-#pragma unroll
-      for (int j = 0; j < V; ++j) s += v[j];
-    }
-  }
-  const float mu = warp_sum(s) / D;
-  float q = 0.f;
+  // one pass over the registers for both moments (shifted by the row's first element so that the
+  // E[x^2] - E[x]^2 form does not cancel for rows with a large common offset), one pair of warp
+  // reductions issued back to back
+  const float shift = __shfl_sync(0xffffffffu, to_f<T>(reinterpret_cast<const T*>(&raw[0])[0]), 0);
+  float s = 0.f, q = 0.f;
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     const int c = (i * 32 + lane) * V;
@@ -129,17 +121,26 @@ __global__ void __launch_bounds__(128) layernorm_fwd_kernel(const T* __restrict_
       unpack_vec<T>(raw[i], v);
 #pragma unroll
       for (int j = 0; j < V; ++j) {
-        const float d = v[j] - mu;
-        q += d * d;
+        const float d = v[j] - shift;
+        s += d;
+        q = fmaf(d, d, q);
       }
     }
   }
-  const float rs = rsqrtf(warp_sum(q) / D + eps);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s += __shfl_xor_sync(0xffffffffu, s, o);
+    q += __shfl_xor_sync(0xffffffffu, q, o);
+  }
+  const float ms = s / D;
+  const float mu = ms + shift;
+  const float rs = rsqrtf(fmaxf(q / D - ms * ms, 0.f) + eps);
   if (lane == 0) {
     if (mean) mean[row] = mu;
     if (rstd) rstd[row] = rs;
   }
   T* yr = y + (size_t)row * D;
+  const float nmr = -mu * rs;
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     const int c = (i * 32 + lane) * V;
@@ -150,8 +151,8 @@ __global__ void __launch_bounds__(128) layernorm_fwd_kernel(const T* __restrict_
       if (beta) load_vec<T>(beta + c, b);
 #pragma unroll
       for (int j = 0; j < V; ++j) {
-        float n = (v[j] - mu) * rs;
-        o[j] = n * (gamma ? g[j] : 1.f) + (beta ? b[j] : 0.f);
+        const float n = fmaf(v[j], rs, nmr);
+        o[j] = gamma ? fmaf(n, g[j], beta ? b[j] : 0.f) : (n + (beta ? b[j] : 0.f));
       }
       store_vec<T>(yr + c, o);
     }
@@ -162,7 +163,7 @@ __global__ void __launch_bounds__(128) layernorm_fwd_kernel(const T* __restrict_
 // 16-byte form (half the registers of keeping them as floats, so twice as many rows are in flight
 // per SM for this bandwidth-bound pass) and are unpacked once for the two sums and once for dx.
 template <typename T, int VPL>
-__global__ void __launch_bounds__(128) layernorm_bwd_dx_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+__global__ void __launch_bounds__(128, 4) layernorm_bwd_dx_kernel(const T* __restrict__ dy, const T* __restrict__ x,
                                                               const T* __restrict__ gamma, const float* __restrict__ mean,
                                                               const float* __restrict__ rstd, T* __restrict__ dx,
                                                               int rows, int D) {
