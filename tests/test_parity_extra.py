@@ -125,3 +125,84 @@ def test_vmap_over_all_reduce_on_simulated_mesh():
     out = nb.vmap(per_example)(xs)
     ref = xs.to_numpy()[:, :2] + xs.to_numpy()[:, 2:]
     np.testing.assert_allclose(out.to_numpy(), ref)
+
+
+# ---------------------------------------------------------------- control flow on sharded state
+def test_while_loop_with_sharded_state(mesh_2x4):
+    """Loop-carried state split over a mesh axis stays sharded through the loop
+    (reference: tests/unit/test_control_flow.py:246)."""
+    x = np.arange(32, dtype=np.float32).reshape(8, 4)
+    xs = nb.shard(nb.constant(x), mesh_2x4, nb.P("dp", None))
+    i, out = nb.while_loop(lambda i, v: i < 5.0, lambda i, v: (i + 1.0, v + 1.0), (nb.constant(np.float32(0)), xs))
+    assert i.item() == 5.0 and tuple(int(d) for d in out.shape) == (8, 4)
+    assert out.is_sharded
+    np.testing.assert_allclose(out.to_numpy(), x + 5.0)
+
+
+def test_cond_and_compiled_while_on_sharded_operands(mesh_2x4):
+    x = np.arange(16, dtype=np.float32).reshape(8, 2)
+    xs = nb.shard(nb.constant(x), mesh_2x4, nb.P("dp", None))
+    r = nb.cond(nb.reduce_sum(xs) > 0.0, lambda a: a * 2.0, lambda a: a - 1.0, xs)
+    np.testing.assert_allclose(r.to_numpy(), x * 2.0)
+    f = nb.compile(lambda v: nb.while_loop(lambda t: nb.reduce_sum(t) < 500.0, lambda t: t * 2.0 + 1.0, v))
+    for scale in (1.0, 0.1, 1.0):
+        got = f(nb.shard(nb.constant(x * scale), mesh_2x4, nb.P("dp", None))).to_numpy()
+        ref = x * scale
+        while ref.sum() < 500.0:
+            ref = ref * 2.0 + 1.0
+        np.testing.assert_allclose(got, ref, rtol=1e-6)
+    assert f.stats.misses == 1
+
+
+# ---------------------------------------------------------------- introspection, graph walks, debug streams, exports
+def test_tensor_impl_introspection_and_graph_walks(capsys):
+    from nabla_b200.core.graph import utils
+
+    x = nb.constant(np.ones((2, 3), dtype=np.float32))
+    y = nb.relu(x * 2.0) + 1.0
+    im = y._impl
+    assert im.op_name == "add" and not im.is_leaf and x._impl.is_leaf and x._impl.op is None
+    assert [p.op_name for p in im.parents][0] == "relu" and im.ndim == 2
+    assert tuple(im.local_shape) == (2, 3) and tuple(im.logical_shape) == (2, 3) and im.global_shape_ints == (2, 3)
+    ops = utils.get_operations_topological(y)
+    assert [outs[0].op_name for _, outs in ops] == ["mul", "relu", "add"]
+    impls = utils.get_all_impls_topological([y])
+    assert impls[-1] is im and x._impl in impls
+    seen = []
+    utils.apply_to_operations(y, lambda op_id, outs: seen.append(outs[0].op_name))
+    assert seen == ["add", "relu", "mul"]
+    utils.print_trace_graph(y)
+    assert "Computation Graph (3 operations)" in capsys.readouterr().out
+
+
+def test_debug_streams_print_when_switched_on(monkeypatch, capsys):
+    for name in ("OP_CALL", "PHYS", "COT_FLOW", "PHYS_VJP", "NESTED_JVP"):
+        monkeypatch.setenv("NABLA_DEBUG_" + name, "1")
+    x = nb.constant(np.ones((2, 3), dtype=np.float32))
+    nb.grad(lambda a: nb.reduce_sum(a * a))(x).realize()
+    nb.jvp(lambda a: a * a, (x,), (x,))
+    out = capsys.readouterr().out
+    for tag in ("[NABLA_DEBUG_OP_CALL] op=mul", "[NABLA_DEBUG_PHYS] mul.infer_outputs", "[NABLA_DEBUG_COT_FLOW] init",
+                "[NABLA_DEBUG_PHYS_VJP] reduce_sum.vjp", "[NABLA_DEBUG_NESTED_JVP]"):
+        assert tag in out, tag
+    for name in ("OP_CALL", "PHYS", "COT_FLOW", "PHYS_VJP", "NESTED_JVP"):
+        monkeypatch.delenv("NABLA_DEBUG_" + name)
+    nb.grad(lambda a: nb.reduce_sum(a * a))(x).realize()
+    assert "NABLA_DEBUG" not in capsys.readouterr().out
+
+
+def test_reexports_and_path_names():
+    from nabla_b200.core.common import pytree
+    from nabla_b200.nn import finetune, functional as F
+    from nabla_b200.ops import communication as C
+
+    for name in ("relu", "gelu", "sigmoid", "tanh", "softmax", "silu"):
+        assert callable(getattr(F, name))
+    assert finetune.adamw_init is nb.nn.adamw_init and finetune.adamw_update is nb.nn.adamw_update
+    for name in ("shard_op", "all_gather_op", "gather_all_axes_op", "all_reduce_op", "pmean_op", "reduce_scatter_op",
+                 "ppermute_op", "all_to_all_op", "distributed_broadcast_op", "axis_index_op", "CollectiveOperation"):
+        assert hasattr(C, name), name
+    assert C.all_reduce_op.name == "all_reduce" and C.pmean_op.name == "pmean"
+    leaves, names, td = pytree.tree_flatten_full({"b": [1, (2, 3)], "a": {"x": 4}})
+    assert leaves == [4, 1, 2, 3] and names == ["a.x", "b[0]", "b[1][0]", "b[1][1]"]
+    assert pytree.leaf_names(td, "lora") == ["lora.a.x", "lora.b[0]", "lora.b[1][0]", "lora.b[1][1]"]
