@@ -1,12 +1,14 @@
 """Runtime flags (reference: nabla/config.py:26-109).
 
-Three ContextVar-backed flags with environment defaults, module-level read access
+ContextVar-backed flags with environment defaults, module-level read access
 (``config.TRACING``), setters and scoped context managers:
 
 * ``EAGER_MAX_GRAPH``  - execute every op immediately instead of deferring to ``realize()``
   (name kept from the reference; here it means "eager dispatch").
 * ``VERIFY_EAGER_SHAPES`` - cross-check predicted per-shard shapes against produced buffers.
 * ``TRACING`` - set while a function is traced for ``compile``; ``realize_all`` is a no-op.
+* ``DETERMINISTIC`` - deterministic replay (not in the reference, whose backend has no timing-dependent
+  kernels of its own): see ``deterministic``.
 """
 from __future__ import annotations
 
@@ -27,7 +29,12 @@ _TRACING = ContextVar("nabla_tracing", default=False)
 # (cond) pick a lowering that stays on the device
 _CAPTURABLE = ContextVar("nabla_capturable_trace", default=False)
 
-_FLAGS = {"EAGER_MAX_GRAPH": _EAGER, "VERIFY_EAGER_SHAPES": _VERIFY, "TRACING": _TRACING}
+# deterministic replay: every kernel path whose result or work order depends on timing is swapped
+# for one that does not (see `deterministic`)
+_DETERMINISTIC = ContextVar("nabla_deterministic", default=_env("NABLA_B200_DETERMINISTIC"))
+
+_FLAGS = {"EAGER_MAX_GRAPH": _EAGER, "VERIFY_EAGER_SHAPES": _VERIFY, "TRACING": _TRACING,
+          "DETERMINISTIC": _DETERMINISTIC}
 
 
 def __getattr__(name: str):
@@ -80,6 +87,29 @@ def capturable_trace(v: bool = True):
 
 def is_capturable_trace() -> bool:
     return _CAPTURABLE.get()
+
+
+def deterministic(v: bool = True):
+    """Scope in which two runs of the same program from the same state give the same bits and walk
+    their work in the same order (also switched on for a whole process by ``NABLA_B200_DETERMINISTIC=1``):
+
+    * sums that use atomics (embedding scatter-add) take a sorted, serial-per-row path;
+    * the fused GEMM + all-reduce hands its reduce jobs to CTAs in a fixed order instead of
+      first-come-first-served, and adds the ranks' partial tiles with peer loads in rank order
+      instead of in the switch; the all-reduce / all-gather kernels likewise leave ``multimem`` off;
+    * copies and optimizer updates that normally run on side streams stay on the launching stream.
+
+    Timing-dependent bugs (a missing flag wait, a buffer reused too early) then either reproduce on
+    every run or never, and `nabla_b200.utils.replay.replay_check` can tell which."""
+    return _scoped(_DETERMINISTIC, v)
+
+
+def set_deterministic(v: bool) -> None:
+    _DETERMINISTIC.set(bool(v))
+
+
+def is_deterministic() -> bool:
+    return _DETERMINISTIC.get()
 
 
 _DEBUG_ON = ("1", "true", "TRUE", "True")

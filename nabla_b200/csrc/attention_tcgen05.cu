@@ -30,6 +30,7 @@
 // A small kernel before the backward computes delta = rowsum(dO * O) and log2-domain row
 // statistics padded to whole tiles.
 #include "sm100_ptx.cuh"
+#include "nb_debug.cuh"
 
 namespace nba {
 using namespace nb;
@@ -38,8 +39,14 @@ constexpr int BT = 128;          // tile edge, queries and keys
 constexpr int NTHREADS = 384;
 constexpr float LOG2E = 1.4426950408889634f;
 
+// Tile load at (column c0, row c1, head c2, batch c3) of a [batch][heads][rows][head_dim] bf16 tensor.
+// Debug build: the origin lies inside the tensor and c0 starts on a 16-byte boundary, else the copy is
+// not issued (the consumer's bounded wait then ends the kernel with an error status).
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2,
-                                            int c3) {
+                                            int c3, int rows, int heads, int batch) {
+  if (!(NB_ALIGNED(NB_SITE_ATTN_TMA_COORD, c0 * 2, 16) && NB_IN_BOUNDS(NB_SITE_ATTN_TMA_COORD, c1, rows) &&
+        NB_IN_BOUNDS(NB_SITE_ATTN_TMA_COORD, c2, heads) && NB_IN_BOUNDS(NB_SITE_ATTN_TMA_COORD, c3, batch)))
+    return;
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4, %5, %6}], [%2];"
@@ -230,7 +237,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_arrive_expect_tx(&q_full[t], L::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c)
-          tma_load_4d(sQ + t * L::TILE_BYTES + c * (BT * 128), &tmQ, &q_full[t], c * 64, q0 + t * BT, h, b);
+          tma_load_4d(sQ + t * L::TILE_BYTES + c * (BT * 128), &tmQ, &q_full[t], c * 64, q0 + t * BT, h, b, args.Sq, args.H, args.B);
       }
       for (int j = 0; j < n_max; ++j) {
         const int st = j & 1;
@@ -239,12 +246,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_arrive_expect_tx(&k_full[st], L::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c)
-          tma_load_4d(sK + st * L::TILE_BYTES + c * (BT * 128), &tmK, &k_full[st], c * 64, j * BT, h, b);
+          tma_load_4d(sK + st * L::TILE_BYTES + c * (BT * 128), &tmK, &k_full[st], c * 64, j * BT, h, b, args.Skv, args.H, args.B);
         if (!mbar_wait(&v_empty[st], ph)) { atomicExch(args.status, NB_ERR_TIMEOUT_PRODUCER); break; }
         mbar_arrive_expect_tx(&v_full[st], L::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c)
-          tma_load_4d(sV + st * L::TILE_BYTES + c * (BT * 128), &tmV, &v_full[st], c * 64, j * BT, h, b);
+          tma_load_4d(sV + st * L::TILE_BYTES + c * (BT * 128), &tmV, &v_full[st], c * 64, j * BT, h, b, args.Skv, args.H, args.B);
       }
     }
   } else if (warp == 1) {
@@ -559,8 +566,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_arrive_expect_tx(kv_full, 2 * L::TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < HD / 64; ++c) {
-        tma_load_4d(sK + c * (BT * 128), &tmK, kv_full, c * 64, k0, h, b);
-        tma_load_4d(sV + c * (BT * 128), &tmV, kv_full, c * 64, k0, h, b);
+        tma_load_4d(sK + c * (BT * 128), &tmK, kv_full, c * 64, k0, h, b, args.Skv, args.H, args.B);
+        tma_load_4d(sV + c * (BT * 128), &tmV, kv_full, c * 64, k0, h, b, args.Skv, args.H, args.B);
       }
       for (int it = 0; it < n_it; ++it) {
         const int st = it & 1;
@@ -570,13 +577,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         mbar_arrive_expect_tx(&q_full[st], L::TILE_BYTES + BT * 4);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c)
-          tma_load_4d(sQ + st * L::TILE_BYTES + c * (BT * 128), &tmQ, &q_full[st], c * 64, q0, h, b);
+          tma_load_4d(sQ + st * L::TILE_BYTES + c * (BT * 128), &tmQ, &q_full[st], c * 64, q0, h, b, args.Sq, args.H, args.B);
+        if (!NB_IN_BOUNDS(NB_SITE_ATTN_STAT_INDEX, q0 + BT - 1, args.Sq_pad)) break;   // debug build only
         bulk_load_1d(s_nlse2 + st * BT, args.nlse2 + bh * args.Sq_pad + q0, BT * 4, &q_full[st]);
         if (!mbar_wait(&do_empty[st], ph)) { atomicExch(args.status, NB_ERR_TIMEOUT_PRODUCER); break; }
         mbar_arrive_expect_tx(&do_full[st], L::TILE_BYTES + BT * 4);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c)
-          tma_load_4d(sDO + st * L::TILE_BYTES + c * (BT * 128), &tmDO, &do_full[st], c * 64, q0, h, b);
+          tma_load_4d(sDO + st * L::TILE_BYTES + c * (BT * 128), &tmDO, &do_full[st], c * 64, q0, h, b, args.Sq, args.H, args.B);
         bulk_load_1d(s_ndelta + st * BT, args.ndelta + bh * args.Sq_pad + q0, BT * 4, &do_full[st]);
       }
     }
@@ -856,8 +864,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_arrive_expect_tx(qdo_full, 2 * L::TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < HD / 64; ++c) {
-        tma_load_4d(sQ + c * (BT * 128), &tmQ, qdo_full, c * 64, q0, h, b);
-        tma_load_4d(sDO + c * (BT * 128), &tmDO, qdo_full, c * 64, q0, h, b);
+        tma_load_4d(sQ + c * (BT * 128), &tmQ, qdo_full, c * 64, q0, h, b, args.Sq, args.H, args.B);
+        tma_load_4d(sDO + c * (BT * 128), &tmDO, qdo_full, c * 64, q0, h, b, args.Sq, args.H, args.B);
       }
       for (int j = 0; j < n; ++j) {
         const int ks = j % KST, vs = j & 1;
@@ -865,12 +873,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_arrive_expect_tx(&k_full[ks], L::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c)
-          tma_load_4d(sK + ks * L::TILE_BYTES + c * (BT * 128), &tmK, &k_full[ks], c * 64, j * BT, h, b);
+          tma_load_4d(sK + ks * L::TILE_BYTES + c * (BT * 128), &tmK, &k_full[ks], c * 64, j * BT, h, b, args.Skv, args.H, args.B);
         if (!mbar_wait(&v_empty[vs], ((j >> 1) & 1) ^ 1)) { atomicExch(args.status, NB_ERR_TIMEOUT_PRODUCER); break; }
         mbar_arrive_expect_tx(&v_full[vs], L::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c)
-          tma_load_4d(sV + vs * L::TILE_BYTES + c * (BT * 128), &tmV, &v_full[vs], c * 64, j * BT, h, b);
+          tma_load_4d(sV + vs * L::TILE_BYTES + c * (BT * 128), &tmV, &v_full[vs], c * 64, j * BT, h, b, args.Skv, args.H, args.B);
       }
     }
   } else if (warp == 1) {
@@ -927,8 +935,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int q_idx = q0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;
     const uint32_t a_dp = t_dp + lane_addr + grp * 64;
-    const float nlse2 = args.nlse2[bh * args.Sq_pad + q_idx];      // padded: always in range
-    const float ndelta = args.ndelta[bh * args.Sq_pad + q_idx];
+    // padded to whole tiles, so always in range (the debug build checks it and reads nothing otherwise)
+    const bool stat_ok = NB_IN_BOUNDS(NB_SITE_ATTN_STAT_INDEX, q_idx, args.Sq_pad);
+    const float nlse2 = stat_ok ? args.nlse2[bh * args.Sq_pad + q_idx] : -INFINITY;
+    const float ndelta = stat_ok ? args.ndelta[bh * args.Sq_pad + q_idx] : 0.f;
     const float* mrow = nullptr;
     if (args.mask.ptr != nullptr && q_idx < args.Sq)
       mrow = args.mask.ptr + b * args.mask.sb + h * args.mask.sh + (long long)q_idx * args.mask.sq;
@@ -1253,3 +1263,5 @@ extern "C" int nb_attn_bwd(const void* dO, const void* q, const void* k, const v
   a.status = status;
   return D == 128 ? launch_bwd<128>(tq, tk, tv, tdo, a, s) : launch_bwd<64>(tq, tk, tv, tdo, a, s);
 }
+
+NB_DEBUG_DEFINE(attention)

@@ -4,6 +4,11 @@ Each `.cu` / `.cpp` translation unit listed in ``TARGETS`` becomes one shared li
 ``nabla_b200/lib``. The libraries export plain C symbols and are loaded with ctypes
 (`nabla_b200.native`), so there is no dependency on the torch C++ headers and a full rebuild
 takes seconds. nvcc cross-compiles without a GPU present.
+
+``build_all(debug=True)`` (``python -m nabla_b200.csrc.build --debug``) compiles the same sources
+with ``-DNB_DEBUG_CHECKS`` into ``nabla_b200/lib/debug``: every data- or geometry-derived global,
+peer and TMA coordinate is checked before use (``nb_debug.cuh``); ``NABLA_B200_DEBUG_KERNELS=1``
+makes ``nabla_b200.native`` load that build.
 """
 from __future__ import annotations
 
@@ -50,18 +55,22 @@ def _digest(paths: list[Path], flags: list[str]) -> str:
     return h.hexdigest()
 
 
-def build_all(force: bool = False, verbose: bool = False) -> list[Path]:
-    """Compile every target whose sources changed. Returns the list of built libraries."""
-    LIB.mkdir(exist_ok=True)
+def build_all(force: bool = False, verbose: bool = False, debug: bool = False) -> list[Path]:
+    """Compile every target whose sources changed. Returns the list of built libraries.
+    ``debug=True`` builds the bounds-checked variant into ``lib/debug``."""
+    lib_dir = LIB / "debug" if debug else LIB
+    lib_dir.mkdir(parents=True, exist_ok=True)
     built = []
     for name, (srcs, extra) in TARGETS.items():
         paths = [CSRC / s for s in srcs]
         if not all(p.exists() for p in paths):
             continue
-        out = LIB / name
-        stamp = LIB / (name + ".sha")
+        out = lib_dir / name
+        stamp = lib_dir / (name + ".sha")
         is_cuda = any(p.suffix == ".cu" for p in paths)
         flags = (NVCC_FLAGS if is_cuda else ["-O3", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"]) + extra
+        if debug:
+            flags = flags + ["-DNB_DEBUG_CHECKS"]
         dig = _digest(paths, flags)
         if not force and out.exists() and stamp.exists() and stamp.read_text() == dig:
             built.append(out)
@@ -82,6 +91,6 @@ def build_all(force: bool = False, verbose: bool = False) -> list[Path]:
 
 
 if __name__ == "__main__":
-    libs = build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    libs = build_all(force="--force" in sys.argv, verbose="-v" in sys.argv, debug="--debug" in sys.argv)
     for lib in libs:
         print(lib)

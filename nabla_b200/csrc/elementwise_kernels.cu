@@ -16,6 +16,8 @@
 #include <math.h>
 #include <stdint.h>
 
+#include "nb_debug.cuh"
+
 namespace nbe {
 
 typedef __nv_bfloat16 bf16;
@@ -101,6 +103,7 @@ __global__ void __launch_bounds__(256) binary_kernel(const T* __restrict__ a, co
   for (int u = 0; u < EW_U; ++u) {
     const size_t i = base + (size_t)u * 256 * V;
     if (i >= n) break;
+    if (BMODE == 2 && !NB_IN_BOUNDS(NB_SITE_FLAT_INDEX, (i % inner) + V - 1, inner)) continue;   // debug build
     if (i + V <= n) {
       float x[V], y[V], o[V];
       unpack<T>(ra[u], x);
@@ -291,7 +294,9 @@ __global__ void __launch_bounds__(256) col_reduce_kernel(const T* __restrict__ x
     const long long o = t / tiles_i, i = (t - o * tiles_i) * 32 + lane;
     const long long r0 = R * blockIdx.y / splits, r1 = R * (blockIdx.y + 1) / splits;
     Acc a = red_init(op);
-    if (i < inner) {
+    // debug build: the slice of rows and the last element this lane reads lie inside the tensor
+    if (i < inner && NB_IN_BOUNDS(NB_SITE_REDUCE_INDEX, r1 - 1, R) &&
+        NB_IN_BOUNDS(NB_SITE_REDUCE_INDEX, (o * R + (r1 - 1)) * inner + i, outer * R * inner)) {
       const T* p = x + o * R * inner + i;
       long long r = r0 + w;
       for (; r + 24 < r1; r += 32) {
@@ -340,6 +345,7 @@ __global__ void __launch_bounds__(256) cumsum_kernel(const T* __restrict__ x, T*
   const long long total = outer * inner;
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
     const long long o = t / inner, i = t - o * inner;
+    if (!NB_IN_BOUNDS(NB_SITE_REDUCE_INDEX, (o * R + (R - 1)) * inner + i, outer * R * inner)) continue;
     const T* p = x + o * R * inner + i;
     T* q = out + o * R * inner + i;
     float acc = 0.f;
@@ -448,3 +454,5 @@ int nb_cumsum(const void* x, void* out, long long outer, long long R, long long 
 }
 
 }  // extern "C"
+
+NB_DEBUG_DEFINE(elementwise)

@@ -16,6 +16,8 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 
+#include "nb_debug.cuh"
+
 namespace nbk {
 
 typedef __nv_bfloat16 bf16;
@@ -327,6 +329,7 @@ template <typename T, bool LOG>
 __global__ void __launch_bounds__(256) softmax_kernel(const T* __restrict__ x, T* __restrict__ y, int rows, int D) {
   __shared__ float sh[8];
   const int row = blockIdx.x;
+  if (!NB_IN_BOUNDS(NB_SITE_ROW_INDEX, row, rows)) return;   // debug build: one block per row
   const T* xr = x + (size_t)row * D;
   T* yr = y + (size_t)row * D;
   float m = -INFINITY, s = 0.f;
@@ -356,6 +359,7 @@ __global__ void __launch_bounds__(256) lse_pick_fwd_kernel(const T* __restrict__
                                                           float* __restrict__ picked, int rows, int D) {
   __shared__ float sh[8];
   const int row = blockIdx.x;
+  if (!NB_IN_BOUNDS(NB_SITE_ROW_INDEX, row, rows)) return;   // debug build: one block per row
   const T* xr = logits + (size_t)row * D;
   float m = -INFINITY, s = 0.f;
   constexpr int V = Vec<T>::N;
@@ -394,6 +398,7 @@ __global__ void __launch_bounds__(256) lse_pick_bwd_kernel(const T* __restrict__
                                                           const float* __restrict__ g_pick, T* __restrict__ dlogits,
                                                           int rows, int D) {
   const int row = blockIdx.x;
+  if (!NB_IN_BOUNDS(NB_SITE_ROW_INDEX, row, rows)) return;   // debug build: one block per row
   const T* xr = logits + (size_t)row * D;
   T* dr = dlogits + (size_t)row * D;
   const float l = lse[row];
@@ -515,6 +520,7 @@ __global__ void __launch_bounds__(128) embedding_gather_kernel(const T* __restri
                                                               int n_ids, int D, int vocab) {
   constexpr int V = Vec<T>::N;
   const int i = blockIdx.x;
+  if (!NB_IN_BOUNDS(NB_SITE_ROW_INDEX, i, n_ids)) return;   // debug build: one block per id
   long long id = ids[i];
   const bool ok = id >= 0 && id < vocab;
   const T* src = table + (size_t)(ok ? id : 0) * D;
@@ -535,11 +541,37 @@ __global__ void __launch_bounds__(128) embedding_scatter_add_kernel(float* __res
                                                                    const T* __restrict__ upd, int n_ids, int D,
                                                                    int vocab) {
   const int i = blockIdx.x;
+  if (!NB_IN_BOUNDS(NB_SITE_ROW_INDEX, i, n_ids)) return;   // debug build: one block per id
   const long long id = ids[i];
   if (id < 0 || id >= vocab) return;
   float* dst = acc + (size_t)id * D;
   const T* src = upd + (size_t)i * D;
   for (int c = threadIdx.x; c < D; c += blockDim.x) atomicAdd(dst + c, to_f<T>(src[c]));
+}
+// The same sum without atomics, for runs that must repeat bit for bit: the ids come sorted (stable,
+// `perm[k]` = position of the k-th sorted id in the original order); the block at the head of each
+// run of equal ids adds the run's rows in that order and writes base + sum.
+template <typename T>
+__global__ void __launch_bounds__(128) embedding_scatter_sorted_kernel(const long long* __restrict__ sorted_ids,
+                                                                      const long long* __restrict__ perm,
+                                                                      const T* __restrict__ upd, const T* __restrict__ base,
+                                                                      T* __restrict__ out, int n_ids, int D, int vocab) {
+  const int i = blockIdx.x;
+  if (!NB_IN_BOUNDS(NB_SITE_ROW_INDEX, i, n_ids)) return;
+  const long long id = sorted_ids[i];
+  if (id < 0 || id >= vocab) return;
+  if (i > 0 && sorted_ids[i - 1] == id) return;   // not the head of its run
+  int end = i + 1;
+  while (end < n_ids && sorted_ids[end] == id) ++end;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float acc = 0.f;
+    for (int k = i; k < end; ++k) {
+      const long long src = perm[k];
+      if (!NB_IN_BOUNDS(NB_SITE_EMB_SCATTER_ID, src, n_ids)) continue;
+      acc += to_f<T>(upd[(size_t)src * D + c]);
+    }
+    out[(size_t)id * D + c] = from_f<T>(to_f<T>(base[(size_t)id * D + c]) + acc);
+  }
 }
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256) cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n,
@@ -761,38 +793,49 @@ __global__ void __launch_bounds__(256) pool2d_fwd_kernel(const T* __restrict__ x
     y[i] = from_f<T>(mode == 0 ? acc / (kh * kw) : acc);
   }
 }
+// Backward in gather form: one thread per input pixel sums over the windows that cover it (for max
+// pooling it finds each window's first arg-max again and takes the gradient when that is this
+// pixel). No atomics, so the result does not depend on the order in which blocks run, and dx needs
+// no zero fill and no fp32 staging.
 template <typename T>
 __global__ void __launch_bounds__(256) pool2d_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy,
-                                                        float* __restrict__ dx, int N, int H, int W, int C, int OH,
+                                                        T* __restrict__ dx, int N, int H, int W, int C, int OH,
                                                         int OW, int kh, int kw, int sh, int sw, int ph, int pw, int mode) {
-  const size_t total = (size_t)N * OH * OW * C;
+  const size_t total = (size_t)N * H * W * C;
+  const float inv = 1.f / (kh * kw);
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int c = i % C;
     size_t r = i / C;
-    const int ow = r % OW; r /= OW;
-    const int oh = r % OH;
-    const int n = r / OH;
-    const float g = to_f<T>(dy[i]);
-    if (mode == 0) {
-      const float gg = g / (kh * kw);
-      for (int a = 0; a < kh; ++a)
-        for (int b = 0; b < kw; ++b) {
-          const int ih = oh * sh - ph + a, iw = ow * sw - pw + b;
-          if (ih >= 0 && ih < H && iw >= 0 && iw < W) atomicAdd(dx + (((size_t)n * H + ih) * W + iw) * C + c, gg);
+    const int iw = r % W; r /= W;
+    const int ih = r % H;
+    const int n = r / H;
+    // windows (oh, ow) with oh*sh - ph <= ih < oh*sh - ph + kh, likewise for the width
+    const int th = ih + ph - kh + 1, tw = iw + pw - kw + 1;
+    const int oh_lo = th > 0 ? (th + sh - 1) / sh : 0, oh_hi = min(OH - 1, (ih + ph) / sh);
+    const int ow_lo = tw > 0 ? (tw + sw - 1) / sw : 0, ow_hi = min(OW - 1, (iw + pw) / sw);
+    float acc = 0.f;
+    for (int oh = oh_lo; oh <= oh_hi; ++oh)
+      for (int ow = ow_lo; ow <= ow_hi; ++ow) {
+        const size_t yo = (((size_t)n * OH + oh) * OW + ow) * C + c;
+        if (!NB_IN_BOUNDS(NB_SITE_POOL_INPUT, yo, (size_t)N * OH * OW * C)) continue;
+        const float g = to_f<T>(dy[yo]);
+        if (mode == 0) {
+          acc += g * inv;
+        } else {
+          float best = -INFINITY;
+          int bh = -1, bw = -1;
+          for (int a = 0; a < kh; ++a)
+            for (int b = 0; b < kw; ++b) {
+              const int jh = oh * sh - ph + a, jw = ow * sw - pw + b;
+              if (jh >= 0 && jh < H && jw >= 0 && jw < W) {
+                const float v = to_f<T>(x[(((size_t)n * H + jh) * W + jw) * C + c]);
+                if (v > best) { best = v; bh = jh; bw = jw; }
+              }
+            }
+          if (bh == ih && bw == iw) acc += g;
         }
-    } else {
-      float best = -INFINITY;
-      int bh = -1, bw = -1;
-      for (int a = 0; a < kh; ++a)
-        for (int b = 0; b < kw; ++b) {
-          const int ih = oh * sh - ph + a, iw = ow * sw - pw + b;
-          if (ih >= 0 && ih < H && iw >= 0 && iw < W) {
-            const float v = to_f<T>(x[(((size_t)n * H + ih) * W + iw) * C + c]);
-            if (v > best) { best = v; bh = ih; bw = iw; }
-          }
-        }
-      if (bh >= 0) atomicAdd(dx + (((size_t)n * H + bh) * W + bw) * C + c, g);
-    }
+      }
+    dx[i] = from_f<T>(acc);
   }
 }
 
@@ -817,6 +860,7 @@ __global__ void __launch_bounds__(128) conv2d_direct_kernel(const T* __restrict_
       for (int s = 0; s < S; ++s) {
         const int iw = ow * sw - pl + s;
         if (iw < 0 || iw >= W) continue;
+        if (!NB_IN_BOUNDS(NB_SITE_CONV_INPUT, (((size_t)n * H + ih) * W + iw) * C, (size_t)N * H * W * C)) continue;
         const T* xp = x + (((size_t)n * H + ih) * W + iw) * C;
         const T* wp = w + ((size_t)(r * S + s) * C) * F + f;
         for (int c = 0; c < C; ++c) acc += to_f<T>(xp[c]) * to_f<T>(wp[(size_t)c * F]);
@@ -1042,6 +1086,15 @@ int nb_embedding_scatter_add(float* acc, const long long* ids, const void* upd, 
   return CHECK_LAUNCH();
 }
 
+// out = base + scatter_add(ids, upd) from stably sorted ids; `out` already holds a copy of `base`.
+int nb_embedding_scatter_sorted(const long long* sorted_ids, const long long* perm, const void* upd, const void* base,
+                                void* out, int n_ids, int D, int vocab, int dtype, void* stream) {
+  if (n_ids <= 0) return 0;
+  if (dtype) embedding_scatter_sorted_kernel<bf16><<<n_ids, 128, 0, STREAM>>>(sorted_ids, perm, (const bf16*)upd, (const bf16*)base, (bf16*)out, n_ids, D, vocab);
+  else embedding_scatter_sorted_kernel<float><<<n_ids, 128, 0, STREAM>>>(sorted_ids, perm, (const float*)upd, (const float*)base, (float*)out, n_ids, D, vocab);
+  return CHECK_LAUNCH();
+}
+
 int nb_cast(const void* in, void* out, long long n, int in_dtype, int out_dtype, void* stream) {
   if (n <= 0) return 0;
   const int grid = grid_for((size_t)n, 256);
@@ -1133,13 +1186,13 @@ int nb_pool2d_fwd(const void* x, void* y, int N, int H, int W, int C, int OH, in
   return CHECK_LAUNCH();
 }
 // dx must be a zeroed fp32 buffer of the input's shape.
-int nb_pool2d_bwd(const void* x, const void* dy, float* dx, int N, int H, int W, int C, int OH, int OW, int kh, int kw,
+int nb_pool2d_bwd(const void* x, const void* dy, void* dx, int N, int H, int W, int C, int OH, int OW, int kh, int kw,
                   int sh, int sw, int ph, int pw, int mode, int dtype, void* stream) {
-  const size_t total = (size_t)N * OH * OW * C;
+  const size_t total = (size_t)N * H * W * C;
   if (!total) return 0;
   const int grid = grid_for(total, 256);
-  if (dtype) pool2d_bwd_kernel<bf16><<<grid, 256, 0, STREAM>>>((const bf16*)x, (const bf16*)dy, dx, N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw, mode);
-  else pool2d_bwd_kernel<float><<<grid, 256, 0, STREAM>>>((const float*)x, (const float*)dy, dx, N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw, mode);
+  if (dtype) pool2d_bwd_kernel<bf16><<<grid, 256, 0, STREAM>>>((const bf16*)x, (const bf16*)dy, (bf16*)dx, N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw, mode);
+  else pool2d_bwd_kernel<float><<<grid, 256, 0, STREAM>>>((const float*)x, (const float*)dy, (float*)dx, N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw, mode);
   return CHECK_LAUNCH();
 }
 
@@ -1172,3 +1225,5 @@ int nb_conv2d_wgrad_direct(const void* x, const void* dy, void* dw, int N, int H
 }
 
 }  // extern "C"
+
+NB_DEBUG_DEFINE(fused)

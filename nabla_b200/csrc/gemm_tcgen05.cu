@@ -20,6 +20,7 @@
 // Replaces what the reference obtains from MAX's matmul (nabla/ops/binary.py:197-198) and the
 // matmul + add + relu/gelu composition of nabla/nn/functional/layers.py:30-35.
 #include "sm100_ptx.cuh"
+#include "nb_debug.cuh"
 #include <stdio.h>
 
 namespace nb {
@@ -269,6 +270,17 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
           uint8_t* sB = sA + L::A_BYTES;
           mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
           const int k0 = kb * BLOCK_K;
+          // debug build: every tile origin lies inside its tensor and the innermost coordinate
+          // starts on a 16-byte boundary; a failed check skips the copies (the consumers' bounded
+          // waits then end the kernel) instead of issuing them
+          if (!(NB_IN_BOUNDS(NB_SITE_GEMM_TMA_COORD, k0, args.K) && NB_IN_BOUNDS(NB_SITE_GEMM_TMA_COORD, m0, args.M) &&
+                NB_IN_BOUNDS(NB_SITE_GEMM_TMA_COORD, n0, args.N) && NB_IN_BOUNDS(NB_SITE_GEMM_TMA_COORD, b, args.batch) &&
+                NB_IN_BOUNDS(NB_SITE_GEMM_TMA_COORD, ma0, args.M) &&
+                NB_ALIGNED(NB_SITE_GEMM_TMA_ALIGN, (args.a_mn ? m0 : k0) * 2, 16) &&
+                NB_ALIGNED(NB_SITE_GEMM_TMA_ALIGN, (args.b_mn ? n0 : k0) * 2, 16))) {
+            ok = false;
+            break;
+          }
           if (!args.a_mn) {
             tma_load_3d(sA, tmAuse, &full_bar[stage], k0, ma0, b);
           } else {
@@ -370,9 +382,13 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
       if (!ok) continue;   // keep barrier participation uniform, skip the work
       tc_fence_after();
       const int row = m0 + wq * 32 + lane;
-      const bool row_ok = row < args.M;
-      const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(wq * 32) << 16);
       long long out_off = static_cast<long long>(b) * args.stride_c + static_cast<long long>(row) * args.ldc;
+      // debug build: the first element of this lane's output row lies inside the output
+      const bool row_ok =
+          row < args.M && NB_IN_BOUNDS(NB_SITE_GEMM_STORE, out_off,
+                                       static_cast<long long>(args.batch - 1) * args.stride_c +
+                                           static_cast<long long>(args.M - 1) * args.ldc + 1);
+      const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(wq * 32) << 16);
       void* out_ptr = args.out;
       if (MODE == MODE_RS) {
         // push: the tile goes straight into the memory of the rank that owns these rows, into
@@ -621,10 +637,20 @@ __device__ __forceinline__ void reduce_jobs(const GemmArgs& args, const CommArgs
   const int num_n = (args.N + BN - 1) / BN;
   char* local = reinterpret_cast<char*>(comm.bufs[comm.rank]);
   const unsigned* flags = reinterpret_cast<const unsigned*>(local + comm.flag_off);
+  // comm.ticket == nullptr (deterministic replay): CTA c takes jobs c, c + grid, ... in that order
+  // whatever the timing, so which CTA reduces which tile, and after which other tile, is the same in
+  // every run; with the counter the first free CTA takes the next job
+  int fixed_k = (int)blockIdx.x;
   while (true) {
     __syncthreads();
     if (threadIdx.x == 0) {
-      const int k = atomicAdd(comm.ticket, 1);
+      int k;
+      if (comm.ticket != nullptr) {
+        k = atomicAdd(comm.ticket, 1);
+      } else {
+        k = fixed_k;
+        fixed_k += (int)gridDim.x;
+      }
       const int tmo = (k / num_n) * comm.world + comm.rank;
       s_job = k;
       s_ok = 1;
@@ -824,6 +850,10 @@ __device__ __forceinline__ void gather_jobs(const GemmArgs& args, const CommArgs
     const int tm = remap_m<MODE_AG>(ag_unit(cidx + ui * ncomm, num_m, comm), comm);
     const int blk = tm / comm.mpc;                     // row chunk index in the gathered matrix
     const int p = blk % comm.world, g = blk / comm.world, j = tm - blk * comm.mpc;
+    // debug build: the owner is a rank of the group and the block lies inside its staged shard
+    if (!(NB_IN_BOUNDS(NB_SITE_GEMM_PEER_RANK, p, comm.world) &&
+          NB_IN_BOUNDS(NB_SITE_GEMM_PEER_OFFSET, g * comm.mpc + j, comm.per)))
+      return false;
     if (!((ready_mask >> p) & 1u)) {
       if (!wait_flag_ge(reinterpret_cast<const unsigned*>(local + comm.done_off + READY_OFF + 4 * p), comm.epoch))
         return false;
@@ -910,6 +940,7 @@ __device__ __forceinline__ void push_jobs(const GemmArgs& args, const CommArgs& 
   for (int v = cidx; v < comm.per; v += ncomm) {           // this CTA's own 128-row blocks
     const int g = v / comm.mpc, j = v - g * comm.mpc;
     const int tm = (g * comm.world + comm.rank) * comm.mpc + j;   // the block's place in the gathered A
+    if (!NB_IN_BOUNDS(NB_SITE_GEMM_PEER_OFFSET, tm, comm.per * comm.world)) continue;   // CTA-uniform
     const uint4* src = reinterpret_cast<const uint4*>(comm.own_src + (long long)v * comm.unit_bytes);
     const long long dst_off = comm.a_off + (long long)tm * comm.unit_bytes;
     for (long long base = 0; base < nvec; base += (long long)PU * NUM_THREADS) {
@@ -1129,7 +1160,7 @@ extern "C" int nb_gemm_bf16(const void* A, const void* B, void* C, const void* b
 //   ctr           device counters of the workspace (unsigned[4], zero at creation): the kernel
 //                 takes its all-gather epoch and done target relative to them and a one-thread
 //                 kernel advances them afterwards, so replaying the launches from a CUDA graph works
-//   ticket        device int used as job counter (zeroed here on `stream`)
+//   ticket        device int used as job counter (zeroed here on `stream`); nullptr = fixed job order
 // Returns 0, or a negative code when the shape does not fit (the caller then runs the unfused path).
 extern "C" int nb_gemm_fused_grid() {
   if (nb::g_num_sms == 0) {
@@ -1282,7 +1313,7 @@ extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* 
   c.own_src = reinterpret_cast<const char*>(A);
   if (mode == MODE_AG && arena_bufs != nullptr) c.done_target = 0;   // push: no closing barrier, nothing counted
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (mode != MODE_AG && cudaMemsetAsync(ticket, 0, sizeof(int), s) != cudaSuccess) return -4;
+  if (mode != MODE_AG && ticket != nullptr && cudaMemsetAsync(ticket, 0, sizeof(int), s) != cudaSuccess) return -4;
   if (mode == MODE_AR) return launch_fused<MODE_AR>(ta, tb, ta, g, c, grid, n_gemm, s);
   if (mode == MODE_RS) {
     r = launch_fused<MODE_RS>(ta, tb, ta, g, c, grid, n_gemm, s);
@@ -1303,3 +1334,5 @@ extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* 
   if (r) return r;
   return launch_fused<MODE_AG>(ta, tb, ta_own, g, c, grid, n_gemm, s);
 }
+
+NB_DEBUG_DEFINE(gemm)

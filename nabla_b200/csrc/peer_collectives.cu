@@ -21,6 +21,7 @@
 // While the status word is set every kernel of this file returns at its first barrier without
 // waiting, so the collectives queued behind a lost peer drain at once.
 #include "sm100_ptx.cuh"
+#include "nb_debug.cuh"
 
 namespace nbc {
 using namespace nb;
@@ -68,6 +69,10 @@ __device__ __forceinline__ bool wait_ge(const unsigned* p, unsigned target, int*
 __device__ __forceinline__ bool block_barrier(const Group& g, int phase) {
   __syncthreads();
   bool ok = *reinterpret_cast<const volatile int*>(g.status) == 0;   // an earlier wait on this device gave up
+  // debug build: the group fits the flag pad (blocks x world slots of 4 bytes)
+  ok = ok && NB_IN_BOUNDS(NB_SITE_COMM_PEER_RANK, g.rank, g.world) &&
+       NB_IN_BOUNDS(NB_SITE_COMM_PEER_RANK, g.world - 1, MAX_WORLD) &&
+       NB_IN_BOUNDS(NB_SITE_COMM_FLAG, (blockIdx.x * MAX_WORLD + MAX_WORLD - 1) * 4, MAX_BLOCKS * MAX_WORLD * 4);
   if (!__syncthreads_and(ok)) return false;
   const unsigned val = (g.epoch + *reinterpret_cast<const volatile unsigned*>(g.epoch_ctr)) * 4u + (unsigned)phase;
   if (threadIdx.x < g.world) {
@@ -160,6 +165,8 @@ __global__ void __launch_bounds__(512) allreduce_kernel(Group g, long long off, 
   const long long nvec = n / N;                       // n is padded to a multiple of N * world by the host
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
+  // debug build: 16-byte vectors at a 16-byte offset, whole vectors per rank
+  if (!(NB_ALIGNED(NB_SITE_COMM_OFFSET, off, 16) && NB_IN_BOUNDS(NB_SITE_COMM_OFFSET, n % (N * g.world), 1))) return;
   if (!block_barrier(g, 0)) return;
   const char* mine = reinterpret_cast<const char*>(g.bufs[g.rank]) + FLAG_BYTES + off;
   if (algo == 0) {
@@ -283,6 +290,7 @@ __global__ void __launch_bounds__(512) gather_kernel(Group g, long long off, T* 
   const long long cvec = chunk_elems / N;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
+  if (!(NB_ALIGNED(NB_SITE_COMM_OFFSET, off, 16) && NB_IN_BOUNDS(NB_SITE_COMM_OFFSET, chunk_elems % N, 1))) return;
   if (!block_barrier(g, 0)) return;
   if (mode == 1) {
     for (long long i = tid; i < cvec; i += nthreads) {
@@ -486,3 +494,5 @@ int nb_comm_wait_flag(const unsigned* flag, unsigned target, int* status, unsign
 }
 
 }  // extern "C"
+
+NB_DEBUG_DEFINE(comm)

@@ -12,9 +12,16 @@ from pathlib import Path
 
 import torch
 
-_LIB_DIR = Path(__file__).resolve().parent.parent / "lib"
+# NABLA_B200_DEBUG_KERNELS=1 loads the build with device-side index checks (`csrc/nb_debug.cuh`,
+# `python -m nabla_b200.csrc.build --debug`) from lib/debug instead of the release build.
+DEBUG_KERNELS = os.environ.get("NABLA_B200_DEBUG_KERNELS", "0") == "1"
+_LIB_DIR = Path(__file__).resolve().parent.parent / "lib" / ("debug" if DEBUG_KERNELS else "")
 _libs: dict[str, ctypes.CDLL] = {}
 _status: dict[int, torch.Tensor] = {}
+_debug_rec: dict[int, torch.Tensor] = {}
+# translation units of each library (each has its own nb_debug_bind_<tu> / nb_debug_enabled_<tu>)
+_DEBUG_UNITS = {"libnb_gemm.so": ("gemm",), "libnb_kernels.so": ("fused", "elementwise"),
+                "libnb_attention.so": ("attention",), "libnb_comm.so": ("comm",)}
 
 
 class NativeLibraryMissing(RuntimeError):
@@ -39,14 +46,112 @@ def load(name: str) -> ctypes.CDLL:
         try:
             from ..csrc.build import build_all
 
-            build_all()
+            build_all(debug=DEBUG_KERNELS)
         except Exception as e:  # pragma: no cover - build environment problems
             raise NativeLibraryMissing(f"{name} is not built and building failed: {e}") from e
     if not p.exists():
         raise NativeLibraryMissing(f"{p} not found; run `python -m nabla_b200.csrc.build`")
     lib = ctypes.CDLL(str(p))
     _libs[name] = lib
+    if DEBUG_KERNELS and name in _DEBUG_UNITS:
+        for tu in _DEBUG_UNITS[name]:
+            if getattr(lib, f"nb_debug_enabled_{tu}")() != 1:
+                raise NativeLibraryMissing(f"{p} was not built with -DNB_DEBUG_CHECKS")
+        if torch.cuda.is_available():
+            _debug_bind(lib, name, torch.cuda.current_device())
     return lib
+
+
+# ---------------------------------------------------------------- debug-build index checks
+_DEBUG_CODES = {5: "index out of bounds", 6: "misaligned coordinate"}
+_DEBUG_SITES = {
+    1: "embedding gather: row id", 2: "embedding scatter-add: source row", 3: "cross-entropy: class id",
+    4: "row-wise kernel: row index", 5: "flat element index", 6: "pooling: pixel index",
+    7: "direct convolution: input pixel", 8: "NF4: scale block", 9: "reduction: element index",
+    10: "GEMM: TMA tile coordinate", 11: "GEMM: TMA innermost coordinate alignment", 12: "GEMM epilogue: output offset",
+    13: "fused GEMM + collective: peer rank", 14: "fused GEMM + collective: block offset",
+    15: "attention: TMA tile coordinate", 16: "attention: row-statistics index", 17: "attention: output row",
+    18: "peer collectives: rank / world size", 19: "peer collectives: element offset", 20: "peer collectives: flag slot",
+}
+
+
+def debug_record(device: int | None = None) -> torch.Tensor:
+    """The int32[8] record that the checked kernels of ``device`` write their first failure to."""
+    idx = torch.cuda.current_device() if device is None else int(device)
+    rec = _debug_rec.get(idx)
+    if rec is None:
+        rec = torch.zeros(8, dtype=torch.int32, device=torch.device("cuda", idx))
+        _debug_rec[idx] = rec
+    return rec
+
+
+def _debug_bind(lib: ctypes.CDLL, name: str, device: int) -> None:
+    rec = debug_record(device)
+    with torch.cuda.device(device):
+        for tu in _DEBUG_UNITS[name]:
+            fn = getattr(lib, f"nb_debug_bind_{tu}")
+            fn.argtypes = [ctypes.c_void_p]
+            fn.restype = ctypes.c_int
+            if fn(ctypes.c_void_p(rec.data_ptr())) != 0:
+                raise RuntimeError(f"could not bind the debug record of {name}:{tu}")
+
+
+def debug_bind(device: int | None = None) -> None:
+    """Point every loaded debug library at the record of ``device`` (the libraries bind the device
+    that is current when they are loaded; a process that drives more devices calls this per device)."""
+    if not DEBUG_KERNELS:
+        return
+    idx = torch.cuda.current_device() if device is None else int(device)
+    for name, lib in _libs.items():
+        if name in _DEBUG_UNITS:
+            _debug_bind(lib, name, idx)
+
+
+def debug_selftest(name: str, value: int, limit: int, addr: int = 0, align: int = 16) -> None:
+    """Run the one-thread self-test kernel of every translation unit of library ``name``: it
+    evaluates ``0 <= value < limit`` and ``addr % align == 0`` through the same macros as the real
+    kernels and touches nothing but the record."""
+    lib = load(name)
+    for tu in _DEBUG_UNITS[name]:
+        fn = getattr(lib, f"nb_debug_selftest_{tu}")
+        fn.argtypes = [ctypes.c_longlong] * 4 + [ctypes.c_void_p]
+        fn.restype = ctypes.c_int
+        if fn(int(value), int(limit), int(addr), int(align), stream_ptr()) != 0:
+            raise RuntimeError(f"self-test launch of {name}:{tu} failed")
+
+
+def debug_report(device: int | None = None, clear: bool = True) -> dict | None:
+    """What the checked kernels recorded on ``device`` since the last report: ``None`` when every
+    check passed (or the release build is loaded), else ``{"code", "what", "site", "where", "value",
+    "limit", "count"}`` for the first failed check and the number of failed checks. Synchronises."""
+    if not DEBUG_KERNELS:
+        return None
+    idx = torch.cuda.current_device() if device is None else int(device)
+    rec = _debug_rec.get(idx)
+    if rec is None:
+        return None
+    r = rec.cpu().tolist()
+    if r[0] == 0:
+        return None
+    if clear:
+        rec.zero_()
+    u = lambda lo, hi: ((hi & 0xFFFFFFFF) << 32 | (lo & 0xFFFFFFFF))
+    s64 = lambda v: v - (1 << 64) if v >= (1 << 63) else v
+    return {"code": r[0], "what": _DEBUG_CODES.get(r[0], "unknown"), "site": r[1],
+            "where": _DEBUG_SITES.get(r[1], "unknown"), "value": s64(u(r[2], r[3])), "limit": s64(u(r[4], r[5])),
+            "count": r[6]}
+
+
+class KernelDebugCheckFailed(RuntimeError):
+    """A device-side index check of the debug build failed (the access was skipped)."""
+
+
+def debug_check(device: int | None = None) -> None:
+    """Raise ``KernelDebugCheckFailed`` if a checked kernel recorded a failure."""
+    rep = debug_report(device)
+    if rep is not None:
+        raise KernelDebugCheckFailed(f"{rep['where']}: {rep['what']} (value {rep['value']}, limit {rep['limit']}, "
+                                     f"{rep['count']} failed checks)")
 
 
 def use_native(t: torch.Tensor) -> bool:

@@ -33,6 +33,7 @@ def _L():
             "nb_sgd": [c_vp] * 5 + [c_ll] + [c_f] * 4 + [c_int, c_int, c_vp],
             "nb_embedding_gather": [c_vp] * 3 + [c_int] * 4 + [c_vp],
             "nb_embedding_scatter_add": [c_vp] * 5 + [c_int] * 4 + [c_vp],
+            "nb_embedding_scatter_sorted": [c_vp] * 5 + [c_int] * 4 + [c_vp],
             "nb_cast": [c_vp, c_vp, c_ll, c_int, c_int, c_vp],
             "nb_activation": [c_vp] * 3 + [c_ll, c_int, c_int, c_int, c_vp],
             "nb_rng": [c_vp, c_ll, c_ull, c_ull, c_int, c_f, c_f, c_int, c_vp],
@@ -215,6 +216,17 @@ def embedding_scatter_add(base: torch.Tensor, ids: torch.Tensor, upd: torch.Tens
     V, D = base.shape
     flat = ids.contiguous().view(-1).to(torch.int64)
     u = upd.contiguous().view(-1, D).to(base.dtype)
+    from .. import config
+
+    if config.is_deterministic():
+        # no atomics: stable sort of the ids, then one block per run of equal ids adds the run's rows
+        # in their original order
+        sorted_ids, perm = torch.sort(flat, stable=True)
+        out = base.clone()
+        _ok(_L().nb_embedding_scatter_sorted(ptr(sorted_ids), ptr(perm), ptr(u), ptr(base), ptr(out), flat.numel(), D, V,
+                                             _dt(base), stream_ptr()), "embedding_scatter_sorted")
+        launch_count += 1
+        return out
     acc = torch.zeros((V, D), dtype=torch.float32, device=base.device)
     out = torch.empty_like(base)
     _ok(_L().nb_embedding_scatter_add(ptr(acc), ptr(flat), ptr(u), ptr(base), ptr(out), flat.numel(), D, V, _dt(base),
@@ -334,10 +346,10 @@ def pool2d_bwd(x, dy, kh, kw, sh, sw, ph, pw, mode: str):
     dy = dy.contiguous()
     N, H, W, C = x.shape
     _, OH, OW, _ = dy.shape
-    dx = torch.zeros((N, H, W, C), dtype=torch.float32, device=x.device)
+    dx = torch.empty_like(x)
     _ok(_L().nb_pool2d_bwd(ptr(x), ptr(dy), ptr(dx), N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw,
                            0 if mode == "avg" else 1, _dt(x), stream_ptr()), "pool2d_bwd")
-    return dx.to(x.dtype)
+    return dx
 
 
 def conv2d_direct(x, w, bias, stride, padding):

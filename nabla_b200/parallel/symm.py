@@ -296,6 +296,8 @@ def all_reduce(buf: torch.Tensor, mesh, axes, op: str = "sum", algo: str | None 
             algo = "oneshot"
         else:
             algo = "multimem" if ws.mc_ptr else "twoshot"
+    if algo == "multimem" and _deterministic():
+        algo = "twoshot"          # peer loads in rank order instead of a sum inside the switch
     if algo == "multimem" and (not ws.mc_ptr or opi != 0):
         algo = "twoshot" if opi == 0 else "oneshot"
     ai = {"oneshot": 0, "twoshot": 1, "multimem": 2}[algo]
@@ -306,6 +308,12 @@ def all_reduce(buf: torch.Tensor, mesh, axes, op: str = "sum", algo: str | None 
         raise RuntimeError(f"nb_comm_allreduce failed with code {rc}")
     launch_count += 1
     return out[:n].view(x.shape)
+
+
+def _deterministic() -> bool:
+    from .. import config
+
+    return config.is_deterministic()
 
 
 _gemm_fn = None
@@ -389,11 +397,15 @@ def _launch_fused(mode, ws, a, b, out, bias, aux_out, a_full, M, N, K, lda, ldb,
         ws.parity = 1 - getattr(ws, "parity", 1)
         data_off += ws.parity * half
     p = lambda t: c_vp(0 if t is None else t.data_ptr())
-    rc = fn(mode, p(a), p(b), p(out), p(bias), p(aux_out), p(a_full), ws.buf.data_ptr(), ws.ptrs_dev, ws.mc_ptr,
+    # deterministic replay: reduce jobs in a fixed order (no ticket counter), partial tiles added with
+    # peer loads in rank order (no multicast pointer)
+    det = _deterministic()
+    rc = fn(mode, p(a), p(b), p(out), p(bias), p(aux_out), p(a_full), ws.buf.data_ptr(), ws.ptrs_dev,
+            0 if det else ws.mc_ptr,
             data_off, lib.nb_comm_tile_flag_offset(), lib.nb_comm_done_offset(), M, N, K, lda, ldb, a_mn, b_mn,
             1 if (bias is not None and bias.dtype == torch.float32) else 0, epi, aux, int(gelu_tanh), ws.rank, ws.world,
-            chunk_rows, ws.ctr.data_ptr(), n_comm, ws.ticket.data_ptr(), _status().data_ptr(), arena_ptrs, a_off,
-            arena_mc, _stream())
+            chunk_rows, ws.ctr.data_ptr(), n_comm, 0 if det else ws.ticket.data_ptr(), _status().data_ptr(), arena_ptrs,
+            a_off, 0 if det else arena_mc, _stream())
     if rc != 0:
         raise RuntimeError(f"nb_gemm_fused_bf16(mode={mode}) failed with code {rc} for M={M} N={N} K={K}")
     launch_count += 1
@@ -527,9 +539,11 @@ def all_gather_gemm(a_shard: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_ro
     # faster (0.43 ms against 0.57 ms for 65536 x 1536 x 2048), so multicast is the default for pairs only.
     mm = os.environ.get("NABLA_B200_AG_MULTIMEM", "auto")
     arena_mc = ws.arena.mc_ptr if (push and (mm == "1" or (mm == "auto" and ws.world == 2))) else 0
+    if _deterministic():
+        arena_mc = 0
     cs = chunk_rows
     cur = torch.cuda.current_stream()
-    side = _side_stream(x.device)
+    side = cur if _deterministic() else _side_stream(x.device)
     if not arena_mc:
         # this rank's own rows of the gathered matrix (the kernel moves only the peers' rows): a plain
         # copy on a side stream, issued first so that it runs under the fused kernel (which reads the
@@ -583,7 +597,7 @@ def adamw_reduce(p: torch.Tensor, m: torch.Tensor, v: torch.Tensor, grad_off: in
     bc1 = 1.0 - b1 ** step if step is not None else 1.0
     bc2 = 1.0 - b2 ** step if step is not None else 1.0
     blocks = int(max(1, min(256, (n // 8 + 255) // 256)))
-    rc = _L().nb_comm_adamw_reduce(ws.ptrs_dev, ws.rank, ws.world, ws.ctr.data_ptr(), ar.ptrs_dev, ar.mc_ptr, grad_off,
+    rc = _L().nb_comm_adamw_reduce(ws.ptrs_dev, ws.rank, ws.world, ws.ctr.data_ptr(), ar.ptrs_dev, 0 if _deterministic() else ar.mc_ptr, grad_off,
                                    p.data_ptr(), m.data_ptr(), v.data_ptr(), n, float(lr), float(b1), float(b2),
                                    float(eps), float(wd), float(bc1), float(bc2), float(grad_scale),
                                    c_vp(0 if hyper is None else hyper.data_ptr()), blocks, _status().data_ptr(), _stream())

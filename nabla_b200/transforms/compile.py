@@ -262,7 +262,9 @@ class CompiledFunction:
                 sym.append(f)
                 conc.append(f)
         self._last_owner = owner
-        return (td, tuple(sym)), tuple(conc), leaves, td
+        # a plan (and above all a captured CUDA graph) freezes the kernel variants that were chosen
+        # while it was recorded, so deterministic-replay mode gets entries of its own
+        return (td, tuple(sym), config.is_deterministic()), tuple(conc), leaves, td
 
     # ---- call
     def __call__(self, *args, **kwargs):
@@ -551,7 +553,8 @@ class CompiledFunction:
         # Measured on the 24-layer benchmark step (1 GPU, power-capped at 1 kW): 155.8 ms with the updates
         # on the side stream, 155.2 ms without: the step is energy bound, so hiding the AdamW kernels
         # buys nothing there. The side stream is therefore opt-in; the early placement stays.
-        if rec.side_steps and _os.environ.get("NABLA_B200_OPTIMIZER_STREAM", "0") == "1" and torch.cuda.is_available() \
+        if rec.side_steps and _os.environ.get("NABLA_B200_OPTIMIZER_STREAM", "0") == "1" \
+                and not config.is_deterministic() and torch.cuda.is_available() \
                 and rec.placeholders and rec.placeholders[0].device.label == "gpu":
             cur = torch.cuda.current_stream()
             side = _optimizer_stream(cur.device)

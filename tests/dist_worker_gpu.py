@@ -160,6 +160,38 @@ def main():
                     errs[f"dp_adamw_p_{n_el}_{rep}"] = (p1.float() - pr.float()).abs().max().item()
                     errs[f"dp_adamw_m_{n_el}_{rep}"] = ((m1 - mr).abs().max() / mr.abs().max()).item()
                     errs[f"dp_adamw_v_{n_el}_{rep}"] = ((v1 - vr).abs().max() / vr.abs().max()).item()
+        # deterministic replay: fixed reduce-job order, peer loads in rank order instead of sums in
+        # the switch -> the same bits on every call and on every rank
+        from nabla_b200 import config as nb_config
+
+        det_equal, det_same_on_ranks = True, True
+        with nb_config.deterministic():
+            for (M, N, K) in [(1000, 264, 328), (4096, 2048, 1024)]:
+                torch.manual_seed(21 + rank)
+                a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+                b = torch.randn(K, N, device=dev, dtype=torch.bfloat16)
+                ref = a.float() @ b.float()
+                dist.all_reduce(ref)
+                ys = []
+                for rep in range(3):
+                    ys.append(symm.gemm_all_reduce(a, b, mesh, ("x",)).clone())
+                    torch.cuda.synchronize()
+                errs[f"det_ar_{M}x{N}x{K}"] = ((ys[0].float() - ref).abs().max() / ref.abs().max()).item()
+                det_equal &= all(torch.equal(ys[0], y) for y in ys[1:])
+                hi, lo = ys[0].float().clone(), ys[0].float().clone()
+                dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+                dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+                det_same_on_ranks &= bool(torch.equal(hi, lo))
+            g = torch.randn((1 << 21) + 24, device=dev, dtype=torch.bfloat16)
+            r1 = symm.all_reduce(g, mesh, ("x",)).clone()
+            r2 = symm.all_reduce(g, mesh, ("x",)).clone()
+            torch.cuda.synchronize()
+            det_equal &= bool(torch.equal(r1, r2))
+            gs = g.float().clone()
+            dist.all_reduce(gs)
+            errs["det_allreduce"] = ((r1.float() - gs).abs().max() / gs.abs().max()).item()
+        out["det_equal"] = det_equal
+        out["det_same_on_ranks"] = det_same_on_ranks
         native.check_status()
         out["max_err"] = max(errs.values())
         out["errs"] = {k: v for k, v in errs.items() if v > 2e-2}

@@ -56,6 +56,8 @@ def test_fused_gemm_all_reduce_matches_nccl(nvls, n):
     assert len(rs) == n, res.stdout[-2000:] + res.stderr[-3000:]
     for r in rs:
         assert r["max_err"] < 2e-2 and not r["errs"], r
+        # deterministic-replay mode: the same bits on every call and on every rank
+        assert r["det_equal"] and r["det_same_on_ranks"], r
 
 
 @pytest.mark.parametrize("n", [pytest.param(2, marks=_need(2)), pytest.param(4, marks=_need(4)),
