@@ -227,6 +227,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--small", action="store_true", help="reduced sizes (functional check, not a benchmark number)")
+    ap.add_argument("--dump-plan", default=None, help="rank 0 writes the recorded schedule (one line per step) to this file")
     args = ap.parse_args()
 
     if args.config == "cpu_mlp":
@@ -255,6 +256,10 @@ def main() -> None:
     out.update(n_gpus=world, steps=args.steps, warmup=args.warmup, small=bool(args.small), cuda_graph=_graph())
     if rank == 0:
         print(json.dumps(out), flush=True)
+        if args.dump_plan:
+            with open(args.dump_plan, "w") as f:
+                for c in _COMPILED:
+                    c.dump_plan(file=f)
     finish()
 
 

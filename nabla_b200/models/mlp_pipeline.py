@@ -99,12 +99,13 @@ def gpipe_loss(w, b, xs: Tensor, ys: Tensor, mesh, stage_axis: str = "stage",
                dp_axis: str | None = None) -> Tensor:
     """Mean squared error of the pipe's outputs against ``ys`` (micro_batches, batch, dim).
 
-    The outputs never leave the last stage: every tick the last stage's rows are compared with
-    their targets in place (a stage mask zeroes the other stages' rows) and the squared error is
-    accumulated per stage; ONE reduction over the stage (and replica) axes at the very end gives the
-    loss. The only communication of a tick is the ``ppermute`` shift, where the reference recipe
-    (examples/07_mlp_pipeline_parallel.ipynb) sums a masked (S, batch, dim) tensor over the stage
-    axis every tick."""
+    The outputs never leave the last stage and no tick does any loss arithmetic: every stage keeps
+    what it computed in the ticks that matter (t >= S - 1) and, after the last tick, ONE masked
+    difference against the targets, one square and one reduction over the stacked
+    (S, micro_batches, batch, dim) tensor give the loss (fp32 accumulation). A tick is therefore the
+    stage's GEMM, the input select and the ``ppermute`` shift, nothing else, where the reference
+    recipe (examples/07_mlp_pipeline_parallel.ipynb) sums a masked (S, batch, dim) tensor over the
+    stage axis every tick."""
     S = mesh.get_axis_size(stage_axis)
     MB, B, D = (int(d) for d in xs.shape)
     two = isinstance(w, (tuple, list))
@@ -116,23 +117,24 @@ def gpipe_loss(w, b, xs: Tensor, ys: Tensor, mesh, stage_axis: str = "stage",
     state_spec = (stage_axis, dp_axis, None)
     state = shard(zeros((S, B, D), dtype=xs.dtype, device=xs.device), mesh, state_spec)
     first = _stage_mask(S, 0, xs, mesh, stage_axis)
-    last = _stage_mask(S, S - 1, xs, mesh, stage_axis)
     perm = _perm(mesh, stage_axis)
     zero_x = zeros((B, D), dtype=xs.dtype, device=xs.device)
-    zero_s = None
-    acc = None
+    kept = []
     for t in range(MB + S - 1):
         fresh = xs[t] if t < MB else zero_x
         fresh = shard(broadcast_to(unsqueeze(fresh, axis=0), (S, B, D)), mesh, state_spec)
         inp = where(first, fresh, state)
         computed = step(inp, w, None if two else unsqueeze(b, axis=1))
         if t >= S - 1:
-            target = shard(broadcast_to(unsqueeze(ys[t - (S - 1)], axis=0), (S, B, D)), mesh, state_spec)
-            if zero_s is None:
-                zero_s = zeros_like_state(computed)
-            d = where(last, computed - target, zero_s)
-            e = cast(reduce_sum(reduce_sum(d * d, axis=2), axis=1), DType.float32)   # (S,), one value per stage
-            acc = e if acc is None else acc + e
+            kept.append(computed)
         if t + 1 < MB + S - 1:
             state = ppermute(computed, perm)
-    return reduce_sum(acc, axis=0) * (1.0 / float(MB * B * D))
+    all_spec = (stage_axis, None, dp_axis, None)
+    got = shard(stack(kept, axis=1), mesh, all_spec)                                   # (S, MB, B, D)
+    want = shard(broadcast_to(unsqueeze(ys, axis=0), (S, MB, B, D)), mesh, all_spec)
+    m = np.zeros((S, 1, 1, 1), dtype=bool)
+    m[S - 1] = True
+    last = shard(constant(m, device=xs.device), mesh, (stage_axis, None, None, None))
+    d = cast(where(last, got - want, zeros_like_state(got)), DType.float32)
+    e = reduce_sum(reduce_sum(reduce_sum(d * d, axis=3), axis=2), axis=1)              # (S,), one value per stage
+    return reduce_sum(e, axis=0) * (1.0 / float(MB * B * D))

@@ -117,10 +117,17 @@ def reduce_scatter(buf: torch.Tensor, mesh, axes: Sequence[str], dim: int) -> to
 
 def permute(buf: torch.Tensor, mesh, perm: Sequence[tuple[int, int]]) -> torch.Tensor:
     """Point-to-point shift: rank ``src`` sends its shard to ``dst`` for every pair; ranks
-    nobody sends to receive zeros. Grouped NCCL send/recv."""
+    nobody sends to receive zeros. One peer-memory kernel per call (``symm.permute``); grouped NCCL
+    send/recv when the native path is off or the payload does not fit it."""
     me = mesh.rank
     if _local_only():
         return buf.clone()
+    nat = _native()
+    if nat is not None and os.environ.get("NABLA_B200_PERMUTE", "native") != "nccl" and nat.permute_supported(buf, mesh, perm):
+        # one peer-memory kernel on every rank of the mesh instead of a grouped NCCL send / recv
+        stats["native_calls"] += 1
+        stats["native_permute"] = stats.get("native_permute", 0) + 1
+        return nat.permute(buf, mesh, perm)
     ops = []
     out = torch.zeros_like(buf)
     send_to = [d for s, d in perm if s == me]

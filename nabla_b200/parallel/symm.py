@@ -45,6 +45,8 @@ def _L():
         lib.nb_comm_adamw_reduce.restype = c_int
         lib.nb_comm_adamw_reduce.argtypes = ([c_vp, c_int, c_int, c_vp, c_vp, c_vp, c_ll, c_vp, c_vp, c_vp, c_ll] +
                                              [ctypes.c_float] * 8 + [c_vp, c_int, c_vp, c_vp])
+        lib.nb_comm_permute.restype = c_int
+        lib.nb_comm_permute.argtypes = [c_vp, c_int, c_int, c_vp, c_ll, c_vp, c_vp, c_ll, c_int, c_int, c_int, c_vp, c_vp]
         lib.nb_comm_wait_flag.restype = c_int
         lib.nb_comm_wait_flag.argtypes = [c_vp, c_uint, c_vp, c_ull, c_vp]
         _lib = lib
@@ -624,6 +626,47 @@ def _gather_call(x: torch.Tensor, mesh, axes, mode: int, chunk_elems: int, out_e
                              1 if x.dtype == torch.bfloat16 else 0, mode, root, blocks, _status().data_ptr(), _stream())
     if rc != 0:
         raise RuntimeError(f"nb_comm_gather failed with code {rc}")
+    launch_count += 1
+    return out
+
+
+def permute_supported(buf: torch.Tensor, mesh, perm) -> bool:
+    """One launch of the peer-memory shift handles a (partial) permutation of the mesh's ranks whose
+    payload is a whole number of 16-byte vectors and fits the workspace."""
+    srcs = [s for s, _ in perm]
+    dsts = [d for _, d in perm]
+    return (buf.is_cuda and len(set(srcs)) == len(srcs) and len(set(dsts)) == len(dsts)
+            and (buf.numel() * buf.element_size()) % 16 == 0 and buf.numel() > 0
+            and buf.numel() * buf.element_size() + 8192 <= DEFAULT_BYTES - 65536)
+
+
+def permute(buf: torch.Tensor, mesh, perm) -> torch.Tensor:
+    """Point-to-point shift over the whole mesh with one peer-memory kernel (`permute_kernel`):
+    rank ``s`` stores its buffer into rank ``d``'s workspace for every pair ``(s, d)``; ranks nobody
+    sends to get zeros. Every rank of the mesh makes the call, whether it sends, receives or neither
+    (reference: nabla/ops/communication/p_permute.py:85-119, a device-to-device copy per pair)."""
+    global launch_count
+    axes = tuple(mesh.axis_names)
+    ws = workspace(mesh, axes)
+    _, ranks = mesh.process_group(axes)
+    me = mesh.rank
+    dst = next((d for s, d in perm if s == me), None)
+    src = next((s for s, d in perm if d == me), None)
+    x = buf.contiguous()
+    if dst == me:                                   # a fixed point of the permutation: nothing crosses a link
+        dst = src = None
+        out = x.clone()
+        keep_own = True
+    else:
+        out = torch.empty_like(x)
+        keep_own = False
+    nbytes = x.numel() * x.element_size()
+    tmp = out if not keep_own else torch.empty_like(x)
+    rc = _L().nb_comm_permute(ws.ptrs_dev, ws.rank, ws.world, ws.ctr.data_ptr(), 0, x.data_ptr(), tmp.data_ptr(), nbytes,
+                              -1 if dst is None else ranks.index(dst), -1 if src is None else ranks.index(src),
+                              8 if nbytes <= (1 << 20) else 32, _status().data_ptr(), _stream())
+    if rc != 0:
+        raise RuntimeError(f"nb_comm_permute failed with code {rc}")
     launch_count += 1
     return out
 

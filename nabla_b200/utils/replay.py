@@ -152,13 +152,14 @@ def replay_check(fn: Callable, *args, repeats: int = 3, seed: int | None = None,
     from the same random seed, and compare the results bit for bit with the first run.
 
     ``fn`` is usually a compiled training step (its donated arguments are why every run gets its own
-    copy). ``check_args=True`` also compares the arguments after the call (parameters and optimizer
-    state updated in place). ``deterministic=False`` runs the release configuration instead, which
+    copy). ``check_args=True`` also compares the arguments after the call (state that a plain function
+    updates in place), except those a compiled function was given with ``donate_argnums``. ``deterministic=False`` runs the release configuration instead, which
     is allowed to differ in the last bit where it uses atomics or in-switch sums: useful to measure how
     much, not as a pass/fail test. The caller's own arguments are never modified."""
     if repeats < 2:
         raise ValueError("replay_check needs at least two runs")
     base_seed = GRAPH.seed if seed is None else int(seed)
+    donated = set(getattr(fn, "donate_argnums", ()) or ())
     ref = None
     mismatches: list[Mismatch] = []
     n_leaves = 0
@@ -168,7 +169,10 @@ def replay_check(fn: Callable, *args, repeats: int = 3, seed: int | None = None,
         _reseed(base_seed)
         with config.deterministic(deterministic):
             out = fn(*a, **kw)
-        snap = _snapshot({"out": out, "args": (a, kw)} if check_args else {"out": out})
+        # a donated argument belongs to the function after the call (its contents are unspecified:
+        # updated in place on one path, copied into a captured graph's own memory on another)
+        kept = tuple(x for i, x in enumerate(a) if i not in donated)
+        snap = _snapshot({"out": out, "args": (kept, kw)} if check_args else {"out": out})
         if torch.cuda.is_available():
             torch.cuda.synchronize()
         if ref is None:

@@ -64,6 +64,25 @@ def main():
         bc = big.clone()
         dist.broadcast(bc, src=0)
         errs["broadcast"] = (symm.broadcast(big, mesh, ("x",), 0) - bc).abs().max().item()
+        # point-to-point shift: a pipeline shift (no wrap-around: rank 0 receives zeros, the last rank
+        # sends nothing), a ring, and a swap of two ranks that leaves the others out; repeated, so
+        # that an inbox is overwritten while the flags and counters carry on
+        for shape, dtype in (((64, 4096), torch.bfloat16), ((3, 5, 8), torch.float32), ((1 << 20,), torch.bfloat16)):
+            for name, perm in (("pipe", [(i, i + 1) for i in range(world - 1)]),
+                               ("ring", [(i, (i + 1) % world) for i in range(world)]),
+                               ("swap", [(0, 1), (1, 0)])):
+                for rep in range(3):
+                    torch.manual_seed(1000 * rep + rank)
+                    x = torch.randn(*shape, device=dev).to(dtype)
+                    got = backend.permute(x, mesh, perm)
+                    src = next((s_ for s_, d_ in perm if d_ == rank), None)
+                    if src is None:
+                        want = torch.zeros_like(x)
+                    else:
+                        torch.manual_seed(1000 * rep + src)
+                        want = torch.randn(*shape, device=dev).to(dtype)
+                    errs[f"permute_{name}_{len(shape)}_{rep}"] = (got.float() - want.float()).abs().max().item()
+        out["native_permute"] = backend.stats.get("native_permute", 0)
         torch.cuda.synchronize()
         native.check_status()
         out["max_err"] = max(errs.values())

@@ -144,11 +144,11 @@ a = torch.randn(333, 136, device=dev, dtype=torch.bfloat16); b = torch.randn(136
 c = gemm.gemm_bf16(a, b)
 out["gemm"] = ((c.float() - a.float() @ b.float()).abs().max() / (a.float() @ b.float()).abs().max()).item()
 q, k, v = (torch.randn(2, 4, 300, 64, device=dev, dtype=torch.bfloat16) for _ in range(3))
-o, lse = attention.sdpa_fwd(q, k, v, causal=True)
+o, lse = attention.sdpa_fwd(q, k, v, causal=True, scale=64 ** -0.5)
 ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float(), is_causal=True)
 out["attn"] = (o.float() - ref).abs().max().item()
 do = torch.randn_like(o)
-dq, dk, dv = attention.sdpa_bwd(do, q, k, v, o, lse, causal=True)
+dq, dk, dv = attention.sdpa_bwd(do, q, k, v, o, lse, causal=True, scale=64 ** -0.5)
 qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
 torch.nn.functional.scaled_dot_product_attention(qf, kf, vf, is_causal=True).backward(do.float())
 out["attn_bwd"] = max((dq.float() - qf.grad).abs().max().item(), (dk.float() - kf.grad).abs().max().item(),

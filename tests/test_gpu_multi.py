@@ -33,18 +33,19 @@ def _run(mode, n, env=None, timeout=300):
     return res, found
 
 
-@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-def test_peer_collectives_match_nccl():
-    res, rs = _run("collectives", 2)
-    assert len(rs) == 2, res.stdout[-2000:] + res.stderr[-3000:]
+def _need(n):
+    return pytest.mark.skipif(_ngpu() < n, reason=f"needs {n} GPUs")
+
+
+@pytest.mark.parametrize("n", [pytest.param(2, marks=_need(2)), pytest.param(4, marks=_need(4))])
+def test_peer_collectives_match_nccl(n):
+    res, rs = _run("collectives", n)
+    assert len(rs) == n, res.stdout[-2000:] + res.stderr[-3000:]
     for r in rs:
         assert r["symm_ready"] and r["max_err"] < 2e-2 and not r["errs"], r
         assert r["timeout_probe_status"] == 4      # the bounded wait reported NB_ERR_TIMEOUT_PEER, context alive
         assert r["canary_ok"]
-
-
-def _need(n):
-    return pytest.mark.skipif(_ngpu() < n, reason=f"needs {n} GPUs")
+        assert r["native_permute"] == 27           # every point-to-point shift went through the peer-memory kernel
 
 
 @pytest.mark.parametrize("n", [pytest.param(2, marks=_need(2)), pytest.param(4, marks=_need(4))])
