@@ -223,7 +223,133 @@ __global__ void __launch_bounds__(128, 4) layernorm_bwd_dx_kernel(const T* __res
   }
 }
 
-// Backward, part 2: dgamma = sum_rows dy * xhat, dbeta = sum_rows dy. Block = 32*V columns x a
+// Backward in one pass (rows of up to 8 vectors per lane): a persistent grid of warps walks the rows,
+// each warp computing dx of its row as above while it also adds the row's dy * xhat and dy into
+// per-lane register accumulators for the columns it holds, so dy and x are read from DRAM once
+// instead of twice. At the end the four warps of a block fold their accumulators through shared
+// memory and the block writes one row of `partial` ([gridDim.x][2][D] fp32), which
+// colsum_partials_kernel adds up into dgamma / dbeta.
+// 16-byte vector <-> pairs of floats, for the packed two-wide fp32 instructions (fma.rn.f32x2).
+template <typename T> __device__ __forceinline__ void unpack_pairs(const uint4& raw, float2* out);
+template <> __device__ __forceinline__ void unpack_pairs<float>(const uint4& raw, float2* out) {
+  out[0] = make_float2(__uint_as_float(raw.x), __uint_as_float(raw.y));
+  out[1] = make_float2(__uint_as_float(raw.z), __uint_as_float(raw.w));
+}
+template <> __device__ __forceinline__ void unpack_pairs<bf16>(const uint4& raw, float2* out) {
+  const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) out[k] = make_float2(__uint_as_float(w[k] << 16), __uint_as_float(w[k] & 0xffff0000u));
+}
+template <typename T> __device__ __forceinline__ uint4 pack_pairs(const float2* in);
+template <> __device__ __forceinline__ uint4 pack_pairs<float>(const float2* in) {
+  return make_uint4(__float_as_uint(in[0].x), __float_as_uint(in[0].y), __float_as_uint(in[1].x), __float_as_uint(in[1].y));
+}
+template <> __device__ __forceinline__ uint4 pack_pairs<bf16>(const float2* in) {
+  unsigned w[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    __nv_bfloat162 h = __float22bfloat162_rn(in[k]);
+    w[k] = *reinterpret_cast<unsigned*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+template <typename T, int VPL>
+__global__ void __launch_bounds__(128, (VPL * Vec<T>::N >= 64 ? 2 : VPL * Vec<T>::N >= 32 ? 3 : 4))
+    layernorm_bwd_fused_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+                               const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
+                               float* __restrict__ partial, int rows, int D) {
+  constexpr int V = Vec<T>::N, P = V / 2;
+  __shared__ float sh[2][32 * V * VPL];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float2 ag[VPL][P], ab[VPL][P];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i)
+#pragma unroll
+    for (int k = 0; k < P; ++k) { ag[i][k] = make_float2(0.f, 0.f); ab[i][k] = make_float2(0.f, 0.f); }
+  for (int row = blockIdx.x * 4 + warp; row < rows; row += gridDim.x * 4) {
+    const T* xr = x + (size_t)row * D;
+    const T* dyr = dy + (size_t)row * D;
+    uint4 xraw[VPL], draw[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int c = (i * 32 + lane) * V;
+      if (c < D) {
+        xraw[i] = *reinterpret_cast<const uint4*>(xr + c);
+        draw[i] = *reinterpret_cast<const uint4*>(dyr + c);
+      }
+    }
+    const float mu = mean[row], rs = rstd[row];
+    const float2 rs2 = make_float2(rs, rs), nmr2 = make_float2(-mu * rs, -mu * rs);
+    float2 s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int c = (i * 32 + lane) * V;
+      if (c < D) {
+        float2 xv[P], dv[P], gm[P];
+        unpack_pairs<T>(xraw[i], xv);
+        unpack_pairs<T>(draw[i], dv);
+        if (gamma) unpack_pairs<T>(*reinterpret_cast<const uint4*>(gamma + c), gm);
+#pragma unroll
+        for (int k = 0; k < P; ++k) {
+          const float2 xh = __ffma2_rn(xv[k], rs2, nmr2);              // (x - mean) * rstd
+          const float2 g = gamma ? __fmul2_rn(dv[k], gm[k]) : dv[k];
+          s1 = __fadd2_rn(s1, g);
+          s2 = __ffma2_rn(g, xh, s2);
+          ag[i][k] = __ffma2_rn(dv[k], xh, ag[i][k]);
+          ab[i][k] = __fadd2_rn(ab[i][k], dv[k]);
+        }
+      }
+    }
+    const float m1 = warp_sum(s1.x + s1.y) / D;
+    const float m2 = warp_sum(s2.x + s2.y) / D;
+    // dx = rstd * (g - m1 - xhat * m2) = g * rstd + (xhat * (-rstd * m2) + (-rstd * m1))
+    const float2 a2 = make_float2(-rs * m2, -rs * m2), b2 = make_float2(-rs * m1, -rs * m1);
+    T* dxr = dx + (size_t)row * D;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int c = (i * 32 + lane) * V;
+      if (c < D) {
+        float2 xv[P], dv[P], gm[P], o[P];
+        unpack_pairs<T>(xraw[i], xv);
+        unpack_pairs<T>(draw[i], dv);
+        if (gamma) unpack_pairs<T>(*reinterpret_cast<const uint4*>(gamma + c), gm);
+#pragma unroll
+        for (int k = 0; k < P; ++k) {
+          const float2 xh = __ffma2_rn(xv[k], rs2, nmr2);
+          const float2 g = gamma ? __fmul2_rn(dv[k], gm[k]) : dv[k];
+          o[k] = __ffma2_rn(g, rs2, __ffma2_rn(xh, a2, b2));
+        }
+        *reinterpret_cast<uint4*>(dxr + c) = pack_pairs<T>(o);
+      }
+    }
+  }
+  for (int w = 0; w < 4; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int c = (i * 32 + lane) * V;
+        if (c < D) {
+#pragma unroll
+          for (int k = 0; k < P; ++k) {
+            sh[0][c + 2 * k] = (w == 0 ? 0.f : sh[0][c + 2 * k]) + ag[i][k].x;
+            sh[0][c + 2 * k + 1] = (w == 0 ? 0.f : sh[0][c + 2 * k + 1]) + ag[i][k].y;
+            sh[1][c + 2 * k] = (w == 0 ? 0.f : sh[1][c + 2 * k]) + ab[i][k].x;
+            sh[1][c + 2 * k + 1] = (w == 0 ? 0.f : sh[1][c + 2 * k + 1]) + ab[i][k].y;
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  float* prow = partial + (size_t)blockIdx.x * 2 * D;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    prow[c] = sh[0][c];
+    prow[D + c] = sh[1][c];
+  }
+}
+
+// Backward, part 2 (rows wider than that): dgamma = sum_rows dy * xhat, dbeta = sum_rows dy. Block = 32*V columns x a
 // slab of rows; 8 warps stride over the slab's rows with register accumulators; partial sums go
 // to `partial` ([gridDim.y][2][D] fp32) and are folded by colsum_partials_kernel.
 template <typename T>
@@ -959,8 +1085,22 @@ int nb_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y
   return CHECK_LAUNCH();
 }
 
-// Number of row slabs (= rows of the `partial` scratch buffer, each 2*D floats).
-int nb_layernorm_bwd_nblocks(int rows) {
+// Number of rows of the `partial` scratch buffer (each 2*D floats) that nb_layernorm_bwd writes for
+// this problem: the grid of the one-pass kernel when the row fits 8 vectors per lane, else the
+// number of row slabs of the two-kernel path.
+static int ln_bwd_vpl(int D, int dtype) { const int V = dtype ? 8 : 4; return (D / V + 31) / 32; }
+static int g_ln_bwd_two_kernels = 0;
+// 1: always take the two-kernel path (dx, then dgamma / dbeta), for comparisons.
+void nb_layernorm_bwd_two_kernels(int on) { g_ln_bwd_two_kernels = on; }
+int nb_layernorm_bwd_nblocks(int rows, int D, int dtype) {
+  const int vpl = ln_bwd_vpl(D, dtype);
+  if (vpl <= 8 && !g_ln_bwd_two_kernels) {
+    const int V = dtype ? 8 : 4;
+    const int cap = 148 * (vpl * V >= 64 ? 2 : vpl * V >= 32 ? 3 : 4);   // resident blocks of the kernel
+    int nb = (rows + 3) / 4;
+    if (nb > cap) nb = cap;
+    return nb < 1 ? 1 : nb;
+  }
   int nb = (rows + 255) / 256;
   if (nb > 128) nb = 128;
   return nb < 1 ? 1 : nb;
@@ -971,11 +1111,17 @@ int nb_layernorm_bwd(const void* dy, const void* x, const void* gamma, const flo
   if (rows <= 0) return 0;
   const int V = dtype ? 8 : 4;
   if (D % V) return -2;
-  const int vpl = (D / V + 31) / 32;
-  const int nb = nb_layernorm_bwd_nblocks(rows);
+  const int vpl = ln_bwd_vpl(D, dtype);
+  const int nb = nb_layernorm_bwd_nblocks(rows, D, dtype);
   const int rpb = (rows + nb - 1) / nb;
   dim3 grid_dx((rows + 3) / 4);
   dim3 grid_gb((D + 32 * V - 1) / (32 * V), nb);
+#define LN_BWD1(T, VPL)                                                                                               \
+  {                                                                                                                   \
+    layernorm_bwd_fused_kernel<T, VPL><<<nb, 128, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)gamma, mean, rstd, \
+                                                               (T*)dx, partial, rows, D);                            \
+    colsum_partials_kernel<T><<<(D + 255) / 256, 256, 0, STREAM>>>(partial, (T*)dgamma, (T*)dbeta, nb, D);            \
+  }
 #define LN_BWD(T, VPL)                                                                                                \
   {                                                                                                                   \
     layernorm_bwd_dx_kernel<T, VPL><<<grid_dx, 128, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)gamma, mean,    \
@@ -984,12 +1130,20 @@ int nb_layernorm_bwd(const void* dy, const void* x, const void* gamma, const flo
                                                               rpb);                                                   \
     colsum_partials_kernel<T><<<(D + 255) / 256, 256, 0, STREAM>>>(partial, (T*)dgamma, (T*)dbeta, nb, D);            \
   }
-  if (dtype) {
-    if (vpl <= 1) LN_BWD(bf16, 1) else if (vpl <= 2) LN_BWD(bf16, 2) else if (vpl <= 4) LN_BWD(bf16, 4)
-    else if (vpl <= 8) LN_BWD(bf16, 8) else if (vpl <= 16) LN_BWD(bf16, 16) else return -3;
+  if (g_ln_bwd_two_kernels) {
+    if (dtype) {
+      if (vpl <= 1) LN_BWD(bf16, 1) else if (vpl <= 2) LN_BWD(bf16, 2) else if (vpl <= 4) LN_BWD(bf16, 4)
+      else if (vpl <= 8) LN_BWD(bf16, 8) else if (vpl <= 16) LN_BWD(bf16, 16) else return -3;
+    } else {
+      if (vpl <= 1) LN_BWD(float, 1) else if (vpl <= 2) LN_BWD(float, 2) else if (vpl <= 4) LN_BWD(float, 4)
+      else if (vpl <= 8) LN_BWD(float, 8) else if (vpl <= 16) LN_BWD(float, 16) else return -3;
+    }
+  } else if (dtype) {
+    if (vpl <= 1) LN_BWD1(bf16, 1) else if (vpl <= 2) LN_BWD1(bf16, 2) else if (vpl <= 4) LN_BWD1(bf16, 4)
+    else if (vpl <= 8) LN_BWD1(bf16, 8) else if (vpl <= 16) LN_BWD(bf16, 16) else return -3;
   } else {
-    if (vpl <= 1) LN_BWD(float, 1) else if (vpl <= 2) LN_BWD(float, 2) else if (vpl <= 4) LN_BWD(float, 4)
-    else if (vpl <= 8) LN_BWD(float, 8) else if (vpl <= 16) LN_BWD(float, 16) else return -3;
+    if (vpl <= 1) LN_BWD1(float, 1) else if (vpl <= 2) LN_BWD1(float, 2) else if (vpl <= 4) LN_BWD1(float, 4)
+    else if (vpl <= 8) LN_BWD1(float, 8) else if (vpl <= 16) LN_BWD(float, 16) else return -3;
   }
   return CHECK_LAUNCH();
 }

@@ -326,27 +326,32 @@ __global__ void __launch_bounds__(512) gather_kernel(Group g, long long off, T* 
 __global__ void barrier_kernel(Group g) { block_barrier(g, 0); }
 
 // ---------------------------------------------------------------- point-to-point shift (ppermute)
-// Every rank of the group runs this kernel in the same call. Rank r stores `in` (nvec 16-byte
-// vectors) into the data region of rank `dst` (its inbox; dst < 0: r sends nothing) and then copies
-// its own inbox to `out` (src < 0: nobody sends to r, `out` is zero-filled). Two group barriers per
-// call: the first says that every rank has finished reading its inbox of the previous call (so it
-// may be overwritten), the second that every store has landed. Block b of the sender writes the
-// vectors that block b of the receiver reads (same grid and same thread <-> vector mapping on every
-// rank), so the per-block barrier covers them. One launch replaces a grouped NCCL send / recv pair,
-// which for the pipeline's 0.5 MB activations is all latency.
-__global__ void __launch_bounds__(512) permute_kernel(Group g, long long off, const V4* __restrict__ in,
+// Every rank of the group runs this kernel in the same call, on a workspace that only these calls
+// use. Rank r stores `in` (nvec 16-byte vectors) into the inbox of rank `dst` (dst < 0: r sends
+// nothing), all ranks meet, and r copies its own inbox to `out` (src < 0: nobody sends to r, `out` is
+// zero-filled). The inbox has two slots used in turn (slot = call number & 1, `slot_bytes` apart):
+// a sender that is one call ahead writes the other slot, and it cannot be two calls ahead, because
+// leaving call n + 1 takes every rank's arrival at that call's barrier, which a rank reaches only
+// after it has read its inbox of call n. So one barrier per call is enough. Block b of the sender
+// writes the vectors that block b of the receiver reads (same grid and same thread <-> vector
+// mapping on every rank), so the per-block barrier covers them. One launch replaces a grouped
+// NCCL send / recv pair, which for the pipeline's 0.5 MB activations is all latency.
+__global__ void __launch_bounds__(512) permute_kernel(Group g, long long slot_bytes, const V4* __restrict__ in,
                                                      V4* __restrict__ out, long long nvec, int dst, int src) {
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
-  if (!(NB_ALIGNED(NB_SITE_COMM_OFFSET, off, 16) && NB_IN_BOUNDS(NB_SITE_COMM_PEER_RANK, dst + 1, g.world + 1) &&
+  const unsigned call = g.epoch + *reinterpret_cast<const volatile unsigned*>(g.epoch_ctr);
+  const long long off = (long long)(call & 1u) * slot_bytes;
+  if (!(NB_ALIGNED(NB_SITE_COMM_OFFSET, slot_bytes, 16) && NB_IN_BOUNDS(NB_SITE_COMM_OFFSET, nvec * 16, slot_bytes + 1) &&
+        NB_IN_BOUNDS(NB_SITE_COMM_PEER_RANK, dst + 1, g.world + 1) &&
         NB_IN_BOUNDS(NB_SITE_COMM_PEER_RANK, src + 1, g.world + 1)))
     return;
-  if (!block_barrier(g, 0)) return;
+  if (*reinterpret_cast<const volatile int*>(g.status) != 0) return;   // an earlier wait on this device gave up
   if (dst >= 0) {
     char* remote = reinterpret_cast<char*>(g.bufs[dst]) + FLAG_BYTES + off;
     for (long long i = tid; i < nvec; i += nthreads) st_peer(remote + i * 16, in[i]);
   }
-  if (!block_barrier(g, 1)) return;
+  if (!block_barrier(g, 0)) return;
   if (src >= 0) {
     const char* mine = reinterpret_cast<const char*>(g.bufs[g.rank]) + FLAG_BYTES + off;
     for (long long i = tid; i < nvec; i += nthreads) out[i] = ld_peer(mine + i * 16);
@@ -522,15 +527,16 @@ int nb_comm_adamw_reduce(void* const* bufs, int rank, int world, unsigned* epoch
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
-// Shift of `nbytes` (a multiple of 16) from `in` to rank `dst`'s `out`; see permute_kernel. `dst` / `src`
-// are ranks of the group or -1.
-int nb_comm_permute(void* const* bufs, int rank, int world, unsigned* epoch_ctr, long long off, const void* in, void* out,
-                    long long nbytes, int dst, int src, int blocks, int* status, void* stream) {
+// Shift of `nbytes` (a multiple of 16, at most `slot_bytes`) from `in` to rank `dst`'s `out`; see
+// permute_kernel. `dst` / `src` are ranks of the group or -1. The workspace behind `bufs` holds the
+// flag pad followed by two inbox slots of `slot_bytes` each and serves no other collective.
+int nb_comm_permute(void* const* bufs, int rank, int world, unsigned* epoch_ctr, long long slot_bytes, const void* in,
+                    void* out, long long nbytes, int dst, int src, int blocks, int* status, void* stream) {
   if (world > MAX_WORLD || blocks > MAX_BLOCKS || blocks < 1) return -2;
-  if ((nbytes & 15) || (off & 15) || dst >= world || src >= world) return -12;
+  if ((nbytes & 15) || (slot_bytes & 15) || nbytes > slot_bytes || dst >= world || src >= world) return -12;
   if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return -11;
   Group g = make_group(bufs, nullptr, rank, world, epoch_ctr, status);
-  permute_kernel<<<blocks, 512, 0, STREAM>>>(g, off, reinterpret_cast<const V4*>(in), reinterpret_cast<V4*>(out),
+  permute_kernel<<<blocks, 512, 0, STREAM>>>(g, slot_bytes, reinterpret_cast<const V4*>(in), reinterpret_cast<V4*>(out),
                                              nbytes / 16, dst, src);
   bump_kernel<<<1, 1, 0, STREAM>>>(epoch_ctr, 1u);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;

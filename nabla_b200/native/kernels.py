@@ -6,6 +6,7 @@ from torch's caching allocator. ``launch_count`` counts kernel launches issued f
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -22,7 +23,7 @@ def _L():
         lib = load("libnb_kernels.so")
         sig = {
             "nb_layernorm_fwd": [c_vp] * 6 + [c_int, c_int, c_f, c_int, c_vp],
-            "nb_layernorm_bwd_nblocks": [c_int],
+            "nb_layernorm_bwd_nblocks": [c_int, c_int, c_int],
             "nb_layernorm_bwd": [c_vp] * 9 + [c_int, c_int, c_int, c_vp],
             "nb_colsum_nparts": [c_int],
             "nb_colsum": [c_vp] * 3 + [c_int] * 4 + [c_vp],
@@ -57,6 +58,11 @@ def _L():
             fn = getattr(lib, name)
             fn.argtypes = args
             fn.restype = c_int
+        lib.nb_layernorm_bwd_two_kernels.argtypes = [c_int]
+        lib.nb_layernorm_bwd_two_kernels.restype = None
+        # NABLA_B200_LN_BWD=two_kernels: dx and dgamma / dbeta in separate passes (the layout for rows
+        # wider than 8 vectors per lane), instead of the one-pass kernel
+        lib.nb_layernorm_bwd_two_kernels(1 if os.environ.get("NABLA_B200_LN_BWD", "fused") == "two_kernels" else 0)
         _lib = lib
     return _lib
 
@@ -114,7 +120,7 @@ def layernorm_bwd(dy: torch.Tensor, x: torch.Tensor, gamma, mean: torch.Tensor, 
     dx = torch.empty_like(x2)
     dgamma = torch.empty(D, dtype=x.dtype, device=x.device)
     dbeta = torch.empty(D, dtype=x.dtype, device=x.device)
-    nb = _L().nb_layernorm_bwd_nblocks(rows)
+    nb = _L().nb_layernorm_bwd_nblocks(rows, D, _dt(x))
     partial = torch.empty((nb, 2, D), dtype=torch.float32, device=x.device)
     g = gamma.contiguous().to(x.dtype) if gamma is not None else None
     _ok(_L().nb_layernorm_bwd(ptr(dy2), ptr(x2), ptr(g), ptr(mean), ptr(rstd), ptr(dx), ptr(dgamma), ptr(dbeta),

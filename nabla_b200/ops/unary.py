@@ -49,6 +49,23 @@ def _sign(x):
 
 
 _relu = _u("ReluOp", torch.relu, lambda x, y: _step(x))
+
+
+def _relu_vjp(self, primals, cotangents, outputs, kwargs):
+    # one kernel (cot * [x > 0]) instead of greater -> cast -> mul
+    from .fused import dact_mul
+
+    return (dact_mul(cotangents, primals[0], "relu"),)
+
+
+def _relu_jvp(self, primals, tangents, outputs, kwargs):
+    from .fused import dact_mul
+
+    return dact_mul(tangents[0], primals[0], "relu")
+
+
+type(_relu).vjp_rule = _relu_vjp
+type(_relu).jvp_rule = _relu_jvp
 _sigmoid = _u("SigmoidOp", torch.sigmoid, lambda x, y: y * (1.0 - y), native="sigmoid")
 _tanh = _u("TanhOp", torch.tanh, lambda x, y: 1.0 - y * y, native="tanh")
 _exp = _u("ExpOp", torch.exp, lambda x, y: y, native="exp")

@@ -228,6 +228,7 @@ def release_all() -> None:
     for ws in set(_workspaces.values()):
         ws.arena = None
     _workspaces.clear()
+    _permute_ws.clear()
     _side_streams.clear()
     gc.collect()
 
@@ -630,45 +631,57 @@ def _gather_call(x: torch.Tensor, mesh, axes, mode: int, chunk_elems: int, out_e
     return out
 
 
+PERMUTE_SLOT_BYTES = int(os.environ.get("NABLA_B200_PERMUTE_SLOT_MB", "32")) * 1024 * 1024
+_permute_ws: dict = {}
+
+
+def _permute_workspace(mesh) -> Workspace:
+    """The whole mesh's workspace for point-to-point shifts: the flag pad and two inbox slots. No other
+    collective uses it, which is what lets ``permute_kernel`` get by with one barrier per call."""
+    axes = tuple(mesh.axis_names)
+    pg, ranks = mesh.process_group(axes)
+    ws = _permute_ws.get(tuple(ranks))
+    if ws is None:
+        ws = Workspace(pg, ranks, _L().nb_comm_flag_bytes() + 2 * PERMUTE_SLOT_BYTES + CANARY_BYTES + 4096)
+        _permute_ws[tuple(ranks)] = ws
+    return ws
+
+
 def permute_supported(buf: torch.Tensor, mesh, perm) -> bool:
     """One launch of the peer-memory shift handles a (partial) permutation of the mesh's ranks whose
-    payload is a whole number of 16-byte vectors and fits the workspace."""
+    payload is a whole number of 16-byte vectors and fits an inbox slot."""
     srcs = [s for s, _ in perm]
     dsts = [d for _, d in perm]
+    nbytes = buf.numel() * buf.element_size()
     return (buf.is_cuda and len(set(srcs)) == len(srcs) and len(set(dsts)) == len(dsts)
-            and (buf.numel() * buf.element_size()) % 16 == 0 and buf.numel() > 0
-            and buf.numel() * buf.element_size() + 8192 <= DEFAULT_BYTES - 65536)
+            and nbytes % 16 == 0 and 0 < nbytes <= PERMUTE_SLOT_BYTES)
 
 
 def permute(buf: torch.Tensor, mesh, perm) -> torch.Tensor:
     """Point-to-point shift over the whole mesh with one peer-memory kernel (`permute_kernel`):
-    rank ``s`` stores its buffer into rank ``d``'s workspace for every pair ``(s, d)``; ranks nobody
+    rank ``s`` stores its buffer into rank ``d``'s inbox for every pair ``(s, d)``; ranks nobody
     sends to get zeros. Every rank of the mesh makes the call, whether it sends, receives or neither
     (reference: nabla/ops/communication/p_permute.py:85-119, a device-to-device copy per pair)."""
     global launch_count
-    axes = tuple(mesh.axis_names)
-    ws = workspace(mesh, axes)
-    _, ranks = mesh.process_group(axes)
+    ws = _permute_workspace(mesh)
+    ranks = ws.ranks
     me = mesh.rank
     dst = next((d for s, d in perm if s == me), None)
     src = next((s for s, d in perm if d == me), None)
     x = buf.contiguous()
-    if dst == me:                                   # a fixed point of the permutation: nothing crosses a link
+    own = dst == me                                 # a fixed point of the permutation: nothing crosses a link,
+    if own:                                         # but the rank still meets the others at the barrier
         dst = src = None
-        out = x.clone()
-        keep_own = True
-    else:
-        out = torch.empty_like(x)
-        keep_own = False
+    out = torch.empty_like(x)
     nbytes = x.numel() * x.element_size()
-    tmp = out if not keep_own else torch.empty_like(x)
-    rc = _L().nb_comm_permute(ws.ptrs_dev, ws.rank, ws.world, ws.ctr.data_ptr(), 0, x.data_ptr(), tmp.data_ptr(), nbytes,
-                              -1 if dst is None else ranks.index(dst), -1 if src is None else ranks.index(src),
-                              8 if nbytes <= (1 << 20) else 32, _status().data_ptr(), _stream())
+    rc = _L().nb_comm_permute(ws.ptrs_dev, ws.rank, ws.world, ws.ctr.data_ptr(), PERMUTE_SLOT_BYTES, x.data_ptr(),
+                              out.data_ptr(), nbytes, -1 if dst is None else ranks.index(dst),
+                              -1 if src is None else ranks.index(src), 8 if nbytes <= (1 << 20) else 32,
+                              _status().data_ptr(), _stream())
     if rc != 0:
         raise RuntimeError(f"nb_comm_permute failed with code {rc}")
     launch_count += 1
-    return out
+    return x.clone() if own else out
 
 
 def all_gather_dim0(x: torch.Tensor, mesh, axes) -> torch.Tensor:
