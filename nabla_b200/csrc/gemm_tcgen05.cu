@@ -66,6 +66,25 @@ struct SmemLayout {
   static constexpr int TOTAL = RING_BYTES + BIAS_BYTES + BAR_BYTES + 112 + OUT_STAGE_BYTES + 1024;  // + alignment slack
 };
 
+// CTA-pair variant (cta_group::2): a 256 x BN tile per pair; each CTA stages its own 128 rows of A and
+// BN / 2 columns of B per k-block (32 KB for BN = 256, against 48 KB for a lone CTA), which is what
+// cuts the shared-memory bytes the tensor core reads per FLOP by a third.
+template <int BN>
+struct SmemLayoutPair {
+  static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
+  static constexpr int B_BYTES = (BN / 2) * BLOCK_K * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 6 : 8;
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int BIAS_BYTES = BN * 4;
+  static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+  static constexpr int OUT_ROW_BYTES = 64 * 2 + 16;
+  static constexpr int OUT_STAGE_BYTES = 4 * 32 * OUT_ROW_BYTES;
+  static constexpr int TOTAL = RING_BYTES + BIAS_BYTES + BAR_BYTES + 112 + OUT_STAGE_BYTES + 1024;
+};
+template <int BN, bool PAIR> struct SmemSelect { using type = SmemLayout<BN>; };
+template <int BN> struct SmemSelect<BN, true> { using type = SmemLayoutPair<BN>; };
+
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& b, int& m, int& n) {
   const int per_batch = num_m * num_n;
   b = t / per_batch;
@@ -164,13 +183,21 @@ __device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
 
 // One CTA's share of the GEMM. `cta` / `nctas` replace blockIdx / gridDim so that the fused
 // kernel can dedicate some CTAs to communication. Returns false if the CTA left early.
-template <int BN, int MODE>
+// PAIR: this CTA is one of a cluster of two (cta_group::2). `cta` / `nctas` then count pairs, a tile
+// is 256 rows (this CTA's 128 rows start at tile * 256 + rank * 128), the tensor map of B has a box
+// of BN / 2 rows, the leader's MMA warp issues for both CTAs and the other CTA's MMA warp only
+// tells the leader when its operands have landed.
+template <int BN, int MODE, bool PAIR = false>
 __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensorMap* tmBp, const GemmArgs& args,
                                          const CommArgs& comm, const int cta, const int nctas,
                                          const CUtensorMap* tmAownp = nullptr) {
   const CUtensorMap& tmA = *tmAp;
   const CUtensorMap& tmB = *tmBp;
-  using L = SmemLayout<BN>;
+  using L = typename SmemSelect<BN, PAIR>::type;
+  constexpr int TILE_M = PAIR ? 2 * BLOCK_M : BLOCK_M;
+  constexpr int BNL = PAIR ? BN / 2 : BN;            // columns of B this CTA stages
+  const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = crank == 0u;
   constexpr int STAGES = L::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -186,14 +213,16 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   // a previous bounded wait failed on this device: do not pile more waits on top of it
-  {
+  // (a pair does not leave early: both CTAs must reach the cluster barriers below, and their waits
+  // are bounded anyway)
+  if (!PAIR) {
     __shared__ int s_abort;
     if (threadIdx.x == 0) s_abort = *reinterpret_cast<volatile int*>(args.status);
     __syncthreads();
     if (s_abort != 0) return false;   // uniform for the whole CTA
   }
 
-  const int num_m = (args.M + BLOCK_M - 1) / BLOCK_M;
+  const int num_m = (args.M + TILE_M - 1) / TILE_M;
   const int num_n = (args.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n * args.batch;
   const int num_kb = (args.K + BLOCK_K - 1) / BLOCK_K;
@@ -202,22 +231,34 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
+      // pair, leader: its own producer's arrival plus the other CTA's "my operands have landed"
+      mbar_init(&full_bar[s], (PAIR && leader) ? 2 : 1);
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(&tmem_full[0], 1);
     mbar_init(&tmem_full[1], 1);
-    mbar_init(&tmem_empty[0], EPI_THREADS);
-    mbar_init(&tmem_empty[1], EPI_THREADS);
+    // pair: one arrival per epilogue warp of both CTAs, all on the leader's barrier
+    mbar_init(&tmem_empty[0], PAIR ? 2 * (EPI_THREADS / 32) : EPI_THREADS);
+    mbar_init(&tmem_empty[1], PAIR ? 2 * (EPI_THREADS / 32) : EPI_THREADS);
     fence_mbar_init();
     fence_proxy_async_smem();
   }
+  if (PAIR) {
+    __syncthreads();
+    cluster_sync_all();              // the other CTA is running before the allocator is asked for the pair
+  }
   if (warp == 2) {
-    tmem_alloc(tmem_slot, 2 * BN);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(tmem_slot, 2 * BN);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, 2 * BN);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();      // the other CTA's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -231,7 +272,7 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
         int b, tm, tn;
         tile_coords(t, num_m, num_n, b, tm, tn);
         tm = remap_m<MODE>(tm, comm);
-        const int m0 = tm * BLOCK_M, n0 = tn * BN;
+        const int m0 = tm * TILE_M + (int)crank * BLOCK_M, n0 = tn * BN + (int)crank * BNL;
         // MODE_AG: this rank's own rows are read from its shard directly (no copy to wait for)
         const CUtensorMap* tmAuse = tmAp;
         int ma0 = m0;
@@ -261,7 +302,7 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
           asm volatile("fence.proxy.async;" ::: "memory");   // the rows were written by bulk copies
         }
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+          if (!(PAIR ? mbar_wait_cluster(&empty_bar[stage], phase ^ 1) : mbar_wait(&empty_bar[stage], phase ^ 1))) {
             ok = false;
             atomicExch(args.status, NB_ERR_TIMEOUT_PRODUCER);
             break;
@@ -273,9 +314,12 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
           // debug build: every tile origin lies inside its tensor and the innermost coordinate
           // starts on a 16-byte boundary; a failed check skips the copies (the consumers' bounded
           // waits then end the kernel) instead of issuing them
-          if (!(NB_IN_BOUNDS(NB_SITE_GEMM_TMA_COORD, k0, args.K) && NB_IN_BOUNDS(NB_SITE_GEMM_TMA_COORD, m0, args.M) &&
-                NB_IN_BOUNDS(NB_SITE_GEMM_TMA_COORD, n0, args.N) && NB_IN_BOUNDS(NB_SITE_GEMM_TMA_COORD, b, args.batch) &&
-                NB_IN_BOUNDS(NB_SITE_GEMM_TMA_COORD, ma0, args.M) &&
+          // (in a pair the second CTA's half tile may start past the edge: those loads read the fill value)
+          if (!(NB_IN_BOUNDS(NB_SITE_GEMM_TMA_COORD, k0, args.K) &&
+                NB_IN_BOUNDS(NB_SITE_GEMM_TMA_COORD, m0, args.M + (PAIR ? BLOCK_M : 0)) &&
+                NB_IN_BOUNDS(NB_SITE_GEMM_TMA_COORD, n0, args.N + (PAIR ? BNL : 0)) &&
+                NB_IN_BOUNDS(NB_SITE_GEMM_TMA_COORD, b, args.batch) &&
+                NB_IN_BOUNDS(NB_SITE_GEMM_TMA_COORD, ma0, args.M + (PAIR ? BLOCK_M : 0)) &&
                 NB_ALIGNED(NB_SITE_GEMM_TMA_ALIGN, (args.a_mn ? m0 : k0) * 2, 16) &&
                 NB_ALIGNED(NB_SITE_GEMM_TMA_ALIGN, (args.b_mn ? n0 : k0) * 2, 16))) {
             ok = false;
@@ -292,7 +336,7 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
             tma_load_3d(sB, &tmB, &full_bar[stage], k0, n0, b);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
+            for (int j = 0; j < BNL / 64; ++j)
               tma_load_3d(sB + j * (BLOCK_K * 128), &tmB, &full_bar[stage], n0 + j * 64, k0, b);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -301,8 +345,28 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16(BLOCK_M, BN, args.a_mn, args.b_mn);
+    if (PAIR && !leader) {
+      // the other CTA of the pair: tell the leader's MMA thread when this CTA's operands of a stage
+      // have landed (an arrival on the leader's full barrier of the same stage)
+      if (lane == 0) {
+        const uint32_t remote_full = mapa_shared(smem_u32(&full_bar[0]), 0u);
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int t = cta; t < num_tiles && ok; t += nctas) {
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (!mbar_wait(&full_bar[stage], phase)) {
+              atomicExch(args.status, NB_ERR_TIMEOUT_MMA);
+              ok = false;
+              break;
+            }
+            mbar_arrive_cluster(remote_full + 8u * stage);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+        }
+      }
+    } else if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(TILE_M, BN, args.a_mn, args.b_mn);
       // Per-operand descriptor constants.
       const uint32_t a_lbo = args.a_mn ? BLOCK_K * 128 : 16, a_sbo = 1024;
       const uint32_t b_lbo = args.b_mn ? BLOCK_K * 128 : 16, b_sbo = 1024;
@@ -316,7 +380,7 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
       for (int t = cta; t < num_tiles && ok; t += nctas, ++it) {
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1)) {
+        if (!(PAIR ? mbar_wait_cluster(&tmem_empty[buf], acc_phase ^ 1) : mbar_wait(&tmem_empty[buf], acc_phase ^ 1))) {
           atomicExch(args.status, NB_ERR_TIMEOUT_MMA);
           ok = false;
           break;
@@ -324,7 +388,7 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase)) {
+          if (!(PAIR ? mbar_wait_cluster(&full_bar[stage], phase) : mbar_wait(&full_bar[stage], phase))) {
             atomicExch(args.status, NB_ERR_TIMEOUT_MMA);
             ok = false;
             break;
@@ -336,13 +400,22 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
           const uint64_t db = make_smem_desc_sw128(sB, b_lbo, b_sbo);
 #pragma unroll
           for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-            umma_f16_ss(tmem_d, da + static_cast<uint64_t>(k * a_kstep), db + static_cast<uint64_t>(k * b_kstep),
-                        idesc, (kb | k) != 0 ? 1u : 0u);
+            if (PAIR)
+              umma_f16_ss_pair(tmem_d, da + static_cast<uint64_t>(k * a_kstep), db + static_cast<uint64_t>(k * b_kstep),
+                               idesc, (kb | k) != 0 ? 1u : 0u);
+            else
+              umma_f16_ss(tmem_d, da + static_cast<uint64_t>(k * a_kstep), db + static_cast<uint64_t>(k * b_kstep),
+                          idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(&empty_bar[stage]);   // frees the smem slot when these MMAs retire
+          // frees the smem slot (of both CTAs of a pair) when these MMAs retire
+          if (PAIR) umma_commit_pair(&empty_bar[stage], 3);
+          else umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(&tmem_full[buf]);
+        if (ok) {
+          if (PAIR) umma_commit_pair(&tmem_full[buf], 3);
+          else umma_commit(&tmem_full[buf]);
+        }
       }
     }
   } else if (warp >= 4) {
@@ -360,7 +433,7 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
       tile_coords(t, num_m, num_n, b, tm, tn);
       const int tm_order = tm;
       tm = remap_m<MODE>(tm, comm);
-      const int m0 = tm * BLOCK_M, n0 = tn * BN;
+      const int m0 = tm * TILE_M + (int)crank * BLOCK_M, n0 = tn * BN;
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       // stage the bias slice of this tile
@@ -572,7 +645,16 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
         }
       }
       tc_fence_before();
-      mbar_arrive(&tmem_empty[buf]);
+      if (PAIR) {
+        // one arrival per warp, on the leader's barrier (it holds the MMA issuer of both CTAs)
+        __syncwarp();
+        if (lane == 0) {
+          if (leader) mbar_arrive(&tmem_empty[buf]);
+          else mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty[buf]), 0u));
+        }
+      } else {
+        mbar_arrive(&tmem_empty[buf]);
+      }
       if (MODE == MODE_AR) {
         // the tile is in this rank's workspace: make it visible system-wide, then count it on
         // the rank that reduces it (tile (tm_order, tn) belongs to rank tm_order % world)
@@ -590,9 +672,11 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
 
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // neither CTA's shared or tensor memory goes away while the other may still use it
   if (warp == 2) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * BN);
+    if (PAIR) tmem_dealloc_pair(tmem_base, 2 * BN);
+    else tmem_dealloc(tmem_base, 2 * BN);
   }
   return true;
 }
@@ -603,6 +687,33 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                          const GemmArgs args) {
   CommArgs none{};
   gemm_cta<BN, MODE_NONE>(&tmA, &tmB, args, none, blockIdx.x, gridDim.x);
+}
+
+// The same GEMM on CTA pairs: launched as clusters of two CTAs, one pair per two SMs.
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                              const GemmArgs args) {
+  CommArgs none{};
+  gemm_cta<BN, MODE_NONE, true>(&tmA, &tmB, args, none, blockIdx.x >> 1, gridDim.x >> 1);
+}
+
+// Probe of the tensor-memory allocator for CTA pairs, run once before the pair GEMM is used: both
+// CTAs of one cluster ask for 256 columns with cta_group::2 and report the base they were given.
+// 2 x 256 columns fit the 512 of an SM, so neither request can wait for the other whichever way the
+// hardware counts them; equal bases mean that the two requests were one allocation made together.
+__global__ void __launch_bounds__(32, 1) pair_alloc_probe_kernel(unsigned* out) {
+  __shared__ uint32_t slot;
+  cluster_sync_all();              // the other CTA is running before the allocator is asked for the pair
+  tmem_alloc_pair(&slot, 256);
+  tmem_relinquish_pair();
+  tc_fence_before();
+  __syncwarp();
+  tc_fence_after();
+  const uint32_t base = slot;
+  if (threadIdx.x == 0) out[cluster_ctarank()] = base;
+  cluster_sync_all();
+  tmem_dealloc_pair(base, 256);
 }
 
 // ------------------------------------------------------------------ fused GEMM + all-reduce
@@ -1079,7 +1190,68 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& 
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
+// 0: lone CTAs only; 1: CTA pairs for 256-wide tiles of problems with at least one 256-row tile per pair
+static int g_pair_mode = 0;
+
+template <int BN>
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, int max_ctas,
+                       cudaStream_t stream) {
+  using L = SmemLayoutPair<BN>;
+  static int max_clusters = -1;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = L::TOTAL;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (max_clusters < 0) {
+    if (cudaFuncSetAttribute(gemm_bf16_tcgen05_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             L::TOTAL) != cudaSuccess)
+      return -2;
+    cfg.gridDim = dim3(2 * (g_num_sms / 2));
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_tcgen05_pair_kernel<BN>, &cfg) != cudaSuccess || n < 1) return -2;
+    max_clusters = n;
+  }
+  const int num_m = (a.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M), num_n = (a.N + BN - 1) / BN;
+  long long tiles = (long long)num_m * num_n * a.batch;
+  int pairs = max_clusters < max_ctas / 2 ? max_clusters : max_ctas / 2;
+  if (tiles < pairs) pairs = (int)tiles;
+  if (pairs < 1) return 0;
+  cfg.gridDim = dim3(2 * pairs);
+  return cudaLaunchKernelEx(&cfg, gemm_bf16_tcgen05_pair_kernel<BN>, ta, tb, a) == cudaSuccess ? 0 : -3;
+}
+
 }  // namespace nb
+
+// CTA-pair GEMM on (1) or off (0). Returns the previous setting.
+extern "C" int nb_gemm_set_pair_mode(int mode) {
+  const int old = nb::g_pair_mode;
+  nb::g_pair_mode = mode;
+  return old;
+}
+
+// Runs pair_alloc_probe_kernel on one cluster; out2 = device unsigned[2] (tensor-memory base of CTA 0, 1).
+extern "C" int nb_gemm_pair_alloc_probe(unsigned* out2, void* stream) {
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3(2);
+  cfg.blockDim = dim3(32);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, nb::pair_alloc_probe_kernel, out2) == cudaSuccess ? 0 : -3;
+}
 
 // C entry point. All leading dimensions / strides are in elements.
 //   A: a_mn == 0 -> [batch][M][K] (K contiguous, row stride lda); a_mn == 1 -> [batch][K][M]
@@ -1116,7 +1288,10 @@ extern "C" int nb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   if (!a_mn) r = make_map(&ta, A, K, M, batch, lda, stride_a, BLOCK_M);
   else       r = make_map(&ta, A, M, K, batch, lda, stride_a, BLOCK_K);
   if (r) return r;
-  if (!b_mn) r = make_map(&tb, B, K, N, batch, ldb, stride_b, bn);
+  // CTA pairs: wide tiles of problems with enough 256 x 256 tiles to give every pair of SMs one
+  const bool pair = g_pair_mode == 1 && bn == 256 && M >= 2 * BLOCK_M &&
+                    (long long)((M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((N + 255) / 256) * batch >= g_num_sms / 2;
+  if (!b_mn) r = make_map(&tb, B, K, N, batch, ldb, stride_b, pair ? bn / 2 : bn);
   else       r = make_map(&tb, B, N, K, batch, ldb, stride_b, BLOCK_K);
   if (r) return r;
   GemmArgs g;
@@ -1139,6 +1314,7 @@ extern "C" int nb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   }
   g.vec_ok = vec ? 1 : 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (pair) return launch_pair<256>(ta, tb, g, max_ctas, s);
   if (bn == 256) return launch<256>(ta, tb, g, max_ctas, s);
   if (bn == 128) return launch<128>(ta, tb, g, max_ctas, s);
   return launch<64>(ta, tb, g, max_ctas, s);

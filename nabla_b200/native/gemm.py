@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -22,8 +23,53 @@ def _get():
         fn.restype = ctypes.c_int
         fn.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 4 + [ctypes.c_longlong] * 8 + [ctypes.c_int] * 8 + [
             ctypes.c_float, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+        lib.nb_gemm_set_pair_mode.argtypes = [ctypes.c_int]
+        lib.nb_gemm_set_pair_mode.restype = ctypes.c_int
+        lib.nb_gemm_pair_alloc_probe.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        lib.nb_gemm_pair_alloc_probe.restype = ctypes.c_int
         _fn = fn
+        if os.environ.get("NABLA_B200_GEMM_PAIR", "0") == "1":
+            set_pair_mode(True)
     return _fn
+
+
+def pair_alloc_probe() -> tuple[int, int]:
+    """Tensor-memory base addresses that the two CTAs of one cluster get when each asks the pair
+    allocator (``tcgen05.alloc.cta_group::2``) for 256 columns. Equal: the two requests are one
+    allocation made together, which is what the CTA-pair GEMM assumes."""
+    from . import load, stream_ptr
+
+    lib = load("libnb_gemm.so")
+    _get()
+    out = torch.full((2,), 0xFFFFFFFF, dtype=torch.int64, device="cuda").to(torch.int32)
+    rc = lib.nb_gemm_pair_alloc_probe(ctypes.c_void_p(out.data_ptr()), stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"nb_gemm_pair_alloc_probe failed with code {rc}")
+    torch.cuda.synchronize()
+    a, b = (int(v) & 0xFFFFFFFF for v in out.tolist())
+    return a, b
+
+
+_pair_checked = False
+
+
+def set_pair_mode(on: bool) -> bool:
+    """Run wide-tile GEMMs on CTA pairs (``cta_group::2``: 256 x 256 tiles, each CTA staging half of
+    B). Switched on only after the allocator probe has shown that a pair's two allocation requests
+    are one joint allocation; otherwise the lone-CTA kernel stays. Returns whether pairs are on."""
+    global _pair_checked
+    from . import load
+
+    lib = load("libnb_gemm.so")
+    _get()
+    if on and not _pair_checked:
+        a, b = pair_alloc_probe()
+        if a != b:
+            lib.nb_gemm_set_pair_mode(0)
+            return False
+        _pair_checked = True
+    lib.nb_gemm_set_pair_mode(1 if on else 0)
+    return bool(on)
 
 
 def _prep(t: torch.Tensor):
