@@ -185,8 +185,8 @@ __device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
 // kernel can dedicate some CTAs to communication. Returns false if the CTA left early.
 // PAIR: this CTA is one of a cluster of two (cta_group::2). `cta` / `nctas` then count pairs, a tile
 // is 256 rows (this CTA's 128 rows start at tile * 256 + rank * 128), the tensor map of B has a box
-// of BN / 2 rows, the leader's MMA warp issues for both CTAs and the other CTA's MMA warp only
-// tells the leader when its operands have landed.
+// of BN / 2 rows, the loads of both CTAs complete on the leader's full barriers, and the leader's MMA
+// warp issues for both CTAs.
 template <int BN, int MODE, bool PAIR = false>
 __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensorMap* tmBp, const GemmArgs& args,
                                          const CommArgs& comm, const int cta, const int nctas,
@@ -231,8 +231,8 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     for (int s = 0; s < STAGES; ++s) {
-      // pair, leader: its own producer's arrival plus the other CTA's "my operands have landed"
-      mbar_init(&full_bar[s], (PAIR && leader) ? 2 : 1);
+      // pair: only the leader's full barriers are used; the loads of both CTAs complete on them
+      mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(&tmem_full[0], 1);
@@ -268,6 +268,8 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const uint32_t leader_full = PAIR ? mapa_shared(smem_u32(&full_bar[0]), 0u) : 0u;
+      (void)leader_full;
       for (int t = cta; t < num_tiles && ok; t += nctas) {
         int b, tm, tn;
         tile_coords(t, num_m, num_n, b, tm, tn);
@@ -309,7 +311,9 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
           }
           uint8_t* sA = ring + stage * L::STAGE_BYTES;
           uint8_t* sB = sA + L::A_BYTES;
-          mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+          // pair: the leader expects the bytes of both CTAs on its barrier; the other CTA only loads
+          if (!PAIR) mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+          else if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * L::STAGE_BYTES);
           const int k0 = kb * BLOCK_K;
           // debug build: every tile origin lies inside its tensor and the innermost coordinate
           // starts on a 16-byte boundary; a failed check skips the copies (the consumers' bounded
@@ -325,19 +329,37 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
             ok = false;
             break;
           }
-          if (!args.a_mn) {
-            tma_load_3d(sA, tmAuse, &full_bar[stage], k0, ma0, b);
-          } else {
+          if (PAIR) {
+            const uint32_t lbar = leader_full + 8u * stage;   // the leader's full barrier of this stage
+            if (!args.a_mn) {
+              tma_load_3d_pair(sA, tmAuse, lbar, k0, ma0, b);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BLOCK_M / 64; ++j)
-              tma_load_3d(sA + j * (BLOCK_K * 128), &tmA, &full_bar[stage], m0 + j * 64, k0, b);
-          }
-          if (!args.b_mn) {
-            tma_load_3d(sB, &tmB, &full_bar[stage], k0, n0, b);
-          } else {
+              for (int j = 0; j < BLOCK_M / 64; ++j)
+                tma_load_3d_pair(sA + j * (BLOCK_K * 128), &tmA, lbar, m0 + j * 64, k0, b);
+            }
+            if (!args.b_mn) {
+              tma_load_3d_pair(sB, &tmB, lbar, k0, n0, b);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BNL / 64; ++j)
-              tma_load_3d(sB + j * (BLOCK_K * 128), &tmB, &full_bar[stage], n0 + j * 64, k0, b);
+              for (int j = 0; j < BNL / 64; ++j)
+                tma_load_3d_pair(sB + j * (BLOCK_K * 128), &tmB, lbar, n0 + j * 64, k0, b);
+            }
+          } else {
+            if (!args.a_mn) {
+              tma_load_3d(sA, tmAuse, &full_bar[stage], k0, ma0, b);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BLOCK_M / 64; ++j)
+                tma_load_3d(sA + j * (BLOCK_K * 128), &tmA, &full_bar[stage], m0 + j * 64, k0, b);
+            }
+            if (!args.b_mn) {
+              tma_load_3d(sB, &tmB, &full_bar[stage], k0, n0, b);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BNL / 64; ++j)
+                tma_load_3d(sB + j * (BLOCK_K * 128), &tmB, &full_bar[stage], n0 + j * 64, k0, b);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -346,25 +368,7 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (PAIR && !leader) {
-      // the other CTA of the pair: tell the leader's MMA thread when this CTA's operands of a stage
-      // have landed (an arrival on the leader's full barrier of the same stage)
-      if (lane == 0) {
-        const uint32_t remote_full = mapa_shared(smem_u32(&full_bar[0]), 0u);
-        int stage = 0;
-        uint32_t phase = 0;
-        bool ok = true;
-        for (int t = cta; t < num_tiles && ok; t += nctas) {
-          for (int kb = 0; kb < num_kb; ++kb) {
-            if (!mbar_wait(&full_bar[stage], phase)) {
-              atomicExch(args.status, NB_ERR_TIMEOUT_MMA);
-              ok = false;
-              break;
-            }
-            mbar_arrive_cluster(remote_full + 8u * stage);
-            if (++stage == STAGES) { stage = 0; phase ^= 1; }
-          }
-        }
-      }
+      // the other CTA of the pair issues nothing: the leader's thread drives both tensor cores
     } else if (lane == 0) {
       const uint32_t idesc = make_idesc_bf16(TILE_M, BN, args.a_mn, args.b_mn);
       // Per-operand descriptor constants.
@@ -1192,12 +1196,13 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& 
 
 // 0: lone CTAs only; 1: CTA pairs for 256-wide tiles of problems with at least one 256-row tile per pair
 static int g_pair_mode = 0;
+static int g_pair_max_clusters = -1;   // co-resident clusters of the pair kernel (set at its first launch)
 
 template <int BN>
 static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, int max_ctas,
                        cudaStream_t stream) {
   using L = SmemLayoutPair<BN>;
-  static int max_clusters = -1;
+  int& max_clusters = g_pair_max_clusters;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1235,6 +1240,9 @@ extern "C" int nb_gemm_set_pair_mode(int mode) {
   nb::g_pair_mode = mode;
   return old;
 }
+
+// Co-resident clusters of the pair kernel on this device (-1 before its first launch).
+extern "C" int nb_gemm_pair_max_clusters() { return nb::g_pair_max_clusters; }
 
 // Runs pair_alloc_probe_kernel on one cluster; out2 = device unsigned[2] (tensor-memory base of CTA 0, 1).
 extern "C" int nb_gemm_pair_alloc_probe(unsigned* out2, void* stream) {

@@ -28,7 +28,11 @@ def _get():
         lib.nb_gemm_pair_alloc_probe.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         lib.nb_gemm_pair_alloc_probe.restype = ctypes.c_int
         _fn = fn
-        if os.environ.get("NABLA_B200_GEMM_PAIR", "0") == "1":
+        # CTA pairs are the default for wide tiles (NABLA_B200_GEMM_PAIR=0: lone CTAs only). The first
+        # call runs the allocator probe, so it must not happen inside a stream capture; `compile`
+        # replays a step once uncaptured before it captures.
+        if os.environ.get("NABLA_B200_GEMM_PAIR", "1") != "0" and torch.cuda.is_available() \
+                and not torch.cuda.is_current_stream_capturing():
             set_pair_mode(True)
     return _fn
 
