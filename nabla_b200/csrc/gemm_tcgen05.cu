@@ -183,10 +183,11 @@ __device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
 
 // One CTA's share of the GEMM. `cta` / `nctas` replace blockIdx / gridDim so that the fused
 // kernel can dedicate some CTAs to communication. Returns false if the CTA left early.
-// PAIR: this CTA is one of a cluster of two (cta_group::2). `cta` / `nctas` then count pairs, a tile
-// is 256 rows (this CTA's 128 rows start at tile * 256 + rank * 128), the tensor map of B has a box
-// of BN / 2 rows, the loads of both CTAs complete on the leader's full barriers, and the leader's MMA
-// warp issues for both CTAs.
+// PAIR: this CTA is one of a cluster of two (cta_group::2). `cta` / `nctas` then count pairs; a pair
+// takes the 128-row tiles 2 * i and 2 * i + 1 (one each: the two CTAs share only the tile of B, so
+// their row blocks need not be neighbours once a fused mode has re-ordered them), the tensor map of
+// B has a box of BN / 2 rows, the loads of both CTAs complete on the leader's full barriers, and the
+// leader's MMA warp issues for both CTAs.
 template <int BN, int MODE, bool PAIR = false>
 __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensorMap* tmBp, const GemmArgs& args,
                                          const CommArgs& comm, const int cta, const int nctas,
@@ -222,6 +223,8 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
     if (s_abort != 0) return false;   // uniform for the whole CTA
   }
 
+  // pair: tiles are counted in pairs of 128-row tiles; an odd last tile leaves the second CTA a tile
+  // past the edge (its loads read the fill value and its epilogue stores nothing)
   const int num_m = (args.M + TILE_M - 1) / TILE_M;
   const int num_n = (args.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n * args.batch;
@@ -273,8 +276,9 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
       for (int t = cta; t < num_tiles && ok; t += nctas) {
         int b, tm, tn;
         tile_coords(t, num_m, num_n, b, tm, tn);
+        if (PAIR) tm = 2 * tm + (int)crank;
         tm = remap_m<MODE>(tm, comm);
-        const int m0 = tm * TILE_M + (int)crank * BLOCK_M, n0 = tn * BN + (int)crank * BNL;
+        const int m0 = tm * BLOCK_M, n0 = tn * BN + (int)crank * BNL;
         // MODE_AG: this rank's own rows are read from its shard directly (no copy to wait for)
         const CUtensorMap* tmAuse = tmAp;
         int ma0 = m0;
@@ -435,9 +439,10 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
     for (int t = cta; t < num_tiles; t += nctas, ++it) {
       int b, tm, tn;
       tile_coords(t, num_m, num_n, b, tm, tn);
+      if (PAIR) tm = 2 * tm + (int)crank;
       const int tm_order = tm;
       tm = remap_m<MODE>(tm, comm);
-      const int m0 = tm * TILE_M + (int)crank * BLOCK_M, n0 = tn * BN;
+      const int m0 = tm * BLOCK_M, n0 = tn * BN;
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       // stage the bias slice of this tile
@@ -1104,7 +1109,9 @@ __device__ __forceinline__ void push_jobs(const GemmArgs& args, const CommArgs& 
   }
 }
 
-template <int BN, int MODE>
+// PAIR: the grid is launched as clusters of two CTAs and n_gemm is even; CTAs 2i and 2i + 1 below
+// n_gemm work as a pair (see gemm_cta), the communication CTAs are unaffected.
+template <int BN, int MODE, bool PAIR = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmAown, const GemmArgs args, const CommArgs comm_in,
@@ -1114,7 +1121,9 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   comm.done_target += *reinterpret_cast<const volatile unsigned*>(comm_in.ctr + 2);
   const bool is_gemm = (int)blockIdx.x < n_gemm;
   if (is_gemm) {
-    if (!gemm_cta<BN, MODE>(&tmA, &tmB, args, comm, blockIdx.x, n_gemm, &tmAown)) return;
+    if (!gemm_cta<BN, MODE, PAIR>(&tmA, &tmB, args, comm, PAIR ? blockIdx.x >> 1 : blockIdx.x,
+                                  PAIR ? n_gemm >> 1 : n_gemm, &tmAown))
+      return;
   } else {
     __shared__ int s_abort2;
     if (threadIdx.x == 0) s_abort2 = *reinterpret_cast<volatile int*>(args.status);
@@ -1194,7 +1203,8 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& 
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-// 0: lone CTAs only; 1: CTA pairs for 256-wide tiles of problems with at least one 256-row tile per pair
+// bit 0: CTA pairs for 256-wide tiles of plain GEMMs with at least one tile pair per two SMs;
+// bit 1: CTA pairs in the fused GEMM + collective kernels (even number of 128-row tiles). 0: lone CTAs only
 static int g_pair_mode = 0;
 static int g_pair_max_clusters = -1;   // co-resident clusters of the pair kernel (set at its first launch)
 
@@ -1234,7 +1244,7 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmA
 
 }  // namespace nb
 
-// CTA-pair GEMM on (1) or off (0). Returns the previous setting.
+// CTA pairs: bit 0 plain GEMM, bit 1 fused GEMM + collective kernels. Returns the previous setting.
 extern "C" int nb_gemm_set_pair_mode(int mode) {
   const int old = nb::g_pair_mode;
   nb::g_pair_mode = mode;
@@ -1297,7 +1307,7 @@ extern "C" int nb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   else       r = make_map(&ta, A, M, K, batch, lda, stride_a, BLOCK_K);
   if (r) return r;
   // CTA pairs: wide tiles of problems with enough 256 x 256 tiles to give every pair of SMs one
-  const bool pair = g_pair_mode == 1 && bn == 256 && M >= 2 * BLOCK_M &&
+  const bool pair = (g_pair_mode & 1) && bn == 256 && M >= 2 * BLOCK_M &&
                     (long long)((M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((N + 255) / 256) * batch >= g_num_sms / 2;
   if (!b_mn) r = make_map(&tb, B, K, N, batch, ldb, stride_b, pair ? bn / 2 : bn);
   else       r = make_map(&tb, B, N, K, batch, ldb, stride_b, BLOCK_K);
@@ -1427,6 +1437,37 @@ static int launch_fused(const CUtensorMap& ta, const CUtensorMap& tb, const CUte
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
+// The same launch with the GEMM CTAs working as pairs (grid and n_gemm even; B's tensor map has a box
+// of BN / 2 rows).
+template <int MODE>
+static int launch_fused_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ta_own,
+                             const nb::GemmArgs& g, const nb::CommArgs& c, int grid, int n_gemm, cudaStream_t s) {
+  using namespace nb;
+  constexpr int BN = 256;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_fused_kernel<BN, MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SmemLayoutPair<BN>::TOTAL) != cudaSuccess)
+      return -2;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = SmemLayoutPair<BN>::TOTAL;
+  cfg.stream = s;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, gemm_fused_kernel<BN, MODE, true>, ta, tb, ta_own, g, c, n_gemm) != cudaSuccess) return -3;
+  bump_fused_kernel<<<1, 1, 0, s>>>(const_cast<unsigned*>(c.ctr), MODE == nb::MODE_AG ? 1u : 0u, c.done_target);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
 extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* out, const void* bias, void* aux_out,
                                   void* a_full, void* ws_local, void* const* ws_bufs, void* mc, long long data_off,
                                   int flag_off, int done_off, int M, int N, int K, long long lda, long long ldb,
@@ -1454,13 +1495,17 @@ extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* 
   if (n_comm_ctas < 1) n_comm_ctas = 1;
   if (n_comm_ctas > grid / 2) n_comm_ctas = grid / 2;
   if (mode == MODE_RS) n_comm_ctas = 0;        // the epilogue pushes the tiles; no communication CTAs
+  // CTA pairs: clusters of two, so the GEMM CTAs and the whole grid come in even numbers (the same
+  // rule on every rank)
+  const bool pair = (g_pair_mode & 2) && (num_m % 2 == 0) && (grid % 2 == 0) && grid >= 4;
+  if (pair && (n_comm_ctas & 1)) n_comm_ctas += 1;
   const int n_gemm = grid - n_comm_ctas;
   CUtensorMap ta, tb;
   int r;
   if (!a_mn) r = make_map(&ta, Aop, K, M, 1, lda, 0, BLOCK_M);
   else       r = make_map(&ta, Aop, M, K, 1, lda, 0, BLOCK_K);
   if (r) return r;
-  if (!b_mn) r = make_map(&tb, B, K, N, 1, ldb, 0, BN);
+  if (!b_mn) r = make_map(&tb, B, K, N, 1, ldb, 0, pair ? BN / 2 : BN);
   else       r = make_map(&tb, B, N, K, 1, ldb, 0, BLOCK_K);
   if (r) return r;
   GemmArgs g{};
@@ -1498,9 +1543,12 @@ extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* 
   if (mode == MODE_AG && arena_bufs != nullptr) c.done_target = 0;   // push: no closing barrier, nothing counted
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (mode != MODE_AG && ticket != nullptr && cudaMemsetAsync(ticket, 0, sizeof(int), s) != cudaSuccess) return -4;
-  if (mode == MODE_AR) return launch_fused<MODE_AR>(ta, tb, ta, g, c, grid, n_gemm, s);
+  if (mode == MODE_AR)
+    return pair ? launch_fused_pair<MODE_AR>(ta, tb, ta, g, c, grid, n_gemm, s)
+                : launch_fused<MODE_AR>(ta, tb, ta, g, c, grid, n_gemm, s);
   if (mode == MODE_RS) {
-    r = launch_fused<MODE_RS>(ta, tb, ta, g, c, grid, n_gemm, s);
+    r = pair ? launch_fused_pair<MODE_RS>(ta, tb, ta, g, c, grid, n_gemm, s)
+             : launch_fused<MODE_RS>(ta, tb, ta, g, c, grid, n_gemm, s);
     if (r) return r;
     const long long rows = M / world;
     const long long n_vec = rows * N / 8;
@@ -1516,7 +1564,8 @@ extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* 
   if ((reinterpret_cast<uintptr_t>(A) & 15)) return -11;
   r = make_map(&ta_own, A, K, M / world, 1, K, 0, BLOCK_M);
   if (r) return r;
-  return launch_fused<MODE_AG>(ta, tb, ta_own, g, c, grid, n_gemm, s);
+  return pair ? launch_fused_pair<MODE_AG>(ta, tb, ta_own, g, c, grid, n_gemm, s)
+              : launch_fused<MODE_AG>(ta, tb, ta_own, g, c, grid, n_gemm, s);
 }
 
 NB_DEBUG_DEFINE(gemm)

@@ -60,7 +60,8 @@ _pair_checked = False
 def set_pair_mode(on: bool) -> bool:
     """Run wide-tile GEMMs on CTA pairs (``cta_group::2``: 256 x 256 tiles, each CTA staging half of
     B). Switched on only after the allocator probe has shown that a pair's two allocation requests
-    are one joint allocation; otherwise the lone-CTA kernel stays. Returns whether pairs are on."""
+    are one joint allocation; otherwise the lone-CTA kernel stays. The fused GEMM + collective kernels
+    follow unless ``NABLA_B200_GEMM_PAIR_FUSED=0``. Returns whether pairs are on."""
     global _pair_checked
     from . import load
 
@@ -72,7 +73,8 @@ def set_pair_mode(on: bool) -> bool:
             lib.nb_gemm_set_pair_mode(0)
             return False
         _pair_checked = True
-    lib.nb_gemm_set_pair_mode(1 if on else 0)
+    fused = os.environ.get("NABLA_B200_GEMM_PAIR_FUSED", "1") != "0"
+    lib.nb_gemm_set_pair_mode((3 if fused else 1) if on else 0)
     return bool(on)
 
 
