@@ -46,6 +46,7 @@ struct GemmArgs {
   int out_fp32, bias_fp32;
   int epi, aux, accumulate, gelu_tanh;
   int vec_ok;               // output/aux rows are 16-byte aligned
+  int vec32_ok;             // ... and 32-byte aligned: a lane's 32 columns go out as 32-byte stores (whole sectors)
   float alpha;              // scale applied to the accumulator before the epilogue
   int* status;              // device status word (0 = ok)
 };
@@ -179,6 +180,13 @@ __device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
   unsigned v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+
+// 32-byte store (one whole sector per lane and instruction; the address must be 32-byte aligned).
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t* w) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+               "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
 }
 
 // One CTA's share of the GEMM. `cta` / `nctas` replace blockIdx / gridDim so that the fused
@@ -481,29 +489,49 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
       }
       const long long aux_off =
           static_cast<long long>(b) * args.stride_aux + static_cast<long long>(row) * args.ld_aux;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int nb0 = n0 + c * 32;
-        if (nb0 >= args.N) break;   // warp-uniform
-        // epilogues with per-element transcendental math are split between the two groups by
-        // 64-column pairs; the plain ones (and the peer-store path, whose staging buffers exist
-        // once per lane quarter) stay with group 0, whose warps then stream the whole tile
-        if (MODE != MODE_RS && heavy) {
-          if (((c >> 1) & 1) != grp) continue;
-        } else if (grp != 0) {
-          break;
+      // epilogues with per-element transcendental math are split between the two groups by
+      // 64-column pairs; the plain ones (and the peer-store path, whose staging buffers exist
+      // once per lane quarter) stay with group 0, whose warps then stream the whole tile.
+      // next_chunk(c): the first 32-column chunk after c that this warp handles (BN / 32: none)
+      auto next_chunk = [&](int c) -> int {
+        for (++c; c < BN / 32; ++c) {
+          if (n0 + c * 32 >= args.N) break;   // warp-uniform
+          if (MODE != MODE_RS && heavy) {
+            if (((c >> 1) & 1) == grp) return c;
+          } else {
+            return grp == 0 ? c : BN / 32;
+          }
         }
-        uint32_t v[32];
-        tmem_ld_32x32(taddr + c * 32, v);
-        tmem_ld_wait();
+        return BN / 32;
+      };
+      // the accumulator chunk after the current one is fetched from tensor memory while the current
+      // one goes through the epilogue math and its stores
+      uint32_t v[32];
+      int c = next_chunk(-1);
+      if (c < BN / 32) tmem_ld_32x32(taddr + c * 32, v);
+#pragma unroll 1
+      while (c < BN / 32) {
+        const int nb0 = n0 + c * 32;
+        tmem_ld_wait_regs(v);
         float f[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * args.alpha + sbias[c * 32 + j];
+        const int c_next = next_chunk(c);
+        if (c_next < BN / 32) tmem_ld_32x32(taddr + c_next * 32, v);
         const bool full = (nb0 + 32 <= args.N) && args.vec_ok;
         // ---- auxiliary output: pre-activation
         if (args.aux == AUX_STORE_PREACT && row_ok) {
           __nv_bfloat16* ap = args.aux_out + aux_off + nb0;
-          if (full) {
+          if (full && args.vec32_ok) {
+            uint32_t pw[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+              pw[j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            st_global_v8(ap, pw);
+            st_global_v8(ap + 16, pw + 8);
+          } else if (full) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               uint4 pk;
@@ -607,7 +635,10 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
         } else if (row_ok) {
           if (args.out_fp32) {
             float* op = reinterpret_cast<float*>(args.out) + out_off + nb0;
-            if (full) {
+            if (full && args.vec32_ok && !args.accumulate) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) st_global_v8(op + q * 8, reinterpret_cast<const uint32_t*>(f) + q * 8);
+            } else if (full) {
 #pragma unroll
               for (int q = 0; q < 8; ++q) {
                 float4 o = make_float4(f[q * 4], f[q * 4 + 1], f[q * 4 + 2], f[q * 4 + 3]);
@@ -623,7 +654,16 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
             }
           } else {
             __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(out_ptr) + out_off + nb0;
-            if (full) {
+            if (full && args.vec32_ok && !args.accumulate) {
+              uint32_t pw[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+                pw[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              st_global_v8(op, pw);
+              st_global_v8(op + 16, pw + 8);
+            } else if (full) {
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 uint4 pk;
@@ -652,6 +692,7 @@ __device__ __forceinline__ bool gemm_cta(const CUtensorMap* tmAp, const CUtensor
             }
           }
         }
+        c = c_next;
       }
       tc_fence_before();
       if (PAIR) {
@@ -1331,6 +1372,12 @@ extern "C" int nb_gemm_bf16(const void* A, const void* B, void* C, const void* b
           (batch == 1 || (stride_aux * 2) % 16 == 0);
   }
   g.vec_ok = vec ? 1 : 0;
+  bool vec32 = vec && ((reinterpret_cast<uintptr_t>(C) & 31) == 0) && ((ldc * oes) % 32 == 0) &&
+               (batch == 1 || (stride_c * oes) % 32 == 0);
+  if (aux == AUX_STORE_PREACT)
+    vec32 = vec32 && ((reinterpret_cast<uintptr_t>(aux_out) & 31) == 0) && ((ld_aux * 2) % 32 == 0) &&
+            (batch == 1 || (stride_aux * 2) % 32 == 0);
+  g.vec32_ok = vec32 ? 1 : 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (pair) return launch_pair<256>(ta, tb, g, max_ctas, s);
   if (bn == 256) return launch<256>(ta, tb, g, max_ctas, s);
@@ -1513,6 +1560,7 @@ extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* 
   g.ldc = N; g.stride_c = (long long)M * N;
   g.a_mn = a_mn; g.b_mn = b_mn; g.out_fp32 = 0; g.accumulate = 0;
   g.alpha = 1.0f; g.status = status; g.vec_ok = 1;
+  g.vec32_ok = 0;   // set below for the mode whose epilogue stores to ordinary memory
   if (mode == MODE_AG) {
     if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(aux_out) & 15)) return -11;
     g.out = out; g.bias = bias; g.bias_fp32 = bias_fp32; g.epi = epi; g.gelu_tanh = gelu_tanh;
@@ -1522,6 +1570,7 @@ extern "C" int nb_gemm_fused_bf16(int mode, const void* A, const void* B, void* 
     g.aux_out = reinterpret_cast<__nv_bfloat16*>(aux_out);
     g.aux_in = reinterpret_cast<const __nv_bfloat16*>(aux_out);
     g.ld_aux = N; g.stride_aux = (long long)M * N;
+    g.vec32_ok = (((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(aux_out)) & 31) == 0 && (N % 16) == 0) ? 1 : 0;
   } else {
     g.out = reinterpret_cast<char*>(ws_local) + data_off;
     g.epi = EPI_NONE; g.aux = AUX_NONE;
