@@ -557,7 +557,7 @@ def all_gather_gemm(a_shard: torch.Tensor, b: torch.Tensor, mesh, axes, chunk_ro
     # copy CTAs: an SM moves about 32 GB/s (pull) to 38 GB/s (push); take as many as it needs to move
     # its share within the GEMM's own time, up to what saturates the link
     if comm_ctas is None:
-        gemm_s = 2.0 * M * N * K / 1.3e15
+        gemm_s = 2.0 * M * N * K / 1.5e15          # the GEMM's own time on CTA pairs
         out_bytes = Ml * K * 2 if arena_mc else (M - Ml) * K * 2
         need = out_bytes / max(gemm_s, 1e-6) / (38e9 if push else 32e9)
         # measured: below 8 copy CTAs a multicast push does not keep up with the GEMM (0.57 ms with 5,
