@@ -21,6 +21,46 @@ def _check_status():
     native.check_status()
 
 
+def test_gemm_on_cta_pairs_matches_lone_ctas_and_fp32():
+    """Wide-tile GEMMs run on CTA pairs (cta_group::2) by default: the pair kernel must have been the
+    one that ran, agree with the lone-CTA kernel (to bf16 rounding) and with an fp32 reference, for every operand layout, for an odd number of 128-row tiles and
+    through the fused epilogues."""
+    from nabla_b200 import native
+    from nabla_b200.native import gemm
+
+    lib = native.load("libnb_gemm.so")
+    assert gemm.set_pair_mode(True)
+    a0, b0 = gemm.pair_alloc_probe()
+    assert a0 == b0
+    torch.manual_seed(4)
+    for (M, N, K) in [(4096, 4608, 320), (19072, 2048, 1024), (4224, 4616, 136)]:
+        for layout in ("NN", "NT", "TN", "TT"):
+            A = torch.randn(K, M, device="cuda", dtype=torch.bfloat16).t() if layout[0] == "T" else \
+                torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+            B = torch.randn(N, K, device="cuda", dtype=torch.bfloat16).t() if layout[1] == "T" else \
+                torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
+            gemm.set_pair_mode(True)
+            c_pair = gemm.gemm_bf16(A, B)
+            assert lib.nb_gemm_pair_max_clusters() > 0          # the pair kernel has been launched
+            gemm.set_pair_mode(False)
+            c_lone = gemm.gemm_bf16(A, B)
+            ref = A.float() @ B.float()
+            assert _rel(c_pair, ref) < 1e-2
+            assert _rel(c_pair, c_lone) < 4e-3, (M, N, K, layout)
+    gemm.set_pair_mode(True)
+    A = torch.randn(8192, 1024, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(1024, 8192, device="cuda", dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(8192, device="cuda", dtype=torch.bfloat16)
+    y, z = gemm.gemm_bf16(A, B, bias=bias, epilogue="gelu", aux="store_preact")
+    zr = A.float() @ B.float() + bias.float()
+    assert _rel(z, zr) < 1e-2 and _rel(y, torch.nn.functional.gelu(zr)) < 1e-2
+    acc = torch.randn(8192, 8192, device="cuda", dtype=torch.float32)
+    want = acc + A.float() @ B.float()
+    got = gemm.gemm_bf16(A, B, out=acc, out_dtype=torch.float32, accumulate=True)
+    assert _rel(got, want) < 1e-2
+    native.check_status()
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (100, 72, 40), (333, 520, 136), (1, 8, 8),
                                    (2048, 2048, 2048), (64, 4096, 1024)])
 @pytest.mark.parametrize("layout", ["NN", "NT", "TN", "TT"])
@@ -93,6 +133,35 @@ def test_layernorm_fwd_bwd(dtype, rows, D):
     assert _rel(y, ref) < tol
     dx, dg, db = kernels.layernorm_bwd(dy, x, g, mean, rstd)
     assert _rel(dx, xr.grad) < tol and _rel(dg, gr.grad) < tol and _rel(db, br.grad) < tol
+    # the same through the dx + dgamma/dbeta kernel pair (the path of rows wider than 8 vectors per lane)
+    lib = kernels._L()
+    lib.nb_layernorm_bwd_two_kernels(1)
+    try:
+        dx2, dg2, db2 = kernels.layernorm_bwd(dy, x, g, mean, rstd)
+    finally:
+        lib.nb_layernorm_bwd_two_kernels(0)
+    assert _rel(dx2, xr.grad) < tol and _rel(dg2, gr.grad) < tol and _rel(db2, br.grad) < tol
+
+
+def test_layernorm_backward_many_rows_and_wide_rows():
+    """More rows than the persistent grid of the one-pass kernel holds at once (every warp walks
+    several rows), no gamma, and a row too wide for it (4096 bf16 = 16 vectors per lane)."""
+    from nabla_b200.native import kernels
+
+    torch.manual_seed(3)
+    for rows, D, with_gamma in ((5000, 512, True), (3001, 2048, False), (65, 4096, True)):
+        x = torch.randn(rows, D, device="cuda", dtype=torch.bfloat16)
+        g = torch.randn(D, device="cuda", dtype=torch.bfloat16) if with_gamma else None
+        dy = torch.randn(rows, D, device="cuda", dtype=torch.bfloat16)
+        xr = x.float().requires_grad_(True)
+        gr = g.float().requires_grad_(True) if with_gamma else None
+        torch.nn.functional.layer_norm(xr, (D,), gr, None).backward(dy.float())
+        _, mean, rstd = kernels.layernorm_fwd(x, g, None, 1e-5)
+        dx, dg, db = kernels.layernorm_bwd(dy, x, g, mean, rstd)
+        assert _rel(dx, xr.grad) < 3e-2
+        assert _rel(db, dy.float().sum(0)) < 2e-2
+        if with_gamma:
+            assert _rel(dg, gr.grad) < 2e-2
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
