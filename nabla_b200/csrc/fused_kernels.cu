@@ -919,6 +919,35 @@ __global__ void __launch_bounds__(256) pool2d_fwd_kernel(const T* __restrict__ x
     y[i] = from_f<T>(mode == 0 ? acc / (kh * kw) : acc);
   }
 }
+// out[window] = t[first arg-max of x over the window] (0 for a window that lies in the padding): the
+// forward-mode derivative of max pooling, and the transpose of its backward routing.
+template <typename T>
+__global__ void __launch_bounds__(256) pool2d_select_kernel(const T* __restrict__ x, const T* __restrict__ t,
+                                                           T* __restrict__ y, int N, int H, int W, int C, int OH, int OW,
+                                                           int kh, int kw, int sh, int sw, int ph, int pw) {
+  const size_t total = (size_t)N * OH * OW * C;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int c = i % C;
+    size_t r = i / C;
+    const int ow = r % OW; r /= OW;
+    const int oh = r % OH;
+    const int n = r / OH;
+    float best = -INFINITY;
+    size_t at = 0;
+    bool found = false;
+    for (int a = 0; a < kh; ++a)
+      for (int b = 0; b < kw; ++b) {
+        const int ih = oh * sh - ph + a, iw = ow * sw - pw + b;
+        if (ih >= 0 && ih < H && iw >= 0 && iw < W) {
+          const size_t off = (((size_t)n * H + ih) * W + iw) * C + c;
+          const float v = to_f<T>(x[off]);
+          if (v > best || !found) { best = v; at = off; found = true; }
+        }
+      }
+    y[i] = found ? t[at] : from_f<T>(0.f);
+  }
+}
+
 // Backward in gather form: one thread per input pixel sums over the windows that cover it (for max
 // pooling it finds each window's first arg-max again and takes the gradient when that is this
 // pixel). No atomics, so the result does not depend on the order in which blocks run, and dx needs
@@ -1347,6 +1376,16 @@ int nb_pool2d_bwd(const void* x, const void* dy, void* dx, int N, int H, int W, 
   const int grid = grid_for(total, 256);
   if (dtype) pool2d_bwd_kernel<bf16><<<grid, 256, 0, STREAM>>>((const bf16*)x, (const bf16*)dy, (bf16*)dx, N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw, mode);
   else pool2d_bwd_kernel<float><<<grid, 256, 0, STREAM>>>((const float*)x, (const float*)dy, (float*)dx, N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw, mode);
+  return CHECK_LAUNCH();
+}
+
+int nb_pool2d_select(const void* x, const void* t, void* y, int N, int H, int W, int C, int OH, int OW, int kh, int kw,
+                     int sh, int sw, int ph, int pw, int dtype, void* stream) {
+  const size_t total = (size_t)N * OH * OW * C;
+  if (!total) return 0;
+  const int grid = grid_for(total, 256);
+  if (dtype) pool2d_select_kernel<bf16><<<grid, 256, 0, STREAM>>>((const bf16*)x, (const bf16*)t, (bf16*)y, N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw);
+  else pool2d_select_kernel<float><<<grid, 256, 0, STREAM>>>((const float*)x, (const float*)t, (float*)y, N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw);
   return CHECK_LAUNCH();
 }
 

@@ -45,6 +45,7 @@ def _L():
             "nb_nf4_dequant_codes": [c_vp] * 4 + [c_ll, c_int, c_int, c_vp],
             "nb_pool2d_fwd": [c_vp, c_vp] + [c_int] * 14 + [c_vp],
             "nb_pool2d_bwd": [c_vp] * 3 + [c_int] * 14 + [c_vp],
+            "nb_pool2d_select": [c_vp] * 3 + [c_int] * 13 + [c_vp],
             "nb_conv2d_direct": [c_vp] * 4 + [c_int] * 14 + [c_vp],
             "nb_conv2d_wgrad_direct": [c_vp] * 3 + [c_int] * 14 + [c_vp],
             "nb_sum_slices": [c_vp, c_vp, c_ll, c_int, c_int, c_vp],
@@ -356,6 +357,19 @@ def pool2d_bwd(x, dy, kh, kw, sh, sw, ph, pw, mode: str):
     _ok(_L().nb_pool2d_bwd(ptr(x), ptr(dy), ptr(dx), N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw,
                            0 if mode == "avg" else 1, _dt(x), stream_ptr()), "pool2d_bwd")
     return dx
+
+
+def pool2d_select(x, t, kh, kw, sh, sw, ph, pw):
+    """``out[window] = t[arg-max of x over the window]`` (NHWC; the tangent of max pooling)."""
+    x = x.contiguous()
+    t = t.contiguous().to(x.dtype)
+    N, H, W, C = x.shape
+    OH = (H + 2 * ph - kh) // sh + 1
+    OW = (W + 2 * pw - kw) // sw + 1
+    y = torch.empty((N, OH, OW, C), dtype=x.dtype, device=x.device)
+    _ok(_L().nb_pool2d_select(ptr(x), ptr(t), ptr(y), N, H, W, C, OH, OW, kh, kw, sh, sw, ph, pw, _dt(x), stream_ptr()),
+        "pool2d_select")
+    return y
 
 
 def conv2d_direct(x, w, bias, stride, padding):

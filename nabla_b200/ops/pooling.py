@@ -58,15 +58,9 @@ class Pool2dOp(Operation):
     def jvp_rule(self, primals, tangents, outputs, kwargs):
         if kwargs["mode"] == "avg":
             return _pool(tangents[0], **kwargs)
-        from ..transforms.vjp import vjp  # max: tangent follows the arg-max (same routing as the VJP transpose)
-        from .creation import ones_like
-
-        x = primals[0]
-        mask = _pool_bwd(x, ones_like(outputs), **kwargs)
-        kw = dict(kwargs)
-        kw["mode"] = "avg"
-        kh, kw_ = kwargs["kernel_size"]
-        return _pool(tangents[0] * mask, **kw) * float(kh * kw_)
+        # max: every window's tangent is the tangent at its arg-max (the transpose of the VJP routing)
+        kw = {k: v for k, v in kwargs.items() if k != "mode"}
+        return _pool_select(primals[0], tangents[0], **kw)
 
 
 class Pool2dBwdOp(Operation):
@@ -95,10 +89,48 @@ class Pool2dBwdOp(Operation):
     def vjp_rule(self, primals, cot, outputs, kwargs):
         if kwargs["mode"] == "avg":
             return (None, _pool(cot, **kwargs))
-        raise NotImplementedError("second derivative of max_pool2d")
+        # the routing is linear in dy (and piecewise constant in x): its transpose picks, for every
+        # window, the cotangent at the window's arg-max
+        kw = {k: v for k, v in kwargs.items() if k != "mode"}
+        return (None, _pool_select(primals[0], cot, **kw))
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return _pool_bwd(primals[0], tangents[1], **kwargs) if tangents[1] is not None else None
 
 
-_pool, _pool_bwd = Pool2dOp(), Pool2dBwdOp()
+class Pool2dSelectOp(Operation):
+    """``out[window] = t[arg-max of x over the window]`` for max pooling's windows: the forward-mode
+    derivative of ``max_pool2d`` at ``x`` applied to ``t``."""
+
+    def kernel(self, x, t, *, kernel_size, stride, padding):
+        x4, lead = _fold(x)
+        t4, _ = _fold(t)
+        kh, kw = kernel_size
+        pt, pb, pl, pr = padding
+        if _native_ok(x4) and pt == pb and pl == pr and t4.dtype == x4.dtype:
+            from ..native import kernels
+
+            y = kernels.pool2d_select(x4, t4, kh, kw, stride[0], stride[1], pt, pl)
+            return y.reshape(*lead, *y.shape[1:])
+        xc = TF.pad(x4.float().permute(0, 3, 1, 2), (pl, pr, pt, pb), value=float("-inf"))
+        tc = TF.pad(t4.float().permute(0, 3, 1, 2), (pl, pr, pt, pb))
+        y, idx = TF.max_pool2d(xc, (kh, kw), stride, return_indices=True)
+        out = tc.flatten(2).gather(2, idx.flatten(2)).view_as(y)
+        out = out.permute(0, 2, 3, 1).contiguous().to(t.dtype)
+        return out.reshape(*lead, *out.shape[1:])
+
+    def sharding_rule(self, input_shapes, output_shapes, **kw):
+        m, out = _rule(input_shapes)
+        return OpShardingRule([m, dict(m)], [out])
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        return (None, _pool_bwd(primals[0], cot, mode="max", **kwargs))
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return _pool_select(primals[0], tangents[1], **kwargs) if tangents[1] is not None else None
+
+
+_pool, _pool_bwd, _pool_select = Pool2dOp(), Pool2dBwdOp(), Pool2dSelectOp()
 
 
 def _call(x, kernel_size, stride, padding, dilation, mode):

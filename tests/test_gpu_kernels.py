@@ -242,6 +242,13 @@ def test_adamw_sgd_activation_rng_dropout_nf4_pool_conv():
         dy = torch.randn_like(yk)
         r.backward(dy.cpu().permute(0, 3, 1, 2).contiguous())
         assert _rel(kernels.pool2d_bwd(x, dy, 3, 2, 2, 2, 1, 1, mode).cpu(), xr.grad.permute(0, 2, 3, 1)) < 1e-5
+    # tangent of max pooling: every window picks the tangent at its arg-max
+    tan = torch.randn_like(x)
+    xc = torch.nn.functional.pad(x.cpu().permute(0, 3, 1, 2), (1, 1, 1, 1), value=float("-inf"))
+    tc = torch.nn.functional.pad(tan.cpu().permute(0, 3, 1, 2), (1, 1, 1, 1))
+    yy, idx = torch.nn.functional.max_pool2d(xc, (3, 2), (2, 2), return_indices=True)
+    sel = tc.flatten(2).gather(2, idx.flatten(2)).view_as(yy).permute(0, 2, 3, 1)
+    assert _rel(kernels.pool2d_select(x, tan, 3, 2, 2, 2, 1, 1).cpu(), sel) < 1e-6
     w = torch.randn(3, 3, 5, 4, device="cuda")
     bconv = torch.randn(4, device="cuda")
     ref = torch.nn.functional.conv2d(torch.nn.functional.pad(x.permute(0, 3, 1, 2), (2, 0, 1, 1)), w.permute(3, 2, 0, 1),

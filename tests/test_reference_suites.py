@@ -1,0 +1,348 @@
+"""Behaviour suites that the reference keeps in files of their own (tests/unit/test_tensor_index_update_api.py,
+test_hessian_per_op.py, test_hessian_four_combos_ops.py, test_multi_output.py, test_pooling.py,
+test_pytree_custom.py, test_indexing_creation.py), written against this package with torch / numpy
+oracles: in-place and functional index updates under grad / vmap / sharding, second derivatives of
+single ops through all four forward / reverse combinations, multi-output ops on sharded inputs,
+pooling derivatives, custom pytree nodes, gather / scatter with sharding."""
+import numpy as np
+import pytest
+import torch
+
+import nabla_b200 as nb
+from nabla_b200 import P
+
+from common import T, close, rand
+
+
+def _mesh(n=2, name="x"):
+    return nb.DeviceMesh("m", (n,), (name,))
+
+
+# ---------------------------------------------------------------- index updates
+def test_setitem_slice_rebinds_the_tensor():
+    x = T(np.arange(6, dtype=np.float32).reshape(2, 3))
+    x[:, 1:3] = T(np.array([[10.0, 11.0], [12.0, 13.0]], dtype=np.float32))
+    close(x, np.array([[0.0, 10.0, 11.0], [3.0, 12.0, 13.0]]))
+
+
+def test_setitem_with_tensor_indices_broadcasts_a_scalar():
+    x = T(np.arange(5, dtype=np.float32))
+    x[T(np.array([0, 2, 4], dtype=np.int32))] = 9.0
+    close(x, np.array([9.0, 1.0, 9.0, 3.0, 9.0]))
+
+
+def test_at_set_and_add_are_functional():
+    x = T(np.arange(5, dtype=np.float32))
+    idx = T(np.array([1, 3], dtype=np.int32))
+    y = x.at[idx].set(7.0)
+    z = x.at[idx].add(2.0)
+    close(x, np.arange(5))
+    close(y, np.array([0.0, 7.0, 2.0, 7.0, 4.0]))
+    close(z, np.array([0.0, 3.0, 2.0, 5.0, 4.0]))
+
+
+def test_chained_updates_match_numpy_and_leave_the_input_alone():
+    base = np.arange(12, dtype=np.float32).reshape(3, 4)
+    x = T(base)
+    y = x.at[0, :].set(1.0).at[:, 1:3].add(T(np.full((3, 2), 0.5, dtype=np.float32))).at[2, 3].set(-4.0)
+    ref = base.copy()
+    ref[0, :] = 1.0
+    ref[:, 1:3] += 0.5
+    ref[2, 3] = -4.0
+    close(y, ref)
+    close(x, base)
+    x2 = T(base)
+    x2[0, :] = 1.0
+    x2[:, 1:3] = x2[:, 1:3] + 0.5
+    x2[2, 3] = -4.0
+    close(x2, ref)
+
+
+def test_grad_through_setitem_and_at():
+    u0 = rand(2, 2, seed=3)
+    x0 = rand(3, 4, seed=4)
+
+    def loss_setitem(x, u):
+        y = x * 2.0
+        y[1:3, 0:2] = u * u
+        return nb.reduce_sum(y * y)
+
+    def loss_at(x, u):
+        y = (x * 2.0).at[1:3, 0:2].set(u * u).at[0, 3].add(1.0)
+        return nb.reduce_sum(y * y)
+
+    def oracle(with_add):
+        xt, ut = x0.clone().requires_grad_(True), u0.clone().requires_grad_(True)
+        y = (xt * 2.0).clone()
+        y[1:3, 0:2] = ut * ut
+        if with_add:
+            y = y.clone()
+            y[0, 3] = y[0, 3] + 1.0
+        (y * y).sum().backward()
+        return xt.grad, ut.grad
+
+    gx, gu = nb.grad(loss_setitem, argnums=(0, 1))(T(x0), T(u0))
+    rx, ru = oracle(False)
+    close(gx, rx, rtol=1e-4, atol=1e-4)
+    close(gu, ru, rtol=1e-4, atol=1e-4)
+    gx, gu = nb.grad(loss_at, argnums=(0, 1))(T(x0), T(u0))
+    rx, ru = oracle(True)
+    close(gx, rx, rtol=1e-4, atol=1e-4)
+    close(gu, ru, rtol=1e-4, atol=1e-4)
+
+
+def test_vmap_of_an_index_update_and_of_its_gradient():
+    xs = rand(4, 5, seed=5)
+    us = rand(4, 2, seed=6)
+
+    def f(x, u):
+        return x.at[1:3].set(u * 3.0)
+
+    out = nb.vmap(f)(T(xs), T(us))
+    ref = xs.clone()
+    ref[:, 1:3] = us * 3.0
+    close(out, ref)
+
+    def loss(x, u):
+        y = x.at[1:3].set(u * u)
+        return nb.reduce_sum(y * y)
+
+    g = nb.vmap(nb.grad(loss, argnums=1))(T(xs), T(us))
+    close(g, 4.0 * us ** 3, rtol=1e-4, atol=1e-4)
+
+
+def test_sharded_index_update_and_its_gradient():
+    mesh = _mesh(2)
+    x0 = rand(4, 6, seed=7)
+    u0 = rand(4, 2, seed=8)
+
+    def loss(x, u):
+        xs = nb.shard(x, mesh, ("x", None))
+        y = xs.at[:, 1:3].set(nb.shard(u, mesh, ("x", None)) * 2.0)
+        return nb.reduce_sum(y * y)
+
+    xt, ut = x0.clone().requires_grad_(True), u0.clone().requires_grad_(True)
+    y = xt.clone()
+    y[:, 1:3] = ut * 2.0
+    (y * y).sum().backward()
+    val, (gx, gu) = nb.value_and_grad(loss, argnums=(0, 1))(T(x0), T(u0))
+    close(val, (y * y).sum().detach(), rtol=1e-4)
+    close(gx, xt.grad, rtol=1e-4, atol=1e-4)
+    close(gu, ut.grad, rtol=1e-4, atol=1e-4)
+    xs = nb.shard(T(x0), mesh, ("x", None))
+    xs[:, 1:3] = nb.shard(T(u0), mesh, ("x", None))
+    ref = x0.clone()
+    ref[:, 1:3] = u0
+    close(xs, ref)
+
+
+# ---------------------------------------------------------------- second derivatives of single ops
+def _hessian(f, mode):
+    return {"rev_rev": lambda: nb.jacrev(nb.jacrev(f)), "fwd_fwd": lambda: nb.jacfwd(nb.jacfwd(f)),
+            "rev_fwd": lambda: nb.jacrev(nb.jacfwd(f)), "fwd_rev": lambda: nb.jacfwd(nb.jacrev(f)),
+            "fwd_grad": lambda: nb.jacfwd(nb.grad(f)), "rev_grad": lambda: nb.jacrev(nb.grad(f))}[mode]()
+
+
+_W = rand(3, 3, seed=11)
+_HESSIAN_CASES = {
+    "exp_sum": ((5,), lambda a: nb.reduce_sum(nb.exp(a)), lambda a: a.exp().sum()),
+    "exp_sum_2d": ((2, 3), lambda a: nb.reduce_sum(nb.exp(a)), lambda a: a.exp().sum()),
+    "poly": ((4,), lambda a: nb.reduce_sum(a * a * a + 2.0 * a * a), lambda a: (a ** 3 + 2 * a ** 2).sum()),
+    "matmul_quadratic": ((3,), lambda a: nb.reduce_sum(nb.matmul(nb.reshape(a, (1, 3)), T(_W)) * a),
+                         lambda a: ((a.reshape(1, 3) @ _W) * a).sum()),
+    "reduce_axis_chain": ((2, 3), lambda a: nb.reduce_sum(nb.reduce_sum(a * a, axis=0) * nb.mean(a, axis=0)),
+                          lambda a: ((a * a).sum(0) * a.mean(0)).sum()),
+    "view_chain": ((2, 3), lambda a: nb.reduce_sum(nb.swap_axes(nb.reshape(a * a, (3, 2)), 0, 1) * nb.moveaxis(
+        nb.reshape(a, (3, 2)), 0, 1)), lambda a: ((a * a).reshape(3, 2).transpose(0, 1) * a.reshape(3, 2).movedim(0, 1)).sum()),
+    "broadcast_chain": ((3,), lambda a: nb.reduce_sum(nb.broadcast_to(nb.unsqueeze(a, axis=0), (4, 3)) ** 2.0
+                                                     * nb.squeeze(nb.unsqueeze(nb.sin(a), axis=1), axis=1)),
+                        lambda a: ((a.unsqueeze(0).expand(4, 3) ** 2) * a.sin()).sum()),
+    "getitem_scalar": ((4,), lambda a: a[1] * a[1] * a[2] + nb.reduce_sum(a[0:2] * a[2:4]),
+                       lambda a: a[1] * a[1] * a[2] + (a[0:2] * a[2:4]).sum()),
+}
+
+
+@pytest.mark.parametrize("mode", ["rev_rev", "fwd_fwd", "rev_fwd", "fwd_rev", "fwd_grad", "rev_grad"])
+@pytest.mark.parametrize("case", sorted(_HESSIAN_CASES))
+def test_hessian_of_single_ops_through_every_combination(case, mode):
+    shape, f, ft = _HESSIAN_CASES[case]
+    a0 = rand(*shape, seed=13) * 0.7
+    ref = torch.autograd.functional.hessian(ft, a0)
+    got = _hessian(f, mode)(T(a0))
+    close(got, ref, rtol=2e-4, atol=2e-4, msg=f"{case}/{mode}")
+
+
+# ---------------------------------------------------------------- multi-output ops
+def test_split_chunk_unbind_on_sharded_inputs():
+    mesh = _mesh(2)
+    a = rand(4, 6, seed=21)
+    xs = nb.shard(T(a), mesh, ("x", None))
+    parts = nb.split(xs, 3, axis=1)                       # the split axis is not the sharded one
+    for p, r in zip(parts, torch.split(a, 2, dim=1)):
+        close(p, r)
+    parts = nb.split(xs, 2, axis=0)                       # the split axis is the sharded one
+    for p, r in zip(parts, torch.split(a, 2, dim=0)):
+        close(p, r)
+    parts = nb.split(xs, [1, 2, 3], axis=1)
+    for p, r in zip(parts, torch.split(a, [1, 2, 3], dim=1)):
+        close(p, r)
+    for p, r in zip(nb.chunk(xs, 3, axis=1), torch.chunk(a, 3, dim=1)):
+        close(p, r)
+    uneven = nb.chunk(T(rand(7, 2, seed=22)), 3, axis=0)
+    assert [tuple(int(d) for d in u.shape) for u in uneven] == [(3, 2), (3, 2), (1, 2)]
+    for p, r in zip(nb.unbind(xs, axis=0), torch.unbind(a, 0)):
+        close(p, r)
+    b = rand(2, 4, 3, seed=23)
+    for p, r in zip(nb.unbind(nb.shard(T(b), mesh, (None, "x", None)), axis=1), torch.unbind(b, 1)):
+        close(p, r)
+
+
+def test_split_on_a_two_axis_mesh_and_minmax():
+    mesh = nb.DeviceMesh("m2", (2, 2), ("a", "b"))
+    a = rand(4, 8, seed=24)
+    xs = nb.shard(T(a), mesh, ("a", "b"))
+    for p, r in zip(nb.split(xs, 2, axis=1), torch.split(a, 4, dim=1)):
+        close(p, r)
+    mm = nb.minmax(T(a), axis=1)
+    close(mm["min"], a.min(1).values)
+    close(mm["max"], a.max(1).values)
+    mm = nb.minmax(nb.shard(T(a), _mesh(2), ("x", None)), axis=0)
+    close(mm["min"], a.min(0).values)
+    close(mm["max"], a.max(0).values)
+
+
+def test_vmap_over_multi_output_ops_and_edge_cases():
+    a = rand(3, 4, 6, seed=25)
+    outs = nb.vmap(lambda t: nb.split(t, 2, axis=1))(T(a))
+    for p, r in zip(outs, torch.split(a, 3, dim=2)):
+        close(p, r)
+    outs = nb.vmap(lambda t: tuple(nb.chunk(t, 2, axis=0)))(T(a))
+    for p, r in zip(outs, torch.chunk(a, 2, dim=1)):
+        close(p, r)
+    outs = nb.vmap(lambda t: nb.unbind(t, axis=0))(T(a))
+    for p, r in zip(outs, torch.unbind(a, 1)):
+        close(p, r)
+    one = nb.split(T(a), 1, axis=0)
+    assert len(one) == 1
+    close(one[0], a)
+    many = nb.chunk(T(rand(2, 3, seed=26)), 5, axis=0)     # more chunks than elements
+    assert len(many) == 2
+    single = nb.unbind(T(rand(1, 3, seed=27)), axis=0)
+    assert len(single) == 1 and tuple(int(d) for d in single[0].shape) == (3,)
+
+
+def test_gradient_through_split_and_unbind():
+    a = rand(4, 6, seed=28)
+
+    def f(t):
+        p, q, r = nb.split(t, 3, axis=1)
+        u = nb.unbind(p * q, axis=0)
+        return nb.reduce_sum(u[0] * u[1]) + nb.reduce_sum(r * r * r)
+
+    at = a.clone().requires_grad_(True)
+    p, q, r = torch.split(at, 2, dim=1)
+    u = torch.unbind(p * q, 0)
+    ((u[0] * u[1]).sum() + (r ** 3).sum()).backward()
+    close(nb.grad(f)(T(a)), at.grad, rtol=1e-4, atol=1e-4)
+
+
+# ---------------------------------------------------------------- pooling (NHWC)
+def _pool_ref(fn, x, k, s, p):
+    return fn(x.permute(0, 3, 1, 2), k, s, padding=p).permute(0, 2, 3, 1)
+
+
+@pytest.mark.parametrize("kind", ["avg", "max"])
+def test_pool2d_forward_vjp_and_jvp_match_torch(kind):
+    op = nb.avg_pool2d if kind == "avg" else nb.max_pool2d
+    ref_fn = torch.nn.functional.avg_pool2d if kind == "avg" else torch.nn.functional.max_pool2d
+    x0 = rand(2, 6, 7, 3, seed=31)
+    k, s, p = (3, 2), (2, 1), (1, 0)
+    y = op(T(x0), k, stride=s, padding=p)
+    xt = x0.clone().requires_grad_(True)
+    yt = _pool_ref(ref_fn, xt, k, s, p)
+    close(y, yt.detach(), rtol=1e-5, atol=1e-5)
+    cot = rand(*yt.shape, seed=32)
+    yt.backward(cot)
+    _, pull = nb.vjp(lambda t: op(t, k, stride=s, padding=p), T(x0))
+    (gx,) = pull(T(cot))
+    close(gx, xt.grad, rtol=1e-4, atol=1e-5)
+    tan = rand(*x0.shape, seed=33)
+    _, jt = torch.autograd.functional.jvp(lambda t: _pool_ref(ref_fn, t, k, s, p), x0, tan)
+    _, tout = nb.jvp(lambda t: op(t, k, stride=s, padding=p), (T(x0),), (T(tan),))
+    close(tout, jt, rtol=1e-4, atol=1e-5)
+
+
+def test_avg_pool2d_under_nested_vmap_and_bad_parameters():
+    x0 = rand(2, 3, 1, 4, 4, 2, seed=34)
+    f = lambda t: nb.avg_pool2d(t, (2, 2), stride=(2, 2))
+    out = nb.vmap(nb.vmap(f))(T(x0))
+    ref = torch.stack([torch.stack([_pool_ref(torch.nn.functional.avg_pool2d, x0[i, j], 2, 2, 0) for j in range(3)])
+                       for i in range(2)])
+    close(out, ref, rtol=1e-5, atol=1e-5)
+    with pytest.raises(Exception):
+        nb.avg_pool2d(T(rand(1, 4, 4, 1)), (0, 2))
+    with pytest.raises(Exception):
+        nb.max_pool2d(T(rand(4, 4, 1)), (2, 2))           # not NHWC
+
+
+# ---------------------------------------------------------------- custom pytree nodes
+def test_custom_pytree_node_roundtrip_map_and_grad():
+    from nabla_b200.core.common import pytree
+
+    class Pair:
+        def __init__(self, a, b, tag):
+            self.a, self.b, self.tag = a, b, tag
+
+    pytree.register_pytree_node(Pair, lambda p: ((p.a, p.b), p.tag), lambda tag, ch: Pair(ch[0], ch[1], tag))
+    tree = {"p": Pair(T(rand(2, seed=41)), T(rand(2, seed=42)), "meta"), "k": [T(rand(3, seed=43)), 5]}
+    leaves, td = pytree.tree_flatten(tree)
+    assert sum(isinstance(l, nb.Tensor) for l in leaves) == 3
+    back = pytree.tree_unflatten(td, leaves)
+    assert isinstance(back["p"], Pair) and back["p"].tag == "meta" and back["k"][1] == 5
+    doubled = pytree.tree_map(lambda t: t * 2.0 if isinstance(t, nb.Tensor) else t, tree)
+    close(doubled["p"].a, tree["p"].a.to_numpy() * 2.0)
+    g = nb.grad(lambda pr: nb.reduce_sum(pr.a * pr.b * pr.b))(tree["p"])
+    assert isinstance(g, Pair)
+    close(g.a, tree["p"].b.to_numpy() ** 2, rtol=1e-5)
+    close(g.b, 2.0 * tree["p"].a.to_numpy() * tree["p"].b.to_numpy(), rtol=1e-5)
+
+
+# ---------------------------------------------------------------- gather / scatter with sharding and vmap
+def test_gather_and_scatter_on_sharded_inputs():
+    mesh = _mesh(2)
+    a = rand(4, 6, seed=51)
+    idx = torch.tensor([2, 0, 5], dtype=torch.int64)
+    close(nb.gather(T(a), T(idx), axis=1), a[:, idx])
+    close(nb.gather(nb.shard(T(a), mesh, ("x", None)), T(idx), axis=1), a[:, idx])       # sharded on the other axis
+    close(nb.gather(nb.shard(T(a), mesh, ("x", None)), T(torch.tensor([3, 1])), axis=0), a[[3, 1]])
+    b = rand(2, 4, 3, seed=52)
+    close(nb.gather(nb.shard(T(b), mesh, ("x", None, None)), T(torch.tensor([1, 3, 3])), axis=1), b[:, [1, 3, 3]])
+    close(nb.gather(T(b), T(torch.tensor([2, 0])), axis=-1), b[..., [2, 0]])
+    upd = rand(4, 3, seed=53)
+    ref = a.clone()
+    ref[:, idx] = upd
+    close(nb.scatter(T(a), T(idx), T(upd), axis=1), ref)
+    close(nb.scatter(nb.shard(T(a), mesh, ("x", None)), T(idx), nb.shard(T(upd), mesh, ("x", None)), axis=1), ref)
+    # gather then scatter of the same rows gives the original back
+    rows = torch.tensor([3, 0, 2, 1])
+    close(nb.scatter(T(torch.zeros(4, 6)), T(rows), nb.gather(T(a), T(rows), axis=0), axis=0), a)
+
+
+@pytest.mark.parametrize("batch", [2, 4])
+def test_vmap_gather_with_shared_and_batched_indices(batch):
+    a = rand(batch, 5, 3, seed=54)
+    idx = torch.tensor([4, 0, 2])
+    close(nb.vmap(lambda t: nb.gather(t, T(idx), axis=0))(T(a)), a[:, idx])
+    bidx = torch.stack([torch.randperm(5, generator=torch.Generator().manual_seed(i))[:2] for i in range(batch)])
+    out = nb.vmap(lambda t, i: nb.gather(t, i, axis=0))(T(a), T(bidx))
+    close(out, torch.stack([a[i][bidx[i]] for i in range(batch)]))
+
+
+def test_random_creation_does_not_depend_on_the_sharding():
+    mesh = _mesh(2)
+    nb.seed(123)
+    full = nb.uniform((4, 6)).to_numpy()
+    nb.seed(123)
+    sharded = nb.shard(nb.uniform((4, 6)), mesh, ("x", None)).to_numpy()
+    assert np.array_equal(full, sharded)
+    assert 0.0 <= full.min() and full.max() <= 1.0 and full.std() > 0.1
