@@ -346,3 +346,111 @@ def test_random_creation_does_not_depend_on_the_sharding():
     sharded = nb.shard(nb.uniform((4, 6)), mesh, ("x", None)).to_numpy()
     assert np.array_equal(full, sharded)
     assert 0.0 <= full.min() and full.max() <= 1.0 and full.std() > 0.1
+
+
+# ---------------------------------------------------------------- vmap over collectives
+def _rng_array(*shape, seed=0):
+    return np.random.default_rng(seed).standard_normal(shape).astype(np.float32)
+
+
+def test_vmap_over_all_gather_all_reduce_and_reduce_scatter():
+    mesh = nb.DeviceMesh("mesh_tp", (2,), ("tp",))
+    x0 = _rng_array(4, 16, seed=61)
+    r = nb.vmap(lambda x: nb.all_gather(x.shard(mesh, P("tp")), axis=0))(T(x0))
+    assert tuple(int(d) for d in r.shape) == (4, 16) and r.sharding.is_fully_replicated()
+    close(r, x0)
+    # all_reduce of a spatially split vector adds the halves (the op's own semantics)
+    r = nb.vmap(lambda x: nb.all_reduce(x.shard(mesh, P("tp")), reduce_op="sum"))(T(x0))
+    assert tuple(int(d) for d in r.shape) == (4, 8)
+    close(r, x0[:, :8] + x0[:, 8:])
+    r = nb.vmap(lambda x: nb.reduce_scatter(x.shard(mesh, P("tp")), axis=0))(T(x0))
+    assert tuple(int(d) for d in r.shape) == (4, 8)
+
+
+def test_vmap_on_a_dp_axis_with_tp_communication_inside():
+    mesh = nb.DeviceMesh("mesh_hybrid", (2, 2), ("dp", "tp"))
+    x0 = _rng_array(4, 16, seed=62)
+    r = nb.vmap(lambda x: nb.all_gather(x.shard(mesh, P("tp")), axis=0))(T(x0).shard(mesh, P("dp", None)))
+    close(r, x0)
+    assert "dp" in r.sharding.dim_specs[0].axes
+
+
+def test_nested_vmap_and_shifted_in_axes_over_all_gather():
+    mesh = nb.DeviceMesh("mesh_n", (2,), ("tp",))
+    x0 = _rng_array(2, 3, 8, seed=63)
+    f = lambda x: nb.all_gather(x.shard(mesh, P("tp")), axis=0) * 2.0
+    close(nb.vmap(nb.vmap(f))(T(x0)), 2.0 * x0)
+    x1 = _rng_array(8, 5, seed=64)                      # the mapped axis is the second one
+    r = nb.vmap(f, in_axes=1, out_axes=1)(T(x1))
+    close(r, 2.0 * x1)
+    x3 = _rng_array(3, 4, 4, seed=65)
+    r = nb.vmap(lambda x: nb.all_to_all(x.shard(mesh, P("tp", None)), 0, 1))(T(x3))
+    assert tuple(int(d) for d in r.shape) == (3, 4, 4)
+    close(r, x3)
+
+
+def test_gradient_through_vmapped_collectives():
+    mesh = nb.DeviceMesh("mesh_g", (2,), ("tp",))
+    x0 = _rng_array(4, 16, seed=66)
+
+    def loss_ar(x):
+        y = nb.vmap(lambda t: nb.all_reduce(t.shard(mesh, P("tp")), reduce_op="sum"))(x)
+        return nb.reduce_sum(y * y)
+
+    s = x0[:, :8] + x0[:, 8:]
+    close(nb.grad(loss_ar)(T(x0)), np.concatenate([2 * s, 2 * s], 1), rtol=1e-5, atol=1e-5)
+
+    def loss_ag(x):
+        y = nb.vmap(lambda t: nb.all_gather(t.shard(mesh, P("tp")), axis=0))(x)
+        return nb.reduce_sum(y * y * y)
+
+    close(nb.grad(loss_ag)(T(x0)), 3.0 * x0 * x0, rtol=1e-4, atol=1e-5)
+
+
+# ---------------------------------------------------------------- physical-shape ops on sharded inputs
+def test_reductions_and_view_ops_keep_or_resolve_the_sharding():
+    mesh = _mesh(2)
+    a = rand(4, 6, seed=71)
+    xs = nb.shard(T(a), mesh, ("x", None))
+    r = nb.reduce_sum(xs, axis=1)                        # the reduced axis is not the sharded one
+    close(r, a.sum(1))
+    assert r.sharding is not None and "x" in r.sharding.dim_specs[0].axes
+    close(nb.reduce_sum(xs, axis=0), a.sum(0))           # the reduced axis is the sharded one
+    close(nb.mean(xs, axis=1), a.mean(1))
+    close(nb.mean(xs, axis=0), a.mean(0), rtol=1e-5, atol=1e-6)
+    b = rand(4, 1, 6, seed=72)
+    sq = nb.squeeze(nb.shard(T(b), mesh, ("x", None, None)), axis=1)
+    close(sq, b.squeeze(1))
+    assert "x" in sq.sharding.dim_specs[0].axes
+    un = nb.unsqueeze(xs, axis=0)
+    close(un, a.unsqueeze(0))
+    assert "x" in un.sharding.dim_specs[1].axes
+    bc = nb.broadcast_to(nb.unsqueeze(xs, axis=0), (3, 4, 6))
+    close(bc, a.unsqueeze(0).expand(3, 4, 6))
+    assert "x" in bc.sharding.dim_specs[1].axes
+
+
+# ---------------------------------------------------------------- a small CNN trained for a few steps
+def test_cnn_training_loop_realizes_every_step_and_learns():
+    rng = np.random.default_rng(5)
+    xb = rng.standard_normal((16, 8, 8, 1)).astype(np.float32)
+    yb = (xb.mean(axis=(1, 2, 3)) > 0).astype(np.int64)
+    params = {"w1": T(rng.standard_normal((3, 3, 1, 4)).astype(np.float32) * 0.3), "b1": T(np.zeros(4, np.float32)),
+              "w2": T(rng.standard_normal((4 * 4 * 4, 2)).astype(np.float32) * 0.1), "b2": T(np.zeros(2, np.float32))}
+    onehot = T(np.eye(2, dtype=np.float32)[yb])
+
+    def loss_fn(p, x):
+        h = nb.relu(nb.conv2d(x, p["w1"], stride=(1, 1), padding=(1, 1)) + p["b1"])
+        h = nb.max_pool2d(h, (2, 2), stride=(2, 2))
+        logits = nb.reshape(h, (16, 4 * 4 * 4)) @ p["w2"] + p["b2"]
+        logp = logits - nb.unsqueeze(nb.logsumexp(logits, axis=1), axis=1) if hasattr(nb, "logsumexp") else nb.logsoftmax(logits, axis=1)
+        return -nb.mean(nb.reduce_sum(logp * onehot, axis=1))
+
+    losses = []
+    for _ in range(12):
+        loss, g = nb.value_and_grad(loss_fn)(params, T(xb))
+        params = {k: params[k] - 0.5 * g[k] for k in params}
+        nb.realize_all(*params.values())                 # the lazy graph is cut every step
+        assert all(v.is_realized for v in params.values())
+        losses.append(loss.item())
+    assert losses[-1] < losses[0] * 0.8, losses
