@@ -143,6 +143,11 @@ dev = "cuda"
 a = torch.randn(333, 136, device=dev, dtype=torch.bfloat16); b = torch.randn(136, 520, device=dev, dtype=torch.bfloat16)
 c = gemm.gemm_bf16(a, b)
 out["gemm"] = ((c.float() - a.float() @ b.float()).abs().max() / (a.float() @ b.float()).abs().max()).item()
+# a shape wide enough for the CTA-pair kernel, with an odd number of 128-row tiles and a ragged last column tile
+a2 = torch.randn(4224, 320, device=dev, dtype=torch.bfloat16); b2 = torch.randn(320, 4616, device=dev, dtype=torch.bfloat16)
+c2 = gemm.gemm_bf16(a2, b2)
+out["gemm_pair"] = ((c2.float() - a2.float() @ b2.float()).abs().max() / (a2.float() @ b2.float()).abs().max()).item()
+out["pair_ran"] = native.load("libnb_gemm.so").nb_gemm_pair_max_clusters() > 0
 q, k, v = (torch.randn(2, 4, 300, 64, device=dev, dtype=torch.bfloat16) for _ in range(3))
 o, lse = attention.sdpa_fwd(q, k, v, causal=True, scale=64 ** -0.5)
 ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float(), is_causal=True)
@@ -207,6 +212,7 @@ def test_checked_build_runs_the_kernels_and_records_failed_checks():
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     out = json.loads([l for l in res.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
     assert out["gemm"] < 1e-2 and out["attn"] < 3e-2 and out["attn_bwd"] < 8e-2
+    assert out["gemm_pair"] < 1e-2 and out["pair_ran"]
     for k in ("softmax", "gather", "reduce", "binary", "pool_bwd", "scatter"):
         assert out[k] < 1e-4, (k, out[k])
     assert out["scatter_equal"] and out["clean"] and out["selftest_pass"]
