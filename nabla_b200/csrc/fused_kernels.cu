@@ -394,19 +394,32 @@ __global__ void __launch_bounds__(256) layernorm_bwd_dgb_kernel(const T* __restr
   }
 }
 
-// out[k][c] = sum_b partial[b][k][c]  (k < K planes of width D)
+// out0[c] = sum_b partial[b][0][c], out1[c] = sum_b partial[b][1][c]  (two planes of width D per row
+// of `partial`). A block covers 32 columns; its 8 warps take every 8th row, so a few hundred rows of
+// partials are a few dozen dependent loads per thread instead of a few hundred.
 template <typename T>
-__global__ void colsum_partials_kernel(const float* __restrict__ partial, T* __restrict__ out0, T* __restrict__ out1,
-                                       int nblocks, int D) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= D) return;
+__global__ void __launch_bounds__(256) colsum_partials_kernel(const float* __restrict__ partial, T* __restrict__ out0,
+                                                             T* __restrict__ out1, int nblocks, int D) {
+  __shared__ float sh[2][8][32];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   float a = 0.f, b = 0.f;
-  for (int i = 0; i < nblocks; ++i) {
-    a += partial[(size_t)i * 2 * D + c];
-    b += partial[(size_t)i * 2 * D + D + c];
+  if (c < D) {
+    for (int i = w; i < nblocks; i += 8) {
+      a += partial[(size_t)i * 2 * D + c];
+      b += partial[(size_t)i * 2 * D + D + c];
+    }
   }
-  if (out0) out0[c] = from_f<T>(a);
-  if (out1) out1[c] = from_f<T>(b);
+  sh[0][w][lane] = a;
+  sh[1][w][lane] = b;
+  __syncthreads();
+  if (w == 0 && c < D) {
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { sa += sh[0][k][lane]; sb += sh[1][k][lane]; }
+    if (out0) out0[c] = from_f<T>(sa);
+    if (out1) out1[c] = from_f<T>(sb);
+  }
 }
 
 // ============================================================== column sum (bias gradient)
@@ -1149,7 +1162,7 @@ int nb_layernorm_bwd(const void* dy, const void* x, const void* gamma, const flo
   {                                                                                                                   \
     layernorm_bwd_fused_kernel<T, VPL><<<nb, 128, 0, STREAM>>>((const T*)dy, (const T*)x, (const T*)gamma, mean, rstd, \
                                                                (T*)dx, partial, rows, D);                            \
-    colsum_partials_kernel<T><<<(D + 255) / 256, 256, 0, STREAM>>>(partial, (T*)dgamma, (T*)dbeta, nb, D);            \
+    colsum_partials_kernel<T><<<(D + 31) / 32, 256, 0, STREAM>>>(partial, (T*)dgamma, (T*)dbeta, nb, D);            \
   }
 #define LN_BWD(T, VPL)                                                                                                \
   {                                                                                                                   \
@@ -1157,7 +1170,7 @@ int nb_layernorm_bwd(const void* dy, const void* x, const void* gamma, const flo
                                                                   rstd, (T*)dx, rows, D);                            \
     layernorm_bwd_dgb_kernel<T><<<grid_gb, 256, 0, STREAM>>>((const T*)dy, (const T*)x, mean, rstd, partial, rows, D, \
                                                               rpb);                                                   \
-    colsum_partials_kernel<T><<<(D + 255) / 256, 256, 0, STREAM>>>(partial, (T*)dgamma, (T*)dbeta, nb, D);            \
+    colsum_partials_kernel<T><<<(D + 31) / 32, 256, 0, STREAM>>>(partial, (T*)dgamma, (T*)dbeta, nb, D);            \
   }
   if (g_ln_bwd_two_kernels) {
     if (dtype) {
