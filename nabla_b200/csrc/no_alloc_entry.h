@@ -3,10 +3,10 @@
 // This entry point has no counterpart in the reference framework. It exists for callers that
 // must not allocate device memory at the moment they need a column sum (a bias gradient, a
 // per-feature statistic):
-//   * code that runs with the device memory budget already handed out in full, such as a serving
+//   * code that runs with all of the device memory already handed out, such as a serving
 //     process that sized its KV cache to fill the GPU, where an allocation could fail or push
 //     the caching allocator into a synchronising free-and-retry;
-//   * code that runs between other people's kernels on a latency budget, where a device-wide
+//   * code that runs between other people's kernels under a latency limit, where a device-wide
 //     synchronisation hidden inside an allocation or a free stalls every stream of the process;
 //   * hosts that call this library from C, C++ or another runtime and have no torch allocator
 //     to hand scratch tensors to the regular entry point (`nb_colsum`, which expects the caller

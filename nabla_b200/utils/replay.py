@@ -13,7 +13,7 @@ load. ``replay_check`` makes that visible and repeatable:
 * the outputs (and, optionally, the arguments after the call, which is where in-place optimizer
   updates land) are compared bit for bit with those of the first run.
 
-With more than one rank each rank compares its own shards, and the verdict is combined over the
+With more than one rank each rank compares its own shards, and the result is combined over the
 process group, so every rank returns the same ``ok``.
 
 The reference has no counterpart (its only concurrency hardening is ContextVar isolation of the
