@@ -104,7 +104,7 @@ def test_lost_peer_is_reported_not_hung():
 @pytest.mark.parametrize("config", ["gpipe", "pp_dp", "lora"])
 def test_pipeline_and_lora_configurations_train_on_two_gpus(config):
     """Reduced sizes of the GPipe / PP x DP / LoRA configurations, one rank per GPU, replayed from a
-    CUDA graph (ppermute over NCCL send/recv inside the graph): the step runs and the loss is finite."""
+    CUDA graph (the stage shift is the peer-memory ppermute kernel inside the graph): the step runs and the loss is finite."""
     port = 29700 + (os.getpid() % 1000)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", str(port), "-m", "nabla_b200.models.configs", config, "--small", "--steps", "2",
