@@ -210,10 +210,40 @@ def cond(pred, true_fn: Callable, false_fn: Callable, *operands: Any):
     return pytree.tree_unflatten(out_td, [next(outs) if isinstance(l, Tensor) else l for l in t_leaves])
 
 
+def _n_positional(fn: Callable) -> int | None:
+    """Number of positional parameters ``fn`` accepts (None: any number, or unknown)."""
+    import inspect
+
+    try:
+        params = inspect.signature(fn).parameters.values()
+    except (TypeError, ValueError):
+        return None
+    n = 0
+    for p in params:
+        if p.kind is p.VAR_POSITIONAL:
+            return None
+        if p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD):
+            n += 1
+    return n
+
+
+def _apply_state(fn: Callable, state: tuple):
+    """Call a loop function on the loop state the way the reference does (nabla/ops/control_flow.py:
+    419-436): ONE argument holding the whole state, i.e. ``fn((i, acc))`` for a tuple state. A function
+    written with one parameter per element of a tuple state (``lambda i, acc: ...``) is called
+    unpacked instead; for a single-tensor state the two are the same."""
+    if len(state) == 1:
+        return fn(state[0])
+    n = _n_positional(fn)
+    if n is not None and n == len(state):
+        return fn(*state)
+    return fn(state)
+
+
 def _while_eager(cond_fn: Callable, body_fn: Callable, state: tuple, max_iters: int | None = None) -> tuple:
     n = 0
-    while _host_bool(cond_fn(*state)):
-        new = body_fn(*state)
+    while _host_bool(_apply_state(cond_fn, state)):
+        new = _apply_state(body_fn, state)
         state = tuple(new) if isinstance(new, (tuple, list)) else (new,)
         realize_all(*pytree.tensor_leaves(state))
         n += 1
@@ -223,8 +253,9 @@ def _while_eager(cond_fn: Callable, body_fn: Callable, state: tuple, max_iters: 
 
 
 def while_loop(cond_fn: Callable, body_fn: Callable, init_val: Any):
-    """``while cond_fn(*state): state = body_fn(*state)``. ``init_val`` may be a single value or a
-    tuple; the loop state is realized every iteration so the lazy graph does not grow with the trip
+    """``while cond_fn(state): state = body_fn(state)`` (reference: nabla/ops/control_flow.py:560-577).
+    ``init_val`` may be a single value or a tuple / list of pytrees, handed to both functions as one
+    argument; the loop state is realized every iteration so the lazy graph does not grow with the trip
     count. Inside ``compile`` the whole loop is one recorded node whose trip count follows each
     call's data (module docstring)."""
     is_tuple = isinstance(init_val, (tuple, list))
@@ -233,7 +264,7 @@ def while_loop(cond_fn: Callable, body_fn: Callable, init_val: Any):
     st_tensors = [l for l in st_leaves if isinstance(l, Tensor)]
     if config.get_flag("TRACING") and st_tensors:
         # one lazy application of the body checks that the state keeps its structure
-        probe = body_fn(*state)
+        probe = _apply_state(body_fn, state)
         probe = tuple(probe) if isinstance(probe, (tuple, list)) else (probe,)
         _same_structure(st_leaves, pytree.tree_flatten(probe)[0], "while_loop")
         extra = [t for t in _closure_tensors(cond_fn, body_fn) if all(t._impl is not o._impl for o in st_tensors)]
@@ -248,19 +279,21 @@ def while_loop(cond_fn: Callable, body_fn: Callable, init_val: Any):
 
 def scan(f: Callable, init: Any, xs: Any, length: int | None = None, reverse: bool = False):
     """``carry, y_t = f(carry, x_t)`` over the leading axis of ``xs`` (unrolled in Python, so it
-    is differentiable). Returns ``(final_carry, stacked ys)``."""
-    if reverse:
-        raise NotImplementedError("scan(reverse=True) is not supported")
+    is differentiable). Returns ``(final_carry, stacked ys)``. ``reverse=True`` walks the axis from
+    its end; ``ys[t]`` still belongs to ``xs[t]`` (the reference accepts the flag but does not
+    implement it, nabla/ops/control_flow.py:598)."""
     from .view import stack
 
     leaves = pytree.tensor_leaves(xs)
     n = length if length is not None else (int(leaves[0].shape[0]) if leaves else 0)
     carry = init
     ys = []
-    for t in range(n):
+    for t in (range(n - 1, -1, -1) if reverse else range(n)):
         x_t = pytree.tree_map(lambda a: a[t] if isinstance(a, Tensor) else a, xs)
         carry, y = f(carry, x_t)
         ys.append(y)
+    if reverse:
+        ys.reverse()
     if not ys or ys[0] is None:
         return carry, None
     flat0, td = pytree.tree_flatten(ys[0])

@@ -203,8 +203,9 @@ def test_control_flow():
     close(ys, torch.tensor([1.0, 4.0, 12.0]))
     g = nb.grad(lambda v: nb.scan(lambda c, xt: (c * xt, c), nb.constant(1.0), v)[0])(T(torch.tensor([2.0, 3.0, 4.0])))
     close(g, torch.tensor([12.0, 8.0, 6.0]))
-    with pytest.raises(NotImplementedError):
-        nb.scan(lambda c, x: (c, x), 0, x, reverse=True)
+    carry, ys = nb.scan(lambda c, xt: (c + xt, c), nb.constant(0.0), T(torch.tensor([1.0, 2.0, 3.0])), reverse=True)
+    assert carry.item() == 6.0
+    close(ys, torch.tensor([5.0, 3.0, 0.0]))       # ys[t] belongs to xs[t]: the carry before element t, coming from the end
 
 
 def test_complex_views():

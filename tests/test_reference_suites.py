@@ -454,3 +454,61 @@ def test_cnn_training_loop_realizes_every_step_and_learns():
         assert all(v.is_realized for v in params.values())
         losses.append(loss.item())
     assert losses[-1] < losses[0] * 0.8, losses
+
+
+# ---------------------------------------------------------------- control flow, reference calling conventions
+def test_while_loop_passes_the_whole_state_as_one_argument():
+    def cond_fn(state):
+        i, _ = state
+        return i < 11.0
+
+    def body_fn(state):
+        i, acc = state
+        return (i + 1.0, acc + i)
+
+    i, acc = nb.while_loop(cond_fn, body_fn, (T(np.float32(1.0)), T(np.float32(0.0))))
+    assert i.item() == 11.0 and acc.item() == 55.0
+    assert nb.while_loop(lambda c: c < 10.0, lambda c: c + 1.0, T(np.float32(0.0))).item() == 10.0
+    # a sharded tensor in the loop state keeps its value and its shape
+    mesh = _mesh(2)
+    a = rand(8, 4, seed=81)
+    n, out = nb.while_loop(lambda st: st[0] < 5.0, lambda st: (st[0] + 1.0, st[1] + 1.0),
+                           (T(np.float32(0.0)), nb.shard(T(a), mesh, ("x", None))))
+    assert n.item() == 5.0 and tuple(int(d) for d in out.shape) == (8, 4)
+    close(out, a + 5.0)
+    # the loop leaves as soon as the condition fails, also when that is before the first iteration
+    v = nb.while_loop(lambda t: nb.reduce_sum(t) < 0.0, lambda t: t * 2.0, T(np.ones(3, np.float32)))
+    close(v, np.ones(3))
+    # a dict inside the state
+    st = nb.while_loop(lambda s: s[0]["k"] < 3.0, lambda s: ({"k": s[0]["k"] + 1.0}, s[1] * 2.0),
+                       ({"k": T(np.float32(0.0))}, T(np.ones(2, np.float32))))
+    assert st[0]["k"].item() == 3.0
+    close(st[1], np.full(2, 8.0))
+
+
+def test_cond_and_scan_conventions():
+    a = rand(4, 6, seed=82)
+    yes, no = nb.constant(np.array(True)), nb.constant(np.array(False))
+    close(nb.cond(yes, lambda u, v: u + v, lambda u, v: u - v, T(a), T(a)), 2 * a)
+    close(nb.cond(no, lambda u, v: u + v, lambda u, v: u - v, T(a), T(a)), 0 * a)
+    out = nb.cond(yes, lambda u: {"a": u * 2.0, "b": [u + 1.0]}, lambda u: {"a": u, "b": [u]}, T(a))
+    close(out["a"], 2 * a)
+    close(out["b"][0], a + 1)
+    mesh = _mesh(2)
+    xs = nb.shard(T(a), mesh, ("x", None))
+    r = nb.cond(no, lambda u: u * 2.0, lambda u: nb.reduce_sum(u, axis=0, keepdims=True) + u, xs)
+    close(r, a.sum(0, keepdim=True) + a, rtol=1e-5, atol=1e-5)
+    carry, ys = nb.scan(lambda c, v: (c + v, c + v), T(np.zeros(6, np.float32)), T(a))
+    close(ys, torch.cumsum(a, 0), rtol=1e-5, atol=1e-5)
+    close(carry, a.sum(0), rtol=1e-5, atol=1e-5)
+    carry, ys = nb.scan(lambda c, v: (c * v, c * v), T(np.ones(6, np.float32)), nb.shard(T(a), mesh, (None, "x")))
+    close(ys, torch.cumprod(a, 0), rtol=1e-4, atol=1e-5)
+    seqs = rand(3, 5, 2, seed=83)
+    f = lambda seq: nb.scan(lambda c, v: ({"s": c["s"] + v, "n": c["n"] + 1.0}, c["s"]),
+                            {"s": T(np.zeros(2, np.float32)), "n": nb.constant(np.float32(0.0))}, seq)
+    carry, ys = nb.vmap(f)(T(seqs))
+    close(carry["s"], seqs.sum(1), rtol=1e-5, atol=1e-5)
+    close(carry["n"], np.full(3, 5.0))
+    rev_carry, rev = nb.scan(lambda c, v: (c + v, c), T(np.zeros(6, np.float32)), T(a), reverse=True)
+    close(rev_carry, a.sum(0), rtol=1e-5, atol=1e-5)
+    close(rev[0], a[1:].sum(0), rtol=1e-5, atol=1e-5)
