@@ -9,6 +9,8 @@ needs torch.
 """
 from __future__ import annotations
 
+from importlib import metadata  # noqa: F401  (the reference exposes it the same way)
+
 from . import config, nn, testing
 from .core import (GRAPH, PyTreeDef, Tensor, TensorImpl, default_device, default_dtype, defaults, defaults_like,
                    is_tensor, realize_all, register_pytree_node, tensor_leaves, traced, tree_flatten, tree_leaves,

@@ -112,6 +112,11 @@ def is_deterministic() -> bool:
     return _DETERMINISTIC.get()
 
 
+# names the reference uses for the same things (nabla/config.py:26-39, 103-109)
+_EAGER_MAX_GRAPH = _EAGER
+_VERIFY_EAGER_SHAPES = _VERIFY
+tracing_context = tracing
+
 _DEBUG_ON = ("1", "true", "TRUE", "True")
 
 

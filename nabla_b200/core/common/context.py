@@ -71,3 +71,14 @@ def defaults_like(like):
 
 def set_default_device(device) -> None:
     _DEVICE.set(as_device(device))
+
+
+def _in_running_loop() -> bool:
+    """True inside a running asyncio event loop (reference: nabla/core/common/context.py:142-148)."""
+    import asyncio
+
+    try:
+        asyncio.get_running_loop()
+    except RuntimeError:
+        return False
+    return True

@@ -180,10 +180,16 @@ def leaf_names(treedef: PyTreeDef, prefix: str = "") -> list[str]:
     return out
 
 
-def tree_flatten_full(tree: Any, is_leaf=None) -> tuple[list, list[str], PyTreeDef]:
+def tree_flatten_with_names(tree: Any, is_leaf=None) -> tuple[list, list[str], PyTreeDef]:
     """``tree_flatten`` plus the path name of every leaf: ``(leaves, names, treedef)``."""
     leaves, td = tree_flatten(tree, is_leaf)
     return leaves, leaf_names(td), td
+
+
+def tree_flatten_full(tree: Any, is_leaf=None) -> tuple[list, PyTreeDef]:
+    """``tree_flatten`` that keeps ``None`` as a leaf instead of a structural node
+    (reference: nabla/core/common/pytree.py:227-236)."""
+    return tree_flatten(tree, is_leaf=lambda x: x is None or (is_leaf(x) if is_leaf else False))
 
 
 def tree_structure(tree: Any, is_leaf=None) -> PyTreeDef:
@@ -276,3 +282,8 @@ def with_batch_dims(tree: Any, delta: int) -> Any:
         return x
 
     return tree_map(f, tree)
+
+
+def tree_unflatten_full(treedef: PyTreeDef, leaves: list) -> Any:
+    """Inverse of a flatten that kept ``None`` leaves (reference: nabla/core/common/pytree.py:239-241)."""
+    return tree_unflatten(treedef, leaves)

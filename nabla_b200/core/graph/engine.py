@@ -213,7 +213,13 @@ def run_node(node: OpNode) -> None:
 
 
 _GRAPH_VAR: ContextVar[ComputeGraph | None] = ContextVar("nabla_graph", default=None)
+_CURRENT_GRAPH = _GRAPH_VAR          # the reference's name for the per-context graph variable (engine.py:922)
 _DEFAULT_GRAPH = ComputeGraph()
+
+
+def _get_current_graph() -> ComputeGraph:
+    """The graph of the current context (reference: nabla/core/graph/engine.py, same name)."""
+    return _GRAPH_VAR.get() or _DEFAULT_GRAPH
 
 
 class _GraphProxy:

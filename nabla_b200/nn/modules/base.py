@@ -15,6 +15,7 @@ from ...core.common.pytree import is_tensor, register_pytree_node
 from ...core.tensor.api import Tensor, realize_all
 
 _CALL_DEPTH: ContextVar[int] = ContextVar("nabla_module_call_depth", default=0)
+_MODULE_CALL_DEPTH = _CALL_DEPTH      # the reference's name (nabla/nn/modules/base.py:15)
 _RESERVED = ("_parameters", "_buffers", "_modules", "_training")
 
 

@@ -30,3 +30,5 @@ pmean_op = _ComposedOp("pmean", pmean)
 all_to_all_op = _ComposedOp("all_to_all", all_to_all)
 distributed_broadcast_op = _ComposedOp("distributed_broadcast", distributed_broadcast)
 axis_index_op = _ComposedOp("axis_index", axis_index)
+from .collectives import (AllGatherOp, AllReduceOp, GatherAllAxesOp, PPermuteOp, ReduceScatterOp, RelabelOp, ShardOp,  # noqa: F401,E402
+                          TransferOp)

@@ -289,6 +289,57 @@ def reduce_sum_physical(x, axis: int, keepdims: bool = False) -> Tensor:
     return _reduce_sum_physical(x, axis=axis, keepdims=keepdims)
 
 
+class _PhysExtremeMixin(_PhysMixin):
+    """Derivative rules of max / min over a physical axis: the cotangent (tangent) goes to (comes
+    from) the positions that hold the extreme value, shared equally between ties."""
+
+    def _mask(self, x, outputs, kwargs):
+        from .comparison import equal
+        from .unary import cast
+        from .view.axes import unsqueeze_physical
+        from .view.shape import broadcast_to_physical
+
+        y = outputs if kwargs.get("keepdims", False) else unsqueeze_physical(outputs, axis=kwargs["axis"])
+        shape = tuple(x._impl._shape)
+        mask = cast(equal(x, broadcast_to_physical(y, shape)), x.dtype)
+        count = reduce_sum_physical(mask, axis=kwargs["axis"], keepdims=True)
+        return mask / broadcast_to_physical(count, shape), shape
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        from .view.axes import unsqueeze_physical
+        from .view.shape import broadcast_to_physical
+
+        w, shape = self._mask(primals[0], outputs, kwargs)
+        if not kwargs.get("keepdims", False):
+            cot = unsqueeze_physical(cot, axis=kwargs["axis"])
+        return (broadcast_to_physical(cot, shape) * w,)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        w, _ = self._mask(primals[0], outputs, kwargs)
+        return reduce_sum_physical(tangents[0] * w, **kwargs)
+
+
+class ReduceMaxPhysicalOp(_PhysExtremeMixin, ReduceMaxOp):
+    _name = "reduce_max_physical"
+
+
+class ReduceMinPhysicalOp(_PhysExtremeMixin, ReduceMinOp):
+    _name = "reduce_min_physical"
+
+
+_reduce_max_physical, _reduce_min_physical = ReduceMaxPhysicalOp(), ReduceMinPhysicalOp()
+
+
+def reduce_max_physical(x, axis: int, keepdims: bool = False) -> Tensor:
+    """Maximum over a PHYSICAL axis (batch dimensions count; reference: nabla/ops/reduction.py:712)."""
+    return _reduce_max_physical(x, axis=axis, keepdims=keepdims)
+
+
+def reduce_min_physical(x, axis: int, keepdims: bool = False) -> Tensor:
+    """Minimum over a PHYSICAL axis (reference: nabla/ops/reduction.py:735)."""
+    return _reduce_min_physical(x, axis=axis, keepdims=keepdims)
+
+
 def mean_physical(x, axis: int, keepdims: bool = False) -> Tensor:
     n = x._impl._shape[axis]
     return reduce_sum_physical(x, axis=axis, keepdims=keepdims) * (1.0 / max(n, 1))

@@ -42,3 +42,52 @@ def call_custom_kernel(func_name: str, kernel_path: Any, values, out_types, devi
     from .custom import call_custom_kernel as impl
 
     return impl(func_name, kernel_path, values, out_types, device=device, **kwargs)
+
+
+# ---------------------------------------------------------------- hashable keys (reference: nabla/ops/utils.py:74-160)
+_HASHABLE_CACHE: dict[int, Any] = {}
+
+
+def _clear_hashable_cache() -> None:
+    """Drop the per-object cache of ``_make_hashable``."""
+    _HASHABLE_CACHE.clear()
+
+
+def _get_tensor_hash(t) -> tuple:
+    """Structural key of a tensor: shape, dtype, device and sharding signature (no values)."""
+    impl = t._impl if hasattr(t, "_impl") else t
+    sp = impl.sharding
+    sharding_key = None
+    if sp is not None:
+        mesh = sp.mesh
+        sharding_key = ((mesh.name, tuple(mesh.shape), tuple(mesh.axis_names)),
+                        tuple((tuple(d.axes),) for d in sp.dim_specs), tuple(sorted(sp.replicated_axes)),
+                        tuple(sorted(sp.partial_sum_axes)))
+    return ("tensor", tuple(int(d) for d in impl._shape), str(impl.dtype), str(impl.device), int(impl.batch_dims),
+            sharding_key)
+
+
+def _make_hashable(obj: Any) -> Any:
+    """Stable, hashable key of an op argument: tensors by structure, containers element-wise,
+    everything else by value (or by ``repr`` when it is not hashable)."""
+    from ..core.tensor.api import Tensor
+
+    if isinstance(obj, Tensor):
+        key = _HASHABLE_CACHE.get(id(obj))
+        if key is None:
+            key = _get_tensor_hash(obj)
+            if len(_HASHABLE_CACHE) > 1024:
+                _HASHABLE_CACHE.clear()
+            _HASHABLE_CACHE[id(obj)] = key
+        return key
+    if isinstance(obj, (list, tuple)):
+        return tuple(_make_hashable(o) for o in obj)
+    if isinstance(obj, dict):
+        return tuple(sorted(((k, _make_hashable(v)) for k, v in obj.items()), key=lambda kv: str(kv[0])))
+    if isinstance(obj, (set, frozenset)):
+        return tuple(sorted((_make_hashable(o) for o in obj), key=repr))
+    try:
+        hash(obj)
+        return obj
+    except TypeError:
+        return repr(obj)

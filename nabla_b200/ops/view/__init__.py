@@ -6,3 +6,4 @@ from .complex import as_interleaved_complex, view_as_real_interleaved
 from .indexing import gather, scatter, scatter_add, take
 from .shape import (broadcast_to, broadcast_to_physical, concatenate, flatten, pad, rebind, reshape, slice_tensor,
                     slice_update, slice_update_inplace, stack)
+from .axes import SqueezePhysicalOp, UnsqueezePhysicalOp  # noqa: F401,E402

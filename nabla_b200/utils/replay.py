@@ -85,7 +85,7 @@ def _copy_leaf(x: Any) -> Any:
 
 def _snapshot(tree: Any) -> list[tuple[str, list[torch.Tensor]]]:
     """(path, [clone of every local shard]) for every tensor leaf of ``tree``."""
-    leaves, names, _ = pytree.tree_flatten_full(tree, is_leaf=_is_tensor)
+    leaves, names, _ = pytree.tree_flatten_with_names(tree, is_leaf=_is_tensor)
     out = []
     for name, leaf in zip(names, leaves):
         if isinstance(leaf, Tensor):

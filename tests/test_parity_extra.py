@@ -9,6 +9,8 @@ import torch
 
 import nabla_b200 as nb
 
+from common import T, close, rand
+
 
 def _f(x):
     return nb.sum(nb.tanh(x) * x * x)
@@ -203,6 +205,66 @@ def test_reexports_and_path_names():
                  "ppermute_op", "all_to_all_op", "distributed_broadcast_op", "axis_index_op", "CollectiveOperation"):
         assert hasattr(C, name), name
     assert C.all_reduce_op.name == "all_reduce" and C.pmean_op.name == "pmean"
-    leaves, names, td = pytree.tree_flatten_full({"b": [1, (2, 3)], "a": {"x": 4}})
+    leaves, names, td = pytree.tree_flatten_with_names({"b": [1, (2, 3)], "a": {"x": 4}})
     assert leaves == [4, 1, 2, 3] and names == ["a.x", "b[0]", "b[1][0]", "b[1][1]"]
     assert pytree.leaf_names(td, "lora") == ["lora.a.x", "lora.b[0]", "lora.b[1][0]", "lora.b[1][1]"]
+
+
+def test_names_the_reference_tests_import_resolve_here():
+    """Every name that the reference's unit tests and examples import from `nabla...` resolves under
+    `nabla_b200...` (private context variables, op classes, helper functions)."""
+    import importlib
+
+    wanted = {
+        "": ["metadata"],
+        ".config": ["_EAGER_MAX_GRAPH", "_VERIFY_EAGER_SHAPES", "_TRACING", "tracing_context"],
+        ".core": ["ComputeGraph", "apply_to_operations", "get_all_impls_topological", "get_operations_topological",
+                  "print_trace_graph", "driver_tensor_type", "_in_running_loop"],
+        ".core.common": ["_in_running_loop", "tree_flatten_full", "tree_unflatten_full"],
+        ".core.graph": ["apply_to_operations", "driver_tensor_type", "get_all_impls_topological",
+                        "get_operations_topological"],
+        ".core.graph.engine": ["_CURRENT_GRAPH", "_get_current_graph", "_GraphProxy", "ComputeGraph", "GRAPH"],
+        ".nn.modules.base": ["_MODULE_CALL_DEPTH"],
+        ".ops": ["BinaryOp", "UnaryOp", "ReduceOp", "CreationOp", "CollectiveOp", "_make_hashable", "_get_tensor_hash",
+                 "_clear_hashable_cache", "shard", "reshard", "all_reduce", "all_gather", "all_to_all", "reduce_scatter",
+                 "ppermute", "cpu", "gpu", "accelerator", "to_device", "transfer_to", "distributed_broadcast", "cond",
+                 "scan", "where", "while_loop", "conv2d", "conv2d_transpose", "avg_pool2d", "max_pool2d"],
+        ".ops.view": ["SqueezePhysicalOp", "squeeze_physical", "unsqueeze_physical"],
+        ".ops.reduction": ["reduce_max_physical", "reduce_min_physical", "reduce_sum_physical", "mean_physical"],
+        ".ops.communication": ["AllGatherOp", "AllReduceOp", "ReduceScatterOp", "all_gather", "reshard"],
+        ".ops.custom_op": ["call_custom_kernel"],
+        ".transforms.utils": ["std_basis", "lift_basis_to_batch_prefix"],
+    }
+    for mod, names in wanted.items():
+        m = importlib.import_module("nabla_b200" + mod)
+        for n in names:
+            assert hasattr(m, n), f"nabla_b200{mod}.{n}"
+
+
+def test_physical_extreme_reductions_and_basis_helpers():
+    from nabla_b200.ops.reduction import reduce_max_physical, reduce_min_physical
+    from nabla_b200.ops.view import broadcast_batch_dims
+    from nabla_b200.transforms.utils import lift_basis_to_batch_prefix, std_basis
+
+    x0 = rand(2, 3, 4, seed=91)
+    for red, tred, axis in ((reduce_max_physical, torch.amax, 2), (reduce_min_physical, torch.amin, 1)):
+        f = lambda t: nb.reduce_sum(red(t * t + 0.1, axis=axis))
+        xt = x0.clone().requires_grad_(True)
+        tred(xt * xt + 0.1, axis).sum().backward()
+        close(nb.grad(f)(T(x0)), xt.grad, rtol=1e-5, atol=1e-5)
+        hs = [h(T(x0)).to_numpy() for h in (nb.jacrev(nb.jacrev(f)), nb.jacfwd(nb.jacrev(f)), nb.jacrev(nb.jacfwd(f)),
+                                             nb.jacfwd(nb.jacfwd(f)))]
+        for h in hs[1:]:
+            np.testing.assert_allclose(h, hs[0], rtol=5e-3, atol=5e-3)
+    ref = broadcast_batch_dims(T(torch.tensor([1.0, 2.0, 3.0])), (4,))
+    sizes, basis = std_basis([ref])
+    assert sizes == [3] and basis[0].batch_dims == 0
+    lifted = lift_basis_to_batch_prefix(basis, [ref])
+    assert lifted[0].batch_dims == ref.batch_dims
+    assert tuple(lifted[0]._impl.physical_global_shape[:1]) == tuple(ref._impl.physical_global_shape[:1]) == (4,)
+    assert lift_basis_to_batch_prefix(lifted, [ref])[0].batch_dims == 1       # already lifted: left alone
+    x = T(torch.tensor([[1.0, 2.0], [3.0, 4.0]]))
+    for jac in (nb.jacrev, nb.jacfwd):
+        j = nb.vmap(jac(lambda v: nb.reduce_sum(v * v * v)))(x)
+        assert j.batch_dims == 0 and tuple(int(d) for d in j.shape) == (2, 2)
+        close(j, 3.0 * x.to_numpy() ** 2, rtol=1e-5)
