@@ -14,6 +14,7 @@ import torch
 
 from ...types import CPU, Accelerator, Device, DType, Shape, as_device, as_dtype
 from .impl import TensorImpl
+from ..common.context import default_device, default_dtype, defaults, defaults_like  # noqa: F401  (re-exported as in the reference)
 
 
 class Tensor:
@@ -731,3 +732,13 @@ def _install_operators() -> None:
 
 
 _install_operators()
+
+
+def __getattr__(name: str):
+    # `GRAPH` is importable from here as in the reference (nabla/core/tensor/api.py:44); resolved
+    # lazily because the engine module imports this one
+    if name == "GRAPH":
+        from ..graph.engine import GRAPH
+
+        return GRAPH
+    raise AttributeError(name)

@@ -26,9 +26,33 @@ class _ComposedOp:
         return f"<composed op {self.name}>"
 
 
-pmean_op = _ComposedOp("pmean", pmean)
-all_to_all_op = _ComposedOp("all_to_all", all_to_all)
-distributed_broadcast_op = _ComposedOp("distributed_broadcast", distributed_broadcast)
-axis_index_op = _ComposedOp("axis_index", axis_index)
+class PMeanOp(_ComposedOp):
+    """all-reduce followed by a scale by 1 / group size."""
+
+
+class AllToAllOp(_ComposedOp):
+    """a change of layout: the split axis becomes replicated and the concat axis sharded."""
+
+
+class DistributedBroadcastOp(_ComposedOp):
+    """replication of one rank's value over the mesh."""
+
+
+class AxisIndexOp(_ComposedOp):
+    """a constant per device: its coordinate along a mesh axis."""
+
+
+pmean_op = PMeanOp("pmean", pmean)
+all_to_all_op = AllToAllOp("all_to_all", all_to_all)
+distributed_broadcast_op = DistributedBroadcastOp("distributed_broadcast", distributed_broadcast)
+axis_index_op = AxisIndexOp("axis_index", axis_index)
+
+
+def create_replicated_spec(mesh, rank: int):
+    """Fully replicated sharding spec of a rank-``rank`` tensor on ``mesh``
+    (reference: nabla/ops/communication/shard.py:356-368)."""
+    from ...core.sharding.spec import DimSpec, ShardingSpec
+
+    return ShardingSpec(mesh, [DimSpec([]) for _ in range(rank)])
 from .collectives import (AllGatherOp, AllReduceOp, GatherAllAxesOp, PPermuteOp, ReduceScatterOp, RelabelOp, ShardOp,  # noqa: F401,E402
                           TransferOp)

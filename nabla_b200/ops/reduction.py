@@ -238,6 +238,26 @@ def mean(x, *, axis=None, keepdims: bool = False) -> Tensor:
     return s * (1.0 / max(n, 1))
 
 
+class MeanOp(ReduceSumOp):
+    """``mean`` under the reference's op name (nabla/ops/reduction.py). Calling the op gives the
+    same composition as ``mean``: a sum (all-reduced when the axis is sharded) scaled by one over the
+    GLOBAL extent, so sharded inputs need no rule of their own."""
+
+    _name = "mean"
+
+    def __call__(self, x, *, axis=None, keepdims: bool = False):
+        return mean(x, axis=axis, keepdims=keepdims)
+
+
+class MeanPhysicalOp(MeanOp):
+    """``mean_physical`` under the reference's op name: the axis indexes the physical shape."""
+
+    _name = "mean_physical"
+
+    def __call__(self, x, *, axis: int, keepdims: bool = False):
+        return mean_physical(x, axis=axis, keepdims=keepdims)
+
+
 def argmax(x, axis: int = -1, keepdims: bool = False) -> Tensor:
     return _argmax(ensure_tensor(x), axis=axis, keepdims=keepdims)
 

@@ -252,3 +252,5 @@ def unsqueeze_physical(x, axis: int) -> Tensor:
 
 def squeeze_physical(x, axis: int) -> Tensor:
     return _squeeze_p(x, axis=int(axis))
+
+MoveAxisOp = MoveaxisOp      # spelling of the reference (nabla/ops/view/axes.py)

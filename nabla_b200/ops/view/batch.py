@@ -153,3 +153,5 @@ def broadcast_batch_dims(x, batch_shape) -> Tensor:
     if x._impl.batch_dims >= len(batch_shape):
         return x
     return _bbd(x, batch_shape=batch_shape, own=x._impl.batch_dims)
+
+MoveAxisPhysicalOp = MoveaxisPhysicalOp      # spelling of the reference (nabla/ops/view/batch.py)

@@ -234,9 +234,24 @@ def test_names_the_reference_tests_import_resolve_here():
         ".ops.communication": ["AllGatherOp", "AllReduceOp", "ReduceScatterOp", "all_gather", "reshard"],
         ".ops.custom_op": ["call_custom_kernel"],
         ".transforms.utils": ["std_basis", "lift_basis_to_batch_prefix"],
+        ".ops.reduction ": ["MeanOp", "MeanPhysicalOp"],
+        ".ops.view.axes": ["MoveAxisOp"],
+        ".ops.view.batch": ["MoveAxisPhysicalOp"],
+        ".core.tensor.api": ["GRAPH", "default_device", "default_dtype", "defaults", "defaults_like"],
+        ".ops.communication.all_gather": ["AllGatherOp", "GatherAllAxesOp", "all_gather", "gather_all_axes"],
+        ".ops.communication.all_reduce": ["AllReduceOp", "PMeanOp", "all_reduce", "pmean"],
+        ".ops.communication.all_to_all": ["AllToAllOp", "all_to_all"],
+        ".ops.communication.axis_index": ["AxisIndexOp", "axis_index"],
+        ".ops.communication.base": ["CollectiveOperation"],
+        ".ops.communication.broadcast": ["DistributedBroadcastOp", "distributed_broadcast"],
+        ".ops.communication.p_permute": ["PPermuteOp", "ppermute"],
+        ".ops.communication.reduce_scatter": ["ReduceScatterOp", "reduce_scatter"],
+        ".ops.communication.reshard": ["reshard", "reshard_tensor", "create_replicated_spec"],
+        ".ops.communication.shard": ["ShardOp", "create_replicated_spec", "shard", "broadcast"],
+        ".ops.communication.transfer": ["TransferOp", "to_device", "transfer_to", "cpu", "gpu", "accelerator"],
     }
     for mod, names in wanted.items():
-        m = importlib.import_module("nabla_b200" + mod)
+        m = importlib.import_module("nabla_b200" + mod.strip())
         for n in names:
             assert hasattr(m, n), f"nabla_b200{mod}.{n}"
 
