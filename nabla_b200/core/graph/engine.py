@@ -117,6 +117,13 @@ class ComputeGraph:
         self.seed = 0
         self.rng_counter = 0
         self.seed_epoch = 0          # bumped by set_seed: device-resident stream states re-read (seed, counter)
+        # attributes of the reference's graph object (nabla/core/graph/engine.py). There `graph` is the
+        # MAX graph under construction and `sources` / `unrealized` its inputs and pending outputs;
+        # evaluation here walks the trace from the requested tensors, so these only identify the
+        # context's graph object and stay empty.
+        self.graph = self
+        self.sources: dict = {}
+        self.unrealized: dict = {}
 
     # ---- RNG: counter-based, carried by the engine across evaluations
     def set_seed(self, seed: int) -> None:

@@ -56,6 +56,23 @@ class OpNode:
     def op_name(self) -> str:
         return self.op.name
 
+    # ---- the reference's names for the same things (nabla/core/graph/tracing.py:28-60)
+    @property
+    def num_outputs(self) -> int:
+        return len(self.out_refs)
+
+    @property
+    def op_args(self):
+        return self.args_as_tensors()
+
+    @property
+    def tree_def(self):
+        return self.out_treedef
+
+    def get_alive_outputs(self) -> list[TensorImpl | None]:
+        """Outputs that are still referenced (``None`` for those already collected)."""
+        return self.outputs()
+
     def __repr__(self) -> str:
         return f"OpNode({self.op.name}, inputs={len(self.input_impls())}, outputs={len(self.out_refs)})"
 

@@ -71,6 +71,8 @@ class DeviceMesh:
             raise ValueError(f"mesh of shape {self.shape} needs {n} devices, got {len(self.devices)}")
         self.bandwidth = float(bandwidth)
         self.strides = tuple(math.prod(self.shape[i + 1:]) for i in range(len(self.shape)))
+        self.phys_strides = list(self.strides)                                   # the reference's name
+        self.axis_lookup = {a: i for i, a in enumerate(self.axis_names)}
         self._groups: dict[tuple[str, ...], Any] = {}
         # ---- execution mode
         self.rank: int | None = None
@@ -165,6 +167,23 @@ class DeviceMesh:
 
     def get_devices_on_axis_slice(self, axis_name: str, index: int) -> list[int]:
         return [d for d in range(len(self.devices)) if self.get_coordinate(d, axis_name) == index]
+
+    def get_signal_buffers(self, buffer_size: int = 65536, use_cache: bool = False) -> list:
+        """Flag memory that the collectives of this mesh synchronise through, one entry per locally
+        held device (reference: nabla/core/sharding/spec.py:152, MAX signal buffers). Here the flags
+        are the first 64 KB of the symmetric workspace of the whole-mesh group
+        (`parallel/symm.py`); a simulated mesh, or a process without a GPU, has none."""
+        if not self.is_distributed:
+            return []
+        try:
+            from ...parallel import symm
+
+            if not symm.is_ready():
+                return []
+            ws = symm.workspace(self, tuple(self.axis_names))
+            return [ws.buf[: min(int(buffer_size), ws.flag_bytes)]]
+        except Exception:
+            return []
 
     def process_group(self, axes: Iterable[str]):
         """torch.distributed group of this rank along ``axes`` (distributed mode only)."""
@@ -299,6 +318,14 @@ class ShardingSpec:
     @property
     def total_shards(self) -> int:
         return math.prod(d.get_total_shards(self.mesh) for d in self.dim_specs)
+
+    def get_max_priority(self) -> int:
+        """Largest (least urgent) propagation priority among the dimensions."""
+        return max((d.priority for d in self.dim_specs), default=0)
+
+    def get_min_priority(self) -> int:
+        """Smallest (most urgent) propagation priority among the dimensions."""
+        return min((d.priority for d in self.dim_specs), default=0)
 
     def clone(self, **changes) -> "ShardingSpec":
         return ShardingSpec(changes.get("mesh", self.mesh),

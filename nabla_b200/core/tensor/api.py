@@ -43,6 +43,37 @@ class Tensor:
     def real(self) -> bool:
         return self._impl.is_realized
 
+    # ---- the reference's accessors of the backing storage (nabla/core/tensor/api.py:95-160, 431-439,
+    # 617-674). There the storage is a MAX driver buffer or a value of the graph being built; here it
+    # is the list of torch tensors of the locally held shards.
+    @property
+    def driver_tensor(self) -> torch.Tensor:
+        if (b := self.buffers) is None:
+            raise TypeError("Can't get driver tensor for symbolic tensor")
+        return b
+
+    @property
+    def values(self) -> list[torch.Tensor]:
+        """The locally held shards (realizes the tensor first)."""
+        self.hydrate()
+        return list(self._impl._buffers)
+
+    @property
+    def type(self):
+        """(shape, dtype, device) of the global tensor."""
+        return tuple(int(d) for d in self._impl.global_shape), self._impl.dtype, self._impl.device
+
+    def hydrate(self) -> "Tensor":
+        """Make the data available: realize a promise, leave a realized tensor alone."""
+        if not self._impl.is_realized:
+            self.realize()
+        return self
+
+    @classmethod
+    def _create_unsafe(cls, **kwargs: Any) -> "Tensor":
+        """Tensor straight from ``TensorImpl`` arguments (no validation)."""
+        return cls(impl=TensorImpl(**kwargs))
+
     @property
     def is_realized(self) -> bool:
         return self._impl.is_realized

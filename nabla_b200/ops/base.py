@@ -134,6 +134,40 @@ class Operation:
         return len(input_shapes[0]) if input_shapes else 0
 
     # ------------------------------------------------------------------ partial-sum policy
+    multiple_results: bool = False       # the reference's flag for ops with several outputs (ops/base.py:121)
+
+    @property
+    def allows_partial_passthrough(self) -> bool:
+        """Whether this op may ever defer the all-reduce of a pending partial sum
+        (reference: nabla/ops/base.py:140-146); `partial_passthrough_axes` decides per call."""
+        return self.partial_policy != "none"
+
+    def get_sharding_rule_template(self):
+        """Ops here give their rule through `sharding_rule` (instantiated per call); there is no
+        shape-independent template object (reference: nabla/ops/base.py:472-473 returns None too)."""
+        return None
+
+    def compute_physical_shape(self, args, kwargs, output_sharding=None):
+        """Per-shard output shapes, dtypes and devices of a call, without running it
+        (reference: nabla/ops/base.py:397-410). Shapes come from the op's own shape inference on
+        meta tensors; with an output sharding every shard's extent follows the ceil-div rule."""
+        from ..core.sharding.spec import compute_local_shape
+        from ..core.tensor.api import Tensor
+
+        probe = self(*args, **(kwargs or {}))
+        outs = [t for t in pytree.tree_leaves(probe) if isinstance(t, Tensor)]
+        shapes, dtypes, devices = [], [], []
+        for t in outs:
+            sp = output_sharding if output_sharding is not None else t.sharding
+            g = tuple(int(d) for d in t._impl.physical_global_shape)
+            if sp is None:
+                shapes.append(g)
+            else:
+                shapes.append([compute_local_shape(g, sp, d) for d in range(len(sp.mesh.devices))])
+            dtypes.append(t.dtype)
+            devices.append(t.device)
+        return shapes, dtypes, devices
+
     def partial_passthrough_axes(self, input_specs: Sequence, kwargs: dict | None = None) -> set[str]:
         specs = [s for s in input_specs if s is not None]
         if not specs or self.partial_policy == "none":

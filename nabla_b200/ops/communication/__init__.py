@@ -56,3 +56,15 @@ def create_replicated_spec(mesh, rank: int):
     return ShardingSpec(mesh, [DimSpec([]) for _ in range(rank)])
 from .collectives import (AllGatherOp, AllReduceOp, GatherAllAxesOp, PPermuteOp, ReduceScatterOp, RelabelOp, ShardOp,  # noqa: F401,E402
                           TransferOp)
+
+# The reference keeps every collective in a module named like its function (`.shard`, `.all_reduce`, ...).
+# Those module paths exist here as thin re-exports; they are loaded now, and the function names are
+# bound again afterwards, because loading a submodule binds its name on the package.
+import importlib as _importlib  # noqa: E402
+
+for _m in ("all_gather", "all_reduce", "all_to_all", "axis_index", "base", "broadcast", "p_permute", "reduce_scatter",
+           "reshard", "shard", "transfer"):
+    _importlib.import_module(__name__ + "." + _m)      # (`from . import shard` would just return the function)
+del _m
+from .collectives import (all_gather, all_reduce, all_to_all, axis_index, broadcast, reduce_scatter, reshard,  # noqa: F401,E402,F811
+                          shard)

@@ -71,6 +71,17 @@ class CompilationStats:
     cuda_graphs: int = 0
     launches_per_graph: int = 0      # this package's kernels inside the last captured CUDA graph
 
+    cache_size: int = 0              # entries in the LRU cache of the owning CompiledFunction
+
+    # the reference's field names (nabla/transforms/compile.py:48-58), in milliseconds
+    @property
+    def total_compile_time_ms(self) -> float:
+        return self.compile_time_s * 1e3
+
+    @property
+    def total_cached_exec_time_ms(self) -> float:
+        return self.replay_time_s * 1e3
+
     @property
     def hit_rate(self) -> float:
         t = self.hits + self.misses
@@ -281,6 +292,7 @@ class CompiledFunction:
             self._cache[key] = entry
             while len(self._cache) > self.max_cache_size:
                 self._cache.popitem(last=False)
+            self._stats.cache_size = len(self._cache)
         else:
             self._cache.move_to_end(key)
             self._stats.hits += 1

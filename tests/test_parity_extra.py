@@ -283,3 +283,36 @@ def test_physical_extreme_reductions_and_basis_helpers():
         j = nb.vmap(jac(lambda v: nb.reduce_sum(v * v * v)))(x)
         assert j.batch_dims == 0 and tuple(int(d) for d in j.shape) == (2, 2)
         close(j, 3.0 * x.to_numpy() ** 2, rtol=1e-5)
+
+
+def test_small_members_the_reference_exposes_on_its_classes():
+    import nabla_b200.ops.binary as B
+    from nabla_b200.core.graph.engine import GRAPH, _get_current_graph
+
+    x = T(torch.ones(2, 3))
+    y = x * 2.0
+    with pytest.raises(TypeError):
+        (x * 3.0).driver_tensor                       # a promise has no storage yet
+    assert y.hydrate().real and len(y.values) == 1 and tuple(y.driver_tensor.shape) == (2, 3)
+    assert y.type[0] == (2, 3)
+    g = _get_current_graph()
+    assert GRAPH.graph is g.graph and GRAPH.sources is g.sources
+    node = (x * 2.0)._impl.output_refs
+    assert node.num_outputs == 1 and len(node.get_alive_outputs()) == 1 and len(node.op_args) == 2
+    mesh = nb.DeviceMesh("m4", (2, 2), ("a", "b"))
+    assert mesh.axis_lookup == {"a": 0, "b": 1} and mesh.phys_strides == [2, 1] and mesh.get_signal_buffers() == []
+    spec = nb.ShardingSpec(mesh, [nb.DimSpec(["a"], priority=2), nb.DimSpec([])])
+    assert spec.get_max_priority() == 2 and spec.get_min_priority() == 0
+    add_op = next(v for v in vars(B).values() if getattr(v, "name", None) == "add")
+    assert add_op.allows_partial_passthrough and not add_op.multiple_results
+    shapes, dtypes, devices = add_op.compute_physical_shape((x, x), {})
+    assert shapes == [(2, 3)] and dtypes == [nb.DType.float32]
+    c = nb.compile(lambda t: t * 2.0)
+    c(x)
+    assert c.stats.cache_size == 1 and c.stats.total_compile_time_ms > 0 and c.stats.total_cached_exec_time_ms >= 0
+    # the package's function names survive the import of the like-named reference module paths
+    import nabla_b200.ops.communication.shard  # noqa: F401
+    import nabla_b200.ops.communication.all_reduce  # noqa: F401
+    from nabla_b200.ops.communication import all_reduce, shard
+
+    assert callable(shard) and callable(all_reduce) and callable(nb.shard)
