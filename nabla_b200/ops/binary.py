@@ -196,42 +196,42 @@ _add, _sub, _mul, _div, _mod, _pow, _outer, _matmul = (AddOp(), SubOp(), MulOp()
                                                        OuterOp(), MatmulOp())
 
 
-def add(a, b) -> Tensor:
-    return _add(a, b)
+def add(x, y) -> Tensor:
+    return _add(x, y)
 
 
-def sub(a, b) -> Tensor:
-    return _sub(a, b)
+def sub(x, y) -> Tensor:
+    return _sub(x, y)
 
 
-def mul(a, b) -> Tensor:
-    return _mul(a, b)
+def mul(x, y) -> Tensor:
+    return _mul(x, y)
 
 
-def div(a, b) -> Tensor:
-    return _div(a, b)
+def div(x, y) -> Tensor:
+    return _div(x, y)
 
 
-def mod(a, b) -> Tensor:
-    return _mod(a, b)
+def mod(x, y) -> Tensor:
+    return _mod(x, y)
 
 
-def pow(a, b) -> Tensor:
-    return _pow(a, b)
+def pow(x, y) -> Tensor:
+    return _pow(x, y)
 
 
-def outer(a, b) -> Tensor:
-    a = ensure_tensor(a)
-    b = ensure_tensor(b, a)
+def outer(x, y) -> Tensor:
+    a = ensure_tensor(x)
+    b = ensure_tensor(y, a)
     return _outer(a, b)
 
 
-def matmul(a, b) -> Tensor:
+def matmul(x, y) -> Tensor:
     """Matrix product with numpy semantics (1-D operands are promoted and squeezed back)."""
     from .view import squeeze, unsqueeze
 
-    a = ensure_tensor(a, b if isinstance(b, Tensor) else None)
-    b = ensure_tensor(b, a)
+    a = ensure_tensor(x, y if isinstance(y, Tensor) else None)
+    b = ensure_tensor(y, a)
     a1 = a.rank == 1
     b1 = b.rank == 1
     if a1:

@@ -545,8 +545,8 @@ def all_gather(x, axis: int | None = None, **kwargs):
     return _all_gather_op(x, dim=dim)
 
 
-def gather_all_axes(x):
-    x = ensure_tensor(x)
+def gather_all_axes(sharded_tensor):
+    x = ensure_tensor(sharded_tensor)
     if x._impl.sharding is None:
         return x
     return _gather_all_op(x)
@@ -571,8 +571,8 @@ def all_reduce(x, mesh: DeviceMesh | None = None, reduce_axes=None, reduce_op: s
     return _all_reduce_op(x, reduce_axes=reduce_axes, reduce_op=reduce_op)
 
 
-def pmean(x, axis_name: str | None = None):
-    x = ensure_tensor(x)
+def pmean(sharded_tensor, axis_name: str | None = None):
+    x = ensure_tensor(sharded_tensor)
     sp = x._impl.sharding
     if sp is None:
         return x
@@ -607,10 +607,10 @@ def reduce_scatter(x, axis: int, scatter_axes=None, **kwargs):
     return _reduce_scatter_op(x, dim=dim, scatter_axes=ordered)
 
 
-def all_to_all(x, split_axis: int, concat_axis: int, tiled: bool = True):
+def all_to_all(sharded_tensor, split_axis: int, concat_axis: int, tiled: bool = True):
     """Move the mesh axes that split ``concat_axis`` onto ``split_axis`` (Ulysses-style swap).
     Value-preserving in the global view; its VJP is the swap in the other direction."""
-    x = ensure_tensor(x)
+    x = ensure_tensor(sharded_tensor)
     sp = x._impl.sharding
     if sp is None:
         return x
@@ -625,8 +625,8 @@ def all_to_all(x, split_axis: int, concat_axis: int, tiled: bool = True):
     return reshard_to_spec(x, tgt)
 
 
-def ppermute(x, permutation=None, perm=None):
-    x = ensure_tensor(x)
+def ppermute(sharded_tensor, permutation=None, perm=None):
+    x = ensure_tensor(sharded_tensor)
     p = permutation if permutation is not None else perm
     if p is None:
         raise TypeError("ppermute needs a permutation [(src, dst), ...]")

@@ -56,13 +56,13 @@ class LogicalNotOp(UnaryOperation):
 _logical_not = LogicalNotOp()
 
 
-def equal(a, b) -> Tensor: return _equal(a, b)
-def not_equal(a, b) -> Tensor: return _not_equal(a, b)
-def greater(a, b) -> Tensor: return _greater(a, b)
-def greater_equal(a, b) -> Tensor: return _greater_equal(a, b)
-def less(a, b) -> Tensor: return _less(a, b)
-def less_equal(a, b) -> Tensor: return _less_equal(a, b)
-def logical_and(a, b) -> Tensor: return _logical_and(a, b)
-def logical_or(a, b) -> Tensor: return _logical_or(a, b)
-def logical_xor(a, b) -> Tensor: return _logical_xor(a, b)
-def logical_not(a) -> Tensor: return _logical_not(a)
+def equal(x, y) -> Tensor: return _equal(x, y)
+def not_equal(x, y) -> Tensor: return _not_equal(x, y)
+def greater(x, y) -> Tensor: return _greater(x, y)
+def greater_equal(x, y) -> Tensor: return _greater_equal(x, y)
+def less(x, y) -> Tensor: return _less(x, y)
+def less_equal(x, y) -> Tensor: return _less_equal(x, y)
+def logical_and(x, y) -> Tensor: return _logical_and(x, y)
+def logical_or(x, y) -> Tensor: return _logical_or(x, y)
+def logical_xor(x, y) -> Tensor: return _logical_xor(x, y)
+def logical_not(x) -> Tensor: return _logical_not(x)

@@ -179,21 +179,25 @@ _triu, _tril = TriuOp(), TrilOp()
 TriuOp._inst, TrilOp._inst = _triu, _tril
 
 
-def full(shape, value, *, dtype=None, device=None) -> Tensor:
+def full(shape, value, *, dtype=None, device=None, is_traced: bool = False) -> Tensor:
     dt, dev = defaults(dtype, device)
     if isinstance(value, Tensor):
         from .view import broadcast_to
 
-        return broadcast_to(value, _shape(shape))
-    return _full(shape=_shape(shape), value=value, dtype=dt, device=dev)
+        out = broadcast_to(value, _shape(shape))
+    else:
+        out = _full(shape=_shape(shape), value=value, dtype=dt, device=dev)
+    if is_traced:
+        out.is_traced = True
+    return out
 
 
-def zeros(shape, *, dtype=None, device=None) -> Tensor:
-    return full(shape, 0, dtype=dtype, device=device)
+def zeros(shape, *, dtype=None, device=None, is_traced: bool = False) -> Tensor:
+    return full(shape, 0, dtype=dtype, device=device, is_traced=is_traced)
 
 
-def ones(shape, *, dtype=None, device=None) -> Tensor:
-    return full(shape, 1, dtype=dtype, device=device)
+def ones(shape, *, dtype=None, device=None, is_traced: bool = False) -> Tensor:
+    return full(shape, 1, dtype=dtype, device=device, is_traced=is_traced)
 
 
 def arange(start=0, stop=None, step=1, *, dtype=None, device=None) -> Tensor:

@@ -117,8 +117,14 @@ class MinMaxOp(AxisOp):
 _split, _unbind, _minmax = SplitOp(), UnbindOp(), MinMaxOp()
 
 
-def split(x, num_or_sizes, axis: int = 0) -> tuple[Tensor, ...]:
-    """Split into equal parts (int) or the given sizes (list)."""
+def split(x, num_splits=None, axis: int = 0, *, num_or_sizes=None) -> tuple[Tensor, ...]:
+    """Split into ``num_splits`` equal parts (int, the reference's form, nabla/ops/multi_output.py:481)
+    or into the given sizes (list)."""
+    if num_splits is None:
+        num_splits = num_or_sizes
+    if num_splits is None:
+        raise TypeError("split() needs the number of parts or their sizes")
+    num_or_sizes = num_splits
     x = ensure_tensor(x)
     rank = len(x._impl.global_shape)
     n = x._impl.global_shape[axis + rank if axis < 0 else axis]

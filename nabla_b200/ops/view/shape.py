@@ -464,8 +464,8 @@ def slice_update(x, update, start, size) -> Tensor:
 slice_update_inplace = slice_update
 
 
-def concatenate(xs, axis: int = 0) -> Tensor:
-    xs = [ensure_tensor(x) for x in xs]
+def concatenate(tensors, axis: int = 0) -> Tensor:
+    xs = [ensure_tensor(x) for x in tensors]
     if len(xs) == 1:
         return xs[0]
     if any(x._impl.batch_dims for x in xs):
@@ -475,8 +475,8 @@ def concatenate(xs, axis: int = 0) -> Tensor:
     return _concat(xs, axis=int(axis))
 
 
-def stack(xs, axis: int = 0) -> Tensor:
-    xs = [ensure_tensor(x) for x in xs]
+def stack(tensors, axis: int = 0) -> Tensor:
+    xs = [ensure_tensor(x) for x in tensors]
     if any(x._impl.batch_dims for x in xs):
         from ..base import _align_batch_dims
 
@@ -484,7 +484,16 @@ def stack(xs, axis: int = 0) -> Tensor:
     return _stack(xs, axis=int(axis))
 
 
-def pad(x, paddings, value: float = 0.0) -> Tensor:
+def pad(x, paddings=None, mode: str = "constant", value: float = 0.0, **kwargs) -> Tensor:
+    """Pad every logical dimension by ``(before, after)`` with ``value`` (``pad_width`` is accepted as
+    an alias of ``paddings``; only ``mode="constant"`` exists, as in the reference,
+    nabla/ops/view/shape.py:1472-1495)."""
+    if paddings is None:
+        paddings = kwargs.get("pad_width")
+    if paddings is None:
+        raise ValueError("pad() requires paddings or pad_width")
+    if mode != "constant":
+        raise NotImplementedError(f"pad mode {mode!r} is not supported (only 'constant')")
     x = ensure_tensor(x)
     paddings = tuple((int(a), int(b)) for a, b in paddings)
     if all(a == 0 and b == 0 for a, b in paddings):

@@ -316,3 +316,29 @@ def test_small_members_the_reference_exposes_on_its_classes():
     from nabla_b200.ops.communication import all_reduce, shard
 
     assert callable(shard) and callable(all_reduce) and callable(nb.shard)
+
+
+def test_keyword_names_of_the_reference_signatures():
+    """Calls written with the reference's parameter names work unchanged."""
+    a, b = T(torch.tensor([[1.0, 2.0], [3.0, 4.0]])), T(torch.tensor([[2.0, 2.0], [2.0, 2.0]]))
+    close(nb.add(x=a, y=b), a.to_numpy() + 2.0)
+    close(nb.matmul(x=a, y=b), a.to_numpy() @ b.to_numpy())
+    close(nb.pow(x=a, y=b), a.to_numpy() ** 2)
+    assert nb.greater(x=a, y=b).to_numpy().tolist() == [[False, False], [True, True]]
+    assert nb.logical_not(x=nb.greater(x=a, y=b)).to_numpy().tolist() == [[True, True], [False, False]]
+    close(nb.concatenate(tensors=[a, b], axis=0), np.concatenate([a.to_numpy(), b.to_numpy()], 0))
+    close(nb.stack(tensors=[a, b], axis=0), np.stack([a.to_numpy(), b.to_numpy()], 0))
+    close(nb.pad(a, paddings=[(1, 0), (0, 1)], mode="constant", value=9.0), np.pad(a.to_numpy(), [(1, 0), (0, 1)], constant_values=9.0))
+    close(nb.pad(a, pad_width=[(0, 1), (0, 0)]), np.pad(a.to_numpy(), [(0, 1), (0, 0)]))
+    with pytest.raises(NotImplementedError):
+        nb.pad(a, paddings=[(1, 0), (0, 1)], mode="reflect")
+    p, q = nb.split(a, num_splits=2, axis=1)
+    close(p, a.to_numpy()[:, :1])
+    z = nb.zeros((2, 2), is_traced=True)
+    assert z.is_traced and nb.ones((2,), is_traced=False).to_numpy().tolist() == [1.0, 1.0]
+    mesh = nb.DeviceMesh("mk", (2,), ("x",))
+    xs = nb.shard(a, mesh, ("x", None))
+    close(nb.gather_all_axes(sharded_tensor=xs), a.to_numpy())
+    close(nb.pmean(sharded_tensor=xs, axis_name="x"), (a.to_numpy()[:1] + a.to_numpy()[1:]) / 2.0)
+    close(nb.ppermute(sharded_tensor=xs, permutation=[(0, 1), (1, 0)]), a.to_numpy()[::-1])
+    close(nb.all_to_all(sharded_tensor=xs, split_axis=1, concat_axis=0), a.to_numpy())
