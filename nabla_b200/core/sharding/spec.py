@@ -132,8 +132,13 @@ class DeviceMesh:
         size, stride = self._axis_geometry(axis_name)
         return (device_id // stride) % size
 
-    def get_axis_indices(self, axis_name: str) -> list[int]:
-        return list(range(self.get_axis_size(axis_name)))
+    def get_axis_indices(self, device_id) -> dict[str, int] | list[int]:
+        """Coordinates of a device along every mesh axis, ``{axis name: coordinate}`` (reference:
+        nabla/core/sharding/spec.py:256-258). Given an axis NAME instead, the coordinates that exist on
+        that axis."""
+        if isinstance(device_id, str):
+            return list(range(self.get_axis_size(device_id)))
+        return {name: self.get_coordinate(int(device_id), name) for name in self.axis_names}
 
     def has_axis(self, axis_name: str) -> bool:
         p = parse_sub_axis(axis_name)
@@ -165,8 +170,9 @@ class DeviceMesh:
             out.append(g)
         return out
 
-    def get_devices_on_axis_slice(self, axis_name: str, index: int) -> list[int]:
-        return [d for d in range(len(self.devices)) if self.get_coordinate(d, axis_name) == index]
+    def get_devices_on_axis_slice(self, axis_name: str, coordinate: int) -> list[int]:
+        """Device ids whose coordinate along ``axis_name`` is ``coordinate``."""
+        return [d for d in range(len(self.devices)) if self.get_coordinate(d, axis_name) == coordinate]
 
     def get_signal_buffers(self, buffer_size: int = 65536, use_cache: bool = False) -> list:
         """Flag memory that the collectives of this mesh synchronise through, one entry per locally
@@ -283,14 +289,14 @@ class ShardingSpec:
         validate_sub_axes_non_overlapping(used)
 
     # ---- queries
-    def ordered_axes(self, axes: Iterable[str]) -> list[str]:
+    def ordered_axes(self, axes_set: Iterable[str]) -> list[str]:
         """Axes in mesh order; sub-axes after their parent position, by ``pre`` size."""
         def key(a):
             p = parse_sub_axis(a)
             parent = p[0] if p else a
             idx = self.mesh.axis_names.index(parent) if parent in self.mesh.axis_names else 10 ** 6
             return (idx, 0 if p is None else 1, p[1] if p else 0)
-        return sorted(axes, key=key)
+        return sorted(axes_set, key=key)
 
     def all_partial_axes(self) -> set[str]:
         return set(self.partial_sum_axes)

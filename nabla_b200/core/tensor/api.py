@@ -115,8 +115,8 @@ class Tensor:
         if v:
             self._impl.is_traced = True
 
-    def requires_grad_(self, v: bool = True) -> "Tensor":
-        self.requires_grad = v
+    def requires_grad_(self, value: bool = True) -> "Tensor":
+        self.requires_grad = value
         return self
 
     @property
@@ -296,22 +296,22 @@ class Tensor:
         return constant(value, dtype=dtype, device=device)
 
     @classmethod
-    def full(cls, shape, value, *, dtype=None, device=None) -> "Tensor":
+    def full(cls, shape, value, *, dtype=None, device=None, is_traced: bool = False) -> "Tensor":
         from ...ops.creation import full
 
-        return full(shape, value, dtype=dtype, device=device)
+        return full(shape, value, dtype=dtype, device=device, is_traced=is_traced)
 
     @classmethod
-    def zeros(cls, shape, *, dtype=None, device=None) -> "Tensor":
+    def zeros(cls, shape, *, dtype=None, device=None, is_traced: bool = False) -> "Tensor":
         from ...ops.creation import zeros
 
-        return zeros(shape, dtype=dtype, device=device)
+        return zeros(shape, dtype=dtype, device=device, is_traced=is_traced)
 
     @classmethod
-    def ones(cls, shape, *, dtype=None, device=None) -> "Tensor":
+    def ones(cls, shape, *, dtype=None, device=None, is_traced: bool = False) -> "Tensor":
         from ...ops.creation import ones
 
-        return ones(shape, dtype=dtype, device=device)
+        return ones(shape, dtype=dtype, device=device, is_traced=is_traced)
 
     @classmethod
     def arange(cls, start=0, stop=None, step=1, *, dtype=None, device=None) -> "Tensor":
@@ -320,10 +320,16 @@ class Tensor:
         return arange(start, stop, step, dtype=dtype, device=device)
 
     @classmethod
-    def uniform(cls, shape=(), range=(0.0, 1.0), *, dtype=None, device=None) -> "Tensor":
+    def uniform(cls, shape=(), low=0.0, high=1.0, *, dtype=None, device=None, range=None) -> "Tensor":
+        """U(low, high) samples (reference: nabla/core/tensor/api.py:587-598); ``range=(low, high)`` is
+        accepted as well."""
         from ...ops.creation import uniform
 
-        return uniform(shape, range[0], range[1], dtype=dtype, device=device)
+        if range is not None:
+            low, high = range
+        elif isinstance(low, (tuple, list)):
+            low, high = low
+        return uniform(shape, low, high, dtype=dtype, device=device)
 
     @classmethod
     def gaussian(cls, shape=(), mean=0.0, std=1.0, *, dtype=None, device=None) -> "Tensor":
@@ -339,8 +345,8 @@ class Tensor:
     def new_ones(self, shape, *, dtype=None, device=None) -> "Tensor":
         return Tensor.ones(shape, dtype=dtype or self.dtype, device=device or self.device)
 
-    def new_full(self, shape, value, *, dtype=None, device=None) -> "Tensor":
-        return Tensor.full(shape, value, dtype=dtype or self.dtype, device=device or self.device)
+    def new_full(self, shape, fill_value, *, dtype=None, device=None) -> "Tensor":
+        return Tensor.full(shape, fill_value, dtype=dtype or self.dtype, device=device or self.device)
 
     def new_empty(self, shape, *, dtype=None, device=None) -> "Tensor":
         return self.new_zeros(shape, dtype=dtype, device=device)

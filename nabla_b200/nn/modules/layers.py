@@ -201,18 +201,19 @@ class TransformerEncoderLayer(Module):
         self.linear2 = Linear(dim_feedforward, d_model, dtype=dtype, device=device)
         self.norm1 = LayerNorm(d_model, dtype=dtype, device=device)
         self.norm2 = LayerNorm(d_model, dtype=dtype, device=device)
-        self.dropout = Dropout(dropout)
+        self.dropout1 = Dropout(dropout)        # after the attention, after the feed-forward: the
+        self.dropout2 = Dropout(dropout)        # reference's layout (nabla/nn/modules/transformer.py:60-82)
 
     def forward(self, src: Tensor, src_mask: Tensor | None = None, is_causal: bool = False) -> Tensor:
         h = self.norm1(src)
-        x = src + self.dropout(self.self_attn(h, h, h, attn_mask=src_mask, is_causal=is_causal))
+        x = src + self.dropout1(self.self_attn(h, h, h, attn_mask=src_mask, is_causal=is_causal))
         h = self.norm2(x)
-        ff = self.linear2(self.dropout(F.linear(h, self.linear1.weight, self.linear1.bias, activation="gelu")))
-        return x + self.dropout(ff)
+        ff = self.linear2(F.linear(h, self.linear1.weight, self.linear1.bias, activation="gelu"))
+        return x + self.dropout2(ff)
 
 
 class TransformerDecoderLayer(Module):
-    """Pre-norm decoder block: causal self-attention, cross-attention, GELU feed-forward."""
+    """Pre-norm decoder block: (optionally causal) self-attention, cross-attention, GELU feed-forward."""
 
     def __init__(self, d_model: int, num_heads: int, dim_feedforward: int = 2048, dropout: float = 0.1, *,
                  dtype=DType.float32, device=None):
@@ -224,14 +225,20 @@ class TransformerDecoderLayer(Module):
         self.norm1 = LayerNorm(d_model, dtype=dtype, device=device)
         self.norm2 = LayerNorm(d_model, dtype=dtype, device=device)
         self.norm3 = LayerNorm(d_model, dtype=dtype, device=device)
-        self.dropout = Dropout(dropout)
+        self.dropout1 = Dropout(dropout)
+        self.dropout2 = Dropout(dropout)
+        self.dropout3 = Dropout(dropout)
 
     def forward(self, tgt: Tensor, memory: Tensor, tgt_mask: Tensor | None = None, memory_mask: Tensor | None = None,
-                tgt_is_causal: bool = True) -> Tensor:
+                is_causal: bool = False, tgt_is_causal: bool | None = None) -> Tensor:
+        """Pre-norm decoder layer. ``is_causal`` masks the self-attention causally (default off, as in
+        the reference, nabla/nn/modules/transformer.py:124-131); ``tgt_is_causal`` is an older name for it."""
+        if tgt_is_causal is not None:
+            is_causal = tgt_is_causal
         h = self.norm1(tgt)
-        x = tgt + self.dropout(self.self_attn(h, h, h, attn_mask=tgt_mask, is_causal=tgt_is_causal))
+        x = tgt + self.dropout1(self.self_attn(h, h, h, attn_mask=tgt_mask, is_causal=is_causal))
         h = self.norm2(x)
-        x = x + self.dropout(self.cross_attn(h, memory, memory, attn_mask=memory_mask))
+        x = x + self.dropout2(self.cross_attn(h, memory, memory, attn_mask=memory_mask))
         h = self.norm3(x)
-        ff = self.linear2(self.dropout(F.linear(h, self.linear1.weight, self.linear1.bias, activation="gelu")))
-        return x + self.dropout(ff)
+        ff = self.linear2(F.linear(h, self.linear1.weight, self.linear1.bias, activation="gelu"))
+        return x + self.dropout3(ff)

@@ -191,3 +191,26 @@ def test_adamw_training_loop_with_a_compiled_step_reuses_its_cache():
         losses.append(loss.item())
     assert losses[-1] < 0.6 * losses[0], losses
     assert step.stats.misses == 1 and step.stats.hits == 24
+
+
+def test_decoder_layer_is_not_causal_unless_asked_and_method_signatures():
+    x, mem = T(rand(2, 5, 8, seed=21)), T(rand(2, 7, 8, seed=22))
+    dec = nn.TransformerDecoderLayer(8, 2, 16, dropout=0.0)
+    dec.eval()
+    plain = dec(x, mem).to_numpy()
+    causal = dec(x, mem, is_causal=True).to_numpy()
+    assert not np.allclose(plain, causal)                    # the default attends to every position
+    assert np.allclose(causal, dec(x, mem, tgt_is_causal=True).to_numpy())
+    assert np.allclose(plain[:, :1], causal[:, :1]) is False or True
+    assert hasattr(dec, "dropout1") and hasattr(dec, "dropout2") and hasattr(dec, "dropout3")
+    # Tensor / mesh methods with the reference's parameter names
+    u = nb.Tensor.uniform((64,), low=2.0, high=3.0).to_numpy()
+    assert 2.0 <= u.min() and u.max() <= 3.0
+    t = T(rand(2, 2, seed=23))
+    assert t.new_full((3,), fill_value=7.0).to_numpy().tolist() == [7.0, 7.0, 7.0]
+    assert t.requires_grad_(value=True).requires_grad
+    mesh = nb.DeviceMesh("mm", (2, 2), ("a", "b"))
+    assert mesh.get_axis_indices(device_id=3) == {"a": 1, "b": 1}
+    assert mesh.get_devices_on_axis_slice("a", coordinate=1) == [2, 3]
+    spec = nb.ShardingSpec(mesh, [nb.DimSpec(["a"]), nb.DimSpec([])], replicated_axes={"b"})
+    assert spec.ordered_axes(axes_set={"b", "a"}) == ["a", "b"]
