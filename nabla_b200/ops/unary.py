@@ -284,8 +284,10 @@ def gelu(x, approximate: str = "none") -> Tensor:
     return _gelu(ensure_tensor(x), approximate=approximate)
 
 
-def cast(x, dtype) -> Tensor:
+def cast(x, dtype=None) -> Tensor:
     x = ensure_tensor(x)
+    if dtype is None:          # the reference returns the tensor unchanged (nabla/ops/unary.py:792-798)
+        return x
     dtype = as_dtype(dtype)
     if x.dtype is dtype:
         return x

@@ -211,7 +211,9 @@ def unsqueeze(x, axis: int = 0) -> Tensor:
     return _unsqueeze(x, axis=int(axis))
 
 
-def squeeze(x, axis=None) -> Tensor:
+def squeeze(x, axis=0) -> Tensor:
+    """Remove the size-1 dimension at ``axis`` (default 0, as in the reference,
+    nabla/ops/view/axes.py:413); a tuple removes several, ``None`` every size-1 dimension."""
     x = ensure_tensor(x)
     rank = len(x._impl.global_shape)
     if axis is None:
@@ -246,11 +248,11 @@ def flip(x, axis) -> Tensor:
     return _flip(ensure_tensor(x), axis=axis)
 
 
-def unsqueeze_physical(x, axis: int) -> Tensor:
+def unsqueeze_physical(x, axis: int = 0) -> Tensor:
     return _unsqueeze_p(x, axis=int(axis))
 
 
-def squeeze_physical(x, axis: int) -> Tensor:
+def squeeze_physical(x, axis: int = 0) -> Tensor:
     return _squeeze_p(x, axis=int(axis))
 
 MoveAxisOp = MoveaxisOp      # spelling of the reference (nabla/ops/view/axes.py)

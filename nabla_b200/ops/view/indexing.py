@@ -141,8 +141,14 @@ class ScatterOp(Operation):
 _gather, _scatter = GatherOp(), ScatterOp()
 
 
-def gather(x, indices, axis: int = 0) -> Tensor:
+def gather(x, indices=None, axis: int = 0) -> Tensor:
+    """``numpy.take`` along ``axis``; without ``indices`` it collects the shards of a distributed
+    tensor into a replicated one (reference: nabla/ops/view/indexing.py:454-470)."""
     x = ensure_tensor(x)
+    if indices is None:
+        from ..communication import gather_all_axes
+
+        return gather_all_axes(x)
     indices = ensure_tensor(indices)
     return _gather(x, indices, axis=int(axis))
 

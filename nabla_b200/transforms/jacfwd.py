@@ -10,12 +10,25 @@ from .jvp import jvp
 from .utils import std_basis
 
 
-def jacfwd(fn: Callable, argnums: int | tuple[int, ...] = 0, has_aux: bool = False) -> Callable:
+def jacfwd(fn: Callable, argnums: int | tuple[int, ...] | list[int] | None = None, has_aux: bool = False) -> Callable:
     def wrapper(*args: Any):
         from ..ops.creation import zeros_like
         from ..ops.view import moveaxis, reshape, stack
 
-        argn = (argnums,) if isinstance(argnums, int) else tuple(argnums)
+        # argnums=None (the default) differentiates with respect to every argument; the result is a
+        # single Jacobian for one differentiated argument given as None / int, a tuple otherwise
+        # (reference: nabla/transforms/utils.py:52-67, jacrev.py:118-160)
+        if argnums is None:
+            argn = tuple(range(len(args)))
+        elif isinstance(argnums, int):
+            argn = (argnums,)
+        else:
+            argn = tuple(argnums)
+        argn = tuple(a if a >= 0 else len(args) + a for a in argn)
+        for a in argn:
+            if not 0 <= a < len(args):
+                raise ValueError(f"argnum {a} out of bounds for {len(args)} arguments")
+        single = isinstance(argnums, int) or (argnums is None and len(argn) == 1)
         jacs = []
         aux = None
         for which in argn:
@@ -44,7 +57,7 @@ def jacfwd(fn: Callable, argnums: int | tuple[int, ...] = 0, has_aux: bool = Fal
             j = stack(cols, axis=0)                     # (n, *out)
             j = moveaxis(j, 0, -1) if len(out_shape) else j   # (*out, n)
             jacs.append(reshape(j, out_shape + tuple(x._impl.global_shape)))
-        jac = jacs[0] if isinstance(argnums, int) else tuple(jacs)
+        jac = jacs[0] if single else tuple(jacs)
         return (jac, aux) if has_aux else jac
 
     wrapper.__name__ = f"jacfwd({getattr(fn, '__name__', 'fn')})"

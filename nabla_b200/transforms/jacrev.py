@@ -12,11 +12,24 @@ from .utils import std_basis
 from .vjp import vjp
 
 
-def jacrev(fn: Callable, argnums: int | tuple[int, ...] = 0, has_aux: bool = False) -> Callable:
+def jacrev(fn: Callable, argnums: int | tuple[int, ...] | list[int] | None = None, has_aux: bool = False) -> Callable:
     def wrapper(*args: Any):
         from ..ops.view import reshape, stack
 
-        argn = (argnums,) if isinstance(argnums, int) else tuple(argnums)
+        # argnums=None (the default) differentiates with respect to every argument; the result is a
+        # single Jacobian for one differentiated argument given as None / int, a tuple otherwise
+        # (reference: nabla/transforms/utils.py:52-67, jacrev.py:118-160)
+        if argnums is None:
+            argn = tuple(range(len(args)))
+        elif isinstance(argnums, int):
+            argn = (argnums,)
+        else:
+            argn = tuple(argnums)
+        argn = tuple(a if a >= 0 else len(args) + a for a in argn)
+        for a in argn:
+            if not 0 <= a < len(args):
+                raise ValueError(f"argnum {a} out of bounds for {len(args)} arguments")
+        single = isinstance(argnums, int) or (argnums is None and len(argn) == 1)
 
         def partial(*diff):
             full = list(args)
@@ -45,7 +58,7 @@ def jacrev(fn: Callable, argnums: int | tuple[int, ...] = 0, has_aux: bool = Fal
                 j = stack(col, axis=0)
                 per_leaf.append(reshape(j, out_shape + tuple(leaf._impl.global_shape)))
             jacs.append(pytree.tree_unflatten(td, per_leaf))
-        jac = jacs[0] if isinstance(argnums, int) else tuple(jacs)
+        jac = jacs[0] if single else tuple(jacs)
         return (jac, res[2]) if has_aux else jac
 
     wrapper.__name__ = f"jacrev({getattr(fn, '__name__', 'fn')})"

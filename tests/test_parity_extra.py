@@ -342,3 +342,27 @@ def test_keyword_names_of_the_reference_signatures():
     close(nb.pmean(sharded_tensor=xs, axis_name="x"), (a.to_numpy()[:1] + a.to_numpy()[1:]) / 2.0)
     close(nb.ppermute(sharded_tensor=xs, permutation=[(0, 1), (1, 0)]), a.to_numpy()[::-1])
     close(nb.all_to_all(sharded_tensor=xs, split_axis=1, concat_axis=0), a.to_numpy())
+
+
+def test_defaults_of_the_reference_signatures():
+    a = T(rand(1, 3, 1, seed=95))
+    assert tuple(int(d) for d in nb.squeeze(a).shape) == (3, 1)                 # default axis 0
+    assert tuple(int(d) for d in nb.squeeze(a, axis=None).shape) == (3,)
+    assert tuple(int(d) for d in a.squeeze().shape) == (3,)                      # the method squeezes everything
+    assert nb.cast(a) is a or nb.cast(a).dtype == a.dtype                        # no dtype: unchanged
+    mesh = nb.DeviceMesh("md", (2,), ("x",))
+    full = rand(4, 2, seed=96)
+    xs = nb.shard(T(full), mesh, ("x", None))
+    g = nb.gather(xs)                                                            # no indices: collect the shards
+    close(g, full)
+    assert g.sharding is None or g.sharding.is_fully_replicated()
+    # jacrev / jacfwd differentiate every argument unless told otherwise
+    f = lambda u, v: u * v * v
+    u, v = T(torch.tensor([1.0, 2.0])), T(torch.tensor([3.0, 4.0]))
+    for jac in (nb.jacrev, nb.jacfwd):
+        ju, jv = jac(f)(u, v)
+        close(ju, np.diag(v.to_numpy() ** 2), rtol=1e-5)
+        close(jv, np.diag(2 * u.to_numpy() * v.to_numpy()), rtol=1e-5)
+        close(jac(f, argnums=1)(u, v), np.diag(2 * u.to_numpy() * v.to_numpy()), rtol=1e-5)
+        close(jac(lambda w: w * w)(u), np.diag(2 * u.to_numpy()), rtol=1e-5)     # one argument: a single Jacobian
+        assert isinstance(jac(f, argnums=(0,))(u, v), tuple)
