@@ -33,11 +33,8 @@ def _run(fun, args, kwargs, argnums, has_aux, create_graph, realize, want_value)
         out, aux = out
     if not isinstance(out, Tensor):
         raise TypeError(f"grad: output must be a Tensor, got {type(out)}")
-    n = 1
-    for d in out._impl.global_shape:
-        n *= d
-    if n != 1:
-        raise ValueError(f"grad requires a scalar output, got shape {tuple(out._impl.global_shape)}")
+    # a non-scalar output is pulled back with a cotangent of ones (the gradient of its sum), exactly as
+    # the reference does (nabla/transforms/grad.py:60-62); its graph-tracing tutorial relies on it
     tr = Trace(diff_args, out)
     tr.compute()
     try:
