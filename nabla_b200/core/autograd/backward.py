@@ -78,6 +78,9 @@ class BackwardEngine:
         self.create_graph = create_graph
         self.cot: dict[int, Tensor] = {}
         self.keep: dict[int, TensorImpl] = {}
+        # the inputs of the trace always receive a gradient, whatever their flags say now: `trace()`
+        # restores `is_traced` on return, and the caller asks for them by naming them as inputs
+        self.wanted: set[int] = {id(i) for i in trace.input_impls}
         cots = [c for c in pytree.tree_leaves(cotangents)]
         outs = trace.output_impls
         if len(cots) != len(outs):
@@ -147,7 +150,7 @@ class BackwardEngine:
             if isinstance(p, Tensor):
                 if not isinstance(g, Tensor):
                     continue
-                if not (p._impl.is_traced or p._impl.requires_grad):
+                if not (p._impl.is_traced or p._impl.requires_grad or id(p._impl) in self.wanted):
                     continue
                 if not p.dtype.is_float():
                     continue

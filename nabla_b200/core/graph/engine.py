@@ -109,11 +109,19 @@ class Plan:
         self.num_nodes = num_nodes
 
 
+# evaluation counter of the current context (the reference's `_GRAPH_EPOCH`, engine.py:30): bumped
+# together with `ComputeGraph.epoch`, so code that only has the context can tell two evaluations apart
+_GRAPH_EPOCH: ContextVar[int] = ContextVar("nabla_graph_epoch", default=0)
+
+
 class ComputeGraph:
     """Owner of evaluation state: epoch counter and RNG (seed, counter)."""
 
     def __init__(self) -> None:
-        self.epoch = 0
+        # a fresh graph starts a new epoch of its context (the reference's constructor does the same,
+        # nabla/core/graph/engine.py), so `epoch` is positive from the start
+        self.epoch = _GRAPH_EPOCH.get() + 1
+        _GRAPH_EPOCH.set(self.epoch)
         self.seed = 0
         self.rng_counter = 0
         self.seed_epoch = 0          # bumped by set_seed: device-resident stream states re-read (seed, counter)
@@ -169,6 +177,7 @@ class ComputeGraph:
         t1 = time.perf_counter() if DEBUG else 0.0
         self._run(nodes, plan)
         self.epoch += 1
+        _GRAPH_EPOCH.set(_GRAPH_EPOCH.get() + 1)
         for t in targets:
             if not t.is_realized:
                 raise RuntimeError("evaluate() finished but a target tensor is still unrealized")
@@ -200,6 +209,7 @@ class ComputeGraph:
     def clear_all(self) -> None:
         clear_cache()
         self.epoch += 1
+        _GRAPH_EPOCH.set(_GRAPH_EPOCH.get() + 1)
 
 
 def store_outputs(node: OpNode, outs: list[list[torch.Tensor]]) -> None:
@@ -219,14 +229,24 @@ def run_node(node: OpNode) -> None:
     store_outputs(node, outs)
 
 
-_GRAPH_VAR: ContextVar[ComputeGraph | None] = ContextVar("nabla_graph", default=None)
-_CURRENT_GRAPH = _GRAPH_VAR          # the reference's name for the per-context graph variable (engine.py:922)
+_UNSET = object()
+# per-context graph. Three states: never set in this context (the process-wide graph is used), set
+# to a graph (`GRAPH.use`), or set to None, which asks for a fresh graph on the next access: a server
+# does that on a copied context so that each request handler gets its own (reference: engine.py:922).
+_GRAPH_VAR: ContextVar = ContextVar("nabla_graph", default=_UNSET)
+_CURRENT_GRAPH = _GRAPH_VAR          # the reference's name for the per-context graph variable
 _DEFAULT_GRAPH = ComputeGraph()
 
 
 def _get_current_graph() -> ComputeGraph:
     """The graph of the current context (reference: nabla/core/graph/engine.py, same name)."""
-    return _GRAPH_VAR.get() or _DEFAULT_GRAPH
+    g = _GRAPH_VAR.get()
+    if g is _UNSET:
+        return _DEFAULT_GRAPH
+    if g is None:
+        g = ComputeGraph()
+        _GRAPH_VAR.set(g)
+    return g
 
 
 class _GraphProxy:
@@ -234,7 +254,7 @@ class _GraphProxy:
     may install its own ``ComputeGraph``; otherwise the process-wide one is used."""
 
     def _get(self) -> ComputeGraph:
-        return _GRAPH_VAR.get() or _DEFAULT_GRAPH
+        return _get_current_graph()
 
     def __getattr__(self, name):
         return getattr(self._get(), name)

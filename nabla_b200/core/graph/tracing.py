@@ -152,6 +152,13 @@ class Trace:
     def __len__(self) -> int:
         return len(self.nodes)
 
+    def refresh_graph_values(self) -> None:
+        """Make the trace ready for a backward pass. The reference replays the ops here to rebuild
+        their values in the graph under construction (nabla/core/graph/tracing.py:189); evaluation
+        in this engine walks the recorded nodes on demand, so only the topology has to be known."""
+        if not self._computed:
+            self.compute()
+
     def __str__(self) -> str:
         if not self._computed:
             self.compute()

@@ -51,12 +51,55 @@ class OpShardingRule:
 class OpShardingRuleTemplate:
     """A rule written with ``...`` for leading batch dims, instantiated against shapes."""
 
-    def __init__(self, inputs: list[list], outputs: list[list]):
-        self.inputs = inputs      # each: list of tokens; token = str | tuple[str,...] | Ellipsis
-        self.outputs = outputs
+    def __init__(self, inputs: list, outputs: list):
+        # each operand: list of tokens; token = str | tuple[str,...] | Ellipsis. The reference's form,
+        # one ``{dim: [factor names]}`` dict per operand (nabla/core/sharding/propagation.py:107-111),
+        # is accepted too and turned into tokens in dim order.
+        self.inputs = [self._tokens(m) for m in inputs]
+        self.outputs = [self._tokens(m) for m in outputs]
 
     @staticmethod
-    def parse(notation: str) -> "OpShardingRuleTemplate":
+    def _tokens(m) -> list:
+        if not isinstance(m, dict):
+            return list(m)
+        out: list = []
+        for d in range(max(m) + 1 if m else 0):
+            fs = [str(f) for f in m.get(d, [f"_free{d}"])]
+            out.append(fs[0] if len(fs) == 1 else tuple(fs))
+        return out
+
+    @staticmethod
+    def _mapping(tokens: list) -> dict:
+        return {d: (list(t) if isinstance(t, tuple) else [t]) for d, t in enumerate(tokens) if t is not Ellipsis}
+
+    @property
+    def input_mappings(self) -> list[dict]:
+        """The operands' ``{dim: [factors]}`` dicts (dims counted without any ``...``)."""
+        return [self._mapping(t) for t in self.inputs]
+
+    @property
+    def output_mappings(self) -> list[dict]:
+        return [self._mapping(t) for t in self.outputs]
+
+    def to_einsum_notation(self) -> str:
+        def one(tokens):
+            return " ".join("..." if t is Ellipsis else ("(" + " ".join(t) + ")" if isinstance(t, tuple) else t)
+                            for t in tokens)
+        return ", ".join(one(t) for t in self.inputs) + " -> " + ", ".join(one(t) for t in self.outputs)
+
+    @staticmethod
+    def parse(notation: str, input_shapes: Sequence[Sequence[int]] | None = None) -> "OpShardingRuleTemplate":
+        """Template from einsum-like notation. With ``input_shapes`` every ``...`` is expanded at
+        once to the batch factors those shapes imply, as the reference's two-argument form does
+        (nabla/core/sharding/propagation.py:161-200)."""
+        tpl = OpShardingRuleTemplate._parse(notation)
+        if input_shapes is None:
+            return tpl
+        rule = tpl.instantiate(input_shapes)
+        return OpShardingRuleTemplate(rule.input_mappings, rule.output_mappings)
+
+    @staticmethod
+    def _parse(notation: str) -> "OpShardingRuleTemplate":
         def toks(s: str) -> list:
             out: list = []
             i, s = 0, s.strip()
@@ -83,11 +126,17 @@ class OpShardingRuleTemplate:
         sizes: dict[str, int] = {}
 
         max_batch = 0
+        batch_extent: dict[int, int] = {}        # right-aligned batch position -> largest extent over the operands
         for i, toks in enumerate(self.inputs):
             if Ellipsis in toks and i < len(input_shapes):
-                max_batch = max(max_batch, len(input_shapes[i]) - sum(1 for t in toks if t is not Ellipsis))
+                nb_ = len(input_shapes[i]) - sum(1 for t in toks if t is not Ellipsis)
+                max_batch = max(max_batch, nb_)
+                at = toks.index(Ellipsis)
+                for b in range(max(nb_, 0)):
+                    pos = nb_ - 1 - b
+                    batch_extent[pos] = max(batch_extent.get(pos, 1), int(input_shapes[i][at + b]))
 
-        def expand(tokens: list, shape: Sequence[int] | None) -> Mapping:
+        def expand(tokens: list, shape: Sequence[int] | None, operand: int = 0) -> Mapping:
             n_named = sum(1 for t in tokens if t is not Ellipsis)
             if shape is not None:
                 n_batch = max(0, len(shape) - n_named) if Ellipsis in tokens else 0
@@ -98,9 +147,15 @@ class OpShardingRuleTemplate:
             d = 0
             for t in tokens:
                 if t is Ellipsis:
-                    # batch factors are right-aligned across operands (numpy broadcasting)
+                    # batch factors are right-aligned across operands (numpy broadcasting); a size-1
+                    # dim that broadcasts against a larger one gets a factor of its own, so the
+                    # other operand's sharding of that position is never pushed onto it
                     for b in range(n_batch):
-                        mapping[d] = [f"_b{n_batch - 1 - b}"]
+                        pos = n_batch - 1 - b
+                        if shape is not None and int(shape[d]) == 1 and batch_extent.get(pos, 1) != 1:
+                            mapping[d] = [f"_bcast{operand}_{pos}"]
+                        else:
+                            mapping[d] = [f"_b{pos}"]
                         d += 1
                 else:
                     fs = list(t) if isinstance(t, tuple) else [t]
@@ -110,7 +165,7 @@ class OpShardingRuleTemplate:
                     d += 1
             return mapping
 
-        ins = [expand(t, input_shapes[i] if i < len(input_shapes) else None) for i, t in enumerate(self.inputs)]
+        ins = [expand(t, input_shapes[i] if i < len(input_shapes) else None, i) for i, t in enumerate(self.inputs)]
         outs = [expand(t, output_shapes[i] if output_shapes and i < len(output_shapes) else None)
                 for i, t in enumerate(self.outputs)]
         return OpShardingRule(ins, outs, sizes)

@@ -280,7 +280,8 @@ class Tensor:
         if isinstance(array, torch.Tensor):
             t = array
         elif isinstance(array, np.ndarray):
-            t = torch.from_numpy(np.ascontiguousarray(array))
+            # np.ascontiguousarray promotes a 0-d array to 1-d: restore the shape
+            t = torch.from_numpy(np.ascontiguousarray(array)).reshape(array.shape)
         else:
             t = torch.from_dlpack(array)
         return cls(buffers=[t])

@@ -96,7 +96,7 @@ def _like(template: Tensor, arr: np.ndarray) -> Tensor:
     """Host array -> tensor with the template's dtype, device, sharding and requires_grad."""
     import torch
 
-    t = torch.from_numpy(np.ascontiguousarray(arr)).to(device=template.device.to_torch(), dtype=template.dtype.to_torch())
+    t = torch.from_numpy(np.ascontiguousarray(arr)).reshape(arr.shape).to(device=template.device.to_torch(), dtype=template.dtype.to_torch())
     out = Tensor(buffers=[t])
     sp = template._impl.sharding
     if sp is not None:

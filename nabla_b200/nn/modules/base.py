@@ -183,18 +183,22 @@ class Module:
             out[k] = v
         return out
 
-    def load_state_dict(self, state_dict) -> None:
+    def load_state_dict(self, state_dict, strict: bool = False) -> None:
+        """Set the parameters and buffers named in ``state_dict``. As in the reference
+        (nabla/nn/modules/base.py:305-311) a partial dict is fine: entries that are not given keep
+        their value. ``strict=True`` also wants every own entry to be present and no unknown names."""
         own = self.state_dict()
-        missing = [k for k in own if k not in state_dict]
-        if missing:
-            raise KeyError(f"missing keys in state_dict: {missing}")
+        if strict:
+            missing = [k for k in own if k not in state_dict]
+            if missing:
+                raise KeyError(f"missing keys in state_dict: {missing}")
         for name, value in state_dict.items():
-            if name not in own:
+            if strict and name not in own:
                 raise KeyError(f"unexpected key in state_dict: {name}")
             mod: Module = self
             parts = name.split(".")
             for p in parts[:-1]:
-                mod = mod._modules[p]
+                mod = mod._modules[p] if p in mod._modules else getattr(mod, p)
             was_param = parts[-1] in mod._parameters
             if was_param:
                 value.requires_grad = True

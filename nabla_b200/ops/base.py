@@ -121,14 +121,15 @@ class Operation:
                 n *= int(d)
         return float(n)
 
-    def memory_cost(self, input_shapes, output_shapes, dtype_bytes: int = 4) -> float:
+    def memory_cost(self, input_shapes, output_shapes, dtype_bytes: int = 4) -> int:
+        """Bytes of the op's outputs (reference: nabla/ops/base.py:226-239)."""
         tot = 0
-        for s in list(input_shapes) + list(output_shapes):
+        for s in output_shapes:
             n = 1
             for d in s:
                 n *= int(d)
-            tot += n
-        return float(tot * dtype_bytes)
+            tot += n * int(dtype_bytes)
+        return tot
 
     def infer_output_rank(self, input_shapes, **kwargs) -> int:
         return len(input_shapes[0]) if input_shapes else 0

@@ -238,11 +238,12 @@ def matmul(x, y) -> Tensor:
         a = unsqueeze(a, axis=0)
     if b1:
         b = unsqueeze(b, axis=-1)
-    if a._impl.batch_dims != b._impl.batch_dims:
-        from .base import _align_batch_dims
-
-        # keep matrix dims last: only align batch dims (logical ranks may differ by broadcasting)
-        bd = max(a._impl.batch_dims, b._impl.batch_dims)
+    bd = max(a._impl.batch_dims, b._impl.batch_dims)
+    if bd:
+        # under vmap the physical arrays carry the mapped dims in front, so numpy's right-aligned
+        # broadcasting of the LOGICAL batch dims has to be made explicit: first give both operands the
+        # same mapped dims, then pad the shorter logical shape with size-1 dims just behind them
+        from .view.axes import unsqueeze_physical
         from .view.batch import broadcast_batch_dims
 
         ref = a if a._impl.batch_dims == bd else b
@@ -251,8 +252,6 @@ def matmul(x, y) -> Tensor:
         if b._impl.batch_dims < bd:
             b = broadcast_batch_dims(b, ref._impl.batch_shape)
         ra, rb = len(a._impl.global_shape), len(b._impl.global_shape)
-        from .view.axes import unsqueeze_physical
-
         while ra < rb:
             a = unsqueeze_physical(a, axis=bd)
             ra += 1

@@ -103,6 +103,8 @@ def _describe(t: torch.Tensor) -> NbTensor:
 
 
 def _out_spec(o) -> tuple[tuple[int, ...], torch.dtype]:
+    if callable(o) and isinstance(getattr(o, "__self__", None), torch.Tensor):
+        o = o.__self__              # `x.type` of an input, the reference's way to say "like x"
     if isinstance(o, torch.Tensor):
         return tuple(o.shape), o.dtype
     shape, dt = o

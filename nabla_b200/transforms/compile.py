@@ -225,6 +225,12 @@ class CompiledFunction:
         return text
 
     # ---- keys
+    def _extract_sharding_key(self, sharding) -> Any:
+        """Hashable identity of a sharding for the cache key: mesh, per-dimension axes, and the
+        explicitly replicated and partial-sum axes, so a replicated input and one with a pending
+        reduction never share a plan (reference: nabla/transforms/compile.py:270-274)."""
+        return None if sharding is None else sharding.effect_signature()
+
     def _signature(self, t: Tensor, arg_idx: int | None) -> tuple[tuple, tuple]:
         im = t._impl
         shape = tuple(im._shape)

@@ -40,7 +40,7 @@ def test_graph_proxy_delegates_to_the_current_graph():
 
 
 def test_default_graph_is_shared_until_a_context_installs_its_own():
-    assert engine._GRAPH_VAR.get() is None or isinstance(engine._GRAPH_VAR.get(), ComputeGraph)
+    assert engine._get_current_graph() is engine._DEFAULT_GRAPH or isinstance(engine._GRAPH_VAR.get(), ComputeGraph)
     g = ComputeGraph()
     tok = GRAPH.use(g)
     try:
@@ -221,3 +221,20 @@ def test_default_dtype_and_device_are_per_context():
     [t.start() for t in ts]
     [t.join() for t in ts]
     assert seen["a"] is nb.DType.float32 and seen["b"] is nb.DType.float64
+
+
+def test_a_context_that_resets_the_graph_variable_gets_a_fresh_graph_lazily():
+    """Reference behaviour (tests/unit/test_contextvar_safety.py, `_gather_isolated`): a copied
+    context that sets the variable to None gets its own graph on first use, with a positive epoch."""
+    import contextvars
+
+    def inside():
+        g = engine._get_current_graph()
+        assert g is engine._get_current_graph()      # created once, then kept
+        return g
+
+    ctx = contextvars.copy_context()
+    ctx.run(engine._CURRENT_GRAPH.set, None)
+    g = ctx.run(inside)
+    assert isinstance(g, ComputeGraph) and g is not engine._DEFAULT_GRAPH and g.epoch > 0
+    assert isinstance(engine._GRAPH_EPOCH, ContextVar)

@@ -97,7 +97,7 @@ def test_modules_pytree_state_dict_and_repr():
     close(m3(x), m(x).to_numpy())
     assert "Linear(in_features=4, out_features=8, bias=True)" in repr(m)
     with pytest.raises(KeyError):
-        m3.load_state_dict({"0.weight": sd["0.weight"]})
+        m3.load_state_dict({"0.weight": sd["0.weight"]}, strict=True)
 
 
 def test_linear_and_mha_match_torch():

@@ -512,3 +512,83 @@ def test_cond_and_scan_conventions():
     rev_carry, rev = nb.scan(lambda c, v: (c + v, c), T(np.zeros(6, np.float32)), T(a), reverse=True)
     close(rev_carry, a.sum(0), rtol=1e-5, atol=1e-5)
     close(rev[0], a[1:].sum(0), rtol=1e-5, atol=1e-5)
+
+
+# ---------------------------------------------------------------- behaviours the reference's older suites rely on
+def test_backward_on_trace_gives_gradients_for_the_trace_inputs_after_trace_returned():
+    """`trace()` restores `is_traced` when it returns; the inputs named to it still get gradients
+    (reference: tests/depr/test_dp_vs_mp_vjp.py, test_sharded_comm_vjp.py)."""
+    from nabla_b200.core.autograd import backward_on_trace
+    from nabla_b200.core.graph.tracing import trace
+
+    mesh = _mesh(2, "tp")
+    xn, wn = rand(4, 8, seed=90), rand(8, 4, seed=91)
+    x = nb.shard(T(xn), mesh, ("tp", None))
+    w = nb.shard(T(wn), mesh, (None, None))
+    t = trace(lambda a, b: nb.reduce_sum(nb.matmul(a, b), axis=0), x, w)
+    assert not x.is_traced
+    g = backward_on_trace(t, nb.full_like(t.outputs, 1.0))
+    close(g[x], wn.sum(1).expand(4, 8), rtol=1e-5, atol=1e-5)
+    close(g[w], xn.sum(0)[:, None].expand(8, 4), rtol=1e-5, atol=1e-5)
+
+
+def test_from_dlpack_keeps_a_zero_dim_array_zero_dim():
+    t = nb.Tensor.from_dlpack(np.array(1.5, dtype=np.float32))
+    assert tuple(int(d) for d in t.shape) == ()
+    assert t.item() == 1.5
+
+
+def test_vmapped_matmul_broadcasts_logical_batch_dims_of_unequal_rank():
+    """Per-stage `x @ W` with x (stages, batch, s, d) and W (stages, d, n): under vmap the mapped dim
+    is in front of both, and W has to broadcast over x's batch dim, sharded or not
+    (reference: tests/depr/test_pp_transformer.py)."""
+    xn, wn = rand(2, 4, 6, 8, seed=92), rand(2, 8, 5, seed=93)
+    ref = torch.einsum("sbik,skn->sbin", xn, wn)
+    f = nb.vmap(lambda a, b: a @ b)
+    close(f(T(xn), T(wn)), ref, rtol=1e-5, atol=1e-5)
+    ga, gb = nb.grad(lambda a, b: nb.reduce_sum(f(a, b)), argnums=(0, 1))(T(xn), T(wn))
+    close(ga, wn.sum(-1)[:, None, None, :].expand(2, 4, 6, 8), rtol=1e-5, atol=1e-5)
+    close(gb, xn.sum((1, 2))[:, :, None].expand(2, 8, 5), rtol=1e-4, atol=1e-4)
+    mesh = nb.DeviceMesh("pp_dp", (2, 2), ("data", "stage"))
+    xs = nb.shard(T(xn), mesh, ("stage", "data", None, None))
+    ws = nb.shard(T(wn), mesh, ("stage", None, None))
+    y = f(xs, ws)
+    assert [d.axes for d in y.sharding.dim_specs][:2] == [["stage"], ["data"]]
+    close(y, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_sharding_rule_template_takes_the_dict_form_and_shapes():
+    from nabla_b200.core.sharding.propagation import OpShardingRuleTemplate
+
+    m = {0: ["d0"], 1: ["d1"]}
+    rule = OpShardingRuleTemplate([m], [m]).instantiate([(4, 8)], [(4, 8)])
+    assert rule.input_mappings == [m] and rule.output_mappings == [m]
+    assert rule.factor_sizes == {"d0": 4, "d1": 8}
+    tpl = OpShardingRuleTemplate.parse("... m k, ... k n -> ... m n", [(3, 4, 5), (5, 6)])
+    assert len(tpl.input_mappings[0]) == 3 and len(tpl.input_mappings[1]) == 2 and len(tpl.output_mappings[0]) == 3
+    assert tpl.input_mappings[0][0] == tpl.output_mappings[0][0]
+    # a size-1 batch dim that broadcasts never shares the other operand's factor
+    r = OpShardingRuleTemplate.parse("... m k, ... k n -> ... m n").instantiate([(7, 4, 5), (1, 5, 6)])
+    assert r.input_mappings[0][0] != r.input_mappings[1][0]
+    assert r.input_mappings[0][0] == r.output_mappings[0][0]
+
+
+def test_memory_cost_counts_output_bytes():
+    from nabla_b200.ops.binary import MatmulOp
+    from nabla_b200.ops.reduction import ReduceSumOp
+
+    assert MatmulOp().memory_cost([(8, 32, 64), (8, 64, 128)], [(8, 32, 128)]) == 8 * 32 * 128 * 4
+    assert ReduceSumOp().memory_cost([(32, 64, 128)], [(32, 128)], dtype_bytes=2) == 32 * 128 * 2
+
+
+def test_compile_cache_key_separates_replicated_partial_and_explicitly_replicated():
+    from nabla_b200.core.sharding.spec import DimSpec, ShardingSpec
+    from nabla_b200.transforms.compile import CompiledFunction
+
+    mesh = _mesh(2, "tp")
+    dims = [DimSpec([]), DimSpec([])]
+    c = CompiledFunction(lambda x: x)
+    keys = {c._extract_sharding_key(ShardingSpec(mesh, dims)),
+            c._extract_sharding_key(ShardingSpec(mesh, dims, partial_sum_axes={"tp"})),
+            c._extract_sharding_key(ShardingSpec(mesh, dims, replicated_axes={"tp"}))}
+    assert len(keys) == 3 and c._extract_sharding_key(None) is None
