@@ -99,10 +99,10 @@ class Tensor:
         n = self._impl.output_refs
         return dict(n.op_kwargs) if n is not None else {}
 
-    def trace(self):
-        from ..graph.tracing import Trace
-
-        return Trace.from_outputs([self])
+    def trace(self) -> "Tensor":
+        """Mark this tensor as traced for autograd and return it (reference: api.py:247-250)."""
+        self._impl.is_traced = True
+        return self
 
     # ------------------------------------------------------------ autograd flags
     @property
@@ -199,11 +199,14 @@ class Tensor:
 
     @property
     def global_shape(self) -> Shape:
-        return Shape(self._impl.global_shape)
+        """Global shape INCLUDING the leading vmap dims, as in the reference
+        (nabla/core/tensor/api.py:416-418); ``shape`` is the logical one."""
+        return Shape(self._impl.physical_global_shape)
 
     @property
     def local_shape(self) -> Shape:
-        return Shape(self._impl.logical_local_shape(0))
+        """Shape of shard 0 including the leading vmap dims (reference: api.py:411-413)."""
+        return Shape(self._impl.physical_local_shape(0))
 
     @property
     def batch_shape(self) -> Shape:
@@ -593,7 +596,7 @@ class Tensor:
         return res
 
     def __setitem__(self, key, value) -> None:
-        updated = _apply_indexed_update(self, key, value, mode="set")
+        updated = _apply_indexed_update(self, key, value, mode="set", inplace=True)
         self._impl = updated._impl
 
     @property
@@ -686,7 +689,7 @@ def _ensure_like(value, like: Tensor) -> Tensor:
     return constant(value, dtype=like.dtype, device=like.device)
 
 
-def _apply_indexed_update(x: Tensor, key, value, *, mode: str) -> Tensor:
+def _apply_indexed_update(x: Tensor, key, value, *, mode: str, inplace: bool = False) -> Tensor:
     from ...ops import view
 
     if isinstance(key, Tensor):
@@ -712,7 +715,7 @@ def _apply_indexed_update(x: Tensor, key, value, *, mode: str) -> Tensor:
         updates = view.slice_tensor(x, start=tuple(start), size=tuple(size)) + updates
     elif mode != "set":
         raise ValueError(f"Unsupported indexed update mode: {mode}")
-    return view.slice_update(x, updates, start=tuple(start), size=tuple(size))
+    return view.slice_update(x, updates, start=tuple(start), size=tuple(size), use_buffer_ops=inplace)
 
 
 def realize_all(*tensors: Tensor) -> tuple[Tensor, ...]:

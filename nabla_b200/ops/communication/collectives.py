@@ -426,7 +426,28 @@ class RelabelOp(_LayoutOp):
         return _relabel_op(tangents[0], **kwargs)
 
 
+class FanOutOp(_LayoutOp):
+    """Identity on the buffers whose cotangent is summed over the ``copies`` devices that received
+    the value: the derivative of handing one rank's value to every device of a mesh, each copy
+    counted separately (reference: nabla/ops/communication/broadcast.py:89-96, "AllReduce(sum) back
+    to root")."""
+
+    def out_spec(self, x, mesh, kwargs):
+        return x._impl.sharding.clone()
+
+    def execute(self, node):
+        mesh = self._mesh(node)
+        return [self._shards(node.input_impls()[0], mesh)]
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        return (cot * float(kwargs["copies"]),)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return _fan_out_op(tangents[0], **kwargs)
+
+
 _relabel_op = RelabelOp()
+_fan_out_op = FanOutOp()
 
 
 def relabel_spec(x, spec: ShardingSpec):
@@ -523,8 +544,12 @@ def broadcast(x, mesh: DeviceMesh | None = None, root: int = 0):
 
 
 def distributed_broadcast(x, mesh: DeviceMesh | None = None):
-    """Replicate onto every device of the mesh (data of device 0 when unsharded)."""
-    return broadcast(x, mesh)
+    """Hand the root's value to every device of the mesh. Unlike `broadcast` (a change of layout in
+    the global view, gradient 1), every device's copy counts in the backward pass: the gradient is
+    the sum over the ``len(mesh.devices)`` copies, as in the reference
+    (nabla/ops/communication/broadcast.py:89-96; tests/unit/test_communication_rigorous.py:104-123)."""
+    y = broadcast(x, mesh)
+    return _fan_out_op(y, copies=len(y._impl.sharding.mesh.devices))
 
 
 def all_gather(x, axis: int | None = None, **kwargs):
@@ -620,6 +645,12 @@ def all_to_all(sharded_tensor, split_axis: int, concat_axis: int, tiled: bool = 
     c = (concat_axis + rank if concat_axis < 0 else concat_axis) + bd
     tgt = sp.clone()
     moved = list(tgt.dim_specs[c].axes) or list(sp.mesh.axis_names[:1])
+    n = 1
+    for a in moved:
+        n *= sp.mesh.get_axis_size(a)
+    if int(x._impl._shape[s]) % n:
+        raise ValueError(f"all_to_all: split axis {split_axis} of size {int(x._impl._shape[s])} is not divisible "
+                         f"by the {n} devices it is split over")
     tgt.dim_specs[c] = DimSpec([])
     tgt.dim_specs[s] = DimSpec(list(tgt.dim_specs[s].axes) + [a for a in moved if a not in tgt.dim_specs[s].axes])
     return reshard_to_spec(x, tgt)

@@ -290,13 +290,35 @@ def _conv_wgrad(x, dy, *, w_shape, stride, padding):
     return _conv_wgrad_op(x, dy, w_shape=tuple(w_shape), stride=tuple(stride), padding=tuple(padding))
 
 
+def _require_positive(value, name: str) -> None:
+    if any(int(v) <= 0 for v in value):
+        raise ValueError(f"{name} values must be > 0, got {tuple(value)}")
+
+
+def _require_nonnegative(value, name: str) -> None:
+    if any(int(v) < 0 for v in value):
+        raise ValueError(f"{name} values must be >= 0, got {tuple(value)}")
+
+
 def _check(x, w, dilation, groups, name):
     if len(x.shape) < 4 or len(w.shape) != 4:
         raise ValueError(f"{name} expects rank-4 tensors, got x={tuple(x.shape)}, filter={tuple(w.shape)}")
+    _require_positive(_two(dilation, "dilation"), "dilation")
+    if int(groups) <= 0:
+        raise ValueError(f"groups must be > 0, got {int(groups)}")
     if _two(dilation, "dilation") != (1, 1):
         raise ValueError(f"{name} currently supports only dilation=(1, 1)")
     if int(groups) != 1:
-        raise ValueError(f"{name} currently supports only groups=1")
+        raise ValueError(f"{name} grouped mode (groups={int(groups)}) is not supported: only groups=1")
+
+
+def _check_bias(bias, c_out: int, name: str):
+    bias = ensure_tensor(bias)
+    if len(bias.shape) != 1:
+        raise ValueError(f"{name} bias must be rank-1 [C_out], got shape={tuple(int(d) for d in bias.shape)}")
+    if int(bias.shape[0]) != c_out:
+        raise ValueError(f"{name} bias size ({int(bias.shape[0])}) must match filter C_out ({c_out})")
+    return bias
 
 
 def conv2d(x, filter, *, stride=(1, 1), dilation=(1, 1), padding=(0, 0, 0, 0), groups: int = 1, bias=None,
@@ -306,14 +328,12 @@ def conv2d(x, filter, *, stride=(1, 1), dilation=(1, 1), padding=(0, 0, 0, 0), g
         raise ValueError("conv2d supports only the default NHWC / RSCF layouts")
     _check(x, filter, dilation, groups, "conv2d")
     st, pd = _two(stride, "stride"), _pad4(padding)
-    if min(st) <= 0 or min(pd) < 0:
-        raise ValueError("stride must be positive and padding non-negative")
+    _require_positive(st, "stride")
+    _require_nonnegative(pd, "padding")
     if int(x.shape[-1]) != int(filter.shape[2]):
         raise ValueError(f"Input channels ({int(x.shape[-1])}) must match filter channels*groups ({int(filter.shape[2])})")
     if bias is not None:
-        bias = ensure_tensor(bias)
-        if len(bias.shape) != 1 or int(bias.shape[0]) != int(filter.shape[3]):
-            raise ValueError("conv2d bias must be rank-1 [C_out]")
+        bias = _check_bias(bias, int(filter.shape[3]), "conv2d")
         return _conv2d(x, filter, bias, stride=st, padding=pd)
     return _conv2d(x, filter, stride=st, padding=pd)
 
@@ -327,8 +347,10 @@ def conv2d_transpose(x, filter, *, stride=(1, 1), dilation=(1, 1), padding=(0, 0
     if _two(output_paddings, "output_paddings") != (0, 0):
         raise ValueError("conv2d_transpose currently supports only output_paddings=(0, 0)")
     st, pd = _two(stride, "stride"), _pad4(padding)
+    _require_positive(st, "stride")
+    _require_nonnegative(pd, "padding")
     if int(x.shape[-1]) != int(filter.shape[3]):
-        raise ValueError(f"Input channels ({int(x.shape[-1])}) must match filter C_in ({int(filter.shape[3])})")
+        raise ValueError(f"Input channels ({int(x.shape[-1])}) must match filter input channels ({int(filter.shape[3])})")
     if bias is not None:
-        return _conv2d_transpose(x, filter, ensure_tensor(bias), stride=st, padding=pd)
+        return _conv2d_transpose(x, filter, _check_bias(bias, int(filter.shape[2]), "conv2d_transpose"), stride=st, padding=pd)
     return _conv2d_transpose(x, filter, stride=st, padding=pd)

@@ -1,5 +1,5 @@
 """Ops with several outputs (reference: nabla/ops/multi_output.py:52-546): split (tuple),
-chunk (list, uneven tail), unbind (tuple), minmax (dict). The split axis must be whole on
+chunk (list, sizes differ by at most one), unbind (tuple), minmax (dict). The split axis must be whole on
 every shard, so a sharded split axis is gathered first."""
 from __future__ import annotations
 
@@ -140,22 +140,35 @@ def split(x, num_splits=None, axis: int = 0, *, num_or_sizes=None) -> tuple[Tens
 
 
 def chunk(x, chunks: int, axis: int = 0) -> list[Tensor]:
-    """Like torch.chunk: ceil-div pieces, the last may be smaller."""
+    """``chunks`` pieces whose sizes differ by at most one, the larger ones first (numpy's
+    ``array_split``; reference: nabla/ops/multi_output.py:219-226). Empty pieces are dropped, so an
+    axis shorter than ``chunks`` gives one piece per element."""
     x = ensure_tensor(x)
     rank = len(x._impl.global_shape)
     n = x._impl.global_shape[axis + rank if axis < 0 else axis]
-    size = -(-n // chunks)
-    sizes = []
-    left = n
-    while left > 0:
-        sizes.append(min(size, left))
-        left -= sizes[-1]
-    return list(_split(x, sizes=tuple(sizes), axis=int(axis)))
+    div, rem = divmod(int(n), int(chunks))
+    sizes = [div + 1 if i < rem else div for i in range(int(chunks))]
+    return list(_split(x, sizes=tuple(s for s in sizes if s > 0), axis=int(axis)))
 
 
 def unbind(x, axis: int = 0) -> tuple[Tensor, ...]:
     return tuple(_unbind(ensure_tensor(x), axis=int(axis)))
 
 
-def minmax(x, axis: int = -1, keepdims: bool = False) -> dict[str, Tensor]:
-    return _minmax(ensure_tensor(x), axis=int(axis), keepdims=keepdims)
+def minmax(x, axis: int | None = None, keepdims: bool = False) -> dict[str, Tensor]:
+    """``{"min": ..., "max": ...}``. Without ``axis`` both are scalars over the whole tensor (the
+    reference's form, nabla/ops/multi_output.py:528-538); with ``axis`` they are taken along it."""
+    x = ensure_tensor(x)
+    if axis is not None:
+        return _minmax(x, axis=int(axis), keepdims=keepdims)
+    rank = len(x._impl.global_shape)
+    if rank == 0:
+        return {"min": x, "max": x}
+    out = _minmax(x, axis=rank - 1, keepdims=keepdims)
+    lo, hi = out["min"], out["max"]
+    from .reduction import reduce_max, reduce_min
+
+    for ax in reversed(range(rank - 1)):
+        lo = reduce_min(lo, axis=ax, keepdims=keepdims)
+        hi = reduce_max(hi, axis=ax, keepdims=keepdims)
+    return {"min": lo, "max": hi}

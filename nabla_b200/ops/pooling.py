@@ -10,7 +10,7 @@ import torch.nn.functional as TF
 from ..core.sharding.propagation import OpShardingRule
 from ..core.tensor.api import Tensor
 from .base import Operation, ensure_tensor
-from .convolution import _fold, _pad4, _two
+from .convolution import _fold, _pad4, _require_nonnegative, _require_positive, _two
 
 
 def _native_ok(x):
@@ -137,13 +137,14 @@ def _call(x, kernel_size, stride, padding, dilation, mode):
     x = ensure_tensor(x)
     if len(x.shape) < 4:
         raise ValueError(f"pool2d expects an NHWC tensor, got shape {tuple(x.shape)}")
-    if _two(dilation, "dilation") != (1, 1):
-        raise ValueError("pool2d currently supports only dilation=(1, 1)")
     k = _two(kernel_size, "kernel_size")
     s = _two(stride if stride is not None else k, "stride")
     p = _pad4(padding)
-    if min(k) <= 0 or min(s) <= 0 or min(p) < 0:
-        raise ValueError("kernel_size and stride must be positive, padding non-negative")
+    _require_positive(k, "kernel_size")
+    _require_positive(s, "stride")
+    _require_nonnegative(p, "padding")
+    if _two(dilation, "dilation") != (1, 1):
+        raise ValueError("pool2d currently supports only dilation=(1, 1)")
     H, W = int(x.shape[-3]), int(x.shape[-2])
     oh = (H + p[0] + p[1] - k[0]) // s[0] + 1
     ow = (W + p[2] + p[3] - k[1]) // s[1] + 1

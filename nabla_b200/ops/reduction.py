@@ -286,17 +286,31 @@ class _PhysMixin:
         return batch_dims
 
 
+def _restore_reduced_axis(cot, x, outputs, kwargs):
+    """Give the cotangent of a physical reduction its reduced axis back (size 1). When that axis was
+    one of ``x``'s vmap dims, it comes back as a vmap dim, so the result lines up with ``x``."""
+    from .view.axes import unsqueeze_physical
+    from .view.batch import incr_batch_dims
+
+    if kwargs.get("keepdims", False):
+        return cot
+    lead = cot._impl.batch_dims - outputs._impl.batch_dims      # vmap dims that only the cotangent has
+    cot = unsqueeze_physical(cot, axis=kwargs["axis"] + max(lead, 0))
+    if kwargs["axis"] < x._impl.batch_dims and cot._impl.batch_dims - max(lead, 0) < x._impl.batch_dims:
+        cot = incr_batch_dims(cot)
+    return cot
+
+
 class ReduceSumPhysicalOp(_PhysMixin, ReduceSumOp):
     _name = "reduce_sum_physical"
 
     def vjp_rule(self, primals, cot, outputs, kwargs):
-        from .view.axes import unsqueeze_physical
         from .view.shape import broadcast_to_physical
 
         x = primals[0]
-        if not kwargs.get("keepdims", False):
-            cot = unsqueeze_physical(cot, axis=kwargs["axis"])
-        return (broadcast_to_physical(cot, tuple(x._impl._shape)),)
+        cot = _restore_reduced_axis(cot, x, outputs, kwargs)
+        lead = tuple(cot._impl._shape[:len(cot._impl._shape) - len(x._impl._shape)])
+        return (broadcast_to_physical(cot, lead + tuple(x._impl._shape)),)
 
     def jvp_rule(self, primals, tangents, outputs, kwargs):
         return reduce_sum_physical(tangents[0], **kwargs)
@@ -330,9 +344,9 @@ class _PhysExtremeMixin(_PhysMixin):
         from .view.shape import broadcast_to_physical
 
         w, shape = self._mask(primals[0], outputs, kwargs)
-        if not kwargs.get("keepdims", False):
-            cot = unsqueeze_physical(cot, axis=kwargs["axis"])
-        return (broadcast_to_physical(cot, shape) * w,)
+        cot = _restore_reduced_axis(cot, primals[0], outputs, kwargs)
+        lead = tuple(cot._impl._shape[:len(cot._impl._shape) - len(shape)])
+        return (broadcast_to_physical(cot, lead + tuple(shape)) * w,)
 
     def jvp_rule(self, primals, tangents, outputs, kwargs):
         w, _ = self._mask(primals[0], outputs, kwargs)

@@ -75,45 +75,35 @@ class BroadcastToOp(ShapeOp):
 
 
 class BroadcastToPhysicalOp(BroadcastToOp):
+    """Expand to a full PHYSICAL shape (vmap dims included) of the same rank. `broadcast_to_physical`
+    inserts any missing dims first, so the op itself only widens size-1 dims."""
+
     _name = "broadcast_to_physical"
 
     def adapt_kwargs(self, args, kwargs, batch_dims):
         return {"shape": tuple(int(s) for s in kwargs["shape"])}
 
     def kernel(self, x, *, shape):
-        extra = len(shape) - x.dim()
-        if extra > 0:
-            x = x.reshape(*([1] * extra), *x.shape)
         return x.expand(shape)
-
-    def output_batch_dims(self, batch_dims, kwargs):
-        return batch_dims + max(0, len(kwargs["shape"]) - getattr(self, "_in_rank", len(kwargs["shape"])))
-
-    def __call__(self, x, **kwargs):
-        self._in_rank = len(x._impl._shape)
-        self._bd = 0
-        return Operation.__call__(self, x, **kwargs)
-
-    def execute(self, node):
-        self._bd = 0
-        return Operation.execute(self, node)
 
     def vjp_rule(self, primals, cot, outputs, kwargs):
         from ..reduction import reduce_sum_physical
-        from .axes import squeeze_physical
 
         x = primals[0]
-        in_shape = x._impl._shape
-        extra = len(kwargs["shape"]) - len(in_shape)
-        for _ in range(extra):
-            cot = reduce_sum_physical(cot, axis=0, keepdims=False)
-        for i, s in enumerate(in_shape):
-            if s == 1 and cot._impl._shape[i] != 1:
-                cot = reduce_sum_physical(cot, axis=i, keepdims=True)
+        # a cotangent with more vmap dims than the primal keeps them in front: align from the right
+        off = len(cot._impl._shape) - len(x._impl._shape)
+        for i, s in enumerate(x._impl._shape):
+            if s == 1 and cot._impl._shape[i + off] != 1:
+                cot = reduce_sum_physical(cot, axis=i + off, keepdims=True)
         return (cot,)
 
     def jvp_rule(self, primals, tangents, outputs, kwargs):
-        return broadcast_to_physical(tangents[0], kwargs["shape"])
+        t = tangents[0]
+        more = t._impl.batch_dims - primals[0]._impl.batch_dims
+        shape = tuple(kwargs["shape"])
+        if more > 0:      # the tangent is mapped over dims the primal does not have (jacfwd's basis)
+            shape = tuple(t._impl._shape[:more]) + shape
+        return broadcast_to_physical(t, shape)
 
 
 # ---------------------------------------------------------------- reshape
@@ -259,9 +249,13 @@ class SliceUpdateOp(ShapeOp):
         x = args[0]
         bd = max(batch_dims, x._impl.batch_dims)
         return {"start": (0,) * bd + tuple(int(s) for s in kwargs["start"]),
-                "size": tuple(x._impl._shape[:bd]) + tuple(int(s) for s in kwargs["size"])}
+                "size": tuple(x._impl._shape[:bd]) + tuple(int(s) for s in kwargs["size"]),
+                "use_buffer_ops": bool(kwargs.get("use_buffer_ops", False))}
 
-    def kernel(self, x, u, *, start, size):
+    def kernel(self, x, u, *, start, size, use_buffer_ops: bool = False):
+        # `use_buffer_ops` records which API asked (`x[...] = v` sets it, `x.at[...]` and
+        # `slice_update` do not; reference: nabla/ops/view/shape.py:1065-1077). Both write into a
+        # copy: the old value may still be needed by a backward pass.
         out = x.clone()
         idx = tuple(slice(s, s + n) for s, n in zip(start, size))
         out[idx] = u.to(out.dtype)
@@ -280,7 +274,7 @@ class SliceUpdateOp(ShapeOp):
         u = node.input_impls()[1]
         if u.sharding is None:
             return kwargs
-        return {"start": kwargs["start"], "size": tuple(u._buffers[shard_idx].shape)}
+        return {**kwargs, "size": tuple(u._buffers[shard_idx].shape)}
 
     def vjp_rule(self, primals, cot, outputs, kwargs):
         from ..creation import zeros_like
@@ -418,9 +412,18 @@ def broadcast_to(x, shape) -> Tensor:
 
 
 def broadcast_to_physical(x, shape) -> Tensor:
+    """Broadcast to the physical shape ``shape`` (the tensor's vmap dims, then its logical dims).
+    Dims that ``shape`` has and ``x`` lacks are new LOGICAL dims, placed right behind the vmap dims,
+    so the number of vmap dims never changes (reference: nabla/ops/view/shape.py:1127-1161)."""
+    from .axes import unsqueeze_physical
+
+    x = ensure_tensor(x)
     shape = tuple(int(s) for s in shape)
     if tuple(x._impl._shape) == shape:
         return x
+    bd = x._impl.batch_dims
+    for _ in range(len(shape) - len(x._impl._shape)):
+        x = unsqueeze_physical(x, axis=bd)
     return _broadcast_to_p(x, shape=shape)
 
 
@@ -451,17 +454,20 @@ def slice_tensor(x, start, size) -> Tensor:
     return _slice(x, start=start, size=size)
 
 
-def slice_update(x, update, start, size) -> Tensor:
+def slice_update(x, update, start, size, *, use_buffer_ops: bool = False) -> Tensor:
     x = ensure_tensor(x)
     update = ensure_tensor(update, x)
     if update.dtype is not x.dtype:
         from ..unary import cast
 
         update = cast(update, x.dtype)
-    return _slice_update(x, update, start=tuple(int(s) for s in start), size=tuple(int(s) for s in size))
+    return _slice_update(x, update, start=tuple(int(s) for s in start), size=tuple(int(s) for s in size),
+                         use_buffer_ops=bool(use_buffer_ops))
 
 
-slice_update_inplace = slice_update
+def slice_update_inplace(x, update, start, size) -> Tensor:
+    """`slice_update` as issued by ``x[...] = value``: same result, marked ``use_buffer_ops=True``."""
+    return slice_update(x, update, start, size, use_buffer_ops=True)
 
 
 def concatenate(tensors, axis: int = 0) -> Tensor:

@@ -198,7 +198,7 @@ def test_conv2d_transpose_argument_validation():
         nb.conv2d_transpose(x, w, output_paddings=(1, 1))
     with pytest.raises(ValueError, match="dilation"):
         nb.conv2d_transpose(x, w, dilation=(2, 1))
-    with pytest.raises(ValueError, match="C_in"):
+    with pytest.raises(ValueError, match="Input channels"):
         nb.conv2d_transpose(x, T(X(3, 3, 5, 3)))
     with pytest.raises(ValueError, match="layouts"):
         nb.conv2d_transpose(x, w, filter_layout="OIHW")

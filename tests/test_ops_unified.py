@@ -165,7 +165,7 @@ def test_argmax_argmin_minmax_chunk_misc():
     close(mm["min"], x.amin(1))
     close(mm["max"], x.amax(1))
     parts = nb.chunk(T(x), 3, axis=1)
-    assert [int(p.shape[1]) for p in parts] == [3, 3, 1]
+    assert [int(p.shape[1]) for p in parts] == [3, 2, 2]      # sizes differ by at most one, larger first
     close(nb.floor(T(x)), x.floor())
     close(nb.trunc(T(x)), x.trunc())
     close(nb.round(T(x)), x.round())

@@ -189,7 +189,7 @@ def test_split_chunk_unbind_on_sharded_inputs():
     for p, r in zip(nb.chunk(xs, 3, axis=1), torch.chunk(a, 3, dim=1)):
         close(p, r)
     uneven = nb.chunk(T(rand(7, 2, seed=22)), 3, axis=0)
-    assert [tuple(int(d) for d in u.shape) for u in uneven] == [(3, 2), (3, 2), (1, 2)]
+    assert [tuple(int(d) for d in u.shape) for u in uneven] == [(3, 2), (2, 2), (2, 2)]      # numpy array_split sizes
     for p, r in zip(nb.unbind(xs, axis=0), torch.unbind(a, 0)):
         close(p, r)
     b = rand(2, 4, 3, seed=23)
@@ -209,6 +209,11 @@ def test_split_on_a_two_axis_mesh_and_minmax():
     mm = nb.minmax(nb.shard(T(a), _mesh(2), ("x", None)), axis=0)
     close(mm["min"], a.min(0).values)
     close(mm["max"], a.max(0).values)
+    for t in (T(a), nb.shard(T(a), _mesh(2), ("x", None))):      # no axis: over the whole tensor
+        mm = nb.minmax(t)
+        assert tuple(mm["min"].shape) == ()
+        close(mm["min"], a.min())
+        close(mm["max"], a.max())
 
 
 def test_vmap_over_multi_output_ops_and_edge_cases():
@@ -592,3 +597,68 @@ def test_compile_cache_key_separates_replicated_partial_and_explicitly_replicate
             c._extract_sharding_key(ShardingSpec(mesh, dims, partial_sum_axes={"tp"})),
             c._extract_sharding_key(ShardingSpec(mesh, dims, replicated_axes={"tp"}))}
     assert len(keys) == 3 and c._extract_sharding_key(None) is None
+
+
+def test_broadcast_to_physical_adds_logical_dims_and_all_hessian_modes_agree():
+    """reference: tests/unit/test_hessian_physical_ops.py (broadcast_to_physical, batch-dims chain)."""
+    from nabla_b200.ops.view import broadcast_batch_dims
+
+    a = rand(2, 3, seed=94)
+    y = nb.broadcast_to_physical(T(a), (4, 2, 3))
+    assert y.batch_dims == 0 and tuple(int(d) for d in y.shape) == (4, 2, 3)
+
+    def f(x):
+        z = nb.broadcast_to_physical(x, (4, 2, 3))
+        return nb.reduce_sum(z * z)
+
+    def g(x):
+        z = broadcast_batch_dims(x, (3,))
+        z = nb.reduce_sum_physical(z * z, axis=0, keepdims=False)      # sums a vmap dim away again
+        return nb.reduce_sum(z)
+
+    eye = torch.eye(6).reshape(2, 3, 2, 3)
+    for fn, scale in ((f, 8.0), (g, 6.0)):
+        close(nb.grad(fn)(T(a)), scale * a, rtol=1e-5, atol=1e-5)
+        for outer, inner in ((nb.jacrev, nb.jacrev), (nb.jacfwd, nb.jacfwd), (nb.jacrev, nb.jacfwd), (nb.jacfwd, nb.jacrev)):
+            close(outer(inner(fn))(T(a)), scale * eye, rtol=1e-5, atol=1e-5)
+
+
+def test_tensor_global_and_local_shape_include_vmap_dims():
+    seen = {}
+
+    def f(row):
+        seen["g"], seen["l"], seen["s"] = tuple(row.global_shape), tuple(row.local_shape), tuple(row.shape)
+        return row * 2.0
+
+    nb.vmap(f)(T(rand(4, 6, seed=95)))
+    assert seen == {"g": (4, 6), "l": (4, 6), "s": (6,)}
+
+
+def test_distributed_broadcast_gradient_counts_every_copy_and_all_to_all_checks_divisibility():
+    """reference: tests/unit/test_communication_rigorous.py:104-123,
+    test_vmap_communication_comprehensive.py:80-96."""
+    mesh = _mesh(2, "tp")
+    u = rand(4, seed=96)
+
+    def f(t):
+        r = nb.distributed_broadcast(t, mesh=mesh)
+        return nb.reduce_sum(r * r)
+
+    close(f(T(u)), (u * u).sum(), rtol=1e-5, atol=1e-5)
+    close(nb.grad(f)(T(u)), 2 * u * 2, rtol=1e-5, atol=1e-5)
+    x = nb.shard(T(rand(3, 4, seed=97)), mesh, ("tp", None))
+    with pytest.raises(ValueError, match="divisible"):
+        nb.all_to_all(x, split_axis=0, concat_axis=1)
+
+
+def test_index_updates_record_which_api_asked_and_tensor_trace_returns_the_tensor():
+    """reference: tests/unit/test_tensor_index_update_api.py:44-108."""
+    x = T(np.arange(6, dtype=np.float32).reshape(2, 3))
+    upd = T(np.array([[10.0, 11.0], [12.0, 13.0]], dtype=np.float32))
+    y = x.at[:, 1:3].set(upd)
+    assert y.op_kwargs.get("use_buffer_ops") is False
+    t = T(np.arange(6, dtype=np.float32).reshape(2, 3)).trace()
+    assert isinstance(t, nb.Tensor) and t.is_traced
+    t[:, 1:3] = upd
+    assert t.is_traced and t.op_kwargs.get("use_buffer_ops") is True
+    close(t, np.array([[0.0, 10.0, 11.0], [3.0, 12.0, 13.0]]))
