@@ -539,7 +539,10 @@ def reshard_tensor(tensor, from_spec, to_spec, mesh=None):
 
 def broadcast(x, mesh: DeviceMesh | None = None, root: int = 0):
     x = ensure_tensor(x)
-    mesh = mesh or x._impl.sharding.mesh
+    if mesh is None:
+        if x._impl.sharding is None:
+            return x                       # one device, no mesh: nothing to replicate onto
+        mesh = x._impl.sharding.mesh
     return reshard_to_spec(x, replicated_spec(mesh, len(x._impl._shape)))
 
 

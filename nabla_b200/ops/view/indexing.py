@@ -96,6 +96,8 @@ class ScatterOp(Operation):
             ub = upd.reshape(-1, *upd.shape[bd:])
             outs = [self.kernel(xb[i], ib[i], ub[i], axis=axis - bd, mode=mode, bd=0) for i in range(xb.shape[0])]
             return torch.stack(outs, 0).reshape(x.shape)
+        if x.numel() == 0 or upd.numel() == 0:
+            return x.clone()            # an empty shard (uneven split): nothing to write
         xm = torch.movedim(x, axis, 0).clone()
         k = idx.dim()
         um = upd

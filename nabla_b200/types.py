@@ -301,4 +301,8 @@ def as_device(d) -> Device:
         return d
     if isinstance(d, str) and d in ("gpu", "accelerator"):
         return Accelerator(0)
+    if isinstance(d, int) and not isinstance(d, bool):
+        # a device id taken from a mesh (`mesh.devices[i]`): that GPU when this process has it, else
+        # the host, where a mesh larger than the machine is simulated
+        return Accelerator(d) if torch.cuda.is_available() and d < torch.cuda.device_count() else CPU()
     return Device.from_torch(d)

@@ -486,6 +486,17 @@ def _install_array_methods():
         for name, fn in (("max", amax), ("min", amin), ("sum", sum), ("mean", mean), ("prod", prod),
                          ("any", any), ("all", all)):
             setattr(T, name, _numpy_keywords(getattr(T, name), fn))
+        for name in ("__radd__", "__rsub__", "__rmul__", "__rtruediv__"):
+            setattr(T, name, _reflected(getattr(T, name)))
+
+
+def _reflected(orig):
+    """``ndarray - tensor`` ends in ``tensor.__rsub__(ndarray)`` (torch outranks numpy): take the array."""
+    def method(self, other):
+        return orig(self, asarray(other) if isinstance(other, _np.ndarray) else other)
+
+    method.__name__ = orig.__name__
+    return method
 
 
 def _numpy_keywords(orig, np_style):

@@ -662,3 +662,22 @@ def test_index_updates_record_which_api_asked_and_tensor_trace_returns_the_tenso
     t[:, 1:3] = upd
     assert t.is_traced and t.op_kwargs.get("use_buffer_ops") is True
     close(t, np.array([[0.0, 10.0, 11.0], [3.0, 12.0, 13.0]]))
+
+
+def test_edge_cases_from_the_reference_older_suites():
+    """An int device is a mesh device id; `broadcast` of an unsharded tensor without a mesh is the
+    tensor itself; a scatter onto a shard that an uneven split left empty writes nothing
+    (reference: tests/depr/test_streaming_pipeline.py, test_communication_ops.py)."""
+    from nabla_b200.ops.communication import broadcast
+
+    z = nb.zeros((2, 3), device=0)
+    assert tuple(int(d) for d in z.shape) == (2, 3)
+    a = rand(8, 4, seed=98)
+    close(broadcast(T(a), root=0), a)
+    mesh = nb.DeviceMesh("pd", (2, 4), ("stage", "data"))
+    state = nb.shard(T(np.zeros((2, 2, 8), np.float32)), mesh, ("stage", "data", None))   # 2 rows over 4 devices
+    fresh = rand(1, 2, 8, seed=99)
+    out = nb.scatter(state, nb.constant(np.array([0], dtype=np.int32)), T(fresh), axis=0)
+    ref = torch.zeros(2, 2, 8)
+    ref[0] = fresh[0]
+    close(out, ref)
