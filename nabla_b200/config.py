@@ -117,6 +117,26 @@ _EAGER_MAX_GRAPH = _EAGER
 _VERIFY_EAGER_SHAPES = _VERIFY
 tracing_context = tracing
 
+
+@contextlib.contextmanager
+def eager_max_graph_context(value: bool):
+    """Set EAGER_MAX_GRAPH inside a ``with`` block (reference: nabla/config.py:83-89)."""
+    tok = _EAGER.set(bool(value))
+    try:
+        yield
+    finally:
+        _EAGER.reset(tok)
+
+
+@contextlib.contextmanager
+def verify_eager_shapes_context(value: bool):
+    """Set VERIFY_EAGER_SHAPES inside a ``with`` block (reference: nabla/config.py:93-99)."""
+    tok = _VERIFY.set(bool(value))
+    try:
+        yield
+    finally:
+        _VERIFY.reset(tok)
+
 _DEBUG_ON = ("1", "true", "TRUE", "True")
 
 

@@ -82,3 +82,13 @@ def _in_running_loop() -> bool:
     except RuntimeError:
         return False
     return True
+
+
+@contextlib.contextmanager
+def contextvar_context(var: ContextVar, value):
+    """Set any ContextVar inside a ``with`` block (reference: nabla/core/common/context.py:37-42)."""
+    tok = var.set(value)
+    try:
+        yield
+    finally:
+        var.reset(tok)

@@ -287,3 +287,11 @@ def with_batch_dims(tree: Any, delta: int) -> Any:
 def tree_unflatten_full(treedef: PyTreeDef, leaves: list) -> Any:
     """Inverse of a flatten that kept ``None`` leaves (reference: nabla/core/common/pytree.py:239-241)."""
     return tree_unflatten(treedef, leaves)
+
+
+def is_tensor_value(obj: Any) -> bool:
+    """Is ``obj`` a value of the execution backend (reference: pytree.py:416, a MAX graph value)?
+    Here that is a device buffer."""
+    import torch
+
+    return isinstance(obj, torch.Tensor)

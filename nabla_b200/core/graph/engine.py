@@ -272,3 +272,12 @@ GRAPH = _GraphProxy()
 def seed(value: int) -> None:
     """Set the global RNG seed used by ``uniform`` / ``gaussian`` / ``dropout``."""
     GRAPH.set_seed(value)
+
+
+def driver_tensor_type(t):
+    """(shape, dtype, device) of a realized buffer: what the engine needs to know about an input
+    (reference: nabla/core/graph/engine.py:91, which returns the MAX graph tensor type of a driver
+    buffer; the buffers here are torch tensors)."""
+    from ...types import as_dtype
+
+    return tuple(int(d) for d in t.shape), as_dtype(t.dtype), t.device

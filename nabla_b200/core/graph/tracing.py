@@ -185,3 +185,12 @@ def trace(fn: Callable, *args, **kwargs) -> Trace:
     tr = Trace(args if not kwargs else (args, kwargs), out)
     tr.compute()
     return tr
+
+
+def __getattr__(name: str):
+    # `GraphPrinter` lives in `printer.py` (which imports this module); the reference keeps it here
+    if name == "GraphPrinter":
+        from .printer import GraphPrinter
+
+        return GraphPrinter
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

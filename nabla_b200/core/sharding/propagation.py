@@ -271,12 +271,71 @@ def required_input_specs(rule: OpShardingRule, input_specs: Sequence[ShardingSpe
     return out
 
 
-def propagate_sharding(rule: OpShardingRule, input_specs, output_specs, *args, **kwargs) -> bool:
-    """Legacy entry point kept for API compatibility: fills ``output_specs[0]`` in place."""
-    if not input_specs:
+class PropagationStrategy:
+    """How `propagate_sharding` settles a factor that several operands shard differently.
+    BASIC: the proposal with the smallest priority number wins, ties go to the one that splits the
+    factor over more devices, then to the first operand."""
+
+    BASIC = "basic"
+
+
+def propagate_sharding(rule: OpShardingRule, input_specs, output_specs, strategy=PropagationStrategy.BASIC,
+                       **_kw) -> bool:
+    """One bidirectional step over an op: every operand dim proposes its mesh axes for the factor it
+    maps to, one proposal per factor is chosen, and every OPEN dim of every operand (inputs and
+    outputs alike) takes the chosen axes of its factors. Closed dims (``is_open=False``) keep what
+    they have, and an axis is never used twice inside one tensor. Returns whether anything changed;
+    a solver calls this over all ops until nothing does. (The reference kept only a forward stub
+    under this name, nabla/core/sharding/propagation.py:314.)"""
+    operands = [(m, sp) for m, sp in zip(rule.input_mappings, input_specs) if sp is not None]
+    operands += [(m, sp) for m, sp in zip(rule.output_mappings, output_specs) if sp is not None]
+    if not operands:
         return False
-    spec, _ = infer_from_rule(rule, input_specs, input_specs[0].mesh)
-    if output_specs:
-        output_specs[0].dim_specs = spec.dim_specs
-        output_specs[0].partial_sum_axes = spec.partial_sum_axes
-    return True
+    mesh = operands[0][1].mesh
+    best: dict[str, tuple] = {}
+    order = 0
+    for mapping, spec in operands:
+        for dim, factors in mapping.items():
+            if dim >= len(spec.dim_specs) or not factors:
+                continue
+            ds = spec.dim_specs[dim]
+            if not ds.axes:
+                continue
+            shards = 1
+            for a in ds.axes:
+                shards *= mesh.get_axis_size(a)
+            # closed dims are facts, open ones are suggestions: facts first, then priority, then width
+            key = (0 if not ds.is_open else 1, ds.priority, -shards, order)
+            order += 1
+            f = factors[0]                      # a dim made of several factors gives its axes to the major one
+            if f not in best or key < best[f][0]:
+                best[f] = (key, list(ds.axes), ds.priority)
+    changed = False
+    for mapping, spec in operands:
+        used = {a for d, ds in enumerate(spec.dim_specs) if not ds.is_open or d not in mapping for a in ds.axes}
+        used |= set(spec.replicated_axes) | set(spec.partial_sum_axes)
+        for dim in sorted(mapping):
+            if dim >= len(spec.dim_specs):
+                continue
+            ds = spec.dim_specs[dim]
+            if not ds.is_open:
+                continue
+            want: list[str] = []
+            prio = ds.priority
+            for f in mapping[dim]:
+                if f in best:
+                    for a in best[f][1]:
+                        if a not in used and a not in want:
+                            want.append(a)
+                    prio = min(prio, best[f][2]) if ds.axes else best[f][2]
+            size = rule.factor_sizes.get(mapping[dim][0]) if mapping[dim] else None
+            shards = 1
+            for a in want:
+                shards *= mesh.get_axis_size(a)
+            if size is not None and shards > 1 and int(size) % shards:
+                want = []                       # would not divide the dim: leave it alone
+            if want and want != ds.axes and len(want) >= len(ds.axes):
+                spec.dim_specs[dim] = DimSpec(want, is_open=True, priority=prio)
+                changed = True
+            used |= set(spec.dim_specs[dim].axes)
+    return changed

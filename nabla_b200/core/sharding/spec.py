@@ -39,6 +39,23 @@ def parse_sub_axis(axis_name: str) -> tuple[str, int, int] | None:
     return m.group(1), int(m.group(2)), int(m.group(3))
 
 
+def check_sub_axes_maximality(axes: Iterable[str]) -> list[str]:
+    """Warnings for sub-axes of one parent that sit next to each other and could be written as one
+    (``'x:(1)2'`` and ``'x:(2)2'`` are ``'x:(1)4'``). Reference: nabla/core/sharding/spec.py:53-79."""
+    by_parent: dict[str, list[tuple[int, int, str]]] = {}
+    for ax in axes:
+        p = parse_sub_axis(ax)
+        if p is not None:
+            by_parent.setdefault(p[0], []).append((p[1], p[2], ax))
+    out = []
+    for parent, subs in by_parent.items():
+        subs.sort()
+        for (pre1, size1, ax1), (pre2, size2, ax2) in zip(subs, subs[1:]):
+            if pre1 * size1 == pre2:
+                out.append(f"Adjacent sub-axes '{ax1}' and '{ax2}' could be merged into '{parent}:({pre1}){size1 * size2}'")
+    return out
+
+
 def validate_sub_axes_non_overlapping(axes: Iterable[str]) -> None:
     seen: dict[str, list[tuple[int, int, str]]] = {}
     for ax in axes:

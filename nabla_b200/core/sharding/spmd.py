@@ -152,3 +152,67 @@ def infer_output_sharding(op, args, mesh, kwargs=None):
     used = out.used_axes()
     out.partial_sum_axes = {a for a in (contr | keep) if a not in used}
     return out, specs, incoming - keep
+
+
+# ---- shard-level helpers (reference: nabla/core/sharding/spmd.py:44-370). The ops of this package go
+# through `prepare` and their own `execute`; these are the same steps offered one by one, for code
+# that wants to run something of its own once per shard.
+def reshard_inputs(args, required_specs, mesh: DeviceMesh | None):
+    """Lay the tensor leaves of ``args`` out as ``required_specs`` asks (one spec per tensor leaf,
+    ``None`` = leave alone); everything else passes through."""
+    if mesh is None or not required_specs:
+        return args
+    from ...ops.communication.collectives import needs_reshard, reshard_to_spec
+    from ..tensor.api import Tensor
+
+    leaves, td = pytree.tree_flatten(args)
+    specs = iter(required_specs)
+    out = []
+    for leaf in leaves:
+        if isinstance(leaf, Tensor):
+            want = next(specs, None)
+            if want is not None and needs_reshard(leaf._impl.sharding, want):
+                leaf = reshard_to_spec(leaf, want)
+        out.append(leaf)
+    return pytree.tree_unflatten(td, out)
+
+
+def get_shard_args(args, shard_idx: int, per_input_shardings=None, *_unused):
+    """``args`` with every tensor replaced by its buffer on local shard ``shard_idx`` (a tensor
+    that is not on a mesh gives its single buffer to every shard)."""
+    from ..tensor.api import Tensor
+
+    def pick(x):
+        if not isinstance(x, Tensor):
+            return x
+        x.realize()
+        bufs = x._impl._buffers
+        return bufs[shard_idx] if len(bufs) > 1 else bufs[0]
+
+    leaves, td = pytree.tree_flatten(args)
+    return pytree.tree_unflatten(td, [pick(x) for x in leaves])
+
+
+def execute_on_shards(op_fn: Callable, args, kwargs: dict, mesh: DeviceMesh | None, input_shardings=None, op=None) -> list:
+    """Run ``op_fn(*shard buffers, **kwargs)`` once per local shard of ``mesh`` (once when there is
+    no mesh) and return the per-shard results."""
+    n = mesh.num_local if mesh is not None else 1
+    out = []
+    for i in range(n):
+        a = get_shard_args(args, i, input_shardings)
+        out.append(op_fn(*a, **kwargs) if isinstance(a, (tuple, list)) else op_fn(a, **kwargs))
+    return out
+
+
+def create_sharded_output(results: list, sharding: ShardingSpec | None, is_traced: bool = False, batch_dims: int = 0,
+                          mesh: DeviceMesh | None = None, physical_shapes=None, shard_dtypes=None, shard_devices=None):
+    """A tensor made of the per-shard buffers ``results``; with a mesh but no spec they are taken
+    as replicas."""
+    from ..tensor.api import Tensor
+    from ..tensor.impl import TensorImpl
+
+    if sharding is None and mesh is not None:
+        sharding = replicated_spec(mesh, results[0].dim())
+    impl = TensorImpl(list(results) if sharding is not None else [results[0]], sharding=sharding, batch_dims=batch_dims,
+                      is_traced=is_traced)
+    return Tensor(impl=impl)

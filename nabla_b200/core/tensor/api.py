@@ -294,6 +294,15 @@ class Tensor:
         return cls(buffers=[t])
 
     @classmethod
+    def from_graph_value(cls, value) -> "Tensor":
+        """Wrap a value of the execution backend. The reference wraps a node of the MAX graph under
+        construction (nabla/core/tensor/api.py:431-434); the values this engine computes with are
+        device buffers, so that is what is accepted here."""
+        if not isinstance(value, torch.Tensor):
+            raise TypeError(f"{value=} must be a tensor or buffer value")
+        return cls(buffers=[value])
+
+    @classmethod
     def constant(cls, value, *, dtype=None, device=None) -> "Tensor":
         from ...ops.creation import constant
 

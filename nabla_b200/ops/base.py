@@ -455,6 +455,13 @@ class AxisOp(Operation):
     """Op with an ``axis`` kwarg given in logical coordinates; kernels see physical axes."""
 
     axis_keys: tuple[str, ...] = ("axis",)
+    #: ops that INSERT a dim count the axis against the output rank (reference: ops/base.py:704)
+    axis_offset_for_insert: bool = False
+
+    @property
+    def axis_arg_names(self) -> set[str]:
+        """Names of the kwargs that hold axes (the reference's attribute, ops/base.py:706)."""
+        return set(self.axis_keys)
 
     def adapt_kwargs(self, args, kwargs, batch_dims):
         t = None
@@ -489,6 +496,15 @@ class ReduceOperation(AxisOp):
 
     def torch_reduce(self, x, axis, keepdims):
         raise NotImplementedError
+
+    def infer_output_shape(self, input_shapes, **kwargs) -> tuple[int, ...]:
+        """Shape after reducing ``axis`` of ``input_shapes[0]`` (reference: ops/base.py:881-895)."""
+        axis, keepdims = int(kwargs.get("axis", 0)), bool(kwargs.get("keepdims", False))
+        shape = tuple(int(d) for d in input_shapes[0])
+        axis = axis + len(shape) if axis < 0 else axis
+        if keepdims:
+            return tuple(1 if i == axis else d for i, d in enumerate(shape))
+        return tuple(d for i, d in enumerate(shape) if i != axis)
 
     def kernel(self, x, *, axis: int, keepdims: bool = False):
         if self.native_op is not None and x.is_cuda and x.dim() and x.shape[axis] > 0:
@@ -542,3 +558,33 @@ class CollectiveOperation(Operation):
     """Base of the communication ops (see ``nabla_b200.ops.communication``)."""
 
     partial_policy = "any"
+
+    # ---- cost model used by the auto-sharding solver (reference: nabla/ops/communication/base.py:51-66,
+    # 245-279): time of a ring over the devices of ``axes``, in bytes / ``mesh.bandwidth`` units
+    @staticmethod
+    def _ring_cost(size_bytes: int, mesh, axes, factor: float = 1.0) -> float:
+        if not axes:
+            return 0.0
+        n = 1
+        for a in axes:
+            n *= mesh.get_axis_size(a)
+        if n <= 1:
+            return 0.0
+        return factor * (n - 1) / n * size_bytes / float(getattr(mesh, "bandwidth", 1.0) or 1.0)
+
+    @classmethod
+    def estimate_cost(cls, size_bytes: int, mesh, axes, input_specs=None, output_specs=None) -> float:
+        """Cost of moving ``size_bytes`` over the mesh axes ``axes``; 0 for ops that move nothing."""
+        return 0.0
+
+    def communication_cost(self, input_specs, output_specs, input_shapes, output_shapes, mesh) -> float:
+        if not input_shapes:
+            return 0.0
+        n = 1
+        for d in input_shapes[0]:
+            n *= int(d)
+        axes: list[str] = []
+        if input_specs and input_specs[0]:
+            for ds in input_specs[0].dim_specs:
+                axes.extend(ds.axes)
+        return self.estimate_cost(n * 4, mesh, axes, input_specs, output_specs)

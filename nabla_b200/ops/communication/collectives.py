@@ -135,6 +135,10 @@ class ShardOp(_LayoutOp):
 class AllGatherOp(_LayoutOp):
     """Make physical dim ``dim`` whole on every device of its sharding group."""
 
+    @classmethod
+    def estimate_cost(cls, size_bytes: int, mesh, axes, input_specs=None, output_specs=None) -> float:
+        return CollectiveOperation._ring_cost(size_bytes, mesh, axes, factor=1.0)
+
     def out_spec(self, x, mesh, kwargs):
         sp = _spec_of(x, mesh).clone()
         sp.dim_specs[kwargs["dim"]] = DimSpec([])
@@ -208,6 +212,10 @@ class GatherAllAxesOp(_LayoutOp):
 
 # ---------------------------------------------------------------- all_reduce
 class AllReduceOp(_LayoutOp):
+    @classmethod
+    def estimate_cost(cls, size_bytes: int, mesh, axes, input_specs=None, output_specs=None) -> float:
+        return CollectiveOperation._ring_cost(size_bytes, mesh, axes, factor=2.0)
+
     def _plan(self, x: Tensor, mesh, kwargs):
         sp = _spec_of(x, mesh)
         axes = set(kwargs["reduce_axes"])
@@ -301,6 +309,10 @@ def _psum_transpose(cot: Tensor, x: Tensor, kwargs) -> Tensor:
 
 # ---------------------------------------------------------------- reduce_scatter
 class ReduceScatterOp(_LayoutOp):
+    @classmethod
+    def estimate_cost(cls, size_bytes: int, mesh, axes, input_specs=None, output_specs=None) -> float:
+        return CollectiveOperation._ring_cost(size_bytes, mesh, axes, factor=1.0)
+
     def out_spec(self, x, mesh, kwargs):
         sp = _spec_of(x, mesh).clone()
         dim = kwargs["dim"]

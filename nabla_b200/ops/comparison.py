@@ -8,7 +8,9 @@ from ..core.tensor.api import Tensor
 from .base import BinaryOperation, UnaryOperation
 
 
-class _Cmp(BinaryOperation):
+class ComparisonOp(BinaryOperation):
+    """Elementwise binary predicate with a bool result (reference: nabla/ops/comparison.py:27)."""
+
     fn = None
 
     def torch_fn(self, a, b):
@@ -19,6 +21,9 @@ class _Cmp(BinaryOperation):
 
     def jvp_rule(self, primals, tangents, outputs, kwargs):
         return None
+
+
+_Cmp = ComparisonOp
 
 
 class _Logical(_Cmp):
@@ -42,7 +47,22 @@ _logical_or = _mk("LogicalOrOp", torch.logical_or, _Logical)
 _logical_xor = _mk("LogicalXorOp", torch.logical_xor, _Logical)
 
 
-class LogicalNotOp(UnaryOperation):
+for _op in (_equal, _not_equal, _greater, _greater_equal, _less, _less_equal, _logical_and, _logical_or, _logical_xor):
+    globals()[type(_op).__name__] = type(_op)
+del _op
+
+
+class ComparisonUnaryOp(UnaryOperation):
+    """Elementwise unary predicate with a bool result (reference: nabla/ops/comparison.py:43)."""
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        return (None,)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return None
+
+
+class LogicalNotOp(ComparisonUnaryOp):
     def torch_fn(self, x):
         return torch.logical_not(x)
 

@@ -170,6 +170,18 @@ class WhileOp(_HostControlOp):
 
 
 _cond_op, _while_op = CondOp(), WhileOp()
+WhileLoopOp = WhileOp           # the reference's name (nabla/ops/control_flow.py:314)
+
+
+class ScanOp:
+    """`scan` under the reference's op name (nabla/ops/control_flow.py:453). There is no node of its
+    own: the loop is unrolled while tracing, so each step's ops are recorded (and differentiated)
+    like any others."""
+
+    name = "scan"
+
+    def __call__(self, f, init, xs, length=None, reverse: bool = False):
+        return scan(f, init, xs, length=length, reverse=reverse)
 
 
 def _same_structure(a_leaves: list, b_leaves: list, what: str) -> None:

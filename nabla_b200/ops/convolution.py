@@ -280,6 +280,7 @@ class Conv2dTransposeOp(Operation):
 
 
 _conv2d, _conv_dgrad_op, _conv_wgrad_op, _conv2d_transpose = Conv2dOp(), ConvDgradOp(), ConvWgradOp(), Conv2dTransposeOp()
+Conv2DOp, Conv2DTransposeOp = Conv2dOp, Conv2dTransposeOp      # the reference's spelling (nabla/ops/convolution.py)
 
 
 def _conv_dgrad(dy, w, *, x_shape, stride, padding):

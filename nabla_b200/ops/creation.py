@@ -174,8 +174,33 @@ class TrilOp(_BandOp):
     upper = False
 
 
+class ZerosOp(FullOp):
+    """`full` with the value fixed to 0 (reference: nabla/ops/creation.py:66)."""
+
+    def kernel(self, *, shape, dtype: DType, device, value=0, _shard: int = 0):
+        return super().kernel(shape=shape, value=0, dtype=dtype, device=device, _shard=_shard)
+
+
+class OnesOp(FullOp):
+    """`full` with the value fixed to 1 (reference: nabla/ops/creation.py:81)."""
+
+    def kernel(self, *, shape, dtype: DType, device, value=1, _shard: int = 0):
+        return super().kernel(shape=shape, value=1, dtype=dtype, device=device, _shard=_shard)
+
+
+class ConstantOp:
+    """Literal data as a realized tensor (reference: nabla/ops/creation.py:31). Nothing is recorded
+    in a trace for it: the tensor is a leaf that already holds its buffer."""
+
+    name = "constant"
+
+    def __call__(self, value, *, dtype=None, device=None) -> Tensor:
+        return constant(value, dtype=dtype, device=device)
+
+
 _full, _arange, _uniform, _gaussian, _hann = FullOp(), ArangeOp(), UniformOp(), GaussianOp(), HannWindowOp()
 _triu, _tril = TriuOp(), TrilOp()
+TriOp = _BandOp                # the reference's name for the shared base of triu / tril (creation.py:225)
 TriuOp._inst, TrilOp._inst = _triu, _tril
 
 

@@ -114,7 +114,16 @@ class MinMaxOp(AxisOp):
                 "min": _reduce_min.jvp_rule(primals, tangents, outputs["min"], kwargs)}
 
 
-_split, _unbind, _minmax = SplitOp(), UnbindOp(), MinMaxOp()
+class ChunkOp(SplitOp):
+    """`split` as issued by `chunk` (sizes differ by at most one); shows as ``chunk`` in a trace."""
+
+    _name = "chunk"
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return _chunk(tangents[0], **kwargs)
+
+
+_split, _unbind, _minmax, _chunk = SplitOp(), UnbindOp(), MinMaxOp(), ChunkOp()
 
 
 def split(x, num_splits=None, axis: int = 0, *, num_or_sizes=None) -> tuple[Tensor, ...]:
@@ -148,7 +157,7 @@ def chunk(x, chunks: int, axis: int = 0) -> list[Tensor]:
     n = x._impl.global_shape[axis + rank if axis < 0 else axis]
     div, rem = divmod(int(n), int(chunks))
     sizes = [div + 1 if i < rem else div for i in range(int(chunks))]
-    return list(_split(x, sizes=tuple(s for s in sizes if s > 0), axis=int(axis)))
+    return list(_chunk(x, sizes=tuple(s for s in sizes if s > 0), axis=int(axis)))
 
 
 def unbind(x, axis: int = 0) -> tuple[Tensor, ...]:

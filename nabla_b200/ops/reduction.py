@@ -301,6 +301,9 @@ def _restore_reduced_axis(cot, x, outputs, kwargs):
     return cot
 
 
+PhysicalReduceOp = _PhysMixin     # what every *_physical reduction derives from (reference: reduction.py:67)
+
+
 class ReduceSumPhysicalOp(_PhysMixin, ReduceSumOp):
     _name = "reduce_sum_physical"
 

@@ -87,6 +87,13 @@ _is_inf = _nondiff("IsInfOp", torch.isinf)
 _is_nan = _nondiff("IsNanOp", torch.isnan)
 
 
+# the generated op classes under their own names (`ExpOp`, `ReluOp`, ...; reference: nabla/ops/unary.py)
+for _op in (_relu, _sigmoid, _tanh, _exp, _abs, _log, _sqrt, _acos, _atanh, _cos, _sin, _erf, _log1p, _rsqrt, _silu,
+            _floor, _trunc, _round, _is_inf, _is_nan):
+    globals()[type(_op).__name__] = type(_op)
+del _op
+
+
 class NegOp(UnaryOperation):
     partial_policy = "any"
     native_op = "neg"

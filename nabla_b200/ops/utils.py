@@ -91,3 +91,63 @@ def _make_hashable(obj: Any) -> Any:
         return obj
     except TypeError:
         return repr(obj)
+
+
+# ---------------------------------------------------------------- stages of an op call, one by one
+# (reference: nabla/ops/utils.py:410-762, where `Operation.__call__` is assembled from these).
+# `Operation.__call__` of this package does the same work inline; these give the same answers for
+# code that inspects or drives the steps itself.
+def ensure_tensor(x: Any, like: Any = None) -> Tensor:
+    from .base import ensure_tensor as impl
+
+    return impl(x, like)
+
+
+def collect_metadata(args: Any) -> tuple[int, bool, bool, bool]:
+    """``(max vmap depth, any traced, any sharded, any with a tangent attached)`` over the tensors in
+    ``args``. Forward mode here replays a trace instead of attaching tangents to tensors, so the
+    last entry is True only for tensors a caller gave a ``tangent`` by hand."""
+    from ..core.common import pytree
+
+    depth, traced, sharded, tangent = 0, False, False, False
+    for t in pytree.tensor_leaves(args):
+        im = t._impl
+        depth = max(depth, int(im.batch_dims))
+        traced = traced or bool(im.is_traced)
+        sharded = sharded or im.sharding is not None
+        tangent = tangent or im.tangent is not None
+    return depth, traced, sharded, tangent
+
+
+def compute_structural_hash(op_name: str, args: Any, kwargs: dict | None) -> tuple:
+    """Key of an op call that ignores values: the op, the structure of every argument and kwarg."""
+    return (op_name, tuple(_make_hashable(a) for a in args),
+            tuple(sorted(((k, _make_hashable(v)) for k, v in (kwargs or {}).items()), key=lambda kv: str(kv[0]))))
+
+
+def apply_auto_reduction(op: Any, output: Any, mesh: Any, reduce_axes: Any) -> Any:
+    """All-reduce every tensor of ``output`` over ``reduce_axes`` (the op's own reduction kind: sum,
+    or max / min for the extreme reductions); unchanged when there is nothing to reduce."""
+    if not (reduce_axes and mesh):
+        return output
+    from ..core.common import pytree
+    from .communication import all_reduce
+
+    kind = getattr(op, "collective_reduce_type", "sum") or "sum"
+    return pytree.tree_map(lambda t: all_reduce(t, reduce_axes=set(reduce_axes), reduce_op=kind) if isinstance(t, Tensor) else t,
+                           output)
+
+
+def verify_eager_shapes(op: Any, execution_results: Any, output_physical_shapes: Any) -> None:
+    """With ``VERIFY_EAGER_SHAPES`` on: raise when a computed buffer's shape is not the inferred
+    one. ``execution_results`` are per-output lists of per-shard buffers, ``output_physical_shapes``
+    the matching shapes."""
+    from .. import config
+
+    if not config.get_flag("VERIFY_EAGER_SHAPES") or execution_results is None or output_physical_shapes is None:
+        return
+    for o, (bufs, shapes) in enumerate(zip(execution_results, output_physical_shapes)):
+        for i, (b, want) in enumerate(zip(bufs, shapes)):
+            if tuple(b.shape) != tuple(int(d) for d in want):
+                raise RuntimeError(f"{getattr(op, 'name', op)}: output {o} shard {i} has shape {tuple(b.shape)}, "
+                                   f"shape inference said {tuple(want)}")

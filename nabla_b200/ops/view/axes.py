@@ -16,6 +16,7 @@ def _perm_rule(rank: int, perm) -> OpShardingRule:
 
 class UnsqueezeOp(AxisOp):
     partial_policy = "any"
+    axis_offset_for_insert = True
 
     def logical_rank_for_axis(self, rank, kwargs):
         return rank + 1

@@ -77,3 +77,64 @@ def lift_basis_to_batch_prefix(basis: list, references: list) -> list:
         prefix = tuple(int(d) for d in ref._impl.physical_global_shape[: ref.batch_dims])
         lifted.append(broadcast_batch_dims(b, prefix))
     return lifted
+
+
+# ---- small helpers shared by the transforms (reference: nabla/transforms/utils.py:40-127)
+def split_aux(raw: Any, has_aux: bool, name: str) -> tuple[Any, Any]:
+    """``(output, aux)`` of a function called with ``has_aux``; ``(raw, None)`` without it."""
+    if not has_aux:
+        return raw, None
+    if not isinstance(raw, tuple) or len(raw) != 2:
+        raise ValueError(f"{name} with has_aux=True expects fn to return (output, aux), got {type(raw)}")
+    return raw[0], raw[1]
+
+
+def resolve_argnums(argnums, n_args: int) -> tuple[int, ...]:
+    """``argnums`` (None = all, int, or sequence; negatives count from the end) as a tuple of valid
+    positions."""
+    sel = tuple(range(n_args)) if argnums is None else ((argnums,) if isinstance(argnums, int) else tuple(argnums))
+    out = tuple(a + n_args if a < 0 else a for a in sel)
+    for a in out:
+        if not 0 <= a < n_args:
+            raise ValueError(f"argnum {a} out of bounds for {n_args} arguments")
+    return out
+
+
+def collect_grads(grads_map: dict, input_leaves: list, *, skip_non_diff: bool = True) -> list:
+    """Per-leaf gradients out of a ``{input tensor: gradient}`` map: ``None`` for leaves that are
+    not tensors (or not floating point, with ``skip_non_diff``), zeros for tensors the output does
+    not depend on."""
+    from ..core.tensor.api import Tensor
+    from ..ops.creation import zeros_like
+
+    out = []
+    for leaf in input_leaves:
+        if not isinstance(leaf, Tensor) or (skip_non_diff and not leaf.dtype.is_float()):
+            out.append(None)
+        elif leaf in grads_map:
+            out.append(grads_map[leaf])
+        else:
+            out.append(zeros_like(leaf))
+    return out
+
+
+def realize_tensors(tensors: list) -> None:
+    """Realize the lazy tensors of ``tensors`` in one evaluation."""
+    from ..core.tensor.api import Tensor, realize_all
+
+    lazy = [t for t in tensors if isinstance(t, Tensor) and not t.is_realized]
+    if lazy:
+        realize_all(*lazy)
+
+
+def create_jacobian_helpers(fn, argnums, args: tuple):
+    """``(differentiated args, fn with the other args fixed)`` for jacrev / jacfwd."""
+    norm = resolve_argnums(argnums, len(args))
+
+    def partial_fn(*diff):
+        full = list(args)
+        for i, a in zip(norm, diff):
+            full[i] = a
+        return fn(*full)
+
+    return tuple(args[i] for i in norm), partial_fn

@@ -366,3 +366,168 @@ def test_defaults_of_the_reference_signatures():
         close(jac(f, argnums=1)(u, v), np.diag(2 * u.to_numpy() * v.to_numpy()), rtol=1e-5)
         close(jac(lambda w: w * w)(u), np.diag(2 * u.to_numpy()), rtol=1e-5)     # one argument: a single Jacobian
         assert isinstance(jac(f, argnums=(0,))(u, v), tuple)
+
+
+def test_cost_model_and_shape_helpers_of_the_op_base_classes():
+    """reference: nabla/ops/communication/base.py:51-66,245-279; nabla/ops/base.py:704-706,881-895."""
+    import torch
+
+    from nabla_b200.ops.base import AxisOp, CollectiveOperation, ReduceOperation
+    from nabla_b200.ops.communication import AllGatherOp, AllReduceOp, ReduceScatterOp
+    from nabla_b200.ops.reduction import ReduceSumOp
+    from nabla_b200.ops.view.axes import UnsqueezeOp
+
+    m4 = nb.DeviceMesh("c4", (4,), ("d",))
+    m2 = nb.DeviceMesh("c2", (2,), ("d",))
+    assert AllReduceOp.estimate_cost(10000, m4, ["d"]) == pytest.approx(10 * AllReduceOp.estimate_cost(1000, m4, ["d"]))
+    assert AllReduceOp.estimate_cost(1000, m4, ["d"]) > AllReduceOp.estimate_cost(1000, m2, ["d"])
+    assert AllReduceOp.estimate_cost(1000, m4, ["d"]) == pytest.approx(2 * AllGatherOp.estimate_cost(1000, m4, ["d"]))
+    assert ReduceScatterOp.estimate_cost(1000, m4, ["d"]) == pytest.approx(750.0)
+    assert AllReduceOp.estimate_cost(1000, m4, []) == 0.0 and CollectiveOperation.estimate_cost(1000, m4, ["d"]) == 0.0
+    fast = nb.DeviceMesh("f4", (4,), ("d",), bandwidth=10.0)
+    assert AllGatherOp.estimate_cost(1000, fast, ["d"]) == pytest.approx(75.0)
+    spec = nb.ShardingSpec(m4, [nb.DimSpec(["d"]), nb.DimSpec([])])
+    assert AllGatherOp().communication_cost([spec], [spec], [(8, 4)], [(8, 4)], m4) == pytest.approx(0.75 * 8 * 4 * 4)
+    assert ReduceSumOp().infer_output_shape([(2, 3, 4)], axis=-2) == (2, 4)
+    assert ReduceSumOp().infer_output_shape([(2, 3, 4)], axis=0, keepdims=True) == (1, 3, 4)
+    assert isinstance(ReduceSumOp(), ReduceOperation) and ReduceSumOp().axis_arg_names == {"axis"}
+    assert UnsqueezeOp.axis_offset_for_insert is True and AxisOp.axis_offset_for_insert is False
+    t = nb.Tensor.from_graph_value(torch.ones(2, 3))
+    assert tuple(int(d) for d in t.shape) == (2, 3)
+    with pytest.raises(TypeError):
+        nb.Tensor.from_graph_value([1.0])
+
+
+def test_shard_level_helpers_and_small_utilities():
+    """reference: nabla/core/sharding/spmd.py:44-370, nabla/transforms/utils.py:40-127,
+    nabla/config.py:83-99, nabla/core/sharding/spec.py:53-79."""
+    import nabla_b200.config as cfg
+    from nabla_b200.core.common.context import contextvar_context
+    from nabla_b200.core.common.pytree import is_tensor_value
+    from nabla_b200.core.graph.engine import driver_tensor_type
+    from nabla_b200.core.graph.tracing import GraphPrinter
+    from nabla_b200.core.sharding import spmd
+    from nabla_b200.core.sharding.spec import check_sub_axes_maximality
+    from nabla_b200.transforms.utils import (collect_grads, create_jacobian_helpers, realize_tensors, resolve_argnums,
+                                             split_aux)
+
+    mesh = nb.DeviceMesh("sh", (2,), ("x",))
+    a = np.arange(12, dtype=np.float32).reshape(4, 3)
+    want = nb.ShardingSpec(mesh, [nb.DimSpec(["x"]), nb.DimSpec([])])
+    (xs,) = spmd.reshard_inputs((nb.Tensor.from_dlpack(a),), [want], mesh)
+    assert xs.sharding == want
+    parts = spmd.execute_on_shards(lambda t, k: t * k, (xs,), {"k": 2.0}, mesh)
+    assert [tuple(p.shape) for p in parts] == [(2, 3), (2, 3)]
+    y = spmd.create_sharded_output(parts, want)
+    np.testing.assert_allclose(y.to_numpy(), 2 * a)
+    assert tuple(spmd.get_shard_args((xs, 3), 1)[0].shape) == (2, 3) and spmd.get_shard_args((xs, 3), 1)[1] == 3
+
+    assert split_aux((1, 2), True, "f") == (1, 2) and split_aux(5, False, "f") == (5, None)
+    with pytest.raises(ValueError):
+        split_aux(5, True, "f")
+    assert resolve_argnums(None, 3) == (0, 1, 2) and resolve_argnums(-1, 3) == (2,) and resolve_argnums([0, 2], 3) == (0, 2)
+    with pytest.raises(ValueError):
+        resolve_argnums(3, 3)
+    t1, t2 = nb.Tensor.from_dlpack(a), nb.Tensor.from_dlpack(a)
+    got = collect_grads({t1: t2}, [t1, t2, 4.0])
+    assert got[0] is t2 and got[2] is None and float(got[1].to_numpy().sum()) == 0.0
+    lazy = t1 + 1.0
+    realize_tensors([lazy, 3])
+    assert lazy.is_realized
+    diff, part = create_jacobian_helpers(lambda u, v, w: (u, v, w), (0, 2), (1, 2, 3))
+    assert diff == (1, 3) and part(10, 30) == (10, 2, 30)
+
+    with cfg.eager_max_graph_context(True), cfg.verify_eager_shapes_context(True):
+        assert cfg.EAGER_MAX_GRAPH and cfg.VERIFY_EAGER_SHAPES
+    assert not cfg.EAGER_MAX_GRAPH
+    with contextvar_context(cfg._TRACING, True):
+        assert cfg.TRACING
+    assert is_tensor_value(torch.ones(1)) and not is_tensor_value(t1)
+    assert driver_tensor_type(torch.ones(2, 3))[0] == (2, 3)
+    assert GraphPrinter.__name__ == "GraphPrinter"
+    assert len(check_sub_axes_maximality(["x:(1)2", "x:(2)2", "y"])) == 1 and not check_sub_axes_maximality(["x", "y"])
+
+
+def test_json_auto_sharding_solver_picks_data_or_model_parallel_and_keeps_fixed_layouts():
+    """reference: nabla/core/sharding/optimizer/auto_sharding.py:19-330 (same JSON in, same JSON out)."""
+    import json
+
+    from nabla_b200.core.sharding.optimizer.auto_sharding import AutoSharding, graph_to_json
+    from nabla_b200.core.sharding.propagation import OpShardingRuleTemplate, propagate_sharding
+
+    z = lambda *s: nb.Tensor.from_dlpack(np.zeros(s, np.float32))      # noqa: E731
+    g = graph_to_json(lambda x, a, b: nb.relu(x @ a) @ b, (z(64, 32), z(32, 128), z(128, 16)))
+    names = [n["op_name"] for n in json.loads(g)["nodes"]]
+    assert names == ["matmul", "relu", "matmul"]
+    solver = AutoSharding((4,), ("d",))
+    sol = solver.solve(g)
+    assert solver.seeds["0"]["strategy"] == "dp"
+    for node in sol["nodes"].values():                     # rows split everywhere, weights whole
+        assert node["outputs"]["0"]["dims"] == [["d"], None]
+    assert sol["nodes"]["2"]["inputs"]["1"]["dims"] == [None, None]
+    sol = solver.solve(graph_to_json(lambda x, w: nb.exp(x @ w), (z(2, 4096), z(4096, 8))))
+    assert solver.seeds["0"]["strategy"] == "mp"           # 2 rows cannot be split over 4 devices
+    assert sol["nodes"]["0"]["inputs"]["0"]["dims"] == [None, ["d"]] and sol["nodes"]["0"]["inputs"]["1"]["dims"] == [["d"], None]
+    fixed = {"tensors": [{"id": 0, "shape": [64, 32], "fixed_sharding": {"dims": [None, "d"], "replicated": []}},
+                         {"id": 1, "shape": [32, 8], "fixed_sharding": None}, {"id": 2, "shape": [64, 8], "fixed_sharding": None}],
+             "nodes": [{"id": 0, "op_name": "matmul", "inputs": [0, 1], "outputs": [2],
+                        "sharding_rule": {"equation": "m k, k n -> m n", "factor_sizes": {"m": 64, "k": 32, "n": 8}},
+                        "compute_stats": {"flops": 2.0 * 64 * 32 * 8}}]}
+    sol = solver.solve(json.dumps(fixed))
+    assert sol["nodes"]["0"]["inputs"]["0"]["dims"] == [None, ["d"]] and sol["nodes"]["0"]["inputs"]["1"]["dims"] == [["d"], None]
+
+    mesh = nb.DeviceMesh("pr", (4,), ("d",))
+    mk = lambda r: nb.ShardingSpec(mesh, [nb.DimSpec([], is_open=True) for _ in range(r)])      # noqa: E731
+    a, b, c = mk(2), mk(2), mk(2)
+    c.dim_specs[1] = nb.DimSpec(["d"], is_open=False)      # a fact on the output flows back to the weight
+    rule = OpShardingRuleTemplate.parse("m k, k n -> m n").instantiate([(8, 16), (16, 32)], [(8, 32)])
+    assert propagate_sharding(rule, [a, b], [c]) and b.dim_specs[1].axes == ["d"] and not a.dim_specs[0].axes
+    assert not propagate_sharding(rule, [a, b], [c])
+
+
+def test_op_call_stage_helpers_and_op_class_names():
+    """reference: nabla/ops/utils.py:410-762 and the op classes its modules export."""
+    import nabla_b200.config as cfg
+    from nabla_b200.ops import utils as U
+    from nabla_b200.ops.binary import MatmulOp
+    from nabla_b200.ops.comparison import ComparisonOp, ComparisonUnaryOp, EqualOp, LogicalNotOp, LogicalXorOp
+    from nabla_b200.ops.control_flow import ScanOp, WhileLoopOp
+    from nabla_b200.ops.convolution import Conv2DOp, Conv2DTransposeOp
+    from nabla_b200.ops.creation import ConstantOp, OnesOp, TriOp, TrilOp, ZerosOp
+    from nabla_b200.ops.multi_output import ChunkOp, SplitOp
+    from nabla_b200.ops.reduction import PhysicalReduceOp, ReduceSumPhysicalOp
+    from nabla_b200.ops.unary import ExpOp, IsNanOp, ReluOp, UnaryOperation
+
+    a = nb.Tensor.from_dlpack(np.ones((4, 3), np.float32))
+    assert U.collect_metadata((a, 2)) == (0, False, False, False)
+    seen = {}
+    nb.vmap(lambda r: seen.setdefault("m", U.collect_metadata((r,))) and r)(a)
+    assert seen["m"][0] == 1
+    k1 = U.compute_structural_hash("add", (a, a), {"axis": 0})
+    assert k1 == U.compute_structural_hash("add", (a * 2.0, a), {"axis": 0}) and k1 != U.compute_structural_hash("add", (a, a), {"axis": 1})
+    mesh = nb.DeviceMesh("st", (2,), ("x",))
+    y = nb.shard(a, mesh, (None, "x")) @ nb.shard(nb.Tensor.from_dlpack(np.ones((3, 2), np.float32)), mesh, ("x", None))
+    assert y.sharding.partial_sum_axes == {"x"}
+    r = U.apply_auto_reduction(MatmulOp(), y, mesh, {"x"})
+    assert not r.sharding.partial_sum_axes
+    np.testing.assert_allclose(r.to_numpy(), np.full((4, 2), 3.0))
+    assert U.apply_auto_reduction(MatmulOp(), y, mesh, set()) is y
+    with cfg.verify_eager_shapes_context(True):
+        U.verify_eager_shapes("op", [[torch.ones(2, 3)]], [[(2, 3)]])
+        with pytest.raises(RuntimeError):
+            U.verify_eager_shapes("op", [[torch.ones(2, 3)]], [[(2, 4)]])
+    assert tuple(U.ensure_tensor(3.0).shape) == ()
+
+    assert issubclass(ExpOp, UnaryOperation) and ExpOp is not ReluOp and IsNanOp().name == "is_nan"
+    assert issubclass(EqualOp, ComparisonOp) and issubclass(LogicalXorOp, ComparisonOp) and issubclass(LogicalNotOp, ComparisonUnaryOp)
+    assert issubclass(TrilOp, TriOp) and issubclass(ChunkOp, SplitOp) and issubclass(ReduceSumPhysicalOp, PhysicalReduceOp)
+    assert Conv2DOp().name == "conv2d" and Conv2DTransposeOp().name == "conv2d_transpose" and WhileLoopOp is not None
+    np.testing.assert_allclose(ZerosOp()(shape=(2,), dtype=nb.DType.float32, device=nb.CPU()).to_numpy(), [0.0, 0.0])
+    np.testing.assert_allclose(OnesOp()(shape=(2,), dtype=nb.DType.float32, device=nb.CPU()).to_numpy(), [1.0, 1.0])
+    np.testing.assert_allclose(ConstantOp()([1.0, 2.0]).to_numpy(), [1.0, 2.0])
+    carry, ys = ScanOp()(lambda c, v: (c + v, c), nb.Tensor.from_dlpack(np.zeros(3, np.float32)), a)
+    np.testing.assert_allclose(carry.to_numpy(), [4.0, 4.0, 4.0])
+    from nabla_b200.nn.modules.linear import Linear
+    from nabla_b200.nn.modules.transformer import TransformerDecoderLayer
+
+    assert Linear is nb.nn.Linear and TransformerDecoderLayer is nb.nn.TransformerDecoderLayer

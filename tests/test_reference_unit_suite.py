@@ -75,3 +75,45 @@ def test_reference_unit_suite_passes_against_this_package(tmp_path):
     unexpected = sorted(bad - EXPECTED_DIFFERENCES)
     assert not unexpected, "reference tests that fail against this package:\n" + "\n".join(unexpected) + "\n" + out[-3000:]
     assert passed >= 1000, f"only {passed} reference tests passed:\n{out[-3000:]}"
+
+
+# stages of the reference's `Operation.__call__` that only make sense around a MAX graph under
+# construction (attaching tangents to graph values, eager MAX execution, wrapping MAX values into
+# tensors, checking MAX value types); the op call of this package has no such steps
+NO_COUNTERPART = {"nabla_b200.ops.utils": {"adapt_and_reshard", "apply_jvp", "eager_execute", "package_outputs",
+                                           "validate_physical_metadata"}}
+
+
+def test_every_public_name_of_the_reference_package_exists_here():
+    """Module by module: each public function, class and ``__all__`` entry of ``nabla/**.py`` is an
+    attribute of the module of the same path under ``nabla_b200``."""
+    import ast
+    import importlib
+
+    root = os.path.join(REF, "nabla")
+    problems = []
+    for dirpath, _, files in os.walk(root):
+        for f in files:
+            if not f.endswith(".py"):
+                continue
+            path = os.path.join(dirpath, f)
+            rel = os.path.relpath(path, root)[:-3].replace(os.sep, ".")
+            if rel.endswith("__init__"):
+                rel = rel[:-len("__init__")].rstrip(".")
+            name = "nabla_b200" + ("." + rel if rel else "")
+            try:
+                mod = importlib.import_module(name)
+            except Exception as e:
+                problems.append(f"{name}: cannot import ({e})")
+                continue
+            wanted = set()
+            for node in ast.parse(open(path).read()).body:
+                if isinstance(node, (ast.FunctionDef, ast.AsyncFunctionDef, ast.ClassDef)) and not node.name.startswith("_"):
+                    wanted.add(node.name)
+                elif isinstance(node, ast.Assign) and isinstance(node.value, (ast.List, ast.Tuple)):
+                    if any(isinstance(t, ast.Name) and t.id == "__all__" for t in node.targets):
+                        wanted |= {e.value for e in node.value.elts if isinstance(e, ast.Constant)}
+            missing = sorted(n for n in wanted if not hasattr(mod, n) and n not in NO_COUNTERPART.get(name, ()))
+            if missing:
+                problems.append(f"{name}: {missing}")
+    assert not problems, "\n".join(problems)
