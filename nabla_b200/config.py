@@ -48,16 +48,16 @@ def get_flag(name: str) -> bool:
     return _FLAGS[name].get()
 
 
-def set_eager_max_graph(v: bool) -> None:
-    _EAGER.set(bool(v))
+def set_eager_max_graph(value: bool) -> None:
+    _EAGER.set(bool(value))
 
 
-def set_verify_eager_shapes(v: bool) -> None:
-    _VERIFY.set(bool(v))
+def set_verify_eager_shapes(value: bool) -> None:
+    _VERIFY.set(bool(value))
 
 
-def set_tracing(v: bool) -> None:
-    _TRACING.set(bool(v))
+def set_tracing(value: bool) -> None:
+    _TRACING.set(bool(value))
 
 
 @contextlib.contextmanager
@@ -77,8 +77,8 @@ def verify_eager_shapes(v: bool = True):
     return _scoped(_VERIFY, v)
 
 
-def tracing(v: bool = True):
-    return _scoped(_TRACING, v)
+def tracing(value: bool = True):
+    return _scoped(_TRACING, value)
 
 
 def capturable_trace(v: bool = True):

@@ -30,6 +30,14 @@ class OpShardingRule:
                 out.update(fs)
         return out
 
+    def get_factor_tensors(self, factor_name: str) -> list[tuple[str, int, int]]:
+        """Where a factor appears: ``("input" | "output", operand index, dim index)`` triples."""
+        out = []
+        for kind, maps in (("input", self.input_mappings), ("output", self.output_mappings)):
+            for t, m in enumerate(maps):
+                out += [(kind, t, d) for d, fs in m.items() if factor_name in fs]
+        return out
+
     def get_contracting_factors(self) -> set[str]:
         ins: set[str] = set()
         outs: set[str] = set()

@@ -177,20 +177,21 @@ def reshard_inputs(args, required_specs, mesh: DeviceMesh | None):
     return pytree.tree_unflatten(td, out)
 
 
-def get_shard_args(args, shard_idx: int, per_input_shardings=None, *_unused):
+def get_shard_args(args, shard_idx: int, per_input_shardings=None, g=None, Tensor=None, pytree=None):
     """``args`` with every tensor replaced by its buffer on local shard ``shard_idx`` (a tensor
     that is not on a mesh gives its single buffer to every shard)."""
-    from ..tensor.api import Tensor
+    from ..common import pytree as _pt          # (`g`, `Tensor`, `pytree` are the reference's extra parameters: unused)
+    from ..tensor.api import Tensor as _T
 
     def pick(x):
-        if not isinstance(x, Tensor):
+        if not isinstance(x, _T):
             return x
         x.realize()
         bufs = x._impl._buffers
         return bufs[shard_idx] if len(bufs) > 1 else bufs[0]
 
-    leaves, td = pytree.tree_flatten(args)
-    return pytree.tree_unflatten(td, [pick(x) for x in leaves])
+    leaves, td = _pt.tree_flatten(args)
+    return _pt.tree_unflatten(td, [pick(x) for x in leaves])
 
 
 def execute_on_shards(op_fn: Callable, args, kwargs: dict, mesh: DeviceMesh | None, input_shardings=None, op=None) -> list:

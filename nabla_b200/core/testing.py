@@ -26,11 +26,15 @@ def _to_numpy(x: Any) -> np.ndarray:
     return np.asarray(x)
 
 
-def assert_allclose(actual: Any, expected: Any, rtol: float = 1e-5, atol: float = 1e-6, err_msg: str = "") -> None:
+def assert_allclose(actual: Any, expected: Any, rtol: float = 1e-5, atol: float = 1e-6, err_msg: str = "", *,
+                    equal_nan: bool = False, realize: bool = True) -> None:
+    """Leaf-by-leaf numerical comparison of two pytrees of tensors / arrays. ``realize=False`` skips
+    the batched evaluation for callers that already did it (reference: nabla/core/testing.py:59-82)."""
     la = pytree.tree_leaves(actual)
     le = pytree.tree_leaves(expected)
     if len(la) != len(le):
         raise AssertionError(f"pytree leaf count differs: {len(la)} vs {len(le)} {err_msg}")
-    batch_realize(actual, expected)
+    if realize:
+        batch_realize(actual, expected)
     for a, e in zip(la, le):
-        np.testing.assert_allclose(_to_numpy(a), _to_numpy(e), rtol=rtol, atol=atol, err_msg=err_msg)
+        np.testing.assert_allclose(_to_numpy(a), _to_numpy(e), rtol=rtol, atol=atol, err_msg=err_msg, equal_nan=equal_nan)

@@ -219,6 +219,24 @@ class Operation:
     def meta_kwargs(self, kwargs: dict) -> dict:
         return kwargs
 
+    def infer_output_shape(self, input_shapes, **kwargs):
+        """Output shape(s) for operands of the given PHYSICAL shapes, found by running the kernel
+        on storage-less tensors: a tuple for one output, a list of tuples for several. ``dtype=``
+        picks the operands' dtype (float32 by default)."""
+        dt = kwargs.pop("dtype", torch.float32)
+        metas = [torch.empty(tuple(int(d) for d in s), dtype=dt, device="meta") for s in input_shapes]
+        out = self.kernel(*metas, **self.meta_kwargs(kwargs))
+        leaves = [o for o in pytree.tree_leaves(out) if isinstance(o, torch.Tensor)]
+        shapes = [tuple(int(d) for d in o.shape) for o in leaves]
+        return shapes[0] if len(shapes) == 1 else shapes
+
+    def infer_sharding_spec(self, args, mesh, kwargs=None):
+        """``(output spec, input specs as the op wants them, mesh axes whose pending sums must be
+        reduced first)`` from the operands' layouts alone; nothing is moved."""
+        from ..core.sharding import spmd
+
+        return spmd.infer_output_sharding(self, args, mesh, kwargs)
+
     def output_device(self, tensors: list[Tensor], kwargs: dict) -> Device:
         if tensors:
             return tensors[0]._impl.device

@@ -119,10 +119,10 @@ def collect_metadata(args: Any) -> tuple[int, bool, bool, bool]:
     return depth, traced, sharded, tangent
 
 
-def compute_structural_hash(op_name: str, args: Any, kwargs: dict | None) -> tuple:
+def compute_structural_hash(op_name: str, resharded_args: Any, adapted_kwargs: dict | None) -> tuple:
     """Key of an op call that ignores values: the op, the structure of every argument and kwarg."""
-    return (op_name, tuple(_make_hashable(a) for a in args),
-            tuple(sorted(((k, _make_hashable(v)) for k, v in (kwargs or {}).items()), key=lambda kv: str(kv[0]))))
+    return (op_name, tuple(_make_hashable(a) for a in resharded_args),
+            tuple(sorted(((k, _make_hashable(v)) for k, v in (adapted_kwargs or {}).items()), key=lambda kv: str(kv[0]))))
 
 
 def apply_auto_reduction(op: Any, output: Any, mesh: Any, reduce_axes: Any) -> Any:

@@ -29,7 +29,7 @@ def zeros_for_missing(arg, grad):
     return pytree.tree_unflatten(td, [f(a, g) for a, g in zip(leaves_a, leaves_g)])
 
 
-def std_basis(x):
+def std_basis(flat_tensors):
     """One-hot basis of a tensor: shape ``(numel, *x.shape)``. Given a LIST of tensors it follows the
     reference's convention (nabla/transforms/utils.py:130-156): ``(sizes, basis)`` where the basis of
     every tensor spans the joint index space of all of them, shape ``(total, *t.shape)``."""
@@ -37,6 +37,7 @@ def std_basis(x):
 
     from ..ops.creation import constant
 
+    x = flat_tensors
     if isinstance(x, (list, tuple)):
         sizes = []
         for t in x:

@@ -531,3 +531,25 @@ def test_op_call_stage_helpers_and_op_class_names():
     from nabla_b200.nn.modules.transformer import TransformerDecoderLayer
 
     assert Linear is nb.nn.Linear and TransformerDecoderLayer is nb.nn.TransformerDecoderLayer
+
+
+def test_shape_and_layout_inference_entry_points_of_ops():
+    """reference: per-op `infer_output_shape` / `infer_sharding_spec`, `OpShardingRule.get_factor_tensors`
+    (nabla/ops/base.py, nabla/core/sharding/propagation.py:57-67)."""
+    from nabla_b200.core.sharding.propagation import OpShardingRuleTemplate
+    from nabla_b200.ops.binary import MatmulOp, OuterOp
+    from nabla_b200.ops.multi_output import SplitOp
+    from nabla_b200.ops.view.axes import SwapAxesOp
+
+    assert OuterOp().infer_output_shape([(3,), (4,)]) == (3, 4)
+    assert MatmulOp().infer_output_shape([(2, 3, 4), (4, 5)]) == (2, 3, 5)
+    assert SwapAxesOp().infer_output_shape([(2, 3, 4)], axis1=0, axis2=2) == (4, 3, 2)
+    assert SplitOp().infer_output_shape([(6, 2)], sizes=(4, 2), axis=0) == [(4, 2), (2, 2)]
+    rule = OpShardingRuleTemplate.parse("m k, k n -> m n").instantiate([(2, 3), (3, 4)])
+    assert rule.get_factor_tensors("k") == [("input", 0, 1), ("input", 1, 0)]
+    assert rule.get_factor_tensors("m") == [("input", 0, 0), ("output", 0, 0)]
+    mesh = nb.DeviceMesh("inf", (2,), ("x",))
+    x = nb.shard(nb.Tensor.from_dlpack(np.ones((4, 6), np.float32)), mesh, (None, "x"))
+    w = nb.shard(nb.Tensor.from_dlpack(np.ones((6, 2), np.float32)), mesh, ("x", None))
+    out, ins, pre = MatmulOp().infer_sharding_spec((x, w), mesh, {})
+    assert out.partial_sum_axes == {"x"} and len(ins) == 2 and not pre
