@@ -42,7 +42,7 @@ def prepare(op, args: tuple, kwargs: dict, mesh: DeviceMesh):
     ``ShardingSpec`` per output."""
     from ..tensor.api import Tensor
 
-    custom = getattr(op, "infer_sharding_spec", None)
+    custom = getattr(op, "plan_layouts", None)       # ops that lay their output out themselves (collectives)
     if custom is not None:
         return custom(args, mesh, kwargs)
 

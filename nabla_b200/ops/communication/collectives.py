@@ -57,10 +57,17 @@ class _LayoutOp(CollectiveOperation):
     def out_spec(self, x: Tensor, mesh: DeviceMesh, kwargs: dict) -> ShardingSpec:
         raise NotImplementedError
 
-    def infer_sharding_spec(self, args, mesh, kwargs):
+    def plan_layouts(self, args, mesh, kwargs):
+        """Hook of `spmd.prepare`: ``(operands as they are, output specs, nothing to reduce first)``."""
         x = args[0]
         spec = self.out_spec(x, mesh, kwargs)
         return args, (lambda shapes: [spec for _ in shapes]), set()
+
+    def infer_sharding_spec(self, args, mesh, kwargs=None):
+        """``(output spec, the operands' specs, no pre-reduction)``: a collective decides its own output
+        layout (reference: nabla/ops/communication/base.py:124-160)."""
+        x = args[0]
+        return self.out_spec(x, mesh, kwargs or {}), [t._impl.sharding for t in args if isinstance(t, Tensor)], set()
 
     def _mesh(self, node) -> DeviceMesh:
         m = node.kwargs.get("mesh")
