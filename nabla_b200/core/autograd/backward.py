@@ -199,7 +199,7 @@ def _unflatten_with_none(td, cots):
     return rec(td)
 
 
-def backward_on_trace(trace: Trace, cotangents: Any, *, create_graph: bool = False, checkpoint_policy=None
+def backward_on_trace(trace: Trace, cotangents: Any, *, create_graph: bool = False, checkpoint_policy: str = "none"
                       ) -> dict[Tensor, Tensor]:
     """Run the VJP of ``trace``. Returns ``{input Tensor: gradient}`` for the trace inputs.
     ``checkpoint_policy`` is accepted for signature compatibility (no rematerialisation)."""

@@ -117,12 +117,13 @@ _GRAPH_EPOCH: ContextVar[int] = ContextVar("nabla_graph_epoch", default=0)
 class ComputeGraph:
     """Owner of evaluation state: epoch counter and RNG (seed, counter)."""
 
-    def __init__(self) -> None:
+    def __init__(self, context=None, seed: int = 0) -> None:
+        # (`context` is the reference's MLIR context: there is none here, the argument is accepted and unused)
         # a fresh graph starts a new epoch of its context (the reference's constructor does the same,
         # nabla/core/graph/engine.py), so `epoch` is positive from the start
         self.epoch = _GRAPH_EPOCH.get() + 1
         _GRAPH_EPOCH.set(self.epoch)
-        self.seed = 0
+        self.seed = int(seed)
         self.rng_counter = 0
         self.seed_epoch = 0          # bumped by set_seed: device-resident stream states re-read (seed, counter)
         # attributes of the reference's graph object (nabla/core/graph/engine.py). There `graph` is the
@@ -145,7 +146,8 @@ class ComputeGraph:
         return self.seed, c
 
     # ---- evaluation
-    def evaluate(self, *tensors, return_model: bool = False) -> None:
+    def evaluate(self, tensor=None, *extra_outputs, return_model: bool = False) -> None:
+        tensors = (() if tensor is None else (tensor,)) + tuple(extra_outputs)
         targets: list[TensorImpl] = []
         seen: set[int] = set()
         for t in tensors:

@@ -96,11 +96,11 @@ class OpShardingRuleTemplate:
         return ", ".join(one(t) for t in self.inputs) + " -> " + ", ".join(one(t) for t in self.outputs)
 
     @staticmethod
-    def parse(notation: str, input_shapes: Sequence[Sequence[int]] | None = None) -> "OpShardingRuleTemplate":
+    def parse(equation: str, input_shapes: Sequence[Sequence[int]] | None = None) -> "OpShardingRuleTemplate":
         """Template from einsum-like notation. With ``input_shapes`` every ``...`` is expanded at
         once to the batch factors those shapes imply, as the reference's two-argument form does
         (nabla/core/sharding/propagation.py:161-200)."""
-        tpl = OpShardingRuleTemplate._parse(notation)
+        tpl = OpShardingRuleTemplate._parse(equation)
         if input_shapes is None:
             return tpl
         rule = tpl.instantiate(input_shapes)

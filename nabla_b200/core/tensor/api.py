@@ -23,8 +23,10 @@ class Tensor:
     __slots__ = ("_impl", "__weakref__")
     __array_priority__ = 1000
 
-    def __init__(self, *, buffers=None, impl: TensorImpl | None = None, is_traced: bool = False):
+    def __init__(self, *, buffers=None, value=None, impl: TensorImpl | None = None, is_traced: bool = False):
         if impl is None:
+            if buffers is None:
+                buffers = value          # the reference's second spelling (a backend value; here a device buffer)
             if buffers is None:
                 raise ValueError("Tensor needs `buffers` or `impl`")
             impl = TensorImpl(buffers, is_traced=is_traced)

@@ -29,12 +29,14 @@ class TensorImpl:
 
     def __init__(self, buffers: list[torch.Tensor] | torch.Tensor | None = None, *, shape=None, dtype: DType | None = None,
                  device: Device | None = None, sharding: "ShardingSpec | None" = None, batch_dims: int = 0,
-                 is_traced: bool = False):
+                 is_traced: bool = False, bufferss=None, values=None, sharding_constraint=None):
+        if buffers is None:
+            buffers = bufferss if bufferss is not None else values      # the reference's keyword names
         if isinstance(buffers, torch.Tensor):
             buffers = [buffers]
         self._buffers = buffers
         self.sharding = sharding
-        self.sharding_constraint = None
+        self.sharding_constraint = sharding_constraint
         self.is_traced = is_traced
         self.requires_grad = False
         self.grad = None

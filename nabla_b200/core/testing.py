@@ -26,7 +26,7 @@ def _to_numpy(x: Any) -> np.ndarray:
     return np.asarray(x)
 
 
-def assert_allclose(actual: Any, expected: Any, rtol: float = 1e-5, atol: float = 1e-6, err_msg: str = "", *,
+def assert_allclose(actual: Any, expected: Any, rtol: float = 1e-5, atol: float = 1e-8, err_msg: str = "", *,
                     equal_nan: bool = False, realize: bool = True) -> None:
     """Leaf-by-leaf numerical comparison of two pytrees of tensors / arrays. ``realize=False`` skips
     the batched evaluation for callers that already did it (reference: nabla/core/testing.py:59-82)."""

@@ -153,9 +153,9 @@ def _call(x, kernel_size, stride, padding, dilation, mode):
     return _pool(x, kernel_size=k, stride=s, padding=p, mode=mode)
 
 
-def avg_pool2d(x, kernel_size, stride=None, padding=0, dilation=1) -> Tensor:
+def avg_pool2d(x, kernel_size, stride=None, padding=0, dilation=(1, 1)) -> Tensor:
     return _call(x, kernel_size, stride, padding, dilation, "avg")
 
 
-def max_pool2d(x, kernel_size, stride=None, padding=0, dilation=1) -> Tensor:
+def max_pool2d(x, kernel_size, stride=None, padding=0, dilation=(1, 1)) -> Tensor:
     return _call(x, kernel_size, stride, padding, dilation, "max")
