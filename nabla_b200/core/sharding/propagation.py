@@ -204,23 +204,36 @@ def elementwise_rule(input_shapes: Sequence[Sequence[int]], output_rank: int) ->
     return OpShardingRule(ins, [out_map])
 
 
-def infer_from_rule(rule: OpShardingRule, input_specs: Sequence[ShardingSpec | None], mesh: DeviceMesh,
-                    output_index: int = 0) -> tuple[ShardingSpec, set[str]]:
-    """Output sharding and the set of mesh axes that became partial by contraction."""
+def _assign_factor_axes(rule: OpShardingRule, input_specs: Sequence[ShardingSpec | None]) -> dict[str, list[str]]:
+    """Mesh axes of every factor, read off the operands' layouts: the first operand dim that shards
+    a factor decides for it (a dim made of several factors gives its axes to the major one), and a
+    mesh axis goes to ONE factor only. Without the second rule ``x @ x.T`` with the rows of ``x``
+    split over an axis would ask for both output dims on that axis: the output can honour one, so
+    the other operand has to give the axis up (it is gathered) rather than keep a layout the
+    output does not describe."""
     factor_axes: dict[str, list[str]] = {}
+    taken: set[str] = set()
     for t_idx, spec in enumerate(input_specs):
         if spec is None or t_idx >= len(rule.input_mappings):
             continue
         for dim_idx, factors in rule.input_mappings[t_idx].items():
-            if dim_idx >= len(spec.dim_specs):
+            if dim_idx >= len(spec.dim_specs) or not factors:
                 continue
             axes = spec.dim_specs[dim_idx].axes
-            if not axes:
-                continue
-            # a dim made of several factors gives its axes to the first (major) factor
             f = factors[0]
-            if f not in factor_axes:
-                factor_axes[f] = list(axes)
+            if not axes or f in factor_axes:
+                continue
+            free = [a for a in axes if a not in taken]
+            if free:
+                factor_axes[f] = free
+                taken.update(free)
+    return factor_axes
+
+
+def infer_from_rule(rule: OpShardingRule, input_specs: Sequence[ShardingSpec | None], mesh: DeviceMesh,
+                    output_index: int = 0) -> tuple[ShardingSpec, set[str]]:
+    """Output sharding and the set of mesh axes that became partial by contraction."""
+    factor_axes = _assign_factor_axes(rule, input_specs)
     out_map = rule.output_mappings[output_index] if rule.output_mappings else {}
     # contraction is judged per output: a sharded input factor that this output does not carry
     # was summed away on the way to it (e.g. the row factors for LayerNorm's dgamma)
@@ -251,13 +264,7 @@ def required_input_specs(rule: OpShardingRule, input_specs: Sequence[ShardingSpe
     """Input layouts consistent with the factor assignment chosen by ``infer_from_rule``:
     every input dim takes the axes of its factor (first-wins), so operands that disagree are
     resharded to agree before the per-shard kernel runs."""
-    factor_axes: dict[str, list[str]] = {}
-    for t_idx, spec in enumerate(input_specs):
-        if spec is None or t_idx >= len(rule.input_mappings):
-            continue
-        for dim_idx, factors in rule.input_mappings[t_idx].items():
-            if dim_idx < len(spec.dim_specs) and spec.dim_specs[dim_idx].axes and factors[0] not in factor_axes:
-                factor_axes[factors[0]] = list(spec.dim_specs[dim_idx].axes)
+    factor_axes = _assign_factor_axes(rule, input_specs)
     out = []
     for t_idx, rank in enumerate(input_ranks):
         spec = input_specs[t_idx] if t_idx < len(input_specs) else None

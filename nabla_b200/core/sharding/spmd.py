@@ -60,6 +60,11 @@ def prepare(op, args: tuple, kwargs: dict, mesh: DeviceMesh):
     for s in specs:
         incoming |= s.partial_sum_axes
     keep = op.partial_passthrough_axes(specs, kwargs) & incoming if incoming else set()
+    # a mesh axis cannot both split a dim of this op and carry a pending sum through it: the sum over
+    # that axis is taken first (otherwise `(x @ w) @ v`, with the first product pending over "b" and
+    # `v` split over "b", would label the result as split over "b" and lose the sum)
+    splitting = {a for sp in specs for d in sp.dim_specs for a in d.axes}
+    keep -= splitting
     must_reduce = incoming - keep
     if must_reduce:
         from ...ops.communication import all_reduce
@@ -148,6 +153,7 @@ def infer_output_sharding(op, args, mesh, kwargs=None):
     for s in specs:
         incoming |= s.partial_sum_axes
     keep = op.partial_passthrough_axes(specs, kwargs) & incoming
+    keep -= {a for sp in specs for d in sp.dim_specs for a in d.axes}      # as in `prepare`
     out, contr = infer_from_rule(rule, specs, mesh)
     used = out.used_axes()
     out.partial_sum_axes = {a for a in (contr | keep) if a not in used}

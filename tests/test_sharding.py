@@ -209,3 +209,53 @@ def test_to_numpy_all_and_gather(mesh_2x4):
     np.testing.assert_allclose(a, x.numpy())
     np.testing.assert_allclose(b, 2 * x.numpy())
     assert "shard(0)" in repr(xs)
+
+
+def test_one_mesh_axis_serves_one_factor_of_an_op():
+    """``x @ x.T`` with the rows of ``x`` split over an axis: both output dims would want that axis.
+    The output keeps it on the rows, the transposed operand is gathered, and the values, later
+    reductions and gradients match the unsharded run."""
+    mesh = nb.DeviceMesh("cf", (2,), ("a",))
+    x = np.random.RandomState(0).randn(4, 8, 8).astype(np.float32)
+    ref = x @ x.transpose(0, 2, 1)
+    xs = nb.shard(nb.Tensor.from_dlpack(x), mesh, (None, "a", None))
+    t = xs @ nb.swap_axes(xs, -1, -2)
+    assert tuple(int(d) for d in t.shape) == (4, 8, 8)
+    assert [d.axes for d in t.sharding.dim_specs] == [[], ["a"], []]
+    np.testing.assert_allclose(t.to_numpy(), ref, rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(nb.reduce_max(nb.mean(t, axis=1), axis=0).to_numpy(), ref.mean(1).max(0), rtol=1e-5, atol=1e-5)
+
+    def f(u):
+        return nb.reduce_sum(nb.tanh(u @ nb.swap_axes(u, -1, -2)))
+
+    g_ref = nb.grad(f)(nb.Tensor.from_dlpack(x)).to_numpy()
+    np.testing.assert_allclose(nb.grad(f)(xs).to_numpy(), g_ref, rtol=1e-4, atol=1e-5)
+    mesh2 = nb.DeviceMesh("cf2", (2, 2), ("a", "b"))
+    y = np.random.RandomState(1).randn(8, 4).astype(np.float32)
+    a = nb.shard(nb.Tensor.from_dlpack(y), mesh2, ("a", None))
+    b = nb.shard(nb.Tensor.from_dlpack(y), mesh2, ("b", None))
+    s = nb.softmax(a, axis=1)
+    out = nb.broadcast_to(nb.unsqueeze(s, axis=0), (2, 8, 4))
+    out = out @ nb.swap_axes(out, -1, -2)
+    e = np.exp(y - y.max(1, keepdims=True))
+    sm = e / e.sum(1, keepdims=True)
+    np.testing.assert_allclose(out.to_numpy(), np.broadcast_to(sm @ sm.T, (2, 8, 8)), rtol=1e-5, atol=1e-6)
+    assert b.sharding is not None
+
+
+def test_a_pending_sum_is_taken_before_its_axis_splits_a_dim_of_the_next_op():
+    """``(a @ a.T) @ a`` with ``a`` split over "b" along its columns: the first product is pending
+    over "b", and the second one wants "b" for its output columns. The sum comes first."""
+    mesh = nb.DeviceMesh("ps", (2, 2), ("a", "b"))
+    rs = np.random.RandomState(0)
+    A, B = rs.randn(8, 4).astype(np.float32), rs.randn(8, 4).astype(np.float32)
+    a = nb.shard(nb.Tensor.from_dlpack(A), mesh, (None, "b"))
+    b = nb.shard(nb.Tensor.from_dlpack(B), mesh, ("b", "a"))
+    t1 = a @ nb.swap_axes(a, -1, -2)
+    assert t1.sharding.partial_sum_axes == {"b"}
+    for o, O in ((a, A), (b, B)):
+        t2 = t1 @ o
+        np.testing.assert_allclose(t2.to_numpy(), (A @ A.T) @ O, rtol=1e-4, atol=1e-4)
+    g = nb.grad(lambda u: nb.reduce_sum((u @ nb.swap_axes(u, -1, -2)) @ u))(a)
+    g_ref = nb.grad(lambda u: nb.reduce_sum((u @ nb.swap_axes(u, -1, -2)) @ u))(nb.Tensor.from_dlpack(A))
+    np.testing.assert_allclose(g.to_numpy(), g_ref.to_numpy(), rtol=1e-4, atol=1e-4)
