@@ -10,7 +10,7 @@ import torch
 
 from ..core.tensor.api import Tensor
 from ..types import DType
-from .base import AxisOp, ReduceOperation, ensure_tensor
+from .base import AxisOp, ReduceOperation, UnaryOperation, ensure_tensor
 
 
 def _empty_reduce(x, axis, keepdims, value):
@@ -228,6 +228,28 @@ def reduce_min(x, *, axis=None, keepdims: bool = False) -> Tensor:
     return _chain(_reduce_min, x, axis, keepdims)
 
 
+class DivideByCountOp(UnaryOperation):
+    """``x / count`` with ``count`` an INTEGER kwarg: the second half of a mean. Kept as an op of its
+    own, and not as a product with the float ``1.0 / count``, because ``compile(dynamic_dims=...)``
+    re-evaluates integers that follow a dynamic size and cannot do that for a float computed from
+    one: a mean over the batch stays on the path that never re-runs Python for a new batch size."""
+
+    partial_policy = "any"
+    _name = "divide_by_count"
+
+    def kernel(self, x, *, count: int):
+        return x / max(int(count), 1)
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        return (_div_count(cot, **kwargs),)
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        return _div_count(tangents[0], **kwargs)
+
+
+_div_count = DivideByCountOp()
+
+
 def mean(x, *, axis=None, keepdims: bool = False) -> Tensor:
     x = ensure_tensor(x)
     axes = _axes(x, axis)
@@ -235,7 +257,7 @@ def mean(x, *, axis=None, keepdims: bool = False) -> Tensor:
     for a in axes:
         n *= x._impl.global_shape[a]
     s = reduce_sum(x, axis=axis, keepdims=keepdims)
-    return s * (1.0 / max(n, 1))
+    return _div_count(s, count=int(n))
 
 
 class MeanOp(ReduceSumOp):
@@ -379,4 +401,4 @@ def reduce_min_physical(x, axis: int, keepdims: bool = False) -> Tensor:
 
 def mean_physical(x, axis: int, keepdims: bool = False) -> Tensor:
     n = x._impl._shape[axis]
-    return reduce_sum_physical(x, axis=axis, keepdims=keepdims) * (1.0 / max(n, 1))
+    return _div_count(reduce_sum_physical(x, axis=axis, keepdims=keepdims), count=int(n))

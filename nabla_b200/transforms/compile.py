@@ -93,6 +93,70 @@ class CompilationStats:
                 f"nodes={self.graph_nodes}, steps={self.graph_steps})")
 
 
+def _static_values_agree(base: "_Recorded", probe: "_Recorded") -> bool:
+    """Only INTEGERS may move with a dynamic size (they are re-evaluated affinely). A float, a string
+    or a constant tensor whose VALUE differs between the two recordings was computed from the size
+    in Python (``1.0 / n``, an index table built from ``n``): such a function is recorded per size."""
+    def same(a, b) -> bool:
+        if isinstance(a, TensorImpl) or isinstance(b, TensorImpl):
+            if not (isinstance(a, TensorImpl) and isinstance(b, TensorImpl)):
+                return False
+            if a is b or a._buffers is None or b._buffers is None or a.output_refs is not None or b.output_refs is not None:
+                return True                     # the same captured tensor, or a value computed inside the recording
+            if len(a._buffers) != len(b._buffers):
+                return False
+            if any(x.device.type == "meta" or y.device.type == "meta" for x, y in zip(a._buffers, b._buffers)):
+                return True                     # an input placeholder of the shape-only recording
+            return all(x.shape == y.shape and x.dtype == y.dtype and bool(torch.equal(x, y))
+                       for x, y in zip(a._buffers, b._buffers))
+        if isinstance(a, bool) or isinstance(a, (float, str)) or a is None:
+            return type(a) is type(b) and (a == b or (isinstance(a, float) and a != a and b != b))
+        if isinstance(a, (tuple, list)):
+            return isinstance(b, (tuple, list)) and len(a) == len(b) and all(same(x, y) for x, y in zip(a, b))
+        if isinstance(a, dict):
+            return isinstance(b, dict) and a.keys() == b.keys() and all(same(a[k], b[k]) for k in a)
+        return True                             # integers (handled affinely) and opaque objects
+
+    for n0, n1 in zip(base.nodes, probe.nodes):
+        if len(n0.arg_leaves) != len(n1.arg_leaves):
+            return False
+        if not all(same(a, b) for a, b in zip(n0.arg_leaves, n1.arg_leaves)) or not same(n0.kwargs, n1.kwargs):
+            return False
+    return True
+
+
+def _integers_on_a_line(base: "_Recorded", p2: "_Recorded", p3: "_Recorded", name: str) -> bool:
+    """Every integer argument (and output extent) of the three recordings moves linearly with the
+    size called ``name``: v3 - v0 == (v2 - v0) * (s3 - s0) / (s2 - s0)."""
+    s0, s2, s3 = base.sizes[name], p2.sizes[name], p3.sizes[name]
+
+    def ok(a, b, c) -> bool:
+        if isinstance(a, bool) or not isinstance(a, int):
+            if isinstance(a, (tuple, list)):
+                return isinstance(b, (tuple, list)) and isinstance(c, (tuple, list)) and len(a) == len(b) == len(c) \
+                    and all(ok(x, y, z) for x, y, z in zip(a, b, c))
+            if isinstance(a, dict):
+                return isinstance(b, dict) and isinstance(c, dict) and a.keys() == b.keys() == c.keys() \
+                    and all(ok(a[k], b[k], c[k]) for k in a)
+            return True
+        if not (isinstance(b, int) and isinstance(c, int)):
+            return False
+        return (c - a) * (s2 - s0) == (b - a) * (s3 - s0)
+
+    for n0, n2, n3 in zip(base.nodes, p2.nodes, p3.nodes):
+        if not (len(n0.arg_leaves) == len(n2.arg_leaves) == len(n3.arg_leaves)):
+            return False
+        if not all(ok(a, b, c) for a, b, c in zip(n0.arg_leaves, n2.arg_leaves, n3.arg_leaves)):
+            return False
+        if not ok(n0.kwargs, n2.kwargs, n3.kwargs):
+            return False
+        for o0, o2, o3 in zip(n0.outputs(), n2.outputs(), n3.outputs()):
+            if o0 is not None and not ok(tuple(o0._shape), tuple(o2._shape) if o2 is not None else None,
+                                         tuple(o3._shape) if o3 is not None else None):
+                return False
+    return True
+
+
 class _NotAffine(Exception):
     """A recorded integer does not follow an affine function of the named sizes."""
 
@@ -455,6 +519,13 @@ class CompiledFunction:
             for name in names:
                 other = self._record(leaves, td, scale={name: 2})
                 if len(other.nodes) != len(rec.nodes) or any(a.op is not b.op for a, b in zip(other.nodes, rec.nodes)):
+                    return False
+                if not _static_values_agree(rec, other):
+                    return False
+                # two recordings always lie on a line; a third one says whether the integers really do
+                third = self._record(leaves, td, scale={name: 3})
+                if len(third.nodes) != len(rec.nodes) or any(a.op is not b.op for a, b in zip(third.nodes, rec.nodes)) \
+                        or not _static_values_agree(rec, third) or not _integers_on_a_line(rec, other, third, name):
                     return False
                 probes[name] = other
         except Exception:

@@ -258,7 +258,7 @@ def test_dynamic_dims_serves_new_sizes_without_rerunning_python():
         z = np.concatenate([(x @ w).reshape(b * 2, 4), np.zeros((b, 4), np.float32)], 0)
         assert np.allclose(out.to_numpy(), np.maximum(z, 0).sum(0), atol=1e-4)
         assert np.allclose(head.to_numpy(), z[: b // 2], atol=1e-5)
-    assert calls["n"] == 2                      # the real trace and the shape-only probe
+    assert calls["n"] == 3                      # the real trace and two shape-only probes (2x and 3x the size)
     assert g.stats.retraces == 0 and g.stats.respecialisations == 3 and g.stats.misses == 1
 
 
@@ -270,3 +270,46 @@ def test_dynamic_dims_falls_back_when_a_size_is_not_affine():
         x = np.arange(n, dtype=np.float32)
         assert np.allclose(g(nb.constant(x)).to_numpy(), x[: n // 2] * 2)
     assert g.stats.respecialisations == 1 and g.stats.retraces == 1
+
+
+def test_dynamic_dims_records_per_size_when_a_value_is_computed_from_the_size_in_python():
+    """Only integers that move on a line with the size are re-evaluated. A float (``mean`` over the
+    dynamic axis scales by ``1.0 / n``), a constant tensor built from the size, or an integer that is
+    not linear in it (checked with a third, shape-only recording) make the function one that is
+    recorded per size: slower, never wrong."""
+    rng = np.random.default_rng(1)
+    g = nb.compile(lambda x: nb.reduce_sum(x * x, axis=0) * (1.0 / int(x.shape[0])), dynamic_dims={0: {0: "n"}})
+    for n in (4, 8, 6, 8):
+        x = rng.standard_normal((n, 3)).astype(np.float32)
+        assert np.allclose(g(nb.constant(x)).to_numpy(), (x * x).mean(0), atol=1e-5)
+    assert g.stats.respecialisations == 0 and g.stats.retraces == 2
+    # `mean` itself divides by an integer count, which follows the size: no second run of Python
+    g = nb.compile(nb.value_and_grad(lambda x: nb.mean(nb.reduce_sum(x * x, axis=1))), dynamic_dims={0: {0: "n"}})
+    for n in (4, 8, 6, 10):
+        x = rng.standard_normal((n, 3)).astype(np.float32)
+        v, gr = g(nb.constant(x))
+        assert np.allclose(v.to_numpy(), (x * x).sum(1).mean(), atol=1e-5) and np.allclose(gr.to_numpy(), 2 * x / n, atol=1e-5)
+    assert g.stats.respecialisations == 3 and g.stats.retraces == 0
+
+    def last_and_first(x):
+        n = int(x.shape[0])
+        return nb.gather(x, nb.constant(np.array([n - 1, 0], dtype=np.int32)), axis=0)
+
+    g = nb.compile(last_and_first, dynamic_dims={0: {0: "n"}})
+    for n in (4, 8, 5):
+        x = rng.standard_normal((n, 2)).astype(np.float32)
+        assert np.allclose(g(nb.constant(x)).to_numpy(), x[[n - 1, 0]])
+    assert g.stats.respecialisations == 0
+
+    g = nb.compile(lambda x: x[: (int(x.shape[0]) * int(x.shape[0])) // 8 + 1], dynamic_dims={0: {0: "n"}})
+    for n in (4, 8, 6):                                   # n*n // 8 + 1 = 3, 9 -> 8, 5: not a line
+        x = rng.standard_normal((n,)).astype(np.float32)
+        assert np.allclose(g(nb.constant(x)).to_numpy(), x[: n * n // 8 + 1])
+    assert g.stats.respecialisations == 0
+
+    g = nb.compile(lambda x, w: nb.reduce_sum(nb.relu(x @ w), axis=1), dynamic_dims={0: {0: "n"}})
+    w = rng.standard_normal((3, 5)).astype(np.float32)
+    for n in (4, 8, 6, 10):                               # the usual case still needs no second run of Python
+        x = rng.standard_normal((n, 3)).astype(np.float32)
+        assert np.allclose(g(nb.constant(x), nb.constant(w)).to_numpy(), np.maximum(x @ w, 0).sum(1), atol=1e-5)
+    assert g.stats.respecialisations == 3 and g.stats.retraces == 0
