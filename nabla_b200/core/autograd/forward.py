@@ -59,10 +59,15 @@ class ForwardEngine:
 
             tangents = tuple(tan_of(p) for p in primals)
             outputs = node.outputs_as_tensors()
+            # an op that is not differentiable returns None from its rule; one WITHOUT a rule raises,
+            # and that is passed on: a zero tangent here would be a silently wrong derivative
             try:
                 out_t = node.op.jvp_rule(primals, tangents, outputs, node.op_kwargs)
-            except NotImplementedError:
-                out_t = None
+            except NotImplementedError as e:
+                if not any(o is not None and o.dtype.is_float() for o in node.outputs()):
+                    out_t = None          # integer / bool outputs carry no tangent whatever the op
+                else:
+                    raise NotImplementedError(f"forward mode through '{node.op.name}': {e}") from e
             if out_t is None:
                 continue
             outs = node.outputs()

@@ -1,6 +1,7 @@
 """Control flow (reference: nabla/ops/control_flow.py:21-507): ``where`` (differentiable),
-``cond`` and ``while_loop`` (data-dependent, not differentiable, as in the reference), ``scan``
-(Python-unrolled, differentiable through its body).
+``cond`` and ``while_loop`` (data-dependent; the reference gives them no derivative, here reverse mode
+works through them both eagerly and when recorded by ``compile``), ``scan`` (Python-unrolled,
+differentiable through its body).
 
 Outside ``compile`` the predicate of ``cond`` / ``while_loop`` is read on the host and the chosen
 code runs right away. While ``compile`` traces, both become ONE recorded node (``CondOp`` /
@@ -120,13 +121,46 @@ class _HostControlOp(Operation):
         for i, t in enumerate(templates):
             im = t._impl
             impl = TensorImpl(None, shape=im._shape, dtype=im.dtype, device=im.device, sharding=im.sharding,
-                              batch_dims=im.batch_dims, is_traced=False)
+                              batch_dims=im.batch_dims, is_traced=any(t._impl.is_traced for t in inputs))
             impl.output_refs = node
             impl.output_index = i
             node.out_refs.append(weakref.ref(impl))
             outs.append(Tensor(impl=impl))
         _, node.out_treedef = pytree.tree_flatten(list(outs))
         return outs
+
+    def run(self, kw: dict, inputs: list[Tensor]) -> Any:
+        """The Python side of the node on concrete tensors (one per node input): what ``execute``
+        evaluates, and what the backward node differentiates."""
+        raise NotImplementedError
+
+    def closure_objects(self, kw: dict) -> list[Tensor]:
+        """The tensors the kept functions close over, in the order they were appended to the inputs."""
+        return []
+
+    def first_closure_input(self, kw: dict) -> int:
+        raise NotImplementedError
+
+    def vjp_rule(self, primals, cot, outputs, kwargs):
+        """Reverse mode through a recorded ``cond`` / ``while_loop``: one more host node. At replay it
+        runs the taken branch (or the loop) again on that call's data with autograd recording on,
+        pulls the cotangents back through what actually ran, and hands out the gradients of the
+        operands and of the tensors the functions close over."""
+        prim = list(primals)
+        cots = list(cot) if isinstance(cot, (list, tuple)) else [cot]
+        given = [(k, c) for k, c in enumerate(cots) if isinstance(c, Tensor)]     # outputs nobody used have none
+        diff = [i for i, p in enumerate(prim) if isinstance(p, Tensor) and p.dtype.is_float()
+                and not (type(self) is CondOp and i == 0)]
+        if not diff or not given:
+            return tuple(None for _ in prim)
+        kw = {"fwd": self, "fwd_kwargs": kwargs, "n_fwd": len(prim), "diff": tuple(diff),
+              "cot_positions": tuple(k for k, _ in given)}
+        grads = iter(_host_vjp_op.build([*prim, *[c for _, c in given]], [prim[i] for i in diff], kw))
+        return tuple(next(grads) if i in diff else None for i in range(len(prim)))
+
+    def jvp_rule(self, primals, tangents, outputs, kwargs):
+        raise NotImplementedError(f"forward mode through a '{self.name}' recorded by compile is not available: "
+                                  "use reverse mode (grad / vjp / jacrev), or differentiate outside compile")
 
     @staticmethod
     def _result_buffers(tree: Any, n_expected: int, what: str) -> list[list[torch.Tensor]]:
@@ -141,16 +175,21 @@ class CondOp(_HostControlOp):
     """inputs: [pred, *operand tensors, *closed-over tensors]; kwargs keep the two functions and the
     operand tree. Replays read ``pred`` and run the matching branch eagerly."""
 
-    def execute(self, node):
-        kw = node.kwargs
-        ins = node.input_impls()
-        n_op = kw["n_operands"]
-        it = iter(_fresh(i) for i in ins[1:1 + n_op])
+    def run(self, kw, inputs):
+        it = iter(inputs[1:1 + kw["n_operands"]])
         leaves = [next(it) if is_t else v for is_t, v in kw["operand_leaves"]]
         operands = pytree.tree_unflatten(kw["operand_treedef"], leaves)
+        return (kw["true_fn"] if _host_bool(inputs[0]) else kw["false_fn"])(*operands)
+
+    def closure_objects(self, kw):
+        return _closure_tensors(kw["true_fn"], kw["false_fn"])
+
+    def first_closure_input(self, kw):
+        return 1 + kw["n_operands"]
+
+    def execute(self, node):
         with config.tracing(False):
-            take = _host_bool(ins[0])
-            out = (kw["true_fn"] if take else kw["false_fn"])(*operands)
+            out = self.run(node.kwargs, [_fresh(i) for i in node.input_impls()])
             return self._result_buffers(out, len(node.out_refs), "cond branch")
 
 
@@ -158,18 +197,67 @@ class WhileOp(_HostControlOp):
     """inputs: [*loop-state tensors, *closed-over tensors]. Replays run ``cond_fn`` / ``body_fn``
     eagerly until the condition computed from that call's data turns false."""
 
-    def execute(self, node):
-        kw = node.kwargs
-        ins = node.input_impls()
-        n_st = kw["n_state"]
-        it = iter(_fresh(i) for i in ins[:n_st])
+    def run(self, kw, inputs, keep_graph: bool = False):
+        it = iter(inputs[:kw["n_state"]])
         state = tuple(pytree.tree_unflatten(kw["state_treedef"], [next(it) if is_t else v for is_t, v in kw["state_leaves"]]))
+        return _while_eager(kw["cond_fn"], kw["body_fn"], state, kw.get("max_iters"), realize=not keep_graph)
+
+    def closure_objects(self, kw):
+        return _closure_tensors(kw["cond_fn"], kw["body_fn"])
+
+    def first_closure_input(self, kw):
+        return kw["n_state"]
+
+    def execute(self, node):
         with config.tracing(False):
-            state = _while_eager(kw["cond_fn"], kw["body_fn"], state, kw.get("max_iters"))
+            state = self.run(node.kwargs, [_fresh(i) for i in node.input_impls()])
             return self._result_buffers(state, len(node.out_refs), "while_loop body")
 
 
-_cond_op, _while_op = CondOp(), WhileOp()
+class HostVjpOp(_HostControlOp):
+    """Backward of a recorded ``cond`` / ``while_loop``. inputs: [*inputs of the forward node,
+    *cotangents of its outputs]; outputs: one gradient per differentiable forward input."""
+
+    _name = "host_control_vjp"
+
+    def execute(self, node):
+        from ..core.autograd.backward import backward_on_trace
+        from ..core.graph.tracing import Trace
+        from .creation import zeros_like
+
+        kw = node.kwargs
+        fwd, fkw, n = kw["fwd"], kw["fwd_kwargs"], kw["n_fwd"]
+        ins = node.input_impls()
+        inputs = [_fresh(i) for i in ins[:n]]
+        given = dict(zip(kw["cot_positions"], (_fresh(i) for i in ins[n:])))
+        # the kept functions read the tensors they close over from the objects they captured, not
+        # from the node inputs: those objects stand in at their positions
+        first = fwd.first_closure_input(fkw)
+        captured = {id(t._impl): t for t in fwd.closure_objects(fkw)}
+        for j in range(first, n):
+            obj = captured.get(id(ins[j]))
+            if obj is not None:
+                inputs[j] = obj
+        wrt = [inputs[i] for i in kw["diff"]]
+        before = [t._impl.is_traced for t in wrt]
+        for t in wrt:
+            t._impl.is_traced = True
+        try:
+            with config.tracing(False):
+                out = fwd.run(fkw, inputs, keep_graph=True) if isinstance(fwd, WhileOp) else fwd.run(fkw, inputs)
+                leaves = [l for l in pytree.tree_leaves(out) if isinstance(l, Tensor)]
+                tr = Trace(tuple(wrt), leaves)
+                tr.compute()
+                gmap = backward_on_trace(tr, [given[k] if k in given else zeros_like(l) for k, l in enumerate(leaves)])
+                grads = [gmap[t] if t in gmap else zeros_like(t) for t in wrt]
+                realize_all(*grads)
+        finally:
+            for t, b in zip(wrt, before):
+                t._impl.is_traced = b
+        return [list(g._impl._buffers) for g in grads]
+
+
+_cond_op, _while_op, _host_vjp_op = CondOp(), WhileOp(), HostVjpOp()
 WhileLoopOp = WhileOp           # the reference's name (nabla/ops/control_flow.py:314)
 
 
@@ -200,6 +288,13 @@ def cond(pred, true_fn: Callable, false_fn: Callable, *operands: Any):
 
     Eagerly the predicate is read on the host (one device->host sync) and only the taken branch
     runs. Inside ``compile`` the choice is made again on every call (module docstring)."""
+    if isinstance(pred, Tensor) and pred._impl.batch_dims > 0:
+        # under vmap with a predicate per example: both branches run, `where` picks per example
+        t_leaves, out_td = pytree.tree_flatten(true_fn(*operands))
+        f_leaves, _ = pytree.tree_flatten(false_fn(*operands))
+        _same_structure(t_leaves, f_leaves, "cond")
+        return pytree.tree_unflatten(out_td, [where(pred, a, b) if isinstance(a, Tensor) else a
+                                              for a, b in zip(t_leaves, f_leaves)])
     if not (isinstance(pred, Tensor) and config.get_flag("TRACING")):
         return true_fn(*operands) if _host_bool(pred) else false_fn(*operands)
     # both branches are traced lazily to learn (and check) the output structure
@@ -252,12 +347,30 @@ def _apply_state(fn: Callable, state: tuple):
     return fn(state)
 
 
-def _while_eager(cond_fn: Callable, body_fn: Callable, state: tuple, max_iters: int | None = None) -> tuple:
+def _while_eager(cond_fn: Callable, body_fn: Callable, state: tuple, max_iters: int | None = None,
+                 realize: bool = True) -> tuple:
     n = 0
-    while _host_bool(_apply_state(cond_fn, state)):
-        new = _apply_state(body_fn, state)
-        state = tuple(new) if isinstance(new, (tuple, list)) else (new,)
-        realize_all(*pytree.tensor_leaves(state))
+    while True:
+        go = _apply_state(cond_fn, state)
+        if isinstance(go, Tensor) and go._impl.batch_dims > 0:
+            # under vmap with a condition per example: iterate while any example wants to, and let
+            # only those examples take the new state
+            go.realize()
+            if not any(bool(b.any().item()) for b in go._impl._buffers):
+                break
+            new = _apply_state(body_fn, state)
+            new = tuple(new) if isinstance(new, (tuple, list)) else (new,)
+            old_leaves, td = pytree.tree_flatten(state)
+            new_leaves, _ = pytree.tree_flatten(new)
+            state = tuple(pytree.tree_unflatten(td, [where(go, a, b) if isinstance(a, Tensor) else a
+                                                     for a, b in zip(new_leaves, old_leaves)]))
+        else:
+            if not _host_bool(go):
+                break
+            new = _apply_state(body_fn, state)
+            state = tuple(new) if isinstance(new, (tuple, list)) else (new,)
+        if realize:
+            realize_all(*pytree.tensor_leaves(state))
         n += 1
         if max_iters is not None and n >= max_iters:
             break

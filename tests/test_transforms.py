@@ -313,3 +313,64 @@ def test_dynamic_dims_records_per_size_when_a_value_is_computed_from_the_size_in
         x = rng.standard_normal((n, 3)).astype(np.float32)
         assert np.allclose(g(nb.constant(x), nb.constant(w)).to_numpy(), np.maximum(x @ w, 0).sum(1), atol=1e-5)
     assert g.stats.respecialisations == 3 and g.stats.retraces == 0
+
+
+def test_reverse_mode_through_cond_and_while_loop_recorded_by_compile():
+    """The recorded node of a ``cond`` / ``while_loop`` has a backward node: at replay it runs the
+    taken branch (the loop) of THAT call again with autograd on. Gradients follow the data of each
+    call, also for tensors the branch functions close over; forward mode says it is not available."""
+    w = nb.constant(np.array([0.5, -1.0], np.float32))
+    xs = nb.constant(np.ones((3, 2), np.float32))
+
+    def f_cond(c, xs):
+        p = nb.greater(nb.reduce_sum(c), 0.0)
+        r = nb.cond(p, lambda a, b: nb.tanh(a) * w + nb.reduce_sum(b, axis=0), lambda a, b: a * 2.0 + w, c, xs)
+        return nb.reduce_sum(r)
+
+    def f_while(c, xs):
+        i, a = nb.while_loop(lambda s: nb.less(s[0], nb.reduce_sum(nb.abs(c))), lambda s: (s[0] + 1.0, nb.tanh(s[1]) * w),
+                             (nb.constant(np.float32(0.0)), c))
+        return nb.reduce_sum(a)
+
+    for f in (f_cond, f_while):
+        g = nb.compile(nb.value_and_grad(f))
+        for vals in ([1.0, 2.0], [-3.0, 0.5], [0.2, 0.3], [1.0, 2.0]):
+            c = np.array(vals, np.float32)
+            v_ref, g_ref = nb.value_and_grad(f)(nb.constant(c), xs)
+            v, gr = g(nb.constant(c), xs)
+            assert np.allclose(v.to_numpy(), v_ref.to_numpy(), atol=1e-5) and np.allclose(gr.to_numpy(), g_ref.to_numpy(), atol=1e-5)
+        assert g.stats.misses == 1 and g.stats.hits == 3
+
+    def f_w(c, w2):
+        p = nb.greater(nb.reduce_sum(c), 0.0)
+        return nb.reduce_sum(nb.cond(p, lambda a: nb.tanh(a) * w2, lambda a: a * 2.0 + w2 * w2, c))
+
+    g = nb.compile(nb.grad(f_w, argnums=(0, 1)))
+    for vals in ([1.0, 2.0], [-3.0, 0.5]):
+        c = np.array(vals, np.float32)
+        for a, b in zip(g(nb.constant(c), w), nb.grad(f_w, argnums=(0, 1))(nb.constant(c), w)):
+            assert np.allclose(a.to_numpy(), b.to_numpy(), atol=1e-5)
+    with pytest.raises(NotImplementedError, match="forward mode"):
+        nb.compile(nb.jacfwd(f_cond, argnums=0))(nb.constant(np.array([1.0, 2.0], np.float32)), xs)
+
+
+def test_cond_and_while_loop_under_vmap_with_a_predicate_per_example():
+    """vmap over examples that take different branches / different numbers of iterations: ``cond``
+    evaluates both branches and selects, ``while_loop`` runs while any example wants to and freezes
+    the others; values and gradients equal the per-example runs."""
+    C = np.array([[0.5, 0.2], [-1.5, 1.0], [3.0, 0.4]], np.float32)
+
+    def f_cond(c):
+        p = nb.greater(nb.reduce_sum(c), 0.0)
+        return nb.reduce_sum(nb.cond(p, lambda a: nb.tanh(a) * 3.0, lambda a: a * a, c))
+
+    def f_while(c):
+        i, a = nb.while_loop(lambda s: nb.less(s[0], nb.reduce_sum(nb.abs(c))), lambda s: (s[0] + 1.0, nb.tanh(s[1]) + 0.1),
+                             (nb.constant(np.float32(0.0)), c))
+        return nb.reduce_sum(a)
+
+    for f in (f_cond, f_while):
+        ref = np.array([f(nb.constant(C[i])).to_numpy() for i in range(3)])
+        g_ref = np.stack([nb.grad(f)(nb.constant(C[i])).to_numpy() for i in range(3)])
+        assert np.allclose(nb.vmap(f)(nb.constant(C)).to_numpy(), ref, atol=1e-5)
+        assert np.allclose(nb.vmap(nb.grad(f))(nb.constant(C)).to_numpy(), g_ref, atol=1e-5)
