@@ -85,6 +85,13 @@ def prepare(op, args: tuple, kwargs: dict, mesh: DeviceMesh):
                 for s, sp in zip(shapes, specs)]
     else:
         want = required_input_specs(rule, specs, mesh, [len(s) for s in shapes])
+    # a dim of global extent 0 or 1 is never split (the output spec below drops such axes too): an
+    # operand that arrives with one (a (1, n) bias split along its first dim: one device holds the
+    # row, the others nothing) is gathered, so that operands and output label agree
+    for sp, shp in zip(want, shapes):
+        for d, ds in enumerate(sp.dim_specs):
+            if ds.axes and d < len(shp) and int(shp[d]) <= 1:
+                ds.axes = []
     from ...ops.communication import reshard_to_spec
 
     for j, t in enumerate(tensors):

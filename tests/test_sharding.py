@@ -259,3 +259,30 @@ def test_a_pending_sum_is_taken_before_its_axis_splits_a_dim_of_the_next_op():
     g = nb.grad(lambda u: nb.reduce_sum((u @ nb.swap_axes(u, -1, -2)) @ u))(a)
     g_ref = nb.grad(lambda u: nb.reduce_sum((u @ nb.swap_axes(u, -1, -2)) @ u))(nb.Tensor.from_dlpack(A))
     np.testing.assert_allclose(g.to_numpy(), g_ref.to_numpy(), rtol=1e-4, atol=1e-4)
+
+
+def test_an_operand_split_along_an_extent_one_dim_is_gathered_before_the_op():
+    """A (1, n) bias split over an axis along its first dim lives on one device only. Ops never keep
+    an axis on such a dim in their output label, so the operand is gathered first: a training step
+    with that layout matches the unsharded one."""
+    mesh = nb.DeviceMesh("e1", (2,), ("tp",))
+    bn = np.arange(16, dtype=np.float32).reshape(1, 16)
+    b = nb.shard(nb.Tensor.from_dlpack(bn), mesh, ("tp", None))
+    for t, ref in ((b * 0.9, bn * 0.9), (b + b, bn * 2), (nb.tanh(b), np.tanh(bn))):
+        t.realize()
+        assert [tuple(x.shape) for x in t._impl._buffers] == [(1, 16), (1, 16)]
+        assert not any(d.axes for d in t.sharding.dim_specs)
+        np.testing.assert_allclose(t.to_numpy(), ref, rtol=1e-6)
+    x = np.random.RandomState(0).randn(4, 4).astype(np.float32)
+    w = np.random.RandomState(1).randn(4, 16).astype(np.float32)
+
+    def loss(wt, bt):
+        d = nb.nn.functional.linear(nb.Tensor.from_dlpack(x), wt, bt)
+        return nb.mean(d * d)
+
+    g_ref = nb.grad(loss, argnums=(0, 1))(nb.Tensor.from_dlpack(w), nb.Tensor.from_dlpack(bn))
+    g_got = nb.grad(loss, argnums=(0, 1))(nb.shard(nb.Tensor.from_dlpack(w), mesh, (None, "tp")), b)
+    for a, r in zip(g_got, g_ref):
+        np.testing.assert_allclose(a.to_numpy(), r.to_numpy(), rtol=1e-5, atol=1e-6)
+    step = (b - g_got[1] * 0.1) * 0.9 + g_got[1]              # what an SGD-with-momentum update does
+    np.testing.assert_allclose(step.to_numpy(), (bn - g_ref[1].to_numpy() * 0.1) * 0.9 + g_ref[1].to_numpy(), rtol=1e-5)
