@@ -66,14 +66,6 @@ def prepare(op, args: tuple, kwargs: dict, mesh: DeviceMesh):
     splitting = {a for sp in specs for d in sp.dim_specs for a in d.axes}
     keep -= splitting
     must_reduce = incoming - keep
-    if must_reduce:
-        from ...ops.communication import all_reduce
-
-        for j, t in enumerate(tensors):
-            over = specs[j].partial_sum_axes & must_reduce
-            if over:
-                tensors[j] = all_reduce(t, reduce_axes=over)
-                specs[j] = tensors[j]._impl.sharding.clone()
 
     # (b) operand layouts that agree on every factor
     try:
@@ -85,6 +77,18 @@ def prepare(op, args: tuple, kwargs: dict, mesh: DeviceMesh):
                 for s, sp in zip(shapes, specs)]
     else:
         want = required_input_specs(rule, specs, mesh, [len(s) for s in shapes])
+    if must_reduce:
+        from ...ops.communication import all_reduce
+
+        for j, t in enumerate(tensors):
+            # a pending axis that this operand's own required layout puts on a dim is left to the
+            # re-layout below, which turns "sum, then split" into one reduce-scatter
+            over = (specs[j].partial_sum_axes & must_reduce) - want[j].used_axes()
+            if over:
+                tensors[j] = all_reduce(t, reduce_axes=over)
+                specs[j] = tensors[j]._impl.sharding.clone()
+        for sp in want:
+            sp.partial_sum_axes -= must_reduce
     # a dim of global extent 0 or 1 is never split (the output spec below drops such axes too): an
     # operand that arrives with one (a (1, n) bias split along its first dim: one device holds the
     # row, the others nothing) is gathered, so that operands and output label agree
@@ -96,7 +100,8 @@ def prepare(op, args: tuple, kwargs: dict, mesh: DeviceMesh):
 
     for j, t in enumerate(tensors):
         cur = specs[j]
-        if any(a.axes != b.axes for a, b in zip(cur.dim_specs, want[j].dim_specs)) or t._impl.sharding is None:
+        if any(a.axes != b.axes for a, b in zip(cur.dim_specs, want[j].dim_specs)) or t._impl.sharding is None \
+                or (cur.partial_sum_axes - want[j].partial_sum_axes):
             tensors[j] = reshard_to_spec(t, want[j])
             specs[j] = tensors[j]._impl.sharding.clone()
 

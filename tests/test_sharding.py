@@ -286,3 +286,22 @@ def test_an_operand_split_along_an_extent_one_dim_is_gathered_before_the_op():
         np.testing.assert_allclose(a.to_numpy(), r.to_numpy(), rtol=1e-5, atol=1e-6)
     step = (b - g_got[1] * 0.1) * 0.9 + g_got[1]              # what an SGD-with-momentum update does
     np.testing.assert_allclose(step.to_numpy(), (bn - g_ref[1].to_numpy() * 0.1) * 0.9 + g_ref[1].to_numpy(), rtol=1e-5)
+
+
+def test_pending_sum_meeting_a_sequence_parallel_residual_becomes_one_reduce_scatter():
+    """Row-parallel product (pending over "tp") + a residual split over "tp" along the rows: the sum
+    and the split are done by one reduce-scatter, not an all-reduce followed by a slice."""
+    from nabla_b200.core.graph.tracing import trace
+
+    mesh = nb.DeviceMesh("sp", (2,), ("tp",))
+    rs = np.random.RandomState(0)
+    X, W, R = rs.randn(8, 6).astype(np.float32), rs.randn(6, 4).astype(np.float32), rs.randn(8, 4).astype(np.float32)
+    x = nb.shard(nb.Tensor.from_dlpack(X), mesh, (None, "tp"))
+    w = nb.shard(nb.Tensor.from_dlpack(W), mesh, ("tp", None))
+    r = nb.shard(nb.Tensor.from_dlpack(R), mesh, ("tp", None))
+    f = lambda a, b, c: nb.tanh((a @ b) + c)      # noqa: E731
+    text = str(trace(f, x, w, r))
+    assert "reduce_scatter" in text and "all_reduce" not in text
+    out = f(x, w, r)
+    assert [d.axes for d in out.sharding.dim_specs] == [["tp"], []] and not out.sharding.partial_sum_axes
+    np.testing.assert_allclose(out.to_numpy(), np.tanh(X @ W + R), rtol=1e-5, atol=1e-6)
