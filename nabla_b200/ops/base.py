@@ -55,6 +55,8 @@ def ensure_tensor(x: Any, like: Tensor | None = None) -> Tensor:
             dtype = DType.float32
         if isinstance(x, bool):
             dtype = DType.bool if like.dtype is DType.bool else like.dtype
+        elif isinstance(x, int) and like.dtype is DType.bool:
+            dtype = DType.int32            # True + 2 is 3, not True (numpy's promotion of bool with an integer)
         return constant(x, dtype=dtype, device=like.device)
     return constant(x)
 

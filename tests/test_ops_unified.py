@@ -258,3 +258,14 @@ def test_binary_vmap_of_jvp_and_jacobians(name, fn, tfn):
     f = nb.jacfwd(fn, argnums=(0, 1))(T(a[0]), T(b[0]))
     for got_j, ref_j in ((r[0], ja), (r[1], jb), (f[0], ja), (f[1], jb)):
         close(got_j, ref_j, rtol=1e-4, atol=1e-4, msg=f"{name} jacobian")
+
+
+def test_python_scalars_promote_bool_and_integer_tensors_like_numpy():
+    a = nb.Tensor.from_torch(torch.tensor([True, False]))
+    assert (a + 2).to_torch().tolist() == [3, 2] and (a + 2).dtype is nb.DType.int32
+    assert (2 * a).to_torch().tolist() == [2, 0]
+    assert (a / 2).to_torch().tolist() == [0.5, 0.0]
+    assert (a + True).dtype is nb.DType.bool
+    assert (a + 2.5).dtype is nb.DType.float32
+    b = nb.Tensor.from_torch(torch.tensor([1, 2], dtype=torch.int32))
+    assert (b + 2).dtype is nb.DType.int32 and (b * 2.5).dtype is nb.DType.float32
