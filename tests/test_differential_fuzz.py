@@ -87,3 +87,111 @@ def test_vmapped_chain_matches_per_example_runs_and_forward_matches_reverse(seed
     gs = nb.vmap(nb.grad(scalar), in_axes=in_axes)(T(X), T(yb)).to_numpy()
     g_ref = np.stack([nb.grad(scalar)(T(X[i]), T(second(i))).to_numpy() for i in range(B)])
     np.testing.assert_allclose(gs, g_ref, rtol=2e-3, atol=2e-3, err_msg=what)
+
+
+@pytest.mark.parametrize("seed", range(20))
+def test_compiled_chain_matches_eager_over_repeated_calls(seed):
+    """``compile`` of a random chain (value, gradient, or both; plain or sharded inputs) against eager,
+    three calls with fresh data each: the first records, the others replay."""
+    rng = random.Random(seed)
+    nprng = np.random.RandomState(seed)
+    name, mshape, axes = rng.choice(MESHES)
+    mesh = nb.DeviceMesh(name, mshape, axes)
+    rank = rng.choice([2, 3])
+    shape = tuple(rng.choice([4, 8]) for _ in range(rank))
+    sharded = rng.random() < 0.5
+    specs = [F.rand_spec(rng, shape, mesh) for _ in range(2)]
+    nsteps = rng.randrange(2, 6)
+    chain = F.make_chain(rng.randrange(1 << 30), nsteps)
+
+    def loss(a, b):
+        t = chain(a, b)
+        return nb.reduce_sum(t * t)
+
+    kind = rng.choice(["value", "grad", "both"])
+    fn = {"value": loss, "grad": nb.grad(loss), "both": lambda a, b: (loss(a, b), nb.grad(loss)(a, b))}[kind]
+    cfn = nb.compile(fn)
+    for rep in range(3):
+        xs = [nprng.randn(*shape).astype(np.float32) * 0.5 for _ in range(2)]
+        mk = (lambda: [nb.shard(T(x), mesh, s) for x, s in zip(xs, specs)]) if sharded else (lambda: [T(x) for x in xs])
+        ref, got = fn(*mk()), cfn(*mk())
+        for r, g in zip(ref if isinstance(ref, tuple) else (ref,), got if isinstance(got, tuple) else (got,)):
+            assert (r is None) == (g is None)
+            if r is not None and np.isfinite(r.to_numpy()).all():
+                rn = r.to_numpy()
+                np.testing.assert_allclose(g.to_numpy(), rn, rtol=1e-4, atol=1e-4 * (1 + np.abs(rn).max()),
+                                           err_msg=f"kind={kind} sharded={sharded} rep={rep} ops={chain.ops}")
+    assert cfn.stats.misses == 1
+
+
+def _random_index(rng, shape):
+    idx = []
+    for d in range(rng.randrange(0, len(shape) + 1)):
+        size, k = shape[d], rng.random()
+        if k < 0.35:
+            idx.append(rng.randrange(-size, size))
+        elif k < 0.85:
+            idx.append(slice(rng.choice([None, rng.randrange(-size, size)]), rng.choice([None, rng.randrange(-size, size + 1)])))
+        else:
+            idx.append(slice(None))
+    if rng.random() < 0.2 and len(idx) < len(shape):
+        idx.append(Ellipsis)
+    return tuple(idx)
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_indexing_reads_writes_and_their_gradients_match_numpy(seed):
+    rng = random.Random(seed)
+    nprng = np.random.RandomState(seed)
+    name, mshape, axes = rng.choice(MESHES)
+    mesh = nb.DeviceMesh(name, mshape, axes)
+    shape = tuple(rng.choice([2, 4, 5]) for _ in range(rng.choice([1, 2, 3])))
+    x = nprng.randn(*shape).astype(np.float32)
+    spec = F.rand_spec(rng, shape, mesh)
+    mk = (lambda: nb.shard(T(x), mesh, spec)) if rng.random() < 0.6 else (lambda: T(x))
+    idx = _random_index(rng, shape)
+    ref = x[idx]
+    np.testing.assert_allclose(mk()[idx].to_numpy(), ref, err_msg=str(idx))
+    val = np.asarray(nprng.randn(*ref.shape), dtype=np.float32)
+    want = x.copy()
+    want[idx] = val
+    t = mk()
+    t[idx] = T(val) if val.ndim else float(val)
+    np.testing.assert_allclose(t.to_numpy(), want, err_msg=str(idx))
+    want = x.copy()
+    want[idx] += 2.0
+    np.testing.assert_allclose(mk().at[idx].add(2.0).to_numpy(), want, err_msg=str(idx))
+    g = np.zeros_like(x)
+    g[idx] += 3.0
+    np.testing.assert_allclose(nb.grad(lambda u: nb.reduce_sum(u[idx] * 3.0))(mk()).to_numpy(), g, err_msg=str(idx))
+    rows = nprng.randint(0, shape[0], size=(3,)).astype(np.int32)
+    np.testing.assert_allclose(mk()[T(rows)].to_numpy(), x[rows])
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_broadcasting_binary_ops_and_matmul_on_sharded_operands_match_numpy(seed):
+    rng = random.Random(seed)
+    nprng = np.random.RandomState(seed)
+    name, mshape, axes = rng.choice(MESHES)
+    mesh = nb.DeviceMesh(name, mshape, axes)
+    opn, f, nf = rng.choice([("add", lambda a, b: a + b, np.add), ("mul", lambda a, b: a * b, np.multiply),
+                             ("where", lambda a, b: nb.where(nb.greater(a, b), a, b * 2.0), lambda a, b: np.where(a > b, a, b * 2.0)),
+                             ("matmul", lambda a, b: a @ b, np.matmul)])
+    if opn == "matmul":
+        batch = tuple(rng.choice([1, 2, 4]) for _ in range(rng.choice([0, 1, 2])))
+        m, k, n = rng.choice([2, 4]), rng.choice([2, 4]), rng.choice([2, 4])
+        sa = tuple(rng.choice([d, 1]) for d in batch) + (m, k)
+        sb = tuple(rng.choice([d, 1]) for d in batch)[rng.choice([0, 1]) if batch else 0:] + (k, n)
+    else:
+        full = tuple(rng.choice([1, 2, 4]) for _ in range(rng.choice([1, 2, 3])))
+        sa = tuple(rng.choice([d, 1]) for d in full)[rng.randrange(0, len(full)):]
+        sb = tuple(rng.choice([d, 1]) for d in full)[rng.randrange(0, len(full)):]
+    A, B = nprng.randn(*sa).astype(np.float32), nprng.randn(*sb).astype(np.float32)
+    ref = nf(A, B)
+    what = f"op={opn} sa={sa} sb={sb}"
+    sq = lambda u, v: nb.reduce_sum(f(u, v) * f(u, v))      # noqa: E731
+    g_ref = [g.to_numpy() for g in nb.grad(sq, argnums=(0, 1))(T(A), T(B))]
+    a, b = nb.shard(T(A), mesh, F.rand_spec(rng, sa, mesh)), nb.shard(T(B), mesh, F.rand_spec(rng, sb, mesh))
+    np.testing.assert_allclose(f(a, b).to_numpy(), ref, rtol=1e-4, atol=1e-5, err_msg=what)
+    for g, r in zip(nb.grad(sq, argnums=(0, 1))(a, b), g_ref):
+        np.testing.assert_allclose(g.to_numpy(), r, rtol=1e-3, atol=1e-4, err_msg=what)
