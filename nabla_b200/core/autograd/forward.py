@@ -3,7 +3,7 @@
 
 Walks the nodes in execution order, looks up the tangents of each node's tensor inputs
 (zeros where none flows), and calls ``op.jvp_rule(primals, tangents, outputs, kwargs)``.
-An op without a JVP rule, or one that returns ``None``, contributes a zero tangent.
+An op that returns ``None`` from its rule contributes a zero tangent; one without a rule raises.
 """
 from __future__ import annotations
 
@@ -18,6 +18,25 @@ from ..tensor.impl import TensorImpl
 from .backward import suppress_tracing
 
 
+def _lay_out_like(t: Tensor, primal: TensorImpl) -> Tensor:
+    """An input tangent laid out like its primal (same mesh axes on the same dims, no pending sums;
+    gathered when the primal is not on a mesh). The JVP rules combine tangents with values derived
+    from the primal dim by dim, so the two must be split the same way."""
+    ts, ps = t._impl.sharding, primal.sharding
+    if ts is None and ps is None:
+        return t
+    if ps is None:
+        return t.gather()
+    if t._impl.batch_dims != primal.batch_dims or len(t._impl._shape) != len(primal._shape):
+        return t                      # a basis mapped over extra dims (jacfwd): the rules align those themselves
+    from ...ops.communication import reshard_to_spec
+    from ..sharding.spec import needs_reshard
+
+    want = ps.clone()
+    want.partial_sum_axes = set()
+    return reshard_to_spec(t, want) if ts is None or needs_reshard(ts, want) else t
+
+
 class ForwardEngine:
     def __init__(self, trace: Trace, tangents: Any, *, create_graph: bool = True):
         self.trace = trace
@@ -29,7 +48,7 @@ class ForwardEngine:
             raise ValueError(f"expected {len(ins)} tangents, got {len(tans)}")
         for i, t in zip(ins, tans):
             if t is not None:
-                self.tan[id(i)] = t
+                self.tan[id(i)] = _lay_out_like(t, i) if isinstance(t, Tensor) else t
 
     def run(self) -> None:
         if self.create_graph:

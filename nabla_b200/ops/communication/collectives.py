@@ -291,6 +291,16 @@ class AllReduceOp(_LayoutOp):
             return t
         sp = t._impl.sharding
         ax = set(kwargs["reduce_axes"])
+        if kwargs.get("reduce_op", "sum") != "sum":
+            # the max / min combination that finishes a reduction over a sharded axis. The rule of
+            # that reduction already masks with the extreme over ALL shards, so each device holds
+            # its addend of the tangent: they are summed, whatever the primal's combination was
+            # (the counterpart of the identity this op's VJP applies to the cotangent)
+            if any(set(d.axes) & ax for d in sp.dim_specs):
+                return _all_reduce_op(t, reduce_axes=kwargs["reduce_axes"], reduce_op="sum")
+            spec = sp.clone()
+            spec.partial_sum_axes = set(spec.partial_sum_axes) | ax
+            return _all_reduce_op(relabel_spec(t, spec), reduce_axes=kwargs["reduce_axes"], reduce_op="sum")
         if not (sp.partial_sum_axes & ax) and not any(set(d.axes) & ax for d in sp.dim_specs):
             return t
         return _all_reduce_op(t, **kwargs)

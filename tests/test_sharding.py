@@ -305,3 +305,29 @@ def test_pending_sum_meeting_a_sequence_parallel_residual_becomes_one_reduce_sca
     out = f(x, w, r)
     assert [d.axes for d in out.sharding.dim_specs] == [["tp"], []] and not out.sharding.partial_sum_axes
     np.testing.assert_allclose(out.to_numpy(), np.tanh(X @ W + R), rtol=1e-5, atol=1e-6)
+
+
+def test_forward_mode_on_sharded_operands_with_tangents_laid_out_differently():
+    """Input tangents are laid out like their primals before the rules run, and the tangent of a
+    max / min over a sharded axis is the SUM of the devices' addends (the primal is combined with
+    max): both against the unsharded JVP."""
+    mesh = nb.DeviceMesh("fw", (2, 2), ("a", "b"))
+    rs = np.random.RandomState(0)
+    X, TX = rs.randn(8, 8).astype(np.float32), rs.randn(8, 8).astype(np.float32)
+    mk = lambda v, s: nb.shard(nb.Tensor.from_dlpack(v.copy()), mesh, s)      # noqa: E731
+    for red in (nb.reduce_max, nb.reduce_min):
+        for spec in ((None, "a"), ("a", None), ("b", "a"), (("a", "b"), None)):
+            for axis in (0, 1):
+                f = lambda t: red(t, axis=axis, keepdims=True)      # noqa: E731
+                _, t_ref = nb.jvp(f, (nb.Tensor.from_dlpack(X.copy()),), (nb.Tensor.from_dlpack(TX.copy()),))
+                _, t_got = nb.jvp(f, (mk(X, spec),), (mk(TX, spec),))
+                np.testing.assert_allclose(t_got.to_numpy(), t_ref.to_numpy(), rtol=1e-5, atol=1e-6)
+
+    def g(u, v):
+        return nb.softmax(u @ nb.swap_axes(v, -1, -2), axis=-1) - nb.reduce_max(u, axis=-1, keepdims=True)
+
+    plain = [nb.Tensor.from_dlpack(a.copy()) for a in (X, TX, TX, X)]
+    o_ref, t_ref = nb.jvp(g, (plain[0], plain[1]), (plain[2], plain[3]))
+    o, t = nb.jvp(g, (mk(X, ("b", "a")), mk(TX, (None, None))), (mk(TX, ("a", None)), mk(X, (None, "b"))))
+    np.testing.assert_allclose(o.to_numpy(), o_ref.to_numpy(), rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(t.to_numpy(), t_ref.to_numpy(), rtol=1e-4, atol=1e-5)
