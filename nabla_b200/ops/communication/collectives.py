@@ -373,11 +373,14 @@ class ReduceScatterOp(_LayoutOp):
         return full.narrow(dim, st, ln).contiguous()
 
     def vjp_rule(self, primals, cot, outputs, kwargs):
+        # every addend of the scattered sum receives the cotangent of its slice: the cotangent laid
+        # out like the operand, without the pending sum (a cotangent that is not on a mesh, e.g. a
+        # basis vector of jacrev, is placed on the operand's)
         x = primals[0]
-        g = all_gather(cot, axis=kwargs["dim"] - x._impl.batch_dims) if False else cot
-        want = _spec_of(x, cot._impl.sharding.mesh).clone()
+        mesh = (cot._impl.sharding or x._impl.sharding).mesh
+        want = _spec_of(x, mesh).clone()
         want.partial_sum_axes = set()
-        return (reshard_to_spec(g, want),)
+        return (reshard_to_spec(cot, want),)
 
     def jvp_rule(self, primals, tangents, outputs, kwargs):
         return _reduce_scatter_op(tangents[0], **kwargs)
