@@ -195,3 +195,61 @@ def test_broadcasting_binary_ops_and_matmul_on_sharded_operands_match_numpy(seed
     np.testing.assert_allclose(f(a, b).to_numpy(), ref, rtol=1e-4, atol=1e-5, err_msg=what)
     for g, r in zip(nb.grad(sq, argnums=(0, 1))(a, b), g_ref):
         np.testing.assert_allclose(g.to_numpy(), r, rtol=1e-3, atol=1e-4, err_msg=what)
+
+
+@pytest.mark.parametrize("seed", range(25))
+def test_forward_and_reverse_mode_on_sharded_chains_with_independent_layouts(seed):
+    """``jvp`` with primals and tangents each laid out at random, and ``vjp`` with a randomly laid
+    out cotangent, against the unsharded results."""
+    rng = random.Random(seed)
+    nprng = np.random.RandomState(seed)
+    name, mshape, axes = rng.choice(MESHES)
+    mesh = nb.DeviceMesh(name, mshape, axes)
+    shape = tuple(rng.choice([4, 8]) for _ in range(rng.choice([2, 3])))
+    vals = [nprng.randn(*shape).astype(np.float32) * (0.5 if i < 2 else 1.0) for i in range(4)]
+    specs = [F.rand_spec(rng, shape, mesh) for _ in range(4)]
+    nsteps = rng.randrange(2, 6)
+    chain = F.make_chain(rng.randrange(1 << 30), nsteps)
+    o_ref, t_ref = nb.jvp(chain, (T(vals[0]), T(vals[1])), (T(vals[2]), T(vals[3])))
+    what = f"mesh={name} shape={shape} specs={specs} ops={chain.ops}"
+    sh = [nb.shard(T(v), mesh, s) for v, s in zip(vals, specs)]
+    o, t = nb.jvp(chain, (sh[0], sh[1]), (sh[2], sh[3]))
+    ref = t_ref.to_numpy()
+    if not np.isfinite(ref).all():
+        return
+    np.testing.assert_allclose(o.to_numpy(), o_ref.to_numpy(), rtol=2e-4, atol=2e-4, err_msg=what)
+    np.testing.assert_allclose(t.to_numpy(), ref, rtol=2e-3, atol=2e-3 * (1 + np.abs(ref).max()), err_msg=what)
+    ct = np.asarray(nprng.randn(*o_ref.to_numpy().shape), dtype=np.float32)
+    ct_plain = nb.constant(ct)
+    ct_split = nb.shard(nb.constant(ct), mesh, F.rand_spec(rng, ct.shape, mesh)) if ct.ndim else nb.constant(ct)
+    g_ref = nb.vjp(chain, T(vals[0]), T(vals[1]))[1](ct_plain)
+    g_got = nb.vjp(chain, sh[0], sh[1])[1](ct_split)
+    for a, b in zip(g_ref, g_got):
+        assert (a is None) == (b is None), what
+        if a is not None:
+            an = a.to_numpy()
+            np.testing.assert_allclose(b.to_numpy(), an, rtol=2e-3, atol=2e-3 * (1 + np.abs(an).max()), err_msg=what)
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_jacobians_and_hessians_of_sharded_chains_match_plain_ones(seed):
+    rng = random.Random(seed)
+    nprng = np.random.RandomState(seed)
+    name, mshape, axes = rng.choice([m for m in MESHES if m[0] != "f4"])
+    mesh = nb.DeviceMesh(name, mshape, axes)
+    shape = tuple(rng.choice([2, 4]) for _ in range(rng.choice([1, 2])))
+    x = nprng.randn(*shape).astype(np.float32) * 0.5
+    y = T(nprng.randn(*shape).astype(np.float32) * 0.5)
+    spec = F.rand_spec(rng, shape, mesh)
+    nsteps = rng.randrange(1, 4)
+    chain = F.make_chain(rng.randrange(1 << 30), nsteps)
+    f = lambda a: chain(a, y)                                     # noqa: E731
+    s = lambda a: nb.reduce_sum(nb.tanh(chain(a, y)))            # noqa: E731
+    split = lambda: nb.shard(T(x), mesh, spec)                    # noqa: E731
+    j_ref = nb.jacrev(f)(T(x)).to_numpy()
+    what = f"mesh={name} shape={shape} spec={spec} ops={chain.ops}"
+    for tr in (nb.jacrev, nb.jacfwd):
+        np.testing.assert_allclose(tr(f)(split()).to_numpy(), j_ref, rtol=2e-3, atol=2e-3, err_msg=what)
+    h_ref = nb.jacrev(nb.jacrev(s))(T(x)).to_numpy()
+    for outer, inner in ((nb.jacrev, nb.jacrev), (nb.jacfwd, nb.jacfwd), (nb.jacfwd, nb.jacrev), (nb.jacrev, nb.jacfwd)):
+        np.testing.assert_allclose(outer(inner(s))(split()).to_numpy(), h_ref, rtol=5e-3, atol=5e-3, err_msg=what)
